@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized GEMV hot path: the Q4_K projection sweep over Qwen3-8B
+layer shapes at M = 1 (batch-1 decode), all 36 layers' distinct weights streamed once
+per step, so every step reads 3.9 GB of weights -- far larger than L2.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl nnq|reference]
+
+One JSON line on stdout (rank 0). `value` is algorithmic GB/s of the whole job with
+inputs resident in HBM; `e2e` is the same metric through the host entry point of the
+C ABI (host activations in, host outputs out, copies inside the timed region);
+`cpu_baseline` is the CPU oracle (a port of the reference's CPU path) on a bounded
+sample; `--impl reference` times that CPU path alone with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "quant_gemv_hbm_gbs"
+UNIT = "GB/s"
+WORKLOAD = "q4_k_projection_sweep_qwen3_8b_m1"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    BAD = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown"}
+    NOTE = {0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in {**self.BAD, **self.NOTE}.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------- #
+# CPU baseline / reference arm
+# --------------------------------------------------------------------------- #
+
+def cpu_sample(threads: int, reps: int, seed: int = 0x5EED):
+    """One decoder layer's seven Q4_K projections at M = 1 through the CPU oracle
+    (dequantize the whole weight, then the nn-cpu row dot): returns (GB/s, seconds/rep)."""
+    import numpy as np
+    from nn_b200 import formats as F
+    from nn_b200 import workload as W
+    from oracle import cpu as orc
+    orc.build()
+    ws, xs, scratch = [], {}, None
+    for i, (name, n, k) in enumerate(W.PROJECTIONS):
+        ws.append((n, k, W.gen_q4_k_host(seed + i, n, k)))
+        if k not in xs:
+            xs[k] = F.gen_activations(seed + 100 + k, 1, k, bf16=True)
+    scratch = np.empty(max(n * k for n, k, _ in ws), np.float32)
+    algo = W.layer_bytes(1).algorithmic
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for n, k, w in ws:
+            orc.cpu_forward(F.QuantFormat.Q4_K, w, xs[k], None, 1, n, k, threads=threads, scratch=scratch)
+        dt = time.perf_counter() - t0
+        best = dt if best is None or dt < best else best
+    return algo / best / 1e9, best
+
+
+def run_reference(args, rank):
+    """Reference arm: the reference's CPU implementation of the path (restated in C, since
+    the Rust workspace cannot be built here), all host threads, one layer per step."""
+    if rank != 0:
+        return
+    import numpy as np
+    from nn_b200 import formats as F
+    from nn_b200 import workload as W
+    from oracle import cpu as orc
+    orc.build()
+    threads = os.cpu_count() or 1
+    seed = 0x5EED
+    ws, xs = [], {}
+    for i, (name, n, k) in enumerate(W.PROJECTIONS):
+        ws.append((n, k, W.gen_q4_k_host(seed + i, n, k)))
+        if k not in xs:
+            xs[k] = F.gen_activations(seed + 100 + k, 1, k, bf16=True)
+    scratch = np.empty(max(n * k for n, k, _ in ws), np.float32)
+    algo = W.layer_bytes(1).algorithmic
+
+    def step():
+        for n, k, w in ws:
+            orc.cpu_forward(F.QuantFormat.Q4_K, w, xs[k], None, 1, n, k, threads=threads, scratch=scratch)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = algo / dt / 1e9
+    sample = "one layer (7 projections, 108.5 MB of Q4_K) per step: dequantize whole weight + nn-cpu row dot"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "m": 1, "layers_per_step": 1, "format": "Q4_K"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+# --------------------------------------------------------------------------- #
+# GPU arm
+# --------------------------------------------------------------------------- #
+
+def run_nnq(args, rank, world, local_rank):
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+
+    from nn_b200 import api
+    from nn_b200 import workload as W
+    from nn_b200.formats import QuantFormat
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    backend = api.Backend(local_rank)
+    api.register_gpu_backend(backend)
+    lib, ctx = backend._lib, backend._ctx
+    m = args.m
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0x5EED)  # same weights on every rank, each keeps its shard
+
+    # ---- weights: `layers` distinct layers, tensor-parallel shards when world > 1 ----
+    layers = []
+    for li in range(args.layers):
+        lw = {}
+        for name, n, k in W.PROJECTIONS:
+            raw = W.gen_q4_k_device(torch, gen, n, k)
+            shard = (W.TP_AXIS[name], rank, world) if world > 1 else None
+            lw[name] = api.DeviceWeight.from_device(backend, QuantFormat.Q4_K, raw, n, k, shard=shard)
+            del raw
+        layers.append(lw)
+    torch.cuda.synchronize()
+
+    # ---- activations / outputs (bf16), one set per layer ----
+    def shard_k(name, k):
+        return k // world if W.TP_AXIS[name] == 1 else k
+
+    xs, ys = [], []
+    for li in range(args.layers):
+        xg, yg = {}, {}
+        for group in W.GROUPS:
+            k = shard_k(group[0], dict((p[0], p[2]) for p in W.PROJECTIONS)[group[0]])
+            x = torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16)
+            for name in group:
+                xg[name] = x
+                yg[name] = torch.empty(m, layers[li][name].shape[0], dtype=torch.bfloat16, device=dev)
+        xs.append(xg)
+        ys.append(yg)
+
+    VP = ctypes.c_void_p
+    calls = []  # prebuilt ctypes argument packs: one nnq_linear_batch call per group
+    for li in range(args.layers):
+        for group in W.GROUPS:
+            cnt = len(group)
+            wh = (VP * cnt)(*[layers[li][n_].handle().value for n_ in group])
+            xp = (VP * cnt)(*[xs[li][n_].data_ptr() for n_ in group])
+            yp = (VP * cnt)(*[ys[li][n_].data_ptr() for n_ in group])
+            reduce_out = ys[li][group[0]] if (world > 1 and W.TP_AXIS[group[0]] == 1) else None
+            calls.append((cnt, wh, xp, yp, reduce_out))
+    launches_per_step = len(calls)
+
+    def step(stream_ptr):
+        for cnt, wh, xp, yp, reduce_out in calls:
+            st = lib.nnq_linear_batch(ctx, cnt, wh, xp, api.BF16, m, None, yp, api.BF16, stream_ptr)
+            if st != 0:
+                backend.check(st)
+            if reduce_out is not None:
+                dist.all_reduce(reduce_out)  # row-parallel partial sums (o_proj, down_proj)
+
+    stream = torch.cuda.Stream(device=dev)
+    graph = None
+    with torch.cuda.stream(stream):
+        sp = VP(stream.cuda_stream)
+        for _ in range(2):
+            step(sp)
+        stream.synchronize()
+        backend.device_status(stream)
+        if not args.no_graph and (world == 1 or args.graph_tp):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step(VP(torch.cuda.current_stream().cuda_stream))
+
+        def run_step():
+            if graph is not None:
+                graph.replay()
+            else:
+                step(sp)
+
+        def fence():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+                torch.cuda.synchronize()
+
+        for _ in range(args.warmup):
+            run_step()
+        fence()
+        launches_before = backend.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            e0.record(stream)
+            for _ in range(args.steps):
+                run_step()
+            e1.record(stream)
+            fence()
+        ms = e0.elapsed_time(e1)
+    backend.device_status(stream)
+    launched = backend.launch_count() - launches_before
+    if graph is not None:
+        launched = launches_per_step * args.steps  # replays re-issue the captured kernels
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+
+    per_layer = W.layer_bytes(m)
+    algo_step = per_layer.algorithmic * args.layers          # whole job, all ranks
+    value = algo_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel (the only kernel in the step) ----
+    peak, peak_kind = _peaks()
+    per_gpu_bytes_per_launch = algo_step / world / launches_per_step
+    per_launch_s = ms_per_step * 1e-3 / launches_per_step
+    achieved = per_gpu_bytes_per_launch / per_launch_s / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": f"of {peak_kind}", "frac_of_nominal_8000": achieved / 8000.0,
+                "traffic": None, "kernel": "skinny/generic quantized GEMV",
+                "bytes_per_launch": per_gpu_bytes_per_launch, "us_per_launch": per_launch_s * 1e6}
+
+    # ---- end to end through the host entry point of the C ABI ----
+    e2e = None
+    if world == 1 and not args.no_e2e:
+        proj = {p[0]: p for p in W.PROJECTIONS}
+        hx = {k: torch.randn(m, k).to(torch.bfloat16).pin_memory() for k in (W.HIDDEN, W.FFN)}
+        hy = {n: torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for n in (W.HIDDEN, W.KV_DIM, W.FFN)}
+        h2d = d2h = 0
+
+        def host_step():
+            nonlocal h2d, d2h
+            h2d = d2h = 0
+            for li in range(args.layers):
+                for name, n, k in W.PROJECTIONS:
+                    st = lib.nnq_linear_host(ctx, layers[li][name].handle(), hx[k].data_ptr(), api.BF16, m, None,
+                                             hy[n].data_ptr(), api.BF16)
+                    if st != 0:
+                        backend.check(st)
+                    h2d += m * k * 2
+                    d2h += m * n * 2
+
+        host_step()
+        e_steps = max(1, min(args.steps, 5))
+        t0 = time.perf_counter()
+        for _ in range(e_steps):
+            host_step()
+        dt = (time.perf_counter() - t0) / e_steps
+        e2e = {"value": algo_step / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": dt * 1e3, "calls_per_step": args.layers * len(W.PROJECTIONS),
+               "api": "nnq_linear_host (pinned host activations in, host outputs out, per projection)"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v1, s1 = cpu_sample(1, 2)
+        cores = os.cpu_count() or 1
+        vN, sN = cpu_sample(cores, 3)
+        cpu = {"value": v1, "unit": UNIT, "cores": 1, "kind": "port",
+               "sample": "one layer (7 Q4_K projections, 108.5 MB) at M=1: dequantize whole weight + nn-cpu row "
+                         "dot, best of 2; the reference path is single-threaded",
+               "seconds_per_layer": s1,
+               "all_cores": {"value": vN, "cores": cores, "seconds_per_layer": sN}}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "m": m, "layers": args.layers, "format": "Q4_K",
+                       "activations": "bf16", "outputs": "bf16", "accumulate": "f32",
+                       "parallelism": f"tp{world}" if world > 1 else "single",
+                       "weight_bytes_per_step": per_layer.weights * args.layers * world // world,
+                       "l2_policy": "inputs larger than L2 (every step streams all layers' distinct weights)",
+                       "cuda_graph": graph is not None,
+                       "tokens_per_s_equiv": 1e3 / ms_per_step * (36 / args.layers)},
+            "roofline": roofline, "clocks": clocks.summary(), "gpu_launches": int(launched),
+            "e2e": e2e, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="nnq", choices=["nnq", "reference"])
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--graph-tp", action="store_true", help="capture the tensor-parallel step (with its all-reduces) in a CUDA graph")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    run_nnq(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

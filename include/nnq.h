@@ -1,0 +1,220 @@
+/*
+ * nnq.h -- C ABI of libnnq_b200: block-quantized weight x activation products on
+ * NVIDIA B200 (sm_100a), behind the seams the alabsystems/nn reference exposes for
+ * this path. Each entry point names the reference interface it replaces (paths are
+ * relative to the reference repository root). A Rust shim implementing
+ * `GpuBackend::matmul` / `quantized_linear` binds exactly these symbols.
+ *
+ * Conventions
+ *   - Plain C types only. Device pointers are CUDA device addresses; `stream` is a
+ *     cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Every call returns an nnq_status. Nothing throws, aborts or traps the device;
+ *     nnq_last_error(ctx) gives the message of the last failing call on that context.
+ *   - Weights are [N, K] = [out_features, in_features], row-major, quantization blocks
+ *     running along K and never crossing a row, exactly as the reference stores them
+ *     (crates/nn-core/src/dyn_tensor/quantized_matmul.rs:198-203).
+ *   - The library owns nnq_weight objects (a device copy, possibly re-tiled for the
+ *     kernels; the byte count is preserved). The caller owns activation / output
+ *     buffers and the stream.
+ *   - A context is bound to one device. Calls on one context from several host threads
+ *     must be serialised by the caller; distinct contexts are independent.
+ */
+#ifndef NNQ_H
+#define NNQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define NNQ_API __attribute__((visibility("default")))
+#else
+#define NNQ_API
+#endif
+
+#define NNQ_VERSION_MAJOR 0
+#define NNQ_VERSION_MINOR 1
+
+typedef struct nnq_ctx nnq_ctx;
+typedef struct nnq_weight nnq_weight;
+
+/* Status codes. The first group mirrors QuantizedMatmulError
+ * (crates/nn-core/src/dyn_tensor/quantized_matmul.rs:30-76) and the storage
+ * validation errors of QuantizedStorage::new
+ * (crates/nn-core/src/dyn_tensor/quantized.rs:118-139); the second group mirrors
+ * BackendErrorKind (crates/nn-core/src/error.rs:48-93). */
+typedef enum nnq_status {
+    NNQ_OK = 0,
+    NNQ_ERR_INVALID_ARG = 1,      /* null pointer, negative size, unknown enum value      */
+    NNQ_ERR_NOT_QUANTIZED = 2,    /* QuantizedMatmulError::NotQuantized                    */
+    NNQ_ERR_WRONG_QUANT_TYPE = 3, /* QuantizedMatmulError::WrongQuantType                  */
+    NNQ_ERR_SHAPE_MISMATCH = 4,   /* QuantizedMatmulError::ShapeMismatch (input K != W K)  */
+    NNQ_ERR_WEIGHT_RANK = 5,      /* QuantizedMatmulError::WeightRank                      */
+    NNQ_ERR_BIAS_MISMATCH = 6,    /* QuantizedMatmulError::BiasMismatch                    */
+    NNQ_ERR_INVALID_SHAPE = 7,    /* TensorError::InvalidShape: elements % block != 0      */
+    NNQ_ERR_DATA_LENGTH = 8,      /* TensorError::DataLengthMismatch: bytes != blocks*size */
+    NNQ_ERR_RANK_MISMATCH = 9,    /* TensorError::RankMismatch: input rank < 2             */
+    NNQ_ERR_UNSUPPORTED = 10,     /* TensorError::Unsupported                              */
+    NNQ_ERR_OUT_OF_MEMORY = 20,   /* BackendErrorKind::OutOfMemory                         */
+    NNQ_ERR_DISPATCH_FAILED = 21, /* BackendErrorKind::DispatchFailed (launch / CUDA error)*/
+    NNQ_ERR_TIMEOUT = 22,         /* BackendErrorKind::Timeout (a bounded device wait ran out) */
+    NNQ_ERR_NO_DEVICE = 23,       /* no CUDA device / not an sm_100 device                 */
+    NNQ_ERR_OTHER = 24            /* BackendErrorKind::Other                               */
+} nnq_status;
+
+/* Weight formats. Q4_0/Q4_1/Q8_0 are nn-core's QuantType
+ * (crates/nn-core/src/dyn_tensor/quantized.rs:28-56); Q4_K/Q6_K are the nn-gguf block
+ * layouts (crates/nn-gguf/src/dequant.rs:335-398,415-459); Q4_K_GGML is nn-core's
+ * BlockQ4K decode of the same 144-byte block
+ * (crates/nn-core/src/layers/quantized/linear.rs:63-92); the MXFP4 variants are
+ * nn-core's Mxfp4Block (mxfp4.rs:73-78), the [N,K/2]+[N,K/32] buffers of the
+ * reference's GPU kernel contract (crates/nn-metal/src/mxfp4_gemm_msl.rs:47-61) and
+ * nn-gptoss's Mxfp4Tensor (crates/nn-gptoss/src/quantize.rs:55-62). */
+typedef enum nnq_format {
+    NNQ_Q4_0 = 0,
+    NNQ_Q4_1 = 1,
+    NNQ_Q8_0 = 2,
+    NNQ_Q4_K = 3,
+    NNQ_Q4_K_GGML = 4,
+    NNQ_Q6_K = 5,
+    NNQ_MXFP4_CORE = 6,
+    NNQ_MXFP4_SPLIT = 7,
+    NNQ_MXFP4_GPTOSS = 8,
+    NNQ_FORMAT_COUNT = 9
+} nnq_format;
+
+typedef enum nnq_dtype { NNQ_F32 = 0, NNQ_BF16 = 1 } nnq_dtype;
+
+/* Kernel selection for nnq_linear. AUTO picks per shape: M <= 16 the dequant-fused
+ * skinny kernel, larger M the tensor-core tile pipeline. The other values force one
+ * path (tests and measurements use them). */
+typedef enum nnq_path {
+    NNQ_PATH_AUTO = 0,
+    NNQ_PATH_GENERIC = 1, /* portable dequant-fused row kernel on the raw block layout */
+    NNQ_PATH_SKINNY = 2,  /* M <= 16: tiled layout, mma-based streaming kernel           */
+    NNQ_PATH_TENSOR = 3   /* M >= 128: TMA + tcgen05/TMEM tile pipeline                  */
+} nnq_path;
+
+/* ---- library / context ---------------------------------------------------------- */
+
+/* Library version as major*1000 + minor. */
+NNQ_API int nnq_version(void);
+
+/* Human-readable name of a status code (static string). */
+NNQ_API const char *nnq_status_str(nnq_status s);
+
+/* Block geometry of a format: weights per block, bytes per block in the main buffer,
+ * bytes per block in the separate scale buffer (non-zero only for the split MXFP4
+ * layouts). Replaces GgufDType::{block_size,type_size}
+ * (crates/nn-gguf/src/dequant.rs:84-114) and QuantType::{block_size,block_bytes}
+ * (crates/nn-core/src/dyn_tensor/quantized.rs:58-76). */
+NNQ_API nnq_status nnq_format_geometry(nnq_format fmt, int *block_elems, int *block_bytes,
+                               int *scale_bytes);
+
+/* Create / destroy a context on CUDA device `device`. Replaces
+ * init_cuda_runtime(device_ordinal) (crates/nn-cuda/src/dyn_tensor_cuda.rs:117) and
+ * the backend registration of crates/nn-core/src/dyn_tensor/gpu.rs:156-162. */
+NNQ_API nnq_status nnq_init(int device, nnq_ctx **out);
+NNQ_API void nnq_destroy(nnq_ctx *ctx);
+
+/* Message of the last failing call on this context ("" if none). */
+NNQ_API const char *nnq_last_error(const nnq_ctx *ctx);
+
+/* Force a kernel path for subsequent nnq_linear calls on this context. */
+NNQ_API nnq_status nnq_set_path(nnq_ctx *ctx, nnq_path path);
+
+/* Reads and clears the device-side status word that kernels set when a bounded wait
+ * runs out or an internal check fails. Synchronises `stream`. NNQ_OK when clear. */
+NNQ_API nnq_status nnq_device_status(nnq_ctx *ctx, void *stream);
+
+/* ---- weights --------------------------------------------------------------------- */
+
+/* Wrap raw quantized blocks of an [N, K] weight. `data` (and `scales` for the split
+ * MXFP4 layouts, else NULL/0) may be host or device memory; the bytes are copied.
+ * Validation follows QuantizedStorage::new: N*K must be a multiple of the block size
+ * (NNQ_ERR_INVALID_SHAPE), K must be a multiple of it too so that blocks do not cross
+ * rows, and nbytes must equal blocks * block_bytes (NNQ_ERR_DATA_LENGTH).
+ * Replaces DynTensor::from_quantized (crates/nn-core/src/dyn_tensor/quantized.rs:270)
+ * plus GpuBackend::to_gpu (crates/nn-core/src/dyn_tensor/gpu.rs:46-139). */
+NNQ_API nnq_status nnq_weight_create(nnq_ctx *ctx, nnq_format fmt, const void *data, size_t nbytes,
+                             const void *scales, size_t scales_nbytes, int64_t n, int64_t k,
+                             nnq_weight **out);
+
+/* Tensor-parallel shard of an [N, K] weight given as raw bytes (host or device).
+ * axis 0 (column-parallel): rows [rank*N/world, (rank+1)*N/world).
+ * axis 1 (row-parallel): whole blocks [rank*KB/world, (rank+1)*KB/world) of every row,
+ * KB = K / block size, gathered into a contiguous [N, K/world] weight.
+ * The split must be even, else NNQ_ERR_INVALID_SHAPE. No counterpart in the reference,
+ * which runs on one device. */
+NNQ_API nnq_status nnq_weight_create_shard(nnq_ctx *ctx, nnq_format fmt, const void *data, size_t nbytes,
+                                   const void *scales, size_t scales_nbytes, int64_t n,
+                                   int64_t k, int axis, int rank, int world, nnq_weight **out);
+
+NNQ_API void nnq_weight_destroy(nnq_weight *w);
+
+/* Shape, format and stored byte counts of a weight (any out pointer may be NULL). */
+NNQ_API nnq_status nnq_weight_info(const nnq_weight *w, nnq_format *fmt, int64_t *n, int64_t *k,
+                           size_t *nbytes, size_t *scales_nbytes);
+
+/* ---- dequantization (bit-exact gate) ---------------------------------------------- */
+
+/* Dequantize a weight to f32 [N, K] on the device. Bit-identical to the reference's
+ * CPU decoders. Replaces DynTensor::dequantize
+ * (crates/nn-core/src/dyn_tensor/quantized.rs:285-294) and QLinear::dequantize
+ * (crates/nn-core/src/layers/quantized/linear.rs:345-353). */
+NNQ_API nnq_status nnq_dequantize(nnq_ctx *ctx, const nnq_weight *w, float *dst_dev, void *stream);
+
+/* Dequantize raw blocks resident on the device: `num_elements` values from `nbytes`
+ * bytes; as in the reference a short buffer decodes only the whole blocks present.
+ * *decoded (optional) receives the number of values written. Replaces
+ * dequantize_q8_0 / dequantize_q4_k / dequantize_q6_k and the dtype dispatch of
+ * GgufFile::read_tensor_f32 (crates/nn-gguf/src/dequant.rs:123-139,178-196,335-398,
+ * 415-459; crates/nn-gguf/src/reader.rs:253-284), Mxfp4 dequantize_tensor
+ * (crates/nn-core/src/layers/quantized/mxfp4.rs:335-348) and Mxfp4Tensor::dequantize
+ * (crates/nn-gptoss/src/quantize.rs:167-188). */
+NNQ_API nnq_status nnq_dequantize_raw(nnq_ctx *ctx, nnq_format fmt, const void *src_dev, size_t nbytes,
+                              const void *scales_dev, size_t scales_nbytes, int64_t num_elements,
+                              float *dst_dev, int64_t *decoded, void *stream);
+
+/* ---- the product ------------------------------------------------------------------ */
+
+/* y[M, N] = x[M, K] * W^T (+ bias[N]); x and y on the device, contiguous, row-major;
+ * x_dt / y_dt in {F32, BF16}; accumulation in f32. M = product of all leading
+ * dimensions of the reference's [.., M, K] input. bias may be NULL.
+ * Replaces quantized_matmul_q4_0 / quantized_matmul_q8_0 / quantized_linear
+ * (crates/nn-core/src/dyn_tensor/quantized_matmul.rs:296,335,367), QLinear::forward
+ * (crates/nn-core/src/layers/quantized/linear.rs:366-399), the quantized branch of
+ * DynTensor::matmul (crates/nn-core/src/dyn_tensor/ops/mod.rs:284-297) with
+ * GpuBackend::matmul (crates/nn-core/src/dyn_tensor/gpu.rs:76), and the MXFP4 linear
+ * kernel contract (crates/nn-metal/src/compiled_model_kernel_spec_mxfp4.rs:76-104). */
+NNQ_API nnq_status nnq_linear(nnq_ctx *ctx, const nnq_weight *w, const void *x_dev, nnq_dtype x_dt,
+                      int64_t m, const float *bias_dev, void *y_dev, nnq_dtype y_dt,
+                      void *stream);
+
+/* Same product with HOST activations and outputs: copies x (and bias) in, runs
+ * nnq_linear, copies y out and synchronises. This is the shape of the reference's own
+ * call, whose DynTensors live in host memory (quantized_linear(&input, &weight, bias)).
+ * Staging buffers are owned by the context and grow on demand. */
+NNQ_API nnq_status nnq_linear_host(nnq_ctx *ctx, const nnq_weight *w, const void *x_host, nnq_dtype x_dt,
+                           int64_t m, const float *bias_host, void *y_host, nnq_dtype y_dt);
+
+/* Several products in one call: for i in [0, count): y[i] = x[i] * W[i]^T (+ bias[i]),
+ * every x[i] with the same M and dtype. Pointer arrays live in host memory. Used for
+ * the q/k/v and gate/up groups of a decoder layer and for per-expert products.
+ * Replaces the consecutive Linear::forward calls of
+ * crates/nn-qwen3/src/layers.rs:40-47,94-167. */
+NNQ_API nnq_status nnq_linear_batch(nnq_ctx *ctx, int count, const nnq_weight *const *w,
+                            const void *const *x_dev, nnq_dtype x_dt, int64_t m,
+                            const float *const *bias_dev, void *const *y_dev, nnq_dtype y_dt,
+                            void *stream);
+
+/* Number of kernels this library has launched on this context since creation. */
+NNQ_API int64_t nnq_launch_count(const nnq_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNQ_H */

@@ -1,0 +1,67 @@
+"""ctypes binding of libnnq_b200.so (the C ABI declared in include/nnq.h).
+
+The library is the product; there is no fallback. If the shared object is missing and
+cannot be built, or a GPU call is made without a usable device, this raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+_lib = None
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_int64 = ctypes.c_int64
+c_size_t = ctypes.c_size_t
+
+# symbol -> (restype, argtypes); kept in step with include/nnq.h (tests/test_abi.py checks it)
+SIGNATURES = {
+    "nnq_version": (c_int, []),
+    "nnq_status_str": (ctypes.c_char_p, [c_int]),
+    "nnq_format_geometry": (c_int, [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
+    "nnq_init": (c_int, [c_int, ctypes.POINTER(c_void_p)]),
+    "nnq_destroy": (None, [c_void_p]),
+    "nnq_last_error": (ctypes.c_char_p, [c_void_p]),
+    "nnq_set_path": (c_int, [c_void_p, c_int]),
+    "nnq_device_status": (c_int, [c_void_p, c_void_p]),
+    "nnq_weight_create": (c_int, [c_void_p, c_int, c_void_p, c_size_t, c_void_p, c_size_t, c_int64, c_int64,
+                                  ctypes.POINTER(c_void_p)]),
+    "nnq_weight_create_shard": (c_int, [c_void_p, c_int, c_void_p, c_size_t, c_void_p, c_size_t, c_int64, c_int64,
+                                        c_int, c_int, c_int, ctypes.POINTER(c_void_p)]),
+    "nnq_weight_destroy": (None, [c_void_p]),
+    "nnq_weight_info": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int64), ctypes.POINTER(c_int64),
+                                ctypes.POINTER(c_size_t), ctypes.POINTER(c_size_t)]),
+    "nnq_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nnq_dequantize_raw": (c_int, [c_void_p, c_int, c_void_p, c_size_t, c_void_p, c_size_t, c_int64, c_void_p,
+                                   ctypes.POINTER(c_int64), c_void_p]),
+    "nnq_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
+    "nnq_linear_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int]),
+    "nnq_linear_batch": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int64,
+                                 ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_void_p]),
+    "nnq_launch_count": (c_int64, [c_void_p]),
+}
+
+
+def path() -> str:
+    return _build.LIB
+
+
+def load():
+    """Load (building first if the sources are newer) and type the C ABI."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if _build.stale():
+        _build.build()
+    if not os.path.exists(_build.LIB):
+        raise RuntimeError(f"{_build.LIB} is missing and could not be built")
+    lib = ctypes.CDLL(_build.LIB)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,221 @@
+// Device-side block decoders on the RAW reference layouts. Every function decodes 32
+// consecutive weights (one "chunk": flat elements [32c, 32c+32)) to f32, bit-identically
+// to the reference's CPU decoders. Multiplications and subtractions use the explicit
+// round-to-nearest intrinsics so that the compiler can never fuse them.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "nnq_internal.h"
+
+namespace nnq {
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
+    return __half2float(__ushort_as_half(h));  // exact IEEE widening
+}
+
+__device__ __forceinline__ uint16_t ld_u16(const uint8_t *p) {
+    return (uint16_t)(__ldg(p) | ((uint16_t)__ldg(p + 1) << 8));
+}
+
+// E2M1 magnitude for code&7 as f32 bits: 0, .5, 1, 1.5, 2, 3, 4, 6
+__device__ __forceinline__ float e2m1_value(uint32_t code, float scale) {
+    // magnitude m = code&7: m==0 -> 0; m==1 -> 0.5; else (1 + (m&1)/2) * 2^((m>>1)-1)
+    uint32_t m = code & 7u;
+    uint32_t bits = m == 0 ? 0u : (m == 1 ? 0x3F000000u : (((m >> 1) + 126u) << 23) | ((m & 1u) << 22));
+    float v = __fmul_rn(__uint_as_float(bits), scale);
+    return __uint_as_float(__float_as_uint(v) ^ ((code & 8u) << 28));
+}
+
+// nn-core / GPU-contract scale: 2^(e-127), e = 0 -> the f32 subnormal 2^-127, e = 255 -> +inf
+__device__ __forceinline__ float mx_scale_core(uint32_t e) {
+    return __uint_as_float(e ? (e << 23) : 0x00400000u);
+}
+// nn-gptoss scale: e = 0 -> 2^-126
+__device__ __forceinline__ float mx_scale_gptoss(uint32_t e) {
+    return __uint_as_float(e ? (e << 23) : 0x00800000u);
+}
+
+template <int FMT>
+struct Decode;
+
+template <>
+struct Decode<NNQ_Q4_0> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + c * 18;
+        float d = f16_bits_to_f32(ld_u16(b));
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            uint32_t q = __ldg(b + 2 + j);
+            o[2 * j] = __fmul_rn(d, (float)((int)(q & 15u) - 8));
+            o[2 * j + 1] = __fmul_rn(d, (float)((int)(q >> 4) - 8));
+        }
+    }
+};
+
+template <>
+struct Decode<NNQ_Q4_1> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + c * 20;
+        float d = f16_bits_to_f32(ld_u16(b));
+        float m = f16_bits_to_f32(ld_u16(b + 2));
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            uint32_t q = __ldg(b + 4 + j);
+            o[2 * j] = __fadd_rn(__fmul_rn(d, (float)(q & 15u)), m);
+            o[2 * j + 1] = __fadd_rn(__fmul_rn(d, (float)(q >> 4)), m);
+        }
+    }
+};
+
+template <>
+struct Decode<NNQ_Q8_0> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + c * 34;
+        float d = f16_bits_to_f32(ld_u16(b));
+#pragma unroll
+        for (int j = 0; j < 32; j++) o[j] = __fmul_rn(d, (float)(int8_t)__ldg(b + 2 + j));
+    }
+};
+
+template <>
+struct Decode<NNQ_Q4_K> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + (c >> 3) * 144;  // 144-byte blocks are 16-byte aligned
+        int j = (int)(c & 7);
+        uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+        float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
+        float dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
+        // S[0..3] = hdr.y bytes, S[4..7] = hdr.z bytes, S[8..11] = hdr.w bytes
+        uint32_t sc = ((hdr.y >> (8 * (j >> 1) + 4 * (j & 1))) & 15u) |
+                      (((hdr.w >> (8 * (j >> 2) + 2 * (j & 3))) & 3u) << 4);
+        uint32_t mn = ((hdr.z >> (8 * (j >> 1) + 4 * (j & 1))) & 15u) |
+                      (((hdr.w >> (16 + 8 * (j >> 2) + 2 * (j & 3))) & 3u) << 4);
+        float s = __fmul_rn(d, (float)sc);
+        float m = __fmul_rn(dmin, (float)mn);
+        uint4 q = __ldg(reinterpret_cast<const uint4 *>(b + 16 + 16 * j));
+        uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t byte = (qw[v] >> (8 * i)) & 0xFFu;
+                o[8 * v + 2 * i] = __fsub_rn(__fmul_rn(s, (float)(byte & 15u)), m);
+                o[8 * v + 2 * i + 1] = __fsub_rn(__fmul_rn(s, (float)(byte >> 4)), m);
+            }
+        }
+    }
+};
+
+template <>
+struct Decode<NNQ_Q4_K_GGML> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + (c >> 3) * 144;
+        int j = (int)(c & 7);  // sub-block: group g = j/2, low nibbles when j even
+        uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+        float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
+        float dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
+        uint32_t S[3] = {hdr.y, hdr.z, hdr.w};
+        auto sbyte = [&](int i) -> uint32_t { return (S[i >> 2] >> (8 * (i & 3))) & 0xFFu; };
+        uint32_t sc, mn;
+        if (j < 4) {
+            sc = sbyte(j) & 63u;
+            mn = sbyte(j + 4) & 63u;
+        } else {
+            sc = (sbyte(j + 4) & 15u) | ((sbyte(j - 4) >> 6) << 4);
+            mn = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4);
+        }
+        float s = __fmul_rn(d, (float)sc);
+        float m = __fmul_rn(dmin, (float)mn);
+        const uint4 *qp = reinterpret_cast<const uint4 *>(b + 16 + 32 * (j >> 1));
+        int sh = 4 * (j & 1);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint4 q = __ldg(qp + h);
+            uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int v = 0; v < 4; v++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    uint32_t nib = (qw[v] >> (8 * i + sh)) & 15u;
+                    o[16 * h + 4 * v + i] = __fsub_rn(__fmul_rn(s, (float)nib), m);
+                }
+        }
+    }
+};
+
+template <>
+struct Decode<NNQ_Q6_K> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + (c >> 3) * 210;  // only 2-byte aligned: byte loads
+        int idx0 = (int)(c & 7) * 32;
+        float d = f16_bits_to_f32(ld_u16(b + 208));
+        float s0 = __fmul_rn(d, (float)(int8_t)__ldg(b + 192 + idx0 / 16));
+        float s1 = __fmul_rn(d, (float)(int8_t)__ldg(b + 192 + idx0 / 16 + 1));
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            uint32_t qh = __ldg(b + 128 + idx0 / 4 + i);
+            uint32_t ql0 = __ldg(b + idx0 / 2 + 2 * i);
+            uint32_t ql1 = __ldg(b + idx0 / 2 + 2 * i + 1);
+            float s = i < 4 ? s0 : s1;
+            int q0 = (int)((ql0 & 15u) | (((qh >> 0) & 3u) << 4)) - 32;
+            int q1 = (int)((ql0 >> 4) | (((qh >> 2) & 3u) << 4)) - 32;
+            int q2 = (int)((ql1 & 15u) | (((qh >> 4) & 3u) << 4)) - 32;
+            int q3 = (int)((ql1 >> 4) | (((qh >> 6) & 3u) << 4)) - 32;
+            o[4 * i + 0] = __fmul_rn(s, (float)q0);
+            o[4 * i + 1] = __fmul_rn(s, (float)q1);
+            o[4 * i + 2] = __fmul_rn(s, (float)q2);
+            o[4 * i + 3] = __fmul_rn(s, (float)q3);
+        }
+    }
+};
+
+template <>
+struct Decode<NNQ_MXFP4_CORE> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + c * 17;
+        float scale = mx_scale_core(__ldg(b));
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            uint32_t q = __ldg(b + 1 + j);
+            o[2 * j] = e2m1_value(q & 15u, scale);
+            o[2 * j + 1] = e2m1_value(q >> 4, scale);
+        }
+    }
+};
+
+template <>
+struct Decode<NNQ_MXFP4_SPLIT> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *sc, int64_t c, float *o) {
+        float scale = mx_scale_core(__ldg(sc + c));
+        uint4 q = __ldg(reinterpret_cast<const uint4 *>(w + c * 16));
+        uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int v = 0; v < 4; v++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t byte = (qw[v] >> (8 * i)) & 0xFFu;
+                o[8 * v + 2 * i] = e2m1_value(byte & 15u, scale);
+                o[8 * v + 2 * i + 1] = e2m1_value(byte >> 4, scale);
+            }
+    }
+};
+
+template <>
+struct Decode<NNQ_MXFP4_GPTOSS> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *sc, int64_t c, float *o) {
+        float scale = mx_scale_gptoss(__ldg(sc + c));
+        uint4 q = __ldg(reinterpret_cast<const uint4 *>(w + c * 16));
+        uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int v = 0; v < 4; v++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t byte = (qw[v] >> (8 * i)) & 0xFFu;
+                o[8 * v + 2 * i] = e2m1_value(byte >> 4, scale);      // high nibble = even element
+                o[8 * v + 2 * i + 1] = e2m1_value(byte & 15u, scale);
+            }
+    }
+};
+
+}  // namespace nnq

@@ -1,0 +1,27 @@
+// Skinny (M <= 16) streaming kernels on the tiled weight layout.
+#pragma once
+#include "nnq_internal.h"
+
+namespace nnq {
+
+constexpr int kSkinnyMaxJobs = 8;
+constexpr int kSkinnyMaxM = 16;
+
+struct SkinnyJob {
+    const nnq_weight *w;
+    const void *x;
+    const float *bias;
+    void *y;
+};
+
+// Allocates the split-K workspace of a context.
+nnq_status skinny_init(nnq_ctx *ctx);
+// Builds w->d_tiled from w->d_raw when the format / shape has a skinny kernel.
+nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w);
+// True when launch_skinny can run this weight with M rows of activations.
+bool skinny_supported(const nnq_weight *w, int64_t m);
+// One launch computing y_i = x_i * W_i^T (+ bias_i) for all jobs (same format, same M).
+nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int64_t m, int y_dt,
+                         cudaStream_t stream);
+
+}  // namespace nnq

@@ -1,0 +1,191 @@
+"""GPU product parity against the oracle, through the C ABI: every format, skinny and
+ragged M, f32 / bf16 activations and outputs, bias, batch call, host entry point, shards.
+Tolerance: max relative error 2e-3 (f32 accumulation), the bar the task sets."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from nn_b200 import api
+from nn_b200 import formats as F
+from nn_b200.formats import QuantFormat as Q
+from tests import parity as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _run(fmt, n, k, m, x_bf16, y_bf16, with_bias, seed=1, path=api.PATH_AUTO):
+    w, sc = F.gen_weight(fmt, seed, n, k)
+    x = F.gen_activations(seed + 1, m, k, bf16=x_bf16)
+    bias = (F.Stream(seed + 2).normal(n) * 0.5).astype(np.float32) if with_bias else None
+    t = api.from_quantized(w, fmt, [n, k], sc)
+    t.backend.set_path(path)
+    try:
+        xt = torch.from_numpy(x).to(DEV)
+        if x_bf16:
+            xt = xt.to(torch.bfloat16)
+        bt = torch.from_numpy(bias).to(DEV) if with_bias else None
+        y = api.quantized_linear(xt, t, bt, out_dtype=torch.bfloat16 if y_bf16 else torch.float32)
+        torch.cuda.synchronize()
+        t.backend.device_status()
+    finally:
+        t.backend.set_path(api.PATH_AUTO)
+    y32, y64, mag = P.oracle_linear(fmt, w, sc, x, bias, n, k)
+    got = y.float().cpu().numpy()
+    if y_bf16:
+        # output rounding to bf16 adds half an ulp (2^-9 relative) on top of the f32 bar
+        assert P.max_rel_err(got, y32) <= P.TOL_F32_ACC + 2.0 ** -9
+        ref_b = F.bf16_bits_to_f32(F.to_bf16_bits(y32)).reshape(y32.shape)
+        ulp = np.maximum(np.abs(ref_b), 1e-30) * 2.0 ** -7
+        assert np.all(np.abs(got - ref_b) <= ulp + P.TOL_F32_ACC * mag)
+    else:
+        P.assert_close(got, y32, y64, mag)
+    t.release()
+    return got
+
+
+@pytest.mark.parametrize("fmt", list(Q))
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 16])
+def test_skinny_m_all_formats(fmt, m):
+    _run(fmt, 64, 1024, m, x_bf16=True, y_bf16=False, with_bias=False, seed=10 + m)
+
+
+@pytest.mark.parametrize("fmt", list(Q))
+def test_generic_path_all_formats(fmt):
+    _run(fmt, 40, 512, 3, x_bf16=False, y_bf16=False, with_bias=True, seed=5, path=api.PATH_GENERIC)
+
+
+@pytest.mark.parametrize("fmt", [Q.Q8_0, Q.Q4_K, Q.Q6_K, Q.MXFP4_SPLIT])
+@pytest.mark.parametrize("x_bf16,y_bf16", [(False, False), (True, True), (False, True)])
+def test_dtypes_and_bias(fmt, x_bf16, y_bf16):
+    _run(fmt, 128, 2048, 4, x_bf16, y_bf16, with_bias=True, seed=21)
+
+
+@pytest.mark.parametrize("n,k", [(1, 256), (7, 256), (33, 768), (250, 1280), (4096, 4096)])
+def test_q4_k_ragged_shapes(n, k):
+    _run(Q.Q4_K, n, k, 1, x_bf16=True, y_bf16=False, with_bias=False, seed=n)
+
+
+@pytest.mark.parametrize("m", [17, 33, 130])
+def test_q4_k_larger_m(m):
+    _run(Q.Q4_K, 96, 1024, m, x_bf16=True, y_bf16=False, with_bias=False, seed=m)
+
+
+def test_config1_q8_0_gemv_4096():
+    # benchmark configuration 1: W 4096x4096 Q8_0, x f32 [1,4096], y f32 [1,4096]
+    _run(Q.Q8_0, 4096, 4096, 1, x_bf16=False, y_bf16=False, with_bias=False, seed=0x5EED)
+
+
+@pytest.mark.parametrize("n,k", [(1024, 4096), (4096, 12288), (12288, 4096)])
+def test_config2_q4_k_projection_shapes_m1(n, k):
+    _run(Q.Q4_K, n, k, 1, x_bf16=True, y_bf16=True, with_bias=False, seed=0x5EEE)
+
+
+def test_config2_q4_k_m16():
+    _run(Q.Q4_K, 4096, 4096, 16, x_bf16=True, y_bf16=True, with_bias=False, seed=0x5EEF)
+
+
+def test_known_answer_products(golden):
+    for case in golden["matmul"]:
+        fmt = Q[case["fmt"]]
+        w = np.frombuffer(bytes.fromhex(case["bytes"]), np.uint8)
+        x = torch.tensor(case["x"], dtype=torch.float32, device=DEV)
+        t = api.from_quantized(w, fmt, [case["n"], case["k"]])
+        bias = torch.tensor(case["bias"], dtype=torch.float32, device=DEV) if case["bias"] else None
+        y = api.quantized_linear(x, t, bias).cpu().numpy()
+        assert np.all(np.abs(y - np.array(case["expect"], np.float32)) < case["tol"]), case["name"]
+        t.release()
+
+
+def test_batched_leading_dims():
+    # input [2, 3, K] -> [2, 3, N] (crates/nn-core/src/dyn_tensor/quantized_matmul_tests.rs:274-317)
+    n, k = 24, 256
+    w, _ = F.gen_weight(Q.Q8_0, 3, n, k)
+    x = F.gen_activations(4, 6, k, bf16=False)
+    t = api.from_quantized(w, Q.Q8_0, [n, k])
+    y = api.quantized_matmul_q8_0(torch.from_numpy(x.reshape(2, 3, k)).to(DEV), t)
+    assert tuple(y.shape) == (2, 3, n)
+    y32, y64, mag = P.oracle_linear(Q.Q8_0, w, None, x, None, n, k)
+    P.assert_close(y.cpu().numpy().reshape(6, n), y32, y64, mag)
+    t.release()
+
+
+def test_error_cases_on_device():
+    n, k = 8, 64
+    w, _ = F.gen_weight(Q.Q8_0, 3, n, k)
+    t = api.from_quantized(w, Q.Q8_0, [n, k])
+    with pytest.raises(api.ShapeMismatch):
+        api.quantized_matmul_q8_0(torch.zeros(2, 32, device=DEV), t)
+    with pytest.raises(api.RankMismatch):
+        api.quantized_matmul_q8_0(torch.zeros(64, device=DEV), t)
+    with pytest.raises(api.BiasMismatch):
+        api.quantized_linear(torch.zeros(1, 64, device=DEV), t, torch.zeros(n + 1, device=DEV))
+    # the context is still usable afterwards
+    y = api.quantized_matmul_q8_0(torch.zeros(1, 64, device=DEV), t)
+    assert float(y.abs().max()) == 0.0
+    t.release()
+
+
+def test_empty_inputs():
+    w, _ = F.gen_weight(Q.Q4_K, 3, 4, 256)
+    t = api.from_quantized(w, Q.Q4_K, [4, 256])
+    y = api.quantized_matmul(torch.zeros(0, 256, device=DEV), t)
+    assert tuple(y.shape) == (0, 4)
+    t.release()
+    t0 = api.from_quantized(b"", Q.Q8_0, [0, 32])
+    y = api.quantized_matmul(torch.zeros(3, 32, device=DEV), t0)
+    assert tuple(y.shape) == (3, 0)
+    t0.release()
+
+
+def test_host_entry_point_matches_device_entry_point():
+    n, k, m = 64, 512, 2
+    w, _ = F.gen_weight(Q.Q4_K, 8, n, k)
+    x = F.gen_activations(9, m, k, bf16=False)
+    bias = (F.Stream(10).normal(n)).astype(np.float32)
+    t = api.from_quantized(w, Q.Q4_K, [n, k])
+    y_host = api.quantized_linear(x, t, bias)
+    assert isinstance(y_host, np.ndarray)
+    y_dev = api.quantized_linear(torch.from_numpy(x).to(DEV), t, torch.from_numpy(bias).to(DEV)).cpu().numpy()
+    assert np.array_equal(y_host, y_dev)
+    t.release()
+
+
+def test_batch_call_matches_single_calls():
+    k, m = 1024, 1
+    shapes = [(256, k), (64, k), (64, k)]
+    ws = []
+    for i, (n, kk) in enumerate(shapes):
+        w, _ = F.gen_weight(Q.Q4_K, 30 + i, n, kk)
+        ws.append(api.from_quantized(w, Q.Q4_K, [n, kk]))
+    x = torch.from_numpy(F.gen_activations(40, m, k, bf16=True)).to(DEV).to(torch.bfloat16)
+    ys = api.linear_batch([x, x, x], ws, out_dtype=torch.float32)
+    for y, w in zip(ys, ws):
+        single = api.quantized_matmul(x, w, out_dtype=torch.float32)
+        assert torch.equal(y, single)
+        w.release()
+
+
+@pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q8_0, Q.MXFP4_SPLIT])
+def test_tensor_parallel_shards_reassemble(fmt):
+    # column-parallel shards concatenate; row-parallel shard outputs sum (what an
+    # all-reduce would do) -- size-independent linearity property
+    n, k, world = 64, 2048, 4
+    w, sc = F.gen_weight(fmt, 50, n, k)
+    x = F.gen_activations(51, 2, k, bf16=False)
+    full = api.from_quantized(w, fmt, [n, k], sc)
+    xt = torch.from_numpy(x).to(DEV)
+    y_full = api.quantized_matmul(xt, full)
+    cols = [api.quantized_matmul(xt, full.shard(0, r, world)) for r in range(world)]
+    assert torch.equal(torch.cat(cols, dim=-1), y_full)
+    ks = k // world
+    rows = [api.quantized_matmul(xt[:, r * ks:(r + 1) * ks].contiguous(), full.shard(1, r, world))
+            for r in range(world)]
+    y_sum = torch.stack(rows).sum(0)
+    y32, y64, mag = P.oracle_linear(fmt, w, sc, x, None, n, k)
+    P.assert_close(y_sum.cpu().numpy(), y32, y64, mag)
+    with pytest.raises(api.InvalidShape):
+        full.shard(0, 0, 7)
+    full.release()
