@@ -164,7 +164,8 @@ def test_batch_call_matches_single_calls():
     ys = api.linear_batch([x, x, x], ws, out_dtype=torch.float32)
     for y, w in zip(ys, ws):
         single = api.quantized_matmul(x, w, out_dtype=torch.float32)
-        assert torch.equal(y, single)
+        # the k-chunking (hence the f32 summation order) depends on the size of the launch
+        assert float((y - single).abs().max()) <= 1e-5 * float(single.abs().max())
         w.release()
 
 
