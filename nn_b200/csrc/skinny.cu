@@ -35,7 +35,6 @@ namespace nnq {
 
 constexpr int kTileBytes = 2304;
 constexpr int kWarps = 8;               // warps per CTA = row tiles per CTA
-constexpr int kMaxKC = 8;               // super-blocks per CTA k-chunk (bounds shared memory)
 constexpr size_t kPartialFloats = 2u << 20;   // 8 MiB split-K workspace
 constexpr size_t kCounters = 1u << 16;
 
@@ -134,16 +133,31 @@ __global__ void repack_q4k_kernel(const uint8_t *__restrict__ raw, uint8_t *__re
 // ---------------------------------------------------------------------------------
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1) {
+                                        uint2 b) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
 }
 
-// (element pair 2e, 2e+1) of a packed word as fp16x2: pairs 0 and 2 carry +1024, pairs 1 and 3 +64
-__device__ __forceinline__ uint32_t pair_lo(uint32_t w) { return (w & 0x000F000Fu) | 0x64006400u; }
-__device__ __forceinline__ uint32_t pair_hi(uint32_t w) { return (w & 0x00F000F0u) | 0x54005400u; }
+// (a & b) | c in one LOP3 with all three operands in registers. The masks and magic
+// numbers are kept in registers (see Consts) so that the instruction is never split.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+struct Consts {
+    uint32_t mlo, mhi, k1024, k64;
+    __device__ __forceinline__ void init() {
+        // opaque moves: the values live in registers for the whole kernel
+        asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mlo));
+        asm volatile("mov.b32 %0, 0x00F000F0;" : "=r"(mhi));
+        asm volatile("mov.b32 %0, 0x64006400;" : "=r"(k1024));
+        asm volatile("mov.b32 %0, 0x54005400;" : "=r"(k64));
+    }
+};
 
 __device__ __forceinline__ uint32_t sel4(const uint4 &v, int t) {
     uint32_t lo = t & 1 ? v.y : v.x;
@@ -151,26 +165,85 @@ __device__ __forceinline__ uint32_t sel4(const uint4 &v, int t) {
     return t & 2 ? hi : lo;
 }
 
-// Shared memory of one CTA: activations of its k-chunk as fp16 (hi part, and lo part for
-// f32 inputs), then per super-block and t a float4 (Ox[2t], Ox[2t+1], Sx[2t], Sx[2t+1])
-// where Ox = sum of offset * x over the sub-block and Sx = sum of x.
+// Shared memory of one CTA.
+//   img: for every super-block of the k-chunk, the activation operand of its 16 MMAs exactly as
+//        the lanes consume it: img[kb][mma = 4p + e][lane][2] (8 bytes per lane, LDS.64).
+//        Word h of lane (g, t) in MMA (p, e) is the fp16 pair (2e, 2e+1) of word t of sub-block g
+//        when g == 2p + h, and zero otherwise, so that column g of the accumulator tile
+//        receives only sub-block g. The zero pattern is written once per CTA.
+//   tab: per super-block and t a float4 (Ox[2t], Ox[2t+1], Sx[2t], Sx[2t+1]); Ox = sum of
+//        offset * x over the sub-block (offset 1024 or 64 by element), Sx = sum of x.
 template <bool F32X>
 struct SmemLayout {
-    static constexpr int kXBytes = kMaxKC * 256 * 2;
-    static constexpr int kXParts = F32X ? 2 : 1;
-    static constexpr int kTabOff = kXBytes * kXParts;
+    static constexpr int kMaxKC = F32X ? 4 : 8;
+    static constexpr int kImgBytes = kMaxKC * 4096;
+    static constexpr int kImgParts = F32X ? 2 : 1;
+    static constexpr int kTabOff = kImgBytes * kImgParts;
     static constexpr int kTabBytes = kMaxKC * 4 * 16;
-    static constexpr int kRedOff = kTabOff + kTabBytes;  // amax per warp, then flags
+    static constexpr int kRedOff = kTabOff + kTabBytes;  // amax per warp, then the split-K flag
     static constexpr int kTotal = kRedOff + 64;
 };
 
+struct TileRegs {
+    uint4 q[4];
+    uint4 hg, hg8;
+};
+
+__device__ __forceinline__ void load_tile(TileRegs &r, const uint4 *tile, int lane, int g) {
+#pragma unroll
+    for (int p = 0; p < 4; p++) r.q[p] = __ldg(tile + 16 + 32 * p + lane);
+    r.hg = __ldg(tile + g);
+    r.hg8 = __ldg(tile + 8 + g);
+}
+
 template <bool F32X>
-__global__ void __launch_bounds__(kWarps * 32)
+__device__ __forceinline__ void tile_mac(const TileRegs &r, const uint8_t *img_hi, const uint8_t *img_lo,
+                                         const float *tab, int lane, int t, const Consts &K, float &yg,
+                                         float &yg8) {
+    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint2 *bh = reinterpret_cast<const uint2 *>(img_hi) + lane;
+    const uint2 *bl = reinterpret_cast<const uint2 *>(img_lo) + lane;
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        const uint32_t w0 = r.q[p].x, w1 = r.q[p].y, w2 = r.q[p].z, w3 = r.q[p].w;
+        const uint32_t v0 = w0 >> 8, v1 = w1 >> 8, v2 = w2 >> 8, v3 = w3 >> 8;
+        uint32_t a[4][4] = {
+            {and_or(w0, K.mlo, K.k1024), and_or(w1, K.mlo, K.k1024), and_or(w2, K.mlo, K.k1024), and_or(w3, K.mlo, K.k1024)},
+            {and_or(w0, K.mhi, K.k64), and_or(w1, K.mhi, K.k64), and_or(w2, K.mhi, K.k64), and_or(w3, K.mhi, K.k64)},
+            {and_or(v0, K.mlo, K.k1024), and_or(v1, K.mlo, K.k1024), and_or(v2, K.mlo, K.k1024), and_or(v3, K.mlo, K.k1024)},
+            {and_or(v0, K.mhi, K.k64), and_or(v1, K.mhi, K.k64), and_or(v2, K.mhi, K.k64), and_or(v3, K.mhi, K.k64)}};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            mma_f16(c, a[e][0], a[e][1], a[e][2], a[e][3], bh[(4 * p + e) * 32]);
+            if (F32X) mma_f16(c, a[e][0], a[e][1], a[e][2], a[e][3], bl[(4 * p + e) * 32]);
+        }
+    }
+    // c[0], c[1]: row g, sub-blocks 2t, 2t+1; c[2], c[3]: row g+8
+    const float4 tb = *reinterpret_cast<const float4 *>(tab + t * 4);
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const uint4 &hd = h ? r.hg8 : r.hg;
+        uint32_t p01 = __byte_perm(hd.x, hd.y, 0x0073);
+        uint32_t p23 = __byte_perm(hd.z, hd.w, 0x0073);
+        uint32_t dd = __byte_perm(p01, p23, 0x5410);
+        float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&dd));
+        uint32_t o = sel4(hd, t);
+        float sc0 = (float)(o & 63u), sc1 = (float)((o >> 6) & 63u);
+        float mn0 = (float)((o >> 12) & 63u), mn1 = (float)((o >> 18) & 63u);
+        float dot = sc0 * (c[2 * h] - tb.x) + sc1 * (c[2 * h + 1] - tb.y);
+        float mins = mn0 * tb.z + mn1 * tb.w;
+        float v = dm.x * dot - dm.y * mins;
+        if (h) yg8 += v; else yg += v;
+    }
+}
+
+template <bool F32X>
+__global__ void __launch_bounds__(kWarps * 32, 2)
 skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     using L = SmemLayout<F32X>;
     __shared__ __align__(16) uint8_t smem[L::kTotal];
-    uint4 *xs_hi = reinterpret_cast<uint4 *>(smem);
-    uint4 *xs_lo = reinterpret_cast<uint4 *>(smem + L::kXBytes);
+    uint8_t *img_hi = smem;
+    uint8_t *img_lo = smem + L::kImgBytes;
     float *tab = reinterpret_cast<float *>(smem + L::kTabOff);
     float *red = reinterpret_cast<float *>(smem + L::kRedOff);
     int *flag = reinterpret_cast<int *>(smem + L::kRedOff + 32);
@@ -188,56 +261,42 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     const int s = local % J.ksplit;
     const int rg = local / J.ksplit;
     const int kb0 = s * J.kc;
-    const int kb1 = min(kb0 + J.kc, J.kblocks);
-    const int nkb = kb1 - kb0;
+    const int nkb = min(J.kc, J.kblocks - kb0);
     const int rt = rg * kWarps + warp;
     const bool live = rt < J.row_tiles;
 
-    // ---- prefetch the first tile before touching the activations ----
+    // ---- weights first: they do not depend on anything an earlier kernel produced ----
     const uint4 *tile = reinterpret_cast<const uint4 *>(J.tiled + ((size_t)(live ? rt : 0) * J.kblocks + kb0) * kTileBytes);
-    uint4 q[4], hg, hg8;
+    TileRegs r0, r1;
     if (live) {
-#pragma unroll
-        for (int p = 0; p < 4; p++) q[p] = __ldg(tile + 16 + 32 * p + lane);
-        hg = __ldg(tile + g);
-        hg8 = __ldg(tile + 8 + g);
+        load_tile(r0, tile, lane, g);
+        if (nkb > 1) load_tile(r1, tile + kTileBytes / 16, lane, g);
     }
 
-    // ---- stage activations: 8 consecutive elements per thread and iteration ----
-    const int nel = nkb * 256;
-    float amax = 0.0f;
-    for (int i = tid * 8; i < nel; i += kWarps * 32 * 8) {
-        const size_t src = (size_t)kb0 * 256 + i;
-        if (F32X) {
-            const float4 *xp = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(J.x) + src);
-            float4 a = __ldg(xp), b = __ldg(xp + 1);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
+    // ---- zero pattern of the activation image ----
+    {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4 *zi = reinterpret_cast<uint4 *>(smem);
+        const int n16 = nkb * 256 * L::kImgParts;
+        if (!F32X) {
+            for (int i = tid; i < nkb * 256; i += kWarps * 32) zi[i] = z;
         } else {
-            uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(J.x) + src));
-            uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                amax = fmaxf(amax, fabsf(__uint_as_float(w[k] << 16)));
-                amax = fmaxf(amax, fabsf(__uint_as_float(w[k] & 0xFFFF0000u)));
+            for (int i = tid; i < nkb * 256; i += kWarps * 32) {
+                zi[i] = z;
+                zi[L::kImgBytes / 16 + i] = z;
             }
         }
+        (void)n16;
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-    if (lane == 0) red[warp] = amax;
-    __syncthreads();
-#pragma unroll
-    for (int w = 0; w < kWarps; w++) amax = fmaxf(amax, red[w]);
-    // power-of-two prescale so that the chunk's largest |x| lands in [1, 2): exact, keeps fp16 in range
-    uint32_t ex = (__float_as_uint(amax) >> 23) & 0xFFu;
-    ex = amax > 0.0f && ex < 255u ? min(max(ex, 1u), 253u) : 127u;
-    const float scale = __uint_as_float((254u - ex) << 23);
-    const float inv_scale = __uint_as_float(ex << 23);
 
-    for (int i = tid * 8; i < nel; i += kWarps * 32 * 8) {
-        const size_t src = (size_t)kb0 * 256 + i;
-        float xv[8];
+    // ---- activations: 8 consecutive elements per thread (the k-chunk has at most 2048) ----
+    const int i0 = tid * 8;
+    const bool has_x = i0 < nkb * 256;
+    float xv[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) xv[k] = 0.0f;
+    if (has_x) {
+        const size_t src = (size_t)kb0 * 256 + i0;
         if (F32X) {
             const float4 *xp = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(J.x) + src);
             float4 a = __ldg(xp), b = __ldg(xp + 1);
@@ -251,44 +310,60 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
                 xv[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
             }
         }
-        __half hh[8], hl[8];
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(xv[k]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < kWarps; w++) amax = fmaxf(amax, red[w]);
+    // power-of-two prescale so that the chunk's largest |x| lands in [1, 2): exact, keeps fp16 in range
+    uint32_t ex = (__float_as_uint(amax) >> 23) & 0xFFu;
+    ex = amax > 0.0f && ex < 255u ? min(max(ex, 1u), 253u) : 127u;
+    const float scale = __uint_as_float((254u - ex) << 23);
+    const float inv_scale = __uint_as_float(ex << 23);
+    {
+        uint32_t ph[4], pl[4];
         float xr[8];  // the value the MMAs will see
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-            float sx = xv[k] * scale;
-            hh[k] = __float2half_rn(sx);
-            xr[k] = __half2float(hh[k]);
+        for (int k = 0; k < 4; k++) {
+            float s0 = xv[2 * k] * scale, s1 = xv[2 * k + 1] * scale;
+            __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
+            xr[2 * k] = __half2float(h0);
+            xr[2 * k + 1] = __half2float(h1);
+            ph[k] = __half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
             if (F32X) {
-                hl[k] = __float2half_rn(sx - xr[k]);
-                xr[k] += __half2float(hl[k]);
+                __half l0 = __float2half_rn(s0 - xr[2 * k]), l1 = __float2half_rn(s1 - xr[2 * k + 1]);
+                xr[2 * k] += __half2float(l0);
+                xr[2 * k + 1] += __half2float(l1);
+                pl[k] = __half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
             }
         }
-        uint4 o;
-        o.x = __half_as_ushort(hh[0]) | ((uint32_t)__half_as_ushort(hh[1]) << 16);
-        o.y = __half_as_ushort(hh[2]) | ((uint32_t)__half_as_ushort(hh[3]) << 16);
-        o.z = __half_as_ushort(hh[4]) | ((uint32_t)__half_as_ushort(hh[5]) << 16);
-        o.w = __half_as_ushort(hh[6]) | ((uint32_t)__half_as_ushort(hh[7]) << 16);
-        xs_hi[i >> 3] = o;
-        if (F32X) {
-            o.x = __half_as_ushort(hl[0]) | ((uint32_t)__half_as_ushort(hl[1]) << 16);
-            o.y = __half_as_ushort(hl[2]) | ((uint32_t)__half_as_ushort(hl[3]) << 16);
-            o.z = __half_as_ushort(hl[4]) | ((uint32_t)__half_as_ushort(hl[5]) << 16);
-            o.w = __half_as_ushort(hl[6]) | ((uint32_t)__half_as_ushort(hl[7]) << 16);
-            xs_lo[i >> 3] = o;
+        // this thread holds word tt of sub-block sb8 of super-block kbl
+        const int sbk = i0 >> 5, kbl = sbk >> 3, sb8 = sbk & 7, tt = tid & 3;
+        if (has_x) {
+            uint32_t *dst = reinterpret_cast<uint32_t *>(img_hi + kbl * 4096 + (sb8 >> 1) * 1024) + (4 * sb8 + tt) * 2 + (sb8 & 1);
+#pragma unroll
+            for (int e = 0; e < 4; e++) dst[e * 64] = ph[e];
+            if (F32X) {
+                uint32_t *dl = reinterpret_cast<uint32_t *>(img_lo + kbl * 4096 + (sb8 >> 1) * 1024) + (4 * sb8 + tt) * 2 + (sb8 & 1);
+#pragma unroll
+                for (int e = 0; e < 4; e++) dl[e * 64] = pl[e];
+            }
         }
         // elements 0,1,4,5 of each group of 8 carry offset 1024, elements 2,3,6,7 offset 64
         float sa = (xr[0] + xr[1]) + (xr[4] + xr[5]);
         float sb = (xr[2] + xr[3]) + (xr[6] + xr[7]);
         float ox = 1024.0f * sa + 64.0f * sb;
         float sx = sa + sb;
-        // the 4 threads of one sub-block are 4 consecutive lanes
         ox += __shfl_xor_sync(0xFFFFFFFFu, ox, 1);
         sx += __shfl_xor_sync(0xFFFFFFFFu, sx, 1);
         ox += __shfl_xor_sync(0xFFFFFFFFu, ox, 2);
         sx += __shfl_xor_sync(0xFFFFFFFFu, sx, 2);
-        if ((tid & 3) == 0) {
-            int sbk = i >> 5;  // sub-block index within the chunk
-            int kbl = sbk >> 3, sb8 = sbk & 7;
+        if (has_x && tt == 0) {
             float *e = tab + (kbl * 4 + (sb8 >> 1)) * 4 + (sb8 & 1);
             e[0] = ox;
             e[2] = sx;
@@ -296,68 +371,17 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     }
     __syncthreads();
 
-    // ---- main loop over the super-blocks of this k-chunk ----
+    // ---- main loop over the super-blocks of this k-chunk, two register sets in turn ----
     float yg = 0.0f, yg8 = 0.0f;
     if (live) {
-        uint4 lb[4][2], lbl[4][2];
-#pragma unroll
-        for (int p = 0; p < 4; p++)
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                lb[p][h] = make_uint4(0, 0, 0, 0);
-                lbl[p][h] = make_uint4(0, 0, 0, 0);
-            }
-        for (int kbl = 0; kbl < nkb; kbl++) {
-            uint4 cq[4] = {q[0], q[1], q[2], q[3]};
-            uint4 chg = hg, chg8 = hg8;
+        Consts K;
+        K.init();
+        for (int kbl = 0; kbl < nkb; kbl += 2) {
+            tile_mac<F32X>(r0, img_hi + kbl * 4096, img_lo + kbl * 4096, tab + kbl * 16, lane, t, K, yg, yg8);
+            if (kbl + 2 < nkb) load_tile(r0, tile + (kbl + 2) * (kTileBytes / 16), lane, g);
             if (kbl + 1 < nkb) {
-                tile += kTileBytes / 16;
-#pragma unroll
-                for (int p = 0; p < 4; p++) q[p] = __ldg(tile + 16 + 32 * p + lane);
-                hg = __ldg(tile + g);
-                hg8 = __ldg(tile + 8 + g);
-            }
-            // activation operand: only the lane whose column g is the sub-block gets non-zero data
-#pragma unroll
-            for (int p = 0; p < 4; p++)
-#pragma unroll
-                for (int h = 0; h < 2; h++)
-                    if (g == 2 * p + h) {
-                        lb[p][h] = xs_hi[kbl * 32 + lane];
-                        if (F32X) lbl[p][h] = xs_lo[kbl * 32 + lane];
-                    }
-            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int p = 0; p < 4; p++) {
-                const uint32_t w0 = cq[p].x, w1 = cq[p].y, w2 = cq[p].z, w3 = cq[p].w;
-                const uint32_t v0 = w0 >> 8, v1 = w1 >> 8, v2 = w2 >> 8, v3 = w3 >> 8;
-                mma_f16(c, pair_lo(w0), pair_lo(w1), pair_lo(w2), pair_lo(w3), lb[p][0].x, lb[p][1].x);
-                mma_f16(c, pair_hi(w0), pair_hi(w1), pair_hi(w2), pair_hi(w3), lb[p][0].y, lb[p][1].y);
-                mma_f16(c, pair_lo(v0), pair_lo(v1), pair_lo(v2), pair_lo(v3), lb[p][0].z, lb[p][1].z);
-                mma_f16(c, pair_hi(v0), pair_hi(v1), pair_hi(v2), pair_hi(v3), lb[p][0].w, lb[p][1].w);
-                if (F32X) {
-                    mma_f16(c, pair_lo(w0), pair_lo(w1), pair_lo(w2), pair_lo(w3), lbl[p][0].x, lbl[p][1].x);
-                    mma_f16(c, pair_hi(w0), pair_hi(w1), pair_hi(w2), pair_hi(w3), lbl[p][0].y, lbl[p][1].y);
-                    mma_f16(c, pair_lo(v0), pair_lo(v1), pair_lo(v2), pair_lo(v3), lbl[p][0].z, lbl[p][1].z);
-                    mma_f16(c, pair_hi(v0), pair_hi(v1), pair_hi(v2), pair_hi(v3), lbl[p][0].w, lbl[p][1].w);
-                }
-            }
-            // c[0], c[1]: row g, sub-blocks 2t, 2t+1; c[2], c[3]: row g+8
-            const float4 tb = *reinterpret_cast<const float4 *>(tab + (kbl * 4 + t) * 4);
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const uint4 &hd = h ? chg8 : chg;
-                uint32_t p01 = __byte_perm(hd.x, hd.y, 0x0073);
-                uint32_t p23 = __byte_perm(hd.z, hd.w, 0x0073);
-                uint32_t dd = __byte_perm(p01, p23, 0x5410);
-                float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&dd));
-                uint32_t o = sel4(hd, t);
-                float sc0 = (float)(o & 63u), sc1 = (float)((o >> 6) & 63u);
-                float mn0 = (float)((o >> 12) & 63u), mn1 = (float)((o >> 18) & 63u);
-                float dot = sc0 * (c[2 * h] - tb.x) + sc1 * (c[2 * h + 1] - tb.y);
-                float mins = mn0 * tb.z + mn1 * tb.w;
-                float v = dm.x * dot - dm.y * mins;
-                if (h) yg8 += v; else yg += v;
+                tile_mac<F32X>(r1, img_hi + (kbl + 1) * 4096, img_lo + (kbl + 1) * 4096, tab + (kbl + 1) * 16, lane, t, K, yg, yg8);
+                if (kbl + 3 < nkb) load_tile(r1, tile + (kbl + 3) * (kTileBytes / 16), lane, g);
             }
         }
         yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 1);
@@ -391,16 +415,16 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
         part[(size_t)s * npad + rt * 16 + g] = yg;
         part[(size_t)s * npad + rt * 16 + 8 + g] = yg8;
     }
-    __threadfence();
     __syncthreads();
     unsigned int *counter = P.counters + J.group_begin + rg;
     if (tid == 0) {
+        __threadfence();  // cumulative: orders the CTA's partial sums (seen through the barrier) first
         unsigned int old = atomicAdd(counter, 1u);
         *flag = (old == (unsigned int)J.ksplit - 1u);
+        if (*flag) __threadfence();
     }
     __syncthreads();
     if (!*flag) return;
-    __threadfence();
     if (tid < kWarps * 16) {
         int row = rg * kWarps * 16 + tid;
         if (row < npad) {
@@ -476,7 +500,8 @@ nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_d
     int64_t warps_target = (int64_t)ctx->sm_count * 16;
     int kc_want = (int)((tiles + warps_target - 1) / warps_target);
     if (kc_want < 1) kc_want = 1;
-    if (kc_want > kMaxKC) kc_want = kMaxKC;
+    const int kc_max = x_dt == NNQ_F32 ? SmemLayout<true>::kMaxKC : SmemLayout<false>::kMaxKC;
+    if (kc_want > kc_max) kc_want = kc_max;
     int cta = 0, group = 0;
     size_t part = 0;
     for (int i = 0; i < count; i++) {
