@@ -344,7 +344,7 @@ static nnq_status linear_dispatch(nnq_ctx *ctx, const nnq_weight *w, const void 
                                   cudaStream_t stream) {
     if (m == 0 || w->n == 0) return NNQ_OK;
     int path = ctx->path;
-    bool skinny_ok = skinny_supported(w, m);
+    bool skinny_ok = skinny_supported(w, m, x_dt);
     if (path == NNQ_PATH_SKINNY && !skinny_ok)
         return fail(ctx, NNQ_ERR_UNSUPPORTED, "skinny path does not cover format %d, N=%lld, K=%lld, M=%lld",
                     w->fmt, (long long)w->n, (long long)w->k, (long long)m);
@@ -382,7 +382,7 @@ nnq_status nnq_linear_batch(nnq_ctx *ctx, int count, const nnq_weight *const *w,
     for (int i = 0; i < count; i++) {
         s = linear_checked(ctx, w[i], x_dev[i], x_dt, m, bias_dev ? bias_dev[i] : nullptr, y_dev[i], y_dt);
         if (s != NNQ_OK) return s;
-        all_skinny = all_skinny && skinny_supported(w[i], m) && w[i]->fmt == w[0]->fmt;
+        all_skinny = all_skinny && skinny_supported(w[i], m, x_dt) && w[i]->fmt == w[0]->fmt;
     }
     if ((s = set_device(ctx)) != NNQ_OK) return s;
     if (m == 0) return NNQ_OK;

@@ -27,6 +27,8 @@
 // Every global load of the main loop is a fully coalesced 512-byte warp access.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "decode.cuh"
 #include "skinny.h"
@@ -34,31 +36,30 @@
 namespace nnq {
 
 constexpr int kTileBytes = 2304;
-constexpr int kWarps = 8;               // warps per CTA = row tiles per CTA
-constexpr size_t kPartialFloats = 2u << 20;   // 8 MiB split-K workspace
-constexpr size_t kCounters = 1u << 16;
+constexpr int kWarps = 8;          // compute warps per CTA; they split K of one row tile
+constexpr int kMaxStages = 4;      // bulk-copy ring depth per warp (tiles in flight)
+constexpr int kCtasPerSm = 2;
+constexpr int kSmemBudget = 113 * 1024;      // per CTA, so that two CTAs share an SM
+constexpr int kSmemMax = 227 * 1024;         // one CTA per SM
+constexpr unsigned kWaitSpins = 1u << 19;    // bound of every mbarrier wait (about a second in all)
 
 struct SkinnyJobDev {
     const uint8_t *tiled;
-    const void *x;
     const float *bias;
     void *y;
-    int n;            // real rows
-    int row_tiles;    // ceil(n / 16)
-    int kblocks;      // K / 256
-    int kc;           // super-blocks per k-chunk
-    int ksplit;       // ceil(kblocks / kc)
-    int cta_begin;    // first CTA of this job
-    int group_begin;  // first row-group (arrival counter) of this job
-    int partial_begin;  // first float of this job in the split-K workspace
+    int n;              // real rows
+    int row_tiles;      // ceil(n / 16)
+    int tile_begin;     // first row tile of this job in the launch-wide numbering
 };
 
 struct SkinnyParams {
     SkinnyJobDev job[kSkinnyMaxJobs];
+    const void *x;      // activations shared by all jobs, [K]
     int njobs;
     int y_dt;
-    float *partials;
-    unsigned int *counters;
+    int kblocks;        // K / 256
+    int total_tiles;    // row tiles of all jobs
+    int stages;         // ring depth per warp
     int *status;
 };
 
@@ -173,56 +174,119 @@ __device__ __forceinline__ uint32_t sel4(const uint4 &v, int t) {
 //        receives only sub-block g. The zero pattern is written once per CTA.
 //   tab: per super-block and t a float4 (Ox[2t], Ox[2t+1], Sx[2t], Sx[2t+1]); Ox = sum of
 //        offset * x over the sub-block (offset 1024 or 64 by element), Sx = sum of x.
-template <bool F32X>
-struct SmemLayout {
-    static constexpr int kMaxKC = F32X ? 4 : 8;
-    static constexpr int kImgBytes = kMaxKC * 4096;
-    static constexpr int kImgParts = F32X ? 2 : 1;
-    static constexpr int kTabOff = kImgBytes * kImgParts;
-    static constexpr int kTabBytes = kMaxKC * 4 * 16;
-    static constexpr int kRedOff = kTabOff + kTabBytes;  // amax per warp, then the split-K flag
-    static constexpr int kTotal = kRedOff + 64;
+// Shared memory of one CTA (dynamic):
+//   ring   kWarps x stages x 2304 B      per-warp ring of weight tiles filled by bulk copies
+//   xs     K x 4 B (x 2 for f32 inputs)  activations as the MMA operand, "half expanded":
+//          for super-block kb, sub-block sb, word t (32 B at kb*1024 + (4 sb + t)*32):
+//          8 words {b0,b1} x 4 element pairs, b_h = fp16 pair when h == sb & 1, else 0
+//   tab    K/256 x 4 x float4            (Ox[2t], Ox[2t+1], Sx[2t], Sx[2t+1]) per super-block, t
+//   part   2 x kWarps x 16 floats        per-warp partial sums of a row tile, double buffered
+//   red    kWarps floats, bars: kWarps x stages ring barriers + full[2] + empty[2]
+struct SmemPlan {
+    int ring_off, xs_off, xs_lo_off, tab_off, part_off, red_off, bar_off, total;
 };
 
-struct TileRegs {
-    uint4 q[4];
-    uint4 hg, hg8;
-};
-
-__device__ __forceinline__ void load_tile(TileRegs &r, const uint4 *tile, int lane, int g) {
-#pragma unroll
-    for (int p = 0; p < 4; p++) r.q[p] = __ldg(tile + 16 + 32 * p + lane);
-    r.hg = __ldg(tile + g);
-    r.hg8 = __ldg(tile + 8 + g);
+__host__ __device__ inline SmemPlan smem_plan(int kblocks, int stages, bool f32x) {
+    SmemPlan p;
+    p.ring_off = 0;
+    p.xs_off = kWarps * stages * kTileBytes;
+    p.xs_lo_off = p.xs_off + kblocks * 1024;
+    p.tab_off = p.xs_lo_off + (f32x ? kblocks * 1024 : 0);
+    p.part_off = p.tab_off + kblocks * 64;
+    p.red_off = p.part_off + 2 * kWarps * 16 * 4;
+    p.bar_off = p.red_off + 64;
+    p.total = p.bar_off + (kWarps * kMaxStages + 4) * 8;
+    return p;
 }
 
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// global -> shared bulk copy (one contiguous tile), completion counted on an mbarrier
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    // the last operand caps the time one try may suspend the thread (nanoseconds)
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded wait: returns false when the limit ran out (the caller records it and bails out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (unsigned i = 0; i < kWaitSpins; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// predicated 16-byte shared load: the registers keep their value where the predicate is false
+__device__ __forceinline__ void lds128_if(uint4 &v, uint32_t addr, int pred) {
+    asm volatile("{\n .reg .pred q;\n setp.ne.s32 q, %4, 0;\n @q ld.shared.v4.u32 {%0,%1,%2,%3}, [%5];\n}"
+                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w) : "r"(pred), "r"(addr));
+}
+
+struct BRegs {
+    uint4 v[4][2];  // [p][pairs 0-1 | pairs 2-3] = {b0, b1, b0', b1'}: non-zero only for p == g / 2
+};
+
 template <bool F32X>
-__device__ __forceinline__ void tile_mac(const TileRegs &r, const uint8_t *img_hi, const uint8_t *img_lo,
-                                         const float *tab, int lane, int t, const Consts &K, float &yg,
+__device__ __forceinline__ void tile_mac(const uint8_t *stage, uint32_t xs_s, uint32_t xs_lo_s, const float *tab,
+                                         int lane, int g, int t, const Consts &K, BRegs &B, BRegs &BL, float &yg,
                                          float &yg8) {
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    const uint2 *bh = reinterpret_cast<const uint2 *>(img_hi) + lane;
-    const uint2 *bl = reinterpret_cast<const uint2 *>(img_lo) + lane;
+    const uint4 *st = reinterpret_cast<const uint4 *>(stage);
+    // activation operand of this super-block: only the lanes whose column g is a sub-block of
+    // pair p load data for p; every other register of B stays zero for the whole kernel
 #pragma unroll
     for (int p = 0; p < 4; p++) {
-        const uint32_t w0 = r.q[p].x, w1 = r.q[p].y, w2 = r.q[p].z, w3 = r.q[p].w;
-        const uint32_t v0 = w0 >> 8, v1 = w1 >> 8, v2 = w2 >> 8, v3 = w3 >> 8;
-        uint32_t a[4][4] = {
-            {and_or(w0, K.mlo, K.k1024), and_or(w1, K.mlo, K.k1024), and_or(w2, K.mlo, K.k1024), and_or(w3, K.mlo, K.k1024)},
-            {and_or(w0, K.mhi, K.k64), and_or(w1, K.mhi, K.k64), and_or(w2, K.mhi, K.k64), and_or(w3, K.mhi, K.k64)},
-            {and_or(v0, K.mlo, K.k1024), and_or(v1, K.mlo, K.k1024), and_or(v2, K.mlo, K.k1024), and_or(v3, K.mlo, K.k1024)},
-            {and_or(v0, K.mhi, K.k64), and_or(v1, K.mhi, K.k64), and_or(v2, K.mhi, K.k64), and_or(v3, K.mhi, K.k64)}};
+        const int mine = (g >> 1) == p;
+        lds128_if(B.v[p][0], xs_s + lane * 32, mine);
+        lds128_if(B.v[p][1], xs_s + lane * 32 + 16, mine);
+        if (F32X) {
+            lds128_if(BL.v[p][0], xs_lo_s + lane * 32, mine);
+            lds128_if(BL.v[p][1], xs_lo_s + lane * 32 + 16, mine);
+        }
+    }
+    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float c2[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // second accumulator chain: halves the MMA dependency depth
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-            mma_f16(c, a[e][0], a[e][1], a[e][2], a[e][3], bh[(4 * p + e) * 32]);
-            if (F32X) mma_f16(c, a[e][0], a[e][1], a[e][2], a[e][3], bl[(4 * p + e) * 32]);
+    for (int p = 0; p < 4; p++) {
+        const uint4 q = st[16 + 32 * p + lane];
+        const uint32_t w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
+        const uint32_t v0 = w0 >> 8, v1 = w1 >> 8, v2 = w2 >> 8, v3 = w3 >> 8;
+        mma_f16(c, and_or(w0, K.mlo, K.k1024), and_or(w1, K.mlo, K.k1024), and_or(w2, K.mlo, K.k1024),
+                and_or(w3, K.mlo, K.k1024), make_uint2(B.v[p][0].x, B.v[p][0].y));
+        mma_f16(c2, and_or(w0, K.mhi, K.k64), and_or(w1, K.mhi, K.k64), and_or(w2, K.mhi, K.k64),
+                and_or(w3, K.mhi, K.k64), make_uint2(B.v[p][0].z, B.v[p][0].w));
+        mma_f16(c, and_or(v0, K.mlo, K.k1024), and_or(v1, K.mlo, K.k1024), and_or(v2, K.mlo, K.k1024),
+                and_or(v3, K.mlo, K.k1024), make_uint2(B.v[p][1].x, B.v[p][1].y));
+        mma_f16(c2, and_or(v0, K.mhi, K.k64), and_or(v1, K.mhi, K.k64), and_or(v2, K.mhi, K.k64),
+                and_or(v3, K.mhi, K.k64), make_uint2(B.v[p][1].z, B.v[p][1].w));
+        if (F32X) {
+            mma_f16(c, and_or(w0, K.mlo, K.k1024), and_or(w1, K.mlo, K.k1024), and_or(w2, K.mlo, K.k1024),
+                    and_or(w3, K.mlo, K.k1024), make_uint2(BL.v[p][0].x, BL.v[p][0].y));
+            mma_f16(c2, and_or(w0, K.mhi, K.k64), and_or(w1, K.mhi, K.k64), and_or(w2, K.mhi, K.k64),
+                    and_or(w3, K.mhi, K.k64), make_uint2(BL.v[p][0].z, BL.v[p][0].w));
+            mma_f16(c, and_or(v0, K.mlo, K.k1024), and_or(v1, K.mlo, K.k1024), and_or(v2, K.mlo, K.k1024),
+                    and_or(v3, K.mlo, K.k1024), make_uint2(BL.v[p][1].x, BL.v[p][1].y));
+            mma_f16(c2, and_or(v0, K.mhi, K.k64), and_or(v1, K.mhi, K.k64), and_or(v2, K.mhi, K.k64),
+                    and_or(v3, K.mhi, K.k64), make_uint2(BL.v[p][1].z, BL.v[p][1].w));
         }
     }
     // c[0], c[1]: row g, sub-blocks 2t, 2t+1; c[2], c[3]: row g+8
     const float4 tb = *reinterpret_cast<const float4 *>(tab + t * 4);
 #pragma unroll
     for (int h = 0; h < 2; h++) {
-        const uint4 &hd = h ? r.hg8 : r.hg;
+        const uint4 hd = st[8 * h + g];
         uint32_t p01 = __byte_perm(hd.x, hd.y, 0x0073);
         uint32_t p23 = __byte_perm(hd.z, hd.w, 0x0073);
         uint32_t dd = __byte_perm(p01, p23, 0x5410);
@@ -230,106 +294,58 @@ __device__ __forceinline__ void tile_mac(const TileRegs &r, const uint8_t *img_h
         uint32_t o = sel4(hd, t);
         float sc0 = (float)(o & 63u), sc1 = (float)((o >> 6) & 63u);
         float mn0 = (float)((o >> 12) & 63u), mn1 = (float)((o >> 18) & 63u);
-        float dot = sc0 * (c[2 * h] - tb.x) + sc1 * (c[2 * h + 1] - tb.y);
+        float dot = sc0 * ((c[2 * h] + c2[2 * h]) - tb.x) + sc1 * ((c[2 * h + 1] + c2[2 * h + 1]) - tb.y);
         float mins = mn0 * tb.z + mn1 * tb.w;
         float v = dm.x * dot - dm.y * mins;
         if (h) yg8 += v; else yg += v;
     }
 }
 
+// Stage all K activations: power-of-two prescale to fp16 (the largest |x| lands in [1, 2), which
+// is exact and keeps fp16 in range), half-expanded operand layout, per-sub-block offset sums.
+// Called by the whole CTA; returns 1 / prescale.
 template <bool F32X>
-__global__ void __launch_bounds__(kWarps * 32, 2)
-skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
-    using L = SmemLayout<F32X>;
-    __shared__ __align__(16) uint8_t smem[L::kTotal];
-    uint8_t *img_hi = smem;
-    uint8_t *img_lo = smem + L::kImgBytes;
-    float *tab = reinterpret_cast<float *>(smem + L::kTabOff);
-    float *red = reinterpret_cast<float *>(smem + L::kRedOff);
-    int *flag = reinterpret_cast<int *>(smem + L::kRedOff + 32);
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-
-    // ---- which job / row group / k-chunk ----
-    int j = 0;
-#pragma unroll
-    for (int i = 1; i < kSkinnyMaxJobs; i++)
-        if (i < P.njobs && (int)blockIdx.x >= P.job[i].cta_begin) j = i;
-    const SkinnyJobDev &J = P.job[j];
-    const int local = blockIdx.x - J.cta_begin;
-    const int s = local % J.ksplit;
-    const int rg = local / J.ksplit;
-    const int kb0 = s * J.kc;
-    const int nkb = min(J.kc, J.kblocks - kb0);
-    const int rt = rg * kWarps + warp;
-    const bool live = rt < J.row_tiles;
-
-    // ---- weights first: they do not depend on anything an earlier kernel produced ----
-    const uint4 *tile = reinterpret_cast<const uint4 *>(J.tiled + ((size_t)(live ? rt : 0) * J.kblocks + kb0) * kTileBytes);
-    TileRegs r0, r1;
-    if (live) {
-        load_tile(r0, tile, lane, g);
-        if (nkb > 1) load_tile(r1, tile + kTileBytes / 16, lane, g);
-    }
-
-    // ---- zero pattern of the activation image ----
-    {
-        uint4 z = make_uint4(0, 0, 0, 0);
-        uint4 *zi = reinterpret_cast<uint4 *>(smem);
-        const int n16 = nkb * 256 * L::kImgParts;
-        if (!F32X) {
-            for (int i = tid; i < nkb * 256; i += kWarps * 32) zi[i] = z;
-        } else {
-            for (int i = tid; i < nkb * 256; i += kWarps * 32) {
-                zi[i] = z;
-                zi[L::kImgBytes / 16 + i] = z;
-            }
-        }
-        (void)n16;
-    }
-
-    // ---- activations: 8 consecutive elements per thread (the k-chunk has at most 2048) ----
-    const int i0 = tid * 8;
-    const bool has_x = i0 < nkb * 256;
-    float xv[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) xv[k] = 0.0f;
-    if (has_x) {
-        const size_t src = (size_t)kb0 * 256 + i0;
+__device__ __forceinline__ float stage_x(const void *x, int kblocks, uint8_t *xs, uint8_t *xs_lo, float *tab,
+                                         float *red, int tid) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int nel = kblocks * 256;
+    auto load4 = [&](int i, float *xv) {
         if (F32X) {
-            const float4 *xp = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(J.x) + src);
-            float4 a = __ldg(xp), b = __ldg(xp + 1);
-            xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w; xv[4] = b.x; xv[5] = b.y; xv[6] = b.z; xv[7] = b.w;
+            float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + i));
+            xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w;
         } else {
-            uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(J.x) + src));
-            uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                xv[2 * k] = __uint_as_float(w[k] << 16);
-                xv[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
-            }
+            uint2 v = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const __nv_bfloat16 *>(x) + i));
+            xv[0] = __uint_as_float(v.x << 16);
+            xv[1] = __uint_as_float(v.x & 0xFFFF0000u);
+            xv[2] = __uint_as_float(v.y << 16);
+            xv[3] = __uint_as_float(v.y & 0xFFFF0000u);
         }
-    }
+    };
     float amax = 0.0f;
-#pragma unroll
-    for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(xv[k]));
+    for (int i = tid * 4; i < nel; i += kWarps * 32 * 4) {
+        float xv[4];
+        load4(i, xv);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(xv[0]), fabsf(xv[1])), fmaxf(fabsf(xv[2]), fabsf(xv[3]))));
+    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
     if (lane == 0) red[warp] = amax;
     __syncthreads();
 #pragma unroll
     for (int w = 0; w < kWarps; w++) amax = fmaxf(amax, red[w]);
-    // power-of-two prescale so that the chunk's largest |x| lands in [1, 2): exact, keeps fp16 in range
     uint32_t ex = (__float_as_uint(amax) >> 23) & 0xFFu;
     ex = amax > 0.0f && ex < 255u ? min(max(ex, 1u), 253u) : 127u;
     const float scale = __uint_as_float((254u - ex) << 23);
-    const float inv_scale = __uint_as_float(ex << 23);
-    {
-        uint32_t ph[4], pl[4];
-        float xr[8];  // the value the MMAs will see
+    // 4 consecutive elements per thread and iteration = element pairs e0, e0+1 (e0 = 0 or 2) of word
+    // tt of sub-block sb8; a whole warp covers 128 consecutive elements, so the loop is warp-uniform
+    const int tt = (tid >> 1) & 3, e0 = (tid & 1) * 2;
+    for (int i = tid * 4; i < nel; i += kWarps * 32 * 4) {
+        float xv[4];
+        load4(i, xv);
+        uint32_t ph[2], pl[2];
+        float xr[4];  // the value the MMAs will see
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
+        for (int k = 0; k < 2; k++) {
             float s0 = xv[2 * k] * scale, s1 = xv[2 * k + 1] * scale;
             __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
             xr[2 * k] = __half2float(h0);
@@ -342,113 +358,201 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
                 pl[k] = __half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
             }
         }
-        // this thread holds word tt of sub-block sb8 of super-block kbl
-        const int sbk = i0 >> 5, kbl = sbk >> 3, sb8 = sbk & 7, tt = tid & 3;
-        if (has_x) {
-            uint32_t *dst = reinterpret_cast<uint32_t *>(img_hi + kbl * 4096 + (sb8 >> 1) * 1024) + (4 * sb8 + tt) * 2 + (sb8 & 1);
-#pragma unroll
-            for (int e = 0; e < 4; e++) dst[e * 64] = ph[e];
-            if (F32X) {
-                uint32_t *dl = reinterpret_cast<uint32_t *>(img_lo + kbl * 4096 + (sb8 >> 1) * 1024) + (4 * sb8 + tt) * 2 + (sb8 & 1);
-#pragma unroll
-                for (int e = 0; e < 4; e++) dl[e * 64] = pl[e];
-            }
-        }
-        // elements 0,1,4,5 of each group of 8 carry offset 1024, elements 2,3,6,7 offset 64
-        float sa = (xr[0] + xr[1]) + (xr[4] + xr[5]);
-        float sb = (xr[2] + xr[3]) + (xr[6] + xr[7]);
+        const int sbk = i >> 5, kb = sbk >> 3, sb8 = sbk & 7;
+        const int off = kb * 1024 + (4 * sb8 + tt) * 32 + e0 * 8;
+        const bool odd = sb8 & 1;
+        *reinterpret_cast<uint4 *>(xs + off) = odd ? make_uint4(0, ph[0], 0, ph[1]) : make_uint4(ph[0], 0, ph[1], 0);
+        if (F32X)
+            *reinterpret_cast<uint4 *>(xs_lo + off) = odd ? make_uint4(0, pl[0], 0, pl[1]) : make_uint4(pl[0], 0, pl[1], 0);
+        // within a word (8 elements), elements 0,1,4,5 carry offset 1024 and 2,3,6,7 offset 64:
+        // this thread's elements 0,1 are of the first kind and 2,3 of the second
+        float sa = xr[0] + xr[1], sb = xr[2] + xr[3];
         float ox = 1024.0f * sa + 64.0f * sb;
         float sx = sa + sb;
-        ox += __shfl_xor_sync(0xFFFFFFFFu, ox, 1);
-        sx += __shfl_xor_sync(0xFFFFFFFFu, sx, 1);
-        ox += __shfl_xor_sync(0xFFFFFFFFu, ox, 2);
-        sx += __shfl_xor_sync(0xFFFFFFFFu, sx, 2);
-        if (has_x && tt == 0) {
-            float *e = tab + (kbl * 4 + (sb8 >> 1)) * 4 + (sb8 & 1);
+#pragma unroll
+        for (int o2 = 1; o2 < 8; o2 <<= 1) {  // the 8 threads of one sub-block are consecutive lanes
+            ox += __shfl_xor_sync(0xFFFFFFFFu, ox, o2);
+            sx += __shfl_xor_sync(0xFFFFFFFFu, sx, o2);
+        }
+        if ((tid & 7) == 0) {
+            float *e = tab + (kb * 4 + (sb8 >> 1)) * 4 + (sb8 & 1);
             e[0] = ox;
             e[2] = sx;
         }
     }
     __syncthreads();
+    return __uint_as_float(ex << 23);
+}
 
-    // ---- main loop over the super-blocks of this k-chunk, two register sets in turn ----
-    float yg = 0.0f, yg8 = 0.0f;
-    if (live) {
-        Consts K;
-        K.init();
-        for (int kbl = 0; kbl < nkb; kbl += 2) {
-            tile_mac<F32X>(r0, img_hi + kbl * 4096, img_lo + kbl * 4096, tab + kbl * 16, lane, t, K, yg, yg8);
-            if (kbl + 2 < nkb) load_tile(r0, tile + (kbl + 2) * (kTileBytes / 16), lane, g);
-            if (kbl + 1 < nkb) {
-                tile_mac<F32X>(r1, img_hi + (kbl + 1) * 4096, img_lo + (kbl + 1) * 4096, tab + (kbl + 1) * 16, lane, t, K, yg, yg8);
-                if (kbl + 3 < nkb) load_tile(r1, tile + (kbl + 3) * (kTileBytes / 16), lane, g);
+// Persistent kernel: CTA c handles row tiles c, c + grid, ... (numbered across all jobs of the
+// launch); its 8 warps split the K range of each row tile, every warp streaming its tiles
+// through a private ring of bulk copies, and the partial sums meet in shared memory.
+template <bool F32X>
+__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
+skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const SmemPlan L = smem_plan(P.kblocks, P.stages, F32X);
+    uint8_t *xs = smem + L.xs_off;
+    uint8_t *xs_lo = smem + L.xs_lo_off;
+    float *tab = reinterpret_cast<float *>(smem + L.tab_off);
+    float *part = reinterpret_cast<float *>(smem + L.part_off);
+    float *red = reinterpret_cast<float *>(smem + L.red_off);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int cta = blockIdx.x, grid = gridDim.x;
+    const int stages = P.stages;
+    uint8_t *ring = smem + warp * stages * kTileBytes;
+    const uint32_t ring_s = smem_u32(ring);
+    const uint32_t bars_s = smem_u32(smem + L.bar_off);
+    const uint32_t bar_s = bars_s + warp * kMaxStages * 8;
+    const uint32_t full_s = bars_s + kWarps * kMaxStages * 8;   // full[2], then empty[2]
+    const uint32_t empty_s = full_s + 16;
+
+    if (tid == 0) {
+        mbar_init(full_s, kWarps);
+        mbar_init(full_s + 8, kWarps);
+        mbar_init(empty_s, 1);
+        mbar_init(empty_s + 8, 1);
+    }
+    if (lane == 0) {
+        for (int d = 0; d < stages; d++) mbar_init(bar_s + 8 * d, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // this warp's share of K
+    const int kb_lo = (warp * P.kblocks) / kWarps, kb_hi = ((warp + 1) * P.kblocks) / kWarps;
+    const int nkb = kb_hi - kb_lo;
+    const int n_units = cta < P.total_tiles ? (P.total_tiles - cta + grid - 1) / grid : 0;
+
+    auto tile_src = [&](int unit, int k) -> const uint8_t * {
+        int gt = cta + unit * grid;
+        int j = 0;
+#pragma unroll
+        for (int i = 1; i < kSkinnyMaxJobs; i++)
+            if (i < P.njobs && gt >= P.job[i].tile_begin) j = i;
+        return P.job[j].tiled + ((size_t)(gt - P.job[j].tile_begin) * P.kblocks + kb_lo + k) * kTileBytes;
+    };
+
+    // ---- weights first: they do not depend on anything an earlier kernel produced ----
+    int pf_unit = 0, pf_k = 0;
+    unsigned issued = 0;
+    auto issue = [&]() {
+        if (pf_unit < n_units && nkb > 0) {
+            if (lane == 0) {
+                uint32_t d = issued % (unsigned)stages;
+                mbar_expect_tx(bar_s + 8 * d, kTileBytes);
+                bulk_g2s(ring_s + d * kTileBytes, tile_src(pf_unit, pf_k), kTileBytes, bar_s + 8 * d);
+            }
+            issued++;
+            if (++pf_k == nkb) {
+                pf_k = 0;
+                pf_unit++;
             }
         }
+    };
+    for (int d = 0; d < stages; d++) issue();
+
+    // let the next kernel in the stream start its own weight prefetch; wait for the previous
+    // one before touching activations
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const float inv_scale = stage_x<F32X>(P.x, P.kblocks, xs, xs_lo, tab, red, tid);
+    const uint32_t xs_s = smem_u32(xs), xs_lo_s = smem_u32(xs_lo);
+
+    Consts K;
+    K.init();
+    BRegs B, BL;
+#pragma unroll
+    for (int p = 0; p < 4; p++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            B.v[p][h] = make_uint4(0, 0, 0, 0);
+            BL.v[p][h] = make_uint4(0, 0, 0, 0);
+        }
+    unsigned consumed = 0;
+    bool failed = false;
+
+    // writes the 16 outputs of one finished row tile (called by one warp)
+    auto finish = [&](int unit) {
+        const int b = unit & 1;
+        if (!mbar_wait(full_s + 8 * b, (unit >> 1) & 1u)) {
+            failed = true;
+            return;
+        }
+        int gt = cta + unit * grid;
+        int j = 0;
+#pragma unroll
+        for (int i = 1; i < kSkinnyMaxJobs; i++)
+            if (i < P.njobs && gt >= P.job[i].tile_begin) j = i;
+        const SkinnyJobDev &J = P.job[j];
+        if (lane < 16) {
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; w++) v += part[(b * kWarps + w) * 16 + lane];
+            v *= inv_scale;
+            int row = (gt - J.tile_begin) * 16 + lane;
+            if (row < J.n) {
+                if (J.bias) v += __ldg(J.bias + row);
+                if (P.y_dt == NNQ_F32) reinterpret_cast<float *>(J.y)[row] = v;
+                else reinterpret_cast<__nv_bfloat16 *>(J.y)[row] = __float2bfloat16_rn(v);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_s + 8 * b);
+    };
+
+    for (int unit = 0; unit < n_units && !failed; unit++) {
+        float yg = 0.0f, yg8 = 0.0f;
+        for (int k = 0; k < nkb; k++) {
+            const uint32_t d = consumed % (unsigned)stages;
+            if (!mbar_wait(bar_s + 8 * d, (consumed / (unsigned)stages) & 1u)) {
+                failed = true;
+                break;
+            }
+            tile_mac<F32X>(ring + d * kTileBytes, xs_s + (kb_lo + k) * 1024, xs_lo_s + (kb_lo + k) * 1024,
+                           tab + (kb_lo + k) * 16, lane, g, t, K, B, BL, yg, yg8);
+            consumed++;
+            __syncwarp();  // all lanes have read the slot before it is refilled
+            issue();
+        }
+        if (failed) break;
         yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 1);
         yg8 += __shfl_xor_sync(0xFFFFFFFFu, yg8, 1);
         yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 2);
         yg8 += __shfl_xor_sync(0xFFFFFFFFu, yg8, 2);
-        yg *= inv_scale;
-        yg8 *= inv_scale;
-    }
-
-    // ---- output ----
-    const int npad = J.row_tiles * 16;
-    auto store = [&](int row, float v) {
-        if (row < J.n) {
-            if (J.bias) v += __ldg(J.bias + row);
-            if (P.y_dt == NNQ_F32) reinterpret_cast<float *>(J.y)[row] = v;
-            else reinterpret_cast<__nv_bfloat16 *>(J.y)[row] = __float2bfloat16_rn(v);
+        const int b = unit & 1;
+        // the partial-sum slot is free once the row tile two units back has been written out
+        if (unit >= 2 && !mbar_wait(empty_s + 8 * b, ((unit >> 1) - 1) & 1u)) {
+            failed = true;
+            break;
         }
-    };
-    if (J.ksplit == 1) {
-        if (live && t == 0) {
-            store(rt * 16 + g, yg);
-            store(rt * 16 + 8 + g, yg8);
+        if (t == 0) {
+            part[(b * kWarps + warp) * 16 + g] = yg;
+            part[(b * kWarps + warp) * 16 + 8 + g] = yg8;
         }
-        return;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_s + 8 * b);
+        // one warp in turn writes out the previous row tile; its partial sums are long complete
+        if (unit >= 1 && warp == (unit - 1) % kWarps) finish(unit - 1);
     }
-    // split-K: publish this chunk's partial sums; the last CTA of the row group to arrive adds
-    // the chunks in order (deterministic) and writes the output.
-    float *part = P.partials + J.partial_begin;
-    if (live && t == 0) {
-        part[(size_t)s * npad + rt * 16 + g] = yg;
-        part[(size_t)s * npad + rt * 16 + 8 + g] = yg8;
+    if (!failed && n_units >= 1 && warp == (n_units - 1) % kWarps) finish(n_units - 1);
+    if (failed) {
+        // record the failure, then give this warp's copies still in flight a bounded chance to
+        // land before the CTA's shared memory goes away
+        if (lane == 0) atomicExch(P.status, 1);
+        for (unsigned n = consumed; n < issued; n++)
+            mbar_wait(bar_s + 8 * (n % (unsigned)stages), (n / (unsigned)stages) & 1u);
     }
-    __syncthreads();
-    unsigned int *counter = P.counters + J.group_begin + rg;
-    if (tid == 0) {
-        __threadfence();  // cumulative: orders the CTA's partial sums (seen through the barrier) first
-        unsigned int old = atomicAdd(counter, 1u);
-        *flag = (old == (unsigned int)J.ksplit - 1u);
-        if (*flag) __threadfence();
-    }
-    __syncthreads();
-    if (!*flag) return;
-    if (tid < kWarps * 16) {
-        int row = rg * kWarps * 16 + tid;
-        if (row < npad) {
-            float v = 0.0f;
-            for (int ss = 0; ss < J.ksplit; ss++) v += __ldcg(part + (size_t)ss * npad + row);
-            store(row, v);
-        }
-    }
-    if (tid == 0) *counter = 0u;  // ready for the next launch
 }
 
 // ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
 
-nnq_status skinny_init(nnq_ctx *ctx) {
-    nnq_status s = check_cuda(ctx, cudaMalloc(&ctx->d_partials, kPartialFloats * sizeof(float)), "cudaMalloc split-K workspace");
-    if (s != NNQ_OK) return s;
-    ctx->partials_bytes = kPartialFloats * sizeof(float);
-    s = check_cuda(ctx, cudaMalloc(&ctx->d_counters, kCounters * sizeof(unsigned int)), "cudaMalloc counters");
-    if (s != NNQ_OK) return s;
-    ctx->counters_count = kCounters;
-    return check_cuda(ctx, cudaMemset(ctx->d_counters, 0, kCounters * sizeof(unsigned int)), "cudaMemset counters");
-}
+nnq_status skinny_init(nnq_ctx *) { return NNQ_OK; }
 
 nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w) {
     if (w->fmt != NNQ_Q4_K && w->fmt != NNQ_Q4_K_GGML) return NNQ_OK;
@@ -479,61 +583,112 @@ nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w) {
     return NNQ_OK;
 }
 
-bool skinny_supported(const nnq_weight *w, int64_t m) {
-    return w && w->tiled_layout == kTiledQ4K && m == 1;
+// Ring depth and CTAs per SM that fit shared memory for this K: two CTAs per SM with at least a
+// 3-deep ring when possible, else one CTA per SM; stages = 0 when K is too large altogether.
+static void pick_stages(int kblocks, bool f32x, int *stages, int *ctas_per_sm) {
+    for (int st = kMaxStages; st >= 3; st--)
+        if (smem_plan(kblocks, st, f32x).total <= kSmemBudget) {
+            *stages = st;
+            *ctas_per_sm = 2;
+            return;
+        }
+    for (int st = kMaxStages; st >= 2; st--)
+        if (smem_plan(kblocks, st, f32x).total <= kSmemMax) {
+            *stages = st;
+            *ctas_per_sm = 1;
+            return;
+        }
+    *stages = 0;
+    *ctas_per_sm = 0;
+}
+
+bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt) {
+    if (!w || w->tiled_layout != kTiledQ4K || m != 1) return false;
+    int st, cps;
+    pick_stages((int)(w->k / 256), x_dt == NNQ_F32, &st, &cps);
+    return st > 0;
+}
+
+template <bool F32X>
+static cudaError_t launch_kernel(const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_q4k_m1_kernel<F32X>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kWarps * 32);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    // programmatic dependent launch: the kernel prefetches weights while its predecessor in
+    // the stream drains, and waits (griddepcontrol.wait) before reading activations
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, skinny_q4k_m1_kernel<F32X>, P);
+}
+
+// One launch: jobs that share their activations (same x pointer, same K).
+static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int y_dt,
+                               cudaStream_t stream) {
+    SkinnyParams P;
+    memset(&P, 0, sizeof(P));
+    P.njobs = count;
+    P.y_dt = y_dt;
+    P.x = jobs[0].x;
+    P.kblocks = (int)(jobs[0].w->k / 256);
+    P.status = ctx->d_status;
+    const bool f32x = x_dt == NNQ_F32;
+    int ctas_per_sm = 0;
+    pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
+    if (P.stages == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "K = %lld is too large for the skinny kernel", (long long)jobs[0].w->k);
+    int tiles = 0;
+    for (int i = 0; i < count; i++) {
+        const nnq_weight *w = jobs[i].w;
+        SkinnyJobDev &J = P.job[i];
+        J.tiled = w->d_tiled;
+        J.bias = jobs[i].bias;
+        J.y = jobs[i].y;
+        J.n = (int)w->n;
+        J.row_tiles = (int)((w->n + 15) / 16);
+        J.tile_begin = tiles;
+        tiles += J.row_tiles;
+    }
+    P.total_tiles = tiles;
+    // persistent grid: every CTA resident, the same number of row tiles per CTA where possible
+    const int slots = ctx->sm_count * ctas_per_sm;
+    int waves = (tiles + slots - 1) / slots;
+    int grid = (tiles + waves - 1) / waves;
+    static const char *env_grid = getenv("NNQ_SKINNY_GRID");  // tuning aid
+    if (env_grid && atoi(env_grid) > 0) grid = atoi(env_grid);
+    if (grid > tiles) grid = tiles;
+    if (grid < 1) grid = 1;
+    int smem_bytes = smem_plan(P.kblocks, P.stages, f32x).total;
+    cudaError_t e = f32x ? launch_kernel<true>(P, grid, smem_bytes, stream) : launch_kernel<false>(P, grid, smem_bytes, stream);
+    ctx->launches++;
+    return check_cuda(ctx, e, "skinny launch");
 }
 
 nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int64_t m, int y_dt,
                          cudaStream_t stream) {
     if (count < 1 || count > kSkinnyMaxJobs) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad job count %d", count);
     if (m != 1) return fail(ctx, NNQ_ERR_UNSUPPORTED, "skinny kernel covers M = 1 only");
-    SkinnyParams P;
-    memset(&P, 0, sizeof(P));
-    P.njobs = count;
-    P.y_dt = y_dt;
-    P.partials = ctx->d_partials;
-    P.counters = ctx->d_counters;
-    P.status = ctx->d_status;
-    // k-chunk length: enough warps to cover the machine a few times over, at most kMaxKC
-    int64_t tiles = 0;
-    for (int i = 0; i < count; i++) tiles += ((jobs[i].w->n + 15) / 16) * (jobs[i].w->k / 256);
-    int64_t warps_target = (int64_t)ctx->sm_count * 16;
-    int kc_want = (int)((tiles + warps_target - 1) / warps_target);
-    if (kc_want < 1) kc_want = 1;
-    const int kc_max = x_dt == NNQ_F32 ? SmemLayout<true>::kMaxKC : SmemLayout<false>::kMaxKC;
-    if (kc_want > kc_max) kc_want = kc_max;
-    int cta = 0, group = 0;
-    size_t part = 0;
-    for (int i = 0; i < count; i++) {
-        const nnq_weight *w = jobs[i].w;
-        SkinnyJobDev &J = P.job[i];
-        J.tiled = w->d_tiled;
-        J.x = jobs[i].x;
-        J.bias = jobs[i].bias;
-        J.y = jobs[i].y;
-        J.n = (int)w->n;
-        J.row_tiles = (int)((w->n + 15) / 16);
-        J.kblocks = (int)(w->k / 256);
-        J.kc = kc_want < J.kblocks ? kc_want : J.kblocks;
-        J.ksplit = (J.kblocks + J.kc - 1) / J.kc;
-        J.kc = (J.kblocks + J.ksplit - 1) / J.ksplit;  // even out the chunks
-        J.ksplit = (J.kblocks + J.kc - 1) / J.kc;
-        int groups = (J.row_tiles + kWarps - 1) / kWarps;
-        J.cta_begin = cta;
-        J.group_begin = group;
-        J.partial_begin = (int)part;
-        cta += groups * J.ksplit;
-        group += groups;
-        if (J.ksplit > 1) part += (size_t)J.ksplit * J.row_tiles * 16;
+    // consecutive jobs with the same activations and K go out together
+    int i = 0;
+    while (i < count) {
+        int jn = i + 1;
+        while (jn < count && jobs[jn].x == jobs[i].x && jobs[jn].w->k == jobs[i].w->k) jn++;
+        nnq_status s = launch_group(ctx, jobs + i, jn - i, x_dt, y_dt, stream);
+        if (s != NNQ_OK) return s;
+        i = jn;
     }
-    if (part > kPartialFloats || (size_t)group > kCounters)
-        return fail(ctx, NNQ_ERR_UNSUPPORTED, "split-K workspace too small for this launch");
-    if (x_dt == NNQ_F32)
-        skinny_q4k_m1_kernel<true><<<cta, kWarps * 32, 0, stream>>>(P);
-    else
-        skinny_q4k_m1_kernel<false><<<cta, kWarps * 32, 0, stream>>>(P);
-    ctx->launches++;
-    return check_cuda(ctx, cudaGetLastError(), "skinny launch");
+    return NNQ_OK;
 }
 
 }  // namespace nnq

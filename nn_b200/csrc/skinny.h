@@ -14,12 +14,12 @@ struct SkinnyJob {
     void *y;
 };
 
-// Allocates the split-K workspace of a context.
+// Per-context set-up of the skinny kernels (nothing to allocate at present).
 nnq_status skinny_init(nnq_ctx *ctx);
 // Builds w->d_tiled from w->d_raw when the format / shape has a skinny kernel.
 nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w);
 // True when launch_skinny can run this weight with M rows of activations.
-bool skinny_supported(const nnq_weight *w, int64_t m);
+bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt);
 // One launch computing y_i = x_i * W_i^T (+ bias_i) for all jobs (same format, same M).
 nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int64_t m, int y_dt,
                          cudaStream_t stream);
