@@ -39,7 +39,6 @@ constexpr int kTileBytes = 2304;
 constexpr int kWarps = 8;          // compute warps per CTA; they split K of one row tile
 constexpr int kMaxStages = 4;      // bulk-copy ring depth per warp (tiles in flight)
 constexpr int kCtasPerSm = 2;
-constexpr int kSmemBudget = 113 * 1024;      // per CTA, so that two CTAs share an SM
 constexpr int kSmemMax = 227 * 1024;         // one CTA per SM
 constexpr unsigned kWaitSpins = 1u << 19;    // bound of every mbarrier wait (about a second in all)
 
@@ -224,15 +223,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 // Bounded wait: returns false when the limit ran out (the caller records it and bails out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
     for (unsigned i = 0; i < kWaitSpins; i++)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
 
-// predicated 16-byte shared load: the registers keep their value where the predicate is false
-__device__ __forceinline__ void lds128_if(uint4 &v, uint32_t addr, int pred) {
-    asm volatile("{\n .reg .pred q;\n setp.ne.s32 q, %4, 0;\n @q ld.shared.v4.u32 {%0,%1,%2,%3}, [%5];\n}"
-                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w) : "r"(pred), "r"(addr));
+// predicated 32-byte shared load (two 16-byte halves): the registers keep their value where the
+// predicate is false
+__device__ __forceinline__ void lds256_if(uint4 &a, uint4 &b, uint32_t addr, int pred) {
+    asm volatile(
+        "{\n .reg .pred q;\n setp.ne.s32 q, %8, 0;\n @q ld.shared.v4.u32 {%0,%1,%2,%3}, [%9];\n"
+        " @q ld.shared.v4.u32 {%4,%5,%6,%7}, [%9+16];\n}"
+        : "+r"(a.x), "+r"(a.y), "+r"(a.z), "+r"(a.w), "+r"(b.x), "+r"(b.y), "+r"(b.z), "+r"(b.w)
+        : "r"(pred), "r"(addr));
 }
 
 struct BRegs {
@@ -249,12 +253,8 @@ __device__ __forceinline__ void tile_mac(const uint8_t *stage, uint32_t xs_s, ui
 #pragma unroll
     for (int p = 0; p < 4; p++) {
         const int mine = (g >> 1) == p;
-        lds128_if(B.v[p][0], xs_s + lane * 32, mine);
-        lds128_if(B.v[p][1], xs_s + lane * 32 + 16, mine);
-        if (F32X) {
-            lds128_if(BL.v[p][0], xs_lo_s + lane * 32, mine);
-            lds128_if(BL.v[p][1], xs_lo_s + lane * 32 + 16, mine);
-        }
+        lds256_if(B.v[p][0], B.v[p][1], xs_s, mine);
+        if (F32X) lds256_if(BL.v[p][0], BL.v[p][1], xs_lo_s, mine);
     }
     float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     float c2[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // second accumulator chain: halves the MMA dependency depth
@@ -291,7 +291,7 @@ __device__ __forceinline__ void tile_mac(const uint8_t *stage, uint32_t xs_s, ui
         uint32_t p23 = __byte_perm(hd.z, hd.w, 0x0073);
         uint32_t dd = __byte_perm(p01, p23, 0x5410);
         float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&dd));
-        uint32_t o = sel4(hd, t);
+        uint32_t o = reinterpret_cast<const uint32_t *>(stage)[(8 * h + g) * 4 + t];
         float sc0 = (float)(o & 63u), sc1 = (float)((o >> 6) & 63u);
         float mn0 = (float)((o >> 12) & 63u), mn1 = (float)((o >> 18) & 63u);
         float dot = sc0 * ((c[2 * h] + c2[2 * h]) - tb.x) + sc1 * ((c[2 * h + 1] + c2[2 * h + 1]) - tb.y);
@@ -384,12 +384,36 @@ __device__ __forceinline__ float stage_x(const void *x, int kblocks, uint8_t *xs
     return __uint_as_float(ex << 23);
 }
 
-// Persistent kernel: CTA c handles row tiles c, c + grid, ... (numbered across all jobs of the
-// launch); its 8 warps split the K range of each row tile, every warp streaming its tiles
-// through a private ring of bulk copies, and the partial sums meet in shared memory.
-template <bool F32X>
+// Bounded wait written as one PTX loop: try, leave on success, else count down.
+__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .u32 n;\n mov.u32 n, %3;\n"
+        "W_%=:\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n @p bra D_%=;\n"
+        " sub.u32 n, n, 1;\n setp.ne.u32 p, n, 0;\n @p bra W_%=;\n mov.u32 %0, 0;\n bra E_%=;\n"
+        "D_%=:\n mov.u32 %0, 1;\nE_%=:\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(kWaitSpins) : "memory");
+    return ok != 0;
+}
+
+// expect-tx + bulk copy issued by the lanes whose predicate is set (lane 0), without a branch
+__device__ __forceinline__ void issue_tile(uint32_t dst, const void *src, uint32_t bar, int pred) {
+    asm volatile(
+        "{\n .reg .pred q;\n setp.ne.s32 q, %3, 0;\n"
+        " @q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%2], 2304;\n"
+        " @q cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 2304, [%2];\n}"
+        ::"r"(dst), "l"(src), "r"(bar), "r"(pred) : "memory");
+}
+
+// Persistent kernel. A unit is RG = 8 / KS consecutive row tiles; CTA c handles units c, c + grid,
+// ... (row tiles numbered across all jobs of the launch). Warp w works on row tile w / KS of the
+// unit and on the (w % KS)-th part of K, streaming its tiles through a private ring of bulk
+// copies; with KS > 1 the partial sums of a row tile meet in shared memory and one of the KS
+// warps (in turn) writes the 16 outputs while the others already work on the next unit.
+template <bool F32X, int KS>
 __global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
 skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
+    constexpr int RG = kWarps / KS;
     extern __shared__ __align__(128) uint8_t smem[];
     const SmemPlan L = smem_plan(P.kblocks, P.stages, F32X);
     uint8_t *xs = smem + L.xs_off;
@@ -398,10 +422,12 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     float *part = reinterpret_cast<float *>(smem + L.part_off);
     float *red = reinterpret_cast<float *>(smem + L.red_off);
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);   // tells the compiler it is warp-uniform
     const int g = lane >> 2, t = lane & 3;
     const int cta = blockIdx.x, grid = gridDim.x;
     const int stages = P.stages;
+    const int ks = warp % KS, rsub = warp / KS;
     uint8_t *ring = smem + warp * stages * kTileBytes;
     const uint32_t ring_s = smem_u32(ring);
     const uint32_t bars_s = smem_u32(smem + L.bar_off);
@@ -412,8 +438,8 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     if (tid == 0) {
         mbar_init(full_s, kWarps);
         mbar_init(full_s + 8, kWarps);
-        mbar_init(empty_s, 1);
-        mbar_init(empty_s + 8, 1);
+        mbar_init(empty_s, RG);
+        mbar_init(empty_s + 8, RG);
     }
     if (lane == 0) {
         for (int d = 0; d < stages; d++) mbar_init(bar_s + 8 * d, 1);
@@ -421,35 +447,55 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     }
     __syncthreads();
 
-    // this warp's share of K
-    const int kb_lo = (warp * P.kblocks) / kWarps, kb_hi = ((warp + 1) * P.kblocks) / kWarps;
+    // this warp's share of K and of the units
+    const int kb_lo = (ks * P.kblocks) / KS, kb_hi = ((ks + 1) * P.kblocks) / KS;
     const int nkb = kb_hi - kb_lo;
-    const int n_units = cta < P.total_tiles ? (P.total_tiles - cta + grid - 1) / grid : 0;
+    const int total_units = (P.total_tiles + RG - 1) / RG;
+    const int n_units = cta < total_units ? (total_units - cta + grid - 1) / grid : 0;
 
-    auto tile_src = [&](int unit, int k) -> const uint8_t * {
-        int gt = cta + unit * grid;
-        int j = 0;
+    // job and row tile of this warp in a unit; j < 0 when the unit has no row tile for the warp
+    auto locate = [&](int unit, int &j, int &rt) {
+        int gt = (cta + unit * grid) * RG + rsub;
+        j = -1;
+        rt = 0;
+        if (gt < P.total_tiles) {
+            j = 0;
 #pragma unroll
-        for (int i = 1; i < kSkinnyMaxJobs; i++)
-            if (i < P.njobs && gt >= P.job[i].tile_begin) j = i;
-        return P.job[j].tiled + ((size_t)(gt - P.job[j].tile_begin) * P.kblocks + kb_lo + k) * kTileBytes;
+            for (int i = 1; i < kSkinnyMaxJobs; i++)
+                if (i < P.njobs && gt >= P.job[i].tile_begin) j = i;
+            rt = gt - P.job[j].tile_begin;
+        }
     };
 
     // ---- weights first: they do not depend on anything an earlier kernel produced ----
-    int pf_unit = 0, pf_k = 0;
+    int pf_unit = -1, pf_k = 0, pf_slot = 0;
     unsigned issued = 0;
-    auto issue = [&]() {
-        if (pf_unit < n_units && nkb > 0) {
-            if (lane == 0) {
-                uint32_t d = issued % (unsigned)stages;
-                mbar_expect_tx(bar_s + 8 * d, kTileBytes);
-                bulk_g2s(ring_s + d * kTileBytes, tile_src(pf_unit, pf_k), kTileBytes, bar_s + 8 * d);
+    const uint8_t *pf_src = nullptr;
+    bool pf_done = nkb == 0;
+    auto pf_advance_unit = [&]() {   // next unit in which this warp has a row tile
+        for (;;) {
+            if (++pf_unit >= n_units) {
+                pf_done = true;
+                return;
             }
-            issued++;
-            if (++pf_k == nkb) {
+            int j, rt;
+            locate(pf_unit, j, rt);
+            if (j >= 0) {
+                pf_src = P.job[j].tiled + ((size_t)rt * P.kblocks + kb_lo) * kTileBytes;
                 pf_k = 0;
-                pf_unit++;
+                return;
             }
+        }
+    };
+    if (!pf_done) pf_advance_unit();
+    const int is_lane0 = lane == 0;
+    auto issue = [&]() {
+        if (!pf_done) {
+            issue_tile(ring_s + pf_slot * kTileBytes, pf_src, bar_s + 8 * pf_slot, is_lane0);
+            issued++;
+            pf_slot = pf_slot + 1 == stages ? 0 : pf_slot + 1;
+            pf_src += kTileBytes;
+            if (++pf_k == nkb) pf_advance_unit();
         }
     };
     for (int d = 0; d < stages; d++) issue();
@@ -460,7 +506,7 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const float inv_scale = stage_x<F32X>(P.x, P.kblocks, xs, xs_lo, tab, red, tid);
-    const uint32_t xs_s = smem_u32(xs), xs_lo_s = smem_u32(xs_lo);
+    const uint32_t xs_s = smem_u32(xs) + lane * 32, xs_lo_s = smem_u32(xs_lo) + lane * 32;
 
     Consts K;
     K.init();
@@ -473,59 +519,82 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
             BL.v[p][h] = make_uint4(0, 0, 0, 0);
         }
     unsigned consumed = 0;
+    int slot = 0;
+    uint32_t phase = 0;
     bool failed = false;
 
-    // writes the 16 outputs of one finished row tile (called by one warp)
+    auto store16 = [&](int j, int rt, float v) {   // lanes 0..15 hold the 16 outputs of a row tile
+        const SkinnyJobDev &J = P.job[j];
+        int row = rt * 16 + lane;
+        if (lane < 16 && row < J.n) {
+            if (J.bias) v += __ldg(J.bias + row);
+            if (P.y_dt == NNQ_F32) reinterpret_cast<float *>(J.y)[row] = v;
+            else reinterpret_cast<__nv_bfloat16 *>(J.y)[row] = __float2bfloat16_rn(v);
+        }
+    };
+
+    // KS > 1: the warp whose turn it is adds the KS partial sums of its row tile and writes it out
     auto finish = [&](int unit) {
         const int b = unit & 1;
-        if (!mbar_wait(full_s + 8 * b, (unit >> 1) & 1u)) {
+        if (!mbar_wait_fast(full_s + 8 * b, (unit >> 1) & 1u)) {
             failed = true;
             return;
         }
-        int gt = cta + unit * grid;
-        int j = 0;
-#pragma unroll
-        for (int i = 1; i < kSkinnyMaxJobs; i++)
-            if (i < P.njobs && gt >= P.job[i].tile_begin) j = i;
-        const SkinnyJobDev &J = P.job[j];
-        if (lane < 16) {
+        int j, rt;
+        locate(unit, j, rt);
+        if (j >= 0) {
             float v = 0.0f;
+            if (lane < 16) {
 #pragma unroll
-            for (int w = 0; w < kWarps; w++) v += part[(b * kWarps + w) * 16 + lane];
-            v *= inv_scale;
-            int row = (gt - J.tile_begin) * 16 + lane;
-            if (row < J.n) {
-                if (J.bias) v += __ldg(J.bias + row);
-                if (P.y_dt == NNQ_F32) reinterpret_cast<float *>(J.y)[row] = v;
-                else reinterpret_cast<__nv_bfloat16 *>(J.y)[row] = __float2bfloat16_rn(v);
+                for (int w = 0; w < KS; w++) v += part[(b * kWarps + rsub * KS + w) * 16 + lane];
             }
+            store16(j, rt, v * inv_scale);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_s + 8 * b);
     };
 
+#pragma unroll 1
     for (int unit = 0; unit < n_units && !failed; unit++) {
+        int j, rt;
+        locate(unit, j, rt);
         float yg = 0.0f, yg8 = 0.0f;
-        for (int k = 0; k < nkb; k++) {
-            const uint32_t d = consumed % (unsigned)stages;
-            if (!mbar_wait(bar_s + 8 * d, (consumed / (unsigned)stages) & 1u)) {
+        if (j >= 0) {
+#pragma unroll 1
+            bool ok = true;
+            for (int k = 0; k < nkb; k++) {
+                ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
+                tile_mac<F32X>(ring + slot * kTileBytes, xs_s + (kb_lo + k) * 1024, xs_lo_s + (kb_lo + k) * 1024,
+                               tab + (kb_lo + k) * 16, lane, g, t, K, B, BL, yg, yg8);
+                consumed++;
+                if (++slot == stages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+                __syncwarp();  // all lanes have read the slot before it is refilled
+                issue();
+            }
+            if (!ok) {   // a wait ran out: the sums are meaningless, stop here
                 failed = true;
                 break;
             }
-            tile_mac<F32X>(ring + d * kTileBytes, xs_s + (kb_lo + k) * 1024, xs_lo_s + (kb_lo + k) * 1024,
-                           tab + (kb_lo + k) * 16, lane, g, t, K, B, BL, yg, yg8);
-            consumed++;
-            __syncwarp();  // all lanes have read the slot before it is refilled
-            issue();
+            yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 1);
+            yg8 += __shfl_xor_sync(0xFFFFFFFFu, yg8, 1);
+            yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 2);
+            yg8 += __shfl_xor_sync(0xFFFFFFFFu, yg8, 2);
         }
-        if (failed) break;
-        yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 1);
-        yg8 += __shfl_xor_sync(0xFFFFFFFFu, yg8, 1);
-        yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 2);
-        yg8 += __shfl_xor_sync(0xFFFFFFFFu, yg8, 2);
+        if (KS == 1) {
+            // no K split: lanes with t == 0 hold finished rows g and g + 8; gather them into lanes 0..15
+            if (j >= 0) {
+                float lo = __shfl_sync(0xFFFFFFFFu, yg, (lane & 7) * 4);
+                float hi = __shfl_sync(0xFFFFFFFFu, yg8, (lane & 7) * 4);
+                store16(j, rt, (lane < 8 ? lo : hi) * inv_scale);
+            }
+            continue;
+        }
         const int b = unit & 1;
-        // the partial-sum slot is free once the row tile two units back has been written out
-        if (unit >= 2 && !mbar_wait(empty_s + 8 * b, ((unit >> 1) - 1) & 1u)) {
+        // the partial-sum slot is free once the unit two back has been written out
+        if (unit >= 2 && !mbar_wait_fast(empty_s + 8 * b, ((unit >> 1) - 1) & 1u)) {
             failed = true;
             break;
         }
@@ -535,16 +604,21 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(full_s + 8 * b);
-        // one warp in turn writes out the previous row tile; its partial sums are long complete
-        if (unit >= 1 && warp == (unit - 1) % kWarps) finish(unit - 1);
+        // the previous unit's partial sums are long complete: write it out (one warp per row tile)
+        if (unit >= 1 && ks == (unit - 1) % KS) finish(unit - 1);
     }
-    if (!failed && n_units >= 1 && warp == (n_units - 1) % kWarps) finish(n_units - 1);
+    if (KS > 1 && !failed && n_units >= 1 && ks == (n_units - 1) % KS) finish(n_units - 1);
     if (failed) {
         // record the failure, then give this warp's copies still in flight a bounded chance to
         // land before the CTA's shared memory goes away
         if (lane == 0) atomicExch(P.status, 1);
-        for (unsigned n = consumed; n < issued; n++)
-            mbar_wait(bar_s + 8 * (n % (unsigned)stages), (n / (unsigned)stages) & 1u);
+        for (unsigned n = consumed; n < issued; n++) {
+            mbar_wait(bar_s + 8 * slot, phase);
+            if (++slot == stages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
     }
 }
 
@@ -583,21 +657,25 @@ nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w) {
     return NNQ_OK;
 }
 
-// Ring depth and CTAs per SM that fit shared memory for this K: two CTAs per SM with at least a
-// 3-deep ring when possible, else one CTA per SM; stages = 0 when K is too large altogether.
+// Ring depth and CTAs per SM that fit shared memory for this K. More resident warps beat a
+// deeper ring (the kernel is bound by instruction latency, not by bytes in flight), so: three
+// CTAs per SM with a 2-deep ring when that fits, else two with up to 4 stages, else one;
+// stages = 0 when K is too large altogether.
 static void pick_stages(int kblocks, bool f32x, int *stages, int *ctas_per_sm) {
-    for (int st = kMaxStages; st >= 3; st--)
-        if (smem_plan(kblocks, st, f32x).total <= kSmemBudget) {
-            *stages = st;
-            *ctas_per_sm = 2;
-            return;
-        }
-    for (int st = kMaxStages; st >= 2; st--)
-        if (smem_plan(kblocks, st, f32x).total <= kSmemMax) {
-            *stages = st;
-            *ctas_per_sm = 1;
-            return;
-        }
+    static const char *env_st = getenv("NNQ_SKINNY_STAGES");  // tuning aid
+    const int forced = env_st ? atoi(env_st) : 0;
+    const int max_ctas = f32x ? 2 : 3;   // register budget of the two instantiations
+    for (int ctas = max_ctas; ctas >= 1; ctas--) {
+        const int budget = kSmemMax / ctas - 1024;
+        const int hi = forced > 0 ? forced : (ctas == 3 ? 2 : kMaxStages);
+        const int lo = forced > 0 ? forced : 2;
+        for (int st = hi; st >= lo; st--)
+            if (smem_plan(kblocks, st, f32x).total <= budget) {
+                *stages = st;
+                *ctas_per_sm = ctas;
+                return;
+            }
+    }
     *stages = 0;
     *ctas_per_sm = 0;
 }
@@ -609,13 +687,13 @@ bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt) {
     return st > 0;
 }
 
-template <bool F32X>
+template <bool F32X, int KS>
 static cudaError_t launch_kernel(const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_q4k_m1_kernel<F32X>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        cudaError_t e = cudaFuncSetAttribute(skinny_q4k_m1_kernel<F32X, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
@@ -631,7 +709,17 @@ static cudaError_t launch_kernel(const SkinnyParams &P, int grid, int smem_bytes
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, skinny_q4k_m1_kernel<F32X>, P);
+    return cudaLaunchKernelEx(&cfg, skinny_q4k_m1_kernel<F32X, KS>, P);
+}
+
+template <bool F32X>
+static cudaError_t launch_ks(int ksplit, const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
+    switch (ksplit) {
+        case 1: return launch_kernel<F32X, 1>(P, grid, smem_bytes, stream);
+        case 2: return launch_kernel<F32X, 2>(P, grid, smem_bytes, stream);
+        case 4: return launch_kernel<F32X, 4>(P, grid, smem_bytes, stream);
+        default: return launch_kernel<F32X, 8>(P, grid, smem_bytes, stream);
+    }
 }
 
 // One launch: jobs that share their activations (same x pointer, same K).
@@ -661,16 +749,23 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
         tiles += J.row_tiles;
     }
     P.total_tiles = tiles;
-    // persistent grid: every CTA resident, the same number of row tiles per CTA where possible
+    // K split over the warps of a CTA: all 8 warps share a row tile when K allows, so that even
+    // the smallest projections spread over every SM
     const int slots = ctx->sm_count * ctas_per_sm;
-    int waves = (tiles + slots - 1) / slots;
-    int grid = (tiles + waves - 1) / waves;
+    int ksplit = 1;
+    while (ksplit < kWarps && P.kblocks >= 2 * ksplit) ksplit *= 2;
+    static const char *env_ks = getenv("NNQ_SKINNY_KS");  // tuning aid
+    if (env_ks && atoi(env_ks) > 0) ksplit = atoi(env_ks);
+    // persistent grid: every CTA resident
+    const int rg = kWarps / ksplit;
+    const int units = (tiles + rg - 1) / rg;
+    int grid = units < slots ? units : slots;
     static const char *env_grid = getenv("NNQ_SKINNY_GRID");  // tuning aid
     if (env_grid && atoi(env_grid) > 0) grid = atoi(env_grid);
-    if (grid > tiles) grid = tiles;
+    if (grid > units) grid = units;
     if (grid < 1) grid = 1;
     int smem_bytes = smem_plan(P.kblocks, P.stages, f32x).total;
-    cudaError_t e = f32x ? launch_kernel<true>(P, grid, smem_bytes, stream) : launch_kernel<false>(P, grid, smem_bytes, stream);
+    cudaError_t e = f32x ? launch_ks<true>(ksplit, P, grid, smem_bytes, stream) : launch_ks<false>(ksplit, P, grid, smem_bytes, stream);
     ctx->launches++;
     return check_cuda(ctx, e, "skinny launch");
 }
