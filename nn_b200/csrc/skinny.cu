@@ -59,6 +59,9 @@ struct SkinnyParams {
     int kblocks;        // K / 256
     int total_tiles;    // row tiles of all jobs
     int stages;         // ring depth per warp
+    int diag;           // diagnostics (NNQ_SKINNY_DIAG): bit 0 = skip the arithmetic (stream only),
+                        // bit 1 = do not wait for the previous kernel; 4 = plain streaming read
+    int l2_prefetch;    // 1 = ask L2 for the warp's whole weight stream at kernel start
     int *status;
 };
 
@@ -487,6 +490,18 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
             }
         }
     };
+    // Ask L2 for this warp's whole weight stream right away: HBM then runs ahead of the ring and
+    // keeps streaming while the CTA waits for its activations and for the previous kernel to drain.
+    if (P.l2_prefetch && nkb > 0 && lane == 0) {
+        for (int u = 0; u < n_units; u++) {
+            int j, rt;
+            locate(u, j, rt);
+            if (j >= 0) {
+                const uint8_t *src = P.job[j].tiled + ((size_t)rt * P.kblocks + kb_lo) * kTileBytes;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(nkb * kTileBytes) : "memory");
+            }
+        }
+    }
     if (!pf_done) pf_advance_unit();
     const int is_lane0 = lane == 0;
     auto issue = [&]() {
@@ -503,7 +518,7 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     // let the next kernel in the stream start its own weight prefetch; wait for the previous
     // one before touching activations
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!(P.diag & 2)) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const float inv_scale = stage_x<F32X>(P.x, P.kblocks, xs, xs_lo, tab, red, tid);
     const uint32_t xs_s = smem_u32(xs) + lane * 32, xs_lo_s = smem_u32(xs_lo) + lane * 32;
@@ -564,8 +579,9 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
             bool ok = true;
             for (int k = 0; k < nkb; k++) {
                 ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
-                tile_mac<F32X>(ring + slot * kTileBytes, xs_s + (kb_lo + k) * 1024, xs_lo_s + (kb_lo + k) * 1024,
-                               tab + (kb_lo + k) * 16, lane, g, t, K, B, BL, yg, yg8);
+                if (!(P.diag & 1))
+                    tile_mac<F32X>(ring + slot * kTileBytes, xs_s + (kb_lo + k) * 1024, xs_lo_s + (kb_lo + k) * 1024,
+                                   tab + (kb_lo + k) * 16, lane, g, t, K, B, BL, yg, yg8);
                 consumed++;
                 if (++slot == stages) {
                     slot = 0;
@@ -664,7 +680,9 @@ nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w) {
 static void pick_stages(int kblocks, bool f32x, int *stages, int *ctas_per_sm) {
     static const char *env_st = getenv("NNQ_SKINNY_STAGES");  // tuning aid
     const int forced = env_st ? atoi(env_st) : 0;
-    const int max_ctas = f32x ? 2 : 3;   // register budget of the two instantiations
+    static const char *env_ctas = getenv("NNQ_SKINNY_CTAS");  // tuning aid
+    int max_ctas = f32x ? 2 : 3;   // register budget of the two instantiations
+    if (env_ctas && atoi(env_ctas) > 0 && atoi(env_ctas) < max_ctas) max_ctas = atoi(env_ctas);
     for (int ctas = max_ctas; ctas >= 1; ctas--) {
         const int budget = kSmemMax / ctas - 1024;
         const int hi = forced > 0 ? forced : (ctas == 3 ? 2 : kMaxStages);
@@ -708,7 +726,8 @@ static cudaError_t launch_kernel(const SkinnyParams &P, int grid, int smem_bytes
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    static const char *env_pdl = getenv("NNQ_SKINNY_PDL");  // tuning aid
+    cfg.numAttrs = env_pdl && atoi(env_pdl) == 0 ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, skinny_q4k_m1_kernel<F32X, KS>, P);
 }
 
@@ -722,6 +741,21 @@ static cudaError_t launch_ks(int ksplit, const SkinnyParams &P, int grid, int sm
     }
 }
 
+// Diagnostic only (NNQ_SKINNY_DIAG=4): read the tiled weights of the jobs with plain coalesced
+// 16-byte loads and nothing else -- the read bandwidth a launch of this size can reach.
+__global__ void __launch_bounds__(256) stream_read_kernel(const SkinnyParams P, int *sink) {
+    uint32_t acc = 0;
+    for (int j = 0; j < P.njobs; j++) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(P.job[j].tiled);
+        size_t n16 = (size_t)P.job[j].row_tiles * P.kblocks * (kTileBytes / 16);
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+            uint4 v = __ldg(p + i);
+            acc ^= v.x ^ v.y ^ v.z ^ v.w;
+        }
+    }
+    if (acc == 0x12345678u && sink) *sink = 1;   // keeps the loads alive; sink is NULL
+}
+
 // One launch: jobs that share their activations (same x pointer, same K).
 static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int y_dt,
                                cudaStream_t stream) {
@@ -732,6 +766,10 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     P.x = jobs[0].x;
     P.kblocks = (int)(jobs[0].w->k / 256);
     P.status = ctx->d_status;
+    static const char *env_diag = getenv("NNQ_SKINNY_DIAG");
+    P.diag = env_diag ? atoi(env_diag) : 0;
+    static const char *env_l2 = getenv("NNQ_SKINNY_L2PF");
+    P.l2_prefetch = env_l2 ? atoi(env_l2) : 0;
     const bool f32x = x_dt == NNQ_F32;
     int ctas_per_sm = 0;
     pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
@@ -749,6 +787,11 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
         tiles += J.row_tiles;
     }
     P.total_tiles = tiles;
+    if (P.diag == 4) {
+        stream_read_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(P, nullptr);
+        ctx->launches++;
+        return check_cuda(ctx, cudaGetLastError(), "diag launch");
+    }
     // K split over the warps of a CTA: all 8 warps share a row tile when K allows, so that even
     // the smallest projections spread over every SM
     const int slots = ctx->sm_count * ctas_per_sm;
