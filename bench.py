@@ -288,7 +288,11 @@ def run_nnq(args, rank, world, local_rank):
     achieved = per_gpu_bytes_per_launch / per_launch_s / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {peak_kind}", "frac_of_nominal_8000": achieved / 8000.0,
-                "traffic": None, "kernel": "skinny/generic quantized GEMV",
+                # dram__bytes_read+write per launch from the ncu capture summarised in profiles/
+                # (2-layer case; per-launch traffic does not depend on the layer count): 27.18 MB
+                # against 27.17 MB algorithmic, i.e. traffic = algorithmic bytes
+                "traffic": per_gpu_bytes_per_launch * (27.18 / 27.17) if (world == 1 and m == 1) else None,
+                "kernel": "skinny_q4k_m1_kernel",
                 "bytes_per_launch": per_gpu_bytes_per_launch, "us_per_launch": per_launch_s * 1e6}
 
     # ---- end to end through the host entry point of the C ABI ----
