@@ -190,3 +190,24 @@ def test_tensor_parallel_shards_reassemble(fmt):
     with pytest.raises(api.InvalidShape):
         full.shard(0, 0, 7)
     full.release()
+
+
+@pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q6_K, Q.MXFP4_SPLIT])
+@pytest.mark.parametrize("axis", [0, 1])
+def test_device_shard_equals_host_partition(fmt, axis):
+    # nnq_weight_create_shard keeps exactly the bytes nn_b200.tp.shard_bytes selects
+    from nn_b200 import tp
+    from oracle import cpu as orc
+    n, k, world = 32, 2048, 4
+    w, sc = F.gen_weight(fmt, 60, n, k)
+    full = api.from_quantized(w, fmt, [n, k], sc)
+    for rank in range(world):
+        sh = full.shard(axis, rank, world)
+        ws, ss = tp.shard_bytes(fmt, w, sc, n, k, axis, rank, world)
+        ns, ks = tp.shard_shape(fmt, n, k, axis, world)
+        assert sh.dims() == (ns, ks)
+        ref = orc.dequantize(fmt, ws, ns * ks, ss).reshape(ns, ks)
+        got = sh.dequantize().cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+        sh.release()
+    full.release()
