@@ -40,6 +40,7 @@ extern "C" {
 
 typedef struct nnq_ctx nnq_ctx;
 typedef struct nnq_weight nnq_weight;
+typedef struct nnq_moe nnq_moe;
 
 /* Status codes. The first group mirrors QuantizedMatmulError
  * (crates/nn-core/src/dyn_tensor/quantized_matmul.rs:30-76) and the storage
@@ -210,6 +211,47 @@ NNQ_API nnq_status nnq_linear_batch(nnq_ctx *ctx, int count, const nnq_weight *c
                             const void *const *x_dev, nnq_dtype x_dt, int64_t m,
                             const float *const *bias_dev, void *const *y_dev, nnq_dtype y_dt,
                             void *stream);
+
+/* ---- mixture-of-experts block ------------------------------------------------------ */
+
+/* Storage of the expert weight tensors.
+ * NNQ_MOE_KN_GPTOSS: gate_up is [E, hidden, 2*inter] and down is [E, inter, hidden], i.e. each
+ *   expert's matrix is stored [K, N] (x * W), quantized as one flat nn-gptoss Mxfp4Tensor, so the
+ *   32-value blocks run along N (crates/nn-gptoss/src/quantized_model.rs:69-80). fmt must be
+ *   NNQ_MXFP4_GPTOSS.
+ * NNQ_MOE_NK: gate_up is [E, 2*inter, hidden] and down is [E, hidden, inter], each expert an
+ *   [N, K] weight in any nnq_format with blocks along K (the [N,K/2]+[N,K/32] MXFP4 contract of
+ *   crates/nn-metal/src/mxfp4_gemm_msl.rs:47-61 when fmt = NNQ_MXFP4_SPLIT). */
+typedef enum nnq_moe_layout { NNQ_MOE_KN_GPTOSS = 0, NNQ_MOE_NK = 1 } nnq_moe_layout;
+
+/* Build the MoE block of one decoder layer. All tensors may be host or device memory and are
+ * copied. router_w [E, hidden] and router_b [E] are f32; gate_up_bias [E, 2*inter] and down_bias
+ * [E, hidden] are f32; the first `inter` outputs of gate_up are the gate, the rest the up
+ * projection. Replaces QuantizedDecoderLayer::load for the MoE part
+ * (crates/nn-gptoss/src/quantized_model.rs:44-97). */
+NNQ_API nnq_status nnq_moe_create(nnq_ctx *ctx, int n_experts, int hidden, int inter, int top_k,
+                                  float swiglu_limit, const float *router_w, const float *router_b,
+                                  nnq_moe_layout layout, nnq_format fmt, const void *gate_up,
+                                  size_t gate_up_bytes, const void *gate_up_scales,
+                                  size_t gate_up_scales_bytes, const float *gate_up_bias,
+                                  const void *down, size_t down_bytes, const void *down_scales,
+                                  size_t down_scales_bytes, const float *down_bias, nnq_moe **out);
+NNQ_API void nnq_moe_destroy(nnq_moe *m);
+
+/* y[T, hidden] (f32) = MoE(x[T, hidden]): router linear, softmax over all experts, top-k,
+ * renormalisation, per-expert x*W_gu+b, clamp(silu(gate), +-limit)*up, *W_d+b, and the
+ * routing-weighted sum per token with the experts taken in index order. Routing stays on the
+ * device. Replaces QuantizedDecoderLayer::{expert_forward,moe_forward}
+ * (crates/nn-gptoss/src/quantized_model.rs:99-194), GptOssMoeBlock::forward
+ * (crates/nn-gptoss/src/layers.rs:254) and fused_moe_forward (crates/nn-gptoss/src/moe_dispatch.rs:50). */
+NNQ_API nnq_status nnq_moe_forward(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt,
+                                   int64_t tokens, float *y_dev, void *stream);
+
+/* Routing only: expert indices [T, top_k] (descending probability) and renormalised weights
+ * [T, top_k]. Replaces the softmax / topk / renormalise prefix of moe_forward
+ * (crates/nn-gptoss/src/quantized_model.rs:136-144; crates/nn-core/src/dyn_tensor/ops/topk.rs:100-139). */
+NNQ_API nnq_status nnq_moe_route(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt,
+                                 int64_t tokens, int32_t *idx_dev, float *weights_dev, void *stream);
 
 /* Number of kernels this library has launched on this context since creation. */
 NNQ_API int64_t nnq_launch_count(const nnq_ctx *ctx);

@@ -42,6 +42,12 @@ SIGNATURES = {
     "nnq_linear_batch": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int64,
                                  ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_void_p]),
     "nnq_launch_count": (c_int64, [c_void_p]),
+    "nnq_moe_create": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_void_p, c_int, c_int,
+                               c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p,
+                               c_size_t, c_void_p, ctypes.POINTER(c_void_p)]),
+    "nnq_moe_destroy": (None, [c_void_p]),
+    "nnq_moe_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
+    "nnq_moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
 }
 
 

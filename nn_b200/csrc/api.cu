@@ -137,6 +137,7 @@ void nnq_destroy(nnq_ctx *ctx) {
     cudaDeviceSynchronize();
     cudaFree(ctx->d_status);
     cudaFree(ctx->d_partials);
+    cudaFree(ctx->d_moe);
     cudaFree(ctx->d_counters);
     cudaFree(ctx->d_batch_desc);
     cudaFreeHost(ctx->h_batch_desc);

@@ -1,0 +1,499 @@
+// Mixture-of-experts block with block-quantized expert weights (the gpt-oss MoE layer):
+// router linear -> softmax -> top-k -> renormalise -> per-expert (x W_gu + b) -> clamp(silu(gate)) * up
+// -> (h W_d + b) -> routing-weighted sum per token, experts in index order.
+// Follows crates/nn-gptoss/src/quantized_model.rs:99-194 (expert_forward, moe_forward).
+//
+// Everything stays on the device: no host round trip for the routing decisions. Tokens are
+// grouped per expert with a stable counting sort (token order inside an expert, as the
+// reference's assignment lists), the expert products read activations through that index list,
+// and the combine step is a gather (no atomics), so results do not depend on scheduling.
+//
+// Scratch memory (owned by the context, grown on demand before the launches of a call):
+//   idx[T,k] i32, wt[T,k] f32, pos[T,k] i32, count[E] / offset[E+1] i32, rowtok[R] i32,
+//   gu[R, 2I] f32, h[R, I] f32, o[R, H] f32        with R = T * k routed rows.
+#include <cuda_bf16.h>
+#include <math_constants.h>
+
+#include <new>
+
+#include "decode.cuh"
+#include "moe.h"
+
+namespace nnq {
+
+// ---------------------------------------------------------------------------------
+// router: one warp per token
+// ---------------------------------------------------------------------------------
+
+template <typename XT>
+__device__ __forceinline__ float ld_act(const XT *p, int64_t i);
+template <>
+__device__ __forceinline__ float ld_act<float>(const float *p, int64_t i) { return __ldg(p + i); }
+template <>
+__device__ __forceinline__ float ld_act<__nv_bfloat16>(const __nv_bfloat16 *p, int64_t i) {
+    return __bfloat162float(p[i]);
+}
+
+constexpr int kMaxExperts = 64;
+constexpr int kMaxTopK = 8;
+
+template <typename XT>
+__global__ void __launch_bounds__(128)
+moe_router_kernel(const XT *__restrict__ x, const float *__restrict__ rw, const float *__restrict__ rb,
+                  int T, int H, int E, int top_k, int *__restrict__ idx, float *__restrict__ wt) {
+    const int lane = threadIdx.x & 31;
+    const int tok = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (tok >= T) return;
+    // logits: lane e (and e + 32) ends up holding expert e's logit
+    float l0 = -CUDART_INF_F, l1 = -CUDART_INF_F;
+    for (int e = 0; e < E; e++) {
+        float acc = 0.0f;
+        for (int h = lane; h < H; h += 32) acc = fmaf(ld_act<XT>(x, (int64_t)tok * H + h), __ldg(rw + (int64_t)e * H + h), acc);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+        acc += __ldg(rb + e);
+        if (e < 32) { if (lane == e) l0 = acc; } else { if (lane == e - 32) l1 = acc; }
+    }
+    // softmax over the E experts (max-subtracted, f32)
+    float mx = fmaxf(l0, l1);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    float p0 = lane < E ? expf(l0 - mx) : 0.0f;
+    float p1 = lane + 32 < E ? expf(l1 - mx) : 0.0f;
+    float sum = p0 + p1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+    p0 = p0 / sum;
+    p1 = p1 / sum;
+    if (lane >= E) p0 = -1.0f;
+    if (lane + 32 >= E) p1 = -1.0f;
+    // top-k: k rounds of (largest probability, lowest index) selection
+    float sel_p = 0.0f, wsum = 0.0f;
+    int sel_e = 0;
+    for (int s = 0; s < top_k; s++) {
+        float best = p0 >= p1 ? p0 : p1;
+        int be = p0 >= p1 ? lane : lane + 32;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            float ob = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+            int oe = __shfl_xor_sync(0xFFFFFFFFu, be, off);
+            if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+        }
+        if (be == lane) p0 = -1.0f;
+        if (be == lane + 32) p1 = -1.0f;
+        if (lane == s) { sel_p = best; sel_e = be; }
+        wsum += best;
+    }
+    if (lane < top_k) {
+        idx[(int64_t)tok * top_k + lane] = sel_e;
+        wt[(int64_t)tok * top_k + lane] = sel_p / wsum;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// grouping: stable counting sort of the T*k assignments by expert
+// ---------------------------------------------------------------------------------
+
+// block e counts (pass 0) or lists (pass 1) the assignments of expert e in flat order
+__global__ void __launch_bounds__(256)
+moe_group_kernel(const int *__restrict__ idx, int total, int *__restrict__ count, const int *__restrict__ offset,
+                 int *__restrict__ rowtok, int *__restrict__ pos, int pass) {
+    const int e = blockIdx.x;
+    __shared__ int warp_sums[8];
+    __shared__ int base;
+    if (threadIdx.x == 0) base = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int start = 0; start < total; start += 256) {
+        int i = start + threadIdx.x;
+        bool hit = i < total && idx[i] == e;
+        unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
+        if (lane == 0) warp_sums[warp] = __popc(ballot);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; w++) before += warp_sums[w];
+        int mine = base + before + __popc(ballot & ((1u << lane) - 1u));
+        if (pass == 1 && hit) {
+            int row = offset[e] + mine;
+            rowtok[row] = i;
+            pos[i] = row;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < 8; w++) tot += warp_sums[w];
+            base += tot;
+        }
+        __syncthreads();
+    }
+    if (pass == 0 && threadIdx.x == 0) count[e] = base;
+}
+
+__global__ void moe_scan_kernel(const int *__restrict__ count, int *__restrict__ offset, int E) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < E; e++) {
+            offset[e] = acc;
+            acc += count[e];
+        }
+        offset[E] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// expert products
+// ---------------------------------------------------------------------------------
+
+constexpr int kMoeMT = 8;     // routed rows per pass over an expert's weights
+constexpr int kMoeKCH = 128;  // activation chunk staged in shared memory
+
+// Row r of the routed (expert-sorted) order reads its activations either from the token it
+// belongs to (first product) or from row r of the intermediate buffer (second product).
+template <typename XT>
+__device__ __forceinline__ const XT *act_row(const XT *x, const int *rowtok, int top_k, int r, int64_t K) {
+    int64_t src = rowtok ? rowtok[r] / top_k : r;
+    return x + src * K;
+}
+
+// Weights stored [E][K][N] with MXFP4 blocks of 32 running along N (nn-gptoss Mxfp4Tensor over
+// the flattened [ne, K, N] tensor: crates/nn-gptoss/src/quantized_model.rs:69-77,
+// crates/nn-gptoss/src/quantize.rs:122-163): out[r, n] = sum_k x[r, k] * W[e, k, n] + bias[e, n].
+// A warp owns 256 consecutive columns (4 bytes of codes per lane and k); k runs sequentially.
+template <typename XT>
+__global__ void __launch_bounds__(128)
+moe_kn_gptoss_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict__ scales,
+                     const float *__restrict__ bias, const XT *__restrict__ x, const int *__restrict__ rowtok,
+                     int top_k, const int *__restrict__ offset, float *__restrict__ out, int K, int N) {
+    __shared__ float xt[kMoeMT][kMoeKCH];
+    const int e = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n0 = blockIdx.x * 1024 + warp * 256 + lane * 8;
+    const bool col_ok = n0 < N;
+    const uint8_t *wd = data + (size_t)e * K * (N / 2);
+    const uint8_t *ws = scales + (size_t)e * K * (N / 32);
+    const int r_begin = offset[e], r_end = offset[e + 1];
+    for (int r0 = r_begin; r0 < r_end; r0 += kMoeMT) {
+        const int mt = min(kMoeMT, r_end - r0);
+        float acc[kMoeMT][8];
+#pragma unroll
+        for (int t = 0; t < kMoeMT; t++)
+#pragma unroll
+            for (int c = 0; c < 8; c++) acc[t][c] = 0.0f;
+        for (int k0 = 0; k0 < K; k0 += kMoeKCH) {
+            const int kn = min(kMoeKCH, K - k0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < kMoeMT * kMoeKCH; i += 128) {
+                int t = i / kMoeKCH, kk = i % kMoeKCH;
+                float v = 0.0f;
+                if (t < mt && kk < kn) v = ld_act<XT>(act_row<XT>(x, rowtok, top_k, r0 + t, K), k0 + kk);
+                xt[t][kk] = v;
+            }
+            __syncthreads();
+            if (col_ok) {
+                for (int kk = 0; kk < kn; kk++) {
+                    const size_t k = (size_t)(k0 + kk);
+                    uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(wd + k * (N / 2) + n0 / 2));
+                    float scale = mx_scale_gptoss(__ldg(ws + k * (N / 32) + n0 / 32));
+                    float wv[8];
+#pragma unroll
+                    for (int b = 0; b < 4; b++) {
+                        uint32_t byte = (w >> (8 * b)) & 0xFFu;
+                        wv[2 * b] = e2m1_value(byte >> 4, scale);       // high nibble = even column
+                        wv[2 * b + 1] = e2m1_value(byte & 15u, scale);
+                    }
+#pragma unroll
+                    for (int t = 0; t < kMoeMT; t++) {
+                        float xv = xt[t][kk];
+#pragma unroll
+                        for (int c = 0; c < 8; c++) acc[t][c] = fmaf(xv, wv[c], acc[t][c]);
+                    }
+                }
+            }
+        }
+        if (col_ok) {
+            for (int t = 0; t < mt; t++) {
+                float *o = out + (size_t)(r0 + t) * N + n0;
+#pragma unroll
+                for (int c = 0; c < 8; c++) o[c] = acc[t][c] + __ldg(bias + (size_t)e * N + n0 + c);
+            }
+        }
+    }
+}
+
+// Weights stored per expert as [N, K] in any block format (blocks along K):
+// one warp per output column, the lanes share the 32-weight chunks of the row.
+template <int FMT, typename XT>
+__global__ void __launch_bounds__(128)
+moe_nk_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict__ scales, size_t expert_bytes,
+              size_t expert_scale_bytes, const float *__restrict__ bias, const XT *__restrict__ x,
+              const int *__restrict__ rowtok, int top_k, const int *__restrict__ offset,
+              float *__restrict__ out, int K, int N) {
+    const int e = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (n >= N) return;
+    const uint8_t *wd = data + (size_t)e * expert_bytes;
+    const uint8_t *ws = scales ? scales + (size_t)e * expert_scale_bytes : nullptr;
+    const int64_t cpr = K / 32;
+    const int r_begin = offset[e], r_end = offset[e + 1];
+    for (int r0 = r_begin; r0 < r_end; r0 += kMoeMT) {
+        const int mt = min(kMoeMT, r_end - r0);
+        float acc[kMoeMT];
+#pragma unroll
+        for (int t = 0; t < kMoeMT; t++) acc[t] = 0.0f;
+        for (int64_t c = lane; c < cpr; c += 32) {
+            float wv[32];
+            Decode<FMT>::chunk(wd, ws, (int64_t)n * cpr + c, wv);
+#pragma unroll
+            for (int t = 0; t < kMoeMT; t++) {
+                if (t < mt) {
+                    const XT *xr = act_row<XT>(x, rowtok, top_k, r0 + t, K) + c * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; i++) acc[t] = fmaf(wv[i], ld_act<XT>(xr, i), acc[t]);
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kMoeMT; t++) {
+            float v = acc[t];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+            if (lane == 0 && t < mt) out[(size_t)(r0 + t) * N + n] = v + __ldg(bias + (size_t)e * N + n);
+        }
+    }
+}
+
+// h[r, j] = clamp(silu(gu[r, j]), -limit, limit) * gu[r, I + j]   (gate = first half, up = second half)
+__global__ void moe_swiglu_kernel(const float *__restrict__ gu, float *__restrict__ h, const int *__restrict__ offset,
+                                  int E, int inter, float limit) {
+    const int64_t total = (int64_t)offset[E] * inter;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i / inter, j = i % inter;
+        float g = gu[r * 2 * inter + j];
+        float u = gu[r * 2 * inter + inter + j];
+        float s = g / (1.0f + expf(-g));
+        s = fminf(fmaxf(s, -limit), limit);
+        h[i] = s * u;
+    }
+}
+
+// y[t, :] = sum over the token's experts, in expert-index order, of weight * o[row, :]
+__global__ void moe_combine_kernel(const float *__restrict__ o, const int *__restrict__ idx, const float *__restrict__ wt,
+                                   const int *__restrict__ pos, int T, int H, int top_k, float *__restrict__ y) {
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    int order[kMaxTopK];
+    for (int s = 0; s < top_k; s++) order[s] = s;
+    for (int a = 1; a < top_k; a++)   // insertion sort of the slots by expert index
+        for (int b = a; b > 0 && idx[(int64_t)t * top_k + order[b]] < idx[(int64_t)t * top_k + order[b - 1]]; b--) {
+            int tmp = order[b]; order[b] = order[b - 1]; order[b - 1] = tmp;
+        }
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < top_k; s++) {
+            int slot = order[s];
+            float v = o[(size_t)pos[(int64_t)t * top_k + slot] * H + j];
+            acc = __fadd_rn(acc, __fmul_rn(v, wt[(int64_t)t * top_k + slot]));
+        }
+        y[(size_t)t * H + j] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+
+struct MoeScratch {
+    int *idx, *pos, *count, *offset, *rowtok;
+    float *wt, *gu, *h, *o;
+    size_t bytes;
+};
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Carves the scratch buffer; with base == NULL only the size is computed.
+static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
+    MoeScratch s;
+    const int64_t R = T * m->top_k;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { uint8_t *p = base ? base + off : nullptr; off += align256(bytes); return p; };
+    s.idx = (int *)take(R * 4);
+    s.wt = (float *)take(R * 4);
+    s.pos = (int *)take(R * 4);
+    s.count = (int *)take((size_t)m->n_experts * 4);
+    s.offset = (int *)take((size_t)(m->n_experts + 1) * 4);
+    s.rowtok = (int *)take(R * 4);
+    s.gu = (float *)take((size_t)R * 2 * m->inter * 4);
+    s.h = (float *)take((size_t)R * m->inter * 4);
+    s.o = (float *)take((size_t)R * m->hidden * 4);
+    s.bytes = off;
+    return s;
+}
+
+static nnq_status ensure_scratch(nnq_ctx *ctx, const nnq_moe *m, int64_t T, MoeScratch *out) {
+    MoeScratch need = carve(nullptr, T, m);
+    if (need.bytes > ctx->moe_bytes) {
+        cudaFree(ctx->d_moe);
+        ctx->d_moe = nullptr;
+        ctx->moe_bytes = 0;
+        nnq_status s = check_cuda(ctx, cudaMalloc(&ctx->d_moe, need.bytes), "cudaMalloc MoE scratch");
+        if (s != NNQ_OK) return s;
+        ctx->moe_bytes = need.bytes;
+    }
+    *out = carve(ctx->d_moe, T, m);
+    return NNQ_OK;
+}
+
+template <typename XT>
+static void launch_product(const nnq_moe *m, bool first, const XT *x, const int *rowtok, const MoeScratch &s,
+                           float *out, cudaStream_t st) {
+    const int K = first ? m->hidden : m->inter;
+    const int N = first ? 2 * m->inter : m->hidden;
+    const uint8_t *d = first ? m->d_gu : m->d_dn;
+    const uint8_t *sc = first ? m->d_gu_scales : m->d_dn_scales;
+    const float *b = first ? m->d_gu_bias : m->d_dn_bias;
+    const int E = m->n_experts;
+    if (m->layout == NNQ_MOE_KN_GPTOSS) {
+        dim3 grid((N + 1023) / 1024, E);
+        moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, m->top_k, s.offset, out, K, N);
+        return;
+    }
+    Geometry g = geometry(m->fmt);
+    size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
+    dim3 grid((N + 3) / 4, E);
+#define NNQ_NK(F) case F: moe_nk_kernel<F, XT><<<grid, 128, 0, st>>>(d, sc, eb, es, b, x, rowtok, m->top_k, s.offset, out, K, N); break
+    switch (m->fmt) {
+        NNQ_NK(NNQ_Q4_0); NNQ_NK(NNQ_Q4_1); NNQ_NK(NNQ_Q8_0); NNQ_NK(NNQ_Q4_K); NNQ_NK(NNQ_Q4_K_GGML);
+        NNQ_NK(NNQ_Q6_K); NNQ_NK(NNQ_MXFP4_CORE); NNQ_NK(NNQ_MXFP4_SPLIT); NNQ_NK(NNQ_MXFP4_GPTOSS);
+        default: break;
+    }
+#undef NNQ_NK
+}
+
+template <typename XT>
+static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int64_t T, float *y, int *idx_out,
+                                float *wt_out, bool route_only, cudaStream_t st) {
+    MoeScratch s;
+    nnq_status rc = ensure_scratch(ctx, m, T, &s);
+    if (rc != NNQ_OK) return rc;
+    const int E = m->n_experts, k = m->top_k;
+    const int total = (int)(T * k);
+    moe_router_kernel<XT><<<(int)((T + 3) / 4), 128, 0, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, E, k, s.idx, s.wt);
+    ctx->launches++;
+    if (idx_out) cudaMemcpyAsync(idx_out, s.idx, (size_t)total * 4, cudaMemcpyDeviceToDevice, st);
+    if (wt_out) cudaMemcpyAsync(wt_out, s.wt, (size_t)total * 4, cudaMemcpyDeviceToDevice, st);
+    if (route_only) return check_cuda(ctx, cudaGetLastError(), "MoE router launch");
+    moe_group_kernel<<<E, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0);
+    moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, E);
+    moe_group_kernel<<<E, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1);
+    launch_product<XT>(m, true, x, s.rowtok, s, s.gu, st);
+    int64_t hi = (int64_t)total * m->inter;
+    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, E, m->inter, m->limit);
+    launch_product<float>(m, false, s.h, nullptr, s, s.o, st);
+    moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y);
+    ctx->launches += 7;
+    return check_cuda(ctx, cudaGetLastError(), "MoE launch");
+}
+
+}  // namespace nnq
+
+using namespace nnq;
+
+extern "C" {
+
+static nnq_status upload(nnq_ctx *ctx, void **dst, const void *src, size_t bytes, const char *what) {
+    *dst = nullptr;
+    if (bytes == 0) return NNQ_OK;
+    nnq_status s = check_cuda(ctx, cudaMalloc(dst, bytes + 16), what);
+    if (s != NNQ_OK) return s;
+    return check_cuda(ctx, cudaMemcpy(*dst, src, bytes, cudaMemcpyDefault), what);
+}
+
+nnq_status nnq_moe_create(nnq_ctx *ctx, int n_experts, int hidden, int inter, int top_k, float swiglu_limit,
+                          const float *router_w, const float *router_b, nnq_moe_layout layout, nnq_format fmt,
+                          const void *gate_up, size_t gate_up_bytes, const void *gate_up_scales,
+                          size_t gate_up_scales_bytes, const float *gate_up_bias, const void *down,
+                          size_t down_bytes, const void *down_scales, size_t down_scales_bytes,
+                          const float *down_bias, nnq_moe **out) {
+    if (!ctx || !out) return NNQ_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (n_experts < 1 || n_experts > kMaxExperts || top_k < 1 || top_k > kMaxTopK || top_k > n_experts ||
+        hidden < 1 || inter < 1)
+        return fail(ctx, NNQ_ERR_INVALID_ARG, "bad MoE dimensions (experts %d, top_k %d, hidden %d, inter %d)", n_experts, top_k, hidden, inter);
+    if (!router_w || !router_b || !gate_up || !down || !gate_up_bias || !down_bias) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL MoE tensor");
+    if ((int)fmt < 0 || fmt >= NNQ_FORMAT_COUNT) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", (int)fmt);
+    if (layout == NNQ_MOE_KN_GPTOSS && fmt != NNQ_MXFP4_GPTOSS)
+        return fail(ctx, NNQ_ERR_WRONG_QUANT_TYPE, "the [E,K,N] layout holds nn-gptoss MXFP4 tensors only");
+    if (layout != NNQ_MOE_KN_GPTOSS && layout != NNQ_MOE_NK) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown MoE layout %d", (int)layout);
+    Geometry g = geometry(fmt);
+    // blocks must not cross rows of the axis they run along
+    const int64_t gu_inner = layout == NNQ_MOE_KN_GPTOSS ? 2 * (int64_t)inter : hidden;
+    const int64_t dn_inner = layout == NNQ_MOE_KN_GPTOSS ? hidden : inter;
+    if (gu_inner % g.elems || dn_inner % g.elems)
+        return fail(ctx, NNQ_ERR_INVALID_SHAPE, "expert dimensions are not multiples of the block size %d", g.elems);
+    const size_t gu_blocks = (size_t)n_experts * hidden * 2 * inter / g.elems;
+    const size_t dn_blocks = (size_t)n_experts * inter * hidden / g.elems;
+    if (gate_up_bytes != gu_blocks * g.bytes || down_bytes != dn_blocks * g.bytes ||
+        gate_up_scales_bytes != gu_blocks * g.scale_bytes || down_scales_bytes != dn_blocks * g.scale_bytes)
+        return fail(ctx, NNQ_ERR_DATA_LENGTH, "expert tensor byte length does not match its shape");
+    if (g.scale_bytes && (!gate_up_scales || !down_scales)) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL scale tensor");
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    nnq_moe *m = new (std::nothrow) nnq_moe();
+    if (!m) return fail(ctx, NNQ_ERR_OUT_OF_MEMORY, "host allocation failed");
+    memset(m, 0, sizeof(*m));
+    m->ctx = ctx; m->n_experts = n_experts; m->hidden = hidden; m->inter = inter; m->top_k = top_k;
+    m->limit = swiglu_limit; m->layout = layout; m->fmt = fmt;
+    m->gu_bytes = gate_up_bytes; m->gu_scale_bytes = gate_up_scales_bytes;
+    m->dn_bytes = down_bytes; m->dn_scale_bytes = down_scales_bytes;
+    s = upload(ctx, (void **)&m->d_router_w, router_w, (size_t)n_experts * hidden * 4, "router weight");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_router_b, router_b, (size_t)n_experts * 4, "router bias");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_gu, gate_up, gate_up_bytes, "gate_up");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_gu_scales, gate_up_scales, gate_up_scales_bytes, "gate_up scales");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_gu_bias, gate_up_bias, (size_t)n_experts * 2 * inter * 4, "gate_up bias");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn, down, down_bytes, "down");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_scales, down_scales, down_scales_bytes, "down scales");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_bias, down_bias, (size_t)n_experts * hidden * 4, "down bias");
+    if (s != NNQ_OK) {
+        nnq_moe_destroy(m);
+        return s;
+    }
+    *out = m;
+    return NNQ_OK;
+}
+
+void nnq_moe_destroy(nnq_moe *m) {
+    if (!m) return;
+    if (m->ctx) cudaSetDevice(m->ctx->device);
+    cudaFree(m->d_router_w); cudaFree(m->d_router_b); cudaFree(m->d_gu); cudaFree(m->d_gu_scales);
+    cudaFree(m->d_gu_bias); cudaFree(m->d_dn); cudaFree(m->d_dn_scales); cudaFree(m->d_dn_bias);
+    cudaGetLastError();
+    delete m;
+}
+
+static nnq_status moe_call(nnq_ctx *ctx, const nnq_moe *m, const void *x, nnq_dtype x_dt, int64_t tokens, float *y,
+                           int *idx_out, float *wt_out, bool route_only, void *stream) {
+    if (!ctx || !m) return NNQ_ERR_INVALID_ARG;
+    if (m->ctx != ctx) return fail(ctx, NNQ_ERR_INVALID_ARG, "MoE block belongs to another context");
+    if (tokens < 0 || tokens * m->top_k > (int64_t)1 << 30) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad token count");
+    if ((int)x_dt < 0 || x_dt > NNQ_BF16) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown dtype");
+    if (tokens == 0) return NNQ_OK;
+    if (!x || (!route_only && !y)) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dt == NNQ_F32) return forward_typed<float>(ctx, m, (const float *)x, tokens, y, idx_out, wt_out, route_only, st);
+    return forward_typed<__nv_bfloat16>(ctx, m, (const __nv_bfloat16 *)x, tokens, y, idx_out, wt_out, route_only, st);
+}
+
+nnq_status nnq_moe_forward(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt, int64_t tokens,
+                           float *y_dev, void *stream) {
+    return moe_call(ctx, m, x_dev, x_dt, tokens, y_dev, nullptr, nullptr, false, stream);
+}
+
+nnq_status nnq_moe_route(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt, int64_t tokens,
+                         int32_t *idx_dev, float *weights_dev, void *stream) {
+    return moe_call(ctx, m, x_dev, x_dt, tokens, nullptr, idx_dev, weights_dev, true, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,15 @@
+// Mixture-of-experts block: internal declarations.
+#pragma once
+#include "nnq_internal.h"
+
+struct nnq_moe {
+    nnq_ctx *ctx;
+    int n_experts, hidden, inter, top_k;
+    float limit;
+    int layout;            // nnq_moe_layout
+    int fmt;               // nnq_format of the expert weights
+    float *d_router_w, *d_router_b;
+    uint8_t *d_gu, *d_gu_scales, *d_dn, *d_dn_scales;
+    size_t gu_bytes, gu_scale_bytes, dn_bytes, dn_scale_bytes;   // per tensor (all experts)
+    float *d_gu_bias, *d_dn_bias;
+};

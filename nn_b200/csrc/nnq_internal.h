@@ -44,6 +44,9 @@ struct nnq_ctx {
     size_t partials_bytes;
     unsigned int *d_counters;
     size_t counters_count;
+    // scratch of the mixture-of-experts block (routing tables and intermediate activations)
+    uint8_t *d_moe;
+    size_t moe_bytes;
     // batched launch descriptors
     void *d_batch_desc;
     void *h_batch_desc;

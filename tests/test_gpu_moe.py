@@ -1,0 +1,87 @@
+"""GPU MoE block against the oracle's restatement of the reference's moe_forward
+(crates/nn-gptoss/src/quantized_model.rs:99-194), through the C ABI. Router logits are
+continuous (no ties), as the reference's unstable top-k requires."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from nn_b200 import api, moe
+from nn_b200 import formats as F
+from nn_b200.formats import QuantFormat as Q
+from oracle import cpu as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _make(layout, fmt, E, H, I, seed):
+    s = F.Stream(seed)
+    router_w = (s.normal(E * H) * 0.5).astype(np.float32).reshape(E, H)
+    router_b = (s.normal(E) * 0.1).astype(np.float32)
+    b_gu = (s.normal(E * 2 * I) * 0.1).astype(np.float32).reshape(E, 2 * I)
+    b_d = (s.normal(E * H) * 0.1).astype(np.float32).reshape(E, H)
+    if layout == moe.LAYOUT_KN_GPTOSS:
+        # flat nn-gptoss tensors [E, H, 2I] and [E, I, H]: blocks of 32 along the last axis
+        gu, gus = F.gen_weight(Q.MXFP4_GPTOSS, seed + 1, E * H, 2 * I)
+        dn, dns = F.gen_weight(Q.MXFP4_GPTOSS, seed + 2, E * I, H)
+        w_gu = orc.dequantize(Q.MXFP4_GPTOSS, gu, E * H * 2 * I, gus).reshape(E, H, 2 * I)
+        w_d = orc.dequantize(Q.MXFP4_GPTOSS, dn, E * I * H, dns).reshape(E, I, H)
+    else:
+        gu, gus = F.gen_weight(fmt, seed + 1, E * 2 * I, H)
+        dn, dns = F.gen_weight(fmt, seed + 2, E * H, I)
+        w_gu = orc.dequantize(fmt, gu, E * 2 * I * H, gus).reshape(E, 2 * I, H).transpose(0, 2, 1).copy()
+        w_d = orc.dequantize(fmt, dn, E * H * I, dns).reshape(E, H, I).transpose(0, 2, 1).copy()
+    return router_w, router_b, gu, gus, b_gu, dn, dns, b_d, w_gu, w_d
+
+
+@pytest.mark.parametrize("layout,fmt", [(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS), (moe.LAYOUT_NK, Q.MXFP4_SPLIT),
+                                        (moe.LAYOUT_NK, Q.Q4_K)])
+@pytest.mark.parametrize("T", [1, 7, 64])
+def test_moe_forward_matches_oracle(layout, fmt, T):
+    E, H, I, k, limit = 8, 256, 256, 4, 7.0
+    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(layout, fmt, E, H, I, 100 + T)
+    x = F.gen_activations(7 + T, T, H, bf16=True)
+    blk = moe.MoeBlock(E, H, I, k, limit, rw, rb, layout, fmt, gu, gus, bgu, dn, dns, bd)
+    xt = torch.from_numpy(x).to(DEV)
+    idx, wt = blk.route(xt)
+    y = blk(xt).cpu().numpy()
+    torch.cuda.synchronize()
+    y_ref, idx_ref, wt_ref = orc.moe_forward(x, rw, rb, w_gu, bgu, w_d, bd, k, limit)
+    assert np.array_equal(idx.cpu().numpy(), idx_ref)
+    assert np.allclose(wt.cpu().numpy(), wt_ref, rtol=1e-5, atol=1e-7)
+    assert np.all(np.isfinite(y))
+    err = np.max(np.abs(y - y_ref)) / np.max(np.abs(y_ref))
+    assert err <= 2e-3, err
+    # bf16 activations give the same result as their f32 widening
+    y16 = blk(xt.to(torch.bfloat16)).cpu().numpy()
+    assert np.array_equal(y16, y)
+    blk.release()
+
+
+def test_gptoss_shape_decode_batch():
+    # gpt-oss-20b expert geometry (hidden = inter = 2880, not a multiple of 128), fewer experts
+    E, H, I, k, T = 4, 2880, 2880, 2, 5
+    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS, E, H, I, 9)
+    x = F.gen_activations(3, T, H, bf16=True)
+    blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS, gu, gus, bgu, dn, dns, bd)
+    y = blk(torch.from_numpy(x).to(DEV)).cpu().numpy()
+    y_ref, _, _ = orc.moe_forward(x, rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
+    assert np.max(np.abs(y - y_ref)) / np.max(np.abs(y_ref)) <= 2e-3
+    blk.release()
+
+
+def test_moe_argument_errors():
+    E, H, I = 4, 64, 64
+    rw, rb, gu, gus, bgu, dn, dns, bd, _, _ = _make(moe.LAYOUT_NK, Q.Q8_0, E, H, I, 5)
+    with pytest.raises(api.DataLengthMismatch):
+        moe.MoeBlock(E, H, I, 2, 7.0, rw, rb, moe.LAYOUT_NK, Q.Q8_0, gu[:-1], gus, bgu, dn, dns, bd)
+    with pytest.raises(api.WrongQuantType):
+        moe.MoeBlock(E, H, I, 2, 7.0, rw, rb, moe.LAYOUT_KN_GPTOSS, Q.Q8_0, gu, gus, bgu, dn, dns, bd)
+    with pytest.raises(api.InvalidArgument):
+        moe.MoeBlock(E, H, I, 9, 7.0, rw, rb, moe.LAYOUT_NK, Q.Q8_0, gu, gus, bgu, dn, dns, bd)
+    blk = moe.MoeBlock(E, H, I, 2, 7.0, rw, rb, moe.LAYOUT_NK, Q.Q8_0, gu, gus, bgu, dn, dns, bd)
+    with pytest.raises(api.ShapeMismatch):
+        blk(torch.zeros(3, H + 1, device=DEV))
+    assert tuple(blk(torch.zeros(0, H, device=DEV)).shape) == (0, H)
+    blk.release()
