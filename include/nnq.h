@@ -253,6 +253,25 @@ NNQ_API nnq_status nnq_moe_forward(nnq_ctx *ctx, const nnq_moe *m, const void *x
 NNQ_API nnq_status nnq_moe_route(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt,
                                  int64_t tokens, int32_t *idx_dev, float *weights_dev, void *stream);
 
+/* Same computation as nnq_moe_forward for callers that cannot allocate device memory: an
+ * inference server that has handed the whole device to its own memory pool (a library-side
+ * cudaMalloc would fail there), or a latency-critical loop that must not take the device-wide
+ * synchronisation cudaMalloc / cudaFree imply. It has no counterpart in the reference. The
+ * routing tables and intermediate activations live in a fixed 8 MiB area inside the library's
+ * device image (held by every GPU that loads the library until the process exits) instead of the
+ * context's growable scratch buffer, and the call performs no allocation of any kind.
+ * Limits and rules:
+ *   - tokens * top_k * (3*inter + hidden) * 4 bytes (plus small tables) must fit the 8 MiB area,
+ *     e.g. 182 routed rows (45 tokens at top-4) at gpt-oss-20b's hidden = inter = 2880; larger calls are rejected with
+ *     NNQ_ERR_UNSUPPORTED and a message naming both sizes;
+ *   - the first call on a device looks up the area's address (cudaGetSymbolAddress); make that
+ *     first call before any stream capture;
+ *   - all calls on a device share the area: two calls whose kernels overlap on the GPU (different
+ *     streams, or different contexts on one device) race. Calls on one stream are safe. Nothing
+ *     in the area needs clearing between calls. */
+NNQ_API nnq_status nnq_moe_forward_static(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt,
+                                          int64_t tokens, float *y_dev, void *stream);
+
 /* Number of kernels this library has launched on this context since creation. */
 NNQ_API int64_t nnq_launch_count(const nnq_ctx *ctx);
 

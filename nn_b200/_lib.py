@@ -47,6 +47,7 @@ SIGNATURES = {
                                c_size_t, c_void_p, ctypes.POINTER(c_void_p)]),
     "nnq_moe_destroy": (None, [c_void_p]),
     "nnq_moe_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
+    "nnq_moe_forward_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "nnq_moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]),
 }
 

@@ -395,6 +395,52 @@ static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
 }
 
+// ---------------------------------------------------------------------------------
+// scratch that nobody allocates (see nnq_moe_forward_static)
+// ---------------------------------------------------------------------------------
+
+// Fixed scratch area living in the library's device image: every GPU that loads the library
+// holds these bytes until the process exits, so the size is kept modest. All calls of
+// nnq_moe_forward_static on a device share it.
+constexpr size_t kStaticScratchBytes = (size_t)8 << 20;
+static __device__ __align__(256) unsigned char g_moe_static_scratch[kStaticScratchBytes];
+
+// Device address of the area, looked up once per device. In host code the array's name is only
+// a stand-in for the symbol, not an address a kernel may use; cudaGetSymbolAddress (with the
+// device current) gives the real one.
+static nnq_status static_scratch_base(nnq_ctx *ctx, uint8_t **base) {
+    static uint8_t *cached[64] = {};
+    const int dev = ctx->device;
+    if (dev < 0 || dev >= 64) return fail(ctx, NNQ_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    if (!cached[dev]) {
+        void *p = nullptr;
+        nnq_status s = check_cuda(ctx, cudaGetSymbolAddress(&p, g_moe_static_scratch), "cudaGetSymbolAddress");
+        if (s != NNQ_OK) return s;
+        cached[dev] = static_cast<uint8_t *>(p);
+    }
+    *base = cached[dev];
+    return NNQ_OK;
+}
+
+// The launches of one forward pass over a scratch area the caller of this function provides.
+template <typename XT>
+static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int64_t T, float *y,
+                                   const MoeScratch &s, cudaStream_t st) {
+    const int E = m->n_experts, k = m->top_k;
+    const int total = (int)(T * k);
+    moe_router_kernel<XT><<<(int)((T + 3) / 4), 128, 0, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, E, k, s.idx, s.wt);
+    moe_group_kernel<<<E, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0);
+    moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, E);
+    moe_group_kernel<<<E, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1);
+    launch_product<XT>(m, true, x, s.rowtok, s, s.gu, st);
+    int64_t hi = (int64_t)total * m->inter;
+    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, E, m->inter, m->limit);
+    launch_product<float>(m, false, s.h, nullptr, s, s.o, st);
+    moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y);
+    ctx->launches += 8;
+    return check_cuda(ctx, cudaGetLastError(), "MoE launch");
+}
+
 }  // namespace nnq
 
 using namespace nnq;
@@ -494,6 +540,34 @@ nnq_status nnq_moe_forward(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nn
 nnq_status nnq_moe_route(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt, int64_t tokens,
                          int32_t *idx_dev, float *weights_dev, void *stream) {
     return moe_call(ctx, m, x_dev, x_dt, tokens, nullptr, idx_dev, weights_dev, true, stream);
+}
+
+nnq_status nnq_moe_forward_static(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt,
+                                  int64_t tokens, float *y_dev, void *stream) {
+    if (!ctx || !m) return NNQ_ERR_INVALID_ARG;
+    if (m->ctx != ctx) return fail(ctx, NNQ_ERR_INVALID_ARG, "MoE block belongs to another context");
+    if (tokens < 0) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad token count");
+    if ((int)x_dt < 0 || x_dt > NNQ_BF16) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown dtype");
+    if (tokens == 0) return NNQ_OK;
+    if (!x_dev || !y_dev) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
+    // size check first: it needs no device work
+    if (tokens > ((int64_t)1 << 24)) return fail(ctx, NNQ_ERR_UNSUPPORTED, "token count beyond the fixed scratch area");
+    const size_t need = carve(nullptr, tokens, m).bytes;
+    if (need > kStaticScratchBytes)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED,
+                    "this call needs %zu bytes of scratch, the fixed area holds %zu: use nnq_moe_forward or fewer tokens",
+                    need, (size_t)kStaticScratchBytes);
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    uint8_t *base = nullptr;
+    if ((s = static_scratch_base(ctx, &base)) != NNQ_OK) return s;
+    // Nothing in the area has to start at zero: every table and buffer is fully written by the
+    // launches below before it is read (counts are stored, not accumulated), so stale contents
+    // of an earlier call are harmless.
+    const MoeScratch sc = carve(base, tokens, m);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dt == NNQ_F32) return run_with_scratch<float>(ctx, m, (const float *)x_dev, tokens, y_dev, sc, st);
+    return run_with_scratch<__nv_bfloat16>(ctx, m, (const __nv_bfloat16 *)x_dev, tokens, y_dev, sc, st);
 }
 
 }  // extern "C"
