@@ -238,7 +238,7 @@ def run_nnq(args, rank, world, local_rank):
             step(sp)
         stream.synchronize()
         backend.device_status(stream)
-        if not args.no_graph and (world == 1 or args.graph_tp):
+        if not args.no_graph and world == 1:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step(VP(torch.cuda.current_stream().cuda_stream))
@@ -367,7 +367,6 @@ def main():
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--graph-tp", action="store_true", help="capture the tensor-parallel step (with its all-reduces) in a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
