@@ -6,6 +6,7 @@
 #include <new>
 
 #include "nnq_internal.h"
+#include "gemm_tc.h"
 #include "skinny.h"
 
 namespace nnq {
@@ -349,8 +350,13 @@ static nnq_status linear_dispatch(nnq_ctx *ctx, const nnq_weight *w, const void 
     if (path == NNQ_PATH_SKINNY && !skinny_ok)
         return fail(ctx, NNQ_ERR_UNSUPPORTED, "skinny path does not cover format %d, N=%lld, K=%lld, M=%lld",
                     w->fmt, (long long)w->n, (long long)w->k, (long long)m);
-    if (path == NNQ_PATH_TENSOR)
-        return fail(ctx, NNQ_ERR_UNSUPPORTED, "tensor path is not built into this library version");
+    const bool tc_ok = gemm_tc_supported(w, m);
+    if (path == NNQ_PATH_TENSOR && !tc_ok)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "tensor path needs K to be a multiple of 64 (K=%lld)", (long long)w->k);
+    if (path == NNQ_PATH_TENSOR || (path == NNQ_PATH_AUTO && !skinny_ok && tc_ok && m > 16)) {
+        TcArgs a = {w->d_raw, w->d_scales, x_dev, bias_dev, y_dev, m, w->n, w->k, w->fmt, x_dt, y_dt};
+        return launch_gemm_tc(ctx, a, stream);
+    }
     if ((path == NNQ_PATH_AUTO && skinny_ok) || path == NNQ_PATH_SKINNY) {
         SkinnyJob job = {w, x_dev, bias_dev, y_dev};
         return launch_skinny(ctx, &job, 1, x_dt, m, y_dt, stream);

@@ -1,0 +1,292 @@
+// Prefill product (M > 16) on the 5th-generation tensor cores: y[M, N] = x[M, K] * W[N, K]^T (+ bias)
+// with block-quantized W of any format.
+//
+// One CTA computes a (128 * MT) x 128 output tile (MT = 1, 2 or 4 accumulators of 128 x 128 f32
+// in tensor memory). Per 64-wide k step
+//   * 8 producer warps dequantize the 128 x 64 weight tile to bf16 (f32 decode, the bit-exact
+//     one, then round-to-nearest-even) and copy / convert the (128 * MT) x 64 activation tile,
+//     both written to shared memory in the K-major 128-byte-swizzled layout tcgen05 reads;
+//   * one thread issues 4 * MT tcgen05.mma (M 128, N 128, K 16, bf16 x bf16 -> f32) from shared
+//     memory descriptors into the accumulators and commits them onto the stage's "empty" barrier.
+// The larger MT, the more activation rows reuse each dequantized weight tile (the dequantization,
+// not the MMA, is the expensive part at small M). After the last k step the producer warps read
+// the accumulators back with tcgen05.ld, add the bias and store f32 / bf16.
+// Weights are rounded to bf16, so results carry the 1e-2 tolerance of the tensor path.
+// Every barrier wait is bounded; on a timeout the CTA records it, skips the rest and still frees
+// its tensor memory.
+#include <cuda_bf16.h>
+
+#include "decode.cuh"
+#include "gemm_tc.h"
+#include "sync.cuh"
+
+namespace nnq {
+
+constexpr int kTcProducerWarps = 8;
+constexpr int kTcThreads = (kTcProducerWarps + 1) * 32;
+constexpr int kTcBK = 64;                    // k per stage: one 128-byte swizzle row of bf16
+constexpr int kTcTileBytes = 128 * 128;      // 128 rows x 128 bytes
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);           // start address, leading byte offset (unused) = 1
+    uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);          // stride byte offset, descriptor version 1, SWIZZLE_128B
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// byte offset of 16-byte chunk c (0..7) of row r (0..127) inside a swizzled 128 x 128-byte tile
+__device__ __forceinline__ uint32_t swz(int r, int c) {
+    return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+template <int FMT, int MT, typename XT>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscales, const XT *__restrict__ x,
+               const float *__restrict__ bias, void *__restrict__ y, int64_t M, int64_t N, int64_t K, int y_dt,
+               int stages, int *status) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 1024-byte alignment of the tiles (the dynamic window is not guaranteed to start on one)
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int kStageBytes = (MT + 1) * kTcTileBytes;   // MT activation tiles, then the weight tile
+    __shared__ __align__(8) uint64_t bars[2 * 8 + 1];      // full[stages], empty[stages], accumulators ready
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t n0 = (int64_t)blockIdx.x * 128;
+    const int64_t m0 = (int64_t)blockIdx.y * 128 * MT;
+    const int nkb = (int)(K / kTcBK);
+    const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * 8, acc_s = full_s + 16 * 8;
+    constexpr uint32_t kTmemCols = 128 * MT;
+
+    if (tid == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full_s + 8 * s, kTcProducerWarps);
+            mbar_init(empty_s + 8 * s, 1);
+        }
+        mbar_init(acc_s, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kTcProducerWarps) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    bool ok = true;
+
+    if (warp < kTcProducerWarps) {
+        // ---------------- producers ----------------
+        const int64_t cpr = K / 32;                 // 32-weight chunks per weight row
+        const int brow = tid & 127, bhalf = tid >> 7;   // weight tile: row and which 32 of the 64 k
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int kb = 0; kb < nkb && ok; kb++) {
+            if (kb >= stages) ok = mbar_wait_fast(empty_s + 8 * slot, phase ^ 1u);
+            if (!ok) break;
+            uint8_t *stage = smem + (size_t)slot * kStageBytes;
+            // weight tile: 32 consecutive k of one row per thread, bit-exact f32 decode, then bf16
+            {
+                float wv[32];
+                if (n0 + brow < N) {
+                    Decode<FMT>::chunk(w, wscales, (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf, wv);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) wv[i] = 0.0f;
+                }
+                uint8_t *bt = stage + MT * kTcTileBytes;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint4 v = make_uint4(pack_bf16(wv[8 * c], wv[8 * c + 1]), pack_bf16(wv[8 * c + 2], wv[8 * c + 3]),
+                                         pack_bf16(wv[8 * c + 4], wv[8 * c + 5]), pack_bf16(wv[8 * c + 6], wv[8 * c + 7]));
+                    *reinterpret_cast<uint4 *>(bt + swz(brow, bhalf * 4 + c)) = v;
+                }
+            }
+            // activation tiles: 16-byte chunks (8 bf16), 8 per row
+            {
+                const int c = tid & 7;
+#pragma unroll 4
+                for (int r = tid >> 3; r < 128 * MT; r += kTcProducerWarps * 4) {
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    const int64_t row = m0 + r;
+                    if (row < M) {
+                        const XT *src = x + row * K + (int64_t)kb * kTcBK + c * 8;
+                        if (sizeof(XT) == 2) {
+                            v = __ldg(reinterpret_cast<const uint4 *>(src));
+                        } else {
+                            float4 a = __ldg(reinterpret_cast<const float4 *>(src));
+                            float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+                            v = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+                        }
+                    }
+                    *reinterpret_cast<uint4 *>(stage + (r >> 7) * kTcTileBytes + swz(r & 127, c)) = v;
+                }
+            }
+            fence_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_s + 8 * slot);
+            if (++slot == stages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
+        // ---------------- epilogue ----------------
+        if (ok) ok = mbar_wait_fast(acc_s, 0);
+        if (ok) {
+            tc_fence_after();
+            const int q = warp & 3, chalf = warp >> 2;   // TMEM lane quarter, column half
+#pragma unroll 1
+            for (int mt = 0; mt < MT; mt++) {
+                const int64_t row = m0 + mt * 128 + q * 32 + lane;
+#pragma unroll 1
+                for (int cc = 0; cc < 2; cc++) {
+                    const int col0 = chalf * 64 + cc * 32;
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * 128 + col0), v);
+                    if (row < M) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const int64_t col = n0 + col0 + i;
+                            if (col < N) {
+                                float f = __uint_as_float(v[i]);
+                                if (bias) f += __ldg(bias + col);
+                                if (y_dt == NNQ_F32) reinterpret_cast<float *>(y)[row * N + col] = f;
+                                else reinterpret_cast<__nv_bfloat16 *>(y)[row * N + col] = __float2bfloat16_rn(f);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    } else if (lane == 0) {
+        // ---------------- MMA issuer ----------------
+        // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = 128, M = 128
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int kb = 0; kb < nkb && ok; kb++) {
+            ok = mbar_wait_fast(full_s + 8 * slot, phase);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t stage_s = smem_u32(smem + (size_t)slot * kStageBytes);
+            const uint64_t db = smem_desc(stage_s + MT * kTcTileBytes);
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const uint64_t da = smem_desc(stage_s + mt * kTcTileBytes);
+#pragma unroll
+                for (int k = 0; k < 4; k++)   // 16 bf16 = 32 bytes = 2 descriptor units per k step
+                    umma_bf16(tmem_base + mt * 128, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            }
+            umma_commit(empty_s + 8 * slot);   // frees the stage when these MMAs have read it
+            if (++slot == stages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
+        if (ok) umma_commit(acc_s);            // accumulators complete
+    }
+    if (!ok) {
+        abort_s = 1;
+        if (lane == 0) atomicExch(status, 1);
+    }
+    __syncthreads();
+    if (warp == kTcProducerWarps) {
+        // with an aborted CTA, MMAs may still be in flight: give them a bounded chance to finish
+        if (abort_s) mbar_wait(acc_s, 0);
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+
+bool gemm_tc_supported(const nnq_weight *w, int64_t m) {
+    return w && w->d_raw && m >= 1 && w->k >= kTcBK && w->k % kTcBK == 0 && w->n >= 1;
+}
+
+template <int FMT, int MT, typename XT>
+static cudaError_t launch_one(const TcArgs &a, int *status, cudaStream_t stream) {
+    const int stage_bytes = (MT + 1) * kTcTileBytes;
+    int stages = MT == 4 ? 2 : (MT == 2 ? 4 : 6);
+    const int nkb = (int)(a.k / kTcBK);
+    if (stages > nkb) stages = nkb;
+    const int smem_bytes = stages * stage_bytes + 1024;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, MT, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)((a.m + 128 * MT - 1) / (128 * MT)));
+    gemm_tc_kernel<FMT, MT, XT><<<grid, kTcThreads, smem_bytes, stream>>>(
+        a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages, status);
+    return cudaGetLastError();
+}
+
+template <int FMT>
+static cudaError_t launch_fmt(const TcArgs &a, int *status, cudaStream_t stream) {
+    const bool f32 = a.x_dt == NNQ_F32;
+    if (a.m <= 128) return f32 ? launch_one<FMT, 1, float>(a, status, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, stream);
+    if (a.m <= 256) return f32 ? launch_one<FMT, 2, float>(a, status, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, stream);
+    return f32 ? launch_one<FMT, 4, float>(a, status, stream) : launch_one<FMT, 4, __nv_bfloat16>(a, status, stream);
+}
+
+nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
+    cudaError_t e;
+    switch (a.fmt) {
+        case NNQ_Q4_0: e = launch_fmt<NNQ_Q4_0>(a, ctx->d_status, stream); break;
+        case NNQ_Q4_1: e = launch_fmt<NNQ_Q4_1>(a, ctx->d_status, stream); break;
+        case NNQ_Q8_0: e = launch_fmt<NNQ_Q8_0>(a, ctx->d_status, stream); break;
+        case NNQ_Q4_K: e = launch_fmt<NNQ_Q4_K>(a, ctx->d_status, stream); break;
+        case NNQ_Q4_K_GGML: e = launch_fmt<NNQ_Q4_K_GGML>(a, ctx->d_status, stream); break;
+        case NNQ_Q6_K: e = launch_fmt<NNQ_Q6_K>(a, ctx->d_status, stream); break;
+        case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, ctx->d_status, stream); break;
+        case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, ctx->d_status, stream); break;
+        case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, ctx->d_status, stream); break;
+        default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
+    }
+    ctx->launches++;
+    return check_cuda(ctx, e, "tensor-core GEMM launch");
+}
+
+}  // namespace nnq

@@ -34,7 +34,13 @@ def _run(fmt, n, k, m, x_bf16, y_bf16, with_bias, seed=1, path=api.PATH_AUTO):
         t.backend.set_path(api.PATH_AUTO)
     y32, y64, mag = P.oracle_linear(fmt, w, sc, x, bias, n, k)
     got = y.float().cpu().numpy()
-    if y_bf16:
+    tensor_path = path == api.PATH_TENSOR or (path == api.PATH_AUTO and m > 16 and k % 64 == 0)
+    if tensor_path:
+        # weights (and f32 activations) are rounded to bf16 for the tensor cores: 1e-2 bar
+        assert np.all(np.isfinite(got))
+        assert P.max_rel_err(got, y32) <= P.TOL_BF16_MMA, P.max_rel_err(got, y32)
+        assert P.max_scaled_err(got, y64, mag) <= P.TOL_BF16_MMA
+    elif y_bf16:
         # output rounding to bf16 adds half an ulp (2^-9 relative) on top of the f32 bar
         assert P.max_rel_err(got, y32) <= P.TOL_F32_ACC + 2.0 ** -9
         ref_b = F.bf16_bits_to_f32(F.to_bf16_bits(y32)).reshape(y32.shape)
@@ -71,6 +77,46 @@ def test_q4_k_ragged_shapes(n, k):
 @pytest.mark.parametrize("m", [17, 33, 130])
 def test_q4_k_larger_m(m):
     _run(Q.Q4_K, 96, 1024, m, x_bf16=True, y_bf16=False, with_bias=False, seed=m)
+
+
+@pytest.mark.parametrize("fmt", list(Q))
+def test_tensor_path_all_formats(fmt):
+    _run(fmt, 200, 512, 150, x_bf16=True, y_bf16=False, with_bias=True, seed=71, path=api.PATH_TENSOR)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (128, 128, 256), (129, 130, 320), (300, 72, 1024), (512, 256, 2048),
+                                   (700, 384, 512)])
+@pytest.mark.parametrize("x_bf16,y_bf16", [(True, True), (False, False)])
+def test_tensor_path_shapes(m, n, k, x_bf16, y_bf16):
+    _run(Q.Q8_0, n, k, m, x_bf16, y_bf16, with_bias=False, seed=m + n, path=api.PATH_TENSOR)
+
+
+def test_tensor_path_is_exact_on_bf16_representable_weights():
+    # Q8_0 with power-of-two scales and small codes decodes to bf16-exact weights, bf16 x: the
+    # only difference from the oracle is the f32 summation order
+    n, k, m = 128, 512, 128
+    blk = np.zeros((n * k // 32, 34), np.uint8)
+    blk[:, 0:2] = np.frombuffer(np.float16(0.25).tobytes(), np.uint8)
+    blk[:, 2:] = (F.Stream(5).integers(n * k, -8, 7)).astype(np.int8).view(np.uint8).reshape(-1, 32)
+    w = blk.reshape(-1)
+    x = F.gen_activations(6, m, k, bf16=True)
+    t = api.from_quantized(w, Q.Q8_0, [n, k])
+    t.backend.set_path(api.PATH_TENSOR)
+    try:
+        y = api.quantized_matmul(torch.from_numpy(x).to(DEV).to(torch.bfloat16), t, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        t.backend.device_status()
+    finally:
+        t.backend.set_path(api.PATH_AUTO)
+    y32, y64, mag = P.oracle_linear(Q.Q8_0, w, None, x, None, n, k)
+    P.assert_close(y.cpu().numpy(), y32, y64, mag, tol=1e-5)
+    t.release()
+
+
+def test_config2_q4_k_m128_and_m512():
+    # benchmark configuration 2 at the prefill sizes: q_proj 4096 -> 4096
+    _run(Q.Q4_K, 4096, 4096, 128, x_bf16=True, y_bf16=True, with_bias=False, seed=0x5EF0)
+    _run(Q.Q4_K, 4096, 4096, 512, x_bf16=True, y_bf16=True, with_bias=False, seed=0x5EF1)
 
 
 def test_config1_q8_0_gemv_4096():
