@@ -167,7 +167,7 @@ def run_nnq(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
 
-    from nn_b200 import api
+    from nn_b200 import api, comm
     from nn_b200 import workload as W
     from nn_b200.formats import QuantFormat
 
@@ -179,6 +179,8 @@ def run_nnq(args, rank, world, local_rank):
     api.register_gpu_backend(backend)
     lib, ctx = backend._lib, backend._ctx
     m = args.m
+    # row-parallel partial outputs are summed by the library's one-shot all-reduce over peer memory
+    peer = comm.PeerComm(backend, rank, world, max_bytes=max(m, 1) * W.HIDDEN * 4) if world > 1 else None
     gen = torch.Generator(device=dev)
     gen.manual_seed(0x5EED)  # same weights on every rank, each keeps its shard
 
@@ -227,8 +229,10 @@ def run_nnq(args, rank, world, local_rank):
             st = lib.nnq_linear_batch(ctx, cnt, wh, xp, api.BF16, m, None, yp, api.BF16, stream_ptr)
             if st != 0:
                 backend.check(st)
-            if reduce_out is not None:
-                dist.all_reduce(reduce_out)  # row-parallel partial sums (o_proj, down_proj)
+            if reduce_out is not None:   # row-parallel partial sums (o_proj, down_proj)
+                st = peer.all_reduce_raw(reduce_out.data_ptr(), api.BF16, reduce_out.numel(), stream_ptr)
+                if st != 0:
+                    backend.check(st)
 
     stream = torch.cuda.Stream(device=dev)
     graph = None
@@ -238,7 +242,7 @@ def run_nnq(args, rank, world, local_rank):
             step(sp)
         stream.synchronize()
         backend.device_status(stream)
-        if not args.no_graph and world == 1:
+        if not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step(VP(torch.cuda.current_stream().cuda_stream))
@@ -270,7 +274,8 @@ def run_nnq(args, rank, world, local_rank):
     backend.device_status(stream)
     launched = backend.launch_count() - launches_before
     if graph is not None:
-        launched = launches_per_step * args.steps  # replays re-issue the captured kernels
+        n_reduce = sum(1 for c_ in calls if c_[4] is not None)
+        launched = (launches_per_step + n_reduce) * args.steps  # replays re-issue the captured kernels
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

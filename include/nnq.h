@@ -41,6 +41,7 @@ extern "C" {
 typedef struct nnq_ctx nnq_ctx;
 typedef struct nnq_weight nnq_weight;
 typedef struct nnq_moe nnq_moe;
+typedef struct nnq_comm nnq_comm;
 
 /* Status codes. The first group mirrors QuantizedMatmulError
  * (crates/nn-core/src/dyn_tensor/quantized_matmul.rs:30-76) and the storage
@@ -271,6 +272,24 @@ NNQ_API nnq_status nnq_moe_route(nnq_ctx *ctx, const nnq_moe *m, const void *x_d
  *     in the area needs clearing between calls. */
 NNQ_API nnq_status nnq_moe_forward_static(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt,
                                           int64_t tokens, float *y_dev, void *stream);
+
+/* ---- tensor-parallel exchange ------------------------------------------------------ */
+
+/* One-shot all-reduce (sum) of small vectors between the ranks of one NVLink box, one process
+ * per GPU: the partial outputs of row-parallel projections (o_proj, down_proj). The reference
+ * is single-device and has no counterpart. Set-up: every rank creates a communicator, publishes
+ * its 64-byte handle (nnq_comm_get_handle), gathers all ranks' handles in rank order by any
+ * host-side means and opens them (nnq_comm_open_peers). world <= 8; max_bytes bounds one message.
+ * nnq_comm_all_reduce sums `count` elements of `buf_dev` in place over all ranks (rank order,
+ * identical bits everywhere), is a single kernel without host synchronisation (graph-capturable),
+ * and must be called the same number of times, in the same order, by every rank. A peer that
+ * never arrives makes the bounded device wait run out: nnq_device_status then reports
+ * NNQ_ERR_TIMEOUT and the buffer contents are undefined. */
+NNQ_API nnq_status nnq_comm_create(nnq_ctx *ctx, int rank, int world, size_t max_bytes, nnq_comm **out);
+NNQ_API nnq_status nnq_comm_get_handle(nnq_comm *c, void *handle64);
+NNQ_API nnq_status nnq_comm_open_peers(nnq_comm *c, const void *handles);
+NNQ_API nnq_status nnq_comm_all_reduce(nnq_comm *c, void *buf_dev, nnq_dtype dt, int64_t count, void *stream);
+NNQ_API void nnq_comm_destroy(nnq_comm *c);
 
 /* Number of kernels this library has launched on this context since creation. */
 NNQ_API int64_t nnq_launch_count(const nnq_ctx *ctx);

@@ -1,0 +1,41 @@
+"""Tensor-parallel exchange between the ranks of one box (one process per GPU).
+
+``PeerComm`` wraps the library's one-shot all-reduce over peer-mapped buffers (nnq_comm_*);
+the handle exchange goes through ``torch.distributed`` (any backend: it is host data)."""
+from __future__ import annotations
+
+import ctypes
+
+from . import api
+
+
+class PeerComm:
+    def __init__(self, backend: api.Backend, rank: int, world: int, max_bytes: int = 1 << 16, group=None):
+        self.backend, self.rank, self.world = backend, rank, world
+        h = ctypes.c_void_p()
+        backend.check(backend._lib.nnq_comm_create(backend._ctx, rank, world, max_bytes, ctypes.byref(h)))
+        self._handle = h
+        if world > 1:
+            import torch.distributed as dist
+            mine = ctypes.create_string_buffer(64)
+            backend.check(backend._lib.nnq_comm_get_handle(h, mine))
+            gathered = [None] * world
+            dist.all_gather_object(gathered, bytes(mine.raw), group=group)
+            blob = ctypes.create_string_buffer(b"".join(gathered), 64 * world)
+            backend.check(backend._lib.nnq_comm_open_peers(h, blob))
+            dist.barrier(group=group)
+
+    def all_reduce(self, tensor, stream=None):
+        """In-place sum over the ranks of a contiguous f32 / bf16 CUDA tensor."""
+        b = self.backend
+        b.check(b._lib.nnq_comm_all_reduce(self._handle, tensor.data_ptr(), api._dtype_code(tensor), tensor.numel(),
+                                           api._stream_ptr(stream)))
+        return tensor
+
+    def all_reduce_raw(self, ptr: int, dtype_code: int, count: int, stream_ptr):
+        return self.backend._lib.nnq_comm_all_reduce(self._handle, ptr, dtype_code, count, stream_ptr)
+
+    def release(self):
+        if self._handle is not None:
+            self.backend._lib.nnq_comm_destroy(self._handle)
+            self._handle = None

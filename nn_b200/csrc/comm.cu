@@ -1,0 +1,215 @@
+// One-shot all-reduce for the small messages of tensor-parallel decode (the [M, hidden] partial
+// outputs of the row-parallel o_proj / down_proj: 8-16 KB at M = 1), over peer-mapped buffers on
+// one NVLink/NVSwitch box. The reference has no counterpart (it is single-device).
+//
+// Every rank owns a buffer with one slot per (source rank, parity) and one flag per source rank;
+// peers map it through CUDA IPC. A call with sequence number s (kept on the device, so that a
+// captured graph can be replayed):
+//   1. each rank stores its vector into slot[rank][s & 1] of every peer's buffer (plain peer stores),
+//   2. fences, then stores s into flag[rank] of every peer,
+//   3. waits (bounded) until its own flags from all peers show s,
+//   4. sums the slots in rank order (bit-identical on every rank) and writes the result in place.
+// Parity double-buffering is enough: a peer can be at most one call ahead, because call s + 1
+// cannot finish without this rank's flag for s + 1. A wait that runs out sets the context's
+// status word and the kernel returns (the result is then meaningless); nothing spins forever.
+// Only plain loads / stores to peer memory are used: no multimem, no bulk copies.
+#include <cuda_bf16.h>
+#include <string.h>
+
+#include <new>
+
+#include "nnq_internal.h"
+
+struct nnq_comm {
+    nnq_ctx *ctx;
+    int rank, world;
+    size_t slot_bytes;          // capacity of one message
+    uint8_t *d_local;           // this rank's buffer
+    uint8_t *peer[8];           // every rank's buffer as seen from here (peer[rank] == d_local)
+    bool opened[8];
+    uint8_t **d_peer_table;     // device copy of peer[]
+};
+
+namespace nnq {
+
+constexpr int kCommMaxWorld = 8;
+constexpr unsigned kCommSpins = 1u << 22;
+
+// buffer layout: [0, 64) epoch counter, [64, 128) flags (u32 per source rank), then
+// data[parity][source rank][slot_bytes]
+__host__ __device__ inline size_t comm_data_offset(int parity, int src, int world, size_t slot_bytes) {
+    return 256 + ((size_t)parity * world + src) * slot_bytes;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+// loads that bypass L1, so that data a peer has just stored is seen
+__device__ __forceinline__ float ld_fresh(const float *p) { return __ldcv(p); }
+__device__ __forceinline__ __nv_bfloat16 ld_fresh(const __nv_bfloat16 *p) {
+    unsigned short u = __ldcv(reinterpret_cast<const unsigned short *>(p));
+    return __ushort_as_bfloat16(u);
+}
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_oneshot_kernel(uint8_t *const *peers, int rank, int world, size_t slot_bytes, T *buf, int count, int *status) {
+    uint8_t *local = peers[rank];
+    __shared__ unsigned seq_s;
+    __shared__ int failed_s;
+    if (threadIdx.x == 0) {
+        seq_s = *reinterpret_cast<volatile unsigned *>(local) + 1u;
+        failed_s = 0;
+    }
+    __syncthreads();
+    const unsigned seq = seq_s;
+    const int parity = (int)(seq & 1u);
+    // 1. push this rank's vector into every peer (and into its own slot)
+    for (int p = 0; p < world; p++) {
+        T *dst = reinterpret_cast<T *>(peers[p] + comm_data_offset(parity, rank, world, slot_bytes));
+        for (int i = threadIdx.x; i < count; i += blockDim.x) dst[i] = buf[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    // 2. publish, 3. wait for everybody else's publication (one thread per peer)
+    if (threadIdx.x < world) {
+        const int p = threadIdx.x;
+        volatile unsigned *remote_flag = reinterpret_cast<volatile unsigned *>(peers[p] + 64) + rank;
+        *remote_flag = seq;
+        volatile unsigned *my_flag = reinterpret_cast<volatile unsigned *>(local + 64) + p;
+        unsigned spins = 0;
+        while ((int)(*my_flag - seq) < 0) {
+            if (++spins > kCommSpins) {
+                failed_s = 1;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    __threadfence_system();
+    if (failed_s) {
+        if (threadIdx.x == 0) atomicExch(status, 1);
+    } else {
+        // 4. sum in rank order
+        for (int i = threadIdx.x; i < count; i += blockDim.x) {
+            float acc = 0.0f;
+            for (int r = 0; r < world; r++) {
+                const T *src = reinterpret_cast<const T *>(local + comm_data_offset(parity, r, world, slot_bytes));
+                acc += to_f32<T>(ld_fresh(src + i));
+            }
+            buf[i] = from_f32<T>(acc);
+        }
+    }
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned *>(local) = seq;
+}
+
+}  // namespace nnq
+
+using namespace nnq;
+
+extern "C" {
+
+nnq_status nnq_comm_create(nnq_ctx *ctx, int rank, int world, size_t max_bytes, nnq_comm **out) {
+    if (!ctx || !out) return NNQ_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (world < 1 || world > kCommMaxWorld || rank < 0 || rank >= world || max_bytes == 0 || max_bytes > ((size_t)1 << 24))
+        return fail(ctx, NNQ_ERR_INVALID_ARG, "bad communicator spec rank=%d world=%d bytes=%zu", rank, world, max_bytes);
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    nnq_comm *c = new (std::nothrow) nnq_comm();
+    if (!c) return fail(ctx, NNQ_ERR_OUT_OF_MEMORY, "host allocation failed");
+    memset(c, 0, sizeof(*c));
+    c->ctx = ctx;
+    c->rank = rank;
+    c->world = world;
+    c->slot_bytes = (max_bytes + 255) & ~(size_t)255;
+    const size_t total = comm_data_offset(2, 0, world, c->slot_bytes);
+    s = check_cuda(ctx, cudaMalloc(&c->d_local, total), "cudaMalloc comm buffer");
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaMemset(c->d_local, 0, total), "cudaMemset comm buffer");
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaMalloc(&c->d_peer_table, sizeof(uint8_t *) * kCommMaxWorld), "cudaMalloc peer table");
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaDeviceSynchronize(), "comm init");
+    if (s != NNQ_OK) {
+        nnq_comm_destroy(c);
+        return s;
+    }
+    c->peer[rank] = c->d_local;
+    if (world == 1) s = check_cuda(ctx, cudaMemcpy(c->d_peer_table, c->peer, sizeof(c->peer), cudaMemcpyHostToDevice), "peer table");
+    if (s != NNQ_OK) {
+        nnq_comm_destroy(c);
+        return s;
+    }
+    *out = c;
+    return NNQ_OK;
+}
+
+nnq_status nnq_comm_get_handle(nnq_comm *c, void *handle64) {
+    if (!c || !handle64) return NNQ_ERR_INVALID_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaSetDevice(c->ctx->device);
+    cudaIpcMemHandle_t h;
+    nnq_status s = check_cuda(c->ctx, cudaIpcGetMemHandle(&h, c->d_local), "cudaIpcGetMemHandle");
+    if (s != NNQ_OK) return s;
+    memcpy(handle64, &h, 64);
+    return NNQ_OK;
+}
+
+nnq_status nnq_comm_open_peers(nnq_comm *c, const void *handles) {
+    if (!c || !handles) return NNQ_ERR_INVALID_ARG;
+    cudaSetDevice(c->ctx->device);
+    for (int p = 0; p < c->world; p++) {
+        if (p == c->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)handles + 64 * p, 64);
+        void *ptr = nullptr;
+        nnq_status s = check_cuda(c->ctx, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+        if (s != NNQ_OK) return s;
+        c->peer[p] = (uint8_t *)ptr;
+        c->opened[p] = true;
+    }
+    return check_cuda(c->ctx, cudaMemcpy(c->d_peer_table, c->peer, sizeof(c->peer), cudaMemcpyHostToDevice), "peer table");
+}
+
+nnq_status nnq_comm_all_reduce(nnq_comm *c, void *buf_dev, nnq_dtype dt, int64_t count, void *stream) {
+    if (!c) return NNQ_ERR_INVALID_ARG;
+    nnq_ctx *ctx = c->ctx;
+    if ((int)dt < 0 || dt > NNQ_BF16) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown dtype");
+    const size_t es = dt == NNQ_F32 ? 4 : 2;
+    if (count < 0 || (size_t)count * es > c->slot_bytes)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "message of %lld elements exceeds the communicator's %zu-byte slots", (long long)count, c->slot_bytes);
+    if (count == 0) return NNQ_OK;
+    if (!buf_dev) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
+    for (int p = 0; p < c->world; p++)
+        if (!c->peer[p]) return fail(ctx, NNQ_ERR_INVALID_ARG, "peer %d has not been opened", p);
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dt == NNQ_F32)
+        allreduce_oneshot_kernel<float><<<1, 512, 0, st>>>(c->d_peer_table, c->rank, c->world, c->slot_bytes, (float *)buf_dev, (int)count, ctx->d_status);
+    else
+        allreduce_oneshot_kernel<__nv_bfloat16><<<1, 512, 0, st>>>(c->d_peer_table, c->rank, c->world, c->slot_bytes, (__nv_bfloat16 *)buf_dev, (int)count, ctx->d_status);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "all-reduce launch");
+}
+
+void nnq_comm_destroy(nnq_comm *c) {
+    if (!c) return;
+    cudaSetDevice(c->ctx->device);
+    cudaDeviceSynchronize();
+    for (int p = 0; p < c->world; p++)
+        if (c->opened[p]) cudaIpcCloseMemHandle(c->peer[p]);
+    cudaFree(c->d_local);
+    cudaFree(c->d_peer_table);
+    cudaGetLastError();
+    delete c;
+}
+
+}  // extern "C"
