@@ -63,6 +63,10 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { retu
 template <typename T>
 __global__ void __launch_bounds__(512)
 allreduce_oneshot_kernel(uint8_t *const *peers, int rank, int world, size_t slot_bytes, T *buf, int count, int *status) {
+    // let the next kernel of the stream start (it only prefetches weights until this kernel has
+    // completed), and wait for the producer of `buf`
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint8_t *local = peers[rank];
     __shared__ unsigned seq_s;
     __shared__ int failed_s;
@@ -191,13 +195,28 @@ nnq_status nnq_comm_all_reduce(nnq_comm *c, void *buf_dev, nnq_dtype dt, int64_t
         if (!c->peer[p]) return fail(ctx, NNQ_ERR_INVALID_ARG, "peer %d has not been opened", p);
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
-    cudaStream_t st = (cudaStream_t)stream;
-    if (dt == NNQ_F32)
-        allreduce_oneshot_kernel<float><<<1, 512, 0, st>>>(c->d_peer_table, c->rank, c->world, c->slot_bytes, (float *)buf_dev, (int)count, ctx->d_status);
-    else
-        allreduce_oneshot_kernel<__nv_bfloat16><<<1, 512, 0, st>>>(c->d_peer_table, c->rank, c->world, c->slot_bytes, (__nv_bfloat16 *)buf_dev, (int)count, ctx->d_status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(512);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may become resident early; waits inside
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    uint8_t *const *table = c->d_peer_table;
+    int *status = ctx->d_status;
+    int cnt = (int)count;
+    cudaError_t e;
+    if (dt == NNQ_F32) {
+        float *b = (float *)buf_dev;
+        e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<float>, table, c->rank, c->world, c->slot_bytes, b, cnt, status);
+    } else {
+        __nv_bfloat16 *b = (__nv_bfloat16 *)buf_dev;
+        e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<__nv_bfloat16>, table, c->rank, c->world, c->slot_bytes, b, cnt, status);
+    }
     ctx->launches++;
-    return check_cuda(ctx, cudaGetLastError(), "all-reduce launch");
+    return check_cuda(ctx, e, "all-reduce launch");
 }
 
 void nnq_comm_destroy(nnq_comm *c) {
