@@ -39,7 +39,6 @@ namespace nnq {
 constexpr int kTileBytes = 2304;
 constexpr int kWarps = 8;          // compute warps per CTA; they split K of one row tile
 constexpr int kMaxStages = 4;      // bulk-copy ring depth per warp (tiles in flight)
-constexpr int kCtasPerSm = 2;
 constexpr int kSmemMax = 227 * 1024;         // one CTA per SM
 
 struct SkinnyJobDev {
@@ -371,7 +370,7 @@ __device__ __forceinline__ void issue_tile(uint32_t dst, const void *src, uint32
 // copies; with KS > 1 the partial sums of a row tile meet in shared memory and one of the KS
 // warps (in turn) writes the 16 outputs while the others already work on the next unit.
 template <bool F32X, int KS>
-__global__ void __launch_bounds__(kWarps * 32, kCtasPerSm)
+__global__ void __launch_bounds__(kWarps * 32, 2)
 skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     constexpr int RG = kWarps / KS;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -532,8 +531,8 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
         locate(unit, j, rt);
         float yg = 0.0f, yg8 = 0.0f;
         if (j >= 0) {
-#pragma unroll 1
             bool ok = true;
+#pragma unroll 1
             for (int k = 0; k < nkb; k++) {
                 ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
                 if (!(P.diag & 1))

@@ -257,3 +257,24 @@ def test_device_shard_equals_host_partition(fmt, axis):
         assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
         sh.release()
     full.release()
+
+
+@pytest.mark.parametrize("scale", [3.0e5, 1.0e-7, 1.0e30])
+@pytest.mark.parametrize("x_bf16", [True, False])
+def test_q4_k_activation_range(scale, x_bf16):
+    # the skinny kernel feeds fp16 to the tensor cores after an exact power-of-two prescale:
+    # very large and very small activations must come out as accurately as ordinary ones
+    n, k = 64, 1024
+    w, _ = F.gen_weight(Q.Q4_K, 90, n, k)
+    x = (F.gen_activations(91, 1, k, bf16=True) * np.float32(scale)).astype(np.float32)
+    if x_bf16:
+        x = F.bf16_bits_to_f32(F.to_bf16_bits(x)).reshape(1, k)
+    t = api.from_quantized(w, Q.Q4_K, [n, k])
+    xt = torch.from_numpy(x).to(DEV)
+    if x_bf16:
+        xt = xt.to(torch.bfloat16)
+    y = api.quantized_matmul(xt, t, out_dtype=torch.float32).cpu().numpy()
+    t.backend.device_status()
+    y32, y64, mag = P.oracle_linear(Q.Q4_K, w, None, x, None, n, k)
+    P.assert_close(y, y32, y64, mag)
+    t.release()
