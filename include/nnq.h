@@ -237,6 +237,20 @@ NNQ_API nnq_status nnq_moe_create(nnq_ctx *ctx, int n_experts, int hidden, int i
                                   size_t gate_up_scales_bytes, const float *gate_up_bias,
                                   const void *down, size_t down_bytes, const void *down_scales,
                                   size_t down_scales_bytes, const float *down_bias, nnq_moe **out);
+/* Expert-parallel shard of the same block: this device holds experts [expert_begin,
+ * expert_begin + expert_count) only (the expert tensors and biases passed cover just those),
+ * the router covers all n_experts. nnq_moe_forward on a shard adds up the contributions of the
+ * local experts; with activations replicated on every rank, the sum of the shards' outputs over
+ * the ranks (an all-reduce) is the full block's output. The reference is single-device and has
+ * no counterpart. */
+NNQ_API nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, int expert_count,
+                                        int hidden, int inter, int top_k, float swiglu_limit,
+                                        const float *router_w, const float *router_b, nnq_moe_layout layout,
+                                        nnq_format fmt, const void *gate_up, size_t gate_up_bytes,
+                                        const void *gate_up_scales, size_t gate_up_scales_bytes,
+                                        const float *gate_up_bias, const void *down, size_t down_bytes,
+                                        const void *down_scales, size_t down_scales_bytes,
+                                        const float *down_bias, nnq_moe **out);
 NNQ_API void nnq_moe_destroy(nnq_moe *m);
 
 /* y[T, hidden] (f32) = MoE(x[T, hidden]): router linear, softmax over all experts, top-k,

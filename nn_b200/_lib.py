@@ -50,6 +50,9 @@ SIGNATURES = {
     "nnq_moe_create": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_void_p, c_int, c_int,
                                c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p,
                                c_size_t, c_void_p, ctypes.POINTER(c_void_p)]),
+    "nnq_moe_create_shard": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_float, c_void_p,
+                                     c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p,
+                                     c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, ctypes.POINTER(c_void_p)]),
     "nnq_moe_destroy": (None, [c_void_p]),
     "nnq_moe_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "nnq_moe_forward_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]),

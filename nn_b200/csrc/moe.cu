@@ -97,8 +97,9 @@ moe_router_kernel(const XT *__restrict__ x, const float *__restrict__ rw, const 
 // block e counts (pass 0) or lists (pass 1) the assignments of expert e in flat order
 __global__ void __launch_bounds__(256)
 moe_group_kernel(const int *__restrict__ idx, int total, int *__restrict__ count, const int *__restrict__ offset,
-                 int *__restrict__ rowtok, int *__restrict__ pos, int pass) {
-    const int e = blockIdx.x;
+                 int *__restrict__ rowtok, int *__restrict__ pos, int pass, int e_begin) {
+    const int el = blockIdx.x;          // local expert (this device holds experts e_begin .. e_begin + gridDim.x)
+    const int e = e_begin + el;
     __shared__ int warp_sums[8];
     __shared__ int base;
     if (threadIdx.x == 0) base = 0;
@@ -114,7 +115,7 @@ moe_group_kernel(const int *__restrict__ idx, int total, int *__restrict__ count
         for (int w = 0; w < warp; w++) before += warp_sums[w];
         int mine = base + before + __popc(ballot & ((1u << lane) - 1u));
         if (pass == 1 && hit) {
-            int row = offset[e] + mine;
+            int row = offset[el] + mine;
             rowtok[row] = i;
             pos[i] = row;
         }
@@ -126,7 +127,7 @@ moe_group_kernel(const int *__restrict__ idx, int total, int *__restrict__ count
         }
         __syncthreads();
     }
-    if (pass == 0 && threadIdx.x == 0) count[e] = base;
+    if (pass == 0 && threadIdx.x == 0) count[el] = base;
 }
 
 __global__ void moe_scan_kernel(const int *__restrict__ count, int *__restrict__ offset, int E) {
@@ -292,7 +293,9 @@ __global__ void moe_combine_kernel(const float *__restrict__ o, const int *__res
         float acc = 0.0f;
         for (int s = 0; s < top_k; s++) {
             int slot = order[s];
-            float v = o[(size_t)pos[(int64_t)t * top_k + slot] * H + j];
+            int row = pos[(int64_t)t * top_k + slot];
+            if (row < 0) continue;   // expert held by another device
+            float v = o[(size_t)row * H + j];
             acc = __fadd_rn(acc, __fmul_rn(v, wt[(int64_t)t * top_k + slot]));
         }
         y[(size_t)t * H + j] = acc;
@@ -320,8 +323,8 @@ static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
     s.idx = (int *)take(R * 4);
     s.wt = (float *)take(R * 4);
     s.pos = (int *)take(R * 4);
-    s.count = (int *)take((size_t)m->n_experts * 4);
-    s.offset = (int *)take((size_t)(m->n_experts + 1) * 4);
+    s.count = (int *)take((size_t)m->e_local * 4);
+    s.offset = (int *)take((size_t)(m->e_local + 1) * 4);
     s.rowtok = (int *)take(R * 4);
     s.gu = (float *)take((size_t)R * 2 * m->inter * 4);
     s.h = (float *)take((size_t)R * m->inter * 4);
@@ -352,7 +355,7 @@ static void launch_product(const nnq_moe *m, bool first, const XT *x, const int 
     const uint8_t *d = first ? m->d_gu : m->d_dn;
     const uint8_t *sc = first ? m->d_gu_scales : m->d_dn_scales;
     const float *b = first ? m->d_gu_bias : m->d_dn_bias;
-    const int E = m->n_experts;
+    const int E = m->e_local;
     if (m->layout == NNQ_MOE_KN_GPTOSS) {
         dim3 grid((N + 1023) / 1024, E);
         moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, m->top_k, s.offset, out, K, N);
@@ -383,12 +386,14 @@ static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int
     if (idx_out) cudaMemcpyAsync(idx_out, s.idx, (size_t)total * 4, cudaMemcpyDeviceToDevice, st);
     if (wt_out) cudaMemcpyAsync(wt_out, s.wt, (size_t)total * 4, cudaMemcpyDeviceToDevice, st);
     if (route_only) return check_cuda(ctx, cudaGetLastError(), "MoE router launch");
-    moe_group_kernel<<<E, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0);
-    moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, E);
-    moe_group_kernel<<<E, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1);
+    const int EL = m->e_local;
+    if (EL != E) cudaMemsetAsync(s.pos, 0xFF, (size_t)total * 4, st);   // -1: assignment served elsewhere
+    moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
+    moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
+    moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
     launch_product<XT>(m, true, x, s.rowtok, s, s.gu, st);
     int64_t hi = (int64_t)total * m->inter;
-    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, E, m->inter, m->limit);
+    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit);
     launch_product<float>(m, false, s.h, nullptr, s, s.o, st);
     moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y);
     ctx->launches += 7;
@@ -429,12 +434,14 @@ static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, 
     const int E = m->n_experts, k = m->top_k;
     const int total = (int)(T * k);
     moe_router_kernel<XT><<<(int)((T + 3) / 4), 128, 0, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, E, k, s.idx, s.wt);
-    moe_group_kernel<<<E, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0);
-    moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, E);
-    moe_group_kernel<<<E, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1);
+    const int EL = m->e_local;
+    if (EL != E) cudaMemsetAsync(s.pos, 0xFF, (size_t)total * 4, st);   // -1: assignment served elsewhere
+    moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
+    moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
+    moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
     launch_product<XT>(m, true, x, s.rowtok, s, s.gu, st);
     int64_t hi = (int64_t)total * m->inter;
-    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, E, m->inter, m->limit);
+    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit);
     launch_product<float>(m, false, s.h, nullptr, s, s.o, st);
     moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y);
     ctx->launches += 8;
@@ -455,17 +462,20 @@ static nnq_status upload(nnq_ctx *ctx, void **dst, const void *src, size_t bytes
     return check_cuda(ctx, cudaMemcpy(*dst, src, bytes, cudaMemcpyDefault), what);
 }
 
-nnq_status nnq_moe_create(nnq_ctx *ctx, int n_experts, int hidden, int inter, int top_k, float swiglu_limit,
-                          const float *router_w, const float *router_b, nnq_moe_layout layout, nnq_format fmt,
-                          const void *gate_up, size_t gate_up_bytes, const void *gate_up_scales,
-                          size_t gate_up_scales_bytes, const float *gate_up_bias, const void *down,
-                          size_t down_bytes, const void *down_scales, size_t down_scales_bytes,
-                          const float *down_bias, nnq_moe **out) {
+nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, int expert_count, int hidden,
+                                int inter, int top_k, float swiglu_limit, const float *router_w,
+                                const float *router_b, nnq_moe_layout layout, nnq_format fmt, const void *gate_up,
+                                size_t gate_up_bytes, const void *gate_up_scales, size_t gate_up_scales_bytes,
+                                const float *gate_up_bias, const void *down, size_t down_bytes,
+                                const void *down_scales, size_t down_scales_bytes, const float *down_bias,
+                                nnq_moe **out) {
     if (!ctx || !out) return NNQ_ERR_INVALID_ARG;
     *out = nullptr;
     if (n_experts < 1 || n_experts > kMaxExperts || top_k < 1 || top_k > kMaxTopK || top_k > n_experts ||
         hidden < 1 || inter < 1)
         return fail(ctx, NNQ_ERR_INVALID_ARG, "bad MoE dimensions (experts %d, top_k %d, hidden %d, inter %d)", n_experts, top_k, hidden, inter);
+    if (expert_begin < 0 || expert_count < 1 || expert_begin + expert_count > n_experts)
+        return fail(ctx, NNQ_ERR_INVALID_ARG, "bad expert range [%d, %d) of %d", expert_begin, expert_begin + expert_count, n_experts);
     if (!router_w || !router_b || !gate_up || !down || !gate_up_bias || !down_bias) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL MoE tensor");
     if ((int)fmt < 0 || fmt >= NNQ_FORMAT_COUNT) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", (int)fmt);
     if (layout == NNQ_MOE_KN_GPTOSS && fmt != NNQ_MXFP4_GPTOSS)
@@ -477,8 +487,8 @@ nnq_status nnq_moe_create(nnq_ctx *ctx, int n_experts, int hidden, int inter, in
     const int64_t dn_inner = layout == NNQ_MOE_KN_GPTOSS ? hidden : inter;
     if (gu_inner % g.elems || dn_inner % g.elems)
         return fail(ctx, NNQ_ERR_INVALID_SHAPE, "expert dimensions are not multiples of the block size %d", g.elems);
-    const size_t gu_blocks = (size_t)n_experts * hidden * 2 * inter / g.elems;
-    const size_t dn_blocks = (size_t)n_experts * inter * hidden / g.elems;
+    const size_t gu_blocks = (size_t)expert_count * hidden * 2 * inter / g.elems;
+    const size_t dn_blocks = (size_t)expert_count * inter * hidden / g.elems;
     if (gate_up_bytes != gu_blocks * g.bytes || down_bytes != dn_blocks * g.bytes ||
         gate_up_scales_bytes != gu_blocks * g.scale_bytes || down_scales_bytes != dn_blocks * g.scale_bytes)
         return fail(ctx, NNQ_ERR_DATA_LENGTH, "expert tensor byte length does not match its shape");
@@ -489,6 +499,7 @@ nnq_status nnq_moe_create(nnq_ctx *ctx, int n_experts, int hidden, int inter, in
     if (!m) return fail(ctx, NNQ_ERR_OUT_OF_MEMORY, "host allocation failed");
     memset(m, 0, sizeof(*m));
     m->ctx = ctx; m->n_experts = n_experts; m->hidden = hidden; m->inter = inter; m->top_k = top_k;
+    m->e_begin = expert_begin; m->e_local = expert_count;
     m->limit = swiglu_limit; m->layout = layout; m->fmt = fmt;
     m->gu_bytes = gate_up_bytes; m->gu_scale_bytes = gate_up_scales_bytes;
     m->dn_bytes = down_bytes; m->dn_scale_bytes = down_scales_bytes;
@@ -496,16 +507,27 @@ nnq_status nnq_moe_create(nnq_ctx *ctx, int n_experts, int hidden, int inter, in
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_router_b, router_b, (size_t)n_experts * 4, "router bias");
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_gu, gate_up, gate_up_bytes, "gate_up");
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_gu_scales, gate_up_scales, gate_up_scales_bytes, "gate_up scales");
-    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_gu_bias, gate_up_bias, (size_t)n_experts * 2 * inter * 4, "gate_up bias");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_gu_bias, gate_up_bias, (size_t)expert_count * 2 * inter * 4, "gate_up bias");
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn, down, down_bytes, "down");
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_scales, down_scales, down_scales_bytes, "down scales");
-    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_bias, down_bias, (size_t)n_experts * hidden * 4, "down bias");
+    if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_bias, down_bias, (size_t)expert_count * hidden * 4, "down bias");
     if (s != NNQ_OK) {
         nnq_moe_destroy(m);
         return s;
     }
     *out = m;
     return NNQ_OK;
+}
+
+nnq_status nnq_moe_create(nnq_ctx *ctx, int n_experts, int hidden, int inter, int top_k, float swiglu_limit,
+                          const float *router_w, const float *router_b, nnq_moe_layout layout, nnq_format fmt,
+                          const void *gate_up, size_t gate_up_bytes, const void *gate_up_scales,
+                          size_t gate_up_scales_bytes, const float *gate_up_bias, const void *down,
+                          size_t down_bytes, const void *down_scales, size_t down_scales_bytes,
+                          const float *down_bias, nnq_moe **out) {
+    return nnq_moe_create_shard(ctx, n_experts, 0, n_experts, hidden, inter, top_k, swiglu_limit, router_w, router_b,
+                                layout, fmt, gate_up, gate_up_bytes, gate_up_scales, gate_up_scales_bytes,
+                                gate_up_bias, down, down_bytes, down_scales, down_scales_bytes, down_bias, out);
 }
 
 void nnq_moe_destroy(nnq_moe *m) {

@@ -5,6 +5,7 @@
 struct nnq_moe {
     nnq_ctx *ctx;
     int n_experts, hidden, inter, top_k;
+    int e_begin, e_local;  // experts held by this device: [e_begin, e_begin + e_local)
     float limit;
     int layout;            // nnq_moe_layout
     int fmt;               // nnq_format of the expert weights

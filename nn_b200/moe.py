@@ -33,7 +33,8 @@ class MoeBlock:
     """
 
     def __init__(self, n_experts, hidden, inter, top_k, swiglu_limit, router_w, router_b, layout, fmt,
-                 gate_up, gate_up_scales, gate_up_bias, down, down_scales, down_bias, backend=None):
+                 gate_up, gate_up_scales, gate_up_bias, down, down_scales, down_bias, backend=None,
+                 expert_range=None):
         self.backend = backend or api.gpu_backend()
         self.n_experts, self.hidden, self.inter, self.top_k = n_experts, hidden, inter, top_k
         b = self.backend
@@ -42,14 +43,18 @@ class MoeBlock:
         dn, dns, dnb = _u8(down), _u8(down_scales), _f32(down_bias)
         if rw.shape != (n_experts, hidden) or rb.shape != (n_experts,):
             raise api.InvalidShape("router weight must be [E, hidden] and router bias [E]")
-        if gub.shape != (n_experts, 2 * inter) or dnb.shape != (n_experts, hidden):
+        e0, ec = expert_range if expert_range is not None else (0, n_experts)
+        if gub.shape != (ec, 2 * inter) or dnb.shape != (ec, hidden):
             raise api.BiasMismatch("expert biases must be [E, 2*inter] and [E, hidden]")
         h = ctypes.c_void_p()
         p = lambda a: None if a is None else a.ctypes.data
         n = lambda a: 0 if a is None else a.size
-        b.check(b._lib.nnq_moe_create(b._ctx, n_experts, hidden, inter, top_k, ctypes.c_float(swiglu_limit),
-                                      p(rw), p(rb), int(layout), int(QuantFormat(fmt)), p(gu), n(gu), p(gus), n(gus),
-                                      p(gub), p(dn), n(dn), p(dns), n(dns), p(dnb), ctypes.byref(h)))
+        # expert_range = (first expert, count): an expert-parallel shard holding only those experts'
+        # tensors; the router always covers all experts
+        b.check(b._lib.nnq_moe_create_shard(b._ctx, n_experts, e0, ec, hidden, inter, top_k,
+                                            ctypes.c_float(swiglu_limit), p(rw), p(rb), int(layout),
+                                            int(QuantFormat(fmt)), p(gu), n(gu), p(gus), n(gus), p(gub), p(dn),
+                                            n(dn), p(dns), n(dns), p(dnb), ctypes.byref(h)))
         self._handle = h
 
     def forward(self, x):

@@ -85,3 +85,36 @@ def test_moe_argument_errors():
         blk(torch.zeros(3, H + 1, device=DEV))
     assert tuple(blk(torch.zeros(0, H, device=DEV)).shape) == (0, H)
     blk.release()
+
+
+@pytest.mark.parametrize("layout,fmt", [(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS), (moe.LAYOUT_NK, Q.MXFP4_SPLIT)])
+def test_expert_parallel_shards_sum_to_full_block(layout, fmt):
+    # expert parallelism with replicated activations: every "rank" holds E / p experts; the sum of
+    # the shard outputs (what the all-reduce forms) equals the full block
+    E, H, I, k, T, world = 8, 256, 256, 4, 33, 4
+    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(layout, fmt, E, H, I, 300)
+    x = F.gen_activations(301, T, H, bf16=True)
+    xt = torch.from_numpy(x).to(DEV)
+    full = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, layout, fmt, gu, gus, bgu, dn, dns, bd)
+    y_full = full(xt)
+    ec = E // world
+    gu2 = np.asarray(gu).reshape(E, -1)
+    dn2 = np.asarray(dn).reshape(E, -1)
+    gus2 = np.asarray(gus).reshape(E, -1)
+    dns2 = np.asarray(dns).reshape(E, -1)
+    total = torch.zeros_like(y_full)
+    for r in range(world):
+        sl = slice(r * ec, (r + 1) * ec)
+        shard = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, layout, fmt, gu2[sl], gus2[sl], bgu[sl], dn2[sl], dns2[sl],
+                             bd[sl], expert_range=(r * ec, ec))
+        idx_s, wt_s = shard.route(xt)
+        idx_f, wt_f = full.route(xt)
+        assert torch.equal(idx_s, idx_f) and torch.equal(wt_s, wt_f)   # routing is replicated
+        total += shard(xt)
+        shard.release()
+    torch.cuda.synchronize()
+    err = float((total - y_full).abs().max() / y_full.abs().max())
+    assert err <= 1e-5, err
+    y_ref, _, _ = orc.moe_forward(x, rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
+    assert np.max(np.abs(total.cpu().numpy() - y_ref)) / np.max(np.abs(y_ref)) <= 2e-3
+    full.release()
