@@ -276,9 +276,10 @@ NNQ_API nnq_status nnq_moe_route(nnq_ctx *ctx, const nnq_moe *m, const void *x_d
  * device image (held by every GPU that loads the library until the process exits) instead of the
  * context's growable scratch buffer, and the call performs no allocation of any kind.
  * Limits and rules:
- *   - tokens * top_k * (3*inter + hidden) * 4 bytes (plus small tables) must fit the 8 MiB area,
- *     e.g. 182 routed rows (45 tokens at top-4) at gpt-oss-20b's hidden = inter = 2880; larger calls are rejected with
- *     NNQ_ERR_UNSUPPORTED and a message naming both sizes;
+ *   - tokens * top_k * ((2*inter + hidden) * s + inter) * 4 bytes (plus small tables) must fit the
+ *     8 MiB area, with s = 4 for the [E,K,N] layout (partial sums per K slice) and s = 1 otherwise:
+ *     55 routed rows (13 tokens at top-4) at gpt-oss-20b's hidden = inter = 2880 in the [E,K,N]
+ *     layout; larger calls are rejected with NNQ_ERR_UNSUPPORTED and a message naming both sizes;
  *   - the first call on a device looks up the area's address (cudaGetSymbolAddress); make that
  *     first call before any stream capture;
  *   - all calls on a device share the area: two calls whose kernels overlap on the GPU (different

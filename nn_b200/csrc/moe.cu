@@ -159,20 +159,31 @@ __device__ __forceinline__ const XT *act_row(const XT *x, const int *rowtok, int
 // Weights stored [E][K][N] with MXFP4 blocks of 32 running along N (nn-gptoss Mxfp4Tensor over
 // the flattened [ne, K, N] tensor: crates/nn-gptoss/src/quantized_model.rs:69-77,
 // crates/nn-gptoss/src/quantize.rs:122-163): out[r, n] = sum_k x[r, k] * W[e, k, n] + bias[e, n].
-// A warp owns 256 consecutive columns (4 bytes of codes per lane and k); k runs sequentially.
+// A warp owns 256 consecutive columns (4 bytes of codes per lane and k) and one of gridDim.z
+// slices of K; it keeps 8 rows of weights in flight per lane. Slice z writes its partial sums to
+// out + z * slice_stride (slice 0 adds the bias); the consumer kernels add the slices in order.
+constexpr int kMoeKnSplit = 4;
+constexpr int kMoeKnUnroll = 8;
+
 template <typename XT>
 __global__ void __launch_bounds__(128)
 moe_kn_gptoss_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict__ scales,
                      const float *__restrict__ bias, const XT *__restrict__ x, const int *__restrict__ rowtok,
-                     int top_k, const int *__restrict__ offset, float *__restrict__ out, int K, int N) {
+                     int top_k, const int *__restrict__ offset, float *__restrict__ out, size_t slice_stride,
+                     int K, int N) {
     __shared__ float xt[kMoeMT][kMoeKCH];
     const int e = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n0 = blockIdx.x * 1024 + warp * 256 + lane * 8;
     const bool col_ok = n0 < N;
-    const uint8_t *wd = data + (size_t)e * K * (N / 2);
-    const uint8_t *ws = scales + (size_t)e * K * (N / 32);
+    const uint8_t *wd = data + (size_t)e * K * (N / 2) + n0 / 2;
+    const uint8_t *ws = scales + (size_t)e * K * (N / 32) + n0 / 32;
     const int r_begin = offset[e], r_end = offset[e + 1];
+    // this CTA's slice of K (whole chunks of kMoeKCH)
+    const int chunks = (K + kMoeKCH - 1) / kMoeKCH;
+    const int c_lo = (int)(((long long)blockIdx.z * chunks) / gridDim.z);
+    const int c_hi = (int)(((long long)(blockIdx.z + 1) * chunks) / gridDim.z);
+    float *po = out + (size_t)blockIdx.z * slice_stride;
     for (int r0 = r_begin; r0 < r_end; r0 += kMoeMT) {
         const int mt = min(kMoeMT, r_end - r0);
         float acc[kMoeMT][8];
@@ -180,7 +191,8 @@ moe_kn_gptoss_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict
         for (int t = 0; t < kMoeMT; t++)
 #pragma unroll
             for (int c = 0; c < 8; c++) acc[t][c] = 0.0f;
-        for (int k0 = 0; k0 < K; k0 += kMoeKCH) {
+        for (int ch = c_lo; ch < c_hi; ch++) {
+            const int k0 = ch * kMoeKCH;
             const int kn = min(kMoeKCH, K - k0);
             __syncthreads();
             for (int i = threadIdx.x; i < kMoeMT * kMoeKCH; i += 128) {
@@ -191,31 +203,42 @@ moe_kn_gptoss_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict
             }
             __syncthreads();
             if (col_ok) {
-                for (int kk = 0; kk < kn; kk++) {
-                    const size_t k = (size_t)(k0 + kk);
-                    uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(wd + k * (N / 2) + n0 / 2));
-                    float scale = mx_scale_gptoss(__ldg(ws + k * (N / 32) + n0 / 32));
-                    float wv[8];
+                for (int kk = 0; kk < kn; kk += kMoeKnUnroll) {
+                    uint32_t w[kMoeKnUnroll];
+                    uint32_t sc[kMoeKnUnroll];
 #pragma unroll
-                    for (int b = 0; b < 4; b++) {
-                        uint32_t byte = (w >> (8 * b)) & 0xFFu;
-                        wv[2 * b] = e2m1_value(byte >> 4, scale);       // high nibble = even column
-                        wv[2 * b + 1] = e2m1_value(byte & 15u, scale);
+                    for (int u = 0; u < kMoeKnUnroll; u++) {   // all loads first: 8 rows in flight
+                        const size_t k = (size_t)(k0 + min(kk + u, kn - 1));
+                        w[u] = __ldg(reinterpret_cast<const uint32_t *>(wd + k * (N / 2)));
+                        sc[u] = __ldg(ws + k * (N / 32));
                     }
 #pragma unroll
-                    for (int t = 0; t < kMoeMT; t++) {
-                        float xv = xt[t][kk];
+                    for (int u = 0; u < kMoeKnUnroll; u++) {
+                        if (kk + u < kn) {
+                            float scale = mx_scale_gptoss(sc[u]);
+                            float wv[8];
 #pragma unroll
-                        for (int c = 0; c < 8; c++) acc[t][c] = fmaf(xv, wv[c], acc[t][c]);
+                            for (int b = 0; b < 4; b++) {
+                                uint32_t byte = (w[u] >> (8 * b)) & 0xFFu;
+                                wv[2 * b] = e2m1_value(byte >> 4, scale);       // high nibble = even column
+                                wv[2 * b + 1] = e2m1_value(byte & 15u, scale);
+                            }
+#pragma unroll
+                            for (int t = 0; t < kMoeMT; t++) {
+                                float xv = xt[t][kk + u];
+#pragma unroll
+                                for (int c = 0; c < 8; c++) acc[t][c] = fmaf(xv, wv[c], acc[t][c]);
+                            }
+                        }
                     }
                 }
             }
         }
         if (col_ok) {
             for (int t = 0; t < mt; t++) {
-                float *o = out + (size_t)(r0 + t) * N + n0;
+                float *o = po + (size_t)(r0 + t) * N + n0;
 #pragma unroll
-                for (int c = 0; c < 8; c++) o[c] = acc[t][c] + __ldg(bias + (size_t)e * N + n0 + c);
+                for (int c = 0; c < 8; c++) o[c] = acc[t][c] + (blockIdx.z == 0 ? __ldg(bias + (size_t)e * N + n0 + c) : 0.0f);
             }
         }
     }
@@ -266,12 +289,15 @@ moe_nk_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict__ scal
 
 // h[r, j] = clamp(silu(gu[r, j]), -limit, limit) * gu[r, I + j]   (gate = first half, up = second half)
 __global__ void moe_swiglu_kernel(const float *__restrict__ gu, float *__restrict__ h, const int *__restrict__ offset,
-                                  int E, int inter, float limit) {
+                                  int E, int inter, float limit, int slices, size_t slice_stride) {
     const int64_t total = (int64_t)offset[E] * inter;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int64_t r = i / inter, j = i % inter;
-        float g = gu[r * 2 * inter + j];
-        float u = gu[r * 2 * inter + inter + j];
+        float g = 0.0f, u = 0.0f;
+        for (int z = 0; z < slices; z++) {   // K slices of the first product, in order
+            g += gu[z * slice_stride + r * 2 * inter + j];
+            u += gu[z * slice_stride + r * 2 * inter + inter + j];
+        }
         float s = g / (1.0f + expf(-g));
         s = fminf(fmaxf(s, -limit), limit);
         h[i] = s * u;
@@ -280,7 +306,8 @@ __global__ void moe_swiglu_kernel(const float *__restrict__ gu, float *__restric
 
 // y[t, :] = sum over the token's experts, in expert-index order, of weight * o[row, :]
 __global__ void moe_combine_kernel(const float *__restrict__ o, const int *__restrict__ idx, const float *__restrict__ wt,
-                                   const int *__restrict__ pos, int T, int H, int top_k, float *__restrict__ y) {
+                                   const int *__restrict__ pos, int T, int H, int top_k, float *__restrict__ y,
+                                   int slices, size_t slice_stride) {
     const int t = blockIdx.x;
     if (t >= T) return;
     int order[kMaxTopK];
@@ -295,7 +322,8 @@ __global__ void moe_combine_kernel(const float *__restrict__ o, const int *__res
             int slot = order[s];
             int row = pos[(int64_t)t * top_k + slot];
             if (row < 0) continue;   // expert held by another device
-            float v = o[(size_t)row * H + j];
+            float v = 0.0f;
+            for (int z = 0; z < slices; z++) v += o[z * slice_stride + (size_t)row * H + j];   // K slices, in order
             acc = __fadd_rn(acc, __fmul_rn(v, wt[(int64_t)t * top_k + slot]));
         }
         y[(size_t)t * H + j] = acc;
@@ -309,6 +337,8 @@ __global__ void moe_combine_kernel(const float *__restrict__ o, const int *__res
 struct MoeScratch {
     int *idx, *pos, *count, *offset, *rowtok;
     float *wt, *gu, *h, *o;
+    int slices;                 // K slices whose partial sums gu / o hold (1 = complete sums)
+    size_t gu_stride, o_stride; // floats between slices
     size_t bytes;
 };
 
@@ -326,9 +356,13 @@ static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
     s.count = (int *)take((size_t)m->e_local * 4);
     s.offset = (int *)take((size_t)(m->e_local + 1) * 4);
     s.rowtok = (int *)take(R * 4);
-    s.gu = (float *)take((size_t)R * 2 * m->inter * 4);
+    const int slices = m->layout == NNQ_MOE_KN_GPTOSS ? kMoeKnSplit : 1;   // partial sums per K slice
+    s.gu = (float *)take((size_t)R * 2 * m->inter * 4 * slices);
     s.h = (float *)take((size_t)R * m->inter * 4);
-    s.o = (float *)take((size_t)R * m->hidden * 4);
+    s.o = (float *)take((size_t)R * m->hidden * 4 * slices);
+    s.slices = slices;
+    s.gu_stride = (size_t)R * 2 * m->inter;
+    s.o_stride = (size_t)R * m->hidden;
     s.bytes = off;
     return s;
 }
@@ -357,8 +391,9 @@ static void launch_product(const nnq_moe *m, bool first, const XT *x, const int 
     const float *b = first ? m->d_gu_bias : m->d_dn_bias;
     const int E = m->e_local;
     if (m->layout == NNQ_MOE_KN_GPTOSS) {
-        dim3 grid((N + 1023) / 1024, E);
-        moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, m->top_k, s.offset, out, K, N);
+        dim3 grid((N + 1023) / 1024, E, kMoeKnSplit);
+        moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, m->top_k, s.offset, out,
+                                                        first ? s.gu_stride : s.o_stride, K, N);
         return;
     }
     Geometry g = geometry(m->fmt);
@@ -393,9 +428,9 @@ static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
     launch_product<XT>(m, true, x, s.rowtok, s, s.gu, st);
     int64_t hi = (int64_t)total * m->inter;
-    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit);
+    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride);
     launch_product<float>(m, false, s.h, nullptr, s, s.o, st);
-    moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y);
+    moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
     ctx->launches += 7;
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
 }
@@ -441,9 +476,9 @@ static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, 
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
     launch_product<XT>(m, true, x, s.rowtok, s, s.gu, st);
     int64_t hi = (int64_t)total * m->inter;
-    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit);
+    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride);
     launch_product<float>(m, false, s.h, nullptr, s, s.o, st);
-    moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y);
+    moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
     ctx->launches += 8;
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
 }
