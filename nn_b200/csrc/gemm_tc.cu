@@ -245,7 +245,9 @@ bool gemm_tc_supported(const nnq_weight *w, int64_t m) {
 template <int FMT, int MT, typename XT>
 static cudaError_t launch_one(const TcArgs &a, int *status, cudaStream_t stream) {
     const int stage_bytes = (MT + 1) * kTcTileBytes;
-    int stages = MT == 4 ? 2 : (MT == 2 ? 4 : 6);
+    // MT = 1, 2: 96 KB of stages, so that two CTAs (2 x 128 * MT tensor-memory columns) share an SM and
+    // one CTA's decode overlaps the other's MMAs; MT = 4 fills the SM alone
+    int stages = MT == 4 ? 2 : (MT == 2 ? 2 : 3);
     const int nkb = (int)(a.k / kTcBK);
     if (stages > nkb) stages = nkb;
     const int smem_bytes = stages * stage_bytes + 1024;
@@ -264,25 +266,34 @@ static cudaError_t launch_one(const TcArgs &a, int *status, cudaStream_t stream)
 }
 
 template <int FMT>
-static cudaError_t launch_fmt(const TcArgs &a, int *status, cudaStream_t stream) {
+static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, cudaStream_t stream) {
     const bool f32 = a.x_dt == NNQ_F32;
-    if (a.m <= 128) return f32 ? launch_one<FMT, 1, float>(a, status, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, stream);
-    if (a.m <= 256) return f32 ? launch_one<FMT, 2, float>(a, status, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, stream);
+    // Rows per CTA: the more rows share a decoded weight tile the less decode work, but the grid
+    // must still cover the machine. Take the largest tile that leaves at least one CTA per SM.
+    // (Decoding the whole weight to bf16 first and multiplying afterwards was measured slower than
+    // decoding per tile even at M = 4096: the tile pipeline, not the decode, is the limit.)
+    const int64_t ntiles = (a.n + 127) / 128;
+    auto ctas = [&](int mt) { return ntiles * ((a.m + 128 * mt - 1) / (128 * mt)); };
+    int mt = 1;
+    if (a.m > 256 && ctas(4) >= sm_count) mt = 4;
+    else if (a.m > 128 && ctas(2) >= sm_count) mt = 2;
+    if (mt == 1) return f32 ? launch_one<FMT, 1, float>(a, status, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, stream);
+    if (mt == 2) return f32 ? launch_one<FMT, 2, float>(a, status, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, stream);
     return f32 ? launch_one<FMT, 4, float>(a, status, stream) : launch_one<FMT, 4, __nv_bfloat16>(a, status, stream);
 }
 
 nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
     cudaError_t e;
     switch (a.fmt) {
-        case NNQ_Q4_0: e = launch_fmt<NNQ_Q4_0>(a, ctx->d_status, stream); break;
-        case NNQ_Q4_1: e = launch_fmt<NNQ_Q4_1>(a, ctx->d_status, stream); break;
-        case NNQ_Q8_0: e = launch_fmt<NNQ_Q8_0>(a, ctx->d_status, stream); break;
-        case NNQ_Q4_K: e = launch_fmt<NNQ_Q4_K>(a, ctx->d_status, stream); break;
-        case NNQ_Q4_K_GGML: e = launch_fmt<NNQ_Q4_K_GGML>(a, ctx->d_status, stream); break;
-        case NNQ_Q6_K: e = launch_fmt<NNQ_Q6_K>(a, ctx->d_status, stream); break;
-        case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, ctx->d_status, stream); break;
-        case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, ctx->d_status, stream); break;
-        case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, ctx->d_status, stream); break;
+        case NNQ_Q4_0: e = launch_fmt<NNQ_Q4_0>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_Q4_1: e = launch_fmt<NNQ_Q4_1>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_Q8_0: e = launch_fmt<NNQ_Q8_0>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_Q4_K: e = launch_fmt<NNQ_Q4_K>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_Q4_K_GGML: e = launch_fmt<NNQ_Q4_K_GGML>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_Q6_K: e = launch_fmt<NNQ_Q6_K>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, ctx->d_status, ctx->sm_count, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
     }
     ctx->launches++;
