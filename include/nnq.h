@@ -90,8 +90,10 @@ typedef enum nnq_format {
 
 typedef enum nnq_dtype { NNQ_F32 = 0, NNQ_BF16 = 1 } nnq_dtype;
 
-/* Kernel selection for nnq_linear. AUTO picks per shape: M <= 16 the dequant-fused
- * skinny kernel, larger M the tensor-core tile pipeline. The other values force one
+/* Kernel selection for nnq_linear. AUTO picks per shape from measured crossovers: M = 1 the
+ * streaming skinny kernel (Q4_K), M > 16 (M >= 5 with bf16 activations) the tensor-core tile
+ * pipeline (K a multiple of 64; weights and activations rounded to bf16),
+ * otherwise the portable row kernel. The other values force one
  * path (tests and measurements use them). */
 typedef enum nnq_path {
     NNQ_PATH_AUTO = 0,

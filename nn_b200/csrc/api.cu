@@ -353,7 +353,7 @@ static nnq_status linear_dispatch(nnq_ctx *ctx, const nnq_weight *w, const void 
     const bool tc_ok = gemm_tc_supported(w, m);
     if (path == NNQ_PATH_TENSOR && !tc_ok)
         return fail(ctx, NNQ_ERR_UNSUPPORTED, "tensor path needs K to be a multiple of 64 (K=%lld)", (long long)w->k);
-    if (path == NNQ_PATH_TENSOR || (path == NNQ_PATH_AUTO && !skinny_ok && tc_ok && m > 16)) {
+    if (path == NNQ_PATH_TENSOR || (path == NNQ_PATH_AUTO && !skinny_ok && tc_ok && (m > 16 || (m >= 5 && x_dt == NNQ_BF16)))) {
         TcArgs a = {w->d_raw, w->d_scales, x_dev, bias_dev, y_dev, m, w->n, w->k, w->fmt, x_dt, y_dt};
         return launch_gemm_tc(ctx, a, stream);
     }

@@ -75,7 +75,7 @@ template <int FMT, int MT, typename XT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscales, const XT *__restrict__ x,
                const float *__restrict__ bias, void *__restrict__ y, int64_t M, int64_t N, int64_t K, int y_dt,
-               int stages, int *status) {
+               int stages, float *__restrict__ partials, int *status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles (the dynamic window is not guaranteed to start on one)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -87,7 +87,10 @@ gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscale
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t n0 = (int64_t)blockIdx.x * 128;
     const int64_t m0 = (int64_t)blockIdx.y * 128 * MT;
-    const int nkb = (int)(K / kTcBK);
+    // this CTA's share of the k steps (gridDim.z slices of K; partial sums go to `partials`)
+    const int nkb_all = (int)(K / kTcBK);
+    const int kb_lo = (int)(((long long)blockIdx.z * nkb_all) / gridDim.z);
+    const int nkb = (int)(((long long)(blockIdx.z + 1) * nkb_all) / gridDim.z) - kb_lo;
     const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * 8, acc_s = full_s + 16 * 8;
     constexpr uint32_t kTmemCols = 128 * MT;
 
@@ -116,46 +119,55 @@ gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscale
         const int brow = tid & 127, bhalf = tid >> 7;   // weight tile: row and which 32 of the 64 k
         int slot = 0;
         uint32_t phase = 0;
+        // Software pipeline: the tile data of step kb + 1 is fetched and decoded into registers
+        // right after step kb has been handed to the tensor core, so that the global-memory latency
+        // runs under the MMAs and under the wait for a free stage.
+        constexpr int kAChunks = (128 * MT * 8) / (kTcProducerWarps * 32);   // 16-byte activation chunks per thread
+        uint4 wreg[4];
+        uint4 areg[kAChunks];
+        const int ac = tid & 7;
+        auto fetch = [&](int kb) {
+            float wv[32];
+            if (n0 + brow < N) {
+                Decode<FMT>::chunk(w, wscales, (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf, wv);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) wv[i] = 0.0f;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                wreg[c] = make_uint4(pack_bf16(wv[8 * c], wv[8 * c + 1]), pack_bf16(wv[8 * c + 2], wv[8 * c + 3]),
+                                     pack_bf16(wv[8 * c + 4], wv[8 * c + 5]), pack_bf16(wv[8 * c + 6], wv[8 * c + 7]));
+#pragma unroll
+            for (int i = 0; i < kAChunks; i++) {
+                const int r = (tid >> 3) + 32 * i;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                const int64_t row = m0 + r;
+                if (row < M) {
+                    const XT *src = x + row * K + (int64_t)kb * kTcBK + ac * 8;
+                    if (sizeof(XT) == 2) {
+                        v = __ldg(reinterpret_cast<const uint4 *>(src));
+                    } else {
+                        float4 fa = __ldg(reinterpret_cast<const float4 *>(src));
+                        float4 fb = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+                        v = make_uint4(pack_bf16(fa.x, fa.y), pack_bf16(fa.z, fa.w), pack_bf16(fb.x, fb.y), pack_bf16(fb.z, fb.w));
+                    }
+                }
+                areg[i] = v;
+            }
+        };
+        fetch(kb_lo);
         for (int kb = 0; kb < nkb && ok; kb++) {
             if (kb >= stages) ok = mbar_wait_fast(empty_s + 8 * slot, phase ^ 1u);
             if (!ok) break;
             uint8_t *stage = smem + (size_t)slot * kStageBytes;
-            // weight tile: 32 consecutive k of one row per thread, bit-exact f32 decode, then bf16
-            {
-                float wv[32];
-                if (n0 + brow < N) {
-                    Decode<FMT>::chunk(w, wscales, (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf, wv);
-                } else {
+            uint8_t *bt = stage + MT * kTcTileBytes;
 #pragma unroll
-                    for (int i = 0; i < 32; i++) wv[i] = 0.0f;
-                }
-                uint8_t *bt = stage + MT * kTcTileBytes;
+            for (int c = 0; c < 4; c++) *reinterpret_cast<uint4 *>(bt + swz(brow, bhalf * 4 + c)) = wreg[c];
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    uint4 v = make_uint4(pack_bf16(wv[8 * c], wv[8 * c + 1]), pack_bf16(wv[8 * c + 2], wv[8 * c + 3]),
-                                         pack_bf16(wv[8 * c + 4], wv[8 * c + 5]), pack_bf16(wv[8 * c + 6], wv[8 * c + 7]));
-                    *reinterpret_cast<uint4 *>(bt + swz(brow, bhalf * 4 + c)) = v;
-                }
-            }
-            // activation tiles: 16-byte chunks (8 bf16), 8 per row
-            {
-                const int c = tid & 7;
-#pragma unroll 4
-                for (int r = tid >> 3; r < 128 * MT; r += kTcProducerWarps * 4) {
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    const int64_t row = m0 + r;
-                    if (row < M) {
-                        const XT *src = x + row * K + (int64_t)kb * kTcBK + c * 8;
-                        if (sizeof(XT) == 2) {
-                            v = __ldg(reinterpret_cast<const uint4 *>(src));
-                        } else {
-                            float4 a = __ldg(reinterpret_cast<const float4 *>(src));
-                            float4 b = __ldg(reinterpret_cast<const float4 *>(src) + 1);
-                            v = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
-                        }
-                    }
-                    *reinterpret_cast<uint4 *>(stage + (r >> 7) * kTcTileBytes + swz(r & 127, c)) = v;
-                }
+            for (int i = 0; i < kAChunks; i++) {
+                const int r = (tid >> 3) + 32 * i;
+                *reinterpret_cast<uint4 *>(stage + (r >> 7) * kTcTileBytes + swz(r & 127, ac)) = areg[i];
             }
             fence_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
@@ -164,6 +176,7 @@ gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscale
                 slot = 0;
                 phase ^= 1u;
             }
+            if (kb + 1 < nkb) fetch(kb_lo + kb + 1);
         }
         // ---------------- epilogue ----------------
         if (ok) ok = mbar_wait_fast(acc_s, 0);
@@ -184,6 +197,10 @@ gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscale
                             const int64_t col = n0 + col0 + i;
                             if (col < N) {
                                 float f = __uint_as_float(v[i]);
+                                if (partials) {   // K is split over CTAs: bias and conversion happen in the reduction
+                                    partials[((size_t)blockIdx.z * M + row) * N + col] = f;
+                                    continue;
+                                }
                                 if (bias) f += __ldg(bias + col);
                                 if (y_dt == NNQ_F32) reinterpret_cast<float *>(y)[row * N + col] = f;
                                 else reinterpret_cast<__nv_bfloat16 *>(y)[row * N + col] = __float2bfloat16_rn(f);
@@ -234,6 +251,20 @@ gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscale
     }
 }
 
+// y = sum over the K slices (in order) + bias
+__global__ void __launch_bounds__(256)
+gemm_tc_reduce_kernel(const float *__restrict__ partials, int slices, const float *__restrict__ bias, void *__restrict__ y,
+                      int64_t M, int64_t N, int y_dt) {
+    const int64_t total = M * N;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float f = 0.0f;
+        for (int z = 0; z < slices; z++) f += partials[(size_t)z * total + i];
+        if (bias) f += __ldg(bias + i % N);
+        if (y_dt == NNQ_F32) reinterpret_cast<float *>(y)[i] = f;
+        else reinterpret_cast<__nv_bfloat16 *>(y)[i] = __float2bfloat16_rn(f);
+    }
+}
+
 // ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
@@ -243,13 +274,13 @@ bool gemm_tc_supported(const nnq_weight *w, int64_t m) {
 }
 
 template <int FMT, int MT, typename XT>
-static cudaError_t launch_one(const TcArgs &a, int *status, cudaStream_t stream) {
+static cudaError_t launch_one(const TcArgs &a, int *status, int ksplit, float *partials, cudaStream_t stream) {
     const int stage_bytes = (MT + 1) * kTcTileBytes;
     // MT = 1, 2: 96 KB of stages, so that two CTAs (2 x 128 * MT tensor-memory columns) share an SM and
     // one CTA's decode overlaps the other's MMAs; MT = 4 fills the SM alone
     int stages = MT == 4 ? 2 : (MT == 2 ? 2 : 3);
     const int nkb = (int)(a.k / kTcBK);
-    if (stages > nkb) stages = nkb;
+    if (stages > nkb / ksplit) stages = nkb / ksplit > 0 ? nkb / ksplit : 1;
     const int smem_bytes = stages * stage_bytes + 1024;
     static bool configured[64] = {};
     int dev = 0;
@@ -259,14 +290,20 @@ static cudaError_t launch_one(const TcArgs &a, int *status, cudaStream_t stream)
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)((a.m + 128 * MT - 1) / (128 * MT)));
+    dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)((a.m + 128 * MT - 1) / (128 * MT)), (unsigned)ksplit);
     gemm_tc_kernel<FMT, MT, XT><<<grid, kTcThreads, smem_bytes, stream>>>(
-        a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages, status);
+        a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages,
+        ksplit > 1 ? partials : nullptr, status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || ksplit == 1) return e;
+    const int64_t total = a.m * a.n;
+    gemm_tc_reduce_kernel<<<(int)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048), 256, 0, stream>>>(
+        partials, ksplit, a.bias, a.y, a.m, a.n, a.y_dt);
     return cudaGetLastError();
 }
 
 template <int FMT>
-static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, cudaStream_t stream) {
+static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, int ksplit, float *partials, cudaStream_t stream) {
     const bool f32 = a.x_dt == NNQ_F32;
     // Rows per CTA: the more rows share a decoded weight tile the less decode work, but the grid
     // must still cover the machine. Take the largest tile that leaves at least one CTA per SM.
@@ -277,26 +314,53 @@ static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, cudaSt
     int mt = 1;
     if (a.m > 256 && ctas(4) >= sm_count) mt = 4;
     else if (a.m > 128 && ctas(2) >= sm_count) mt = 2;
-    if (mt == 1) return f32 ? launch_one<FMT, 1, float>(a, status, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, stream);
-    if (mt == 2) return f32 ? launch_one<FMT, 2, float>(a, status, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, stream);
-    return f32 ? launch_one<FMT, 4, float>(a, status, stream) : launch_one<FMT, 4, __nv_bfloat16>(a, status, stream);
+    if (mt != 1) ksplit = 1;
+    if (mt == 1) return f32 ? launch_one<FMT, 1, float>(a, status, ksplit, partials, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, ksplit, partials, stream);
+    if (mt == 2) return f32 ? launch_one<FMT, 2, float>(a, status, 1, nullptr, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, 1, nullptr, stream);
+    return f32 ? launch_one<FMT, 4, float>(a, status, 1, nullptr, stream) : launch_one<FMT, 4, __nv_bfloat16>(a, status, 1, nullptr, stream);
 }
 
 nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
     cudaError_t e;
+    // Small grids (few rows, few output tiles) split K over CTAs so that every SM works; the f32
+    // partial sums go through a scratch buffer owned by the context and are added in slice order.
+    int ksplit = 1;
+    {
+        const int64_t ctas = ((a.n + 127) / 128) * ((a.m + 127) / 128);
+        const int64_t nkb = a.k / kTcBK;
+        // aim at two CTAs per SM for very few rows (the partial sums are small), one otherwise
+        const int64_t target = a.m <= 64 ? 2 * ctx->sm_count : ctx->sm_count;
+        if (a.m <= 256 && ctas * 2 <= target) {
+            ksplit = (int)(target / ctas);
+            if (ksplit > 8) ksplit = 8;
+            if (ksplit > nkb / 4) ksplit = (int)(nkb / 4);
+            if (ksplit < 1) ksplit = 1;
+        }
+        if (ksplit > 1) {
+            const size_t need = (size_t)ksplit * a.m * a.n * sizeof(float);
+            if (need > ctx->partials_bytes) {
+                cudaFree(ctx->d_partials);   // synchronises: an earlier product may still use it
+                ctx->d_partials = nullptr;
+                ctx->partials_bytes = 0;
+                nnq_status s = check_cuda(ctx, cudaMalloc(&ctx->d_partials, need), "cudaMalloc split-K scratch");
+                if (s != NNQ_OK) return s;
+                ctx->partials_bytes = need;
+            }
+        }
+    }
     switch (a.fmt) {
-        case NNQ_Q4_0: e = launch_fmt<NNQ_Q4_0>(a, ctx->d_status, ctx->sm_count, stream); break;
-        case NNQ_Q4_1: e = launch_fmt<NNQ_Q4_1>(a, ctx->d_status, ctx->sm_count, stream); break;
-        case NNQ_Q8_0: e = launch_fmt<NNQ_Q8_0>(a, ctx->d_status, ctx->sm_count, stream); break;
-        case NNQ_Q4_K: e = launch_fmt<NNQ_Q4_K>(a, ctx->d_status, ctx->sm_count, stream); break;
-        case NNQ_Q4_K_GGML: e = launch_fmt<NNQ_Q4_K_GGML>(a, ctx->d_status, ctx->sm_count, stream); break;
-        case NNQ_Q6_K: e = launch_fmt<NNQ_Q6_K>(a, ctx->d_status, ctx->sm_count, stream); break;
-        case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, ctx->d_status, ctx->sm_count, stream); break;
-        case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, ctx->d_status, ctx->sm_count, stream); break;
-        case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, ctx->d_status, ctx->sm_count, stream); break;
+        case NNQ_Q4_0: e = launch_fmt<NNQ_Q4_0>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q4_1: e = launch_fmt<NNQ_Q4_1>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q8_0: e = launch_fmt<NNQ_Q8_0>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q4_K: e = launch_fmt<NNQ_Q4_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q4_K_GGML: e = launch_fmt<NNQ_Q4_K_GGML>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q6_K: e = launch_fmt<NNQ_Q6_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
     }
-    ctx->launches++;
+    ctx->launches += ksplit > 1 ? 2 : 1;
     return check_cuda(ctx, e, "tensor-core GEMM launch");
 }
 

@@ -34,7 +34,7 @@ def _run(fmt, n, k, m, x_bf16, y_bf16, with_bias, seed=1, path=api.PATH_AUTO):
         t.backend.set_path(api.PATH_AUTO)
     y32, y64, mag = P.oracle_linear(fmt, w, sc, x, bias, n, k)
     got = y.float().cpu().numpy()
-    tensor_path = path == api.PATH_TENSOR or (path == api.PATH_AUTO and m > 16 and k % 64 == 0)
+    tensor_path = path == api.PATH_TENSOR or (path == api.PATH_AUTO and k % 64 == 0 and (m > 16 or (m >= 5 and x_bf16)))
     if tensor_path:
         # weights (and f32 activations) are rounded to bf16 for the tensor cores: 1e-2 bar
         assert np.all(np.isfinite(got))
