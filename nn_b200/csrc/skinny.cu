@@ -181,10 +181,11 @@ __device__ __forceinline__ uint32_t sel4(const uint4 &v, int t) {
 //          for super-block kb, sub-block sb, word t (32 B at kb*1024 + (4 sb + t)*32):
 //          8 words {b0,b1} x 4 element pairs, b_h = fp16 pair when h == sb & 1, else 0
 //   tab    K/256 x 4 x float4            (Ox[2t], Ox[2t+1], Sx[2t], Sx[2t+1]) per super-block, t
+//   xinv   K/256 floats                  1 / prescale of each super-block's activations
 //   part   2 x kWarps x 16 floats        per-warp partial sums of a row tile, double buffered
-//   red    kWarps floats, bars: kWarps x stages ring barriers + full[2] + empty[2]
+//   bars: kWarps x stages ring barriers + full[2] + empty[2]
 struct SmemPlan {
-    int ring_off, xs_off, xs_lo_off, tab_off, part_off, red_off, bar_off, total;
+    int ring_off, xs_off, xs_lo_off, tab_off, xinv_off, part_off, bar_off, total;
 };
 
 __host__ __device__ inline SmemPlan smem_plan(int kblocks, int stages, bool f32x) {
@@ -193,9 +194,9 @@ __host__ __device__ inline SmemPlan smem_plan(int kblocks, int stages, bool f32x
     p.xs_off = kWarps * stages * kTileBytes;
     p.xs_lo_off = p.xs_off + kblocks * 1024;
     p.tab_off = p.xs_lo_off + (f32x ? kblocks * 1024 : 0);
-    p.part_off = p.tab_off + kblocks * 64;
-    p.red_off = p.part_off + 2 * kWarps * 16 * 4;
-    p.bar_off = p.red_off + 64;
+    p.xinv_off = p.tab_off + kblocks * 64;
+    p.part_off = (p.xinv_off + kblocks * 4 + 15) & ~15;
+    p.bar_off = p.part_off + 2 * kWarps * 16 * 4;
     p.total = p.bar_off + (kWarps * kMaxStages + 4) * 8;
     return p;
 }
@@ -216,8 +217,8 @@ struct BRegs {
 
 template <bool F32X>
 __device__ __forceinline__ void tile_mac(const uint8_t *stage, uint32_t xs_s, uint32_t xs_lo_s, const float *tab,
-                                         int lane, int g, int t, const Consts &K, BRegs &B, BRegs &BL, float &yg,
-                                         float &yg8) {
+                                         float inv, int lane, int g, int t, const Consts &K, BRegs &B, BRegs &BL,
+                                         float &yg, float &yg8) {
     const uint4 *st = reinterpret_cast<const uint4 *>(stage);
     // activation operand of this super-block: only the lanes whose column g is a sub-block of
     // pair p load data for p; every other register of B stays zero for the whole kernel
@@ -268,55 +269,51 @@ __device__ __forceinline__ void tile_mac(const uint8_t *stage, uint32_t xs_s, ui
         float dot = sc0 * ((c[2 * h] + c2[2 * h]) - tb.x) + sc1 * ((c[2 * h + 1] + c2[2 * h + 1]) - tb.y);
         float mins = mn0 * tb.z + mn1 * tb.w;
         float v = dm.x * dot - dm.y * mins;
-        if (h) yg8 += v; else yg += v;
+        if (h) yg8 = fmaf(v, inv, yg8); else yg = fmaf(v, inv, yg);
     }
 }
 
-// Stage all K activations: power-of-two prescale to fp16 (the largest |x| lands in [1, 2), which
-// is exact and keeps fp16 in range), half-expanded operand layout, per-sub-block offset sums.
-// Called by the whole CTA; returns 1 / prescale.
+// Stage the activations of super-blocks kb_begin, kb_begin + kb_step, ... < kb_end; one warp per
+// super-block, 8 consecutive elements (one word of one sub-block) per lane. Every super-block gets
+// its own power-of-two prescale to fp16 (its largest |x| lands in [1, 2): exact, and fp16 stays in
+// range whatever the magnitude of x), so that a warp can stage its own part of K without waiting
+// for the rest of the CTA. Writes the half-expanded operand, the per-sub-block offset sums and
+// 1 / prescale.
 template <bool F32X>
-__device__ __forceinline__ float stage_x(const void *x, int kblocks, uint8_t *xs, uint8_t *xs_lo, float *tab,
-                                         float *red, int tid) {
-    const int lane = tid & 31, warp = tid >> 5;
-    const int nel = kblocks * 256;
-    auto load4 = [&](int i, float *xv) {
+__device__ __forceinline__ void stage_x_warp(const void *x, int kb_begin, int kb_end, int kb_step, uint8_t *xs,
+                                             uint8_t *xs_lo, float *tab, float *xinv, int lane) {
+    const int sb8 = lane >> 2;
+    const bool odd = sb8 & 1;
+#pragma unroll 2
+    for (int kb = kb_begin; kb < kb_end; kb += kb_step) {
+        float xv[8];
+        const int i = kb * 256 + lane * 8;
         if (F32X) {
-            float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + i));
+            const float4 *px = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + i);
+            float4 a = __ldg(px), b = __ldg(px + 1);
             xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w;
+            xv[4] = b.x; xv[5] = b.y; xv[6] = b.z; xv[7] = b.w;
         } else {
-            uint2 v = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const __nv_bfloat16 *>(x) + i));
-            xv[0] = __uint_as_float(v.x << 16);
-            xv[1] = __uint_as_float(v.x & 0xFFFF0000u);
-            xv[2] = __uint_as_float(v.y << 16);
-            xv[3] = __uint_as_float(v.y & 0xFFFF0000u);
+            uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(x) + i));
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                xv[2 * k] = __uint_as_float(u[k] << 16);
+                xv[2 * k + 1] = __uint_as_float(u[k] & 0xFFFF0000u);
+            }
         }
-    };
-    float amax = 0.0f;
-    for (int i = tid * 4; i < nel; i += kWarps * 32 * 4) {
-        float xv[4];
-        load4(i, xv);
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(xv[0]), fabsf(xv[1])), fmaxf(fabsf(xv[2]), fabsf(xv[3]))));
-    }
+        float amax = 0.0f;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-    if (lane == 0) red[warp] = amax;
-    __syncthreads();
+        for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(xv[k]));
 #pragma unroll
-    for (int w = 0; w < kWarps; w++) amax = fmaxf(amax, red[w]);
-    uint32_t ex = (__float_as_uint(amax) >> 23) & 0xFFu;
-    ex = amax > 0.0f && ex < 255u ? min(max(ex, 1u), 253u) : 127u;
-    const float scale = __uint_as_float((254u - ex) << 23);
-    // 4 consecutive elements per thread and iteration = element pairs e0, e0+1 (e0 = 0 or 2) of word
-    // tt of sub-block sb8; a whole warp covers 128 consecutive elements, so the loop is warp-uniform
-    const int tt = (tid >> 1) & 3, e0 = (tid & 1) * 2;
-    for (int i = tid * 4; i < nel; i += kWarps * 32 * 4) {
-        float xv[4];
-        load4(i, xv);
-        uint32_t ph[2], pl[2];
-        float xr[4];  // the value the MMAs will see
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+        uint32_t ex = (__float_as_uint(amax) >> 23) & 0xFFu;
+        ex = amax > 0.0f && ex < 255u ? min(max(ex, 1u), 253u) : 127u;
+        const float scale = __uint_as_float((254u - ex) << 23);
+        uint32_t ph[4], pl[4];
+        float xr[8];  // the values the MMAs will see
 #pragma unroll
-        for (int k = 0; k < 2; k++) {
+        for (int k = 0; k < 4; k++) {
             float s0 = xv[2 * k] * scale, s1 = xv[2 * k + 1] * scale;
             __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
             xr[2 * k] = __half2float(h0);
@@ -329,30 +326,31 @@ __device__ __forceinline__ float stage_x(const void *x, int kblocks, uint8_t *xs
                 pl[k] = __half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
             }
         }
-        const int sbk = i >> 5, kb = sbk >> 3, sb8 = sbk & 7;
-        const int off = kb * 1024 + (4 * sb8 + tt) * 32 + e0 * 8;
-        const bool odd = sb8 & 1;
-        *reinterpret_cast<uint4 *>(xs + off) = odd ? make_uint4(0, ph[0], 0, ph[1]) : make_uint4(ph[0], 0, ph[1], 0);
-        if (F32X)
-            *reinterpret_cast<uint4 *>(xs_lo + off) = odd ? make_uint4(0, pl[0], 0, pl[1]) : make_uint4(pl[0], 0, pl[1], 0);
-        // within a word (8 elements), elements 0,1,4,5 carry offset 1024 and 2,3,6,7 offset 64:
-        // this thread's elements 0,1 are of the first kind and 2,3 of the second
-        float sa = xr[0] + xr[1], sb = xr[2] + xr[3];
+        // lane = 4 * sub-block + word: its 32 bytes of the operand image are contiguous
+        uint4 *dst = reinterpret_cast<uint4 *>(xs + kb * 1024 + lane * 32);
+        dst[0] = odd ? make_uint4(0, ph[0], 0, ph[1]) : make_uint4(ph[0], 0, ph[1], 0);
+        dst[1] = odd ? make_uint4(0, ph[2], 0, ph[3]) : make_uint4(ph[2], 0, ph[3], 0);
+        if (F32X) {
+            uint4 *dl = reinterpret_cast<uint4 *>(xs_lo + kb * 1024 + lane * 32);
+            dl[0] = odd ? make_uint4(0, pl[0], 0, pl[1]) : make_uint4(pl[0], 0, pl[1], 0);
+            dl[1] = odd ? make_uint4(0, pl[2], 0, pl[3]) : make_uint4(pl[2], 0, pl[3], 0);
+        }
+        // within a word (8 elements), elements 0,1,4,5 carry offset 1024 and 2,3,6,7 offset 64
+        float sa = (xr[0] + xr[1]) + (xr[4] + xr[5]), sb = (xr[2] + xr[3]) + (xr[6] + xr[7]);
         float ox = 1024.0f * sa + 64.0f * sb;
         float sx = sa + sb;
 #pragma unroll
-        for (int o2 = 1; o2 < 8; o2 <<= 1) {  // the 8 threads of one sub-block are consecutive lanes
+        for (int o2 = 1; o2 < 4; o2 <<= 1) {  // the 4 lanes of one sub-block are consecutive
             ox += __shfl_xor_sync(0xFFFFFFFFu, ox, o2);
             sx += __shfl_xor_sync(0xFFFFFFFFu, sx, o2);
         }
-        if ((tid & 7) == 0) {
+        if ((lane & 3) == 0) {
             float *e = tab + (kb * 4 + (sb8 >> 1)) * 4 + (sb8 & 1);
             e[0] = ox;
             e[2] = sx;
         }
+        if (lane == 0) xinv[kb] = __uint_as_float(ex << 23);
     }
-    __syncthreads();
-    return __uint_as_float(ex << 23);
 }
 
 // expect-tx + bulk copy issued by the lanes whose predicate is set (lane 0), without a branch
@@ -378,8 +376,8 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     uint8_t *xs = smem + L.xs_off;
     uint8_t *xs_lo = smem + L.xs_lo_off;
     float *tab = reinterpret_cast<float *>(smem + L.tab_off);
+    float *xinv = reinterpret_cast<float *>(smem + L.xinv_off);
     float *part = reinterpret_cast<float *>(smem + L.part_off);
-    float *red = reinterpret_cast<float *>(smem + L.red_off);
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);   // tells the compiler it is warp-uniform
@@ -476,7 +474,14 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (!(P.diag & 2)) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const float inv_scale = stage_x<F32X>(P.x, P.kblocks, xs, xs_lo, tab, red, tid);
+    if (KS == kWarps) {
+        // the warp owns its part of K: no other warp reads what it stages
+        stage_x_warp<F32X>(P.x, kb_lo, kb_hi, 1, xs, xs_lo, tab, xinv, lane);
+        __syncwarp();
+    } else {
+        stage_x_warp<F32X>(P.x, warp, P.kblocks, kWarps, xs, xs_lo, tab, xinv, lane);
+        __syncthreads();
+    }
     const uint32_t xs_s = smem_u32(xs) + lane * 32, xs_lo_s = smem_u32(xs_lo) + lane * 32;
 
     Consts K;
@@ -519,7 +524,7 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
 #pragma unroll
                 for (int w = 0; w < KS; w++) v += part[(b * kWarps + rsub * KS + w) * 16 + lane];
             }
-            store16(j, rt, v * inv_scale);
+            store16(j, rt, v);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_s + 8 * b);
@@ -537,7 +542,7 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
                 ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
                 if (!(P.diag & 1))
                     tile_mac<F32X>(ring + slot * kTileBytes, xs_s + (kb_lo + k) * 1024, xs_lo_s + (kb_lo + k) * 1024,
-                                   tab + (kb_lo + k) * 16, lane, g, t, K, B, BL, yg, yg8);
+                                   tab + (kb_lo + k) * 16, xinv[kb_lo + k], lane, g, t, K, B, BL, yg, yg8);
                 consumed++;
                 if (++slot == stages) {
                     slot = 0;
@@ -560,7 +565,7 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
             if (j >= 0) {
                 float lo = __shfl_sync(0xFFFFFFFFu, yg, (lane & 7) * 4);
                 float hi = __shfl_sync(0xFFFFFFFFu, yg8, (lane & 7) * 4);
-                store16(j, rt, (lane < 8 ? lo : hi) * inv_scale);
+                store16(j, rt, lane < 8 ? lo : hi);
             }
             continue;
         }
