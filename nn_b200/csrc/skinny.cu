@@ -1,4 +1,4 @@
-// Skinny (decode, M = 1) streaming kernels for Q4_K weights on the tiled "T16" layout.
+// Skinny (decode, M <= 16) streaming kernels for Q4_K weights on the tiled "T16" layout.
 //
 // Why tensor cores for a GEMV: at HBM speed an SM receives about 50 four-bit weights per
 // clock, so there are fewer than three issue slots per weight for unpacking, converting,
@@ -54,6 +54,7 @@ struct SkinnyParams {
     SkinnyJobDev job[kSkinnyMaxJobs];
     const void *x;      // activations shared by all jobs, [K]
     int njobs;
+    int m;              // tokens (1 for the M = 1 kernel, 2..16 for the token-column kernel)
     int y_dt;
     int kblocks;        // K / 256
     int total_tiles;    // row tiles of all jobs
@@ -600,6 +601,266 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
 }
 
 // ---------------------------------------------------------------------------------
+// 2 <= M <= 16 kernel: the n-columns of the MMA are tokens
+// ---------------------------------------------------------------------------------
+//
+// Same tiles, same per-warp rings and the same K split over the 8 warps of a CTA as the M = 1
+// kernel, but the eight MMA columns are eight tokens (NT = 2: sixteen) and the activations are
+// used as they are: bf16 pairs loaded straight from global memory (L1 / L2 resident) as the B
+// operand. The weights enter as exact bf16 codes 128 + q (one logic op per two weights); a second
+// MMA with an all-ones A operand yields the activation sum of the sub-block, which removes the
+// offset and carries the Q4_K min term. Scales are applied per sub-block on the f32 accumulators:
+//   y[row][tok] += d sc * (c - 128 s) - dmin m * s = (d sc) * c - (128 d sc + dmin m) * s.
+// The (d sc, 128 d sc + dmin m) pairs of a tile are computed once (lane (g, t): rows g, g + 8,
+// sub-blocks 2t, 2t + 1) and exchanged through a 1 KB per-warp scratch.
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1, const float (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+struct MnPlan {
+    int ring_off, sct_off, part_off, bar_off, total;
+};
+
+__host__ __device__ inline MnPlan mn_plan(int stages, int nt) {
+    MnPlan p;
+    p.ring_off = 0;
+    p.sct_off = kWarps * stages * kTileBytes;
+    p.part_off = p.sct_off + kWarps * 1024;
+    p.bar_off = p.part_off + 2 * kWarps * nt * 32 * 16;
+    p.total = p.bar_off + (kWarps * kMaxStages + 4) * 8;
+    return p;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kWarps * 32, 2)
+skinny_q4k_mn_kernel(const __grid_constant__ SkinnyParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const MnPlan L = mn_plan(P.stages, NT);
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
+    const int g = lane >> 2, t = lane & 3;
+    const int cta = blockIdx.x, grid = gridDim.x;
+    const int stages = P.stages;
+    uint8_t *ring = smem + warp * stages * kTileBytes;
+    float4 *sct4 = reinterpret_cast<float4 *>(smem + L.sct_off + warp * 1024);
+    float4 *part4 = reinterpret_cast<float4 *>(smem + L.part_off);
+    const uint32_t ring_s = smem_u32(ring);
+    const uint32_t bars_s = smem_u32(smem + L.bar_off);
+    const uint32_t bar_s = bars_s + warp * kMaxStages * 8;
+    const uint32_t full_s = bars_s + kWarps * kMaxStages * 8;   // full[2], then empty[2]
+    const uint32_t empty_s = full_s + 16;
+
+    if (tid == 0) {
+        mbar_init(full_s, kWarps);
+        mbar_init(full_s + 8, kWarps);
+        mbar_init(empty_s, 1);
+        mbar_init(empty_s + 8, 1);
+    }
+    if (lane == 0) {
+        for (int d = 0; d < stages; d++) mbar_init(bar_s + 8 * d, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // this warp's share of K; a unit is one row tile, CTA c handles units c, c + grid, ...
+    const int kb_lo = (warp * P.kblocks) / kWarps, kb_hi = ((warp + 1) * P.kblocks) / kWarps;
+    const int nkb = kb_hi - kb_lo;
+    const int n_units = cta < P.total_tiles ? (P.total_tiles - cta + grid - 1) / grid : 0;
+    auto locate = [&](int unit, int &j, int &rt) {
+        const int gt = cta + unit * grid;
+        j = 0;
+#pragma unroll
+        for (int i = 1; i < kSkinnyMaxJobs; i++)
+            if (i < P.njobs && gt >= P.job[i].tile_begin) j = i;
+        rt = gt - P.job[j].tile_begin;
+    };
+
+    // ---- weights first: they do not depend on anything an earlier kernel produced ----
+    int pf_unit = -1, pf_k = 0;
+    unsigned issued = 0;
+    const uint8_t *pf_src = nullptr;
+    bool pf_done = nkb == 0 || n_units == 0;
+    auto pf_advance_unit = [&]() {
+        if (++pf_unit >= n_units) {
+            pf_done = true;
+            return;
+        }
+        int j, rt;
+        locate(pf_unit, j, rt);
+        pf_src = P.job[j].tiled + ((size_t)rt * P.kblocks + kb_lo) * kTileBytes;
+        pf_k = 0;
+    };
+    if (!pf_done) pf_advance_unit();
+    const int is_lane0 = lane == 0;
+    int pf_slot = 0;
+    auto issue = [&]() {
+        if (!pf_done) {
+            issue_tile(ring_s + pf_slot * kTileBytes, pf_src, bar_s + 8 * pf_slot, is_lane0);
+            issued++;
+            pf_slot = pf_slot + 1 == stages ? 0 : pf_slot + 1;
+            pf_src += kTileBytes;
+            if (++pf_k == nkb) pf_advance_unit();
+        }
+    };
+    for (int d = 0; d < stages; d++) issue();
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // activations of this lane's token column(s); a column beyond M reads token 0 and is never stored
+    const __nv_bfloat16 *xrow[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int tok = nt * 8 + g;
+        xrow[nt] = reinterpret_cast<const __nv_bfloat16 *>(P.x) + (size_t)(tok < P.m ? tok : 0) * P.kblocks * 256 + 8 * t;
+    }
+    uint32_t m4, k128, ones;
+    asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(m4));
+    asm volatile("mov.b32 %0, 0x43004300;" : "=r"(k128));
+    asm volatile("mov.b32 %0, 0x3F803F80;" : "=r"(ones));
+    const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+
+    unsigned consumed = 0;
+    int slot = 0;
+    uint32_t phase = 0;
+    bool failed = false;
+
+    auto put = [&](const SkinnyJobDev &J, int tok, int row, float v) {
+        if (tok < P.m && row < J.n) {
+            if (J.bias) v += __ldg(J.bias + row);
+            const size_t at = (size_t)tok * J.n + row;
+            if (P.y_dt == NNQ_F32) reinterpret_cast<float *>(J.y)[at] = v;
+            else reinterpret_cast<__nv_bfloat16 *>(J.y)[at] = __float2bfloat16_rn(v);
+        }
+    };
+    // the warp whose turn it is adds the 8 partial tiles of the unit and writes the outputs
+    auto finish = [&](int unit) {
+        const int b = unit & 1;
+        if (!mbar_wait_fast(full_s + 8 * b, (unit >> 1) & 1u)) {
+            failed = true;
+            return;
+        }
+        int j, rt;
+        locate(unit, j, rt);
+        const SkinnyJobDev &J = P.job[j];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int w = 0; w < kWarps; w++) {
+                const float4 a = part4[((b * kWarps + w) * NT + nt) * 32 + lane];
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
+            const int row = rt * 16 + g, tok = nt * 8 + 2 * t;
+            put(J, tok, row, v.x);
+            put(J, tok + 1, row, v.y);
+            put(J, tok, row + 8, v.z);
+            put(J, tok + 1, row + 8, v.w);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_s + 8 * b);
+    };
+
+#pragma unroll 1
+    for (int unit = 0; unit < n_units && !failed; unit++) {
+        float y[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int r = 0; r < 4; r++) y[nt][r] = 0.0f;
+        bool ok = true;
+#pragma unroll 1
+        for (int k = 0; k < nkb; k++) {
+            ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
+            const uint8_t *stage = ring + slot * kTileBytes;
+            const uint4 *st = reinterpret_cast<const uint4 *>(stage);
+            // scales of the tile: this lane's share, then the exchange
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint4 hd = st[8 * h + g];
+                uint32_t p01 = __byte_perm(hd.x, hd.y, 0x0073);
+                uint32_t p23 = __byte_perm(hd.z, hd.w, 0x0073);
+                uint32_t dd = __byte_perm(p01, p23, 0x5410);
+                float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&dd));
+                uint32_t o = reinterpret_cast<const uint32_t *>(stage)[(8 * h + g) * 4 + t];
+                float sc0 = (float)(o & 63u), sc1 = (float)((o >> 6) & 63u);
+                float mn0 = (float)((o >> 12) & 63u), mn1 = (float)((o >> 18) & 63u);
+                float a0 = dm.x * sc0, a1 = dm.x * sc1;
+                sct4[(8 * h + g) * 4 + t] = make_float4(a0, fmaf(128.0f, a0, dm.y * mn0), a1, fmaf(128.0f, a1, dm.y * mn1));
+            }
+            __syncwarp();
+            const int koff = (kb_lo + k) * 256;
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                const uint4 q = st[16 + 32 * p + lane];
+                const float4 sg = sct4[g * 4 + p], sg8 = sct4[(g + 8) * 4 + p];
+#pragma unroll
+                for (int s2 = 0; s2 < 2; s2++) {
+                    const uint32_t wa = s2 ? q.z : q.x, wb = s2 ? q.w : q.y;
+                    const uint32_t a0 = and_or(wa, m4, k128), a1 = and_or(wb, m4, k128);
+                    const uint32_t a2 = and_or(wa >> 4, m4, k128), a3 = and_or(wb >> 4, m4, k128);
+                    const uint32_t a4 = and_or(wa >> 8, m4, k128), a5 = and_or(wb >> 8, m4, k128);
+                    const uint32_t a6 = and_or(wa >> 12, m4, k128), a7 = and_or(wb >> 12, m4, k128);
+                    const float dsc = s2 ? sg.z : sg.x, e = s2 ? sg.w : sg.y;
+                    const float dsc8 = s2 ? sg8.z : sg8.x, e8 = s2 ? sg8.w : sg8.y;
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        const uint4 xb = __ldg(reinterpret_cast<const uint4 *>(xrow[nt] + koff + (2 * p + s2) * 32));
+                        float c[4], sx[4];
+                        mma_bf16(c, a0, a1, a2, a3, xb.x, xb.y, zero);
+                        mma_bf16(c, a4, a5, a6, a7, xb.z, xb.w, c);
+                        mma_bf16(sx, ones, ones, ones, ones, xb.x, xb.y, zero);
+                        mma_bf16(sx, ones, ones, ones, ones, xb.z, xb.w, sx);
+                        y[nt][0] = fmaf(dsc, c[0], fmaf(-e, sx[0], y[nt][0]));
+                        y[nt][1] = fmaf(dsc, c[1], fmaf(-e, sx[1], y[nt][1]));
+                        y[nt][2] = fmaf(dsc8, c[2], fmaf(-e8, sx[2], y[nt][2]));
+                        y[nt][3] = fmaf(dsc8, c[3], fmaf(-e8, sx[3], y[nt][3]));
+                    }
+                }
+            }
+            consumed++;
+            if (++slot == stages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+            __syncwarp();  // all lanes have read the slot and the scale scratch
+            issue();
+        }
+        if (!ok) {
+            failed = true;
+            break;
+        }
+        const int b = unit & 1;
+        if (unit >= 2 && !mbar_wait_fast(empty_s + 8 * b, ((unit >> 1) - 1) & 1u)) {
+            failed = true;
+            break;
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+            part4[((b * kWarps + warp) * NT + nt) * 32 + lane] = make_float4(y[nt][0], y[nt][1], y[nt][2], y[nt][3]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_s + 8 * b);
+        if (unit >= 1 && warp == (unit - 1) % kWarps) finish(unit - 1);
+    }
+    if (!failed && n_units >= 1 && warp == (n_units - 1) % kWarps) finish(n_units - 1);
+    if (failed) {
+        if (lane == 0) atomicExch(P.status, 1);
+        for (unsigned n = consumed; n < issued; n++) {
+            mbar_wait(bar_s + 8 * slot, phase);
+            if (++slot == stages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
 
@@ -660,7 +921,9 @@ static void pick_stages(int kblocks, bool f32x, int *stages, int *ctas_per_sm) {
 }
 
 bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt) {
-    if (!w || w->tiled_layout != kTiledQ4K || m != 1) return false;
+    if (!w || w->tiled_layout != kTiledQ4K || m < 1 || m > kSkinnyMaxM) return false;
+    // 2..16 tokens: bf16 activations, and K large enough for the 8-way split over the warps
+    if (m > 1) return x_dt == NNQ_BF16 && w->k >= 8 * 256;
     int st, cps;
     pick_stages((int)(w->k / 256), x_dt == NNQ_F32, &st, &cps);
     return st > 0;
@@ -702,6 +965,29 @@ static cudaError_t launch_ks(int ksplit, const SkinnyParams &P, int grid, int sm
     }
 }
 
+template <int NT>
+static cudaError_t launch_mn(const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_q4k_mn_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kWarps * 32);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, skinny_q4k_mn_kernel<NT>, P);
+}
+
 // Diagnostic only (NNQ_SKINNY_DIAG=4): read the tiled weights of the jobs with plain coalesced
 // 16-byte loads and nothing else -- the read bandwidth a launch of this size can reach.
 __global__ void __launch_bounds__(256) stream_read_kernel(const SkinnyParams P, int *sink) {
@@ -718,11 +1004,12 @@ __global__ void __launch_bounds__(256) stream_read_kernel(const SkinnyParams P, 
 }
 
 // One launch: jobs that share their activations (same x pointer, same K).
-static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int y_dt,
+static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int m, int y_dt,
                                cudaStream_t stream) {
     SkinnyParams P;
     memset(&P, 0, sizeof(P));
     P.njobs = count;
+    P.m = m;
     P.y_dt = y_dt;
     P.x = jobs[0].x;
     P.kblocks = (int)(jobs[0].w->k / 256);
@@ -733,7 +1020,8 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     P.l2_prefetch = env_l2 ? atoi(env_l2) : 0;
     const bool f32x = x_dt == NNQ_F32;
     int ctas_per_sm = 0;
-    pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
+    if (m == 1) pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
+    else P.stages = 2;
     if (P.stages == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "K = %lld is too large for the skinny kernel", (long long)jobs[0].w->k);
     int tiles = 0;
     for (int i = 0; i < count; i++) {
@@ -748,6 +1036,17 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
         tiles += J.row_tiles;
     }
     P.total_tiles = tiles;
+    if (m > 1) {
+        // token-column kernel: a unit is one row tile, its K split over the 8 warps
+        const int nt = m <= 8 ? 1 : 2;
+        const int smem_bytes = mn_plan(P.stages, nt).total;
+        int per_sm = kSmemMax / (smem_bytes + 1024);
+        if (per_sm > 2) per_sm = 2;   // register budget of the kernel
+        int grid = tiles < ctx->sm_count * per_sm ? tiles : ctx->sm_count * per_sm;
+        cudaError_t e = nt == 1 ? launch_mn<1>(P, grid, smem_bytes, stream) : launch_mn<2>(P, grid, smem_bytes, stream);
+        ctx->launches++;
+        return check_cuda(ctx, e, "skinny launch");
+    }
     if (P.diag == 4) {
         stream_read_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(P, nullptr);
         ctx->launches++;
@@ -777,13 +1076,13 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
 nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int64_t m, int y_dt,
                          cudaStream_t stream) {
     if (count < 1 || count > kSkinnyMaxJobs) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad job count %d", count);
-    if (m != 1) return fail(ctx, NNQ_ERR_UNSUPPORTED, "skinny kernel covers M = 1 only");
+    if (m < 1 || m > kSkinnyMaxM) return fail(ctx, NNQ_ERR_UNSUPPORTED, "skinny kernels cover 1 <= M <= %d", kSkinnyMaxM);
     // consecutive jobs with the same activations and K go out together
     int i = 0;
     while (i < count) {
         int jn = i + 1;
         while (jn < count && jobs[jn].x == jobs[i].x && jobs[jn].w->k == jobs[i].w->k) jn++;
-        nnq_status s = launch_group(ctx, jobs + i, jn - i, x_dt, y_dt, stream);
+        nnq_status s = launch_group(ctx, jobs + i, jn - i, x_dt, (int)m, y_dt, stream);
         if (s != NNQ_OK) return s;
         i = jn;
     }

@@ -34,7 +34,9 @@ def _run(fmt, n, k, m, x_bf16, y_bf16, with_bias, seed=1, path=api.PATH_AUTO):
         t.backend.set_path(api.PATH_AUTO)
     y32, y64, mag = P.oracle_linear(fmt, w, sc, x, bias, n, k)
     got = y.float().cpu().numpy()
-    tensor_path = path == api.PATH_TENSOR or (path == api.PATH_AUTO and k % 64 == 0 and (m > 16 or (m >= 5 and x_bf16)))
+    skinny = fmt in (Q.Q4_K, Q.Q4_K_GGML) and k % 256 == 0 and (m == 1 or (2 <= m <= 16 and x_bf16 and k >= 2048))
+    tensor_path = path == api.PATH_TENSOR or (
+        path == api.PATH_AUTO and not skinny and k % 64 == 0 and (m > 16 or (m >= 5 and x_bf16)))
     if tensor_path:
         # weights (and f32 activations) are rounded to bf16 for the tensor cores: 1e-2 bar
         assert np.all(np.isfinite(got))
@@ -50,6 +52,15 @@ def _run(fmt, n, k, m, x_bf16, y_bf16, with_bias, seed=1, path=api.PATH_AUTO):
         P.assert_close(got, y32, y64, mag)
     t.release()
     return got
+
+
+@pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q4_K_GGML])
+@pytest.mark.parametrize("m", [2, 3, 7, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(200, 2048), (64, 4096), (1030, 2304)])
+def test_token_column_skinny_kernel(fmt, m, n, k):
+    """2..16 tokens of bf16 activations on the tiled Q4_K layout: ragged row tiles, token counts
+    on both sides of the 8-column boundary, K not a multiple of 8 super-blocks per warp."""
+    _run(fmt, n, k, m, x_bf16=True, y_bf16=(m % 2 == 0), with_bias=(m % 3 == 0), seed=300 + m, path=api.PATH_SKINNY)
 
 
 @pytest.mark.parametrize("fmt", list(Q))
@@ -211,6 +222,24 @@ def test_batch_call_matches_single_calls():
     for y, w in zip(ys, ws):
         single = api.quantized_matmul(x, w, out_dtype=torch.float32)
         # the k-chunking (hence the f32 summation order) depends on the size of the launch
+        assert float((y - single).abs().max()) <= 1e-5 * float(single.abs().max())
+        w.release()
+
+
+@pytest.mark.parametrize("m", [4, 12])
+def test_batch_call_token_column_kernel(m):
+    # three projections sharing their activations go out as one launch of the token-column kernel
+    k = 2048
+    shapes = [(256, k), (72, k), (64, k)]
+    ws = []
+    for i, (n, kk) in enumerate(shapes):
+        w, _ = F.gen_weight(Q.Q4_K, 60 + i, n, kk)
+        ws.append(api.from_quantized(w, Q.Q4_K, [n, kk]))
+    x = torch.from_numpy(F.gen_activations(70, m, k, bf16=True)).to(DEV).to(torch.bfloat16)
+    ys = api.linear_batch([x, x, x], ws, out_dtype=torch.float32)
+    for y, w in zip(ys, ws):
+        single = api.quantized_matmul(x, w, out_dtype=torch.float32)
+        assert y.shape == single.shape
         assert float((y - single).abs().max()) <= 1e-5 * float(single.abs().max())
         w.release()
 
