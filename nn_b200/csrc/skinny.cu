@@ -601,18 +601,34 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
 }
 
 // ---------------------------------------------------------------------------------
-// 2 <= M <= 16 kernel: the n-columns of the MMA are tokens
+// Token-column kernel: 1 <= M <= 16, the n-columns of the MMA are tokens
 // ---------------------------------------------------------------------------------
 //
-// Same tiles, same per-warp rings and the same K split over the 8 warps of a CTA as the M = 1
-// kernel, but the eight MMA columns are eight tokens (NT = 2: sixteen) and the activations are
-// used as they are: bf16 pairs loaded straight from global memory (L1 / L2 resident) as the B
-// operand. The weights enter as exact bf16 codes 128 + q (one logic op per two weights); a second
-// MMA with an all-ones A operand yields the activation sum of the sub-block, which removes the
-// offset and carries the Q4_K min term. Scales are applied per sub-block on the f32 accumulators:
-//   y[row][tok] += d sc * (c - 128 s) - dmin m * s = (d sc) * c - (128 d sc + dmin m) * s.
-// The (d sc, 128 d sc + dmin m) pairs of a tile are computed once (lane (g, t): rows g, g + 8,
-// sub-blocks 2t, 2t + 1) and exchanged through a 1 KB per-warp scratch.
+// Same kind of tiles (16 rows x 256 weights, one bulk copy each), per-warp rings and K split over
+// the 8 warps of a CTA as the M = 1 kernel, but the eight MMA columns are eight tokens (NT = 2:
+// sixteen) and the activations are used as they are: bf16 pairs loaded straight from global
+// memory (L1 / L2 resident) as the B operand (f32 activations are split into two bf16 terms on
+// the fly and cost a second MMA). The weights enter as exact bf16 codes built with one logic op
+// per two weights:
+//   four-bit plane   (w & 0x000F000F) | 0x4300 = 128 + nibble
+//   upper plane      (w & mask)       | 0x4500 = 2048 + 16 * field   (same accumulator)
+// and a second MMA with an all-ones A operand yields the activation sum s of the group, which
+// removes the constant offsets (and carries the Q4_K min term). Scales are applied per scale
+// group on the f32 accumulators:
+//   Q4_K  y += (d sc) * c - (128 d sc + dmin m) * s        group = sub-block of 32
+//   Q8_0  y += d * (c - 2304 s)                            group = block of 32, code = q + 128
+//   Q6_K  y += (d sc) * (c - 2208 s)                       group = 16 weights, code = q6
+// Tiled layouts of Q8_0 and Q6_K (same byte count as the raw blocks; lane l = 4g + t owns rows g
+// and g + 8 of the tile; a "T16 word" packs eight four-bit fields e0..e7 as byte0 = e0 | e2<<4,
+// byte1 = e4 | e6<<4, byte2 = e1 | e3<<4, byte3 = e5 | e7<<4, so that (w >> 4i) & 0x000F000F is
+// the pair (e_2i, e_2i+1)):
+//   Q8_0, 4352 B: [0,256) fp16 d[row][block]; then per block b 512 B, lane l 16 B =
+//         {low nibbles row g, high nibbles row g, low row g+8, high row g+8} of elements 8t..8t+7
+//   Q6_K, 3360 B: [0,256) int8 sc[row][16]; [256,288) fp16 d[row]; then per sub-block 384 B =
+//         128 B low-nibble words row g | 128 B row g+8 | 128 B two-bit words, one word per lane.
+//         Lane t owns elements 4t..4t+3 (scale group 2sb) and 16+4t..16+4t+3 (group 2sb+1) as
+//         e0..e7; two-bit word: row g pair i at bits 2i (e_2i) and 16+2i (e_2i+1), row g+8 at
+//         bits 8+2i and 24+2i.
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1, const float (&c)[4]) {
@@ -622,31 +638,263 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
+// eight activations of one token as four bf16 pairs (and the bf16 remainder when they are f32)
+template <bool F32X>
+struct XB {
+    uint4 hi, lo;
+};
+
+__device__ __forceinline__ void split_bf16(float a, float b, uint32_t &hi, uint32_t &lo) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    float2 hf = __bfloat1622float2(h);
+    __nv_bfloat162 l = __floats2bfloat162_rn(a - hf.x, b - hf.y);
+    hi = *reinterpret_cast<uint32_t *>(&h);
+    lo = *reinterpret_cast<uint32_t *>(&l);
+}
+
+// elements [e0, e0+4) and [e1, e1+4) of the token row x (element offsets)
+template <bool F32X>
+__device__ __forceinline__ XB<F32X> load_xb(const void *x, int e0, int e1) {
+    XB<F32X> r;
+    if (F32X) {
+        const float *p = reinterpret_cast<const float *>(x);
+        const float4 u = __ldg(reinterpret_cast<const float4 *>(p + e0));
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p + e1));
+        split_bf16(u.x, u.y, r.hi.x, r.lo.x);
+        split_bf16(u.z, u.w, r.hi.y, r.lo.y);
+        split_bf16(v.x, v.y, r.hi.z, r.lo.z);
+        split_bf16(v.z, v.w, r.hi.w, r.lo.w);
+    } else {
+        const __nv_bfloat16 *p = reinterpret_cast<const __nv_bfloat16 *>(x);
+        if (e1 == e0 + 4) {
+            r.hi = __ldg(reinterpret_cast<const uint4 *>(p + e0));
+        } else {
+            const uint2 u = __ldg(reinterpret_cast<const uint2 *>(p + e0));
+            const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p + e1));
+            r.hi = make_uint4(u.x, u.y, v.x, v.y);
+        }
+        r.lo = make_uint4(0, 0, 0, 0);
+    }
+    return r;
+}
+
+// d = A * B(pairs 2h, 2h+1 of xb) + c, with the remainder term of f32 activations
+template <bool F32X>
+__device__ __forceinline__ void mma_x(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                      const XB<F32X> &xb, int h, const float (&c)[4]) {
+    mma_bf16(d, a0, a1, a2, a3, h ? xb.hi.z : xb.hi.x, h ? xb.hi.w : xb.hi.y, c);
+    if (F32X) mma_bf16(d, a0, a1, a2, a3, h ? xb.lo.z : xb.lo.x, h ? xb.lo.w : xb.lo.y, d);
+}
+
+struct MnConsts {
+    uint32_t m4, m2, k128, k2048, ones;
+    __device__ __forceinline__ void init() {
+        asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(m4));
+        asm volatile("mov.b32 %0, 0x00030003;" : "=r"(m2));
+        asm volatile("mov.b32 %0, 0x43004300;" : "=r"(k128));
+        asm volatile("mov.b32 %0, 0x45004500;" : "=r"(k2048));
+        asm volatile("mov.b32 %0, 0x3F803F80;" : "=r"(ones));
+    }
+};
+
+template <int FMT>
+struct TileFmt;
+
+// ---- Q4_K (both element orders share the tiled layout) ----
+template <>
+struct TileFmt<NNQ_Q4_K> {
+    static constexpr int kBytes = 2304;
+    template <int NT, bool F32X>
+    static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *sct4, const uint8_t *const (&xrow)[NT],
+                                                int koff, int lane, int g, int t, const MnConsts &K,
+                                                float (&y)[NT][4]) {
+        constexpr int ES = F32X ? 4 : 2;
+        const uint4 *st = reinterpret_cast<const uint4 *>(stage);
+        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // (d sc, 128 d sc + dmin m) of the tile: this lane's share (rows g, g+8; sub-blocks 2t, 2t+1)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint4 hd = st[8 * h + g];
+            uint32_t p01 = __byte_perm(hd.x, hd.y, 0x0073);
+            uint32_t p23 = __byte_perm(hd.z, hd.w, 0x0073);
+            uint32_t dd = __byte_perm(p01, p23, 0x5410);
+            float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&dd));
+            uint32_t o = reinterpret_cast<const uint32_t *>(stage)[(8 * h + g) * 4 + t];
+            float sc0 = (float)(o & 63u), sc1 = (float)((o >> 6) & 63u);
+            float mn0 = (float)((o >> 12) & 63u), mn1 = (float)((o >> 18) & 63u);
+            float a0 = dm.x * sc0, a1 = dm.x * sc1;
+            sct4[(8 * h + g) * 4 + t] = make_float4(a0, fmaf(128.0f, a0, dm.y * mn0), a1, fmaf(128.0f, a1, dm.y * mn1));
+        }
+        __syncwarp();
+#pragma unroll
+        for (int p = 0; p < 4; p++) {
+            const uint4 q = st[16 + 32 * p + lane];
+            const float4 sg = sct4[g * 4 + p], sg8 = sct4[(g + 8) * 4 + p];
+#pragma unroll
+            for (int s2 = 0; s2 < 2; s2++) {
+                const uint32_t wa = s2 ? q.z : q.x, wb = s2 ? q.w : q.y;
+                const uint32_t a0 = and_or(wa, K.m4, K.k128), a1 = and_or(wb, K.m4, K.k128);
+                const uint32_t a2 = and_or(wa >> 4, K.m4, K.k128), a3 = and_or(wb >> 4, K.m4, K.k128);
+                const uint32_t a4 = and_or(wa >> 8, K.m4, K.k128), a5 = and_or(wb >> 8, K.m4, K.k128);
+                const uint32_t a6 = and_or(wa >> 12, K.m4, K.k128), a7 = and_or(wb >> 12, K.m4, K.k128);
+                const float dsc = s2 ? sg.z : sg.x, e = s2 ? sg.w : sg.y;
+                const float dsc8 = s2 ? sg8.z : sg8.x, e8 = s2 ? sg8.w : sg8.y;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int e0 = koff + (2 * p + s2) * 32 + 8 * t;
+                    const XB<F32X> xb = load_xb<F32X>(xrow[nt], e0, e0 + 4);
+                    float c[4], sx[4];
+                    mma_x<F32X>(c, a0, a1, a2, a3, xb, 0, zero);
+                    mma_x<F32X>(c, a4, a5, a6, a7, xb, 1, c);
+                    mma_x<F32X>(sx, K.ones, K.ones, K.ones, K.ones, xb, 0, zero);
+                    mma_x<F32X>(sx, K.ones, K.ones, K.ones, K.ones, xb, 1, sx);
+                    y[nt][0] = fmaf(dsc, c[0], fmaf(-e, sx[0], y[nt][0]));
+                    y[nt][1] = fmaf(dsc, c[1], fmaf(-e, sx[1], y[nt][1]));
+                    y[nt][2] = fmaf(dsc8, c[2], fmaf(-e8, sx[2], y[nt][2]));
+                    y[nt][3] = fmaf(dsc8, c[3], fmaf(-e8, sx[3], y[nt][3]));
+                }
+            }
+        }
+        (void)ES;
+    }
+};
+
+// ---- Q8_0 ----
+template <>
+struct TileFmt<NNQ_Q8_0> {
+    static constexpr int kBytes = 4352;
+    template <int NT, bool F32X>
+    static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *, const uint8_t *const (&xrow)[NT],
+                                                int koff, int lane, int g, int t, const MnConsts &K,
+                                                float (&y)[NT][4]) {
+        const uint4 *st = reinterpret_cast<const uint4 *>(stage);
+        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint4 dg = st[g], dg8 = st[8 + g];   // the eight block scales of rows g and g + 8
+        const uint32_t dgw[4] = {dg.x, dg.y, dg.z, dg.w}, dg8w[4] = {dg8.x, dg8.y, dg8.z, dg8.w};
+#pragma unroll
+        for (int sb = 0; sb < 8; sb++) {
+            const uint4 q = st[16 + 32 * sb + lane];   // {low g, high g, low g+8, high g+8}
+            const float2 d2 = __half22float2(*reinterpret_cast<const __half2 *>(&dgw[sb >> 1]));
+            const float2 d28 = __half22float2(*reinterpret_cast<const __half2 *>(&dg8w[sb >> 1]));
+            const float d = sb & 1 ? d2.y : d2.x, d8 = sb & 1 ? d28.y : d28.x;
+            uint32_t L[4], L8[4], H[4], H8[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                L[i] = and_or(q.x >> (4 * i), K.m4, K.k128);
+                H[i] = and_or(q.y >> (4 * i), K.m4, K.k2048);
+                L8[i] = and_or(q.z >> (4 * i), K.m4, K.k128);
+                H8[i] = and_or(q.w >> (4 * i), K.m4, K.k2048);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int e0 = koff + sb * 32 + 8 * t;
+                const XB<F32X> xb = load_xb<F32X>(xrow[nt], e0, e0 + 4);
+                float c[4], sx[4];
+                mma_x<F32X>(c, L[0], L8[0], L[1], L8[1], xb, 0, zero);
+                mma_x<F32X>(c, L[2], L8[2], L[3], L8[3], xb, 1, c);
+                mma_x<F32X>(c, H[0], H8[0], H[1], H8[1], xb, 0, c);
+                mma_x<F32X>(c, H[2], H8[2], H[3], H8[3], xb, 1, c);
+                mma_x<F32X>(sx, K.ones, K.ones, K.ones, K.ones, xb, 0, zero);
+                mma_x<F32X>(sx, K.ones, K.ones, K.ones, K.ones, xb, 1, sx);
+                y[nt][0] = fmaf(d, fmaf(-2304.0f, sx[0], c[0]), y[nt][0]);
+                y[nt][1] = fmaf(d, fmaf(-2304.0f, sx[1], c[1]), y[nt][1]);
+                y[nt][2] = fmaf(d8, fmaf(-2304.0f, sx[2], c[2]), y[nt][2]);
+                y[nt][3] = fmaf(d8, fmaf(-2304.0f, sx[3], c[3]), y[nt][3]);
+            }
+        }
+    }
+};
+
+// ---- Q6_K ----
+template <>
+struct TileFmt<NNQ_Q6_K> {
+    static constexpr int kBytes = 3360;
+    template <int NT, bool F32X>
+    static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *sct4, const uint8_t *const (&xrow)[NT],
+                                                int koff, int lane, int g, int t, const MnConsts &K,
+                                                float (&y)[NT][4]) {
+        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint32_t *sw = reinterpret_cast<const uint32_t *>(stage);
+        // d * sc of the tile: this lane's share (rows g, g+8; scale groups 4t .. 4t+3)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int r = 8 * h + g;
+            const float d = __half2float(reinterpret_cast<const __half *>(stage + 256)[r]);
+            const uint32_t w = sw[r * 4 + t];
+            sct4[r * 4 + t] = make_float4(d * (float)(int8_t)(w & 0xFFu), d * (float)(int8_t)((w >> 8) & 0xFFu),
+                                          d * (float)(int8_t)((w >> 16) & 0xFFu), d * (float)(int8_t)(w >> 24));
+        }
+        __syncwarp();
+        const float2 *sct2 = reinterpret_cast<const float2 *>(sct4);
+#pragma unroll
+        for (int sb = 0; sb < 8; sb++) {
+            const uint32_t *cw = sw + 72 + sb * 96;   // byte 288 + 384 sb
+            const uint32_t lo = cw[lane], lo8 = cw[32 + lane], hw = cw[64 + lane];
+            const float2 sg = sct2[g * 8 + sb], sg8 = sct2[(g + 8) * 8 + sb];   // groups 2sb, 2sb+1
+            uint32_t L[4], L8[4], H[4], H8[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                L[i] = and_or(lo >> (4 * i), K.m4, K.k128);
+                L8[i] = and_or(lo8 >> (4 * i), K.m4, K.k128);
+                H[i] = and_or(hw >> (2 * i), K.m2, K.k2048);
+                H8[i] = and_or(hw >> (8 + 2 * i), K.m2, K.k2048);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int e0 = koff + sb * 32 + 4 * t;
+                const XB<F32X> xb = load_xb<F32X>(xrow[nt], e0, e0 + 16);
+                float ca[4], cb[4], sa[4], sb4[4];
+                mma_x<F32X>(ca, L[0], L8[0], L[1], L8[1], xb, 0, zero);
+                mma_x<F32X>(ca, H[0], H8[0], H[1], H8[1], xb, 0, ca);
+                mma_x<F32X>(sa, K.ones, K.ones, K.ones, K.ones, xb, 0, zero);
+                mma_x<F32X>(cb, L[2], L8[2], L[3], L8[3], xb, 1, zero);
+                mma_x<F32X>(cb, H[2], H8[2], H[3], H8[3], xb, 1, cb);
+                mma_x<F32X>(sb4, K.ones, K.ones, K.ones, K.ones, xb, 1, zero);
+                y[nt][0] = fmaf(sg.x, fmaf(-2208.0f, sa[0], ca[0]), fmaf(sg.y, fmaf(-2208.0f, sb4[0], cb[0]), y[nt][0]));
+                y[nt][1] = fmaf(sg.x, fmaf(-2208.0f, sa[1], ca[1]), fmaf(sg.y, fmaf(-2208.0f, sb4[1], cb[1]), y[nt][1]));
+                y[nt][2] = fmaf(sg8.x, fmaf(-2208.0f, sa[2], ca[2]), fmaf(sg8.y, fmaf(-2208.0f, sb4[2], cb[2]), y[nt][2]));
+                y[nt][3] = fmaf(sg8.x, fmaf(-2208.0f, sa[3], ca[3]), fmaf(sg8.y, fmaf(-2208.0f, sb4[3], cb[3]), y[nt][3]));
+            }
+        }
+    }
+};
+
+template <int BYTES>
+__device__ __forceinline__ void issue_tile_n(uint32_t dst, const void *src, uint32_t bar, int pred) {
+    asm volatile(
+        "{\n .reg .pred q;\n setp.ne.s32 q, %3, 0;\n"
+        " @q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%2], %4;\n"
+        " @q cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %4, [%2];\n}"
+        ::"r"(dst), "l"(src), "r"(bar), "r"(pred), "n"(BYTES) : "memory");
+}
+
 struct MnPlan {
     int ring_off, sct_off, part_off, bar_off, total;
 };
 
-__host__ __device__ inline MnPlan mn_plan(int stages, int nt) {
+__host__ __device__ inline MnPlan mn_plan(int tile_bytes, int stages, int nt) {
     MnPlan p;
     p.ring_off = 0;
-    p.sct_off = kWarps * stages * kTileBytes;
+    p.sct_off = kWarps * stages * tile_bytes;
     p.part_off = p.sct_off + kWarps * 1024;
     p.bar_off = p.part_off + 2 * kWarps * nt * 32 * 16;
     p.total = p.bar_off + (kWarps * kMaxStages + 4) * 8;
     return p;
 }
 
-template <int NT>
+template <int FMT, int NT, bool F32X>
 __global__ void __launch_bounds__(kWarps * 32, 2)
-skinny_q4k_mn_kernel(const __grid_constant__ SkinnyParams P) {
+skinny_mn_kernel(const __grid_constant__ SkinnyParams P) {
+    using TF = TileFmt<FMT>;
+    constexpr int TB = TF::kBytes;
     extern __shared__ __align__(128) uint8_t smem[];
-    const MnPlan L = mn_plan(P.stages, NT);
+    const MnPlan L = mn_plan(TB, P.stages, NT);
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
     const int g = lane >> 2, t = lane & 3;
     const int cta = blockIdx.x, grid = gridDim.x;
     const int stages = P.stages;
-    uint8_t *ring = smem + warp * stages * kTileBytes;
+    uint8_t *ring = smem + warp * stages * TB;
     float4 *sct4 = reinterpret_cast<float4 *>(smem + L.sct_off + warp * 1024);
     float4 *part4 = reinterpret_cast<float4 *>(smem + L.part_off);
     const uint32_t ring_s = smem_u32(ring);
@@ -681,7 +929,7 @@ skinny_q4k_mn_kernel(const __grid_constant__ SkinnyParams P) {
     };
 
     // ---- weights first: they do not depend on anything an earlier kernel produced ----
-    int pf_unit = -1, pf_k = 0;
+    int pf_unit = -1, pf_k = 0, pf_slot = 0;
     unsigned issued = 0;
     const uint8_t *pf_src = nullptr;
     bool pf_done = nkb == 0 || n_units == 0;
@@ -692,18 +940,17 @@ skinny_q4k_mn_kernel(const __grid_constant__ SkinnyParams P) {
         }
         int j, rt;
         locate(pf_unit, j, rt);
-        pf_src = P.job[j].tiled + ((size_t)rt * P.kblocks + kb_lo) * kTileBytes;
+        pf_src = P.job[j].tiled + ((size_t)rt * P.kblocks + kb_lo) * TB;
         pf_k = 0;
     };
     if (!pf_done) pf_advance_unit();
     const int is_lane0 = lane == 0;
-    int pf_slot = 0;
     auto issue = [&]() {
         if (!pf_done) {
-            issue_tile(ring_s + pf_slot * kTileBytes, pf_src, bar_s + 8 * pf_slot, is_lane0);
+            issue_tile_n<TB>(ring_s + pf_slot * TB, pf_src, bar_s + 8 * pf_slot, is_lane0);
             issued++;
             pf_slot = pf_slot + 1 == stages ? 0 : pf_slot + 1;
-            pf_src += kTileBytes;
+            pf_src += TB;
             if (++pf_k == nkb) pf_advance_unit();
         }
     };
@@ -713,17 +960,14 @@ skinny_q4k_mn_kernel(const __grid_constant__ SkinnyParams P) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // activations of this lane's token column(s); a column beyond M reads token 0 and is never stored
-    const __nv_bfloat16 *xrow[NT];
+    const uint8_t *xrow[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const int tok = nt * 8 + g;
-        xrow[nt] = reinterpret_cast<const __nv_bfloat16 *>(P.x) + (size_t)(tok < P.m ? tok : 0) * P.kblocks * 256 + 8 * t;
+        xrow[nt] = reinterpret_cast<const uint8_t *>(P.x) + (size_t)(tok < P.m ? tok : 0) * P.kblocks * 256 * (F32X ? 4 : 2);
     }
-    uint32_t m4, k128, ones;
-    asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(m4));
-    asm volatile("mov.b32 %0, 0x43004300;" : "=r"(k128));
-    asm volatile("mov.b32 %0, 0x3F803F80;" : "=r"(ones));
-    const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    MnConsts K;
+    K.init();
 
     unsigned consumed = 0;
     int slot = 0;
@@ -777,52 +1021,7 @@ skinny_q4k_mn_kernel(const __grid_constant__ SkinnyParams P) {
 #pragma unroll 1
         for (int k = 0; k < nkb; k++) {
             ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
-            const uint8_t *stage = ring + slot * kTileBytes;
-            const uint4 *st = reinterpret_cast<const uint4 *>(stage);
-            // scales of the tile: this lane's share, then the exchange
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const uint4 hd = st[8 * h + g];
-                uint32_t p01 = __byte_perm(hd.x, hd.y, 0x0073);
-                uint32_t p23 = __byte_perm(hd.z, hd.w, 0x0073);
-                uint32_t dd = __byte_perm(p01, p23, 0x5410);
-                float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&dd));
-                uint32_t o = reinterpret_cast<const uint32_t *>(stage)[(8 * h + g) * 4 + t];
-                float sc0 = (float)(o & 63u), sc1 = (float)((o >> 6) & 63u);
-                float mn0 = (float)((o >> 12) & 63u), mn1 = (float)((o >> 18) & 63u);
-                float a0 = dm.x * sc0, a1 = dm.x * sc1;
-                sct4[(8 * h + g) * 4 + t] = make_float4(a0, fmaf(128.0f, a0, dm.y * mn0), a1, fmaf(128.0f, a1, dm.y * mn1));
-            }
-            __syncwarp();
-            const int koff = (kb_lo + k) * 256;
-#pragma unroll
-            for (int p = 0; p < 4; p++) {
-                const uint4 q = st[16 + 32 * p + lane];
-                const float4 sg = sct4[g * 4 + p], sg8 = sct4[(g + 8) * 4 + p];
-#pragma unroll
-                for (int s2 = 0; s2 < 2; s2++) {
-                    const uint32_t wa = s2 ? q.z : q.x, wb = s2 ? q.w : q.y;
-                    const uint32_t a0 = and_or(wa, m4, k128), a1 = and_or(wb, m4, k128);
-                    const uint32_t a2 = and_or(wa >> 4, m4, k128), a3 = and_or(wb >> 4, m4, k128);
-                    const uint32_t a4 = and_or(wa >> 8, m4, k128), a5 = and_or(wb >> 8, m4, k128);
-                    const uint32_t a6 = and_or(wa >> 12, m4, k128), a7 = and_or(wb >> 12, m4, k128);
-                    const float dsc = s2 ? sg.z : sg.x, e = s2 ? sg.w : sg.y;
-                    const float dsc8 = s2 ? sg8.z : sg8.x, e8 = s2 ? sg8.w : sg8.y;
-#pragma unroll
-                    for (int nt = 0; nt < NT; nt++) {
-                        const uint4 xb = __ldg(reinterpret_cast<const uint4 *>(xrow[nt] + koff + (2 * p + s2) * 32));
-                        float c[4], sx[4];
-                        mma_bf16(c, a0, a1, a2, a3, xb.x, xb.y, zero);
-                        mma_bf16(c, a4, a5, a6, a7, xb.z, xb.w, c);
-                        mma_bf16(sx, ones, ones, ones, ones, xb.x, xb.y, zero);
-                        mma_bf16(sx, ones, ones, ones, ones, xb.z, xb.w, sx);
-                        y[nt][0] = fmaf(dsc, c[0], fmaf(-e, sx[0], y[nt][0]));
-                        y[nt][1] = fmaf(dsc, c[1], fmaf(-e, sx[1], y[nt][1]));
-                        y[nt][2] = fmaf(dsc8, c[2], fmaf(-e8, sx[2], y[nt][2]));
-                        y[nt][3] = fmaf(dsc8, c[3], fmaf(-e8, sx[3], y[nt][3]));
-                    }
-                }
-            }
+            TF::template tile<NT, F32X>(ring + slot * TB, sct4, xrow, (kb_lo + k) * 256, lane, g, t, K, y);
             consumed++;
             if (++slot == stages) {
                 slot = 0;
@@ -861,18 +1060,101 @@ skinny_q4k_mn_kernel(const __grid_constant__ SkinnyParams P) {
 }
 
 // ---------------------------------------------------------------------------------
+// repack of Q8_0 and Q6_K raw blocks into their tiled layouts
+// ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t t16_word(const uint32_t *e) {   // eight four-bit fields
+    return (e[0] | (e[2] << 4)) | ((e[4] | (e[6] << 4)) << 8) | ((e[1] | (e[3] << 4)) << 16) | ((e[5] | (e[7] << 4)) << 24);
+}
+
+// one thread per (row, super-block of 256, sub-block of 32)
+__global__ void repack_q8_0_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ tiled, int n, int kblocks) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)n * kblocks * 8) return;
+    const int sb = (int)(idx & 7);
+    const int64_t blk = idx >> 3;
+    const int kb = (int)(blk % kblocks), row = (int)(blk / kblocks);
+    const uint8_t *b = raw + (((int64_t)row * kblocks + kb) * 8 + sb) * 34;
+    uint8_t *tile = tiled + ((int64_t)(row >> 4) * kblocks + kb) * 4352;
+    const int r16 = row & 15, g = row & 7, upper = (row >> 3) & 1;
+    *reinterpret_cast<uint16_t *>(tile + r16 * 16 + sb * 2) = (uint16_t)(b[0] | (b[1] << 8));
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t u = (uint32_t)b[2 + 8 * t + i] ^ 0x80u;   // q + 128
+            lo[i] = u & 15u;
+            hi[i] = u >> 4;
+        }
+        uint32_t *dst = reinterpret_cast<uint32_t *>(tile + 256 + 512 * sb + 16 * (4 * g + t) + 8 * upper);
+        dst[0] = t16_word(lo);
+        dst[1] = t16_word(hi);
+    }
+}
+
+__global__ void repack_q6_k_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ tiled, int n, int kblocks) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)n * kblocks * 8) return;
+    const int sb = (int)(idx & 7);
+    const int64_t blk = idx >> 3;
+    const int kb = (int)(blk % kblocks), row = (int)(blk / kblocks);
+    const uint8_t *b = raw + blk * 210;
+    uint8_t *tile = tiled + ((int64_t)(row >> 4) * kblocks + kb) * 3360;
+    const int r16 = row & 15, g = row & 7, upper = (row >> 3) & 1;
+    tile[r16 * 16 + 2 * sb] = b[192 + 2 * sb];
+    tile[r16 * 16 + 2 * sb + 1] = b[192 + 2 * sb + 1];
+    if (sb == 0) *reinterpret_cast<uint16_t *>(tile + 256 + 2 * r16) = (uint16_t)(b[208] | (b[209] << 8));
+    // six-bit codes of the sub-block: flat element i -> low nibble i & 1 of ql[i / 2], field i & 3 of qh[i / 4]
+    auto code = [&](int i) -> uint32_t {
+        const int e = sb * 32 + i;
+        const uint32_t ql = (b[e >> 1] >> (4 * (e & 1))) & 15u;
+        const uint32_t qh = (b[128 + (e >> 2)] >> (2 * (e & 3))) & 3u;
+        return ql | (qh << 4);
+    };
+    uint8_t *cw = tile + 288 + 384 * sb;
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        uint32_t lo[8], h2 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t c = code(i < 4 ? 4 * t + i : 16 + 4 * t + (i - 4));
+            lo[i] = c & 15u;
+            // pair i / 2: even element in the low half, odd element in the high half
+            h2 |= (c >> 4) << ((i & 1) * 16 + (i >> 1) * 2);
+        }
+        const int lane = 4 * g + t;
+        reinterpret_cast<uint32_t *>(cw + 128 * upper)[lane] = t16_word(lo);
+        // both rows of a lane share the two-bit word: byte-wise stores keep the other row's bits
+        uint8_t *hb = cw + 256 + 4 * lane;
+        hb[upper] = (uint8_t)(h2 & 0xFFu);
+        hb[2 + upper] = (uint8_t)((h2 >> 16) & 0xFFu);
+    }
+}
+
+// ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
 
 nnq_status skinny_init(nnq_ctx *) { return NNQ_OK; }
 
+static int tile_bytes_of(int fmt) {
+    switch (fmt) {
+        case NNQ_Q4_K: case NNQ_Q4_K_GGML: return TileFmt<NNQ_Q4_K>::kBytes;
+        case NNQ_Q8_0: return TileFmt<NNQ_Q8_0>::kBytes;
+        case NNQ_Q6_K: return TileFmt<NNQ_Q6_K>::kBytes;
+        default: return 0;
+    }
+}
+
 nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w) {
-    if (w->fmt != NNQ_Q4_K && w->fmt != NNQ_Q4_K_GGML) return NNQ_OK;
+    const int tb = tile_bytes_of(w->fmt);
+    if (tb == 0) return NNQ_OK;
     if (w->n == 0 || w->k == 0 || w->k % 256 != 0) return NNQ_OK;
     if (w->n > (1 << 24) || w->k > (1 << 24)) return NNQ_OK;
     int kblocks = (int)(w->k / 256);
     int64_t row_tiles = (w->n + 15) / 16;
-    size_t bytes = (size_t)row_tiles * kblocks * kTileBytes;
+    size_t bytes = (size_t)row_tiles * kblocks * tb;
     nnq_status s = check_cuda(ctx, cudaMalloc(&w->d_tiled, bytes), "cudaMalloc tiled weight");
     if (s != NNQ_OK) return s;
     w->tiled_bytes = bytes;
@@ -882,16 +1164,18 @@ nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w) {
     }
     int64_t total = w->n * kblocks * 8;
     int grid = (int)((total + 255) / 256);
-    if (w->fmt == NNQ_Q4_K)
-        repack_q4k_kernel<false><<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks);
-    else
-        repack_q4k_kernel<true><<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks);
+    switch (w->fmt) {
+        case NNQ_Q4_K: repack_q4k_kernel<false><<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks); break;
+        case NNQ_Q4_K_GGML: repack_q4k_kernel<true><<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks); break;
+        case NNQ_Q8_0: repack_q8_0_kernel<<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks); break;
+        default: repack_q6_k_kernel<<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks); break;
+    }
     ctx->launches++;
     s = check_cuda(ctx, cudaGetLastError(), "repack launch");
     if (s != NNQ_OK) return s;
     s = check_cuda(ctx, cudaDeviceSynchronize(), "repack");
     if (s != NNQ_OK) return s;
-    w->tiled_layout = kTiledQ4K;
+    w->tiled_layout = w->fmt == NNQ_Q8_0 ? kTiledQ8_0 : (w->fmt == NNQ_Q6_K ? kTiledQ6K : kTiledQ4K);
     return NNQ_OK;
 }
 
@@ -921,9 +1205,9 @@ static void pick_stages(int kblocks, bool f32x, int *stages, int *ctas_per_sm) {
 }
 
 bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt) {
-    if (!w || w->tiled_layout != kTiledQ4K || m < 1 || m > kSkinnyMaxM) return false;
-    // 2..16 tokens: bf16 activations, and K large enough for the 8-way split over the warps
-    if (m > 1) return x_dt == NNQ_BF16 && w->k >= 8 * 256;
+    if (!w || w->tiled_layout == kTiledNone || m < 1 || m > kSkinnyMaxM) return false;
+    // token-column kernel: f32 activations (two MMAs per product) up to 8 tokens only
+    if (m > 1 || w->tiled_layout != kTiledQ4K) return x_dt == NNQ_BF16 || m <= 8;
     int st, cps;
     pick_stages((int)(w->k / 256), x_dt == NNQ_F32, &st, &cps);
     return st > 0;
@@ -965,13 +1249,13 @@ static cudaError_t launch_ks(int ksplit, const SkinnyParams &P, int grid, int sm
     }
 }
 
-template <int NT>
+template <int FMT, int NT, bool F32X>
 static cudaError_t launch_mn(const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_q4k_mn_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        cudaError_t e = cudaFuncSetAttribute(skinny_mn_kernel<FMT, NT, F32X>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
@@ -985,7 +1269,13 @@ static cudaError_t launch_mn(const SkinnyParams &P, int grid, int smem_bytes, cu
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, skinny_q4k_mn_kernel<NT>, P);
+    return cudaLaunchKernelEx(&cfg, skinny_mn_kernel<FMT, NT, F32X>, P);
+}
+
+template <int FMT>
+static cudaError_t launch_mn_fmt(const SkinnyParams &P, int nt, bool f32x, int grid, int smem_bytes, cudaStream_t stream) {
+    if (f32x) return launch_mn<FMT, 1, true>(P, grid, smem_bytes, stream);
+    return nt == 1 ? launch_mn<FMT, 1, false>(P, grid, smem_bytes, stream) : launch_mn<FMT, 2, false>(P, grid, smem_bytes, stream);
 }
 
 // Diagnostic only (NNQ_SKINNY_DIAG=4): read the tiled weights of the jobs with plain coalesced
@@ -1020,7 +1310,9 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     P.l2_prefetch = env_l2 ? atoi(env_l2) : 0;
     const bool f32x = x_dt == NNQ_F32;
     int ctas_per_sm = 0;
-    if (m == 1) pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
+    const int layout = jobs[0].w->tiled_layout;
+    const bool token_columns = m > 1 || layout != kTiledQ4K;
+    if (!token_columns) pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
     else P.stages = 2;
     if (P.stages == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "K = %lld is too large for the skinny kernel", (long long)jobs[0].w->k);
     int tiles = 0;
@@ -1036,14 +1328,17 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
         tiles += J.row_tiles;
     }
     P.total_tiles = tiles;
-    if (m > 1) {
-        // token-column kernel: a unit is one row tile, its K split over the 8 warps
+    if (token_columns) {
+        // a unit is one row tile, its K split over the 8 warps
         const int nt = m <= 8 ? 1 : 2;
-        const int smem_bytes = mn_plan(P.stages, nt).total;
+        const int smem_bytes = mn_plan(tile_bytes_of(jobs[0].w->fmt), P.stages, nt).total;
         int per_sm = kSmemMax / (smem_bytes + 1024);
         if (per_sm > 2) per_sm = 2;   // register budget of the kernel
         int grid = tiles < ctx->sm_count * per_sm ? tiles : ctx->sm_count * per_sm;
-        cudaError_t e = nt == 1 ? launch_mn<1>(P, grid, smem_bytes, stream) : launch_mn<2>(P, grid, smem_bytes, stream);
+        cudaError_t e;
+        if (layout == kTiledQ4K) e = launch_mn_fmt<NNQ_Q4_K>(P, nt, f32x, grid, smem_bytes, stream);
+        else if (layout == kTiledQ8_0) e = launch_mn_fmt<NNQ_Q8_0>(P, nt, f32x, grid, smem_bytes, stream);
+        else e = launch_mn_fmt<NNQ_Q6_K>(P, nt, f32x, grid, smem_bytes, stream);
         ctx->launches++;
         return check_cuda(ctx, e, "skinny launch");
     }

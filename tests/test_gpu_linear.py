@@ -34,7 +34,8 @@ def _run(fmt, n, k, m, x_bf16, y_bf16, with_bias, seed=1, path=api.PATH_AUTO):
         t.backend.set_path(api.PATH_AUTO)
     y32, y64, mag = P.oracle_linear(fmt, w, sc, x, bias, n, k)
     got = y.float().cpu().numpy()
-    skinny = fmt in (Q.Q4_K, Q.Q4_K_GGML) and k % 256 == 0 and (m == 1 or (2 <= m <= 16 and x_bf16 and k >= 2048))
+    skinny = (fmt in (Q.Q4_K, Q.Q4_K_GGML, Q.Q8_0, Q.Q6_K) and k % 256 == 0 and 1 <= m <= 16
+              and (x_bf16 or m <= 8 or (m == 1 and fmt in (Q.Q4_K, Q.Q4_K_GGML))))
     tensor_path = path == api.PATH_TENSOR or (
         path == api.PATH_AUTO and not skinny and k % 64 == 0 and (m > 16 or (m >= 5 and x_bf16)))
     if tensor_path:
@@ -61,6 +62,22 @@ def test_token_column_skinny_kernel(fmt, m, n, k):
     """2..16 tokens of bf16 activations on the tiled Q4_K layout: ragged row tiles, token counts
     on both sides of the 8-column boundary, K not a multiple of 8 super-blocks per warp."""
     _run(fmt, n, k, m, x_bf16=True, y_bf16=(m % 2 == 0), with_bias=(m % 3 == 0), seed=300 + m, path=api.PATH_SKINNY)
+
+
+@pytest.mark.parametrize("fmt", [Q.Q8_0, Q.Q6_K, Q.Q4_K])
+@pytest.mark.parametrize("m,x_bf16", [(1, True), (1, False), (2, True), (5, False), (8, True), (8, False), (9, True), (16, True)])
+@pytest.mark.parametrize("n,k", [(200, 2048), (64, 4096), (1030, 2304), (40, 512)])
+def test_token_column_kernel_formats(fmt, m, x_bf16, n, k):
+    """Q8_0 / Q6_K / Q4_K tiles, bf16 and f32 activations (the latter as two bf16 terms), ragged
+    row tiles, K smaller than the 8-way warp split."""
+    if fmt == Q.Q4_K and m == 1:
+        pytest.skip("M = 1 Q4_K has its own kernel")
+    _run(fmt, n, k, m, x_bf16=x_bf16, y_bf16=(m % 2 == 0), with_bias=(m % 3 == 2), seed=400 + m, path=api.PATH_SKINNY)
+
+
+def test_q8_0_gemv_reference_config():
+    """The reference's own CPU-runnable case: Q8_0 4096 x 4096, x f32 [1, 4096], y f32."""
+    _run(Q.Q8_0, 4096, 4096, 1, x_bf16=False, y_bf16=False, with_bias=False, seed=0x5EED)
 
 
 @pytest.mark.parametrize("fmt", list(Q))
