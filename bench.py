@@ -300,6 +300,11 @@ def run_nnq(args, rank, world, local_rank):
                 "kernel": "skinny_q4k_m1_kernel",
                 "bytes_per_launch": per_gpu_bytes_per_launch, "us_per_launch": per_launch_s * 1e6}
 
+    # ---- the other configurations of the path, timed briefly (not the headline) ----
+    others = None
+    if world == 1 and m == 1 and not args.no_others:
+        others = other_configs(torch, backend, layers, gen, dev)
+
     # ---- end to end through the host entry point of the C ABI ----
     e2e = None
     if world == 1 and not args.no_e2e:
@@ -355,12 +360,98 @@ def run_nnq(args, rank, world, local_rank):
                        "cuda_graph": graph is not None,
                        "tokens_per_s_equiv": 1e3 / ms_per_step * (36 / args.layers)},
             "roofline": roofline, "clocks": clocks.summary(), "gpu_launches": int(launched),
-            "e2e": e2e, "cpu_baseline": cpu,
+            "e2e": e2e, "cpu_baseline": cpu, "other_configs": others,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def other_configs(torch, backend, layers, gen, dev):
+    """Short device-timed runs of the path's other configurations (inputs resident in HBM, more
+    weight bytes per pass than L2 holds): the Q4_K sweep at 16 / 128 / 512 tokens over the same
+    36 layers, the Q8_0 4096 x 4096 GEMV with f32 activations, and a Q6_K vocabulary-sized GEMV."""
+    import ctypes
+
+    from nn_b200 import api
+    from nn_b200 import workload as W
+    from nn_b200.formats import QuantFormat, algorithmic_bytes
+
+    lib, ctx = backend._lib, backend._ctx
+    peak_hbm, _ = _peaks()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_tf = float(json.load(f).get("bf16_tflops", 0.0)) or 1590.0
+    except OSError:
+        peak_tf = 1590.0   # fallback figure
+    out = {}
+
+    def timed(fn, reps):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3
+
+    # Q4_K projection sweep at larger token counts (bf16 in / out), one pass over all layers
+    for mm in (16, 128, 512):
+        xs = {k: torch.randn(mm, k, device=dev, generator=gen).to(torch.bfloat16) for k in (W.HIDDEN, W.FFN)}
+        ys = {n: torch.empty(mm, n, dtype=torch.bfloat16, device=dev) for n in (W.HIDDEN, W.KV_DIM, W.FFN)}
+
+        def sweep():
+            for lw in layers:
+                for name, n, k in W.PROJECTIONS:
+                    st = lib.nnq_linear(ctx, lw[name].handle(), xs[k].data_ptr(), api.BF16, mm, None,
+                                        ys[n].data_ptr(), api.BF16, None)
+                    if st != 0:
+                        backend.check(st)
+
+        sec = timed(sweep, 2)
+        algo = W.layer_bytes(mm).algorithmic * len(layers)
+        flops = 2.0 * mm * sum(n * k for _, n, k in W.PROJECTIONS) * len(layers)
+        row = {"ms_per_pass": sec * 1e3, "gbs": algo / sec / 1e9, "tflops": flops / sec / 1e12}
+        if mm <= 16:
+            row["bound"], row["frac"] = "hbm", algo / sec / 1e9 / peak_hbm
+        else:
+            row["bound"], row["frac"] = "tensor", flops / sec / 1e12 / peak_tf
+        out[f"q4_k_projection_sweep_m{mm}"] = row
+
+    def gemv(fmt, gen_fn, n, k, copies, x_f32, reps):
+        ws = []
+        for _ in range(copies):
+            raw = gen_fn(torch, gen, n, k)
+            ws.append(api.DeviceWeight.from_device(backend, fmt, raw, n, k))
+            del raw
+        x = torch.randn(1, k, device=dev, generator=gen)
+        if not x_f32:
+            x = x.to(torch.bfloat16)
+        y = torch.empty(1, n, dtype=torch.float32, device=dev)
+        xdt = api.F32 if x_f32 else api.BF16
+        i = [0]
+
+        def one():
+            st = lib.nnq_linear(ctx, ws[i[0] % copies].handle(), x.data_ptr(), xdt, 1, None, y.data_ptr(), api.F32, None)
+            i[0] += 1
+            if st != 0:
+                backend.check(st)
+
+        sec = timed(one, reps)
+        algo = algorithmic_bytes(fmt, 1, n, k, 4 if x_f32 else 2, 4)
+        for w in ws:
+            w.release()
+        return {"us": sec * 1e6, "gbs": algo / sec / 1e9, "bound": "hbm", "frac": algo / sec / 1e9 / peak_hbm,
+                "weights_rotated": copies}
+
+    out["q8_0_gemv_4096x4096_f32_m1"] = gemv(QuantFormat.Q8_0, W.gen_q8_0_device, 4096, 4096, 10, True, 40)
+    out["q6_k_gemv_151936x4096_bf16_m1"] = gemv(QuantFormat.Q6_K, W.gen_q6_k_device, 151936, 4096, 1, False, 10)
+    backend.device_status()
+    return out
 
 
 def main():
@@ -374,6 +465,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-others", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -1311,7 +1311,8 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     const bool f32x = x_dt == NNQ_F32;
     int ctas_per_sm = 0;
     const int layout = jobs[0].w->tiled_layout;
-    const bool token_columns = m > 1 || layout != kTiledQ4K;
+    static const char *env_tc = getenv("NNQ_SKINNY_TOKCOL");  // tuning aid: token-column kernel at M = 1 too
+    const bool token_columns = m > 1 || layout != kTiledQ4K || (env_tc && atoi(env_tc) == 1 && !f32x);
     if (!token_columns) pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
     else P.stages = 2;
     if (P.stages == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "K = %lld is too large for the skinny kernel", (long long)jobs[0].w->k);

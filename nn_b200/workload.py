@@ -65,6 +65,28 @@ def gen_q4_k_device(torch, gen, n: int, k: int, scale: float = 0.01):
     return out.reshape(-1)
 
 
+def gen_q8_0_device(torch, gen, n: int, k: int, scale: float = 0.02):
+    """Q8_0 blocks drawn on the device: d = f16(|N(0,1)|*scale), quants uniform over all bytes
+    (the configured range is [-127, 127]; -128 appears with probability 1/256)."""
+    nb = n * (k // 32)
+    dev = gen.device
+    out = torch.randint(0, 256, (nb, 34), dtype=torch.uint8, device=dev, generator=gen)
+    d = (torch.randn(nb, 1, device=dev, generator=gen).abs() * scale).to(torch.float16)
+    out[:, 0:2] = d.view(torch.uint8).reshape(nb, 2)
+    return out.reshape(-1)
+
+
+def gen_q6_k_device(torch, gen, n: int, k: int, scale: float = 0.01):
+    """Q6_K blocks drawn on the device: d = f16(|N(0,1)|*scale), int8 scales and six-bit quants
+    uniform."""
+    nb = n * (k // 256)
+    dev = gen.device
+    out = torch.randint(0, 256, (nb, 210), dtype=torch.uint8, device=dev, generator=gen)
+    d = (torch.randn(nb, 1, device=dev, generator=gen).abs() * scale).to(torch.float16)
+    out[:, 208:210] = d.view(torch.uint8).reshape(nb, 2)
+    return out.reshape(-1)
+
+
 def gen_q4_k_host(seed: int, n: int, k: int) -> np.ndarray:
     from .formats import gen_q4_k
     return gen_q4_k(seed, n, k)
