@@ -71,6 +71,7 @@ struct nnq_weight {
     uint8_t *d_tiled;    // re-tiled copy for the skinny kernels (same byte count, padded tiles)
     size_t tiled_bytes;
     int tiled_layout;    // nnq::TiledLayout
+    int tile_sb;         // blocks of 32 weights per tile row (8; 6 for MXFP4 with K % 256 != 0)
 };
 
 namespace nnq {

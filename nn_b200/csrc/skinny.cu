@@ -56,7 +56,7 @@ struct SkinnyParams {
     int njobs;
     int m;              // tokens (1 for the M = 1 kernel, 2..16 for the token-column kernel)
     int y_dt;
-    int kblocks;        // K / 256
+    int kblocks;        // tiles along K (K / 256; K / 192 for six-block MXFP4 tiles)
     int total_tiles;    // row tiles of all jobs
     int stages;         // ring depth per warp
     int diag;           // diagnostics (NNQ_SKINNY_DIAG): bit 0 = skip the arithmetic (stream only),
@@ -697,13 +697,14 @@ struct MnConsts {
     }
 };
 
-template <int FMT>
-struct TileFmt;
+template <int FMT, int SB = 8>
+struct TileFmt;   // SB = sub-blocks of 32 weights per tile row
 
 // ---- Q4_K (both element orders share the tiled layout) ----
 template <>
-struct TileFmt<NNQ_Q4_K> {
+struct TileFmt<NNQ_Q4_K, 8> {
     static constexpr int kBytes = 2304;
+    static constexpr int kElems = 256;
     template <int NT, bool F32X>
     static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *sct4, const uint8_t *const (&xrow)[NT],
                                                 int koff, int lane, int g, int t, const MnConsts &K,
@@ -761,8 +762,9 @@ struct TileFmt<NNQ_Q4_K> {
 
 // ---- Q8_0 ----
 template <>
-struct TileFmt<NNQ_Q8_0> {
+struct TileFmt<NNQ_Q8_0, 8> {
     static constexpr int kBytes = 4352;
+    static constexpr int kElems = 256;
     template <int NT, bool F32X>
     static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *, const uint8_t *const (&xrow)[NT],
                                                 int koff, int lane, int g, int t, const MnConsts &K,
@@ -807,8 +809,9 @@ struct TileFmt<NNQ_Q8_0> {
 
 // ---- Q6_K ----
 template <>
-struct TileFmt<NNQ_Q6_K> {
+struct TileFmt<NNQ_Q6_K, 8> {
     static constexpr int kBytes = 3360;
+    static constexpr int kElems = 256;
     template <int NT, bool F32X>
     static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *sct4, const uint8_t *const (&xrow)[NT],
                                                 int koff, int lane, int g, int t, const MnConsts &K,
@@ -859,6 +862,62 @@ struct TileFmt<NNQ_Q6_K> {
     }
 };
 
+// ---- MXFP4 (K-blocked layouts: 17-byte blocks, or codes [N, K/2] + scales [N, K/32]) ----
+// Tile = 16 rows x SB blocks of 32 (SB = 8, or 6 when K is a multiple of 192 but not of 256, as
+// the 2880-wide gpt-oss experts): [0,128) E8M0 scale bytes, row r at 8r; then per block 256 B,
+// lane l = 4g + t 8 B = {word row g, word row g+8} for elements 8t..8t+7. A word keeps the
+// eight E2M1 magnitudes (3 bits) in nibble order and the sign of pair i = (e_2i, e_2i+1) at
+// bits 4i+3 and 4i+19. Magnitudes become bf16 through two 8-entry byte tables (PRMT), the signs
+// are shifted onto bits 15 / 31: exact values, no offset, one scale per block applied on the
+// f32 accumulators.
+template <int SB>
+struct TileFmt<NNQ_MXFP4_SPLIT, SB> {
+    static constexpr int kBytes = 128 + 256 * SB;
+    static constexpr int kElems = 32 * SB;
+    static __device__ __forceinline__ void pairs(uint32_t w, uint32_t (&a)[4]) {
+        const uint32_t sel = w & 0x77777777u;
+        const uint32_t lo_e = __byte_perm(0xC0800000u, 0xC0804000u, sel), hi_e = __byte_perm(0x3F3F3F00u, 0x40404040u, sel);
+        const uint32_t lo_o = __byte_perm(0xC0800000u, 0xC0804000u, sel >> 16), hi_o = __byte_perm(0x3F3F3F00u, 0x40404040u, sel >> 16);
+        a[0] = __byte_perm(lo_e, hi_e, 0x5140) | ((w << 12) & 0x80008000u);
+        a[1] = __byte_perm(lo_e, hi_e, 0x7362) | ((w << 8) & 0x80008000u);
+        a[2] = __byte_perm(lo_o, hi_o, 0x5140) | ((w << 4) & 0x80008000u);
+        a[3] = __byte_perm(lo_o, hi_o, 0x7362) | (w & 0x80008000u);
+    }
+    static __device__ __forceinline__ float scale_of(uint2 s, int sb) {   // 2^(e-127); e = 0 -> 2^-127
+        const uint32_t e = ((sb < 4 ? s.x : s.y) >> (8 * (sb & 3))) & 0xFFu;
+        return __uint_as_float(e ? e << 23 : 0x00400000u);
+    }
+    template <int NT, bool F32X>
+    static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *, const uint8_t *const (&xrow)[NT],
+                                                int koff, int lane, int g, int t, const MnConsts &K,
+                                                float (&y)[NT][4]) {
+        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint2 sg = reinterpret_cast<const uint2 *>(stage)[g], sg8 = reinterpret_cast<const uint2 *>(stage)[g + 8];
+        const uint2 *cw = reinterpret_cast<const uint2 *>(stage + 128);
+#pragma unroll
+        for (int sb = 0; sb < SB; sb++) {
+            const uint2 q = cw[sb * 32 + lane];
+            uint32_t A[4], A8[4];
+            pairs(q.x, A);
+            pairs(q.y, A8);
+            const float d = scale_of(sg, sb), d8 = scale_of(sg8, sb);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int e0 = koff + sb * 32 + 8 * t;
+                const XB<F32X> xb = load_xb<F32X>(xrow[nt], e0, e0 + 4);
+                float c[4];
+                mma_x<F32X>(c, A[0], A8[0], A[1], A8[1], xb, 0, zero);
+                mma_x<F32X>(c, A[2], A8[2], A[3], A8[3], xb, 1, c);
+                y[nt][0] = fmaf(d, c[0], y[nt][0]);
+                y[nt][1] = fmaf(d, c[1], y[nt][1]);
+                y[nt][2] = fmaf(d8, c[2], y[nt][2]);
+                y[nt][3] = fmaf(d8, c[3], y[nt][3]);
+            }
+        }
+        (void)K;
+    }
+};
+
 template <int BYTES>
 __device__ __forceinline__ void issue_tile_n(uint32_t dst, const void *src, uint32_t bar, int pred) {
     asm volatile(
@@ -882,11 +941,12 @@ __host__ __device__ inline MnPlan mn_plan(int tile_bytes, int stages, int nt) {
     return p;
 }
 
-template <int FMT, int NT, bool F32X>
+template <int FMT, int SB, int NT, bool F32X>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 skinny_mn_kernel(const __grid_constant__ SkinnyParams P) {
-    using TF = TileFmt<FMT>;
+    using TF = TileFmt<FMT, SB>;
     constexpr int TB = TF::kBytes;
+    constexpr int TE = TF::kElems;   // weights per tile row
     extern __shared__ __align__(128) uint8_t smem[];
     const MnPlan L = mn_plan(TB, P.stages, NT);
     const int tid = threadIdx.x, lane = tid & 31;
@@ -964,7 +1024,7 @@ skinny_mn_kernel(const __grid_constant__ SkinnyParams P) {
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const int tok = nt * 8 + g;
-        xrow[nt] = reinterpret_cast<const uint8_t *>(P.x) + (size_t)(tok < P.m ? tok : 0) * P.kblocks * 256 * (F32X ? 4 : 2);
+        xrow[nt] = reinterpret_cast<const uint8_t *>(P.x) + (size_t)(tok < P.m ? tok : 0) * P.kblocks * TE * (F32X ? 4 : 2);
     }
     MnConsts K;
     K.init();
@@ -1021,7 +1081,7 @@ skinny_mn_kernel(const __grid_constant__ SkinnyParams P) {
 #pragma unroll 1
         for (int k = 0; k < nkb; k++) {
             ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
-            TF::template tile<NT, F32X>(ring + slot * TB, sct4, xrow, (kb_lo + k) * 256, lane, g, t, K, y);
+            TF::template tile<NT, F32X>(ring + slot * TB, sct4, xrow, (kb_lo + k) * TE, lane, g, t, K, y);
             consumed++;
             if (++slot == stages) {
                 slot = 0;
@@ -1138,44 +1198,114 @@ __global__ void repack_q6_k_kernel(const uint8_t *__restrict__ raw, uint8_t *__r
 
 nnq_status skinny_init(nnq_ctx *) { return NNQ_OK; }
 
-static int tile_bytes_of(int fmt) {
+// MXFP4 -> tiles. CORE: 17-byte blocks (scale, 16 code bytes); SPLIT: codes [N, K/2] and scales
+// [N, K/32] apart. Low nibble = even element in both. One thread per (row, block of 32).
+template <int SB>
+__global__ void repack_mxfp4_kernel(const uint8_t *__restrict__ raw, const uint8_t *__restrict__ scales,
+                                    uint8_t *__restrict__ tiled, int n, int ktiles, int split) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t bpr = (int64_t)ktiles * SB;   // blocks per row
+    if (idx >= (int64_t)n * bpr) return;
+    const int row = (int)(idx / bpr), blk = (int)(idx % bpr);
+    const int kb = blk / SB, sb = blk % SB;
+    const uint8_t *codes = split ? raw + idx * 16 : raw + idx * 17 + 1;
+    const uint8_t e8 = split ? scales[idx] : raw[idx * 17];
+    uint8_t *tile = tiled + ((int64_t)(row >> 4) * ktiles + kb) * (128 + 256 * SB);
+    const int r16 = row & 15, g = row & 7, upper = (row >> 3) & 1;
+    tile[r16 * 8 + sb] = e8;
+    if (SB < 8 && sb == 0)
+        for (int z = SB; z < 8; z++) tile[r16 * 8 + z] = 0;
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t byte = codes[4 * t + (i >> 1)];
+            const uint32_t c = (i & 1) ? byte >> 4 : byte & 15u;
+            word |= (c & 7u) << (4 * i);                                    // magnitude, nibble order
+            word |= (c >> 3) << (4 * (i >> 1) + 3 + 16 * (i & 1));          // sign of pair i / 2
+        }
+        reinterpret_cast<uint32_t *>(tile + 128 + 256 * sb + 8 * (4 * g + t))[upper] = word;
+    }
+}
+
+static int tile_bytes_of(int fmt, int sb) {
     switch (fmt) {
         case NNQ_Q4_K: case NNQ_Q4_K_GGML: return TileFmt<NNQ_Q4_K>::kBytes;
         case NNQ_Q8_0: return TileFmt<NNQ_Q8_0>::kBytes;
         case NNQ_Q6_K: return TileFmt<NNQ_Q6_K>::kBytes;
+        case NNQ_MXFP4_CORE: case NNQ_MXFP4_SPLIT: return 128 + 256 * sb;
         default: return 0;
     }
 }
 
+// Sub-blocks per tile row for this format and K; 0 = no tiled layout.
+static int tile_sb_of(int fmt, int64_t k) {
+    switch (fmt) {
+        case NNQ_Q4_K: case NNQ_Q4_K_GGML: case NNQ_Q8_0: case NNQ_Q6_K: return k % 256 == 0 ? 8 : 0;
+        case NNQ_MXFP4_CORE: case NNQ_MXFP4_SPLIT: return k % 256 == 0 ? 8 : (k % 192 == 0 ? 6 : 0);
+        default: return 0;
+    }
+}
+
+nnq_status build_tiled_buffer(nnq_ctx *ctx, int fmt, const uint8_t *d_raw, const uint8_t *d_scales, int64_t n,
+                              int64_t k, uint8_t **out, size_t *out_bytes, int *out_sb) {
+    *out = nullptr;
+    *out_bytes = 0;
+    *out_sb = 0;
+    const int sb = tile_sb_of(fmt, k);
+    if (sb == 0 || n == 0 || k == 0) return NNQ_OK;
+    if (n > (1 << 24) || k > (1 << 24)) return NNQ_OK;
+    const int tb = tile_bytes_of(fmt, sb);
+    const int ktiles = (int)(k / (32 * sb));
+    const int64_t row_tiles = (n + 15) / 16;
+    const size_t bytes = (size_t)row_tiles * ktiles * tb;
+    uint8_t *d = nullptr;
+    nnq_status s = check_cuda(ctx, cudaMalloc(&d, bytes), "cudaMalloc tiled weight");
+    if (s != NNQ_OK) return s;
+    if (n % 16) s = check_cuda(ctx, cudaMemset(d, 0, bytes), "cudaMemset tiled weight");
+    if (s == NNQ_OK) {
+        const int64_t total = fmt == NNQ_MXFP4_CORE || fmt == NNQ_MXFP4_SPLIT ? n * (k / 32) : n * ktiles * 8;
+        const int grid = (int)((total + 255) / 256);
+        const int split = fmt == NNQ_MXFP4_SPLIT;
+        switch (fmt) {
+            case NNQ_Q4_K: repack_q4k_kernel<false><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+            case NNQ_Q4_K_GGML: repack_q4k_kernel<true><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+            case NNQ_Q8_0: repack_q8_0_kernel<<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+            case NNQ_Q6_K: repack_q6_k_kernel<<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+            default:
+                if (sb == 8) repack_mxfp4_kernel<8><<<grid, 256>>>(d_raw, d_scales, d, (int)n, ktiles, split);
+                else repack_mxfp4_kernel<6><<<grid, 256>>>(d_raw, d_scales, d, (int)n, ktiles, split);
+                break;
+        }
+        ctx->launches++;
+        s = check_cuda(ctx, cudaGetLastError(), "repack launch");
+        if (s == NNQ_OK) s = check_cuda(ctx, cudaDeviceSynchronize(), "repack");
+    }
+    if (s != NNQ_OK) {
+        cudaFree(d);
+        return s;
+    }
+    *out = d;
+    *out_bytes = bytes;
+    *out_sb = sb;
+    return NNQ_OK;
+}
+
+static int layout_of(int fmt) {
+    switch (fmt) {
+        case NNQ_Q4_K: case NNQ_Q4_K_GGML: return kTiledQ4K;
+        case NNQ_Q8_0: return kTiledQ8_0;
+        case NNQ_Q6_K: return kTiledQ6K;
+        case NNQ_MXFP4_CORE: case NNQ_MXFP4_SPLIT: return kTiledMxfp4;
+        default: return kTiledNone;
+    }
+}
+
 nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w) {
-    const int tb = tile_bytes_of(w->fmt);
-    if (tb == 0) return NNQ_OK;
-    if (w->n == 0 || w->k == 0 || w->k % 256 != 0) return NNQ_OK;
-    if (w->n > (1 << 24) || w->k > (1 << 24)) return NNQ_OK;
-    int kblocks = (int)(w->k / 256);
-    int64_t row_tiles = (w->n + 15) / 16;
-    size_t bytes = (size_t)row_tiles * kblocks * tb;
-    nnq_status s = check_cuda(ctx, cudaMalloc(&w->d_tiled, bytes), "cudaMalloc tiled weight");
+    nnq_status s = build_tiled_buffer(ctx, w->fmt, w->d_raw, w->d_scales, w->n, w->k, &w->d_tiled, &w->tiled_bytes, &w->tile_sb);
     if (s != NNQ_OK) return s;
-    w->tiled_bytes = bytes;
-    if (w->n % 16) {
-        s = check_cuda(ctx, cudaMemset(w->d_tiled, 0, bytes), "cudaMemset tiled weight");
-        if (s != NNQ_OK) return s;
-    }
-    int64_t total = w->n * kblocks * 8;
-    int grid = (int)((total + 255) / 256);
-    switch (w->fmt) {
-        case NNQ_Q4_K: repack_q4k_kernel<false><<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks); break;
-        case NNQ_Q4_K_GGML: repack_q4k_kernel<true><<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks); break;
-        case NNQ_Q8_0: repack_q8_0_kernel<<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks); break;
-        default: repack_q6_k_kernel<<<grid, 256>>>(w->d_raw, w->d_tiled, (int)w->n, kblocks); break;
-    }
-    ctx->launches++;
-    s = check_cuda(ctx, cudaGetLastError(), "repack launch");
-    if (s != NNQ_OK) return s;
-    s = check_cuda(ctx, cudaDeviceSynchronize(), "repack");
-    if (s != NNQ_OK) return s;
-    w->tiled_layout = w->fmt == NNQ_Q8_0 ? kTiledQ8_0 : (w->fmt == NNQ_Q6_K ? kTiledQ6K : kTiledQ4K);
+    w->tiled_layout = w->d_tiled ? layout_of(w->fmt) : kTiledNone;
     return NNQ_OK;
 }
 
@@ -1249,13 +1379,13 @@ static cudaError_t launch_ks(int ksplit, const SkinnyParams &P, int grid, int sm
     }
 }
 
-template <int FMT, int NT, bool F32X>
+template <int FMT, int SB, int NT, bool F32X>
 static cudaError_t launch_mn(const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_mn_kernel<FMT, NT, F32X>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        cudaError_t e = cudaFuncSetAttribute(skinny_mn_kernel<FMT, SB, NT, F32X>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
@@ -1269,13 +1399,13 @@ static cudaError_t launch_mn(const SkinnyParams &P, int grid, int smem_bytes, cu
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, skinny_mn_kernel<FMT, NT, F32X>, P);
+    return cudaLaunchKernelEx(&cfg, skinny_mn_kernel<FMT, SB, NT, F32X>, P);
 }
 
-template <int FMT>
+template <int FMT, int SB = 8>
 static cudaError_t launch_mn_fmt(const SkinnyParams &P, int nt, bool f32x, int grid, int smem_bytes, cudaStream_t stream) {
-    if (f32x) return launch_mn<FMT, 1, true>(P, grid, smem_bytes, stream);
-    return nt == 1 ? launch_mn<FMT, 1, false>(P, grid, smem_bytes, stream) : launch_mn<FMT, 2, false>(P, grid, smem_bytes, stream);
+    if (f32x) return launch_mn<FMT, SB, 1, true>(P, grid, smem_bytes, stream);
+    return nt == 1 ? launch_mn<FMT, SB, 1, false>(P, grid, smem_bytes, stream) : launch_mn<FMT, SB, 2, false>(P, grid, smem_bytes, stream);
 }
 
 // Diagnostic only (NNQ_SKINNY_DIAG=4): read the tiled weights of the jobs with plain coalesced
@@ -1302,7 +1432,8 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     P.m = m;
     P.y_dt = y_dt;
     P.x = jobs[0].x;
-    P.kblocks = (int)(jobs[0].w->k / 256);
+    const int tile_sb = jobs[0].w->tile_sb;
+    P.kblocks = (int)(jobs[0].w->k / (32 * tile_sb));
     P.status = ctx->d_status;
     static const char *env_diag = getenv("NNQ_SKINNY_DIAG");
     P.diag = env_diag ? atoi(env_diag) : 0;
@@ -1332,14 +1463,16 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     if (token_columns) {
         // a unit is one row tile, its K split over the 8 warps
         const int nt = m <= 8 ? 1 : 2;
-        const int smem_bytes = mn_plan(tile_bytes_of(jobs[0].w->fmt), P.stages, nt).total;
+        const int smem_bytes = mn_plan(tile_bytes_of(jobs[0].w->fmt, tile_sb), P.stages, nt).total;
         int per_sm = kSmemMax / (smem_bytes + 1024);
         if (per_sm > 2) per_sm = 2;   // register budget of the kernel
         int grid = tiles < ctx->sm_count * per_sm ? tiles : ctx->sm_count * per_sm;
         cudaError_t e;
         if (layout == kTiledQ4K) e = launch_mn_fmt<NNQ_Q4_K>(P, nt, f32x, grid, smem_bytes, stream);
         else if (layout == kTiledQ8_0) e = launch_mn_fmt<NNQ_Q8_0>(P, nt, f32x, grid, smem_bytes, stream);
-        else e = launch_mn_fmt<NNQ_Q6_K>(P, nt, f32x, grid, smem_bytes, stream);
+        else if (layout == kTiledQ6K) e = launch_mn_fmt<NNQ_Q6_K>(P, nt, f32x, grid, smem_bytes, stream);
+        else if (tile_sb == 8) e = launch_mn_fmt<NNQ_MXFP4_SPLIT, 8>(P, nt, f32x, grid, smem_bytes, stream);
+        else e = launch_mn_fmt<NNQ_MXFP4_SPLIT, 6>(P, nt, f32x, grid, smem_bytes, stream);
         ctx->launches++;
         return check_cuda(ctx, e, "skinny launch");
     }
@@ -1377,7 +1510,7 @@ nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_d
     int i = 0;
     while (i < count) {
         int jn = i + 1;
-        while (jn < count && jobs[jn].x == jobs[i].x && jobs[jn].w->k == jobs[i].w->k) jn++;
+        while (jn < count && jobs[jn].x == jobs[i].x && jobs[jn].w->k == jobs[i].w->k && jobs[jn].w->tiled_layout == jobs[i].w->tiled_layout) jn++;
         nnq_status s = launch_group(ctx, jobs + i, jn - i, x_dt, (int)m, y_dt, stream);
         if (s != NNQ_OK) return s;
         i = jn;

@@ -18,6 +18,10 @@ struct SkinnyJob {
 nnq_status skinny_init(nnq_ctx *ctx);
 // Builds w->d_tiled from w->d_raw when the format / shape has a skinny kernel.
 nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w);
+// Tiled copy of raw blocks [n, k] (NULL when the format / K has no tiled layout); *sb = blocks of
+// 32 weights per tile row.
+nnq_status build_tiled_buffer(nnq_ctx *ctx, int fmt, const uint8_t *d_raw, const uint8_t *d_scales, int64_t n,
+                              int64_t k, uint8_t **out, size_t *out_bytes, int *sb);
 // True when launch_skinny can run this weight with M rows of activations.
 bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt);
 // One launch computing y_i = x_i * W_i^T (+ bias_i) for all jobs (same format, same M).

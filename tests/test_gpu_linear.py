@@ -34,8 +34,9 @@ def _run(fmt, n, k, m, x_bf16, y_bf16, with_bias, seed=1, path=api.PATH_AUTO):
         t.backend.set_path(api.PATH_AUTO)
     y32, y64, mag = P.oracle_linear(fmt, w, sc, x, bias, n, k)
     got = y.float().cpu().numpy()
-    skinny = (fmt in (Q.Q4_K, Q.Q4_K_GGML, Q.Q8_0, Q.Q6_K) and k % 256 == 0 and 1 <= m <= 16
-              and (x_bf16 or m <= 8 or (m == 1 and fmt in (Q.Q4_K, Q.Q4_K_GGML))))
+    tiled = (fmt in (Q.Q4_K, Q.Q4_K_GGML, Q.Q8_0, Q.Q6_K) and k % 256 == 0) or (
+        fmt in (Q.MXFP4_CORE, Q.MXFP4_SPLIT) and (k % 256 == 0 or k % 192 == 0))
+    skinny = tiled and 1 <= m <= 16 and (x_bf16 or m <= 8 or (m == 1 and fmt in (Q.Q4_K, Q.Q4_K_GGML)))
     tensor_path = path == api.PATH_TENSOR or (
         path == api.PATH_AUTO and not skinny and k % 64 == 0 and (m > 16 or (m >= 5 and x_bf16)))
     if tensor_path:
@@ -73,6 +74,15 @@ def test_token_column_kernel_formats(fmt, m, x_bf16, n, k):
     if fmt == Q.Q4_K and m == 1:
         pytest.skip("M = 1 Q4_K has its own kernel")
     _run(fmt, n, k, m, x_bf16=x_bf16, y_bf16=(m % 2 == 0), with_bias=(m % 3 == 2), seed=400 + m, path=api.PATH_SKINNY)
+
+
+@pytest.mark.parametrize("fmt", [Q.MXFP4_CORE, Q.MXFP4_SPLIT])
+@pytest.mark.parametrize("m,x_bf16", [(1, True), (1, False), (4, False), (8, True), (13, True)])
+@pytest.mark.parametrize("n,k", [(200, 2048), (90, 2880), (33, 576), (40, 512)])
+def test_token_column_kernel_mxfp4(fmt, m, x_bf16, n, k):
+    """MXFP4 tiles with eight blocks per tile row, and with six (K = 2880 and 576 are multiples
+    of 192 but not of 256, as the gpt-oss expert width)."""
+    _run(fmt, n, k, m, x_bf16=x_bf16, y_bf16=(m % 2 == 0), with_bias=(m == 4), seed=500 + m, path=api.PATH_SKINNY)
 
 
 def test_q8_0_gemv_reference_config():
