@@ -17,7 +17,10 @@
 #include <new>
 
 #include "decode.cuh"
+#include <stdlib.h>
+
 #include "moe.h"
+#include "skinny.h"
 
 namespace nnq {
 
@@ -37,23 +40,33 @@ __device__ __forceinline__ float ld_act<__nv_bfloat16>(const __nv_bfloat16 *p, i
 constexpr int kMaxExperts = 64;
 constexpr int kMaxTopK = 8;
 
+// One CTA per token: the 8 warps share the experts (warp w: experts w, w + 8, ...), every lane
+// accumulates a strided slice of the hidden dimension, shuffle tree per expert; warp 0 then does
+// the softmax and the top-k selection over the logits in shared memory.
 template <typename XT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_router_kernel(const XT *__restrict__ x, const float *__restrict__ rw, const float *__restrict__ rb,
                   int T, int H, int E, int top_k, int *__restrict__ idx, float *__restrict__ wt) {
-    const int lane = threadIdx.x & 31;
-    const int tok = blockIdx.x * 4 + (threadIdx.x >> 5);
+    extern __shared__ float xs[];          // the token's activations as f32, then E logits
+    float *logits = xs + H;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tok = blockIdx.x;
     if (tok >= T) return;
-    // logits: lane e (and e + 32) ends up holding expert e's logit
-    float l0 = -CUDART_INF_F, l1 = -CUDART_INF_F;
-    for (int e = 0; e < E; e++) {
+    for (int h = threadIdx.x; h < H; h += 256) xs[h] = ld_act<XT>(x, (int64_t)tok * H + h);
+    __syncthreads();
+    for (int e = warp; e < E; e += 8) {
+        const float *w = rw + (int64_t)e * H;
         float acc = 0.0f;
-        for (int h = lane; h < H; h += 32) acc = fmaf(ld_act<XT>(x, (int64_t)tok * H + h), __ldg(rw + (int64_t)e * H + h), acc);
+        for (int h = lane; h < H; h += 32) acc = fmaf(xs[h], __ldg(w + h), acc);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
-        acc += __ldg(rb + e);
-        if (e < 32) { if (lane == e) l0 = acc; } else { if (lane == e - 32) l1 = acc; }
+        if (lane == 0) logits[e] = acc + __ldg(rb + e);
     }
+    __syncthreads();
+    if (warp != 0) return;
+    // lane e (and e + 32) holds expert e's logit
+    float l0 = lane < E ? logits[lane] : -CUDART_INF_F;
+    float l1 = lane + 32 < E ? logits[lane + 32] : -CUDART_INF_F;
     // softmax over the E experts (max-subtracted, f32)
     float mx = fmaxf(l0, l1);
 #pragma unroll
@@ -316,7 +329,7 @@ __global__ void moe_combine_kernel(const float *__restrict__ o, const int *__res
         for (int b = a; b > 0 && idx[(int64_t)t * top_k + order[b]] < idx[(int64_t)t * top_k + order[b - 1]]; b--) {
             int tmp = order[b]; order[b] = order[b - 1]; order[b - 1] = tmp;
         }
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < H; j += gridDim.y * blockDim.x) {
         float acc = 0.0f;
         for (int s = 0; s < top_k; s++) {
             int slot = order[s];
@@ -382,14 +395,27 @@ static nnq_status ensure_scratch(nnq_ctx *ctx, const nnq_moe *m, int64_t T, MoeS
 }
 
 template <typename XT>
-static void launch_product(const nnq_moe *m, bool first, const XT *x, const int *rowtok, const MoeScratch &s,
-                           float *out, cudaStream_t st) {
+struct DtypeOf;
+template <>
+struct DtypeOf<float> { static constexpr int value = NNQ_F32; };
+template <>
+struct DtypeOf<__nv_bfloat16> { static constexpr int value = NNQ_BF16; };
+
+template <typename XT>
+static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT *x, const int *rowtok,
+                           const MoeScratch &s, float *out, int64_t rows, cudaStream_t st) {
     const int K = first ? m->hidden : m->inter;
     const int N = first ? 2 * m->inter : m->hidden;
     const uint8_t *d = first ? m->d_gu : m->d_dn;
     const uint8_t *sc = first ? m->d_gu_scales : m->d_dn_scales;
     const float *b = first ? m->d_gu_bias : m->d_dn_bias;
     const int E = m->e_local;
+    if (m->d_gu_tiled) {
+        GroupedArgs a = {first ? m->d_gu_tiled : m->d_dn_tiled, first ? m->gu_tile_stride : m->dn_tile_stride, b, x,
+                         DtypeOf<XT>::value, rowtok, s.offset, out, E, m->top_k, N, K, m->fmt, rows};
+        launch_grouped(ctx, a, st);
+        return;
+    }
     if (m->layout == NNQ_MOE_KN_GPTOSS) {
         dim3 grid((N + 1023) / 1024, E, kMoeKnSplit);
         moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, m->top_k, s.offset, out,
@@ -408,6 +434,22 @@ static void launch_product(const nnq_moe *m, bool first, const XT *x, const int 
 #undef NNQ_NK
 }
 
+// the router keeps one token's activations in shared memory: allow more than the default 48 KB
+template <typename XT>
+static cudaError_t launch_router(const nnq_moe *m, const XT *x, int64_t T, int *idx, float *wt, cudaStream_t st) {
+    const size_t smem = (size_t)(m->hidden + kMaxExperts) * 4;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    moe_router_kernel<XT><<<(int)T, 256, smem, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, m->n_experts, m->top_k, idx, wt);
+    return cudaGetLastError();
+}
+
 template <typename XT>
 static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int64_t T, float *y, int *idx_out,
                                 float *wt_out, bool route_only, cudaStream_t st) {
@@ -416,7 +458,7 @@ static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int
     if (rc != NNQ_OK) return rc;
     const int E = m->n_experts, k = m->top_k;
     const int total = (int)(T * k);
-    moe_router_kernel<XT><<<(int)((T + 3) / 4), 128, 0, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, E, k, s.idx, s.wt);
+    launch_router<XT>(m, x, T, s.idx, s.wt, st);
     ctx->launches++;
     if (idx_out) cudaMemcpyAsync(idx_out, s.idx, (size_t)total * 4, cudaMemcpyDeviceToDevice, st);
     if (wt_out) cudaMemcpyAsync(wt_out, s.wt, (size_t)total * 4, cudaMemcpyDeviceToDevice, st);
@@ -426,11 +468,11 @@ static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
     moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
-    launch_product<XT>(m, true, x, s.rowtok, s, s.gu, st);
+    launch_product<XT>(ctx, m, true, x, s.rowtok, s, s.gu, total, st);
     int64_t hi = (int64_t)total * m->inter;
     moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride);
-    launch_product<float>(m, false, s.h, nullptr, s, s.o, st);
-    moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
+    launch_product<float>(ctx, m, false, s.h, nullptr, s, s.o, total, st);
+    moe_combine_kernel<<<dim3((unsigned)T, T < 1024 ? 4 : 1), 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
     ctx->launches += 7;
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
 }
@@ -468,17 +510,17 @@ static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, 
                                    const MoeScratch &s, cudaStream_t st) {
     const int E = m->n_experts, k = m->top_k;
     const int total = (int)(T * k);
-    moe_router_kernel<XT><<<(int)((T + 3) / 4), 128, 0, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, E, k, s.idx, s.wt);
+    launch_router<XT>(m, x, T, s.idx, s.wt, st);
     const int EL = m->e_local;
     if (EL != E) cudaMemsetAsync(s.pos, 0xFF, (size_t)total * 4, st);   // -1: assignment served elsewhere
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
     moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
-    launch_product<XT>(m, true, x, s.rowtok, s, s.gu, st);
+    launch_product<XT>(ctx, m, true, x, s.rowtok, s, s.gu, total, st);
     int64_t hi = (int64_t)total * m->inter;
     moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride);
-    launch_product<float>(m, false, s.h, nullptr, s, s.o, st);
-    moe_combine_kernel<<<(int)T, 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
+    launch_product<float>(ctx, m, false, s.h, nullptr, s, s.o, total, st);
+    moe_combine_kernel<<<dim3((unsigned)T, T < 1024 ? 4 : 1), 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
     ctx->launches += 8;
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
 }
@@ -507,7 +549,7 @@ nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, i
     if (!ctx || !out) return NNQ_ERR_INVALID_ARG;
     *out = nullptr;
     if (n_experts < 1 || n_experts > kMaxExperts || top_k < 1 || top_k > kMaxTopK || top_k > n_experts ||
-        hidden < 1 || inter < 1)
+        hidden < 1 || inter < 1 || hidden > 49152)
         return fail(ctx, NNQ_ERR_INVALID_ARG, "bad MoE dimensions (experts %d, top_k %d, hidden %d, inter %d)", n_experts, top_k, hidden, inter);
     if (expert_begin < 0 || expert_count < 1 || expert_begin + expert_count > n_experts)
         return fail(ctx, NNQ_ERR_INVALID_ARG, "bad expert range [%d, %d) of %d", expert_begin, expert_begin + expert_count, n_experts);
@@ -546,6 +588,28 @@ nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, i
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn, down, down_bytes, "down");
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_scales, down_scales, down_scales_bytes, "down scales");
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_bias, down_bias, (size_t)expert_count * hidden * 4, "down bias");
+    // tiled copies for the grouped kernel
+    static const char *env_tiled = getenv("NNQ_MOE_TILED");   // tuning aid: 0 keeps the row kernels
+    if (s == NNQ_OK && layout == NNQ_MOE_NK && !(env_tiled && atoi(env_tiled) == 0)) {
+        const size_t gs = tiled_bytes_for(fmt, 2 * (int64_t)inter, hidden, nullptr);
+        const size_t ds = tiled_bytes_for(fmt, hidden, inter, nullptr);
+        if (gs && ds) {
+            const size_t gu_e = gate_up_bytes / expert_count, gus_e = gate_up_scales_bytes / expert_count;
+            const size_t dn_e = down_bytes / expert_count, dns_e = down_scales_bytes / expert_count;
+            s = check_cuda(ctx, cudaMalloc(&m->d_gu_tiled, gs * expert_count), "cudaMalloc tiled experts");
+            if (s == NNQ_OK) s = check_cuda(ctx, cudaMalloc(&m->d_dn_tiled, ds * expert_count), "cudaMalloc tiled experts");
+            for (int e = 0; e < expert_count && s == NNQ_OK; e++) {
+                s = repack_into(ctx, fmt, m->d_gu + e * gu_e, m->d_gu_scales ? m->d_gu_scales + e * gus_e : nullptr,
+                                2 * (int64_t)inter, hidden, m->d_gu_tiled + e * gs);
+                if (s == NNQ_OK)
+                    s = repack_into(ctx, fmt, m->d_dn + e * dn_e, m->d_dn_scales ? m->d_dn_scales + e * dns_e : nullptr,
+                                    hidden, inter, m->d_dn_tiled + e * ds);
+            }
+            if (s == NNQ_OK) s = check_cuda(ctx, cudaDeviceSynchronize(), "expert repack");
+            m->gu_tile_stride = gs;
+            m->dn_tile_stride = ds;
+        }
+    }
     if (s != NNQ_OK) {
         nnq_moe_destroy(m);
         return s;
@@ -570,6 +634,7 @@ void nnq_moe_destroy(nnq_moe *m) {
     if (m->ctx) cudaSetDevice(m->ctx->device);
     cudaFree(m->d_router_w); cudaFree(m->d_router_b); cudaFree(m->d_gu); cudaFree(m->d_gu_scales);
     cudaFree(m->d_gu_bias); cudaFree(m->d_dn); cudaFree(m->d_dn_scales); cudaFree(m->d_dn_bias);
+    cudaFree(m->d_gu_tiled); cudaFree(m->d_dn_tiled);
     cudaGetLastError();
     delete m;
 }

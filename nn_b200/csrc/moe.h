@@ -13,4 +13,8 @@ struct nnq_moe {
     uint8_t *d_gu, *d_gu_scales, *d_dn, *d_dn_scales;
     size_t gu_bytes, gu_scale_bytes, dn_bytes, dn_scale_bytes;   // per tensor (all experts)
     float *d_gu_bias, *d_dn_bias;
+    // tiled copies of the expert weights for the grouped token-column kernel ([N, K] layouts whose
+    // format and K have a tiled layout); NULL otherwise
+    uint8_t *d_gu_tiled, *d_dn_tiled;
+    size_t gu_tile_stride, dn_tile_stride;   // bytes per expert
 };

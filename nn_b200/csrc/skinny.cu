@@ -40,6 +40,7 @@ constexpr int kTileBytes = 2304;
 constexpr int kWarps = 8;          // compute warps per CTA; they split K of one row tile
 constexpr int kMaxStages = 4;      // bulk-copy ring depth per warp (tiles in flight)
 constexpr int kSmemMax = 227 * 1024;         // one CTA per SM
+constexpr int kMoeMaxExperts = 64;
 
 struct SkinnyJobDev {
     const uint8_t *tiled;
@@ -1120,6 +1121,208 @@ skinny_mn_kernel(const __grid_constant__ SkinnyParams P) {
 }
 
 // ---------------------------------------------------------------------------------
+// Grouped token-column kernel: the expert products of a mixture-of-experts block
+// ---------------------------------------------------------------------------------
+//
+// One launch covers every local expert. The routed rows arrive sorted by expert (offset[e] ..
+// offset[e+1], computed on the device by the grouping kernels); a unit is (expert, group of up
+// to 8 routed rows, row tile of the expert's weight), units are numbered expert-major, then
+// row group, then row tile, and CTA c handles units c, c + grid, ... The eight MMA columns are
+// the rows of the group; their activations are read through the row -> token table (first
+// product) or directly (second product). Everything else is the token-column kernel: per-warp
+// rings of bulk-copied tiles, K split over the 8 warps, partial tiles met in shared memory.
+
+struct GroupedParams {
+    const uint8_t *tiled;     // expert e at tiled + e * expert_stride
+    size_t expert_stride;
+    const float *bias;        // [E][n] or NULL
+    const void *x;            // activations, row stride = kblocks * tile elements
+    const int *rowtok;        // routed row -> flat assignment index (token = index / top_k), or NULL: row itself
+    const int *offset;        // [E + 1] first routed row of each expert
+    float *out;               // [rows][n]
+    int experts, top_k, n, row_tiles, kblocks, stages;
+    int *status;
+};
+
+constexpr int kGroupRows = 8;
+
+template <int FMT, int SB, bool F32X>
+__global__ void __launch_bounds__(kWarps * 32, 2)
+skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
+    using TF = TileFmt<FMT, SB>;
+    constexpr int TB = TF::kBytes;
+    constexpr int TE = TF::kElems;
+    constexpr int NT = 1;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const MnPlan L = mn_plan(TB, P.stages, NT);
+    __shared__ int goff[kMoeMaxExperts + 1];   // first row group of each expert
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
+    const int g = lane >> 2, t = lane & 3;
+    const int cta = blockIdx.x, grid = gridDim.x;
+    const int stages = P.stages;
+    uint8_t *ring = smem + warp * stages * TB;
+    float4 *sct4 = reinterpret_cast<float4 *>(smem + L.sct_off + warp * 1024);
+    float4 *part4 = reinterpret_cast<float4 *>(smem + L.part_off);
+    const uint32_t ring_s = smem_u32(ring);
+    const uint32_t bars_s = smem_u32(smem + L.bar_off);
+    const uint32_t bar_s = bars_s + warp * kMaxStages * 8;
+    const uint32_t full_s = bars_s + kWarps * kMaxStages * 8;
+    const uint32_t empty_s = full_s + 16;
+
+    if (tid == 0) {
+        mbar_init(full_s, kWarps);
+        mbar_init(full_s + 8, kWarps);
+        mbar_init(empty_s, 1);
+        mbar_init(empty_s + 8, 1);
+    }
+    if (lane == 0) {
+        for (int d = 0; d < stages; d++) mbar_init(bar_s + 8 * d, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // the routing tables come from the kernels before this one
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) {
+        int acc = 0;
+        for (int e = 0; e < P.experts; e++) {
+            goff[e] = acc;
+            acc += (P.offset[e + 1] - P.offset[e] + kGroupRows - 1) / kGroupRows;
+        }
+        goff[P.experts] = acc;
+    }
+    __syncthreads();
+    const int total_units = goff[P.experts] * P.row_tiles;
+
+    const int kb_lo = (warp * P.kblocks) / kWarps, kb_hi = ((warp + 1) * P.kblocks) / kWarps;
+    const int nkb = kb_hi - kb_lo;
+    const int n_units = cta < total_units ? (total_units - cta + grid - 1) / grid : 0;
+    // expert, first routed row, rows in the group and row tile of a unit
+    auto locate = [&](int unit, int &e, int &r0, int &cnt, int &rt) {
+        const int u = cta + unit * grid;
+        const int q = u / P.row_tiles;
+        rt = u - q * P.row_tiles;
+        e = 0;
+        for (int i = 1; i < P.experts; i++)
+            if (q >= goff[i]) e = i;
+        r0 = P.offset[e] + (q - goff[e]) * kGroupRows;
+        cnt = min(kGroupRows, P.offset[e + 1] - r0);
+    };
+
+    int pf_unit = -1, pf_k = 0, pf_slot = 0;
+    unsigned issued = 0;
+    const uint8_t *pf_src = nullptr;
+    bool pf_done = nkb == 0 || n_units == 0;
+    auto pf_advance_unit = [&]() {
+        if (++pf_unit >= n_units) {
+            pf_done = true;
+            return;
+        }
+        int e, r0, cnt, rt;
+        locate(pf_unit, e, r0, cnt, rt);
+        pf_src = P.tiled + (size_t)e * P.expert_stride + ((size_t)rt * P.kblocks + kb_lo) * TB;
+        pf_k = 0;
+    };
+    if (!pf_done) pf_advance_unit();
+    const int is_lane0 = lane == 0;
+    auto issue = [&]() {
+        if (!pf_done) {
+            issue_tile_n<TB>(ring_s + pf_slot * TB, pf_src, bar_s + 8 * pf_slot, is_lane0);
+            issued++;
+            pf_slot = pf_slot + 1 == stages ? 0 : pf_slot + 1;
+            pf_src += TB;
+            if (++pf_k == nkb) pf_advance_unit();
+        }
+    };
+    for (int d = 0; d < stages; d++) issue();
+
+    MnConsts K;
+    K.init();
+    unsigned consumed = 0;
+    int slot = 0;
+    uint32_t phase = 0;
+    bool failed = false;
+    const size_t xstride = (size_t)P.kblocks * TE * (F32X ? 4 : 2);
+
+    auto finish = [&](int unit) {
+        const int b = unit & 1;
+        if (!mbar_wait_fast(full_s + 8 * b, (unit >> 1) & 1u)) {
+            failed = true;
+            return;
+        }
+        int e, r0, cnt, rt;
+        locate(unit, e, r0, cnt, rt);
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) {
+            const float4 a = part4[(b * kWarps + w) * 32 + lane];
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        }
+        const int row = rt * 16 + g, tok = 2 * t;
+        const float vals[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int tk = tok + (i & 1), rw = row + (i >> 1) * 8;
+            if (tk < cnt && rw < P.n) {
+                float o = vals[i];
+                if (P.bias) o += __ldg(P.bias + (size_t)e * P.n + rw);
+                P.out[(size_t)(r0 + tk) * P.n + rw] = o;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_s + 8 * b);
+    };
+
+#pragma unroll 1
+    for (int unit = 0; unit < n_units && !failed; unit++) {
+        int e, r0, cnt, rt;
+        locate(unit, e, r0, cnt, rt);
+        // this lane's column: routed row r0 + g (a column beyond the group reads row r0 and is never stored)
+        const int r = r0 + (g < cnt ? g : 0);
+        const int src = P.rowtok ? __ldg(P.rowtok + r) / P.top_k : r;
+        const uint8_t *xrow[NT] = {reinterpret_cast<const uint8_t *>(P.x) + (size_t)src * xstride};
+        float y[NT][4] = {{0.0f, 0.0f, 0.0f, 0.0f}};
+        bool ok = true;
+#pragma unroll 1
+        for (int k = 0; k < nkb; k++) {
+            ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
+            TF::template tile<NT, F32X>(ring + slot * TB, sct4, xrow, (kb_lo + k) * TE, lane, g, t, K, y);
+            consumed++;
+            if (++slot == stages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+            __syncwarp();
+            issue();
+        }
+        if (!ok) {
+            failed = true;
+            break;
+        }
+        const int b = unit & 1;
+        if (unit >= 2 && !mbar_wait_fast(empty_s + 8 * b, ((unit >> 1) - 1) & 1u)) {
+            failed = true;
+            break;
+        }
+        part4[(b * kWarps + warp) * 32 + lane] = make_float4(y[0][0], y[0][1], y[0][2], y[0][3]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_s + 8 * b);
+        if (unit >= 1 && warp == (unit - 1) % kWarps) finish(unit - 1);
+    }
+    if (!failed && n_units >= 1 && warp == (n_units - 1) % kWarps) finish(n_units - 1);
+    if (failed) {
+        if (lane == 0) atomicExch(P.status, 1);
+        for (unsigned n = consumed; n < issued; n++) {
+            mbar_wait(bar_s + 8 * slot, phase);
+            if (++slot == stages) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------
 // repack of Q8_0 and Q6_K raw blocks into their tiled layouts
 // ---------------------------------------------------------------------------------
 
@@ -1248,40 +1451,52 @@ static int tile_sb_of(int fmt, int64_t k) {
     }
 }
 
+size_t tiled_bytes_for(int fmt, int64_t n, int64_t k, int *sb_out) {
+    const int sb = tile_sb_of(fmt, k);
+    if (sb_out) *sb_out = sb;
+    if (sb == 0 || n <= 0 || k <= 0 || n > (1 << 24) || k > (1 << 24)) return 0;
+    return (size_t)((n + 15) / 16) * (size_t)(k / (32 * sb)) * tile_bytes_of(fmt, sb);
+}
+
+nnq_status repack_into(nnq_ctx *ctx, int fmt, const uint8_t *d_raw, const uint8_t *d_scales, int64_t n, int64_t k,
+                       uint8_t *d) {
+    int sb = 0;
+    const size_t bytes = tiled_bytes_for(fmt, n, k, &sb);
+    if (bytes == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "no tiled layout for format %d with K = %lld", fmt, (long long)k);
+    const int ktiles = (int)(k / (32 * sb));
+    nnq_status s = NNQ_OK;
+    if (n % 16) s = check_cuda(ctx, cudaMemset(d, 0, bytes), "cudaMemset tiled weight");
+    if (s != NNQ_OK) return s;
+    const int64_t total = fmt == NNQ_MXFP4_CORE || fmt == NNQ_MXFP4_SPLIT ? n * (k / 32) : n * ktiles * 8;
+    const int grid = (int)((total + 255) / 256);
+    const int split = fmt == NNQ_MXFP4_SPLIT;
+    switch (fmt) {
+        case NNQ_Q4_K: repack_q4k_kernel<false><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+        case NNQ_Q4_K_GGML: repack_q4k_kernel<true><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+        case NNQ_Q8_0: repack_q8_0_kernel<<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+        case NNQ_Q6_K: repack_q6_k_kernel<<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+        default:
+            if (sb == 8) repack_mxfp4_kernel<8><<<grid, 256>>>(d_raw, d_scales, d, (int)n, ktiles, split);
+            else repack_mxfp4_kernel<6><<<grid, 256>>>(d_raw, d_scales, d, (int)n, ktiles, split);
+            break;
+    }
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "repack launch");
+}
+
 nnq_status build_tiled_buffer(nnq_ctx *ctx, int fmt, const uint8_t *d_raw, const uint8_t *d_scales, int64_t n,
                               int64_t k, uint8_t **out, size_t *out_bytes, int *out_sb) {
     *out = nullptr;
     *out_bytes = 0;
     *out_sb = 0;
-    const int sb = tile_sb_of(fmt, k);
-    if (sb == 0 || n == 0 || k == 0) return NNQ_OK;
-    if (n > (1 << 24) || k > (1 << 24)) return NNQ_OK;
-    const int tb = tile_bytes_of(fmt, sb);
-    const int ktiles = (int)(k / (32 * sb));
-    const int64_t row_tiles = (n + 15) / 16;
-    const size_t bytes = (size_t)row_tiles * ktiles * tb;
+    int sb = 0;
+    const size_t bytes = tiled_bytes_for(fmt, n, k, &sb);
+    if (bytes == 0) return NNQ_OK;
     uint8_t *d = nullptr;
     nnq_status s = check_cuda(ctx, cudaMalloc(&d, bytes), "cudaMalloc tiled weight");
     if (s != NNQ_OK) return s;
-    if (n % 16) s = check_cuda(ctx, cudaMemset(d, 0, bytes), "cudaMemset tiled weight");
-    if (s == NNQ_OK) {
-        const int64_t total = fmt == NNQ_MXFP4_CORE || fmt == NNQ_MXFP4_SPLIT ? n * (k / 32) : n * ktiles * 8;
-        const int grid = (int)((total + 255) / 256);
-        const int split = fmt == NNQ_MXFP4_SPLIT;
-        switch (fmt) {
-            case NNQ_Q4_K: repack_q4k_kernel<false><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
-            case NNQ_Q4_K_GGML: repack_q4k_kernel<true><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
-            case NNQ_Q8_0: repack_q8_0_kernel<<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
-            case NNQ_Q6_K: repack_q6_k_kernel<<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
-            default:
-                if (sb == 8) repack_mxfp4_kernel<8><<<grid, 256>>>(d_raw, d_scales, d, (int)n, ktiles, split);
-                else repack_mxfp4_kernel<6><<<grid, 256>>>(d_raw, d_scales, d, (int)n, ktiles, split);
-                break;
-        }
-        ctx->launches++;
-        s = check_cuda(ctx, cudaGetLastError(), "repack launch");
-        if (s == NNQ_OK) s = check_cuda(ctx, cudaDeviceSynchronize(), "repack");
-    }
+    s = repack_into(ctx, fmt, d_raw, d_scales, n, k, d);
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaDeviceSynchronize(), "repack");
     if (s != NNQ_OK) {
         cudaFree(d);
         return s;
@@ -1500,6 +1715,68 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     cudaError_t e = f32x ? launch_ks<true>(ksplit, P, grid, smem_bytes, stream) : launch_ks<false>(ksplit, P, grid, smem_bytes, stream);
     ctx->launches++;
     return check_cuda(ctx, e, "skinny launch");
+}
+
+template <int FMT, int SB, bool F32X>
+static cudaError_t launch_grouped_t(const GroupedParams &P, int grid, int smem_bytes, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_grouped_kernel<FMT, SB, F32X>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemMax - 1024);   // the kernel also has a small static table
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    skinny_grouped_kernel<FMT, SB, F32X><<<grid, kWarps * 32, smem_bytes, stream>>>(P);
+    return cudaGetLastError();
+}
+
+template <int FMT, int SB>
+static cudaError_t launch_grouped_x(const GroupedParams &P, bool f32x, int grid, int smem_bytes, cudaStream_t stream) {
+    return f32x ? launch_grouped_t<FMT, SB, true>(P, grid, smem_bytes, stream)
+                : launch_grouped_t<FMT, SB, false>(P, grid, smem_bytes, stream);
+}
+
+nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t stream) {
+    if (a.experts < 1 || a.experts > kMoeMaxExperts) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad expert count %d", a.experts);
+    int sb = 0;
+    if (tiled_bytes_for(a.fmt, a.n, a.k, &sb) == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "no tiled layout for the grouped product");
+    GroupedParams P;
+    memset(&P, 0, sizeof(P));
+    P.tiled = a.tiled;
+    P.expert_stride = a.expert_stride;
+    P.bias = a.bias;
+    P.x = a.x;
+    P.rowtok = a.rowtok;
+    P.offset = a.offset;
+    P.out = a.out;
+    P.experts = a.experts;
+    P.top_k = a.top_k;
+    P.n = (int)a.n;
+    P.row_tiles = (int)((a.n + 15) / 16);
+    P.kblocks = (int)(a.k / (32 * sb));
+    P.stages = 2;
+    P.status = ctx->d_status;
+    const int smem_bytes = mn_plan(tile_bytes_of(a.fmt, sb), P.stages, 1).total;
+    // every expert may end with a partly filled row group
+    const int64_t max_units = (a.max_rows / kGroupRows + a.experts) * P.row_tiles;
+    int64_t grid = 2 * (int64_t)ctx->sm_count;
+    if (grid > max_units) grid = max_units;
+    if (grid < 1) grid = 1;
+    const bool f32x = a.x_dt == NNQ_F32;
+    cudaError_t e;
+    switch (layout_of(a.fmt)) {
+        case kTiledQ4K: e = launch_grouped_x<NNQ_Q4_K, 8>(P, f32x, (int)grid, smem_bytes, stream); break;
+        case kTiledQ8_0: e = launch_grouped_x<NNQ_Q8_0, 8>(P, f32x, (int)grid, smem_bytes, stream); break;
+        case kTiledQ6K: e = launch_grouped_x<NNQ_Q6_K, 8>(P, f32x, (int)grid, smem_bytes, stream); break;
+        default:
+            e = sb == 8 ? launch_grouped_x<NNQ_MXFP4_SPLIT, 8>(P, f32x, (int)grid, smem_bytes, stream)
+                        : launch_grouped_x<NNQ_MXFP4_SPLIT, 6>(P, f32x, (int)grid, smem_bytes, stream);
+            break;
+    }
+    ctx->launches++;
+    return check_cuda(ctx, e, "grouped product launch");
 }
 
 nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int64_t m, int y_dt,

@@ -22,6 +22,30 @@ nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w);
 // 32 weights per tile row.
 nnq_status build_tiled_buffer(nnq_ctx *ctx, int fmt, const uint8_t *d_raw, const uint8_t *d_scales, int64_t n,
                               int64_t k, uint8_t **out, size_t *out_bytes, int *sb);
+// Size of the tiled copy of raw blocks [n, k] (0 when the format / K has no tiled layout) and the
+// repack into a buffer of that size (asynchronous on the default stream).
+size_t tiled_bytes_for(int fmt, int64_t n, int64_t k, int *sb);
+nnq_status repack_into(nnq_ctx *ctx, int fmt, const uint8_t *d_raw, const uint8_t *d_scales, int64_t n, int64_t k,
+                       uint8_t *dst);
+
+// Expert products of a mixture-of-experts block over tiled expert weights: routed rows sorted by
+// expert (offset[e] .. offset[e+1]), out[r, :] = x[row source of r, :] * W_e^T + bias_e.
+struct GroupedArgs {
+    const uint8_t *tiled;     // expert e at tiled + e * expert_stride
+    size_t expert_stride;
+    const float *bias;        // [experts][n] or NULL
+    const void *x;
+    int x_dt;
+    const int *rowtok;        // routed row -> flat assignment index (token = index / top_k); NULL: the row itself
+    const int *offset;        // device, [experts + 1]
+    float *out;               // [rows][n] f32
+    int experts, top_k;
+    int64_t n, k;
+    int fmt;
+    int64_t max_rows;         // upper bound of offset[experts]
+};
+nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t stream);
+
 // True when launch_skinny can run this weight with M rows of activations.
 bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt);
 // One launch computing y_i = x_i * W_i^T (+ bias_i) for all jobs (same format, same M).

@@ -59,12 +59,14 @@ def test_moe_forward_matches_oracle(layout, fmt, T):
     blk.release()
 
 
-def test_gptoss_shape_decode_batch():
-    # gpt-oss-20b expert geometry (hidden = inter = 2880, not a multiple of 128), fewer experts
-    E, H, I, k, T = 4, 2880, 2880, 2, 5
-    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS, E, H, I, 9)
+@pytest.mark.parametrize("layout,fmt,T", [(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS, 5), (moe.LAYOUT_NK, Q.MXFP4_SPLIT, 5),
+                                          (moe.LAYOUT_NK, Q.MXFP4_SPLIT, 23)])
+def test_gptoss_shape_decode_batch(layout, fmt, T):
+    # gpt-oss-20b expert geometry (hidden = inter = 2880, not a multiple of 128 or 256), fewer experts
+    E, H, I, k = 4, 2880, 2880, 2
+    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(layout, fmt, E, H, I, 9)
     x = F.gen_activations(3, T, H, bf16=True)
-    blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS, gu, gus, bgu, dn, dns, bd)
+    blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, layout, fmt, gu, gus, bgu, dn, dns, bd)
     y = blk(torch.from_numpy(x).to(DEV)).cpu().numpy()
     y_ref, _, _ = orc.moe_forward(x, rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
     assert np.max(np.abs(y - y_ref)) / np.max(np.abs(y_ref)) <= 2e-3
