@@ -1144,15 +1144,13 @@ struct GroupedParams {
     int *status;
 };
 
-constexpr int kGroupRows = 8;
-
-template <int FMT, int SB, bool F32X>
+template <int FMT, int SB, int NT, bool F32X>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
     using TF = TileFmt<FMT, SB>;
     constexpr int TB = TF::kBytes;
     constexpr int TE = TF::kElems;
-    constexpr int NT = 1;
+    constexpr int kGroupRows = 8 * NT;   // routed rows per unit
     extern __shared__ __align__(128) uint8_t smem[];
     const MnPlan L = mn_plan(TB, P.stages, NT);
     __shared__ int goff[kMoeMaxExperts + 1];   // first row group of each expert
@@ -1252,21 +1250,24 @@ skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
         }
         int e, r0, cnt, rt;
         locate(unit, e, r0, cnt, rt);
-        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-        for (int w = 0; w < kWarps; w++) {
-            const float4 a = part4[(b * kWarps + w) * 32 + lane];
-            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-        }
-        const int row = rt * 16 + g, tok = 2 * t;
-        const float vals[4] = {v.x, v.y, v.z, v.w};
+        for (int nt = 0; nt < NT; nt++) {
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int tk = tok + (i & 1), rw = row + (i >> 1) * 8;
-            if (tk < cnt && rw < P.n) {
-                float o = vals[i];
-                if (P.bias) o += __ldg(P.bias + (size_t)e * P.n + rw);
-                P.out[(size_t)(r0 + tk) * P.n + rw] = o;
+            for (int w = 0; w < kWarps; w++) {
+                const float4 a = part4[((b * kWarps + w) * NT + nt) * 32 + lane];
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
+            const int row = rt * 16 + g, tok = nt * 8 + 2 * t;
+            const float vals[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int tk = tok + (i & 1), rw = row + (i >> 1) * 8;
+                if (tk < cnt && rw < P.n) {
+                    float o = vals[i];
+                    if (P.bias) o += __ldg(P.bias + (size_t)e * P.n + rw);
+                    P.out[(size_t)(r0 + tk) * P.n + rw] = o;
+                }
             }
         }
         __syncwarp();
@@ -1277,11 +1278,18 @@ skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
     for (int unit = 0; unit < n_units && !failed; unit++) {
         int e, r0, cnt, rt;
         locate(unit, e, r0, cnt, rt);
-        // this lane's column: routed row r0 + g (a column beyond the group reads row r0 and is never stored)
-        const int r = r0 + (g < cnt ? g : 0);
-        const int src = P.rowtok ? __ldg(P.rowtok + r) / P.top_k : r;
-        const uint8_t *xrow[NT] = {reinterpret_cast<const uint8_t *>(P.x) + (size_t)src * xstride};
-        float y[NT][4] = {{0.0f, 0.0f, 0.0f, 0.0f}};
+        // this lane's column(s): routed row r0 + g (+ 8); a column beyond the group reads row r0 and is never stored
+        const uint8_t *xrow[NT];
+        float y[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const int col = nt * 8 + g;
+            const int r = r0 + (col < cnt ? col : 0);
+            const int src = P.rowtok ? __ldg(P.rowtok + r) / P.top_k : r;
+            xrow[nt] = reinterpret_cast<const uint8_t *>(P.x) + (size_t)src * xstride;
+#pragma unroll
+            for (int i = 0; i < 4; i++) y[nt][i] = 0.0f;
+        }
         bool ok = true;
 #pragma unroll 1
         for (int k = 0; k < nkb; k++) {
@@ -1304,7 +1312,9 @@ skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
             failed = true;
             break;
         }
-        part4[(b * kWarps + warp) * 32 + lane] = make_float4(y[0][0], y[0][1], y[0][2], y[0][3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+            part4[((b * kWarps + warp) * NT + nt) * 32 + lane] = make_float4(y[nt][0], y[nt][1], y[nt][2], y[nt][3]);
         __syncwarp();
         if (lane == 0) mbar_arrive(full_s + 8 * b);
         if (unit >= 1 && warp == (unit - 1) % kWarps) finish(unit - 1);
@@ -1717,25 +1727,26 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     return check_cuda(ctx, e, "skinny launch");
 }
 
-template <int FMT, int SB, bool F32X>
+template <int FMT, int SB, int NT, bool F32X>
 static cudaError_t launch_grouped_t(const GroupedParams &P, int grid, int smem_bytes, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_grouped_kernel<FMT, SB, F32X>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(skinny_grouped_kernel<FMT, SB, NT, F32X>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemMax - 1024);   // the kernel also has a small static table
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    skinny_grouped_kernel<FMT, SB, F32X><<<grid, kWarps * 32, smem_bytes, stream>>>(P);
+    skinny_grouped_kernel<FMT, SB, NT, F32X><<<grid, kWarps * 32, smem_bytes, stream>>>(P);
     return cudaGetLastError();
 }
 
 template <int FMT, int SB>
-static cudaError_t launch_grouped_x(const GroupedParams &P, bool f32x, int grid, int smem_bytes, cudaStream_t stream) {
-    return f32x ? launch_grouped_t<FMT, SB, true>(P, grid, smem_bytes, stream)
-                : launch_grouped_t<FMT, SB, false>(P, grid, smem_bytes, stream);
+static cudaError_t launch_grouped_x(const GroupedParams &P, bool f32x, int nt, int grid, int smem_bytes, cudaStream_t stream) {
+    if (f32x) return launch_grouped_t<FMT, SB, 1, true>(P, grid, smem_bytes, stream);   // two MMAs per product: 8 rows
+    return nt == 2 ? launch_grouped_t<FMT, SB, 2, false>(P, grid, smem_bytes, stream)
+                   : launch_grouped_t<FMT, SB, 1, false>(P, grid, smem_bytes, stream);
 }
 
 nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t stream) {
@@ -1758,21 +1769,23 @@ nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t strea
     P.kblocks = (int)(a.k / (32 * sb));
     P.stages = 2;
     P.status = ctx->d_status;
-    const int smem_bytes = mn_plan(tile_bytes_of(a.fmt, sb), P.stages, 1).total;
+    const bool f32x = a.x_dt == NNQ_F32;
+    // 16-row groups once the experts see 5 or more rows on average (bf16 activations only)
+    const int nt = !f32x && a.max_rows >= 5 * (int64_t)a.experts ? 2 : 1;
+    const int smem_bytes = mn_plan(tile_bytes_of(a.fmt, sb), P.stages, nt).total;
     // every expert may end with a partly filled row group
-    const int64_t max_units = (a.max_rows / kGroupRows + a.experts) * P.row_tiles;
+    const int64_t max_units = (a.max_rows / (8 * nt) + a.experts) * P.row_tiles;
     int64_t grid = 2 * (int64_t)ctx->sm_count;
     if (grid > max_units) grid = max_units;
     if (grid < 1) grid = 1;
-    const bool f32x = a.x_dt == NNQ_F32;
     cudaError_t e;
     switch (layout_of(a.fmt)) {
-        case kTiledQ4K: e = launch_grouped_x<NNQ_Q4_K, 8>(P, f32x, (int)grid, smem_bytes, stream); break;
-        case kTiledQ8_0: e = launch_grouped_x<NNQ_Q8_0, 8>(P, f32x, (int)grid, smem_bytes, stream); break;
-        case kTiledQ6K: e = launch_grouped_x<NNQ_Q6_K, 8>(P, f32x, (int)grid, smem_bytes, stream); break;
+        case kTiledQ4K: e = launch_grouped_x<NNQ_Q4_K, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
+        case kTiledQ8_0: e = launch_grouped_x<NNQ_Q8_0, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
+        case kTiledQ6K: e = launch_grouped_x<NNQ_Q6_K, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
         default:
-            e = sb == 8 ? launch_grouped_x<NNQ_MXFP4_SPLIT, 8>(P, f32x, (int)grid, smem_bytes, stream)
-                        : launch_grouped_x<NNQ_MXFP4_SPLIT, 6>(P, f32x, (int)grid, smem_bytes, stream);
+            e = sb == 8 ? launch_grouped_x<NNQ_MXFP4_SPLIT, 8>(P, f32x, nt, (int)grid, smem_bytes, stream)
+                        : launch_grouped_x<NNQ_MXFP4_SPLIT, 6>(P, f32x, nt, (int)grid, smem_bytes, stream);
             break;
     }
     ctx->launches++;

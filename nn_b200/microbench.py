@@ -1,0 +1,156 @@
+"""Device-timed runs of single products of the library (weights drawn on the device).
+
+  python -m nn_b200.microbench linear --fmt q4_k --n 12288 --k 4096 --m 16 [--x f32] [--path tensor]
+  python -m nn_b200.microbench moe --layout nk --tokens 64
+
+`linear` rotates `--copies` distinct weights so that every call streams its weight from HBM
+(more bytes in rotation than L2 holds unless --copies says otherwise); `moe` times one
+mixture-of-experts block of the gpt-oss expert geometry. CUDA events around `--reps` calls
+after 3 warm-up calls; one line per run.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+
+
+def _formats():
+    from .formats import QuantFormat as Q
+    return {"q8_0": Q.Q8_0, "q4_k": Q.Q4_K, "q6_k": Q.Q6_K, "mxfp4": Q.MXFP4_SPLIT, "q4_0": Q.Q4_0, "q4_1": Q.Q4_1}
+
+
+def _draw(torch, gen, fmt, n, k):
+    """Raw blocks with uniform code bytes and small finite scales; (data, scales or None)."""
+    from . import workload as W
+    from .formats import QuantFormat as Q
+    dev = gen.device
+    if fmt == Q.Q4_K:
+        return W.gen_q4_k_device(torch, gen, n, k), None
+    if fmt == Q.Q8_0:
+        return W.gen_q8_0_device(torch, gen, n, k), None
+    if fmt == Q.Q6_K:
+        return W.gen_q6_k_device(torch, gen, n, k), None
+    if fmt == Q.MXFP4_SPLIT:
+        data = torch.randint(0, 256, (n * k // 2,), dtype=torch.uint8, device=dev, generator=gen)
+        scales = torch.randint(119, 128, (n * k // 32,), dtype=torch.uint8, device=dev, generator=gen)
+        return data, scales
+    nb, bs = n * k // 32, (18 if fmt == Q.Q4_0 else 20)
+    out = torch.randint(0, 256, (nb, bs), dtype=torch.uint8, device=dev, generator=gen)
+    out[:, 1] = 0x20   # high byte of the fp16 scale: a small finite value
+    if fmt == Q.Q4_1:
+        out[:, 3] = 0x20
+    return out.reshape(-1), None
+
+
+def _timed(torch, fn, reps):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e-3
+
+
+def run_linear(a):
+    import torch
+
+    from . import api
+    from .formats import algorithmic_bytes
+    fmt = _formats()[a.fmt]
+    b = api.gpu_backend()
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1)
+    ws = []
+    for _ in range(a.copies):
+        data, scales = _draw(torch, gen, fmt, a.n, a.k)
+        ws.append(api.DeviceWeight.from_device(b, fmt, data, a.n, a.k, scales=scales))
+        del data, scales
+    x = torch.randn(a.m, a.k, device=dev, generator=gen)
+    xdt = api.F32
+    if a.x == "bf16":
+        x, xdt = x.to(torch.bfloat16), api.BF16
+    y = torch.empty(a.m, a.n, dtype=torch.float32, device=dev)
+    b.set_path({"auto": api.PATH_AUTO, "generic": api.PATH_GENERIC, "skinny": api.PATH_SKINNY, "tensor": api.PATH_TENSOR}[a.path])
+    i = [0]
+
+    def one():
+        b.check(b._lib.nnq_linear(b._ctx, ws[i[0] % a.copies].handle(), x.data_ptr(), xdt, a.m, None, y.data_ptr(), api.F32, None))
+        i[0] += 1
+
+    sec = _timed(torch, one, a.reps)
+    b.set_path(api.PATH_AUTO)
+    b.device_status()
+    algo = algorithmic_bytes(fmt, a.m, a.n, a.k, 4 if a.x == "f32" else 2, 4)
+    print(f"linear {a.fmt} N={a.n} K={a.k} M={a.m} x={a.x} path={a.path}: {sec * 1e6:.1f} us, "
+          f"{algo / sec / 1e9:.0f} GB/s algorithmic, {2.0 * a.m * a.n * a.k / sec / 1e12:.1f} TFLOP/s", flush=True)
+    for w in ws:
+        w.release()
+
+
+def run_moe(a):
+    import torch
+
+    from . import api
+    b = api.gpu_backend()
+    lib, ctx = b._lib, b._ctx
+    dev = torch.device("cuda", 0)
+    E, H, I, k = a.experts, a.hidden, a.inter, a.top_k
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+
+    def u8(n, lo=0, hi=256):
+        return torch.randint(lo, hi, (n,), dtype=torch.uint8, device=dev, generator=gen)
+
+    rw = (torch.randn(E, H, device=dev, generator=gen) * 0.5).float()
+    rb = torch.zeros(E, device=dev)
+    gu, gus = u8(E * H * 2 * I // 2), u8(E * H * 2 * I // 32, 119, 128)
+    dn, dns = u8(E * I * H // 2), u8(E * I * H // 32, 119, 128)
+    bgu, bd = torch.zeros(E, 2 * I, device=dev), torch.zeros(E, H, device=dev)
+    layout, fmt = (0, 8) if a.layout == "kn" else (1, 7)   # [E,K,N] nn-gptoss | per-expert [N,K] split MXFP4
+    h = ctypes.c_void_p()
+    b.check(lib.nnq_moe_create(ctx, E, H, I, k, ctypes.c_float(7.0), rw.data_ptr(), rb.data_ptr(), layout, fmt,
+                               gu.data_ptr(), gu.numel(), gus.data_ptr(), gus.numel(), bgu.data_ptr(),
+                               dn.data_ptr(), dn.numel(), dns.data_ptr(), dns.numel(), bd.data_ptr(), ctypes.byref(h)))
+    T = a.tokens
+    x = torch.randn(T, H, device=dev, generator=gen).to(torch.bfloat16)
+    y = torch.empty(T, H, device=dev)
+    sec = _timed(torch, lambda: b.check(lib.nnq_moe_forward(ctx, h, x.data_ptr(), api.BF16, T, y.data_ptr(), None)), a.reps)
+    b.device_status()
+    wbytes = gu.numel() + gus.numel() + dn.numel() + dns.numel()
+    touched = wbytes * min(1.0, T * k / E)
+    print(f"moe layout={a.layout} E={E} hidden={H} inter={I} top{k} tokens={T}: {sec * 1e6:.0f} us, "
+          f"about {touched / 1e6:.0f} MB of expert weights touched -> {touched / sec / 1e9:.0f} GB/s", flush=True)
+    lib.nnq_moe_destroy(h)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("linear")
+    p.add_argument("--fmt", default="q4_k", choices=sorted(_formats()))
+    p.add_argument("--n", type=int, default=4096)
+    p.add_argument("--k", type=int, default=4096)
+    p.add_argument("--m", type=int, default=1)
+    p.add_argument("--x", default="bf16", choices=["bf16", "f32"])
+    p.add_argument("--path", default="auto", choices=["auto", "generic", "skinny", "tensor"])
+    p.add_argument("--copies", type=int, default=8)
+    p.add_argument("--reps", type=int, default=40)
+    p = sub.add_parser("moe")
+    p.add_argument("--layout", default="nk", choices=["nk", "kn"])
+    p.add_argument("--tokens", type=int, default=64)
+    p.add_argument("--experts", type=int, default=32)
+    p.add_argument("--hidden", type=int, default=2880)
+    p.add_argument("--inter", type=int, default=2880)
+    p.add_argument("--top-k", type=int, default=4)
+    p.add_argument("--reps", type=int, default=10)
+    a = ap.parse_args()
+    (run_linear if a.cmd == "linear" else run_moe)(a)
+
+
+if __name__ == "__main__":
+    main()
