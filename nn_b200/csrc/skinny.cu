@@ -689,7 +689,12 @@ __device__ __forceinline__ void mma_x(float (&d)[4], uint32_t a0, uint32_t a1, u
 
 struct MnConsts {
     uint32_t m4, m2, k128, k2048, ones;
+    uint32_t tl0, tl1, th0, th1;   // E2M1 magnitude -> bf16 low / high byte tables
     __device__ __forceinline__ void init() {
+        asm volatile("mov.b32 %0, 0xC0800000;" : "=r"(tl0));
+        asm volatile("mov.b32 %0, 0xC0804000;" : "=r"(tl1));
+        asm volatile("mov.b32 %0, 0x3F3F3F00;" : "=r"(th0));
+        asm volatile("mov.b32 %0, 0x40404040;" : "=r"(th1));
         asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(m4));
         asm volatile("mov.b32 %0, 0x00030003;" : "=r"(m2));
         asm volatile("mov.b32 %0, 0x43004300;" : "=r"(k128));
@@ -875,18 +880,20 @@ template <int SB>
 struct TileFmt<NNQ_MXFP4_SPLIT, SB> {
     static constexpr int kBytes = 128 + 256 * SB;
     static constexpr int kElems = 32 * SB;
-    static __device__ __forceinline__ void pairs(uint32_t w, uint32_t (&a)[4]) {
+    static __device__ __forceinline__ void pairs(uint32_t w, const MnConsts &K, uint32_t (&a)[4]) {
         const uint32_t sel = w & 0x77777777u;
-        const uint32_t lo_e = __byte_perm(0xC0800000u, 0xC0804000u, sel), hi_e = __byte_perm(0x3F3F3F00u, 0x40404040u, sel);
-        const uint32_t lo_o = __byte_perm(0xC0800000u, 0xC0804000u, sel >> 16), hi_o = __byte_perm(0x3F3F3F00u, 0x40404040u, sel >> 16);
+        const uint32_t lo_e = __byte_perm(K.tl0, K.tl1, sel), hi_e = __byte_perm(K.th0, K.th1, sel);
+        const uint32_t lo_o = __byte_perm(K.tl0, K.tl1, sel >> 16), hi_o = __byte_perm(K.th0, K.th1, sel >> 16);
         a[0] = __byte_perm(lo_e, hi_e, 0x5140) | ((w << 12) & 0x80008000u);
         a[1] = __byte_perm(lo_e, hi_e, 0x7362) | ((w << 8) & 0x80008000u);
         a[2] = __byte_perm(lo_o, hi_o, 0x5140) | ((w << 4) & 0x80008000u);
         a[3] = __byte_perm(lo_o, hi_o, 0x7362) | (w & 0x80008000u);
     }
     static __device__ __forceinline__ float scale_of(uint2 s, int sb) {   // 2^(e-127); e = 0 -> 2^-127
-        const uint32_t e = ((sb < 4 ? s.x : s.y) >> (8 * (sb & 3))) & 0xFFu;
-        return __uint_as_float(e ? e << 23 : 0x00400000u);
+        const uint32_t w = sb < 4 ? s.x : s.y;
+        const int i = sb & 3;
+        const uint32_t bits = (i < 3 ? w << (23 - 8 * i) : w >> 1) & 0x7F800000u;
+        return __uint_as_float(max(bits, 0x00400000u));
     }
     template <int NT, bool F32X>
     static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *, const uint8_t *const (&xrow)[NT],
@@ -899,8 +906,8 @@ struct TileFmt<NNQ_MXFP4_SPLIT, SB> {
         for (int sb = 0; sb < SB; sb++) {
             const uint2 q = cw[sb * 32 + lane];
             uint32_t A[4], A8[4];
-            pairs(q.x, A);
-            pairs(q.y, A8);
+            pairs(q.x, K, A);
+            pairs(q.y, K, A8);
             const float d = scale_of(sg, sb), d8 = scale_of(sg8, sb);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
@@ -915,7 +922,6 @@ struct TileFmt<NNQ_MXFP4_SPLIT, SB> {
                 y[nt][3] = fmaf(d8, c[3], y[nt][3]);
             }
         }
-        (void)K;
     }
 };
 
@@ -1195,17 +1201,18 @@ skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
     const int kb_lo = (warp * P.kblocks) / kWarps, kb_hi = ((warp + 1) * P.kblocks) / kWarps;
     const int nkb = kb_hi - kb_lo;
     const int n_units = cta < total_units ? (total_units - cta + grid - 1) / grid : 0;
-    // expert, first routed row, rows in the group and row tile of a unit
-    auto locate = [&](int unit, int &e, int &r0, int &cnt, int &rt) {
+    // expert, first routed row, rows in the group and row tile of a unit. A CTA's units come in
+    // increasing order, so the expert is found by advancing a cursor (one for the copy stream, which
+    // runs ahead, one for the arithmetic).
+    auto locate = [&](int unit, int &ecur, int &r0, int &cnt, int &rt) {
         const int u = cta + unit * grid;
         const int q = u / P.row_tiles;
         rt = u - q * P.row_tiles;
-        e = 0;
-        for (int i = 1; i < P.experts; i++)
-            if (q >= goff[i]) e = i;
-        r0 = P.offset[e] + (q - goff[e]) * kGroupRows;
-        cnt = min(kGroupRows, P.offset[e + 1] - r0);
+        while (ecur + 1 < P.experts && q >= goff[ecur + 1]) ecur++;
+        r0 = P.offset[ecur] + (q - goff[ecur]) * kGroupRows;
+        cnt = min(kGroupRows, P.offset[ecur + 1] - r0);
     };
+    int e_pf = 0, e_main = 0;
 
     int pf_unit = -1, pf_k = 0, pf_slot = 0;
     unsigned issued = 0;
@@ -1216,9 +1223,9 @@ skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
             pf_done = true;
             return;
         }
-        int e, r0, cnt, rt;
-        locate(pf_unit, e, r0, cnt, rt);
-        pf_src = P.tiled + (size_t)e * P.expert_stride + ((size_t)rt * P.kblocks + kb_lo) * TB;
+        int r0, cnt, rt;
+        locate(pf_unit, e_pf, r0, cnt, rt);
+        pf_src = P.tiled + (size_t)e_pf * P.expert_stride + ((size_t)rt * P.kblocks + kb_lo) * TB;
         pf_k = 0;
     };
     if (!pf_done) pf_advance_unit();
@@ -1242,14 +1249,12 @@ skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
     bool failed = false;
     const size_t xstride = (size_t)P.kblocks * TE * (F32X ? 4 : 2);
 
-    auto finish = [&](int unit) {
+    auto finish = [&](int unit, int e, int r0, int cnt, int rt) {
         const int b = unit & 1;
         if (!mbar_wait_fast(full_s + 8 * b, (unit >> 1) & 1u)) {
             failed = true;
             return;
         }
-        int e, r0, cnt, rt;
-        locate(unit, e, r0, cnt, rt);
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -1275,9 +1280,10 @@ skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
     };
 
 #pragma unroll 1
+    int pe = 0, pr0 = 0, pcnt = 0, prt = 0;   // the previous unit, for its deferred write-out
     for (int unit = 0; unit < n_units && !failed; unit++) {
-        int e, r0, cnt, rt;
-        locate(unit, e, r0, cnt, rt);
+        int r0, cnt, rt;
+        locate(unit, e_main, r0, cnt, rt);
         // this lane's column(s): routed row r0 + g (+ 8); a column beyond the group reads row r0 and is never stored
         const uint8_t *xrow[NT];
         float y[NT][4];
@@ -1317,9 +1323,10 @@ skinny_grouped_kernel(const __grid_constant__ GroupedParams P) {
             part4[((b * kWarps + warp) * NT + nt) * 32 + lane] = make_float4(y[nt][0], y[nt][1], y[nt][2], y[nt][3]);
         __syncwarp();
         if (lane == 0) mbar_arrive(full_s + 8 * b);
-        if (unit >= 1 && warp == (unit - 1) % kWarps) finish(unit - 1);
+        if (unit >= 1 && warp == (unit - 1) % kWarps) finish(unit - 1, pe, pr0, pcnt, prt);
+        pe = e_main; pr0 = r0; pcnt = cnt; prt = rt;
     }
-    if (!failed && n_units >= 1 && warp == (n_units - 1) % kWarps) finish(n_units - 1);
+    if (!failed && n_units >= 1 && warp == (n_units - 1) % kWarps) finish(n_units - 1, pe, pr0, pcnt, prt);
     if (failed) {
         if (lane == 0) atomicExch(P.status, 1);
         for (unsigned n = consumed; n < issued; n++) {
