@@ -180,7 +180,7 @@ def run_nnq(args, rank, world, local_rank):
     lib, ctx = backend._lib, backend._ctx
     m = args.m
     # row-parallel partial outputs are summed by the library's one-shot all-reduce over peer memory
-    peer = comm.PeerComm(backend, rank, world, max_bytes=max(m, 1) * W.HIDDEN * 4) if world > 1 else None
+    peer = comm.PeerComm(backend, rank, world, max_bytes=max(m, 2) * W.HIDDEN * 4) if world > 1 else None
     gen = torch.Generator(device=dev)
     gen.manual_seed(0x5EED)  # same weights on every rank, each keeps its shard
 
@@ -226,10 +226,17 @@ def run_nnq(args, rank, world, local_rank):
 
     def step(stream_ptr):
         for cnt, wh, xp, yp, reduce_out in calls:
+            if reduce_out is not None and not args.no_fused:
+                # row-parallel projection (o_proj, down_proj): product and all-reduce in one call
+                # (one kernel at M = 1: partial sums are pushed to the peers as row tiles finish)
+                st = peer.linear_raw(wh[0], xp[0], api.BF16, m, None, yp[0], api.BF16, stream_ptr)
+                if st != 0:
+                    backend.check(st)
+                continue
             st = lib.nnq_linear_batch(ctx, cnt, wh, xp, api.BF16, m, None, yp, api.BF16, stream_ptr)
             if st != 0:
                 backend.check(st)
-            if reduce_out is not None:   # row-parallel partial sums (o_proj, down_proj)
+            if reduce_out is not None:   # separate all-reduce of the partial sums
                 st = peer.all_reduce_raw(reduce_out.data_ptr(), api.BF16, reduce_out.numel(), stream_ptr)
                 if st != 0:
                     backend.check(st)
@@ -274,7 +281,7 @@ def run_nnq(args, rank, world, local_rank):
     backend.device_status(stream)
     launched = backend.launch_count() - launches_before
     if graph is not None:
-        n_reduce = sum(1 for c_ in calls if c_[4] is not None)
+        n_reduce = 0 if (not args.no_fused and m == 1) else sum(1 for c_ in calls if c_[4] is not None)
         launched = (launches_per_step + n_reduce) * args.steps  # replays re-issue the captured kernels
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -466,6 +473,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-others", action="store_true")
+    ap.add_argument("--no-fused", action="store_true", help="N > 1: separate all-reduce kernel after the row-parallel products")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

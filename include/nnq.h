@@ -306,6 +306,15 @@ NNQ_API nnq_status nnq_comm_create(nnq_ctx *ctx, int rank, int world, size_t max
 NNQ_API nnq_status nnq_comm_get_handle(nnq_comm *c, void *handle64);
 NNQ_API nnq_status nnq_comm_open_peers(nnq_comm *c, const void *handles);
 NNQ_API nnq_status nnq_comm_all_reduce(nnq_comm *c, void *buf_dev, nnq_dtype dt, int64_t count, void *stream);
+/* Row-parallel product and its all-reduce in one call: y = sum over ranks of (x_r * W_r^T) + bias,
+ * the same y on every rank (pass the same bias everywhere; it is added once). For M = 1 on a tiled
+ * Q4_K shard (and max_bytes >= 8 * N) this is ONE kernel: the warp that finishes a row tile sends
+ * its partial sums to the peers as 8-byte (value, sequence number) stores over peer memory, waits
+ * (bounded) for theirs and writes the finished rows, so the exchange overlaps the rest of the
+ * product. Otherwise it is nnq_linear followed by nnq_comm_all_reduce. M * N * 4 must fit the
+ * communicator's max_bytes. No counterpart in the reference (single device). */
+NNQ_API nnq_status nnq_comm_linear(nnq_comm *c, const nnq_weight *w, const void *x_dev, nnq_dtype x_dt, int64_t m,
+                                   const float *bias_dev, void *y_dev, nnq_dtype y_dt, void *stream);
 NNQ_API void nnq_comm_destroy(nnq_comm *c);
 
 /* Number of kernels this library has launched on this context since creation. */

@@ -46,6 +46,7 @@ SIGNATURES = {
     "nnq_comm_get_handle": (c_int, [c_void_p, c_void_p]),
     "nnq_comm_open_peers": (c_int, [c_void_p, c_void_p]),
     "nnq_comm_all_reduce": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
+    "nnq_comm_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
     "nnq_comm_destroy": (None, [c_void_p]),
     "nnq_moe_create": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_void_p, c_int, c_int,
                                c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p,

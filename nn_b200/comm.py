@@ -35,6 +35,22 @@ class PeerComm:
     def all_reduce_raw(self, ptr: int, dtype_code: int, count: int, stream_ptr):
         return self.backend._lib.nnq_comm_all_reduce(self._handle, ptr, dtype_code, count, stream_ptr)
 
+    def linear_raw(self, weight_handle, x_ptr: int, x_dt: int, m: int, bias_ptr, y_ptr: int, y_dt: int, stream_ptr):
+        """Row-parallel product fused with its all-reduce (nnq_comm_linear); returns the status."""
+        return self.backend._lib.nnq_comm_linear(self._handle, weight_handle, x_ptr, x_dt, m, bias_ptr, y_ptr, y_dt,
+                                                 stream_ptr)
+
+    def linear(self, x, weight, bias=None, out_dtype=None, stream=None):
+        """y = sum over ranks of x_r @ W_r^T (+ bias once); x is this rank's [M, K/world] slice."""
+        import torch
+        m = x.shape[0] if x.dim() > 1 else 1
+        y = torch.empty((m, weight.shape[0]), dtype=out_dtype or torch.float32, device=x.device)
+        b = self.backend
+        b.check(self.linear_raw(weight.handle(), x.data_ptr(), api._dtype_code(x), m,
+                                bias.data_ptr() if bias is not None else None, y.data_ptr(), api._dtype_code(y),
+                                api._stream_ptr(stream)))
+        return y
+
     def release(self):
         if self._handle is not None:
             self.backend._lib.nnq_comm_destroy(self._handle)

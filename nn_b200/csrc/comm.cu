@@ -18,7 +18,9 @@
 
 #include <new>
 
+#include "comm.cuh"
 #include "nnq_internal.h"
+#include "skinny.h"
 
 struct nnq_comm {
     nnq_ctx *ctx;
@@ -31,15 +33,6 @@ struct nnq_comm {
 };
 
 namespace nnq {
-
-constexpr int kCommMaxWorld = 8;
-constexpr unsigned kCommSpins = 1u << 22;
-
-// buffer layout: [0, 64) epoch counter, [64, 128) flags (u32 per source rank), then
-// data[parity][source rank][slot_bytes]
-__host__ __device__ inline size_t comm_data_offset(int parity, int src, int world, size_t slot_bytes) {
-    return 256 + ((size_t)parity * world + src) * slot_bytes;
-}
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
@@ -217,6 +210,30 @@ nnq_status nnq_comm_all_reduce(nnq_comm *c, void *buf_dev, nnq_dtype dt, int64_t
     }
     ctx->launches++;
     return check_cuda(ctx, e, "all-reduce launch");
+}
+
+nnq_status nnq_comm_linear(nnq_comm *c, const nnq_weight *w, const void *x_dev, nnq_dtype x_dt, int64_t m,
+                           const float *bias_dev, void *y_dev, nnq_dtype y_dt, void *stream) {
+    if (!c || !w) return NNQ_ERR_INVALID_ARG;
+    nnq_ctx *ctx = c->ctx;
+    if (w->ctx != ctx) return fail(ctx, NNQ_ERR_INVALID_ARG, "weight belongs to another context");
+    for (int p = 0; p < c->world; p++)
+        if (!c->peer[p]) return fail(ctx, NNQ_ERR_INVALID_ARG, "peer %d has not been opened", p);
+    if (m >= 1 && (size_t)m * (size_t)w->n * 4 > c->slot_bytes)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "output of %lld x %lld exceeds the communicator's %zu-byte slots",
+                    (long long)m, (long long)w->n, c->slot_bytes);
+    const bool slots_fit_pairs = (size_t)w->n * 8 <= c->slot_bytes;   // (value, sequence number) per row
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    if (m == 1 && slots_fit_pairs && ctx->path == NNQ_PATH_AUTO && skinny_fused_supported(w, m, x_dt)) {
+        FusedReduce fr = {c->d_peer_table, c->slot_bytes, c->rank, c->world, 1};
+        SkinnyJob job = {w, x_dev, bias_dev, y_dev};
+        return launch_skinny_fused(ctx, job, x_dt, y_dt, fr, (cudaStream_t)stream);
+    }
+    // two steps: the product (bias on rank 0 only, so that the sum holds it once), then the exchange
+    s = nnq_linear(ctx, w, x_dev, x_dt, m, c->rank == 0 ? bias_dev : nullptr, y_dev, y_dt, stream);
+    if (s != NNQ_OK) return s;
+    return nnq_comm_all_reduce(c, y_dev, y_dt, m * w->n, stream);
 }
 
 void nnq_comm_destroy(nnq_comm *c) {

@@ -1,0 +1,28 @@
+// Layout of a communicator's peer-mapped buffer, shared by the all-reduce kernel and by the
+// product kernel that pushes its partial outputs straight into the peers' slots.
+//   [0, 64)     epoch: sequence number of the last completed exchange
+//   [64, 128)   flags: u32 per source rank, the sequence number that rank has published
+//   [128, 192)  arrival counter of the fused product kernel (CTAs that finished pushing)
+//   [256, ...)  data[parity][source rank][slot_bytes]
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+namespace nnq {
+
+constexpr int kCommMaxWorld = 8;
+constexpr unsigned kCommSpins = 1u << 22;   // bound of every flag wait
+
+__host__ __device__ inline size_t comm_data_offset(int parity, int src, int world, size_t slot_bytes) {
+    return 256 + ((size_t)parity * world + src) * slot_bytes;
+}
+
+// What the fused product kernel needs to know about the exchange (enabled = 0: plain product).
+struct FusedReduce {
+    uint8_t *const *peers;   // device table of every rank's buffer (peers[rank] = own)
+    size_t slot_bytes;
+    int rank, world;
+    int enabled;
+};
+
+}  // namespace nnq

@@ -64,6 +64,7 @@ struct SkinnyParams {
                         // bit 1 = do not wait for the previous kernel; 4 = plain streaming read
     int l2_prefetch;    // 1 = ask L2 for the warp's whole weight stream at kernel start
     int *status;
+    FusedReduce fr;     // row-parallel product + all-reduce in one kernel (M = 1 kernel, one job)
 };
 
 // ---------------------------------------------------------------------------------
@@ -369,7 +370,7 @@ __device__ __forceinline__ void issue_tile(uint32_t dst, const void *src, uint32
 // unit and on the (w % KS)-th part of K, streaming its tiles through a private ring of bulk
 // copies; with KS > 1 the partial sums of a row tile meet in shared memory and one of the KS
 // warps (in turn) writes the 16 outputs while the others already work on the next unit.
-template <bool F32X, int KS>
+template <bool F32X, int KS, bool FUSED = false>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     constexpr int RG = kWarps / KS;
@@ -475,6 +476,10 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     // one before touching activations
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (!(P.diag & 2)) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // fused all-reduce: the exchange this launch takes part in (the epoch word is written by the
+    // previous exchange, which the wait above has seen complete)
+    unsigned ar_seq = 0;
+    if (FUSED) ar_seq = *reinterpret_cast<volatile unsigned *>(P.fr.peers[P.fr.rank]) + 1u;
 
     if (KS == kWarps) {
         // the warp owns its part of K: no other warp reads what it stages
@@ -504,6 +509,41 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     auto store16 = [&](int j, int rt, float v) {   // lanes 0..15 hold the 16 outputs of a row tile
         const SkinnyJobDev &J = P.job[j];
         int row = rt * 16 + lane;
+        if (FUSED) {
+            // Exchange without fences: every partial sum travels as one 8-byte store (value, sequence
+            // number) into this rank's slot on each peer; the same lane then waits (bounded) for the
+            // peers' pairs of this row and adds them in rank order, so every rank gets the same bits.
+            if (lane < 16 && row < J.n) {
+                const int par = (int)(ar_seq & 1u);
+                const size_t mine = comm_data_offset(par, P.fr.rank, P.fr.world, P.fr.slot_bytes) + (size_t)row * 8;
+                for (int p = 0; p < P.fr.world; p++)
+                    if (p != P.fr.rank)
+                        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(P.fr.peers[p] + mine),
+                                     "r"(__float_as_uint(v)), "r"(ar_seq) : "memory");
+                const uint8_t *local = P.fr.peers[P.fr.rank];
+                float acc = 0.0f;
+                bool ok = true;
+                for (int r = 0; r < P.fr.world; r++) {
+                    if (r == P.fr.rank) {
+                        acc += v;
+                        continue;
+                    }
+                    const uint8_t *src = local + comm_data_offset(par, r, P.fr.world, P.fr.slot_bytes) + (size_t)row * 8;
+                    uint32_t bits = 0, tag = 0;
+                    unsigned spins = 0;
+                    do {
+                        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(tag) : "l"(src) : "memory");
+                    } while (tag != ar_seq && ++spins <= kCommSpins);
+                    ok = ok && tag == ar_seq;
+                    acc += __uint_as_float(bits);
+                }
+                if (!ok) atomicExch(P.status, 1);
+                if (J.bias) acc += __ldg(J.bias + row);
+                if (P.y_dt == NNQ_F32) reinterpret_cast<float *>(J.y)[row] = acc;
+                else reinterpret_cast<__nv_bfloat16 *>(J.y)[row] = __float2bfloat16_rn(acc);
+            }
+            return;
+        }
         if (lane < 16 && row < J.n) {
             if (J.bias) v += __ldg(J.bias + row);
             if (P.y_dt == NNQ_F32) reinterpret_cast<float *>(J.y)[row] = v;
@@ -596,6 +636,18 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
             if (++slot == stages) {
                 slot = 0;
                 phase ^= 1u;
+            }
+        }
+    }
+    if (FUSED) {
+        // the last CTA of this launch to finish advances the communicator's sequence number
+        __syncthreads();
+        if (tid == 0) {
+            uint8_t *local = P.fr.peers[P.fr.rank];
+            unsigned *arrived = reinterpret_cast<unsigned *>(local + 128);
+            if (atomicAdd(arrived, 1u) == gridDim.x - 1) {
+                *arrived = 0;
+                *reinterpret_cast<volatile unsigned *>(local) = ar_seq;
             }
         }
     }
@@ -1575,13 +1627,13 @@ bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt) {
     return st > 0;
 }
 
-template <bool F32X, int KS>
+template <bool F32X, int KS, bool FUSED = false>
 static cudaError_t launch_kernel(const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_q4k_m1_kernel<F32X, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        cudaError_t e = cudaFuncSetAttribute(skinny_q4k_m1_kernel<F32X, KS, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax - 1024);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
@@ -1598,11 +1650,12 @@ static cudaError_t launch_kernel(const SkinnyParams &P, int grid, int smem_bytes
     cfg.attrs = attr;
     static const char *env_pdl = getenv("NNQ_SKINNY_PDL");  // tuning aid
     cfg.numAttrs = env_pdl && atoi(env_pdl) == 0 ? 0 : 1;
-    return cudaLaunchKernelEx(&cfg, skinny_q4k_m1_kernel<F32X, KS>, P);
+    return cudaLaunchKernelEx(&cfg, skinny_q4k_m1_kernel<F32X, KS, FUSED>, P);
 }
 
 template <bool F32X>
 static cudaError_t launch_ks(int ksplit, const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
+    if (P.fr.enabled) return launch_kernel<F32X, 8, true>(P, grid, smem_bytes, stream);   // ksplit is 8 (checked by the caller)
     switch (ksplit) {
         case 1: return launch_kernel<F32X, 1>(P, grid, smem_bytes, stream);
         case 2: return launch_kernel<F32X, 2>(P, grid, smem_bytes, stream);
@@ -1657,9 +1710,10 @@ __global__ void __launch_bounds__(256) stream_read_kernel(const SkinnyParams P, 
 
 // One launch: jobs that share their activations (same x pointer, same K).
 static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int m, int y_dt,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const FusedReduce *fr = nullptr) {
     SkinnyParams P;
     memset(&P, 0, sizeof(P));
+    if (fr) P.fr = *fr;
     P.njobs = count;
     P.m = m;
     P.y_dt = y_dt;
@@ -1678,6 +1732,7 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     const bool token_columns = m > 1 || layout != kTiledQ4K || (env_tc && atoi(env_tc) == 1 && !f32x);
     if (!token_columns) pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
     else P.stages = 2;
+    if (fr && ctas_per_sm > 2) ctas_per_sm = 2;   // register budget of the fused variant
     if (P.stages == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "K = %lld is too large for the skinny kernel", (long long)jobs[0].w->k);
     int tiles = 0;
     for (int i = 0; i < count; i++) {
@@ -1721,6 +1776,7 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     static const char *env_ks = getenv("NNQ_SKINNY_KS");  // tuning aid
     if (env_ks && atoi(env_ks) > 0) ksplit = atoi(env_ks);
     // persistent grid: every CTA resident
+    if (P.fr.enabled && ksplit != kWarps) return fail(ctx, NNQ_ERR_UNSUPPORTED, "fused product + all-reduce needs K >= 2048 per rank");
     const int rg = kWarps / ksplit;
     const int units = (tiles + rg - 1) / rg;
     int grid = units < slots ? units : slots;
@@ -1797,6 +1853,16 @@ nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t strea
     }
     ctx->launches++;
     return check_cuda(ctx, e, "grouped product launch");
+}
+
+bool skinny_fused_supported(const nnq_weight *w, int64_t m, int x_dt) {
+    return m == 1 && w && w->tiled_layout == kTiledQ4K && w->k >= 8 * 256 && skinny_supported(w, m, x_dt);
+}
+
+nnq_status launch_skinny_fused(nnq_ctx *ctx, const SkinnyJob &job, int x_dt, int y_dt, const FusedReduce &fr,
+                               cudaStream_t stream) {
+    if (!skinny_fused_supported(job.w, 1, x_dt)) return fail(ctx, NNQ_ERR_UNSUPPORTED, "fused product + all-reduce needs the M = 1 Q4_K kernel");
+    return launch_group(ctx, &job, 1, x_dt, 1, y_dt, stream, &fr);
 }
 
 nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int64_t m, int y_dt,

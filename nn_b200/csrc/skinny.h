@@ -1,5 +1,6 @@
 // Skinny (M <= 16) streaming kernels on the tiled weight layout.
 #pragma once
+#include "comm.cuh"
 #include "nnq_internal.h"
 
 namespace nnq {
@@ -51,5 +52,13 @@ bool skinny_supported(const nnq_weight *w, int64_t m, int x_dt);
 // One launch computing y_i = x_i * W_i^T (+ bias_i) for all jobs (same format, same M).
 nnq_status launch_skinny(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int64_t m, int y_dt,
                          cudaStream_t stream);
+
+// Row-parallel product fused with its all-reduce (M = 1 Q4_K kernel): the warp that finishes a row
+// tile sends its 16 f32 partial sums to every peer as 8-byte (value, sequence number) stores, waits
+// (bounded) for the peers' pairs of the same rows, adds them in rank order, adds the bias and
+// writes y. The communicator's slots must hold 8 bytes per output row.
+bool skinny_fused_supported(const nnq_weight *w, int64_t m, int x_dt);
+nnq_status launch_skinny_fused(nnq_ctx *ctx, const SkinnyJob &job, int x_dt, int y_dt, const FusedReduce &fr,
+                               cudaStream_t stream);
 
 }  // namespace nnq

@@ -29,6 +29,37 @@ def test_world_one_is_identity_and_sized():
     c.release()
 
 
+def test_fused_linear_world_one_matches_plain_product():
+    """The product kernel with the all-reduce tail, on one rank: partial sums go through the slot
+    and the last CTA writes the outputs; mixed with plain all-reduces on the same communicator."""
+    from nn_b200 import formats as F
+    from nn_b200.formats import QuantFormat as Q
+    b = api.gpu_backend()
+    n, k = 1000, 4096
+    c = comm.PeerComm(b, 0, 1, max_bytes=n * 8)
+    w, _ = F.gen_weight(Q.Q4_K, 77, n, k)
+    wt = api.from_quantized(w, Q.Q4_K, [n, k])
+    bias = torch.randn(n, device="cuda:0")
+    for it, dt in enumerate((torch.bfloat16, torch.float32, torch.bfloat16)):
+        x = torch.from_numpy(F.gen_activations(80 + it, 1, k, bf16=True)).to("cuda:0").to(dt)
+        want = api.quantized_linear(x, wt, bias, out_dtype=torch.float32)
+        got = c.linear(x, wt, bias, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        b.device_status()
+        assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+        c.all_reduce(torch.ones(16, device="cuda:0"))   # shares the sequence number with the fused call
+    # a shape the fused kernel does not cover falls back to product + all-reduce
+    x2 = torch.from_numpy(F.gen_activations(90, 3, k, bf16=True)).to("cuda:0").to(torch.bfloat16)
+    c2 = comm.PeerComm(b, 0, 1, max_bytes=3 * n * 4)
+    got = c2.linear(x2, wt, bias)
+    want = api.quantized_linear(x2, wt, bias, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+    c.release()
+    c2.release()
+    wt.release()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -58,6 +89,22 @@ def _worker(rank, world, port, out):
                 want += parts[r]
             torch.cuda.synchronize()
             ok = ok and torch.equal(x.cpu(), want)
+        b.device_status()
+        # row-parallel product fused with its all-reduce against the unsharded product
+        from nn_b200 import formats as F
+        from nn_b200.formats import QuantFormat as Q
+        n, k = 520, 8192
+        w, _ = F.gen_weight(Q.Q4_K, 5, n, k)
+        full = api.QuantizedTensor(w, Q.Q4_K, [n, k], None, b)
+        shard = full.shard(1, rank, world)
+        bias = torch.from_numpy((F.Stream(6).normal(n) * 0.5).astype(np.float32)).to(dev)
+        for it in range(6):
+            x = torch.from_numpy(F.gen_activations(200 + it, 1, k, bf16=True)).to(dev).to(torch.bfloat16)
+            ks = k // world
+            got = c.linear(x[:, rank * ks:(rank + 1) * ks].contiguous(), shard, bias)
+            want = api.quantized_linear(x, full, bias, out_dtype=torch.float32)
+            torch.cuda.synchronize()
+            ok = ok and float((got - want).abs().max()) <= 1e-4 * float(want.abs().max())
         b.device_status()
         if rank == 0:
             np.save(out, np.array([1 if ok else 0]))
