@@ -1653,15 +1653,20 @@ static cudaError_t launch_kernel(const SkinnyParams &P, int grid, int smem_bytes
     return cudaLaunchKernelEx(&cfg, skinny_q4k_m1_kernel<F32X, KS, FUSED>, P);
 }
 
+template <bool F32X, bool FUSED>
+static cudaError_t launch_ks_f(int ksplit, const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
+    switch (ksplit) {
+        case 1: return launch_kernel<F32X, 1, FUSED>(P, grid, smem_bytes, stream);
+        case 2: return launch_kernel<F32X, 2, FUSED>(P, grid, smem_bytes, stream);
+        case 4: return launch_kernel<F32X, 4, FUSED>(P, grid, smem_bytes, stream);
+        default: return launch_kernel<F32X, 8, FUSED>(P, grid, smem_bytes, stream);
+    }
+}
+
 template <bool F32X>
 static cudaError_t launch_ks(int ksplit, const SkinnyParams &P, int grid, int smem_bytes, cudaStream_t stream) {
-    if (P.fr.enabled) return launch_kernel<F32X, 8, true>(P, grid, smem_bytes, stream);   // ksplit is 8 (checked by the caller)
-    switch (ksplit) {
-        case 1: return launch_kernel<F32X, 1>(P, grid, smem_bytes, stream);
-        case 2: return launch_kernel<F32X, 2>(P, grid, smem_bytes, stream);
-        case 4: return launch_kernel<F32X, 4>(P, grid, smem_bytes, stream);
-        default: return launch_kernel<F32X, 8>(P, grid, smem_bytes, stream);
-    }
+    return P.fr.enabled ? launch_ks_f<F32X, true>(ksplit, P, grid, smem_bytes, stream)
+                        : launch_ks_f<F32X, false>(ksplit, P, grid, smem_bytes, stream);
 }
 
 template <int FMT, int SB, int NT, bool F32X>
@@ -1776,7 +1781,6 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     static const char *env_ks = getenv("NNQ_SKINNY_KS");  // tuning aid
     if (env_ks && atoi(env_ks) > 0) ksplit = atoi(env_ks);
     // persistent grid: every CTA resident
-    if (P.fr.enabled && ksplit != kWarps) return fail(ctx, NNQ_ERR_UNSUPPORTED, "fused product + all-reduce needs K >= 2048 per rank");
     const int rg = kWarps / ksplit;
     const int units = (tiles + rg - 1) / rg;
     int grid = units < slots ? units : slots;
@@ -1856,7 +1860,7 @@ nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t strea
 }
 
 bool skinny_fused_supported(const nnq_weight *w, int64_t m, int x_dt) {
-    return m == 1 && w && w->tiled_layout == kTiledQ4K && w->k >= 8 * 256 && skinny_supported(w, m, x_dt);
+    return m == 1 && w && w->tiled_layout == kTiledQ4K && skinny_supported(w, m, x_dt);
 }
 
 nnq_status launch_skinny_fused(nnq_ctx *ctx, const SkinnyJob &job, int x_dt, int y_dt, const FusedReduce &fr,

@@ -48,6 +48,17 @@ def test_fused_linear_world_one_matches_plain_product():
         b.device_status()
         assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
         c.all_reduce(torch.ones(16, device="cuda:0"))   # shares the sequence number with the fused call
+    # small K: fewer than 8 super-blocks, the warps of a CTA work on several row tiles
+    for kk in (256, 1024):
+        w3, _ = F.gen_weight(Q.Q4_K, 78, 200, kk)
+        wt3 = api.from_quantized(w3, Q.Q4_K, [200, kk])
+        x3 = torch.from_numpy(F.gen_activations(91, 1, kk, bf16=True)).to("cuda:0").to(torch.bfloat16)
+        got = c.linear(x3, wt3, None)
+        want = api.quantized_linear(x3, wt3, None, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        b.device_status()
+        assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+        wt3.release()
     # a shape the fused kernel does not cover falls back to product + all-reduce
     x2 = torch.from_numpy(F.gen_activations(90, 3, k, bf16=True)).to("cuda:0").to(torch.bfloat16)
     c2 = comm.PeerComm(b, 0, 1, max_bytes=3 * n * 4)
