@@ -455,9 +455,68 @@ def other_configs(torch, backend, layers, gen, dev):
         return {"us": sec * 1e6, "gbs": algo / sec / 1e9, "bound": "hbm", "frac": algo / sec / 1e9 / peak_hbm,
                 "weights_rotated": copies}
 
+    out["qwen3_8b_decode_ctx2048"] = decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm)
     out["q8_0_gemv_4096x4096_f32_m1"] = gemv(QuantFormat.Q8_0, W.gen_q8_0_device, 4096, 4096, 10, True, 40)
     out["q6_k_gemv_151936x4096_bf16_m1"] = gemv(QuantFormat.Q6_K, W.gen_q6_k_device, 151936, 4096, 1, False, 10)
     backend.device_status()
+    return out
+
+
+def decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, prompt=2048, new_tokens=256):
+    """Batch-1 greedy decode of a Qwen3-8B-shaped model (the bench's 36 Q4_K layers, a Q6_K
+    vocabulary projection, bf16 embedding, unit norms): 256 tokens from position 2048. The key /
+    value caches of the 2048 earlier positions are filled with seeded random values, which stands
+    in for the prompt pass: the cost of a decode step depends on the context length only."""
+    from nn_b200 import api, decoder
+    from nn_b200 import workload as W
+    from nn_b200.formats import QuantFormat
+    if len(layers) != W.LAYERS:
+        return None
+    cfg = decoder.DecoderConfig(max_seq=prompt + new_tokens + 8, act_dtype=api.BF16)
+    dec = decoder.Decoder(backend, cfg)
+    ones_h = torch.ones(cfg.hidden, device=dev)
+    ones_d = torch.ones(cfg.head_dim, device=dev)
+    for li, lw in enumerate(layers):
+        dec.set_layer(li, lw["q_proj"], lw["k_proj"], lw["v_proj"], lw["o_proj"], lw["gate_proj"], lw["up_proj"],
+                      lw["down_proj"], ones_h, ones_h, ones_d, ones_d)
+    raw = W.gen_q6_k_device(torch, gen, cfg.vocab, cfg.hidden)
+    head = api.DeviceWeight.from_device(backend, QuantFormat.Q6_K, raw, cfg.vocab, cfg.hidden)
+    del raw
+    embed = torch.randn(cfg.vocab, cfg.hidden, device=dev, generator=gen).to(torch.bfloat16)
+    dec.set_head(embed, ones_h, head)
+    kc, vc, _, toks = dec.buffers()
+    kc[:, :, :prompt].normal_(generator=gen)
+    vc[:, :, :prompt].normal_(generator=gen)
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        dec.reset(1, prompt, stream)
+        dec.step(stream)
+        stream.synchronize()
+        dec.reset(1, prompt, stream)
+        launches0 = backend.launch_count()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            dec.step(torch.cuda.current_stream())
+        per_token = backend.launch_count() - launches0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(new_tokens):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    backend.device_status(stream)
+    sec = e0.elapsed_time(e1) * 1e-3 / new_tokens
+    _, pos, steps = dec.state()
+    ctx_mid = prompt + new_tokens // 2
+    weights = W.layer_bytes(1).weights * W.LAYERS + cfg.vocab * (cfg.hidden // 256) * 210
+    kv = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 4 * ctx_mid
+    out = {"tokens_per_s": 1.0 / sec, "ms_per_token": sec * 1e3, "new_tokens": new_tokens, "prompt_positions": prompt,
+           "kernels_per_token": int(per_token), "end_position": pos, "steps": steps,
+           "hbm_bytes_per_token": weights + kv, "gbs": (weights + kv) / sec / 1e9, "bound": "hbm",
+           "frac": (weights + kv) / sec / 1e9 / peak_hbm, "kv_cache": "f32", "product_inputs": "bf16",
+           "prompt": "key/value caches of the first 2048 positions filled with seeded random values"}
+    dec.release()
+    head.release()
     return out
 
 

@@ -317,6 +317,47 @@ NNQ_API nnq_status nnq_comm_linear(nnq_comm *c, const nnq_weight *w, const void 
                                    const float *bias_dev, void *y_dev, nnq_dtype y_dt, void *stream);
 NNQ_API void nnq_comm_destroy(nnq_comm *c);
 
+/* ------------------------------------------------------------------------------------------
+ * One decode step of a Qwen3-shaped decoder around the quantized products (batch 1, greedy).
+ * Replaces, for the decode loop, Qwen3DecoderLayer::forward / Qwen3Attention::forward / Qwen3MLP::forward
+ * (crates/nn-qwen3/src/layers.rs:40-47,94-167,205-226), RmsNorm (crates/nn-core/src/layers/rms_norm.rs:87-100),
+ * RotaryEmbedding tables and the half-split rotation (layers/attention/rope.rs:78-106,
+ * rope_half_split.rs:98-134), sdpa (attention/sdpa.rs:59-71), KvCacheLayer::append
+ * (layers/generation/kv_cache.rs:132) and the greedy argmax of the generation loop
+ * (generation/autoregressive_sampling.rs:14-21: of equal maxima the last wins).
+ * The current token and position live on the device and are advanced by the step itself, so the
+ * launches of nnq_decoder_step may be captured in a CUDA graph once and replayed per token.
+ * head_dim must be 128; activations between the kernels are f32, the inputs of the products are
+ * converted to act_dtype (NNQ_F32 keeps the reference's arithmetic, NNQ_BF16 is faster).
+ * The weights, the embedding table ([vocab, hidden] bf16, device) and the vocabulary projection
+ * stay owned by the caller and must outlive the decoder. */
+typedef struct nnq_decoder nnq_decoder;
+typedef struct nnq_decoder_config {
+    int32_t hidden, n_heads, n_kv_heads, head_dim, ffn, n_layers, vocab, max_seq;
+    float rms_eps;
+    double rope_theta;
+    int32_t act_dtype;   /* nnq_dtype */
+} nnq_decoder_config;
+NNQ_API nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_decoder **out);
+/* norm weights: f32, host or device pointers (copied) */
+NNQ_API nnq_status nnq_decoder_set_layer(nnq_decoder *d, int layer, const nnq_weight *q, const nnq_weight *k,
+                                         const nnq_weight *v, const nnq_weight *o, const nnq_weight *gate,
+                                         const nnq_weight *up, const nnq_weight *down, const float *in_norm,
+                                         const float *post_norm, const float *q_norm, const float *k_norm);
+NNQ_API nnq_status nnq_decoder_set_head(nnq_decoder *d, const void *embed_bf16_dev, const float *final_norm,
+                                        const nnq_weight *lm_head);
+/* next input token and the position it is written at (synchronises the stream) */
+NNQ_API nnq_status nnq_decoder_reset(nnq_decoder *d, int token, int pos, void *stream);
+/* one token: consumes (token, pos), appends to the caches, leaves the logits in the logits buffer,
+ * stores the argmax as the next token and advances the position */
+NNQ_API nnq_status nnq_decoder_step(nnq_decoder *d, void *stream);
+/* reads (next token, next position, steps taken) back; synchronises the stream */
+NNQ_API nnq_status nnq_decoder_state(nnq_decoder *d, int *token, int *pos, int *steps, void *stream);
+/* device buffers: key / value caches [layers, kv_heads, max_seq, head_dim] f32, logits [vocab] f32,
+ * generated tokens [max_seq] (token produced at position p is stored at index p) */
+NNQ_API nnq_status nnq_decoder_buffers(nnq_decoder *d, float **k_cache, float **v_cache, float **logits, int **tokens);
+NNQ_API void nnq_decoder_destroy(nnq_decoder *d);
+
 /* Number of kernels this library has launched on this context since creation. */
 NNQ_API int64_t nnq_launch_count(const nnq_ctx *ctx);
 

@@ -48,6 +48,15 @@ SIGNATURES = {
     "nnq_comm_all_reduce": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
     "nnq_comm_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
     "nnq_comm_destroy": (None, [c_void_p]),
+    "nnq_decoder_create": (c_int, [c_void_p, c_void_p, ctypes.POINTER(c_void_p)]),
+    "nnq_decoder_set_layer": (c_int, [c_void_p, c_int] + [c_void_p] * 11),
+    "nnq_decoder_set_head": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nnq_decoder_reset": (c_int, [c_void_p, c_int, c_int, c_void_p]),
+    "nnq_decoder_step": (c_int, [c_void_p, c_void_p]),
+    "nnq_decoder_state": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_void_p]),
+    "nnq_decoder_buffers": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
+                                    ctypes.POINTER(c_void_p)]),
+    "nnq_decoder_destroy": (None, [c_void_p]),
     "nnq_moe_create": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_void_p, c_int, c_int,
                                c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p,
                                c_size_t, c_void_p, ctypes.POINTER(c_void_p)]),

@@ -1,0 +1,460 @@
+// One decode step (one token, batch 1) of a Qwen3-shaped decoder on the device: embedding row ->
+// N x [RMSNorm -> q/k/v products -> per-head QK-norm + half-split RoPE -> KV append -> grouped-query
+// attention over the cache -> o product -> residual -> RMSNorm -> gate/up products -> silu * up ->
+// down product -> residual] -> final RMSNorm -> vocabulary product -> greedy argmax.
+// Follows crates/nn-qwen3/src/layers.rs:40-47,94-167,205-226 (MLP, attention, decoder layer),
+// crates/nn-core/src/layers/rms_norm.rs:87-100, layers/attention/rope.rs:78-106 (tables),
+// rope_half_split.rs:98-134 (rotation), attention/sdpa.rs:59-71, dyn_tensor/ops/math.rs:140 (silu)
+// and layers/generation/autoregressive_sampling.rs:14-21 (argmax: the last of equal maxima).
+//
+// The quantized products are the library's own (nnq_linear / nnq_linear_batch); this file adds the
+// small kernels between them. Token and position live in device memory and are advanced by the
+// last kernel of a step, so the launches of one step can be captured once and replayed per token.
+#include <cuda_bf16.h>
+#include <math.h>
+#include <string.h>
+
+#include <new>
+
+#include "nnq_internal.h"
+
+struct nnq_decoder {
+    nnq_ctx *ctx;
+    nnq_decoder_config cfg;
+    struct Layer {
+        const nnq_weight *q, *k, *v, *o, *gate, *up, *down;
+        float *in_norm, *post_norm, *q_norm, *k_norm;   // device copies
+    } *layers;
+    const void *d_embed;        // [vocab, hidden] bf16, caller-owned
+    float *d_final_norm;
+    const nnq_weight *lm_head;
+    float *d_cos, *d_sin;       // [max_seq, head_dim / 2]
+    float *d_kcache, *d_vcache; // [layers, kv_heads, max_seq, head_dim]
+    float *d_h, *d_delta, *d_q, *d_k, *d_v, *d_qrot, *d_g, *d_u, *d_logits, *d_part;
+    void *d_xn, *d_attn, *d_mid;   // activations fed to the products (f32 or bf16)
+    int *d_state;               // [0] token, [1] position, [2] steps taken; then the argmax scratch
+    int *d_tokens;              // generated tokens, [max_seq]
+    int act_dt;
+    int ready;                  // bit set of what has been supplied
+};
+
+namespace nnq {
+
+constexpr int kAttnSplits = 16;
+constexpr int kArgmaxBlocks = 128;
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int w = 0; w < nw; w++) t += red[w];
+    return t;
+}
+
+__device__ __forceinline__ void store_act(void *dst, int dt, int i, float v) {
+    if (dt == NNQ_F32) reinterpret_cast<float *>(dst)[i] = v;
+    else reinterpret_cast<__nv_bfloat16 *>(dst)[i] = __float2bfloat16_rn(v);
+}
+
+// h = embedding row of the current token (first layer), or h += delta; xn = RMSNorm(h) * w
+__global__ void __launch_bounds__(1024)
+dec_norm_kernel(float *__restrict__ h, const float *__restrict__ delta, const __nv_bfloat16 *__restrict__ embed,
+                const int *__restrict__ state, const float *__restrict__ w, float eps, void *__restrict__ xn, int act_dt,
+                int hidden) {
+    __shared__ float red[32];
+    const int tok = embed ? state[0] : 0;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = embed ? __bfloat162float(embed[(size_t)tok * hidden + i]) : h[i] + delta[i];
+        h[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float mean = block_sum(ss, red) / (float)hidden;
+    const float rms = sqrtf(mean + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) store_act(xn, act_dt, i, (h[i] / rms) * w[i]);
+}
+
+// One CTA per head (query heads, then key heads, then value heads), one thread per dimension:
+// RMSNorm over the head (q, k), half-split rotation at the current position, append k / v.
+__global__ void __launch_bounds__(256)
+dec_qk_rope_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                   const float *__restrict__ qw, const float *__restrict__ kw, const float *__restrict__ cosv,
+                   const float *__restrict__ sinv, const int *__restrict__ state, float eps, float *__restrict__ qrot,
+                   float *__restrict__ kcache, float *__restrict__ vcache, int n_heads, int n_kv, int hd, int max_seq) {
+    __shared__ float red[32];
+    __shared__ float xs[256];
+    const int head = blockIdx.x, d = threadIdx.x, pos = state[1];
+    const int half = hd / 2;
+    if (head >= n_heads + n_kv) {   // value head: plain append
+        const int kvh = head - n_heads - n_kv;
+        if (d < hd) vcache[((size_t)kvh * max_seq + pos) * hd + d] = v[kvh * hd + d];
+        return;
+    }
+    const bool is_q = head < n_heads;
+    const float *src = is_q ? q + head * hd : k + (head - n_heads) * hd;
+    const float *w = is_q ? qw : kw;
+    const float x = d < hd ? src[d] : 0.0f;
+    const float mean = block_sum(x * x, red) / (float)hd;
+    const float rms = sqrtf(mean + eps);
+    if (d < hd) xs[d] = (x / rms) * w[d];
+    __syncthreads();
+    if (d >= hd) return;
+    const int i = d < half ? d : d - half;
+    const float c = cosv[(size_t)pos * half + i], s = sinv[(size_t)pos * half + i];
+    // y1 = x1 cos - x2 sin; y2 = x1 sin + x2 cos
+    const float y = d < half ? xs[d] * c - xs[d + half] * s : xs[d - half] * s + xs[d] * c;
+    if (is_q) qrot[head * hd + d] = y;
+    else kcache[((size_t)(head - n_heads) * max_seq + pos) * hd + d] = y;
+}
+
+// Grouped-query attention over the cache, split over the keys: CTA (kv head, split) has one warp
+// per query head of the group; lane l owns dimensions 4l .. 4l+3 (head_dim = 128). Every warp
+// keeps an online softmax (running maximum, sum and weighted values) over its part of the keys
+// and writes (m, l, acc[hd]) for the combine step.
+__global__ void __launch_bounds__(256)
+dec_attn_kernel(const float *__restrict__ qrot, const float *__restrict__ kcache, const float *__restrict__ vcache,
+                const int *__restrict__ state, float scale, float *__restrict__ part, int group, int hd, int max_seq) {
+    const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (warp >= group) return;
+    const int ctx = state[1] + 1;
+    const int per = (ctx + kAttnSplits - 1) / kAttnSplits;
+    const int j0 = split * per, j1 = min(ctx, j0 + per);
+    const int head = kvh * group + warp;
+    const float4 qv = *reinterpret_cast<const float4 *>(qrot + head * hd + 4 * lane);
+    float m = -INFINITY, l = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const float *kb = kcache + (size_t)kvh * max_seq * hd, *vb = vcache + (size_t)kvh * max_seq * hd;
+    for (int j = j0; j < j1; j++) {
+        const float4 kv = *reinterpret_cast<const float4 *>(kb + (size_t)j * hd + 4 * lane);
+        float s = qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+        s *= scale;
+        const float mn = fmaxf(m, s);
+        const float corr = expf(m - mn), p = expf(s - mn);
+        const float4 vv = *reinterpret_cast<const float4 *>(vb + (size_t)j * hd + 4 * lane);
+        l = l * corr + p;
+        acc.x = acc.x * corr + p * vv.x;
+        acc.y = acc.y * corr + p * vv.y;
+        acc.z = acc.z * corr + p * vv.z;
+        acc.w = acc.w * corr + p * vv.w;
+        m = mn;
+    }
+    float *o = part + ((size_t)head * kAttnSplits + split) * (hd + 4);   // record: m, l, pad, pad, acc[hd]
+    if (lane == 0) {
+        o[0] = m;
+        o[1] = l;
+    }
+    *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc;
+}
+
+// out[head, d] = sum_s acc_s[d] e^(m_s - M) / sum_s l_s e^(m_s - M)
+__global__ void __launch_bounds__(256)
+dec_attn_combine_kernel(const float *__restrict__ part, void *__restrict__ out, int act_dt, int hd) {
+    const int head = blockIdx.x, d = threadIdx.x;
+    if (d >= hd) return;
+    const float *p = part + (size_t)head * kAttnSplits * (hd + 4);
+    float M = -INFINITY;
+    for (int s = 0; s < kAttnSplits; s++) M = fmaxf(M, p[s * (hd + 4)]);
+    float L = 0.0f, a = 0.0f;
+    for (int s = 0; s < kAttnSplits; s++) {
+        const float ms = p[s * (hd + 4)];
+        if (ms == -INFINITY) continue;   // a split without keys
+        const float e = expf(ms - M);
+        L += p[s * (hd + 4) + 1] * e;
+        a += p[s * (hd + 4) + 4 + d] * e;
+    }
+    store_act(out, act_dt, head * hd + d, a / L);
+}
+
+__global__ void dec_silu_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, void *__restrict__ mid,
+                                    int act_dt, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float x = g[i];
+        store_act(mid, act_dt, i, (x / (1.0f + expf(-x))) * u[i]);
+    }
+}
+
+// larger value wins; of equal values the larger index (the reference keeps the last maximum)
+__device__ __forceinline__ void arg_better(float &bv, int &bi, float v, int i) {
+    if (v > bv || (v == bv && i > bi)) {
+        bv = v;
+        bi = i;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+dec_argmax_stage1_kernel(const float *__restrict__ logits, int n, float *__restrict__ bv_out, int *__restrict__ bi_out) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    float bv = -INFINITY;
+    int bi = -1;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) arg_better(bv, bi, logits[i], i);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+        const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
+        arg_better(bv, bi, ov, oi);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = bv;
+        si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) arg_better(bv, bi, sv[w], si[w]);
+        bv_out[blockIdx.x] = bv;
+        bi_out[blockIdx.x] = bi;
+    }
+}
+
+// picks the winner, records it and advances the device-side (token, position) pair
+__global__ void dec_argmax_stage2_kernel(const float *__restrict__ bv_in, const int *__restrict__ bi_in, int blocks,
+                                         int *__restrict__ state, int *__restrict__ tokens, int max_seq) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    float bv = -INFINITY;
+    int bi = -1;
+    for (int b = 0; b < blocks; b++) arg_better(bv, bi, bv_in[b], bi_in[b]);
+    if (bi < 0) bi = 0;   // all NaN: the reference returns index 0
+    const int pos = state[1];
+    tokens[pos] = bi;
+    state[0] = bi;
+    if (pos + 1 < max_seq) state[1] = pos + 1;
+    state[2] += 1;
+}
+
+}  // namespace nnq
+
+using namespace nnq;
+
+extern "C" {
+
+static nnq_status dev_alloc(nnq_ctx *ctx, void **p, size_t bytes, const char *what) {
+    nnq_status s = check_cuda(ctx, cudaMalloc(p, bytes ? bytes : 16), what);
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaMemset(*p, 0, bytes ? bytes : 16), what);
+    return s;
+}
+
+nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_decoder **out) {
+    if (!ctx || !cfg || !out) return NNQ_ERR_INVALID_ARG;
+    *out = nullptr;
+    const nnq_decoder_config &c = *cfg;
+    if (c.hidden < 1 || c.n_heads < 1 || c.n_kv_heads < 1 || c.ffn < 1 || c.n_layers < 1 || c.vocab < 1 || c.max_seq < 1)
+        return fail(ctx, NNQ_ERR_INVALID_ARG, "bad decoder dimensions");
+    if (c.head_dim != 128) return fail(ctx, NNQ_ERR_UNSUPPORTED, "the attention kernel is written for head_dim = 128 (got %d)", c.head_dim);
+    if (c.n_heads % c.n_kv_heads || c.n_heads / c.n_kv_heads > 8)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must divide evenly and be at most 8");
+    if (c.act_dtype != NNQ_F32 && c.act_dtype != NNQ_BF16) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown activation dtype");
+    if (!(c.rope_theta > 0.0)) return fail(ctx, NNQ_ERR_INVALID_ARG, "rope_theta must be positive");
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    nnq_decoder *d = new (std::nothrow) nnq_decoder();
+    if (!d) return fail(ctx, NNQ_ERR_OUT_OF_MEMORY, "host allocation failed");
+    memset(d, 0, sizeof(*d));
+    d->ctx = ctx;
+    d->cfg = c;
+    d->act_dt = c.act_dtype;
+    d->layers = new (std::nothrow) nnq_decoder::Layer[c.n_layers]();
+    if (!d->layers) {
+        delete d;
+        return fail(ctx, NNQ_ERR_OUT_OF_MEMORY, "host allocation failed");
+    }
+    const int hd = c.head_dim, half = hd / 2, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd;
+    const size_t es = c.act_dtype == NNQ_F32 ? 4 : 2;
+    const size_t cache = (size_t)c.n_layers * c.n_kv_heads * c.max_seq * hd * 4;
+    s = dev_alloc(ctx, (void **)&d->d_cos, (size_t)c.max_seq * half * 4, "rope table");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_sin, (size_t)c.max_seq * half * 4, "rope table");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_kcache, cache, "key cache");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_vcache, cache, "value cache");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_h, (size_t)c.hidden * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_delta, (size_t)c.hidden * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_q, (size_t)qdim * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_k, (size_t)kvdim * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_v, (size_t)kvdim * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_qrot, (size_t)qdim * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_g, (size_t)c.ffn * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_u, (size_t)c.ffn * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_logits, (size_t)c.vocab * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_part, (size_t)c.n_heads * kAttnSplits * (hd + 4) * 4, "attention partials");
+    if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_xn, (size_t)c.hidden * es, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_attn, (size_t)qdim * es, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_mid, (size_t)c.ffn * es, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_state, (4 + 2 * kArgmaxBlocks) * 4, "decoder state");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_tokens, (size_t)c.max_seq * 4, "token log");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_final_norm, (size_t)c.hidden * 4, "final norm");
+    for (int l = 0; l < c.n_layers && s == NNQ_OK; l++) {
+        nnq_decoder::Layer &L = d->layers[l];
+        s = dev_alloc(ctx, (void **)&L.in_norm, (size_t)c.hidden * 4, "norm weight");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&L.post_norm, (size_t)c.hidden * 4, "norm weight");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&L.q_norm, (size_t)hd * 4, "norm weight");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&L.k_norm, (size_t)hd * 4, "norm weight");
+    }
+    if (s == NNQ_OK) {
+        // tables exactly as the reference builds them: inv_freq in f32, the angle rounded to f32
+        float *hc = new (std::nothrow) float[(size_t)c.max_seq * half], *hs = new (std::nothrow) float[(size_t)c.max_seq * half];
+        if (!hc || !hs) s = fail(ctx, NNQ_ERR_OUT_OF_MEMORY, "host allocation failed");
+        if (s == NNQ_OK) {
+            for (int i = 0; i < half; i++) {
+                const float inv = (float)(1.0 / pow(c.rope_theta, (double)(2 * i) / (double)hd));
+                for (int p = 0; p < c.max_seq; p++) {
+                    const float angle = (float)((double)p * (double)inv);
+                    hc[(size_t)p * half + i] = cosf(angle);
+                    hs[(size_t)p * half + i] = sinf(angle);
+                }
+            }
+            s = check_cuda(ctx, cudaMemcpy(d->d_cos, hc, (size_t)c.max_seq * half * 4, cudaMemcpyHostToDevice), "rope table");
+            if (s == NNQ_OK) s = check_cuda(ctx, cudaMemcpy(d->d_sin, hs, (size_t)c.max_seq * half * 4, cudaMemcpyHostToDevice), "rope table");
+        }
+        delete[] hc;
+        delete[] hs;
+    }
+    if (s != NNQ_OK) {
+        nnq_decoder_destroy(d);
+        return s;
+    }
+    *out = d;
+    return NNQ_OK;
+}
+
+static bool shape_is(const nnq_weight *w, int64_t n, int64_t k) { return w && w->n == n && w->k == k; }
+
+nnq_status nnq_decoder_set_layer(nnq_decoder *d, int layer, const nnq_weight *q, const nnq_weight *k, const nnq_weight *v,
+                                 const nnq_weight *o, const nnq_weight *gate, const nnq_weight *up, const nnq_weight *down,
+                                 const float *in_norm, const float *post_norm, const float *q_norm, const float *k_norm) {
+    if (!d) return NNQ_ERR_INVALID_ARG;
+    nnq_ctx *ctx = d->ctx;
+    const nnq_decoder_config &c = d->cfg;
+    if (layer < 0 || layer >= c.n_layers) return fail(ctx, NNQ_ERR_INVALID_ARG, "layer %d out of range", layer);
+    if (!in_norm || !post_norm || !q_norm || !k_norm) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL norm weight");
+    const int64_t qdim = (int64_t)c.n_heads * c.head_dim, kvdim = (int64_t)c.n_kv_heads * c.head_dim;
+    if (!shape_is(q, qdim, c.hidden) || !shape_is(k, kvdim, c.hidden) || !shape_is(v, kvdim, c.hidden) ||
+        !shape_is(o, c.hidden, qdim) || !shape_is(gate, c.ffn, c.hidden) || !shape_is(up, c.ffn, c.hidden) ||
+        !shape_is(down, c.hidden, c.ffn))
+        return fail(ctx, NNQ_ERR_SHAPE_MISMATCH, "projection shapes of layer %d do not match the configuration", layer);
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    nnq_decoder::Layer &L = d->layers[layer];
+    L.q = q; L.k = k; L.v = v; L.o = o; L.gate = gate; L.up = up; L.down = down;
+    s = check_cuda(ctx, cudaMemcpy(L.in_norm, in_norm, (size_t)c.hidden * 4, cudaMemcpyDefault), "norm weight");
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaMemcpy(L.post_norm, post_norm, (size_t)c.hidden * 4, cudaMemcpyDefault), "norm weight");
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaMemcpy(L.q_norm, q_norm, (size_t)c.head_dim * 4, cudaMemcpyDefault), "norm weight");
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaMemcpy(L.k_norm, k_norm, (size_t)c.head_dim * 4, cudaMemcpyDefault), "norm weight");
+    return s;
+}
+
+nnq_status nnq_decoder_set_head(nnq_decoder *d, const void *embed_bf16_dev, const float *final_norm, const nnq_weight *lm_head) {
+    if (!d) return NNQ_ERR_INVALID_ARG;
+    nnq_ctx *ctx = d->ctx;
+    if (!embed_bf16_dev || !final_norm) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL tensor");
+    if (!shape_is(lm_head, d->cfg.vocab, d->cfg.hidden)) return fail(ctx, NNQ_ERR_SHAPE_MISMATCH, "vocabulary projection must be [vocab, hidden]");
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    d->d_embed = embed_bf16_dev;
+    d->lm_head = lm_head;
+    d->ready = 1;
+    return check_cuda(ctx, cudaMemcpy(d->d_final_norm, final_norm, (size_t)d->cfg.hidden * 4, cudaMemcpyDefault), "final norm");
+}
+
+nnq_status nnq_decoder_reset(nnq_decoder *d, int token, int pos, void *stream) {
+    if (!d) return NNQ_ERR_INVALID_ARG;
+    if (token < 0 || token >= d->cfg.vocab || pos < 0 || pos >= d->cfg.max_seq) return fail(d->ctx, NNQ_ERR_INVALID_ARG, "token or position out of range");
+    cudaSetDevice(d->ctx->device);
+    const int st[4] = {token, pos, 0, 0};
+    nnq_status s = check_cuda(d->ctx, cudaMemcpyAsync(d->d_state, st, sizeof(st), cudaMemcpyHostToDevice, (cudaStream_t)stream), "decoder state");
+    if (s == NNQ_OK) s = check_cuda(d->ctx, cudaStreamSynchronize((cudaStream_t)stream), "decoder state");   // st is on the stack
+    return s;
+}
+
+nnq_status nnq_decoder_buffers(nnq_decoder *d, float **k_cache, float **v_cache, float **logits, int **tokens) {
+    if (!d) return NNQ_ERR_INVALID_ARG;
+    if (k_cache) *k_cache = d->d_kcache;
+    if (v_cache) *v_cache = d->d_vcache;
+    if (logits) *logits = d->d_logits;
+    if (tokens) *tokens = d->d_tokens;
+    return NNQ_OK;
+}
+
+nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
+    if (!d) return NNQ_ERR_INVALID_ARG;
+    nnq_ctx *ctx = d->ctx;
+    if (!d->ready) return fail(ctx, NNQ_ERR_INVALID_ARG, "decoder head has not been set");
+    const nnq_decoder_config &c = d->cfg;
+    for (int l = 0; l < c.n_layers; l++)
+        if (!d->layers[l].q) return fail(ctx, NNQ_ERR_INVALID_ARG, "layer %d has not been set", l);
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int hd = c.head_dim, group = c.n_heads / c.n_kv_heads;
+    const nnq_dtype adt = (nnq_dtype)d->act_dt;
+    const size_t layer_cache = (size_t)c.n_kv_heads * c.max_seq * hd;
+    const float scale = (float)(1.0 / sqrt((double)hd));
+    const __nv_bfloat16 *embed = (const __nv_bfloat16 *)d->d_embed;
+    for (int l = 0; l < c.n_layers; l++) {
+        const nnq_decoder::Layer &L = d->layers[l];
+        dec_norm_kernel<<<1, 1024, 0, st>>>(d->d_h, d->d_delta, l == 0 ? embed : nullptr, d->d_state, L.in_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+        const nnq_weight *w3[3] = {L.q, L.k, L.v};
+        const void *x3[3] = {d->d_xn, d->d_xn, d->d_xn};
+        void *y3[3] = {d->d_q, d->d_k, d->d_v};
+        if ((s = nnq_linear_batch(ctx, 3, w3, x3, adt, 1, nullptr, y3, NNQ_F32, st)) != NNQ_OK) return s;
+        dec_qk_rope_kernel<<<c.n_heads + 2 * c.n_kv_heads, hd, 0, st>>>(d->d_q, d->d_k, d->d_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, d->d_state, c.rms_eps, d->d_qrot,
+                                                                        d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, c.n_heads, c.n_kv_heads, hd, c.max_seq);
+        dec_attn_kernel<<<dim3(c.n_kv_heads, kAttnSplits), 32 * group, 0, st>>>(d->d_qrot, d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, d->d_state, scale,
+                                                                               d->d_part, group, hd, c.max_seq);
+        dec_attn_combine_kernel<<<c.n_heads, hd, 0, st>>>(d->d_part, d->d_attn, d->act_dt, hd);
+        if ((s = nnq_linear(ctx, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st)) != NNQ_OK) return s;
+        dec_norm_kernel<<<1, 1024, 0, st>>>(d->d_h, d->d_delta, nullptr, d->d_state, L.post_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+        const nnq_weight *w2[2] = {L.gate, L.up};
+        const void *x2[2] = {d->d_xn, d->d_xn};
+        void *y2[2] = {d->d_g, d->d_u};
+        if ((s = nnq_linear_batch(ctx, 2, w2, x2, adt, 1, nullptr, y2, NNQ_F32, st)) != NNQ_OK) return s;
+        dec_silu_mul_kernel<<<(c.ffn + 255) / 256, 256, 0, st>>>(d->d_g, d->d_u, d->d_mid, d->act_dt, c.ffn);
+        if ((s = nnq_linear(ctx, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st)) != NNQ_OK) return s;
+        ctx->launches += 6;
+    }
+    dec_norm_kernel<<<1, 1024, 0, st>>>(d->d_h, d->d_delta, nullptr, d->d_state, d->d_final_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+    if ((s = nnq_linear(ctx, d->lm_head, d->d_xn, adt, 1, nullptr, d->d_logits, NNQ_F32, st)) != NNQ_OK) return s;
+    float *bv = reinterpret_cast<float *>(d->d_state + 4);
+    int *bi = d->d_state + 4 + kArgmaxBlocks;
+    dec_argmax_stage1_kernel<<<kArgmaxBlocks, 256, 0, st>>>(d->d_logits, c.vocab, bv, bi);
+    dec_argmax_stage2_kernel<<<1, 32, 0, st>>>(bv, bi, kArgmaxBlocks, d->d_state, d->d_tokens, c.max_seq);
+    ctx->launches += 3;
+    return check_cuda(ctx, cudaGetLastError(), "decoder step launch");
+}
+
+nnq_status nnq_decoder_state(nnq_decoder *d, int *token, int *pos, int *steps, void *stream) {
+    if (!d) return NNQ_ERR_INVALID_ARG;
+    cudaSetDevice(d->ctx->device);
+    int st[4] = {0, 0, 0, 0};
+    nnq_status s = check_cuda(d->ctx, cudaMemcpyAsync(st, d->d_state, sizeof(st), cudaMemcpyDeviceToHost, (cudaStream_t)stream), "decoder state");
+    if (s == NNQ_OK) s = check_cuda(d->ctx, cudaStreamSynchronize((cudaStream_t)stream), "decoder state");
+    if (token) *token = st[0];
+    if (pos) *pos = st[1];
+    if (steps) *steps = st[2];
+    return s;
+}
+
+void nnq_decoder_destroy(nnq_decoder *d) {
+    if (!d) return;
+    cudaSetDevice(d->ctx->device);
+    cudaDeviceSynchronize();
+    if (d->layers) {
+        for (int l = 0; l < d->cfg.n_layers; l++) {
+            cudaFree(d->layers[l].in_norm); cudaFree(d->layers[l].post_norm);
+            cudaFree(d->layers[l].q_norm); cudaFree(d->layers[l].k_norm);
+        }
+        delete[] d->layers;
+    }
+    cudaFree(d->d_final_norm); cudaFree(d->d_cos); cudaFree(d->d_sin); cudaFree(d->d_kcache); cudaFree(d->d_vcache);
+    cudaFree(d->d_h); cudaFree(d->d_delta); cudaFree(d->d_q); cudaFree(d->d_k); cudaFree(d->d_v); cudaFree(d->d_qrot);
+    cudaFree(d->d_g); cudaFree(d->d_u); cudaFree(d->d_logits); cudaFree(d->d_part); cudaFree(d->d_xn); cudaFree(d->d_attn);
+    cudaFree(d->d_mid); cudaFree(d->d_state); cudaFree(d->d_tokens);
+    cudaGetLastError();
+    delete d;
+}
+
+}  // extern "C"
