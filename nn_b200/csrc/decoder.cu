@@ -40,7 +40,7 @@ struct nnq_decoder {
 
 namespace nnq {
 
-constexpr int kAttnSplits = 16;
+constexpr int kAttnSplits = 64;
 constexpr int kArgmaxBlocks = 128;
 
 __device__ __forceinline__ float block_sum(float v, float *red) {
@@ -111,45 +111,89 @@ dec_qk_rope_kernel(const float *__restrict__ q, const float *__restrict__ k, con
     else kcache[((size_t)(head - n_heads) * max_seq + pos) * hd + d] = y;
 }
 
-// Grouped-query attention over the cache, split over the keys: CTA (kv head, split) has one warp
-// per query head of the group; lane l owns dimensions 4l .. 4l+3 (head_dim = 128). Every warp
-// keeps an online softmax (running maximum, sum and weighted values) over its part of the keys
-// and writes (m, l, acc[hd]) for the combine step.
-__global__ void __launch_bounds__(256)
+// Grouped-query attention over the cache, split over the keys: one warp per (kv head, split)
+// serves all query heads of the group. Keys are taken 32 at a time: lane j forms the dot products
+// of key j with every query head of the group (the query vectors sit in shared memory, the key row
+// is read once for the whole group), the batch joins the running softmax of each head (maximum,
+// sum), then the value rows are read coalesced (lane l owns dimensions 4l .. 4l+3) and weighted
+// with the probabilities passed by shuffle. Output per head and split: (m, l, acc[hd]).
+template <int G>
+__global__ void __launch_bounds__(32)
 dec_attn_kernel(const float *__restrict__ qrot, const float *__restrict__ kcache, const float *__restrict__ vcache,
-                const int *__restrict__ state, float scale, float *__restrict__ part, int group, int hd, int max_seq) {
-    const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (warp >= group) return;
+                const int *__restrict__ state, float scale, float *__restrict__ part, int hd, int max_seq) {
+    __shared__ __align__(16) float qs[G][128];
+    const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x;
     const int ctx = state[1] + 1;
     const int per = (ctx + kAttnSplits - 1) / kAttnSplits;
     const int j0 = split * per, j1 = min(ctx, j0 + per);
-    const int head = kvh * group + warp;
-    const float4 qv = *reinterpret_cast<const float4 *>(qrot + head * hd + 4 * lane);
-    float m = -INFINITY, l = 0.0f;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    const float *kb = kcache + (size_t)kvh * max_seq * hd, *vb = vcache + (size_t)kvh * max_seq * hd;
-    for (int j = j0; j < j1; j++) {
-        const float4 kv = *reinterpret_cast<const float4 *>(kb + (size_t)j * hd + 4 * lane);
-        float s = qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
-        s *= scale;
-        const float mn = fmaxf(m, s);
-        const float corr = expf(m - mn), p = expf(s - mn);
-        const float4 vv = *reinterpret_cast<const float4 *>(vb + (size_t)j * hd + 4 * lane);
-        l = l * corr + p;
-        acc.x = acc.x * corr + p * vv.x;
-        acc.y = acc.y * corr + p * vv.y;
-        acc.z = acc.z * corr + p * vv.z;
-        acc.w = acc.w * corr + p * vv.w;
-        m = mn;
+    for (int g = 0; g < G; g++)
+        *reinterpret_cast<float4 *>(&qs[g][4 * lane]) = *reinterpret_cast<const float4 *>(qrot + (kvh * G + g) * hd + 4 * lane);
+    __syncwarp();
+    float m[G], l[G];
+    float4 acc[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+        acc[g] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
-    float *o = part + ((size_t)head * kAttnSplits + split) * (hd + 4);   // record: m, l, pad, pad, acc[hd]
-    if (lane == 0) {
-        o[0] = m;
-        o[1] = l;
+    const float *kb = kcache + (size_t)kvh * max_seq * hd, *vb = vcache + (size_t)kvh * max_seq * hd;
+    for (int b0 = j0; b0 < j1; b0 += 32) {
+        const int j = b0 + lane;
+        const bool valid = j < j1;
+        const float4 *krow = reinterpret_cast<const float4 *>(kb + (size_t)(valid ? j : b0) * hd);
+        float dot[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) dot[g] = 0.0f;
+#pragma unroll 8
+        for (int d4 = 0; d4 < 32; d4++) {
+            const float4 kv = krow[d4];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float4 qv = *reinterpret_cast<const float4 *>(&qs[g][4 * d4]);
+                dot[g] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, dot[g]))));
+            }
+        }
+        float p[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const float s = valid ? dot[g] * scale : -INFINITY;
+            float bm = s;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
+            const float mn = fmaxf(m[g], bm);   // finite: the batch holds at least one key
+            const float corr = expf(m[g] - mn);
+            p[g] = expf(s - mn);
+            float ps = p[g];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xFFFFFFFFu, ps, off);
+            l[g] = l[g] * corr + ps;
+            acc[g].x *= corr; acc[g].y *= corr; acc[g].z *= corr; acc[g].w *= corr;
+            m[g] = mn;
+        }
+        const int nb = min(32, j1 - b0);
+        for (int jj = 0; jj < nb; jj++) {
+            const float4 vv = *reinterpret_cast<const float4 *>(vb + (size_t)(b0 + jj) * hd + 4 * lane);
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float pj = __shfl_sync(0xFFFFFFFFu, p[g], jj);
+                acc[g].x = fmaf(pj, vv.x, acc[g].x);
+                acc[g].y = fmaf(pj, vv.y, acc[g].y);
+                acc[g].z = fmaf(pj, vv.z, acc[g].z);
+                acc[g].w = fmaf(pj, vv.w, acc[g].w);
+            }
+        }
     }
-    *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc;
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        float *o = part + ((size_t)(kvh * G + g) * kAttnSplits + split) * (hd + 4);   // record: m, l, pad, pad, acc[hd]
+        if (lane == 0) {
+            o[0] = m[g];
+            o[1] = l[g];
+        }
+        *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc[g];
+    }
 }
 
 // out[head, d] = sum_s acc_s[d] e^(m_s - M) / sum_s l_s e^(m_s - M)
@@ -247,8 +291,9 @@ nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_d
     if (c.hidden < 1 || c.n_heads < 1 || c.n_kv_heads < 1 || c.ffn < 1 || c.n_layers < 1 || c.vocab < 1 || c.max_seq < 1)
         return fail(ctx, NNQ_ERR_INVALID_ARG, "bad decoder dimensions");
     if (c.head_dim != 128) return fail(ctx, NNQ_ERR_UNSUPPORTED, "the attention kernel is written for head_dim = 128 (got %d)", c.head_dim);
-    if (c.n_heads % c.n_kv_heads || c.n_heads / c.n_kv_heads > 8)
-        return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must divide evenly and be at most 8");
+    const int grp = c.n_heads % c.n_kv_heads ? 0 : c.n_heads / c.n_kv_heads;
+    if (grp != 1 && grp != 2 && grp != 4 && grp != 8)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must be 1, 2, 4 or 8");
     if (c.act_dtype != NNQ_F32 && c.act_dtype != NNQ_BF16) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown activation dtype");
     if (!(c.rope_theta > 0.0)) return fail(ctx, NNQ_ERR_INVALID_ARG, "rope_theta must be positive");
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
@@ -403,8 +448,17 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
         if ((s = nnq_linear_batch(ctx, 3, w3, x3, adt, 1, nullptr, y3, NNQ_F32, st)) != NNQ_OK) return s;
         dec_qk_rope_kernel<<<c.n_heads + 2 * c.n_kv_heads, hd, 0, st>>>(d->d_q, d->d_k, d->d_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, d->d_state, c.rms_eps, d->d_qrot,
                                                                         d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, c.n_heads, c.n_kv_heads, hd, c.max_seq);
-        dec_attn_kernel<<<dim3(c.n_kv_heads, kAttnSplits), 32 * group, 0, st>>>(d->d_qrot, d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, d->d_state, scale,
-                                                                               d->d_part, group, hd, c.max_seq);
+        {
+            const dim3 ag(c.n_kv_heads, kAttnSplits);
+            const float *kc = d->d_kcache + l * layer_cache, *vc = d->d_vcache + l * layer_cache;
+            switch (group) {
+                case 1: dec_attn_kernel<1><<<ag, 32, 0, st>>>(d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                case 2: dec_attn_kernel<2><<<ag, 32, 0, st>>>(d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                case 4: dec_attn_kernel<4><<<ag, 32, 0, st>>>(d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                case 8: dec_attn_kernel<8><<<ag, 32, 0, st>>>(d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                default: return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must be 1, 2, 4 or 8");
+            }
+        }
         dec_attn_combine_kernel<<<c.n_heads, hd, 0, st>>>(d->d_part, d->d_attn, d->act_dt, hd);
         if ((s = nnq_linear(ctx, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st)) != NNQ_OK) return s;
         dec_norm_kernel<<<1, 1024, 0, st>>>(d->d_h, d->d_delta, nullptr, d->d_state, L.post_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
