@@ -40,8 +40,31 @@ struct nnq_decoder {
 
 namespace nnq {
 
-constexpr int kAttnSplits = 64;
+constexpr int kAttnSplits = 128;
 constexpr int kArgmaxBlocks = 128;
+
+// Every kernel of the step is launched with programmatic stream serialization and waits for its
+// predecessor before touching any data, so that its launch overlaps the predecessor's tail. The
+// small kernels do NOT release their successor early: a quantized product that became resident
+// while they run would hold most of the registers of every SM and starve them (measured: slower).
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float block_sum(float v, float *red) {
 #pragma unroll
@@ -60,22 +83,42 @@ __device__ __forceinline__ void store_act(void *dst, int dt, int i, float v) {
     else reinterpret_cast<__nv_bfloat16 *>(dst)[i] = __float2bfloat16_rn(v);
 }
 
-// h = embedding row of the current token (first layer), or h += delta; xn = RMSNorm(h) * w
+// h = embedding row of the current token (first layer), or h += delta; xn = RMSNorm(h) * w.
+// One CTA; every thread keeps its (up to 8) elements in registers between the two phases.
 __global__ void __launch_bounds__(1024)
 dec_norm_kernel(float *__restrict__ h, const float *__restrict__ delta, const __nv_bfloat16 *__restrict__ embed,
                 const int *__restrict__ state, const float *__restrict__ w, float eps, void *__restrict__ xn, int act_dt,
                 int hidden) {
+    pdl_prologue();
     __shared__ float red[32];
     const int tok = embed ? state[0] : 0;
+    float v[8], wv[8];
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = embed ? __bfloat162float(embed[(size_t)tok * hidden + i]) : h[i] + delta[i];
-        h[i] = v;
-        ss = fmaf(v, v, ss);
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        const int i = threadIdx.x + r * 1024;
+        v[r] = 0.0f;
+        wv[r] = 0.0f;
+        if (i < hidden) {
+            v[r] = embed ? __bfloat162float(embed[(size_t)tok * hidden + i]) : h[i] + delta[i];
+            wv[r] = w[i];
+            h[i] = v[r];
+            ss = fmaf(v[r], v[r], ss);
+        }
+    }
+    for (int i = threadIdx.x + 8 * 1024; i < hidden; i += 1024) {   // wider models: the tail goes through memory
+        const float t = embed ? __bfloat162float(embed[(size_t)tok * hidden + i]) : h[i] + delta[i];
+        h[i] = t;
+        ss = fmaf(t, t, ss);
     }
     const float mean = block_sum(ss, red) / (float)hidden;
     const float rms = sqrtf(mean + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) store_act(xn, act_dt, i, (h[i] / rms) * w[i]);
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        const int i = threadIdx.x + r * 1024;
+        if (i < hidden) store_act(xn, act_dt, i, (v[r] / rms) * wv[r]);
+    }
+    for (int i = threadIdx.x + 8 * 1024; i < hidden; i += 1024) store_act(xn, act_dt, i, (h[i] / rms) * w[i]);
 }
 
 // One CTA per head (query heads, then key heads, then value heads), one thread per dimension:
@@ -85,6 +128,7 @@ dec_qk_rope_kernel(const float *__restrict__ q, const float *__restrict__ k, con
                    const float *__restrict__ qw, const float *__restrict__ kw, const float *__restrict__ cosv,
                    const float *__restrict__ sinv, const int *__restrict__ state, float eps, float *__restrict__ qrot,
                    float *__restrict__ kcache, float *__restrict__ vcache, int n_heads, int n_kv, int hd, int max_seq) {
+    pdl_prologue();
     __shared__ float red[32];
     __shared__ float xs[256];
     const int head = blockIdx.x, d = threadIdx.x, pos = state[1];
@@ -121,6 +165,7 @@ template <int G>
 __global__ void __launch_bounds__(32)
 dec_attn_kernel(const float *__restrict__ qrot, const float *__restrict__ kcache, const float *__restrict__ vcache,
                 const int *__restrict__ state, float scale, float *__restrict__ part, int hd, int max_seq) {
+    pdl_prologue();
     __shared__ __align__(16) float qs[G][128];
     const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x;
     const int ctx = state[1] + 1;
@@ -146,7 +191,7 @@ dec_attn_kernel(const float *__restrict__ qrot, const float *__restrict__ kcache
         float dot[G];
 #pragma unroll
         for (int g = 0; g < G; g++) dot[g] = 0.0f;
-#pragma unroll 8
+#pragma unroll 16
         for (int d4 = 0; d4 < 32; d4++) {
             const float4 kv = krow[d4];
 #pragma unroll
@@ -196,27 +241,40 @@ dec_attn_kernel(const float *__restrict__ qrot, const float *__restrict__ kcache
     }
 }
 
-// out[head, d] = sum_s acc_s[d] e^(m_s - M) / sum_s l_s e^(m_s - M)
-__global__ void __launch_bounds__(256)
+// out[head, d] = sum_s acc_s[d] e^(m_s - M) / sum_s l_s e^(m_s - M); the split weights are formed
+// once per head by the first kAttnSplits threads
+__global__ void __launch_bounds__(128)
 dec_attn_combine_kernel(const float *__restrict__ part, void *__restrict__ out, int act_dt, int hd) {
+    pdl_prologue();
+    __shared__ float wgt[kAttnSplits];
+    __shared__ float red[32];
     const int head = blockIdx.x, d = threadIdx.x;
-    if (d >= hd) return;
     const float *p = part + (size_t)head * kAttnSplits * (hd + 4);
-    float M = -INFINITY;
-    for (int s = 0; s < kAttnSplits; s++) M = fmaxf(M, p[s * (hd + 4)]);
-    float L = 0.0f, a = 0.0f;
-    for (int s = 0; s < kAttnSplits; s++) {
-        const float ms = p[s * (hd + 4)];
-        if (ms == -INFINITY) continue;   // a split without keys
-        const float e = expf(ms - M);
-        L += p[s * (hd + 4) + 1] * e;
-        a += p[s * (hd + 4) + 4 + d] * e;
+    float ms = -INFINITY, ls = 0.0f;
+    if (d < kAttnSplits) {
+        ms = p[d * (hd + 4)];
+        ls = p[d * (hd + 4) + 1];
     }
-    store_act(out, act_dt, head * hd + d, a / L);
+    float M = ms;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, off));
+    if ((d & 31) == 0) red[d >> 5] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float e = ms == -INFINITY ? 0.0f : expf(ms - M);   // a split without keys has weight 0
+    if (d < kAttnSplits) wgt[d] = e;
+    const float L = block_sum(ls * e, red);
+    float a = 0.0f;
+    if (d < hd) {
+#pragma unroll 8
+        for (int s = 0; s < kAttnSplits; s++) a = fmaf(p[s * (hd + 4) + 4 + d], wgt[s], a);
+        store_act(out, act_dt, head * hd + d, a / L);
+    }
 }
 
 __global__ void dec_silu_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, void *__restrict__ mid,
                                     int act_dt, int n) {
+    pdl_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         const float x = g[i];
@@ -234,6 +292,7 @@ __device__ __forceinline__ void arg_better(float &bv, int &bi, float v, int i) {
 
 __global__ void __launch_bounds__(256)
 dec_argmax_stage1_kernel(const float *__restrict__ logits, int n, float *__restrict__ bv_out, int *__restrict__ bi_out) {
+    pdl_prologue();
     __shared__ float sv[8];
     __shared__ int si[8];
     float bv = -INFINITY;
@@ -260,6 +319,7 @@ dec_argmax_stage1_kernel(const float *__restrict__ logits, int n, float *__restr
 // picks the winner, records it and advances the device-side (token, position) pair
 __global__ void dec_argmax_stage2_kernel(const float *__restrict__ bv_in, const int *__restrict__ bi_in, int blocks,
                                          int *__restrict__ state, int *__restrict__ tokens, int max_seq) {
+    pdl_prologue();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     float bv = -INFINITY;
     int bi = -1;
@@ -441,41 +501,41 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
     const __nv_bfloat16 *embed = (const __nv_bfloat16 *)d->d_embed;
     for (int l = 0; l < c.n_layers; l++) {
         const nnq_decoder::Layer &L = d->layers[l];
-        dec_norm_kernel<<<1, 1024, 0, st>>>(d->d_h, d->d_delta, l == 0 ? embed : nullptr, d->d_state, L.in_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+        launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, l == 0 ? embed : nullptr, d->d_state, L.in_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
         const nnq_weight *w3[3] = {L.q, L.k, L.v};
         const void *x3[3] = {d->d_xn, d->d_xn, d->d_xn};
         void *y3[3] = {d->d_q, d->d_k, d->d_v};
         if ((s = nnq_linear_batch(ctx, 3, w3, x3, adt, 1, nullptr, y3, NNQ_F32, st)) != NNQ_OK) return s;
-        dec_qk_rope_kernel<<<c.n_heads + 2 * c.n_kv_heads, hd, 0, st>>>(d->d_q, d->d_k, d->d_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, d->d_state, c.rms_eps, d->d_qrot,
-                                                                        d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, c.n_heads, c.n_kv_heads, hd, c.max_seq);
+        launch_pdl(dec_qk_rope_kernel, dim3(c.n_heads + 2 * c.n_kv_heads), dim3(hd), st, d->d_q, d->d_k, d->d_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, d->d_state,
+                   c.rms_eps, d->d_qrot, d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, c.n_heads, c.n_kv_heads, hd, c.max_seq);
         {
             const dim3 ag(c.n_kv_heads, kAttnSplits);
             const float *kc = d->d_kcache + l * layer_cache, *vc = d->d_vcache + l * layer_cache;
             switch (group) {
-                case 1: dec_attn_kernel<1><<<ag, 32, 0, st>>>(d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
-                case 2: dec_attn_kernel<2><<<ag, 32, 0, st>>>(d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
-                case 4: dec_attn_kernel<4><<<ag, 32, 0, st>>>(d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
-                case 8: dec_attn_kernel<8><<<ag, 32, 0, st>>>(d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                case 1: launch_pdl(dec_attn_kernel<1>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                case 2: launch_pdl(dec_attn_kernel<2>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                case 4: launch_pdl(dec_attn_kernel<4>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                case 8: launch_pdl(dec_attn_kernel<8>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
                 default: return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must be 1, 2, 4 or 8");
             }
         }
-        dec_attn_combine_kernel<<<c.n_heads, hd, 0, st>>>(d->d_part, d->d_attn, d->act_dt, hd);
+        launch_pdl(dec_attn_combine_kernel, dim3(c.n_heads), dim3(128), st, d->d_part, d->d_attn, d->act_dt, hd);
         if ((s = nnq_linear(ctx, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st)) != NNQ_OK) return s;
-        dec_norm_kernel<<<1, 1024, 0, st>>>(d->d_h, d->d_delta, nullptr, d->d_state, L.post_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+        launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, L.post_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
         const nnq_weight *w2[2] = {L.gate, L.up};
         const void *x2[2] = {d->d_xn, d->d_xn};
         void *y2[2] = {d->d_g, d->d_u};
         if ((s = nnq_linear_batch(ctx, 2, w2, x2, adt, 1, nullptr, y2, NNQ_F32, st)) != NNQ_OK) return s;
-        dec_silu_mul_kernel<<<(c.ffn + 255) / 256, 256, 0, st>>>(d->d_g, d->d_u, d->d_mid, d->act_dt, c.ffn);
+        launch_pdl(dec_silu_mul_kernel, dim3((c.ffn + 255) / 256), dim3(256), st, d->d_g, d->d_u, d->d_mid, d->act_dt, c.ffn);
         if ((s = nnq_linear(ctx, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st)) != NNQ_OK) return s;
         ctx->launches += 6;
     }
-    dec_norm_kernel<<<1, 1024, 0, st>>>(d->d_h, d->d_delta, nullptr, d->d_state, d->d_final_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+    launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, d->d_final_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
     if ((s = nnq_linear(ctx, d->lm_head, d->d_xn, adt, 1, nullptr, d->d_logits, NNQ_F32, st)) != NNQ_OK) return s;
     float *bv = reinterpret_cast<float *>(d->d_state + 4);
     int *bi = d->d_state + 4 + kArgmaxBlocks;
-    dec_argmax_stage1_kernel<<<kArgmaxBlocks, 256, 0, st>>>(d->d_logits, c.vocab, bv, bi);
-    dec_argmax_stage2_kernel<<<1, 32, 0, st>>>(bv, bi, kArgmaxBlocks, d->d_state, d->d_tokens, c.max_seq);
+    launch_pdl(dec_argmax_stage1_kernel, dim3(kArgmaxBlocks), dim3(256), st, d->d_logits, c.vocab, bv, bi);
+    launch_pdl(dec_argmax_stage2_kernel, dim3(1), dim3(32), st, bv, bi, kArgmaxBlocks, d->d_state, d->d_tokens, c.max_seq);
     ctx->launches += 3;
     return check_cuda(ctx, cudaGetLastError(), "decoder step launch");
 }
