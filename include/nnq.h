@@ -337,6 +337,7 @@ typedef struct nnq_decoder_config {
     float rms_eps;
     double rope_theta;
     int32_t act_dtype;   /* nnq_dtype */
+    int32_t tp_rank, tp_world;   /* tensor parallelism over key/value heads and the FFN width; 0 of 1 = none */
 } nnq_decoder_config;
 NNQ_API nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_decoder **out);
 /* norm weights: f32, host or device pointers (copied) */
@@ -346,6 +347,12 @@ NNQ_API nnq_status nnq_decoder_set_layer(nnq_decoder *d, int layer, const nnq_we
                                          const float *post_norm, const float *q_norm, const float *k_norm);
 NNQ_API nnq_status nnq_decoder_set_head(nnq_decoder *d, const void *embed_bf16_dev, const float *final_norm,
                                         const nnq_weight *lm_head);
+/* Tensor-parallel decoder (tp_world > 1): set_layer takes this rank's shards (q / k / v / gate / up
+ * split by rows: heads [rank * n_heads / world, ...), FFN rows likewise; o / down split along K in
+ * the same ranges), norms, embedding and the vocabulary projection are replicated, and the o and
+ * down products are exchanged through `comm` (nnq_comm_linear; max_bytes >= 8 * hidden). All ranks
+ * hold identical hidden states and produce the same token. */
+NNQ_API nnq_status nnq_decoder_set_comm(nnq_decoder *d, nnq_comm *comm);
 /* next input token and the position it is written at (synchronises the stream) */
 NNQ_API nnq_status nnq_decoder_reset(nnq_decoder *d, int token, int pos, void *stream);
 /* one token: consumes (token, pos), appends to the caches, leaves the logits in the logits buffer,

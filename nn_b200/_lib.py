@@ -51,6 +51,7 @@ SIGNATURES = {
     "nnq_decoder_create": (c_int, [c_void_p, c_void_p, ctypes.POINTER(c_void_p)]),
     "nnq_decoder_set_layer": (c_int, [c_void_p, c_int] + [c_void_p] * 11),
     "nnq_decoder_set_head": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nnq_decoder_set_comm": (c_int, [c_void_p, c_void_p]),
     "nnq_decoder_reset": (c_int, [c_void_p, c_int, c_int, c_void_p]),
     "nnq_decoder_step": (c_int, [c_void_p, c_void_p]),
     "nnq_decoder_state": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_void_p]),

@@ -36,6 +36,8 @@ struct nnq_decoder {
     int *d_tokens;              // generated tokens, [max_seq]
     int act_dt;
     int ready;                  // bit set of what has been supplied
+    nnq_comm *comm;             // tensor parallel: exchange of the row-parallel products (NULL when tp_world = 1)
+    int lh, lkv;                // query / key-value heads held by this rank
 };
 
 namespace nnq {
@@ -347,7 +349,8 @@ static nnq_status dev_alloc(nnq_ctx *ctx, void **p, size_t bytes, const char *wh
 nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_decoder **out) {
     if (!ctx || !cfg || !out) return NNQ_ERR_INVALID_ARG;
     *out = nullptr;
-    const nnq_decoder_config &c = *cfg;
+    nnq_decoder_config c = *cfg;
+    if (c.tp_world == 0) c.tp_world = 1;   // a zeroed field means no tensor parallelism
     if (c.hidden < 1 || c.n_heads < 1 || c.n_kv_heads < 1 || c.ffn < 1 || c.n_layers < 1 || c.vocab < 1 || c.max_seq < 1)
         return fail(ctx, NNQ_ERR_INVALID_ARG, "bad decoder dimensions");
     if (c.head_dim != 128) return fail(ctx, NNQ_ERR_UNSUPPORTED, "the attention kernel is written for head_dim = 128 (got %d)", c.head_dim);
@@ -355,6 +358,10 @@ nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_d
     if (grp != 1 && grp != 2 && grp != 4 && grp != 8)
         return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must be 1, 2, 4 or 8");
     if (c.act_dtype != NNQ_F32 && c.act_dtype != NNQ_BF16) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown activation dtype");
+    if (c.tp_world < 1 || c.tp_world > 8 || c.tp_rank < 0 || c.tp_rank >= c.tp_world)
+        return fail(ctx, NNQ_ERR_INVALID_ARG, "bad tensor-parallel rank %d of %d", c.tp_rank, c.tp_world);
+    if (c.n_kv_heads % c.tp_world || c.ffn % c.tp_world)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "key/value heads and the FFN width must divide by the tensor-parallel world size");
     if (!(c.rope_theta > 0.0)) return fail(ctx, NNQ_ERR_INVALID_ARG, "rope_theta must be positive");
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
@@ -364,14 +371,16 @@ nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_d
     d->ctx = ctx;
     d->cfg = c;
     d->act_dt = c.act_dtype;
+    d->lh = c.n_heads / c.tp_world;
+    d->lkv = c.n_kv_heads / c.tp_world;
     d->layers = new (std::nothrow) nnq_decoder::Layer[c.n_layers]();
     if (!d->layers) {
         delete d;
         return fail(ctx, NNQ_ERR_OUT_OF_MEMORY, "host allocation failed");
     }
-    const int hd = c.head_dim, half = hd / 2, qdim = c.n_heads * hd, kvdim = c.n_kv_heads * hd;
+    const int hd = c.head_dim, half = hd / 2, qdim = d->lh * hd, kvdim = d->lkv * hd, lffn = c.ffn / c.tp_world;
     const size_t es = c.act_dtype == NNQ_F32 ? 4 : 2;
-    const size_t cache = (size_t)c.n_layers * c.n_kv_heads * c.max_seq * hd * 4;
+    const size_t cache = (size_t)c.n_layers * d->lkv * c.max_seq * hd * 4;
     s = dev_alloc(ctx, (void **)&d->d_cos, (size_t)c.max_seq * half * 4, "rope table");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_sin, (size_t)c.max_seq * half * 4, "rope table");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_kcache, cache, "key cache");
@@ -382,13 +391,13 @@ nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_d
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_k, (size_t)kvdim * 4, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_v, (size_t)kvdim * 4, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_qrot, (size_t)qdim * 4, "decoder buffer");
-    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_g, (size_t)c.ffn * 4, "decoder buffer");
-    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_u, (size_t)c.ffn * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_g, (size_t)lffn * 4, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_u, (size_t)lffn * 4, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_logits, (size_t)c.vocab * 4, "decoder buffer");
-    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_part, (size_t)c.n_heads * kAttnSplits * (hd + 4) * 4, "attention partials");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_part, (size_t)d->lh * kAttnSplits * (hd + 4) * 4, "attention partials");
     if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_xn, (size_t)c.hidden * es, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_attn, (size_t)qdim * es, "decoder buffer");
-    if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_mid, (size_t)c.ffn * es, "decoder buffer");
+    if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_mid, (size_t)lffn * es, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_state, (4 + 2 * kArgmaxBlocks) * 4, "decoder state");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_tokens, (size_t)c.max_seq * 4, "token log");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_final_norm, (size_t)c.hidden * 4, "final norm");
@@ -436,10 +445,11 @@ nnq_status nnq_decoder_set_layer(nnq_decoder *d, int layer, const nnq_weight *q,
     const nnq_decoder_config &c = d->cfg;
     if (layer < 0 || layer >= c.n_layers) return fail(ctx, NNQ_ERR_INVALID_ARG, "layer %d out of range", layer);
     if (!in_norm || !post_norm || !q_norm || !k_norm) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL norm weight");
-    const int64_t qdim = (int64_t)c.n_heads * c.head_dim, kvdim = (int64_t)c.n_kv_heads * c.head_dim;
+    // with tensor parallelism: this rank's column shards of q / k / v / gate / up and row shards of o / down
+    const int64_t qdim = (int64_t)d->lh * c.head_dim, kvdim = (int64_t)d->lkv * c.head_dim, lffn = c.ffn / c.tp_world;
     if (!shape_is(q, qdim, c.hidden) || !shape_is(k, kvdim, c.hidden) || !shape_is(v, kvdim, c.hidden) ||
-        !shape_is(o, c.hidden, qdim) || !shape_is(gate, c.ffn, c.hidden) || !shape_is(up, c.ffn, c.hidden) ||
-        !shape_is(down, c.hidden, c.ffn))
+        !shape_is(o, c.hidden, qdim) || !shape_is(gate, lffn, c.hidden) || !shape_is(up, lffn, c.hidden) ||
+        !shape_is(down, c.hidden, lffn))
         return fail(ctx, NNQ_ERR_SHAPE_MISMATCH, "projection shapes of layer %d do not match the configuration", layer);
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
@@ -463,6 +473,13 @@ nnq_status nnq_decoder_set_head(nnq_decoder *d, const void *embed_bf16_dev, cons
     d->lm_head = lm_head;
     d->ready = 1;
     return check_cuda(ctx, cudaMemcpy(d->d_final_norm, final_norm, (size_t)d->cfg.hidden * 4, cudaMemcpyDefault), "final norm");
+}
+
+nnq_status nnq_decoder_set_comm(nnq_decoder *d, nnq_comm *comm) {
+    if (!d) return NNQ_ERR_INVALID_ARG;
+    if (d->cfg.tp_world > 1 && !comm) return fail(d->ctx, NNQ_ERR_INVALID_ARG, "a tensor-parallel decoder needs a communicator");
+    d->comm = comm;
+    return NNQ_OK;
 }
 
 nnq_status nnq_decoder_reset(nnq_decoder *d, int token, int pos, void *stream) {
@@ -489,14 +506,15 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
     nnq_ctx *ctx = d->ctx;
     if (!d->ready) return fail(ctx, NNQ_ERR_INVALID_ARG, "decoder head has not been set");
     const nnq_decoder_config &c = d->cfg;
+    if (c.tp_world > 1 && !d->comm) return fail(ctx, NNQ_ERR_INVALID_ARG, "communicator has not been set");
     for (int l = 0; l < c.n_layers; l++)
         if (!d->layers[l].q) return fail(ctx, NNQ_ERR_INVALID_ARG, "layer %d has not been set", l);
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
     cudaStream_t st = (cudaStream_t)stream;
-    const int hd = c.head_dim, group = c.n_heads / c.n_kv_heads;
+    const int hd = c.head_dim, group = c.n_heads / c.n_kv_heads, lh = d->lh, lkv = d->lkv, lffn = c.ffn / c.tp_world;
     const nnq_dtype adt = (nnq_dtype)d->act_dt;
-    const size_t layer_cache = (size_t)c.n_kv_heads * c.max_seq * hd;
+    const size_t layer_cache = (size_t)lkv * c.max_seq * hd;
     const float scale = (float)(1.0 / sqrt((double)hd));
     const __nv_bfloat16 *embed = (const __nv_bfloat16 *)d->d_embed;
     for (int l = 0; l < c.n_layers; l++) {
@@ -506,10 +524,10 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
         const void *x3[3] = {d->d_xn, d->d_xn, d->d_xn};
         void *y3[3] = {d->d_q, d->d_k, d->d_v};
         if ((s = nnq_linear_batch(ctx, 3, w3, x3, adt, 1, nullptr, y3, NNQ_F32, st)) != NNQ_OK) return s;
-        launch_pdl(dec_qk_rope_kernel, dim3(c.n_heads + 2 * c.n_kv_heads), dim3(hd), st, d->d_q, d->d_k, d->d_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, d->d_state,
-                   c.rms_eps, d->d_qrot, d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, c.n_heads, c.n_kv_heads, hd, c.max_seq);
+        launch_pdl(dec_qk_rope_kernel, dim3(lh + 2 * lkv), dim3(hd), st, d->d_q, d->d_k, d->d_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, d->d_state,
+                   c.rms_eps, d->d_qrot, d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, lh, lkv, hd, c.max_seq);
         {
-            const dim3 ag(c.n_kv_heads, kAttnSplits);
+            const dim3 ag(lkv, kAttnSplits);
             const float *kc = d->d_kcache + l * layer_cache, *vc = d->d_vcache + l * layer_cache;
             switch (group) {
                 case 1: launch_pdl(dec_attn_kernel<1>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
@@ -519,15 +537,20 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
                 default: return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must be 1, 2, 4 or 8");
             }
         }
-        launch_pdl(dec_attn_combine_kernel, dim3(c.n_heads), dim3(128), st, d->d_part, d->d_attn, d->act_dt, hd);
-        if ((s = nnq_linear(ctx, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st)) != NNQ_OK) return s;
+        launch_pdl(dec_attn_combine_kernel, dim3(lh), dim3(128), st, d->d_part, d->d_attn, d->act_dt, hd);
+        // row-parallel products: with tensor parallelism the partial sums are exchanged inside the kernel
+        s = d->comm ? nnq_comm_linear(d->comm, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st)
+                    : nnq_linear(ctx, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st);
+        if (s != NNQ_OK) return s;
         launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, L.post_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
         const nnq_weight *w2[2] = {L.gate, L.up};
         const void *x2[2] = {d->d_xn, d->d_xn};
         void *y2[2] = {d->d_g, d->d_u};
         if ((s = nnq_linear_batch(ctx, 2, w2, x2, adt, 1, nullptr, y2, NNQ_F32, st)) != NNQ_OK) return s;
-        launch_pdl(dec_silu_mul_kernel, dim3((c.ffn + 255) / 256), dim3(256), st, d->d_g, d->d_u, d->d_mid, d->act_dt, c.ffn);
-        if ((s = nnq_linear(ctx, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st)) != NNQ_OK) return s;
+        launch_pdl(dec_silu_mul_kernel, dim3((lffn + 255) / 256), dim3(256), st, d->d_g, d->d_u, d->d_mid, d->act_dt, lffn);
+        s = d->comm ? nnq_comm_linear(d->comm, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st)
+                    : nnq_linear(ctx, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st);
+        if (s != NNQ_OK) return s;
         ctx->launches += 6;
     }
     launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, d->d_final_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);

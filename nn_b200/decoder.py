@@ -19,7 +19,8 @@ class _Config(ctypes.Structure):
     _fields_ = [("hidden", ctypes.c_int32), ("n_heads", ctypes.c_int32), ("n_kv_heads", ctypes.c_int32),
                 ("head_dim", ctypes.c_int32), ("ffn", ctypes.c_int32), ("n_layers", ctypes.c_int32),
                 ("vocab", ctypes.c_int32), ("max_seq", ctypes.c_int32), ("rms_eps", ctypes.c_float),
-                ("rope_theta", ctypes.c_double), ("act_dtype", ctypes.c_int32)]
+                ("rope_theta", ctypes.c_double), ("act_dtype", ctypes.c_int32), ("tp_rank", ctypes.c_int32),
+                ("tp_world", ctypes.c_int32)]
 
 
 @dataclass
@@ -35,6 +36,8 @@ class DecoderConfig:
     rms_eps: float = 1e-6
     rope_theta: float = 1e6
     act_dtype: int = api.BF16
+    tp_rank: int = 0
+    tp_world: int = 1
 
 
 class _DevArray:
@@ -48,7 +51,7 @@ class Decoder:
     def __init__(self, backend: api.Backend, cfg: DecoderConfig):
         self.backend, self.cfg = backend, cfg
         c = _Config(cfg.hidden, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.n_layers, cfg.vocab,
-                    cfg.max_seq, cfg.rms_eps, cfg.rope_theta, cfg.act_dtype)
+                    cfg.max_seq, cfg.rms_eps, cfg.rope_theta, cfg.act_dtype, cfg.tp_rank, cfg.tp_world)
         h = ctypes.c_void_p()
         backend.check(backend._lib.nnq_decoder_create(backend._ctx, ctypes.byref(c), ctypes.byref(h)))
         self._handle = h
@@ -65,6 +68,11 @@ class Decoder:
         self._keep.extend([embed_bf16, lm_head])
         self.backend.check(self.backend._lib.nnq_decoder_set_head(self._handle, embed_bf16.data_ptr(), self._ptr(final_norm),
                                                                   lm_head.handle()))
+
+    def set_comm(self, peer):
+        """Tensor parallel: the PeerComm whose slots carry the o / down exchanges (max_bytes >= 8 * hidden)."""
+        self._keep.append(peer)
+        self.backend.check(self.backend._lib.nnq_decoder_set_comm(self._handle, peer._handle))
 
     @staticmethod
     def _ptr(t):
@@ -95,7 +103,7 @@ class Decoder:
                                                                  ctypes.byref(tk)))
         c = self.cfg
         dev = torch.device("cuda", self.backend.device)
-        shape = (c.n_layers, c.n_kv_heads, c.max_seq, c.head_dim)
+        shape = (c.n_layers, c.n_kv_heads // c.tp_world, c.max_seq, c.head_dim)
         return (torch.as_tensor(_DevArray(k.value, shape, "<f4"), device=dev),
                 torch.as_tensor(_DevArray(v.value, shape, "<f4"), device=dev),
                 torch.as_tensor(_DevArray(lg.value, (c.vocab,), "<f4"), device=dev),
