@@ -311,6 +311,16 @@ def run_nnq(args, rank, world, local_rank):
     others = None
     if world == 1 and m == 1 and not args.no_others:
         others = other_configs(torch, backend, layers, gen, dev)
+    elif world > 1 and m == 1 and not args.no_others:
+        # tensor-parallel decode: the same shards, o / down exchanged inside the product kernel
+        peak_hbm, _ = _peaks()
+        dec = decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, tp=(rank, world), peer=peer)
+        if dec is not None:
+            t = torch.tensor([dec["ms_per_token"]], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dec["ms_per_token"] = float(t.item())
+            dec["tokens_per_s"] = 1e3 / dec["ms_per_token"]
+        others = {"qwen3_8b_decode_ctx2048": dec}
 
     # ---- end to end through the host entry point of the C ABI ----
     e2e = None
@@ -462,7 +472,7 @@ def other_configs(torch, backend, layers, gen, dev):
     return out
 
 
-def decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, prompt=2048, new_tokens=256):
+def decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, prompt=2048, new_tokens=256, tp=(0, 1), peer=None):
     """Batch-1 greedy decode of a Qwen3-8B-shaped model (the bench's 36 Q4_K layers, a Q6_K
     vocabulary projection, bf16 embedding, unit norms): 256 tokens from position 2048. The key /
     value caches of the 2048 earlier positions are filled with seeded random values, which stands
@@ -472,8 +482,10 @@ def decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, prompt=2048,
     from nn_b200.formats import QuantFormat
     if len(layers) != W.LAYERS:
         return None
-    cfg = decoder.DecoderConfig(max_seq=prompt + new_tokens + 8, act_dtype=api.BF16)
+    cfg = decoder.DecoderConfig(max_seq=prompt + new_tokens + 8, act_dtype=api.BF16, tp_rank=tp[0], tp_world=tp[1])
     dec = decoder.Decoder(backend, cfg)
+    if peer is not None:
+        dec.set_comm(peer)
     ones_h = torch.ones(cfg.hidden, device=dev)
     ones_d = torch.ones(cfg.head_dim, device=dev)
     for li, lw in enumerate(layers):
@@ -508,11 +520,12 @@ def decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, prompt=2048,
     sec = e0.elapsed_time(e1) * 1e-3 / new_tokens
     _, pos, steps = dec.state()
     ctx_mid = prompt + new_tokens // 2
-    weights = W.layer_bytes(1).weights * W.LAYERS + cfg.vocab * (cfg.hidden // 256) * 210
-    kv = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 4 * ctx_mid
-    out = {"tokens_per_s": 1.0 / sec, "ms_per_token": sec * 1e3, "new_tokens": new_tokens, "prompt_positions": prompt,
+    # per GPU: its shard of the layers and of the caches, and the whole (replicated) vocabulary projection
+    weights = W.layer_bytes(1).weights * W.LAYERS // tp[1] + cfg.vocab * (cfg.hidden // 256) * 210
+    kv = 2 * cfg.n_layers * (cfg.n_kv_heads // tp[1]) * cfg.head_dim * 4 * ctx_mid
+    out = {"tokens_per_s": 1.0 / sec, "tp": tp[1], "ms_per_token": sec * 1e3, "new_tokens": new_tokens, "prompt_positions": prompt,
            "kernels_per_token": int(per_token), "end_position": pos, "steps": steps,
-           "hbm_bytes_per_token": weights + kv, "gbs": (weights + kv) / sec / 1e9, "bound": "hbm",
+           "hbm_bytes_per_token_per_gpu": weights + kv, "gbs_per_gpu": (weights + kv) / sec / 1e9, "bound": "hbm",
            "frac": (weights + kv) / sec / 1e9 / peak_hbm, "kv_cache": "f32", "product_inputs": "bf16",
            "prompt": "key/value caches of the first 2048 positions filled with seeded random values"}
     dec.release()
