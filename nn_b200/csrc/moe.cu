@@ -369,7 +369,7 @@ static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
     s.count = (int *)take((size_t)m->e_local * 4);
     s.offset = (int *)take((size_t)(m->e_local + 1) * 4);
     s.rowtok = (int *)take(R * 4);
-    const int slices = m->layout == NNQ_MOE_KN_GPTOSS ? kMoeKnSplit : 1;   // partial sums per K slice
+    const int slices = m->layout == NNQ_MOE_KN_GPTOSS && !m->d_gu_tiled ? kMoeKnSplit : 1;   // partial sums per K slice (row kernel only)
     s.gu = (float *)take((size_t)R * 2 * m->inter * 4 * slices);
     s.h = (float *)take((size_t)R * m->inter * 4);
     s.o = (float *)take((size_t)R * m->hidden * 4 * slices);
@@ -412,7 +412,8 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
     const int E = m->e_local;
     if (m->d_gu_tiled) {
         GroupedArgs a = {first ? m->d_gu_tiled : m->d_dn_tiled, first ? m->gu_tile_stride : m->dn_tile_stride, b, x,
-                         DtypeOf<XT>::value, rowtok, s.offset, out, E, m->top_k, N, K, m->fmt, rows};
+                         DtypeOf<XT>::value, rowtok, s.offset, out, E, m->top_k, N, K, m->fmt, rows,
+                         m->layout == NNQ_MOE_KN_GPTOSS ? 1 : 0};
         launch_grouped(ctx, a, st);
         return;
     }
@@ -590,6 +591,24 @@ nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, i
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_bias, down_bias, (size_t)expert_count * hidden * 4, "down bias");
     // tiled copies for the grouped kernel
     static const char *env_tiled = getenv("NNQ_MOE_TILED");   // tuning aid: 0 keeps the row kernels
+    if (s == NNQ_OK && layout == NNQ_MOE_KN_GPTOSS && !(env_tiled && atoi(env_tiled) == 0)) {
+        // [E, K, N] tensors: tiles of the transposed products (rows = N)
+        const size_t gs = tiled_bytes_kn(2 * (int64_t)inter, hidden, nullptr);
+        const size_t ds = tiled_bytes_kn(hidden, inter, nullptr);
+        if (gs && ds) {
+            const size_t gu_e = gate_up_bytes / expert_count, gus_e = gate_up_scales_bytes / expert_count;
+            const size_t dn_e = down_bytes / expert_count, dns_e = down_scales_bytes / expert_count;
+            s = check_cuda(ctx, cudaMalloc(&m->d_gu_tiled, gs * expert_count), "cudaMalloc tiled experts");
+            if (s == NNQ_OK) s = check_cuda(ctx, cudaMalloc(&m->d_dn_tiled, ds * expert_count), "cudaMalloc tiled experts");
+            for (int e = 0; e < expert_count && s == NNQ_OK; e++) {
+                s = repack_kn_into(ctx, m->d_gu + e * gu_e, m->d_gu_scales + e * gus_e, 2 * (int64_t)inter, hidden, m->d_gu_tiled + e * gs);
+                if (s == NNQ_OK) s = repack_kn_into(ctx, m->d_dn + e * dn_e, m->d_dn_scales + e * dns_e, hidden, inter, m->d_dn_tiled + e * ds);
+            }
+            if (s == NNQ_OK) s = check_cuda(ctx, cudaDeviceSynchronize(), "expert repack");
+            m->gu_tile_stride = gs;
+            m->dn_tile_stride = ds;
+        }
+    }
     if (s == NNQ_OK && layout == NNQ_MOE_NK && !(env_tiled && atoi(env_tiled) == 0)) {
         const size_t gs = tiled_bytes_for(fmt, 2 * (int64_t)inter, hidden, nullptr);
         const size_t ds = tiled_bytes_for(fmt, hidden, inter, nullptr);

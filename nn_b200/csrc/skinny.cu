@@ -977,6 +977,55 @@ struct TileFmt<NNQ_MXFP4_SPLIT, SB> {
     }
 };
 
+// ---- MXFP4, nn-gptoss [K, N] layout (blocks of 32 along N, i.e. across the rows of a tile) ----
+// A tile (16 rows n x SB*32 k) lies inside one 32-wide block of n, so its scales depend on k only:
+// [0, 32 SB) E8M0 scale per k; then the code words as in the K-blocked MXFP4 tile. The scales are
+// applied to the activations (an exact power-of-two multiply of the bf16 pairs, e = 0 -> 2^-126),
+// the accumulators need no further scaling.
+template <int SB>
+struct TileFmt<NNQ_MXFP4_GPTOSS, SB> {
+    static constexpr int kBytes = 32 * SB + 256 * SB;
+    static constexpr int kElems = 32 * SB;
+    static __device__ __forceinline__ uint32_t scale_pair(uint32_t w, uint32_t sel) {   // two bytes -> bf16x2 2^(e-127)
+        return __vmaxu2(__byte_perm(w, 0u, sel) << 7, 0x00800080u);
+    }
+    static __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+        __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
+        return *reinterpret_cast<uint32_t *>(&r);
+    }
+    template <int NT, bool F32X>
+    static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *, const uint8_t *const (&xrow)[NT],
+                                                int koff, int lane, int g, int t, const MnConsts &K,
+                                                float (&y)[NT][4]) {
+        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint2 *cw = reinterpret_cast<const uint2 *>(stage + 32 * SB);
+#pragma unroll
+        for (int sb = 0; sb < SB; sb++) {
+            const uint2 q = cw[sb * 32 + lane];
+            const uint2 e8 = *reinterpret_cast<const uint2 *>(stage + sb * 32 + 8 * t);   // scales of k = 8t .. 8t+7
+            uint32_t A[4], A8[4];
+            TileFmt<NNQ_MXFP4_SPLIT, SB>::pairs(q.x, K, A);
+            TileFmt<NNQ_MXFP4_SPLIT, SB>::pairs(q.y, K, A8);
+            const uint32_t s0 = scale_pair(e8.x, 0x4140), s1 = scale_pair(e8.x, 0x4342);
+            const uint32_t s2 = scale_pair(e8.y, 0x4140), s3 = scale_pair(e8.y, 0x4342);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int e0 = koff + sb * 32 + 8 * t;
+                XB<F32X> xb = load_xb<F32X>(xrow[nt], e0, e0 + 4);
+                xb.hi = make_uint4(mul2(xb.hi.x, s0), mul2(xb.hi.y, s1), mul2(xb.hi.z, s2), mul2(xb.hi.w, s3));
+                if (F32X) xb.lo = make_uint4(mul2(xb.lo.x, s0), mul2(xb.lo.y, s1), mul2(xb.lo.z, s2), mul2(xb.lo.w, s3));
+                float c[4];
+                mma_x<F32X>(c, A[0], A8[0], A[1], A8[1], xb, 0, zero);
+                mma_x<F32X>(c, A[2], A8[2], A[3], A8[3], xb, 1, c);
+                y[nt][0] += c[0];
+                y[nt][1] += c[1];
+                y[nt][2] += c[2];
+                y[nt][3] += c[3];
+            }
+        }
+    }
+};
+
 template <int BYTES>
 __device__ __forceinline__ void issue_tile_n(uint32_t dst, const void *src, uint32_t bar, int pred) {
     asm volatile(
@@ -1501,6 +1550,55 @@ __global__ void repack_mxfp4_kernel(const uint8_t *__restrict__ raw, const uint8
     }
 }
 
+// nn-gptoss expert tensor [K, N] (codes [K, N/2], high nibble = even column; scales [K, N/32]) ->
+// tiles of the transposed product (rows = n). One thread per (n, block of 32 k).
+template <int SB>
+__global__ void repack_mxfp4_kn_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ scales,
+                                       uint8_t *__restrict__ tiled, int n, int k, int ktiles) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int kblocks = k / 32;
+    if (idx >= (int64_t)n * kblocks) return;
+    const int row = (int)(idx / kblocks), blk = (int)(idx % kblocks);
+    const int kt = blk / SB, sb = blk % SB;
+    constexpr int TB = 32 * SB + 256 * SB;
+    uint8_t *tile = tiled + ((int64_t)(row >> 4) * ktiles + kt) * TB;
+    const int r16 = row & 15, g = row & 7, upper = (row >> 3) & 1;
+    const int k0 = blk * 32;
+    if (r16 == 0)
+        for (int i = 0; i < 32; i++) tile[sb * 32 + i] = scales[(int64_t)(k0 + i) * (n / 32) + row / 32];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t byte = codes[(int64_t)(k0 + 8 * t + i) * (n / 2) + row / 2];
+            const uint32_t c = (row & 1) ? byte & 15u : byte >> 4;
+            word |= (c & 7u) << (4 * i);
+            word |= (c >> 3) << (4 * (i >> 1) + 3 + 16 * (i & 1));
+        }
+        reinterpret_cast<uint32_t *>(tile + 32 * SB + 256 * sb + 8 * (4 * g + t))[upper] = word;
+    }
+}
+
+size_t tiled_bytes_kn(int64_t n, int64_t k, int *sb_out) {
+    const int sb = k % 256 == 0 ? 8 : (k % 192 == 0 ? 6 : 0);
+    if (sb_out) *sb_out = sb;
+    if (sb == 0 || n <= 0 || n % 32 != 0 || n > (1 << 24) || k > (1 << 24)) return 0;
+    return (size_t)(n / 16) * (size_t)(k / (32 * sb)) * (size_t)(288 * sb);
+}
+
+nnq_status repack_kn_into(nnq_ctx *ctx, const uint8_t *d_codes, const uint8_t *d_scales, int64_t n, int64_t k, uint8_t *dst) {
+    int sb = 0;
+    if (tiled_bytes_kn(n, k, &sb) == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "no tiled layout for a [K, N] expert tensor with K = %lld, N = %lld", (long long)k, (long long)n);
+    const int64_t total = n * (k / 32);
+    const int grid = (int)((total + 255) / 256);
+    const int ktiles = (int)(k / (32 * sb));
+    if (sb == 8) repack_mxfp4_kn_kernel<8><<<grid, 256>>>(d_codes, d_scales, dst, (int)n, (int)k, ktiles);
+    else repack_mxfp4_kn_kernel<6><<<grid, 256>>>(d_codes, d_scales, dst, (int)n, (int)k, ktiles);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "repack launch");
+}
+
 static int tile_bytes_of(int fmt, int sb) {
     switch (fmt) {
         case NNQ_Q4_K: case NNQ_Q4_K_GGML: return TileFmt<NNQ_Q4_K>::kBytes;
@@ -1819,7 +1917,8 @@ static cudaError_t launch_grouped_x(const GroupedParams &P, bool f32x, int nt, i
 nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t stream) {
     if (a.experts < 1 || a.experts > kMoeMaxExperts) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad expert count %d", a.experts);
     int sb = 0;
-    if (tiled_bytes_for(a.fmt, a.n, a.k, &sb) == 0) return fail(ctx, NNQ_ERR_UNSUPPORTED, "no tiled layout for the grouped product");
+    if ((a.kn_gptoss ? tiled_bytes_kn(a.n, a.k, &sb) : tiled_bytes_for(a.fmt, a.n, a.k, &sb)) == 0)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "no tiled layout for the grouped product");
     GroupedParams P;
     memset(&P, 0, sizeof(P));
     P.tiled = a.tiled;
@@ -1839,13 +1938,19 @@ nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t strea
     const bool f32x = a.x_dt == NNQ_F32;
     // 16-row groups once the experts see 5 or more rows on average (bf16 activations only)
     const int nt = !f32x && a.max_rows >= 5 * (int64_t)a.experts ? 2 : 1;
-    const int smem_bytes = mn_plan(tile_bytes_of(a.fmt, sb), P.stages, nt).total;
+    const int smem_bytes = mn_plan(a.kn_gptoss ? 288 * sb : tile_bytes_of(a.fmt, sb), P.stages, nt).total;
     // every expert may end with a partly filled row group
     const int64_t max_units = (a.max_rows / (8 * nt) + a.experts) * P.row_tiles;
     int64_t grid = 2 * (int64_t)ctx->sm_count;
     if (grid > max_units) grid = max_units;
     if (grid < 1) grid = 1;
     cudaError_t e;
+    if (a.kn_gptoss) {
+        e = sb == 8 ? launch_grouped_x<NNQ_MXFP4_GPTOSS, 8>(P, f32x, nt, (int)grid, smem_bytes, stream)
+                    : launch_grouped_x<NNQ_MXFP4_GPTOSS, 6>(P, f32x, nt, (int)grid, smem_bytes, stream);
+        ctx->launches++;
+        return check_cuda(ctx, e, "grouped product launch");
+    }
     switch (layout_of(a.fmt)) {
         case kTiledQ4K: e = launch_grouped_x<NNQ_Q4_K, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
         case kTiledQ8_0: e = launch_grouped_x<NNQ_Q8_0, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;

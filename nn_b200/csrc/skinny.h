@@ -29,6 +29,11 @@ size_t tiled_bytes_for(int fmt, int64_t n, int64_t k, int *sb);
 nnq_status repack_into(nnq_ctx *ctx, int fmt, const uint8_t *d_raw, const uint8_t *d_scales, int64_t n, int64_t k,
                        uint8_t *dst);
 
+// The same for an nn-gptoss [K, N] MXFP4 expert tensor (blocks along N): tiles of the transposed
+// product, rows = n (a multiple of 32), scales per k inside a tile.
+size_t tiled_bytes_kn(int64_t n, int64_t k, int *sb);
+nnq_status repack_kn_into(nnq_ctx *ctx, const uint8_t *d_codes, const uint8_t *d_scales, int64_t n, int64_t k, uint8_t *dst);
+
 // Expert products of a mixture-of-experts block over tiled expert weights: routed rows sorted by
 // expert (offset[e] .. offset[e+1]), out[r, :] = x[row source of r, :] * W_e^T + bias_e.
 struct GroupedArgs {
@@ -44,6 +49,7 @@ struct GroupedArgs {
     int64_t n, k;
     int fmt;
     int64_t max_rows;         // upper bound of offset[experts]
+    int kn_gptoss;            // 1: tiles built from nn-gptoss [K, N] expert tensors (scales along N)
 };
 nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t stream);
 
