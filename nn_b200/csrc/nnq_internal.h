@@ -30,7 +30,7 @@ __host__ __device__ inline Geometry geometry(int fmt) {
 }
 
 // Tiled ("T16") device layouts used by the skinny kernels; kNone = raw blocks only.
-enum TiledLayout { kTiledNone = 0, kTiledQ4K = 1, kTiledQ8_0 = 2, kTiledQ6K = 3, kTiledMxfp4 = 4 };
+enum TiledLayout { kTiledNone = 0, kTiledQ4K = 1, kTiledQ8_0 = 2, kTiledQ6K = 3, kTiledMxfp4 = 4, kTiledQ4_0 = 5, kTiledQ4_1 = 6 };
 
 }  // namespace nnq
 

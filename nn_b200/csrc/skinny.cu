@@ -920,6 +920,74 @@ struct TileFmt<NNQ_Q6_K, 8> {
     }
 };
 
+// ---- Q4_0 / Q4_1: 32-blocks with an fp16 scale (and an fp16 minimum) ----
+// Tile: [0,256) fp16 d[row][block] (Q4_1: then 256 B fp16 m[row][block]); then per block 256 B,
+// lane l = 4g + t 8 B = {T16 word row g, T16 word row g+8} of elements 8t..8t+7.
+//   Q4_0  y += d * (c - 136 s)      (code q, value d (q - 8))
+//   Q4_1  y += d * (c - 128 s) + m * s
+template <int FMT>
+struct TileQ4x {
+    static constexpr bool kMin = FMT == NNQ_Q4_1;
+    static constexpr int kBytes = (kMin ? 512 : 256) + 2048;
+    static constexpr int kElems = 256;
+    template <int NT, bool F32X>
+    static __device__ __forceinline__ void tile(const uint8_t *stage, float4 *, const uint8_t *const (&xrow)[NT],
+                                                int koff, int lane, int g, int t, const MnConsts &K,
+                                                float (&y)[NT][4]) {
+        const uint4 *st = reinterpret_cast<const uint4 *>(stage);
+        const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const uint4 dg = st[g], dg8 = st[8 + g];
+        const uint32_t dgw[4] = {dg.x, dg.y, dg.z, dg.w}, dg8w[4] = {dg8.x, dg8.y, dg8.z, dg8.w};
+        uint32_t mgw[4] = {0, 0, 0, 0}, mg8w[4] = {0, 0, 0, 0};
+        if (kMin) {
+            const uint4 mg = st[16 + g], mg8 = st[24 + g];
+            mgw[0] = mg.x; mgw[1] = mg.y; mgw[2] = mg.z; mgw[3] = mg.w;
+            mg8w[0] = mg8.x; mg8w[1] = mg8.y; mg8w[2] = mg8.z; mg8w[3] = mg8.w;
+        }
+        const uint2 *cw = reinterpret_cast<const uint2 *>(stage + (kMin ? 512 : 256));
+#pragma unroll
+        for (int sb = 0; sb < 8; sb++) {
+            const uint2 q = cw[sb * 32 + lane];
+            const float2 d2 = __half22float2(*reinterpret_cast<const __half2 *>(&dgw[sb >> 1]));
+            const float2 d28 = __half22float2(*reinterpret_cast<const __half2 *>(&dg8w[sb >> 1]));
+            const float d = sb & 1 ? d2.y : d2.x, d8 = sb & 1 ? d28.y : d28.x;
+            float mn = 0.0f, mn8 = 0.0f;
+            if (kMin) {
+                const float2 m2 = __half22float2(*reinterpret_cast<const __half2 *>(&mgw[sb >> 1]));
+                const float2 m28 = __half22float2(*reinterpret_cast<const __half2 *>(&mg8w[sb >> 1]));
+                mn = sb & 1 ? m2.y : m2.x;
+                mn8 = sb & 1 ? m28.y : m28.x;
+            }
+            uint32_t L[4], L8[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                L[i] = and_or(q.x >> (4 * i), K.m4, K.k128);
+                L8[i] = and_or(q.y >> (4 * i), K.m4, K.k128);
+            }
+            // per unit of the activation sum: -136 d (Q4_0), -128 d + m (Q4_1)
+            const float e = kMin ? fmaf(-128.0f, d, mn) : -136.0f * d, e8 = kMin ? fmaf(-128.0f, d8, mn8) : -136.0f * d8;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const int e0 = koff + sb * 32 + 8 * t;
+                const XB<F32X> xb = load_xb<F32X>(xrow[nt], e0, e0 + 4);
+                float c[4], sx[4];
+                mma_x<F32X>(c, L[0], L8[0], L[1], L8[1], xb, 0, zero);
+                mma_x<F32X>(c, L[2], L8[2], L[3], L8[3], xb, 1, c);
+                mma_x<F32X>(sx, K.ones, K.ones, K.ones, K.ones, xb, 0, zero);
+                mma_x<F32X>(sx, K.ones, K.ones, K.ones, K.ones, xb, 1, sx);
+                y[nt][0] = fmaf(d, c[0], fmaf(e, sx[0], y[nt][0]));
+                y[nt][1] = fmaf(d, c[1], fmaf(e, sx[1], y[nt][1]));
+                y[nt][2] = fmaf(d8, c[2], fmaf(e8, sx[2], y[nt][2]));
+                y[nt][3] = fmaf(d8, c[3], fmaf(e8, sx[3], y[nt][3]));
+            }
+        }
+    }
+};
+template <>
+struct TileFmt<NNQ_Q4_0, 8> : TileQ4x<NNQ_Q4_0> {};
+template <>
+struct TileFmt<NNQ_Q4_1, 8> : TileQ4x<NNQ_Q4_1> {};
+
 // ---- MXFP4 (K-blocked layouts: 17-byte blocks, or codes [N, K/2] + scales [N, K/32]) ----
 // Tile = 16 rows x SB blocks of 32 (SB = 8, or 6 when K is a multiple of 192 but not of 256, as
 // the 2880-wide gpt-oss experts): [0,128) E8M0 scale bytes, row r at 8r; then per block 256 B,
@@ -1519,6 +1587,34 @@ __global__ void repack_q6_k_kernel(const uint8_t *__restrict__ raw, uint8_t *__r
 
 nnq_status skinny_init(nnq_ctx *) { return NNQ_OK; }
 
+// Q4_0 (18-byte blocks: d, 16 code bytes) / Q4_1 (20-byte blocks: d, m, 16 code bytes); element 2j is
+// the low nibble of byte j, element 2j + 1 the high nibble (the reference's order). One thread per
+// (row, block of 32).
+template <bool MIN>
+__global__ void repack_q4x_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ tiled, int n, int ktiles) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)n * ktiles * 8) return;
+    constexpr int BS = MIN ? 20 : 18, TB = (MIN ? 512 : 256) + 2048;
+    const int row = (int)(idx / (ktiles * 8)), blk = (int)(idx % (ktiles * 8));
+    const int kb = blk >> 3, sb = blk & 7;
+    const uint8_t *b = raw + idx * BS;
+    uint8_t *tile = tiled + ((int64_t)(row >> 4) * ktiles + kb) * TB;
+    const int r16 = row & 15, g = row & 7, upper = (row >> 3) & 1;
+    *reinterpret_cast<uint16_t *>(tile + r16 * 16 + sb * 2) = (uint16_t)(b[0] | (b[1] << 8));
+    if (MIN) *reinterpret_cast<uint16_t *>(tile + 256 + r16 * 16 + sb * 2) = (uint16_t)(b[2] | (b[3] << 8));
+    const uint8_t *qs = b + (MIN ? 4 : 2);
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        uint32_t e[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int el = 8 * t + i;
+            e[i] = (el & 1) ? (uint32_t)(qs[el >> 1] >> 4) : (uint32_t)(qs[el >> 1] & 15u);
+        }
+        reinterpret_cast<uint32_t *>(tile + (MIN ? 512 : 256) + 256 * sb + 8 * (4 * g + t))[upper] = t16_word(e);
+    }
+}
+
 // MXFP4 -> tiles. CORE: 17-byte blocks (scale, 16 code bytes); SPLIT: codes [N, K/2] and scales
 // [N, K/32] apart. Low nibble = even element in both. One thread per (row, block of 32).
 template <int SB>
@@ -1604,6 +1700,8 @@ static int tile_bytes_of(int fmt, int sb) {
         case NNQ_Q4_K: case NNQ_Q4_K_GGML: return TileFmt<NNQ_Q4_K>::kBytes;
         case NNQ_Q8_0: return TileFmt<NNQ_Q8_0>::kBytes;
         case NNQ_Q6_K: return TileFmt<NNQ_Q6_K>::kBytes;
+        case NNQ_Q4_0: return TileFmt<NNQ_Q4_0>::kBytes;
+        case NNQ_Q4_1: return TileFmt<NNQ_Q4_1>::kBytes;
         case NNQ_MXFP4_CORE: case NNQ_MXFP4_SPLIT: return 128 + 256 * sb;
         default: return 0;
     }
@@ -1612,7 +1710,7 @@ static int tile_bytes_of(int fmt, int sb) {
 // Sub-blocks per tile row for this format and K; 0 = no tiled layout.
 static int tile_sb_of(int fmt, int64_t k) {
     switch (fmt) {
-        case NNQ_Q4_K: case NNQ_Q4_K_GGML: case NNQ_Q8_0: case NNQ_Q6_K: return k % 256 == 0 ? 8 : 0;
+        case NNQ_Q4_K: case NNQ_Q4_K_GGML: case NNQ_Q8_0: case NNQ_Q6_K: case NNQ_Q4_0: case NNQ_Q4_1: return k % 256 == 0 ? 8 : 0;
         case NNQ_MXFP4_CORE: case NNQ_MXFP4_SPLIT: return k % 256 == 0 ? 8 : (k % 192 == 0 ? 6 : 0);
         default: return 0;
     }
@@ -1642,6 +1740,8 @@ nnq_status repack_into(nnq_ctx *ctx, int fmt, const uint8_t *d_raw, const uint8_
         case NNQ_Q4_K_GGML: repack_q4k_kernel<true><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
         case NNQ_Q8_0: repack_q8_0_kernel<<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
         case NNQ_Q6_K: repack_q6_k_kernel<<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+        case NNQ_Q4_0: repack_q4x_kernel<false><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
+        case NNQ_Q4_1: repack_q4x_kernel<true><<<grid, 256>>>(d_raw, d, (int)n, ktiles); break;
         default:
             if (sb == 8) repack_mxfp4_kernel<8><<<grid, 256>>>(d_raw, d_scales, d, (int)n, ktiles, split);
             else repack_mxfp4_kernel<6><<<grid, 256>>>(d_raw, d_scales, d, (int)n, ktiles, split);
@@ -1680,6 +1780,8 @@ static int layout_of(int fmt) {
         case NNQ_Q8_0: return kTiledQ8_0;
         case NNQ_Q6_K: return kTiledQ6K;
         case NNQ_MXFP4_CORE: case NNQ_MXFP4_SPLIT: return kTiledMxfp4;
+        case NNQ_Q4_0: return kTiledQ4_0;
+        case NNQ_Q4_1: return kTiledQ4_1;
         default: return kTiledNone;
     }
 }
@@ -1861,6 +1963,8 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
         if (layout == kTiledQ4K) e = launch_mn_fmt<NNQ_Q4_K>(P, nt, f32x, grid, smem_bytes, stream);
         else if (layout == kTiledQ8_0) e = launch_mn_fmt<NNQ_Q8_0>(P, nt, f32x, grid, smem_bytes, stream);
         else if (layout == kTiledQ6K) e = launch_mn_fmt<NNQ_Q6_K>(P, nt, f32x, grid, smem_bytes, stream);
+        else if (layout == kTiledQ4_0) e = launch_mn_fmt<NNQ_Q4_0>(P, nt, f32x, grid, smem_bytes, stream);
+        else if (layout == kTiledQ4_1) e = launch_mn_fmt<NNQ_Q4_1>(P, nt, f32x, grid, smem_bytes, stream);
         else if (tile_sb == 8) e = launch_mn_fmt<NNQ_MXFP4_SPLIT, 8>(P, nt, f32x, grid, smem_bytes, stream);
         else e = launch_mn_fmt<NNQ_MXFP4_SPLIT, 6>(P, nt, f32x, grid, smem_bytes, stream);
         ctx->launches++;
@@ -1955,6 +2059,8 @@ nnq_status launch_grouped(nnq_ctx *ctx, const GroupedArgs &a, cudaStream_t strea
         case kTiledQ4K: e = launch_grouped_x<NNQ_Q4_K, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
         case kTiledQ8_0: e = launch_grouped_x<NNQ_Q8_0, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
         case kTiledQ6K: e = launch_grouped_x<NNQ_Q6_K, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
+        case kTiledQ4_0: e = launch_grouped_x<NNQ_Q4_0, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
+        case kTiledQ4_1: e = launch_grouped_x<NNQ_Q4_1, 8>(P, f32x, nt, (int)grid, smem_bytes, stream); break;
         default:
             e = sb == 8 ? launch_grouped_x<NNQ_MXFP4_SPLIT, 8>(P, f32x, nt, (int)grid, smem_bytes, stream)
                         : launch_grouped_x<NNQ_MXFP4_SPLIT, 6>(P, f32x, nt, (int)grid, smem_bytes, stream);

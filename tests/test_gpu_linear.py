@@ -34,7 +34,7 @@ def _run(fmt, n, k, m, x_bf16, y_bf16, with_bias, seed=1, path=api.PATH_AUTO):
         t.backend.set_path(api.PATH_AUTO)
     y32, y64, mag = P.oracle_linear(fmt, w, sc, x, bias, n, k)
     got = y.float().cpu().numpy()
-    tiled = (fmt in (Q.Q4_K, Q.Q4_K_GGML, Q.Q8_0, Q.Q6_K) and k % 256 == 0) or (
+    tiled = (fmt in (Q.Q4_K, Q.Q4_K_GGML, Q.Q8_0, Q.Q6_K, Q.Q4_0, Q.Q4_1) and k % 256 == 0) or (
         fmt in (Q.MXFP4_CORE, Q.MXFP4_SPLIT) and (k % 256 == 0 or k % 192 == 0))
     skinny = tiled and 1 <= m <= 16 and (x_bf16 or m <= 8 or (m == 1 and fmt in (Q.Q4_K, Q.Q4_K_GGML)))
     tensor_path = path == api.PATH_TENSOR or (
@@ -65,7 +65,7 @@ def test_token_column_skinny_kernel(fmt, m, n, k):
     _run(fmt, n, k, m, x_bf16=True, y_bf16=(m % 2 == 0), with_bias=(m % 3 == 0), seed=300 + m, path=api.PATH_SKINNY)
 
 
-@pytest.mark.parametrize("fmt", [Q.Q8_0, Q.Q6_K, Q.Q4_K])
+@pytest.mark.parametrize("fmt", [Q.Q8_0, Q.Q6_K, Q.Q4_K, Q.Q4_0, Q.Q4_1])
 @pytest.mark.parametrize("m,x_bf16", [(1, True), (1, False), (2, True), (5, False), (8, True), (8, False), (9, True), (16, True)])
 @pytest.mark.parametrize("n,k", [(200, 2048), (64, 4096), (1030, 2304), (40, 512)])
 def test_token_column_kernel_formats(fmt, m, x_bf16, n, k):
