@@ -330,17 +330,27 @@ def run_nnq(args, rank, world, local_rank):
         hy = {n: torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for n in (W.HIDDEN, W.KV_DIM, W.FFN)}
         h2d = d2h = 0
 
+        VPh = ctypes.c_void_p
+        host_calls = []   # one nnq_linear_batch_host call per launch group of a layer
+        for li in range(args.layers):
+            for group in W.GROUPS:
+                cnt = len(group)
+                k = proj[group[0]][2]
+                wh = (VPh * cnt)(*[layers[li][n_].handle().value for n_ in group])
+                xp = (VPh * cnt)(*[hx[k].data_ptr()] * cnt)
+                houts = [torch.empty(m, proj[n_][1], dtype=torch.bfloat16).pin_memory() for n_ in group] if li == 0 else host_calls[len(host_calls) - len(W.GROUPS)][4]
+                yp = (VPh * cnt)(*[t.data_ptr() for t in houts])
+                host_calls.append((cnt, wh, xp, yp, houts, m * k * 2, sum(m * proj[n_][1] * 2 for n_ in group)))
+
         def host_step():
             nonlocal h2d, d2h
             h2d = d2h = 0
-            for li in range(args.layers):
-                for name, n, k in W.PROJECTIONS:
-                    st = lib.nnq_linear_host(ctx, layers[li][name].handle(), hx[k].data_ptr(), api.BF16, m, None,
-                                             hy[n].data_ptr(), api.BF16)
-                    if st != 0:
-                        backend.check(st)
-                    h2d += m * k * 2
-                    d2h += m * n * 2
+            for cnt, wh, xp, yp, _, bi, bo in host_calls:
+                st = lib.nnq_linear_batch_host(ctx, cnt, wh, xp, api.BF16, m, None, yp, api.BF16)
+                if st != 0:
+                    backend.check(st)
+                h2d += bi
+                d2h += bo
 
         host_step()
         e_steps = max(1, min(args.steps, 5))
@@ -349,8 +359,9 @@ def run_nnq(args, rank, world, local_rank):
             host_step()
         dt = (time.perf_counter() - t0) / e_steps
         e2e = {"value": algo_step / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": dt * 1e3, "calls_per_step": args.layers * len(W.PROJECTIONS),
-               "api": "nnq_linear_host (pinned host activations in, host outputs out, per projection)"}
+               "ms_per_step": dt * 1e3, "calls_per_step": len(host_calls),
+               "api": "nnq_linear_batch_host (host activations in, host outputs out, one synchronous call per group "
+                      "of projections that share their input: 4 per layer)"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

@@ -215,6 +215,16 @@ NNQ_API nnq_status nnq_linear_batch(nnq_ctx *ctx, int count, const nnq_weight *c
                             const float *const *bias_dev, void *const *y_dev, nnq_dtype y_dt,
                             void *stream);
 
+/* nnq_linear_batch with host-resident tensors: the activations (each distinct pointer once), the
+ * biases and the outputs go through the context's pinned staging buffers with one copy in each
+ * direction and one synchronisation for the whole batch (count <= 16). Products that pass the same
+ * x_host pointer share their device copy and, on the skinny path, one launch: the q / k / v or
+ * gate / up projections of a layer called as the reference's consecutive Linear::forward calls on
+ * one input (crates/nn-qwen3/src/layers.rs:40-47,94-110). */
+NNQ_API nnq_status nnq_linear_batch_host(nnq_ctx *ctx, int count, const nnq_weight *const *w,
+                                         const void *const *x_host, nnq_dtype x_dt, int64_t m,
+                                         const float *const *bias_host, void *const *y_host, nnq_dtype y_dt);
+
 /* ---- mixture-of-experts block ------------------------------------------------------ */
 
 /* Storage of the expert weight tensors.

@@ -41,6 +41,8 @@ SIGNATURES = {
     "nnq_linear_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int]),
     "nnq_linear_batch": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int64,
                                  ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_void_p]),
+    "nnq_linear_batch_host": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int64,
+                                      ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int]),
     "nnq_launch_count": (c_int64, [c_void_p]),
     "nnq_comm_create": (c_int, [c_void_p, c_int, c_int, c_size_t, ctypes.POINTER(c_void_p)]),
     "nnq_comm_get_handle": (c_int, [c_void_p, c_void_p]),

@@ -472,8 +472,40 @@ def quantized_linear(input, weight, bias=None, out_dtype=None):
     return y
 
 
+def _linear_batch_host(inputs, weights, biases):
+    """Host tensors (numpy f32): one staged copy in, one out, one synchronisation for the batch."""
+    count = len(weights)
+    b = weights[0].backend
+    xs = [np.ascontiguousarray(x, dtype=np.float32) for x in inputs]
+    # inputs given as the same array object share their device copy (and one launch)
+    for i in range(count):
+        for j in range(i):
+            if inputs[i] is inputs[j]:
+                xs[i] = xs[j]
+    m = math.prod(xs[0].shape[:-1])
+    ys = []
+    for x, w in zip(xs, weights):
+        n, k = w.dims()
+        if x.shape[-1] != k:
+            raise ShapeMismatch(f"input last dim {x.shape[-1]} != weight in_features {k}")
+        ys.append(np.empty(tuple(x.shape[:-1]) + (n,), np.float32))
+    VP = ctypes.c_void_p * count
+    wh = VP(*[w.handle().value for w in weights])
+    xp = VP(*[x.ctypes.data for x in xs])
+    yp = VP(*[y.ctypes.data for y in ys])
+    bp, keep = None, []
+    if biases is not None:
+        keep = [np.ascontiguousarray(bb, dtype=np.float32) if bb is not None else None for bb in biases]
+        bp = VP(*[(t.ctypes.data if t is not None else None) for t in keep])
+    b.check(b._lib.nnq_linear_batch_host(b._ctx, count, wh, xp, F32, m, bp, yp, F32))
+    return ys
+
+
 def linear_batch(inputs, weights, biases=None, out_dtype=None):
-    """Several products in one call (same M and dtype): q/k/v or gate/up of a decoder layer."""
+    """Several products in one call (same M and dtype): q/k/v or gate/up of a decoder layer.
+    numpy inputs take the host entry point (nnq_linear_batch_host) and return numpy arrays."""
+    if isinstance(inputs[0], np.ndarray):
+        return _linear_batch_host(inputs, weights, biases)
     torch = _torch()
     count = len(weights)
     b = weights[0].backend

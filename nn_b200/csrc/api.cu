@@ -58,6 +58,18 @@ static nnq_status validate_weight(nnq_ctx *ctx, int fmt, const void *data, size_
     return NNQ_OK;
 }
 
+// Waits for everything queued on the context's host stream. The event is polled: a blocking
+// stream synchronisation costs an interrupt round trip, which dominates a call that moves a few KB.
+static nnq_status wait_host_stream(nnq_ctx *ctx) {
+    nnq_status s = check_cuda(ctx, cudaEventRecord(ctx->host_event, ctx->host_stream), "event record");
+    if (s != NNQ_OK) return s;
+    for (;;) {
+        cudaError_t e = cudaEventQuery(ctx->host_event);
+        if (e == cudaSuccess) return NNQ_OK;
+        if (e != cudaErrorNotReady) return check_cuda(ctx, e, "sync");
+    }
+}
+
 static nnq_status finish_weight(nnq_ctx *ctx, nnq_weight *w) {
     // Build the tiled copy when a skinny kernel exists for this format and shape.
     return build_tiled(ctx, w);
@@ -123,6 +135,7 @@ nnq_status nnq_init(int device, nnq_ctx **out) {
     if (s == NNQ_OK) s = check_cuda(ctx, cudaMalloc(&ctx->d_status, sizeof(int)), "cudaMalloc status");
     if (s == NNQ_OK) s = check_cuda(ctx, cudaMemset(ctx->d_status, 0, sizeof(int)), "cudaMemset status");
     if (s == NNQ_OK) s = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking), "stream");
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaEventCreateWithFlags(&ctx->host_event, cudaEventDisableTiming), "event");
     if (s == NNQ_OK) s = skinny_init(ctx);
     if (s != NNQ_OK) {
         nnq_destroy(ctx);
@@ -147,6 +160,7 @@ void nnq_destroy(nnq_ctx *ctx) {
     cudaFree(ctx->d_stage_x);
     cudaFree(ctx->d_stage_y);
     cudaFree(ctx->d_stage_bias);
+    if (ctx->host_event) cudaEventDestroy(ctx->host_event);
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
     cudaGetLastError();
     delete ctx;
@@ -457,9 +471,82 @@ nnq_status nnq_linear_host(nnq_ctx *ctx, const nnq_weight *w, const void *x_host
     if (s == NNQ_OK) s = linear_dispatch(ctx, w, ctx->d_stage_x, x_dt, m, bias_dev, ctx->d_stage_y, y_dt, st);
     if (s != NNQ_OK) return s;
     s = check_cuda(ctx, cudaMemcpyAsync(ctx->h_stage_y, ctx->d_stage_y, yb, cudaMemcpyDeviceToHost, st), "d2h");
-    if (s == NNQ_OK) s = check_cuda(ctx, cudaStreamSynchronize(st), "sync");
+    if (s == NNQ_OK) s = wait_host_stream(ctx);
     if (s != NNQ_OK) return s;
     memcpy(y_host, ctx->h_stage_y, yb);
+    return NNQ_OK;
+}
+
+nnq_status nnq_linear_batch_host(nnq_ctx *ctx, int count, const nnq_weight *const *w, const void *const *x_host,
+                                 nnq_dtype x_dt, int64_t m, const float *const *bias_host, void *const *y_host,
+                                 nnq_dtype y_dt) {
+    if (!ctx) return NNQ_ERR_INVALID_ARG;
+    constexpr int kMaxBatch = 16;
+    if (count < 0 || count > kMaxBatch || (count && (!w || !x_host || !y_host))) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad batch arguments");
+    if (m < 0) return fail(ctx, NNQ_ERR_INVALID_ARG, "negative row count");
+    if ((int)x_dt < 0 || x_dt > NNQ_BF16 || (int)y_dt < 0 || y_dt > NNQ_BF16) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown dtype");
+    if (count == 0 || m == 0) return NNQ_OK;
+    nnq_status s = set_device(ctx);
+    if (s != NNQ_OK) return s;
+    // layout of the staging buffers: every distinct activation pointer once, then the biases;
+    // products that share their host activations also share the device copy (and one launch)
+    size_t x_off[kMaxBatch], b_off[kMaxBatch], y_off[kMaxBatch];
+    size_t in_bytes = 0, out_bytes = 0;
+    for (int i = 0; i < count; i++) {
+        if (!w[i]) return fail(ctx, NNQ_ERR_NOT_QUANTIZED, "weight tensor is not quantized");
+        if (!x_host[i] || !y_host[i]) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL host buffer");
+        int same = -1;
+        for (int j = 0; j < i; j++)
+            if (x_host[j] == x_host[i] && w[j]->k == w[i]->k) same = j;
+        if (same >= 0) {
+            x_off[i] = x_off[same];
+        } else {
+            x_off[i] = in_bytes;
+            in_bytes += ((size_t)m * w[i]->k * elem_size(x_dt) + 255) & ~(size_t)255;
+        }
+        y_off[i] = out_bytes;
+        out_bytes += ((size_t)m * w[i]->n * elem_size(y_dt) + 255) & ~(size_t)255;
+    }
+    for (int i = 0; i < count; i++) {
+        b_off[i] = in_bytes;
+        if (bias_host && bias_host[i]) in_bytes += ((size_t)w[i]->n * 4 + 255) & ~(size_t)255;
+    }
+    size_t cap_hx = ctx->stage_x_bytes, cap_dx = ctx->stage_x_bytes;
+    if (in_bytes > ctx->stage_x_bytes) {
+        if ((s = grow(ctx, &ctx->h_stage_x, &cap_hx, in_bytes, true)) != NNQ_OK) return s;
+        if ((s = grow(ctx, &ctx->d_stage_x, &cap_dx, in_bytes, false)) != NNQ_OK) return s;
+        ctx->stage_x_bytes = cap_hx < cap_dx ? cap_hx : cap_dx;
+    }
+    size_t cap_hy = ctx->stage_y_bytes, cap_dy = ctx->stage_y_bytes;
+    if (out_bytes > ctx->stage_y_bytes) {
+        if ((s = grow(ctx, &ctx->h_stage_y, &cap_hy, out_bytes, true)) != NNQ_OK) return s;
+        if ((s = grow(ctx, &ctx->d_stage_y, &cap_dy, out_bytes, false)) != NNQ_OK) return s;
+        ctx->stage_y_bytes = cap_hy < cap_dy ? cap_hy : cap_dy;
+    }
+    const void *xd[kMaxBatch];
+    const float *bd[kMaxBatch];
+    void *yd[kMaxBatch];
+    for (int i = 0; i < count; i++) {
+        bool first = true;
+        for (int j = 0; j < i; j++) first = first && x_off[j] != x_off[i];
+        if (first) memcpy((uint8_t *)ctx->h_stage_x + x_off[i], x_host[i], (size_t)m * w[i]->k * elem_size(x_dt));
+        xd[i] = (uint8_t *)ctx->d_stage_x + x_off[i];
+        bd[i] = nullptr;
+        if (bias_host && bias_host[i]) {
+            memcpy((uint8_t *)ctx->h_stage_x + b_off[i], bias_host[i], (size_t)w[i]->n * 4);
+            bd[i] = (const float *)((uint8_t *)ctx->d_stage_x + b_off[i]);
+        }
+        yd[i] = (uint8_t *)ctx->d_stage_y + y_off[i];
+    }
+    cudaStream_t st = ctx->host_stream;
+    s = check_cuda(ctx, cudaMemcpyAsync(ctx->d_stage_x, ctx->h_stage_x, in_bytes, cudaMemcpyHostToDevice, st), "h2d");
+    if (s != NNQ_OK) return s;
+    s = nnq_linear_batch(ctx, count, w, xd, x_dt, m, bd, yd, y_dt, st);
+    if (s != NNQ_OK) return s;
+    s = check_cuda(ctx, cudaMemcpyAsync(ctx->h_stage_y, ctx->d_stage_y, out_bytes, cudaMemcpyDeviceToHost, st), "d2h");
+    if (s == NNQ_OK) s = wait_host_stream(ctx);
+    if (s != NNQ_OK) return s;
+    for (int i = 0; i < count; i++) memcpy(y_host[i], (uint8_t *)ctx->h_stage_y + y_off[i], (size_t)m * w[i]->n * elem_size(y_dt));
     return NNQ_OK;
 }
 

@@ -57,6 +57,7 @@ struct nnq_ctx {
     float *d_stage_bias;
     size_t stage_x_bytes, stage_y_bytes, stage_bias_bytes;
     cudaStream_t host_stream;
+    cudaEvent_t host_event;   // completion of a host entry point's last copy (polled: lower latency than a blocking wait)
     long long launches;
     char last_error[512];
 };

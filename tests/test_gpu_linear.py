@@ -253,6 +253,25 @@ def test_batch_call_matches_single_calls():
         w.release()
 
 
+def test_batch_host_entry_point_matches_device_calls():
+    """nnq_linear_batch_host: shared and distinct host activations, a bias, mixed shapes."""
+    k = 2048
+    shapes = [(256, k), (64, k), (130, 4096)]
+    ws = []
+    for i, (n, kk) in enumerate(shapes):
+        w, _ = F.gen_weight(Q.Q4_K, 90 + i, n, kk)
+        ws.append(api.from_quantized(w, Q.Q4_K, [n, kk]))
+    xa = F.gen_activations(95, 1, k, bf16=True)
+    xb = F.gen_activations(96, 1, 4096, bf16=True)
+    bias = (F.Stream(97).normal(64) * 0.5).astype(np.float32)
+    ys = api.linear_batch([xa, xa, xb], ws, biases=[None, bias, None])
+    for y, w, x, bb in zip(ys, ws, (xa, xa, xb), (None, bias, None)):
+        assert isinstance(y, np.ndarray)
+        want = api.quantized_linear(torch.from_numpy(x).to(DEV), w, torch.from_numpy(bb).to(DEV) if bb is not None else None)
+        assert float(np.max(np.abs(y - want.cpu().numpy()))) <= 1e-5 * float(want.abs().max())
+        w.release()
+
+
 @pytest.mark.parametrize("m", [4, 12])
 def test_batch_call_token_column_kernel(m):
     # three projections sharing their activations go out as one launch of the token-column kernel
