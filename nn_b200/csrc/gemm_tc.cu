@@ -3,9 +3,11 @@
 //
 // One CTA computes a (128 * MT) x 128 output tile (MT = 1, 2 or 4 accumulators of 128 x 128 f32
 // in tensor memory). Per 64-wide k step
+//   * the (128 * MT) x 64 bf16 activation tile arrives by TMA (cp.async.bulk.tensor.2d through a
+//     tensor map of x with 128-byte swizzle, issued by one thread, counted on the stage's "full"
+//     barrier; rows beyond M are zero-filled); f32 activations are converted by the producers;
 //   * 8 producer warps dequantize the 128 x 64 weight tile to bf16 (f32 decode, the bit-exact
-//     one, then round-to-nearest-even) and copy / convert the (128 * MT) x 64 activation tile,
-//     both written to shared memory in the K-major 128-byte-swizzled layout tcgen05 reads;
+//     one, then round-to-nearest-even) into the same K-major 128-byte-swizzled layout;
 //   * one thread issues 4 * MT tcgen05.mma (M 128, N 128, K 16, bf16 x bf16 -> f32) from shared
 //     memory descriptors into the accumulators and commits them onto the stage's "empty" barrier.
 // The larger MT, the more activation rows reuse each dequantized weight tile (the dequantization,
@@ -14,10 +16,13 @@
 // Weights are rounded to bf16, so results carry the 1e-2 tolerance of the tensor path.
 // Every barrier wait is bounded; on a timeout the CTA records it, skips the rest and still frees
 // its tensor memory.
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include "decode.cuh"
 #include "gemm_tc.h"
+#include <string.h>
+
 #include "sync.cuh"
 
 namespace nnq {
@@ -61,6 +66,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void mbar_expect_tx_only(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// one 64 x 128 box (k0 .. k0+63, rows r0 .. r0+127) of the activation tensor -> swizzled shared tile
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int k0, int r0, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(k0), "r"(r0), "r"(bar) : "memory");
+}
+
 // byte offset of 16-byte chunk c (0..7) of row r (0..127) inside a swizzled 128 x 128-byte tile
 __device__ __forceinline__ uint32_t swz(int r, int c) {
     return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
@@ -71,11 +86,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
-template <int FMT, int MT, typename XT>
+template <int FMT, int MT, typename XT, bool TMAX>
 __global__ void __launch_bounds__(kTcThreads, 1)
-gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscales, const XT *__restrict__ x,
-               const float *__restrict__ bias, void *__restrict__ y, int64_t M, int64_t N, int64_t K, int y_dt,
-               int stages, float *__restrict__ partials, int *status) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscales,
+               const XT *__restrict__ x, const float *__restrict__ bias, void *__restrict__ y, int64_t M, int64_t N,
+               int64_t K, int y_dt, int stages, float *__restrict__ partials, int *status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles (the dynamic window is not guaranteed to start on one)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -139,7 +154,7 @@ gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscale
                 wreg[c] = make_uint4(pack_bf16(wv[8 * c], wv[8 * c + 1]), pack_bf16(wv[8 * c + 2], wv[8 * c + 3]),
                                      pack_bf16(wv[8 * c + 4], wv[8 * c + 5]), pack_bf16(wv[8 * c + 6], wv[8 * c + 7]));
 #pragma unroll
-            for (int i = 0; i < kAChunks; i++) {
+            for (int i = 0; i < (TMAX ? 0 : kAChunks); i++) {
                 const int r = (tid >> 3) + 32 * i;
                 uint4 v = make_uint4(0, 0, 0, 0);
                 const int64_t row = m0 + r;
@@ -162,10 +177,18 @@ gemm_tc_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscale
             if (!ok) break;
             uint8_t *stage = smem + (size_t)slot * kStageBytes;
             uint8_t *bt = stage + MT * kTcTileBytes;
+            if (TMAX && tid == 0) {
+                // the stage is free: let the activation tiles of this k step stream in while the
+                // weight tile is written
+                mbar_expect_tx_only(full_s + 8 * slot, MT * kTcTileBytes);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+                    tma_load_2d(smem_u32(stage + mt * kTcTileBytes), &xmap, (kb_lo + kb) * kTcBK, (int)m0 + mt * 128, full_s + 8 * slot);
+            }
 #pragma unroll
             for (int c = 0; c < 4; c++) *reinterpret_cast<uint4 *>(bt + swz(brow, bhalf * 4 + c)) = wreg[c];
 #pragma unroll
-            for (int i = 0; i < kAChunks; i++) {
+            for (int i = 0; i < (TMAX ? 0 : kAChunks); i++) {
                 const int r = (tid >> 3) + 32 * i;
                 *reinterpret_cast<uint4 *>(stage + (r >> 7) * kTcTileBytes + swz(r & 127, ac)) = areg[i];
             }
@@ -273,6 +296,50 @@ bool gemm_tc_supported(const nnq_weight *w, int64_t m) {
     return w && w->d_raw && m >= 1 && w->k >= kTcBK && w->k % kTcBK == 0 && w->n >= 1;
 }
 
+// Tensor map of the bf16 activations [M, K]: boxes of 64 x 128 elements, 128-byte swizzle, zero fill
+// beyond M. Returns false when the driver entry point is not available (the producers then stage
+// the activations themselves).
+static bool make_x_map(const TcArgs &a, CUtensorMap *map) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+        cudaGetLastError();
+    }
+    if (!fn || ((uintptr_t)a.x & 15u) || (a.k * 2) % 16) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTcBK, 128u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(a.x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int FMT, int MT, typename XT, bool TMAX>
+static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, int *status, int ksplit, float *partials, int stages,
+                              int smem_bytes, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, MT, XT, TMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)((a.m + 128 * MT - 1) / (128 * MT)), (unsigned)ksplit);
+    gemm_tc_kernel<FMT, MT, XT, TMAX><<<grid, kTcThreads, smem_bytes, stream>>>(
+        map, a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages,
+        ksplit > 1 ? partials : nullptr, status);
+    return cudaGetLastError();
+}
+
 template <int FMT, int MT, typename XT>
 static cudaError_t launch_one(const TcArgs &a, int *status, int ksplit, float *partials, cudaStream_t stream) {
     const int stage_bytes = (MT + 1) * kTcTileBytes;
@@ -282,19 +349,13 @@ static cudaError_t launch_one(const TcArgs &a, int *status, int ksplit, float *p
     const int nkb = (int)(a.k / kTcBK);
     if (stages > nkb / ksplit) stages = nkb / ksplit > 0 ? nkb / ksplit : 1;
     const int smem_bytes = stages * stage_bytes + 1024;
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, MT, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
-    dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)((a.m + 128 * MT - 1) / (128 * MT)), (unsigned)ksplit);
-    gemm_tc_kernel<FMT, MT, XT><<<grid, kTcThreads, smem_bytes, stream>>>(
-        a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages,
-        ksplit > 1 ? partials : nullptr, status);
-    cudaError_t e = cudaGetLastError();
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    cudaError_t e;
+    if (sizeof(XT) == 2 && make_x_map(a, &map))
+        e = launch_cfg<FMT, MT, XT, sizeof(XT) == 2>(a, map, status, ksplit, partials, stages, smem_bytes, stream);
+    else
+        e = launch_cfg<FMT, MT, XT, false>(a, map, status, ksplit, partials, stages, smem_bytes, stream);
     if (e != cudaSuccess || ksplit == 1) return e;
     const int64_t total = a.m * a.n;
     gemm_tc_reduce_kernel<<<(int)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048), 256, 0, stream>>>(
