@@ -21,6 +21,7 @@
 
 #include "decode.cuh"
 #include "gemm_tc.h"
+#include <stdlib.h>
 #include <string.h>
 
 #include "sync.cuh"
@@ -367,14 +368,18 @@ template <int FMT>
 static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, int ksplit, float *partials, cudaStream_t stream) {
     const bool f32 = a.x_dt == NNQ_F32;
     // Rows per CTA: the more rows share a decoded weight tile the less decode work, but the grid
-    // must still cover the machine. Take the largest tile that leaves at least one CTA per SM.
+    // must still cover the machine. Take the largest tile that leaves at least one CTA per two SMs.
     // (Decoding the whole weight to bf16 first and multiplying afterwards was measured slower than
     // decoding per tile even at M = 4096: the tile pipeline, not the decode, is the limit.)
     const int64_t ntiles = (a.n + 127) / 128;
     auto ctas = [&](int mt) { return ntiles * ((a.m + 128 * mt - 1) / (128 * mt)); };
     int mt = 1;
-    if (a.m > 256 && ctas(4) >= sm_count) mt = 4;
-    else if (a.m > 128 && ctas(2) >= sm_count) mt = 2;
+    // (measured with the activation tiles arriving by TMA: half a wave of the largest tile still beats
+    // a full wave of smaller ones, because every CTA decodes its weight tile for itself)
+    if (a.m > 256 && 2 * ctas(4) >= sm_count) mt = 4;
+    else if (a.m > 128 && 2 * ctas(2) >= sm_count) mt = 2;
+    static const char *env_mt = getenv("NNQ_TC_MT");   // tuning aid
+    if (env_mt && (atoi(env_mt) == 1 || atoi(env_mt) == 2 || atoi(env_mt) == 4)) mt = atoi(env_mt);
     if (mt != 1) ksplit = 1;
     if (mt == 1) return f32 ? launch_one<FMT, 1, float>(a, status, ksplit, partials, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, ksplit, partials, stream);
     if (mt == 2) return f32 ? launch_one<FMT, 2, float>(a, status, 1, nullptr, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, 1, nullptr, stream);
