@@ -80,10 +80,8 @@ struct Decode<NNQ_Q8_0> {
 
 template <>
 struct Decode<NNQ_Q4_K> {
-    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
-        const uint8_t *b = w + (c >> 3) * 144;  // 144-byte blocks are 16-byte aligned
-        int j = (int)(c & 7);
-        uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+    // sub-block j of a super-block whose 16-byte header and 16 quant bytes are already in registers
+    static __device__ __forceinline__ void chunk_regs(const uint4 &hdr, const uint4 &q, int j, float *o) {
         float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
         float dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
         // S[0..3] = hdr.y bytes, S[4..7] = hdr.z bytes, S[8..11] = hdr.w bytes
@@ -93,7 +91,6 @@ struct Decode<NNQ_Q4_K> {
                       (((hdr.w >> (16 + 8 * (j >> 2) + 2 * (j & 3))) & 3u) << 4);
         float s = __fmul_rn(d, (float)sc);
         float m = __fmul_rn(dmin, (float)mn);
-        uint4 q = __ldg(reinterpret_cast<const uint4 *>(b + 16 + 16 * j));
         uint32_t qw[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int v = 0; v < 4; v++) {
@@ -104,6 +101,13 @@ struct Decode<NNQ_Q4_K> {
                 o[8 * v + 2 * i + 1] = __fsub_rn(__fmul_rn(s, (float)(byte >> 4)), m);
             }
         }
+    }
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + (c >> 3) * 144;  // 144-byte blocks are 16-byte aligned
+        int j = (int)(c & 7);
+        uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+        uint4 q = __ldg(reinterpret_cast<const uint4 *>(b + 16 + 16 * j));
+        chunk_regs(hdr, q, j, o);
     }
 };
 

@@ -135,17 +135,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
         const int brow = tid & 127, bhalf = tid >> 7;   // weight tile: row and which 32 of the 64 k
         int slot = 0;
         uint32_t phase = 0;
-        // Software pipeline: the tile data of step kb + 1 is fetched and decoded into registers
-        // right after step kb has been handed to the tensor core, so that the global-memory latency
-        // runs under the MMAs and under the wait for a free stage.
+        // Software pipeline: the tile data of step kb + 1 is decoded into registers right after step kb
+        // has been handed to the tensor core, so that the work runs under the MMAs and under the wait
+        // for a free stage. For Q4_K the raw bytes are loaded one step earlier still (two steps
+        // ahead of their use), so that the decode never waits for global memory.
         constexpr int kAChunks = (128 * MT * 8) / (kTcProducerWarps * 32);   // 16-byte activation chunks per thread
         uint4 wreg[4];
         uint4 areg[kAChunks];
         const int ac = tid & 7;
+        constexpr bool kSplitLoad = FMT == NNQ_Q4_K;
+        uint4 raw_h = make_uint4(0, 0, 0, 0), raw_q = make_uint4(0, 0, 0, 0);
+        auto load_raw = [&](int kb) {
+            if (kSplitLoad && n0 + brow < N) {
+                const int64_t c = (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf;
+                const uint8_t *b = w + (c >> 3) * 144;
+                raw_h = __ldg(reinterpret_cast<const uint4 *>(b));
+                raw_q = __ldg(reinterpret_cast<const uint4 *>(b + 16 + 16 * (int)(c & 7)));
+            }
+        };
         auto fetch = [&](int kb) {
             float wv[32];
             if (n0 + brow < N) {
-                Decode<FMT>::chunk(w, wscales, (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf, wv);
+                if (kSplitLoad) Decode<NNQ_Q4_K>::chunk_regs(raw_h, raw_q, (kb * 2 + bhalf) & 7, wv);
+                else Decode<FMT>::chunk(w, wscales, (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf, wv);
             } else {
 #pragma unroll
                 for (int i = 0; i < 32; i++) wv[i] = 0.0f;
@@ -172,7 +184,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
                 areg[i] = v;
             }
         };
+        load_raw(kb_lo);
         fetch(kb_lo);
+        if (nkb > 1) load_raw(kb_lo + 1);
         for (int kb = 0; kb < nkb && ok; kb++) {
             if (kb >= stages) ok = mbar_wait_fast(empty_s + 8 * slot, phase ^ 1u);
             if (!ok) break;
@@ -200,7 +214,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
                 slot = 0;
                 phase ^= 1u;
             }
-            if (kb + 1 < nkb) fetch(kb_lo + kb + 1);
+            if (kb + 1 < nkb) {
+                fetch(kb_lo + kb + 1);
+                if (kb + 2 < nkb) load_raw(kb_lo + kb + 2);
+            }
         }
         // ---------------- epilogue ----------------
         if (ok) ok = mbar_wait_fast(acc_s, 0);
