@@ -271,8 +271,10 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     const bool f32x = x_dt == NNQ_F32;
     int ctas_per_sm = 0;
     const int layout = jobs[0].w->tiled_layout;
-    static const char *env_tc = getenv("NNQ_SKINNY_TOKCOL");  // tuning aid: token-column kernel at M = 1 too
-    const bool token_columns = m > 1 || layout != kTiledQ4K || (env_tc && atoi(env_tc) == 1 && !f32x);
+    static const char *env_tc = getenv("NNQ_SKINNY_TOKCOL");  // tuning aid: token-column kernel at M = 1 for launches of up to this many row tiles
+    int64_t job_tiles = 0;
+    for (int i = 0; i < count; i++) job_tiles += (jobs[i].w->n + 15) / 16;
+    const bool token_columns = m > 1 || layout != kTiledQ4K || (env_tc && !f32x && !fr && job_tiles <= atoi(env_tc));
     if (!token_columns) pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
     else P.stages = 2;
     if (fr && ctas_per_sm > 2) ctas_per_sm = 2;   // register budget of the fused variant
