@@ -87,11 +87,19 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+// Grouped launches (expert products): rows sorted by expert, blockIdx.y numbers the row tiles of
+// all experts (expert-major); offsets == NULL means a plain product.
+struct TcGroup {
+    const int *offsets;
+    int experts;
+    size_t w_stride, s_stride;
+};
+
 template <int FMT, int MT, typename XT, bool TMAX>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscales,
                const XT *__restrict__ x, const float *__restrict__ bias, void *__restrict__ y, int64_t M, int64_t N,
-               int64_t K, int y_dt, int stages, float *__restrict__ partials, int *status) {
+               int64_t K, int y_dt, int stages, float *__restrict__ partials, int *status, const TcGroup grp) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles (the dynamic window is not guaranteed to start on one)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -102,7 +110,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t n0 = (int64_t)blockIdx.x * 128;
-    const int64_t m0 = (int64_t)blockIdx.y * 128 * MT;
+    int64_t m0 = (int64_t)blockIdx.y * 128 * MT;
+    if (grp.offsets) {
+        // which expert this row tile belongs to; row tiles beyond the last expert have nothing to do
+        __shared__ int gsel[3];
+        if (tid == 0) {
+            int q = (int)blockIdx.y, e = -1, begin = 0, end = 0;
+            for (int i = 0; i < grp.experts; i++) {
+                const int lo = grp.offsets[i], hi = grp.offsets[i + 1];
+                const int tiles = (hi - lo + 128 * MT - 1) / (128 * MT);
+                if (q < tiles) {
+                    e = i;
+                    begin = lo + q * 128 * MT;
+                    end = hi;
+                    break;
+                }
+                q -= tiles;
+            }
+            gsel[0] = e;
+            gsel[1] = begin;
+            gsel[2] = end;
+        }
+        __syncthreads();
+        if (gsel[0] < 0) return;
+        m0 = gsel[1];
+        M = gsel[2];                    // rows of this expert end here: later rows are not stored
+        w += (size_t)gsel[0] * grp.w_stride;
+        if (wscales) wscales += (size_t)gsel[0] * grp.s_stride;
+        if (bias) bias += (size_t)gsel[0] * N;
+    }
     // this CTA's share of the k steps (gridDim.z slices of K; partial sums go to `partials`)
     const int nkb_all = (int)(K / kTcBK);
     const int kb_lo = (int)(((long long)blockIdx.z * nkb_all) / gridDim.z);
@@ -342,7 +378,7 @@ static bool make_x_map(const TcArgs &a, CUtensorMap *map) {
 
 template <int FMT, int MT, typename XT, bool TMAX>
 static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, int *status, int ksplit, float *partials, int stages,
-                              int smem_bytes, cudaStream_t stream) {
+                              int smem_bytes, cudaStream_t stream, const TcGroup &grp = TcGroup{nullptr, 0, 0, 0}, int grid_y = 0) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -351,10 +387,10 @@ static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, int *stat
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)((a.m + 128 * MT - 1) / (128 * MT)), (unsigned)ksplit);
+    dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)(grid_y ? grid_y : (a.m + 128 * MT - 1) / (128 * MT)), (unsigned)ksplit);
     gemm_tc_kernel<FMT, MT, XT, TMAX><<<grid, kTcThreads, smem_bytes, stream>>>(
         map, a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages,
-        ksplit > 1 ? partials : nullptr, status);
+        ksplit > 1 ? partials : nullptr, status, grp);
     return cudaGetLastError();
 }
 
@@ -401,6 +437,49 @@ static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, int ks
     if (mt == 1) return f32 ? launch_one<FMT, 1, float>(a, status, ksplit, partials, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, ksplit, partials, stream);
     if (mt == 2) return f32 ? launch_one<FMT, 2, float>(a, status, 1, nullptr, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, 1, nullptr, stream);
     return f32 ? launch_one<FMT, 4, float>(a, status, 1, nullptr, stream) : launch_one<FMT, 4, __nv_bfloat16>(a, status, 1, nullptr, stream);
+}
+
+template <int FMT, int MT>
+static cudaError_t launch_grouped_mt(const TcGroupArgs &g, int *status, cudaStream_t stream) {
+    TcArgs a = {g.w, g.scales, g.x_bf16, g.bias, g.y, g.rows_upper, g.n, g.k, g.fmt, NNQ_BF16, NNQ_F32};
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    if (!make_x_map(a, &map)) return cudaErrorNotSupported;
+    const int stage_bytes = (MT + 1) * kTcTileBytes;
+    int stages = MT == 4 ? 2 : (MT == 2 ? 2 : 3);
+    const int nkb = (int)(g.k / kTcBK);
+    if (stages > nkb) stages = nkb;
+    const TcGroup grp = {g.offsets, g.experts, g.w_stride, g.s_stride};
+    // every expert may end with a partly filled row tile
+    const int grid_y = (int)(g.rows_upper / (128 * MT)) + g.experts;
+    return launch_cfg<FMT, MT, __nv_bfloat16, true>(a, map, status, 1, nullptr, stages, stages * stage_bytes + 1024, stream, grp, grid_y);
+}
+
+template <int FMT>
+static cudaError_t launch_grouped_fmt(const TcGroupArgs &g, int *status, cudaStream_t stream) {
+    const int64_t avg = g.rows_upper / (g.experts > 0 ? g.experts : 1);
+    if (avg >= 384) return launch_grouped_mt<FMT, 4>(g, status, stream);
+    if (avg >= 160) return launch_grouped_mt<FMT, 2>(g, status, stream);
+    return launch_grouped_mt<FMT, 1>(g, status, stream);
+}
+
+nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStream_t stream) {
+    if (g.k < kTcBK || g.k % kTcBK || g.experts < 1 || g.rows_upper < 1) return fail(ctx, NNQ_ERR_UNSUPPORTED, "grouped tensor product: unsupported shape");
+    cudaError_t e;
+    switch (g.fmt) {
+        case NNQ_Q4_0: e = launch_grouped_fmt<NNQ_Q4_0>(g, ctx->d_status, stream); break;
+        case NNQ_Q4_1: e = launch_grouped_fmt<NNQ_Q4_1>(g, ctx->d_status, stream); break;
+        case NNQ_Q8_0: e = launch_grouped_fmt<NNQ_Q8_0>(g, ctx->d_status, stream); break;
+        case NNQ_Q4_K: e = launch_grouped_fmt<NNQ_Q4_K>(g, ctx->d_status, stream); break;
+        case NNQ_Q4_K_GGML: e = launch_grouped_fmt<NNQ_Q4_K_GGML>(g, ctx->d_status, stream); break;
+        case NNQ_Q6_K: e = launch_grouped_fmt<NNQ_Q6_K>(g, ctx->d_status, stream); break;
+        case NNQ_MXFP4_CORE: e = launch_grouped_fmt<NNQ_MXFP4_CORE>(g, ctx->d_status, stream); break;
+        case NNQ_MXFP4_SPLIT: e = launch_grouped_fmt<NNQ_MXFP4_SPLIT>(g, ctx->d_status, stream); break;
+        case NNQ_MXFP4_GPTOSS: e = launch_grouped_fmt<NNQ_MXFP4_GPTOSS>(g, ctx->d_status, stream); break;
+        default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", g.fmt);
+    }
+    ctx->launches++;
+    return check_cuda(ctx, e, "grouped tensor-core GEMM launch");
 }
 
 nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {

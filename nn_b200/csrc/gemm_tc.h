@@ -14,6 +14,24 @@ struct TcArgs {
     int fmt, x_dt, y_dt;
 };
 
+// Grouped variant for the expert products of a mixture-of-experts block: the rows of x are sorted
+// by expert (device-side offsets[e] .. offsets[e+1]), expert e multiplies its rows with the weight
+// at w + e * w_stride (scales + e * s_stride) and adds bias + e * n. x is bf16 [rows_upper, k]
+// (rows beyond offsets[experts] are never stored), y is f32 [rows_upper, n].
+struct TcGroupArgs {
+    const uint8_t *w, *scales;
+    size_t w_stride, s_stride;
+    const void *x_bf16;
+    const float *bias;      // [experts][n] or NULL
+    float *y;
+    const int *offsets;     // device, [experts + 1]
+    int experts;
+    int64_t rows_upper;     // upper bound of offsets[experts] (allocation size of x and y in rows)
+    int64_t n, k;
+    int fmt;
+};
+nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &a, cudaStream_t stream);
+
 // K must be a multiple of 64 (one 128-byte swizzle row of bf16 per stage).
 bool gemm_tc_supported(const nnq_weight *w, int64_t m);
 nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream);

@@ -19,6 +19,7 @@
 #include "decode.cuh"
 #include <stdlib.h>
 
+#include "gemm_tc.h"
 #include "moe.h"
 #include "skinny.h"
 
@@ -302,7 +303,8 @@ moe_nk_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict__ scal
 
 // h[r, j] = clamp(silu(gu[r, j]), -limit, limit) * gu[r, I + j]   (gate = first half, up = second half)
 __global__ void moe_swiglu_kernel(const float *__restrict__ gu, float *__restrict__ h, const int *__restrict__ offset,
-                                  int E, int inter, float limit, int slices, size_t slice_stride) {
+                                  int E, int inter, float limit, int slices, size_t slice_stride,
+                                  __nv_bfloat16 *__restrict__ h_bf16) {
     const int64_t total = (int64_t)offset[E] * inter;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int64_t r = i / inter, j = i % inter;
@@ -314,7 +316,18 @@ __global__ void moe_swiglu_kernel(const float *__restrict__ gu, float *__restric
         float s = g / (1.0f + expf(-g));
         s = fminf(fmaxf(s, -limit), limit);
         h[i] = s * u;
+        if (h_bf16) h_bf16[i] = __float2bfloat16_rn(s * u);   // input of the tensor-core second product
     }
+}
+
+// xg[r, :] = bf16(x[token of routed row r, :]): the gathered input of the tensor-core first product
+template <typename XT>
+__global__ void moe_gather_bf16_kernel(const XT *__restrict__ x, const int *__restrict__ rowtok, int top_k,
+                                       const int *__restrict__ offset, int E, int H, __nv_bfloat16 *__restrict__ xg) {
+    const int r = blockIdx.x;
+    if (r >= offset[E]) return;
+    const XT *src = x + (size_t)(rowtok[r] / top_k) * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) xg[(size_t)r * H + j] = __float2bfloat16_rn(ld_act<XT>(src, j));
 }
 
 // y[t, :] = sum over the token's experts, in expert-index order, of weight * o[row, :]
@@ -350,12 +363,22 @@ __global__ void moe_combine_kernel(const float *__restrict__ o, const int *__res
 struct MoeScratch {
     int *idx, *pos, *count, *offset, *rowtok;
     float *wt, *gu, *h, *o;
+    __nv_bfloat16 *xg, *hb;     // bf16 inputs of the tensor-core products (prefill-sized calls only)
     int slices;                 // K slices whose partial sums gu / o hold (1 = complete sums)
     size_t gu_stride, o_stride; // floats between slices
     size_t bytes;
 };
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Prefill-sized calls on [N, K] expert weights go through the grouped tcgen05 product: from 64 routed
+// rows per local expert on average (below that the weights are streamed once per 16 rows by the
+// grouped token-column kernel, which is HBM-bound and wins).
+static bool moe_tensor_mode(const nnq_moe *m, int64_t T) {
+    static const char *env = getenv("NNQ_MOE_TENSOR");   // tuning aid: 0 keeps the token-column kernel
+    if (env && atoi(env) == 0) return false;
+    return m->layout == NNQ_MOE_NK && m->hidden % 64 == 0 && m->inter % 64 == 0 && T * m->top_k >= 64 * (int64_t)m->n_experts;   // per expert of the whole block: shards of one block agree
+}
 
 // Carves the scratch buffer; with base == NULL only the size is computed.
 static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
@@ -373,6 +396,9 @@ static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
     s.gu = (float *)take((size_t)R * 2 * m->inter * 4 * slices);
     s.h = (float *)take((size_t)R * m->inter * 4);
     s.o = (float *)take((size_t)R * m->hidden * 4 * slices);
+    const bool tensor = moe_tensor_mode(m, T);
+    s.xg = tensor ? (__nv_bfloat16 *)take((size_t)R * m->hidden * 2) : nullptr;
+    s.hb = tensor ? (__nv_bfloat16 *)take((size_t)R * m->inter * 2) : nullptr;
     s.slices = slices;
     s.gu_stride = (size_t)R * 2 * m->inter;
     s.o_stride = (size_t)R * m->hidden;
@@ -410,6 +436,14 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
     const uint8_t *sc = first ? m->d_gu_scales : m->d_dn_scales;
     const float *b = first ? m->d_gu_bias : m->d_dn_bias;
     const int E = m->e_local;
+    if (s.xg) {
+        // prefill-sized: grouped tcgen05 product over bf16 inputs in routed order
+        Geometry g = geometry(m->fmt);
+        const size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
+        TcGroupArgs a = {d, sc, eb, es, first ? (const void *)s.xg : (const void *)s.hb, b, out, s.offset, E, rows, N, K, m->fmt};
+        launch_gemm_tc_grouped(ctx, a, st);
+        return;
+    }
     if (m->d_gu_tiled) {
         GroupedArgs a = {first ? m->d_gu_tiled : m->d_dn_tiled, first ? m->gu_tile_stride : m->dn_tile_stride, b, x,
                          DtypeOf<XT>::value, rowtok, s.offset, out, E, m->top_k, N, K, m->fmt, rows,
@@ -469,9 +503,13 @@ static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
     moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
+    if (s.xg) {
+        moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, m->top_k, s.offset, m->e_local, m->hidden, s.xg);
+        ctx->launches++;
+    }
     launch_product<XT>(ctx, m, true, x, s.rowtok, s, s.gu, total, st);
     int64_t hi = (int64_t)total * m->inter;
-    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride);
+    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
     launch_product<float>(ctx, m, false, s.h, nullptr, s, s.o, total, st);
     moe_combine_kernel<<<dim3((unsigned)T, T < 1024 ? 4 : 1), 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
     ctx->launches += 7;
@@ -517,9 +555,13 @@ static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, 
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
     moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
     moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
+    if (s.xg) {
+        moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, m->top_k, s.offset, m->e_local, m->hidden, s.xg);
+        ctx->launches++;
+    }
     launch_product<XT>(ctx, m, true, x, s.rowtok, s, s.gu, total, st);
     int64_t hi = (int64_t)total * m->inter;
-    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride);
+    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
     launch_product<float>(ctx, m, false, s.h, nullptr, s, s.o, total, st);
     moe_combine_kernel<<<dim3((unsigned)T, T < 1024 ? 4 : 1), 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
     ctx->launches += 8;

@@ -271,10 +271,14 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     const bool f32x = x_dt == NNQ_F32;
     int ctas_per_sm = 0;
     const int layout = jobs[0].w->tiled_layout;
-    static const char *env_tc = getenv("NNQ_SKINNY_TOKCOL");  // tuning aid: token-column kernel at M = 1 for launches of up to this many row tiles
+    // One token of bf16 activations on few row tiles (one wave of the token-column kernel, e.g. the
+    // 4096-row o / down projections): the token-column kernel has no activation staging after the
+    // dependency wait and wins by a few percent; larger launches keep the M = 1 kernel.
+    static const char *env_tc = getenv("NNQ_SKINNY_TOKCOL");  // tuning aid: the row-tile limit of that rule
     int64_t job_tiles = 0;
     for (int i = 0; i < count; i++) job_tiles += (jobs[i].w->n + 15) / 16;
-    const bool token_columns = m > 1 || layout != kTiledQ4K || (env_tc && !f32x && !fr && job_tiles <= atoi(env_tc));
+    const int64_t tokcol_limit = env_tc ? atoi(env_tc) : 2 * ctx->sm_count;
+    const bool token_columns = m > 1 || layout != kTiledQ4K || (!f32x && !fr && job_tiles <= tokcol_limit);
     if (!token_columns) pick_stages(P.kblocks, f32x, &P.stages, &ctas_per_sm);
     else P.stages = 2;
     if (fr && ctas_per_sm > 2) ctas_per_sm = 2;   // register budget of the fused variant

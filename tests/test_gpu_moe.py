@@ -59,6 +59,22 @@ def test_moe_forward_matches_oracle(layout, fmt, T):
     blk.release()
 
 
+@pytest.mark.parametrize("fmt", [Q.MXFP4_SPLIT, Q.Q4_K])
+def test_prefill_sized_batch_takes_the_tensor_core_path(fmt):
+    """From 64 routed rows per expert on, [N, K] experts run the grouped tcgen05 product (bf16
+    operands: the 1e-2 bar of the tensor path); ragged expert loads, rows not a multiple of 128."""
+    E, H, I, k, T = 8, 256, 256, 4, 333
+    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(moe.LAYOUT_NK, fmt, E, H, I, 77)
+    x = F.gen_activations(78, T, H, bf16=True)
+    blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, moe.LAYOUT_NK, fmt, gu, gus, bgu, dn, dns, bd)
+    y = blk(torch.from_numpy(x).to(DEV)).cpu().numpy()
+    blk.backend.device_status()
+    y_ref, _, _ = orc.moe_forward(x, rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
+    assert np.all(np.isfinite(y))
+    assert np.max(np.abs(y - y_ref)) / np.max(np.abs(y_ref)) <= 1e-2
+    blk.release()
+
+
 @pytest.mark.parametrize("layout,fmt,T", [(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS, 5), (moe.LAYOUT_NK, Q.MXFP4_SPLIT, 5),
                                           (moe.LAYOUT_NK, Q.MXFP4_SPLIT, 23)])
 def test_gptoss_shape_decode_batch(layout, fmt, T):
