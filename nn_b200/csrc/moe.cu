@@ -21,6 +21,7 @@
 
 #include "gemm_tc.h"
 #include "moe.h"
+#include "pdl.cuh"
 #include "skinny.h"
 
 namespace nnq {
@@ -48,6 +49,7 @@ template <typename XT>
 __global__ void __launch_bounds__(256)
 moe_router_kernel(const XT *__restrict__ x, const float *__restrict__ rw, const float *__restrict__ rb,
                   int T, int H, int E, int top_k, int *__restrict__ idx, float *__restrict__ wt) {
+    pdl_prologue();
     extern __shared__ float xs[];          // the token's activations as f32, then E logits
     float *logits = xs + H;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -142,6 +144,54 @@ moe_group_kernel(const int *__restrict__ idx, int total, int *__restrict__ count
         __syncthreads();
     }
     if (pass == 0 && threadIdx.x == 0) count[el] = base;
+}
+
+// The same grouping for decode-sized calls (total <= kGroupSmallMax assignments) in one CTA:
+// warp w lists the assignments of experts w, w + 8, ... in flat order (ballot compaction), the
+// counts are scanned in shared memory, then every warp writes its experts' rows.
+constexpr int kGroupSmallMax = 2048;
+
+__global__ void __launch_bounds__(256)
+moe_group_small_kernel(const int *__restrict__ idx, int total, int *__restrict__ count, int *__restrict__ offset,
+                       int *__restrict__ rowtok, int *__restrict__ pos, int e_begin, int e_local) {
+    pdl_prologue();
+    __shared__ int cnt[kMaxExperts], off[kMaxExperts + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int el = warp; el < e_local; el += 8) {
+        int c = 0;
+        for (int start = 0; start < total; start += 32) {
+            const int i = start + lane;
+            c += __popc(__ballot_sync(0xFFFFFFFFu, i < total && idx[i] == e_begin + el));
+        }
+        if (lane == 0) cnt[el] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < e_local; e++) {
+            off[e] = acc;
+            count[e] = cnt[e];
+            offset[e] = acc;
+            acc += cnt[e];
+        }
+        off[e_local] = acc;
+        offset[e_local] = acc;
+    }
+    __syncthreads();
+    for (int el = warp; el < e_local; el += 8) {
+        int base = off[el];
+        for (int start = 0; start < total; start += 32) {
+            const int i = start + lane;
+            const bool hit = i < total && idx[i] == e_begin + el;
+            const unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
+            if (hit) {
+                const int row = base + __popc(ballot & ((1u << lane) - 1u));
+                rowtok[row] = i;
+                pos[i] = row;
+            }
+            base += __popc(ballot);
+        }
+    }
 }
 
 __global__ void moe_scan_kernel(const int *__restrict__ count, int *__restrict__ offset, int E) {
@@ -305,6 +355,7 @@ moe_nk_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict__ scal
 __global__ void moe_swiglu_kernel(const float *__restrict__ gu, float *__restrict__ h, const int *__restrict__ offset,
                                   int E, int inter, float limit, int slices, size_t slice_stride,
                                   __nv_bfloat16 *__restrict__ h_bf16) {
+    pdl_prologue();
     const int64_t total = (int64_t)offset[E] * inter;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int64_t r = i / inter, j = i % inter;
@@ -324,6 +375,7 @@ __global__ void moe_swiglu_kernel(const float *__restrict__ gu, float *__restric
 template <typename XT>
 __global__ void moe_gather_bf16_kernel(const XT *__restrict__ x, const int *__restrict__ rowtok, int top_k,
                                        const int *__restrict__ offset, int E, int H, __nv_bfloat16 *__restrict__ xg) {
+    pdl_prologue();
     const int r = blockIdx.x;
     if (r >= offset[E]) return;
     const XT *src = x + (size_t)(rowtok[r] / top_k) * H;
@@ -334,6 +386,7 @@ __global__ void moe_gather_bf16_kernel(const XT *__restrict__ x, const int *__re
 __global__ void moe_combine_kernel(const float *__restrict__ o, const int *__restrict__ idx, const float *__restrict__ wt,
                                    const int *__restrict__ pos, int T, int H, int top_k, float *__restrict__ y,
                                    int slices, size_t slice_stride) {
+    pdl_prologue();
     const int t = blockIdx.x;
     if (t >= T) return;
     int order[kMaxTopK];
@@ -451,6 +504,7 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
         launch_grouped(ctx, a, st);
         return;
     }
+    ctx->launches++;   // one of the row kernels below
     if (m->layout == NNQ_MOE_KN_GPTOSS) {
         dim3 grid((N + 1023) / 1024, E, kMoeKnSplit);
         moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, m->top_k, s.offset, out,
@@ -500,19 +554,24 @@ static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int
     if (route_only) return check_cuda(ctx, cudaGetLastError(), "MoE router launch");
     const int EL = m->e_local;
     if (EL != E) cudaMemsetAsync(s.pos, 0xFF, (size_t)total * 4, st);   // -1: assignment served elsewhere
-    moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
-    moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
-    moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
+    if (total <= kGroupSmallMax) {
+        launch_pdl(moe_group_small_kernel, dim3(1), dim3(256), st, s.idx, total, s.count, s.offset, s.rowtok, s.pos, m->e_begin, EL);
+    } else {
+        moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
+        moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
+        moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
+        ctx->launches += 2;
+    }
     if (s.xg) {
         moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, m->top_k, s.offset, m->e_local, m->hidden, s.xg);
         ctx->launches++;
     }
     launch_product<XT>(ctx, m, true, x, s.rowtok, s, s.gu, total, st);
     int64_t hi = (int64_t)total * m->inter;
-    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
+    launch_pdl(moe_swiglu_kernel, dim3((unsigned)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
     launch_product<float>(ctx, m, false, s.h, nullptr, s, s.o, total, st);
-    moe_combine_kernel<<<dim3((unsigned)T, T < 1024 ? 4 : 1), 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
-    ctx->launches += 7;
+    launch_pdl(moe_combine_kernel, dim3((unsigned)T, T < 1024 ? 4 : 1), dim3(256), st, s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
+    ctx->launches += 3;   // grouping, SwiGLU, combine (the products count themselves)
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
 }
 
@@ -552,19 +611,24 @@ static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, 
     launch_router<XT>(m, x, T, s.idx, s.wt, st);
     const int EL = m->e_local;
     if (EL != E) cudaMemsetAsync(s.pos, 0xFF, (size_t)total * 4, st);   // -1: assignment served elsewhere
-    moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
-    moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
-    moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
+    if (total <= kGroupSmallMax) {
+        launch_pdl(moe_group_small_kernel, dim3(1), dim3(256), st, s.idx, total, s.count, s.offset, s.rowtok, s.pos, m->e_begin, EL);
+    } else {
+        moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
+        moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
+        moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
+        ctx->launches += 2;
+    }
     if (s.xg) {
         moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, m->top_k, s.offset, m->e_local, m->hidden, s.xg);
         ctx->launches++;
     }
     launch_product<XT>(ctx, m, true, x, s.rowtok, s, s.gu, total, st);
     int64_t hi = (int64_t)total * m->inter;
-    moe_swiglu_kernel<<<(int)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096), 256, 0, st>>>(s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
+    launch_pdl(moe_swiglu_kernel, dim3((unsigned)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
     launch_product<float>(ctx, m, false, s.h, nullptr, s, s.o, total, st);
-    moe_combine_kernel<<<dim3((unsigned)T, T < 1024 ? 4 : 1), 256, 0, st>>>(s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
-    ctx->launches += 8;
+    launch_pdl(moe_combine_kernel, dim3((unsigned)T, T < 1024 ? 4 : 1), dim3(256), st, s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
+    ctx->launches += 4;   // router, grouping, SwiGLU, combine (the products count themselves)
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
 }
 
