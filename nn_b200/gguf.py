@@ -518,3 +518,47 @@ def load_qwen3_decoder(f: GgufFile, backend=None, *, max_seq: Optional[int] = No
     head_name = "output.weight" if "output.weight" in f.tensors else "token_embd.weight"
     dec.set_head(embed.contiguous(), norm("output_norm.weight"), proj(head_name))
     return dec, c
+
+
+# --------------------------------------------------------------------------- #
+# gpt-oss: tensor names
+# --------------------------------------------------------------------------- #
+_GPTOSS_LAYER = dict(_LAYER_SUFFIX)
+for _s in ("attn_q_norm.weight", "attn_k_norm.weight", "ffn_gate.weight", "ffn_up.weight", "ffn_down.weight"):
+    del _GPTOSS_LAYER[_s]
+_GPTOSS_LAYER.update({
+    "attn_q.bias": "self_attn.q_proj.bias", "attn_k.bias": "self_attn.k_proj.bias", "attn_v.bias": "self_attn.v_proj.bias",
+    "attn_output.bias": "self_attn.o_proj.bias", "attn_sinks": "self_attn.sinks", "ffn_router.weight": "mlp.router.weight",
+    "ffn_router.bias": "mlp.router.bias", "ffn_experts_gate_up": "mlp.experts.gate_up_proj",
+    "ffn_experts_gate_up_bias": "mlp.experts.gate_up_proj_bias", "ffn_experts_down": "mlp.experts.down_proj",
+    "ffn_experts_down_bias": "mlp.experts.down_proj_bias",
+})
+
+
+def gptoss_map_tensor_name(name: str) -> Optional[str]:
+    """GGUF tensor name -> gpt-oss weight name (crates/nn-gptoss/src/gguf_loader.rs:35-96); the
+    layer field must be a non-negative decimal integer."""
+    if name in _GLOBAL:
+        return _GLOBAL[name]
+    layer = gptoss_layer_index(name)
+    if layer is None:
+        return None
+    rest = name[4:]
+    dot = rest.find(".")
+    suffix = _GPTOSS_LAYER.get(rest[dot + 1:])
+    return None if suffix is None else f"model.layers.{rest[:dot]}.{suffix}"
+
+
+def gptoss_layer_index(name: str) -> Optional[int]:
+    """Layer index of `blk.{i}.xxx`, None for other names (gguf_loader.rs:98-106)."""
+    if not name.startswith("blk."):
+        return None
+    rest = name[4:]
+    dot = rest.find(".")
+    if dot < 0:
+        return None
+    field = rest[:dot]
+    digits = field[1:] if field.startswith("+") else field   # Rust's usize parser accepts a leading '+'
+    if not digits or not digits.isascii() or not digits.isdigit():
+        return None
+    return int(digits)

@@ -247,3 +247,19 @@ def test_qwen3_config_keys_defaults_and_errors():
     # a count stored with another integer type does not satisfy the u32 getter
     with pytest.raises(G.MissingMetadata):
         G.qwen3_config_from_gguf(G.GgufFile.from_bytes(G.write_gguf(None, _qwen3_md(**{"qwen3.block_count": G.Typed(10, 2)}), [])))
+
+
+def test_gptoss_name_map():
+    m = G.gptoss_map_tensor_name
+    assert m("token_embd.weight") == "model.embed_tokens.weight" and m("output.weight") == "lm_head.weight"
+    assert m("blk.3.attn_q.bias") == "model.layers.3.self_attn.q_proj.bias"
+    assert m("blk.0.attn_sinks") == "model.layers.0.self_attn.sinks"
+    assert m("blk.23.ffn_router.weight") == "model.layers.23.mlp.router.weight"
+    assert m("blk.5.ffn_experts_gate_up") == "model.layers.5.mlp.experts.gate_up_proj"
+    assert m("blk.5.ffn_experts_gate_up_bias") == "model.layers.5.mlp.experts.gate_up_proj_bias"
+    assert m("blk.5.ffn_experts_down") == "model.layers.5.mlp.experts.down_proj"
+    assert m("blk.5.ffn_experts_down_bias") == "model.layers.5.mlp.experts.down_proj_bias"
+    assert m("blk.7.ffn_norm.weight") == "model.layers.7.post_attention_layernorm.weight"
+    for other in ("blk.x.attn_q.weight", "blk.-1.attn_q.weight", "blk.2.ffn_gate.weight", "blk.2", "foo", "blk.2.attn_q_norm.weight"):
+        assert m(other) is None
+    assert G.gptoss_layer_index("blk.12.attn_sinks") == 12 and G.gptoss_layer_index("output.weight") is None
