@@ -85,7 +85,14 @@ typedef enum nnq_format {
     NNQ_MXFP4_CORE = 6,
     NNQ_MXFP4_SPLIT = 7,
     NNQ_MXFP4_GPTOSS = 8,
-    NNQ_FORMAT_COUNT = 9
+    /* the other nn-gguf block decoders (crates/nn-gguf/src/dequant.rs:241-316,476-684): dequantization
+     * and nnq_linear on the row kernel / tensor path; no tiled layout, not accepted by nnq_moe_create */
+    NNQ_Q5_0 = 9,
+    NNQ_Q5_1 = 10,
+    NNQ_Q2_K = 11,
+    NNQ_Q3_K = 12,
+    NNQ_Q5_K = 13,
+    NNQ_FORMAT_COUNT = 14
 } nnq_format;
 
 typedef enum nnq_dtype { NNQ_F32 = 0, NNQ_BF16 = 1 } nnq_dtype;

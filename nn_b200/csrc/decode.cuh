@@ -174,6 +174,121 @@ struct Decode<NNQ_Q6_K> {
     }
 };
 
+// Q5_0 / Q5_1 (crates/nn-gguf/src/dequant.rs:241-316): element 2j = low nibble of qs[j] with bit 2j
+// of the 32-bit qh word as its fifth bit, element 2j+1 = high nibble with bit 2j+1.
+template <>
+struct Decode<NNQ_Q5_0> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + c * 22;
+        float d = f16_bits_to_f32(ld_u16(b));
+        uint32_t qh = (uint32_t)ld_u16(b + 2) | ((uint32_t)ld_u16(b + 4) << 16);
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            uint32_t q = __ldg(b + 6 + j);
+            int x0 = (int)((q & 15u) | (((qh >> (2 * j)) & 1u) << 4)) - 16;
+            int x1 = (int)((q >> 4) | (((qh >> (2 * j + 1)) & 1u) << 4)) - 16;
+            o[2 * j] = __fmul_rn(d, (float)x0);
+            o[2 * j + 1] = __fmul_rn(d, (float)x1);
+        }
+    }
+};
+
+template <>
+struct Decode<NNQ_Q5_1> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + c * 24;
+        float d = f16_bits_to_f32(ld_u16(b));
+        float m = f16_bits_to_f32(ld_u16(b + 2));
+        uint32_t qh = (uint32_t)ld_u16(b + 4) | ((uint32_t)ld_u16(b + 6) << 16);
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            uint32_t q = __ldg(b + 8 + j);
+            uint32_t x0 = (q & 15u) | (((qh >> (2 * j)) & 1u) << 4);
+            uint32_t x1 = (q >> 4) | (((qh >> (2 * j + 1)) & 1u) << 4);
+            o[2 * j] = __fadd_rn(__fmul_rn(d, (float)x0), m);
+            o[2 * j + 1] = __fadd_rn(__fmul_rn(d, (float)x1), m);
+        }
+    }
+};
+
+// Q2_K, nn-gguf variant (dequant.rs:476-512): flat element index; scale byte per 16 weights
+// (low nibble scale, high nibble minimum); w = (d*sc)*q2 - dmin*m.
+template <>
+struct Decode<NNQ_Q2_K> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + (c >> 3) * 84;
+        int idx0 = (int)(c & 7) * 32;
+        float d = f16_bits_to_f32(ld_u16(b + 80));
+        float dmin = f16_bits_to_f32(ld_u16(b + 82));
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint32_t sb = __ldg(b + idx0 / 16 + h);
+            float s = __fmul_rn(d, (float)(sb & 15u));
+            float m = __fmul_rn(dmin, (float)(sb >> 4));
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t q = __ldg(b + 16 + idx0 / 4 + 4 * h + i);
+#pragma unroll
+                for (int t = 0; t < 4; t++)
+                    o[16 * h + 4 * i + t] = __fsub_rn(__fmul_rn(s, (float)((q >> (2 * t)) & 3u)), m);
+            }
+        }
+    }
+};
+
+// Q3_K, nn-gguf variant (dequant.rs:536-600): 16 six-bit scales (stored + 32), q3 = crumb | hmask bit << 2.
+template <>
+struct Decode<NNQ_Q3_K> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + (c >> 3) * 110;
+        int idx0 = (int)(c & 7) * 32;
+        float d = f16_bits_to_f32(ld_u16(b + 108));
+        int k0 = idx0 / 16;   // even
+        uint32_t lo = __ldg(b + 96 + k0 / 2);
+        uint32_t hi = __ldg(b + 104 + k0 / 4);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            int k = k0 + h;
+            int sc = (int)(((lo >> (4 * h)) & 15u) | (((hi >> (2 * (k & 3))) & 3u) << 4)) - 32;
+            float s = __fmul_rn(d, (float)sc);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t q = __ldg(b + 32 + idx0 / 4 + 4 * h + i);
+                uint32_t hm = __ldg(b + idx0 / 8 + 2 * h + i / 2) >> (4 * (i & 1));
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    int q3 = (int)(((q >> (2 * t)) & 3u) | (((hm >> t) & 1u) << 2)) - 4;
+                    o[16 * h + 4 * i + t] = __fmul_rn(s, (float)q3);
+                }
+            }
+        }
+    }
+};
+
+// Q5_K, nn-gguf variant (dequant.rs:614-684): scales packed as in the nn-gguf Q4_K, flat element
+// index; q5 = nibble(qs[idx/2]) | bit(qh[idx/8], idx%8) << 4; w = (d*sc)*q5 - dmin*m.
+template <>
+struct Decode<NNQ_Q5_K> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + (c >> 3) * 176;   // 16-byte aligned blocks
+        int j = (int)(c & 7);
+        float d = f16_bits_to_f32(ld_u16(b));
+        float dmin = f16_bits_to_f32(ld_u16(b + 2));
+        const uint8_t *S = b + 4;
+        uint32_t sc = ((__ldg(S + j / 2) >> (4 * (j & 1))) & 15u) | (((__ldg(S + 8 + j / 4) >> (2 * (j & 3))) & 3u) << 4);
+        uint32_t mn = ((__ldg(S + 4 + j / 2) >> (4 * (j & 1))) & 15u) | (((__ldg(S + 10 + j / 4) >> (2 * (j & 3))) & 3u) << 4);
+        float s = __fmul_rn(d, (float)sc), m = __fmul_rn(dmin, (float)mn);
+        uint32_t qh = __ldg(reinterpret_cast<const uint32_t *>(b + 16 + 4 * j));
+        uint4 qs = __ldg(reinterpret_cast<const uint4 *>(b + 48 + 16 * j));
+        uint32_t qw[4] = {qs.x, qs.y, qs.z, qs.w};
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            uint32_t q5 = ((qw[i / 8] >> (4 * (i & 7))) & 15u) | (((qh >> i) & 1u) << 4);
+            o[i] = __fsub_rn(__fmul_rn(s, (float)q5), m);
+        }
+    }
+};
+
 template <>
 struct Decode<NNQ_MXFP4_CORE> {
     static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {

@@ -58,6 +58,11 @@ nnq_status launch_dequant_raw(nnq_ctx *ctx, int fmt, const uint8_t *src, const u
         case NNQ_MXFP4_CORE: e = launch<NNQ_MXFP4_CORE>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
         case NNQ_MXFP4_SPLIT: e = launch<NNQ_MXFP4_SPLIT>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
         case NNQ_MXFP4_GPTOSS: e = launch<NNQ_MXFP4_GPTOSS>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
+        case NNQ_Q5_0: e = launch<NNQ_Q5_0>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
+        case NNQ_Q5_1: e = launch<NNQ_Q5_1>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
+        case NNQ_Q2_K: e = launch<NNQ_Q2_K>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
+        case NNQ_Q3_K: e = launch<NNQ_Q3_K>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
+        case NNQ_Q5_K: e = launch<NNQ_Q5_K>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", fmt);
     }
     ctx->launches++;

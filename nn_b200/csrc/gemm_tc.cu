@@ -520,6 +520,11 @@ nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
         case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
         case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
         case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q5_0: e = launch_fmt<NNQ_Q5_0>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q5_1: e = launch_fmt<NNQ_Q5_1>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q2_K: e = launch_fmt<NNQ_Q2_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q3_K: e = launch_fmt<NNQ_Q3_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q5_K: e = launch_fmt<NNQ_Q5_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
     }
     ctx->launches += ksplit > 1 ? 2 : 1;

@@ -113,6 +113,11 @@ nnq_status launch_linear_generic(nnq_ctx *ctx, const LinearArgs &a, cudaStream_t
         case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, stream); break;
         case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, stream); break;
         case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, stream); break;
+        case NNQ_Q5_0: e = launch_fmt<NNQ_Q5_0>(a, stream); break;
+        case NNQ_Q5_1: e = launch_fmt<NNQ_Q5_1>(a, stream); break;
+        case NNQ_Q2_K: e = launch_fmt<NNQ_Q2_K>(a, stream); break;
+        case NNQ_Q3_K: e = launch_fmt<NNQ_Q3_K>(a, stream); break;
+        case NNQ_Q5_K: e = launch_fmt<NNQ_Q5_K>(a, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
     }
     ctx->launches++;

@@ -430,7 +430,7 @@ static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 static bool moe_tensor_mode(const nnq_moe *m, int64_t T) {
     static const char *env = getenv("NNQ_MOE_TENSOR");   // tuning aid: 0 keeps the token-column kernel
     if (env && atoi(env) == 0) return false;
-    return m->layout == NNQ_MOE_NK && m->hidden % 64 == 0 && m->inter % 64 == 0 && T * m->top_k >= 64 * (int64_t)m->n_experts;   // per expert of the whole block: shards of one block agree
+    return m->layout == NNQ_MOE_NK && m->fmt < NNQ_Q5_0 && m->hidden % 64 == 0 && m->inter % 64 == 0 && T * m->top_k >= 64 * (int64_t)m->n_experts;   // per expert of the whole block: shards of one block agree
 }
 
 // Carves the scratch buffer; with base == NULL only the size is computed.
@@ -518,6 +518,7 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
     switch (m->fmt) {
         NNQ_NK(NNQ_Q4_0); NNQ_NK(NNQ_Q4_1); NNQ_NK(NNQ_Q8_0); NNQ_NK(NNQ_Q4_K); NNQ_NK(NNQ_Q4_K_GGML);
         NNQ_NK(NNQ_Q6_K); NNQ_NK(NNQ_MXFP4_CORE); NNQ_NK(NNQ_MXFP4_SPLIT); NNQ_NK(NNQ_MXFP4_GPTOSS);
+        NNQ_NK(NNQ_Q5_0); NNQ_NK(NNQ_Q5_1); NNQ_NK(NNQ_Q2_K); NNQ_NK(NNQ_Q3_K); NNQ_NK(NNQ_Q5_K);
         default: break;
     }
 #undef NNQ_NK

@@ -25,6 +25,11 @@ __host__ __device__ inline Geometry geometry(int fmt) {
         case NNQ_MXFP4_CORE: return {32, 17, 0};
         case NNQ_MXFP4_SPLIT: return {32, 16, 1};
         case NNQ_MXFP4_GPTOSS: return {32, 16, 1};
+        case NNQ_Q5_0: return {32, 22, 0};
+        case NNQ_Q5_1: return {32, 24, 0};
+        case NNQ_Q2_K: return {256, 84, 0};
+        case NNQ_Q3_K: return {256, 110, 0};
+        case NNQ_Q5_K: return {256, 176, 0};
         default: return {0, 0, 0};
     }
 }

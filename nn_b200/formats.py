@@ -32,6 +32,11 @@ class QuantFormat(enum.IntEnum):
     MXFP4_CORE = 6    # 17-byte interleaved blocks, low nibble = even element
     MXFP4_SPLIT = 7   # packed[N][K/2] + exps[N][K/32], low nibble = even element
     MXFP4_GPTOSS = 8  # data[n/2] + scales[n/32], high nibble = even element
+    Q5_0 = 9          # nn-gguf decoders without a tiled layout: dequantization, row kernel and
+    Q5_1 = 10         # tensor-core product only
+    Q2_K = 11
+    Q3_K = 12
+    Q5_K = 13
 
 
 @dataclass(frozen=True)
@@ -51,6 +56,11 @@ GEOMETRY = {
     QuantFormat.MXFP4_CORE: BlockGeometry(32, 17, 0),
     QuantFormat.MXFP4_SPLIT: BlockGeometry(32, 16, 1),
     QuantFormat.MXFP4_GPTOSS: BlockGeometry(32, 16, 1),
+    QuantFormat.Q5_0: BlockGeometry(32, 22, 0),
+    QuantFormat.Q5_1: BlockGeometry(32, 24, 0),
+    QuantFormat.Q2_K: BlockGeometry(256, 84, 0),
+    QuantFormat.Q3_K: BlockGeometry(256, 110, 0),
+    QuantFormat.Q5_K: BlockGeometry(256, 176, 0),
 }
 
 
@@ -181,6 +191,23 @@ def gen_q6_k(seed: int, n: int, k: int, scale: float = 0.01) -> np.ndarray:
     return out.reshape(-1)
 
 
+def gen_uniform_blocks(fmt: "QuantFormat", seed: int, n: int, k: int, scale: float = 0.01) -> np.ndarray:
+    """Q5_0 / Q5_1 / Q2_K / Q3_K / Q5_K blocks: every code, high-bit and packed-scale byte uniform in
+    0..255, the f16 super-block scales |N(0,1)| * scale (Q5_1's minimum signed)."""
+    fmt = QuantFormat(fmt)
+    g = GEOMETRY[fmt]
+    s = Stream(seed)
+    nb = n * (k // g.elems)
+    out = s.integers(nb * g.bytes, 0, 255).astype(np.uint8).reshape(nb, g.bytes)
+    f16_at = {QuantFormat.Q5_0: [(0, False)], QuantFormat.Q5_1: [(0, False), (2, True)],
+              QuantFormat.Q2_K: [(80, False), (82, False)], QuantFormat.Q3_K: [(108, False)],
+              QuantFormat.Q5_K: [(0, False), (2, False)]}[fmt]
+    for off, signed in f16_at:
+        v = s.normal(nb) * scale
+        out[:, off:off + 2] = _f16_bytes(v if signed else np.abs(v))
+    return out.reshape(-1)
+
+
 def gen_mxfp4(seed: int, n: int, k: int, e_lo: int = 119, e_hi: int = 127):
     """Codes uniform over the 16 E2M1 values, exponent byte uniform in [e_lo, e_hi].
 
@@ -216,6 +243,8 @@ def gen_weight(fmt: QuantFormat, seed: int, n: int, k: int):
         return gen_q4_k(seed, n, k), None
     if fmt == QuantFormat.Q6_K:
         return gen_q6_k(seed, n, k), None
+    if fmt >= QuantFormat.Q5_0:
+        return gen_uniform_blocks(fmt, seed, n, k), None
     codes, exps = gen_mxfp4(seed, n, k)
     if fmt == QuantFormat.MXFP4_CORE:
         return mxfp4_core_bytes(codes, exps), None

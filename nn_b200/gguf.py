@@ -80,7 +80,8 @@ DTYPES: Dict[int, Tuple[str, int, int]] = {
 DTYPE_ID = {v[0]: k for k, v in DTYPES.items()}
 # GGUF dtypes the library multiplies with directly (the reference's nn-gguf element orders)
 QUANT_OF = {"Q4_0": QuantFormat.Q4_0, "Q4_1": QuantFormat.Q4_1, "Q8_0": QuantFormat.Q8_0, "Q4K": QuantFormat.Q4_K,
-            "Q6K": QuantFormat.Q6_K}
+            "Q6K": QuantFormat.Q6_K, "Q5_0": QuantFormat.Q5_0, "Q5_1": QuantFormat.Q5_1, "Q2K": QuantFormat.Q2_K,
+            "Q3K": QuantFormat.Q3_K, "Q5K": QuantFormat.Q5_K}
 U64_MAX = (1 << 64) - 1
 
 
@@ -466,8 +467,8 @@ def load_qwen3_decoder(f: GgufFile, backend=None, *, max_seq: Optional[int] = No
                        tp=(0, 1), comm=None):
     """Build a decoder.Decoder from a Qwen3 GGUF file.
 
-    Projection weights stay in their quantized blocks (Q4_0 / Q4_1 / Q8_0 / Q4_K / Q6_K go to
-    the device as stored and are multiplied there); norms are read as f32; the embedding table
+    Projection weights stay in their quantized blocks (every block format the reference decodes
+    goes to the device as stored and is multiplied there); norms are read as f32; the embedding table
     is decoded once to bf16 on the device. `output.weight` falls back to the embedding tensor
     when the file ties them (arch_qwen3.rs:231-236). With tp = (rank, world) the decoder holds
     that rank's shards of the projections and `comm` carries the exchanges.

@@ -38,7 +38,8 @@ def lib():
         _lib.orc_f16_to_f32.restype = ctypes.c_float
         _lib.orc_f16_to_f32.argtypes = [ctypes.c_uint16]
         for name in ("orc_dequant_q4_0", "orc_dequant_q4_1", "orc_dequant_q8_0", "orc_dequant_q4_k",
-                     "orc_dequant_q4_k_ggml", "orc_dequant_q6_k"):
+                     "orc_dequant_q4_k_ggml", "orc_dequant_q6_k", "orc_dequant_q5_0", "orc_dequant_q5_1",
+                     "orc_dequant_q2_k", "orc_dequant_q3_k", "orc_dequant_q5_k"):
             f = getattr(_lib, name)
             f.restype = ctypes.c_size_t
             f.argtypes = [_u8p, ctypes.c_size_t, ctypes.c_size_t, _f32p]
@@ -82,7 +83,8 @@ def _f32(a):
 
 
 _DEQ = {0: "orc_dequant_q4_0", 1: "orc_dequant_q4_1", 2: "orc_dequant_q8_0", 3: "orc_dequant_q4_k",
-        4: "orc_dequant_q4_k_ggml", 5: "orc_dequant_q6_k"}
+        4: "orc_dequant_q4_k_ggml", 5: "orc_dequant_q6_k", 9: "orc_dequant_q5_0", 10: "orc_dequant_q5_1",
+        11: "orc_dequant_q2_k", 12: "orc_dequant_q3_k", 13: "orc_dequant_q5_k"}
 
 
 def f16_to_f32(bits: int) -> float:

@@ -246,6 +246,118 @@ ORC_API size_t orc_dequant_q6_k(const uint8_t *data, size_t nbytes, size_t num_e
     return nb * 256;
 }
 
+/* Q5_0: 22 B / 32 weights. [0,2) d  [2,6) qh (u32 LE)  [6,22) qs
+ *   element 2j = low nibble of qs[j] | bit 2j of qh << 4; element 2j+1 = high nibble | bit 2j+1 << 4
+ *   w = d * (q5 - 16)
+ * crates/nn-gguf/src/dequant.rs:241-271. */
+ORC_API size_t orc_dequant_q5_0(const uint8_t *data, size_t nbytes, size_t num_elements,
+                                float *out) {
+    size_t nb = usable_blocks(nbytes, num_elements, 32, 22);
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = data + b * 22;
+        float d = f16_at(blk);
+        uint32_t qh = (uint32_t)blk[2] | ((uint32_t)blk[3] << 8) | ((uint32_t)blk[4] << 16) | ((uint32_t)blk[5] << 24);
+        for (int j = 0; j < 16; j++) {
+            int x0 = (int)((blk[6 + j] & 0x0F) | (((qh >> (2 * j)) & 1u) << 4)) - 16;
+            int x1 = (int)((blk[6 + j] >> 4) | (((qh >> (2 * j + 1)) & 1u) << 4)) - 16;
+            out[b * 32 + 2 * j] = d * (float)x0;
+            out[b * 32 + 2 * j + 1] = d * (float)x1;
+        }
+    }
+    return nb * 32;
+}
+
+/* Q5_1: 24 B / 32 weights. [0,2) d  [2,4) m  [4,8) qh  [8,24) qs; w = d * q5 + m.
+ * crates/nn-gguf/src/dequant.rs:285-316. */
+ORC_API size_t orc_dequant_q5_1(const uint8_t *data, size_t nbytes, size_t num_elements,
+                                float *out) {
+    size_t nb = usable_blocks(nbytes, num_elements, 32, 24);
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = data + b * 24;
+        float d = f16_at(blk), m = f16_at(blk + 2);
+        uint32_t qh = (uint32_t)blk[4] | ((uint32_t)blk[5] << 8) | ((uint32_t)blk[6] << 16) | ((uint32_t)blk[7] << 24);
+        for (int j = 0; j < 16; j++) {
+            uint32_t x0 = (uint32_t)(blk[8 + j] & 0x0F) | (((qh >> (2 * j)) & 1u) << 4);
+            uint32_t x1 = (uint32_t)(blk[8 + j] >> 4) | (((qh >> (2 * j + 1)) & 1u) << 4);
+            out[b * 32 + 2 * j] = d * (float)x0 + m;
+            out[b * 32 + 2 * j + 1] = d * (float)x1 + m;
+        }
+    }
+    return nb * 32;
+}
+
+/* Q2_K, nn-gguf variant: 84 B / 256 weights, flat element index.
+ *   [0,16) scales (low nibble = scale, high nibble = min, per 16 weights)  [16,80) qs  [80,82) d  [82,84) dmin
+ *   q2 = crumb(qs[idx/4], idx%4);  w = (d * sc) * q2 - dmin * m
+ * crates/nn-gguf/src/dequant.rs:476-512. */
+ORC_API size_t orc_dequant_q2_k(const uint8_t *data, size_t nbytes, size_t num_elements,
+                                float *out) {
+    size_t nb = usable_blocks(nbytes, num_elements, 256, 84);
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = data + b * 84;
+        const uint8_t *qs = blk + 16;
+        float d = f16_at(blk + 80), dmin = f16_at(blk + 82);
+        for (int idx = 0; idx < 256; idx++) {
+            float sc = (float)(blk[idx / 16] & 0x0F);
+            float m = (float)(blk[idx / 16] >> 4);
+            float q2 = (float)((qs[idx / 4] >> ((idx % 4) * 2)) & 0x03);
+            out[b * 256 + idx] = d * sc * q2 - dmin * m;
+        }
+    }
+    return nb * 256;
+}
+
+/* Q3_K, nn-gguf variant: 110 B / 256 weights, flat element index.
+ *   [0,32) hmask  [32,96) qs  [96,108) S[12]  [108,110) d
+ *   scale_k = (lo4(S[k/2], k%2) | crumb(S[8 + k/4], k%4) << 4) - 32   (16 scales, one per 16 weights)
+ *   q3 = crumb(qs[idx/4], idx%4) | bit(hmask[idx/8], idx%8) << 2;  w = (d * scale) * (q3 - 4)
+ * crates/nn-gguf/src/dequant.rs:536-600. */
+ORC_API size_t orc_dequant_q3_k(const uint8_t *data, size_t nbytes, size_t num_elements,
+                                float *out) {
+    size_t nb = usable_blocks(nbytes, num_elements, 256, 110);
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = data + b * 110;
+        const uint8_t *hmask = blk, *qs = blk + 32, *S = blk + 96;
+        float d = f16_at(blk + 108);
+        for (int k = 0; k < 16; k++) {
+            int lo4 = (S[k / 2] >> (4 * (k % 2))) & 0x0F;
+            int hi2 = (S[8 + k / 4] >> (2 * (k % 4))) & 0x03;
+            float sc = d * (float)((lo4 | (hi2 << 4)) - 32);
+            for (int i = 0; i < 16; i++) {
+                int idx = 16 * k + i;
+                int q3 = ((qs[idx / 4] >> ((idx % 4) * 2)) & 0x03) | (((hmask[idx / 8] >> (idx % 8)) & 1) << 2);
+                out[b * 256 + idx] = sc * (float)(q3 - 4);
+            }
+        }
+    }
+    return nb * 256;
+}
+
+/* Q5_K, nn-gguf variant: 176 B / 256 weights, flat element index.
+ *   [0,2) d  [2,4) dmin  [4,16) S[12] (packed as in the nn-gguf Q4_K)  [16,48) qh  [48,176) qs
+ *   q5 = nibble(qs[idx/2], idx%2) | bit(qh[idx/8], idx%8) << 4;  w = (d*sc_j)*q5 - dmin*m_j, j = idx/32
+ * crates/nn-gguf/src/dequant.rs:614-684. */
+ORC_API size_t orc_dequant_q5_k(const uint8_t *data, size_t nbytes, size_t num_elements,
+                                float *out) {
+    size_t nb = usable_blocks(nbytes, num_elements, 256, 176);
+    for (size_t b = 0; b < nb; b++) {
+        const uint8_t *blk = data + b * 176;
+        const uint8_t *qh = blk + 16, *qs = blk + 48;
+        float d = f16_at(blk), dmin = f16_at(blk + 2);
+        uint8_t sc[8], mn[8];
+        q4k_gguf_scales(blk + 4, sc, mn);
+        for (int j = 0; j < 8; j++) {
+            float s = d * (float)sc[j], m = dmin * (float)mn[j];
+            for (int i = 0; i < 32; i++) {
+                int idx = 32 * j + i;
+                int q5 = ((qs[idx / 2] >> (4 * (idx % 2))) & 0x0F) | (((qh[idx / 8] >> (idx % 8)) & 1) << 4);
+                out[b * 256 + idx] = s * (float)q5 - m;
+            }
+        }
+    }
+    return nb * 256;
+}
+
 /* ------------------------------------------------------------------------- */
 /* MXFP4 decoders                                                            */
 /* ------------------------------------------------------------------------- */
@@ -530,6 +642,11 @@ ORC_API int orc_cpu_forward(int fmt, const uint8_t *w, size_t wbytes, const floa
         case 2: be = 32; bb = 34; break;
         case 3: case 4: be = 256; bb = 144; break;
         case 5: be = 256; bb = 210; break;
+        case 9: be = 32; bb = 22; break;
+        case 10: be = 32; bb = 24; break;
+        case 11: be = 256; bb = 84; break;
+        case 12: be = 256; bb = 110; break;
+        case 13: be = 256; bb = 176; break;
         default: return -1;
     }
     size_t row_bytes = k / be * bb;
@@ -545,7 +662,12 @@ ORC_API int orc_cpu_forward(int fmt, const uint8_t *w, size_t wbytes, const floa
             case 2: orc_dequant_q8_0(src, row_bytes, k, dst); break;
             case 3: orc_dequant_q4_k(src, row_bytes, k, dst); break;
             case 4: orc_dequant_q4_k_ggml(src, row_bytes, k, dst); break;
-            default: orc_dequant_q6_k(src, row_bytes, k, dst); break;
+            case 5: orc_dequant_q6_k(src, row_bytes, k, dst); break;
+            case 9: orc_dequant_q5_0(src, row_bytes, k, dst); break;
+            case 10: orc_dequant_q5_1(src, row_bytes, k, dst); break;
+            case 11: orc_dequant_q2_k(src, row_bytes, k, dst); break;
+            case 12: orc_dequant_q3_k(src, row_bytes, k, dst); break;
+            default: orc_dequant_q5_k(src, row_bytes, k, dst); break;
         }
     }
     orc_nncpu_linear(x, scratch, bias, y, m, n, k, nt);

@@ -166,6 +166,179 @@ for e, v in ((127, 1.0), (128, 2.0), (126, 0.5)):
     add(f"mxfp4_gptoss_scale_e{e}", "MXFP4_GPTOSS", one_hi, 32, [(0, 1, v, 0.0), (1, 32, 0.0, 0.0)],
         "crates/nn-gptoss/src/quantize.rs:373-377", scales=bytes([e]))
 
+# ---- Q5_0 / Q5_1 ----------------------------------------------------------
+D = "crates/nn-gguf/src/dequant.rs:"
+add("q5_0_zero_scale", "Q5_0", bytearray(22), 32, [(0, 32, 0.0, 0.0)], D + "898-907")
+b = bytearray(22)
+b[0:2] = f16(1.0)
+b[2:6] = b"\xff" * 4
+add("q5_0_centered", "Q5_0", b, 32, [(0, 32, 0.0, 1e-4)], D + "909-928")
+b = bytearray(22)
+b[0:2] = f16(0.5)
+b[6:22] = b"\x55" * 16
+add("q5_0_known_values", "Q5_0", b, 32, [(0, 32, -5.5, 1e-3)], D + "930-951")
+b = bytearray(44)
+b[0:2] = f16(1.0)
+b[22:24] = f16(2.0)
+add("q5_0_two_blocks", "Q5_0", b, 64, [(0, 32, -16.0, 1e-3), (32, 64, -32.0, 1e-3)], D + "953-984")
+b = bytearray(22)
+b[0:2] = f16(1.0)
+b[2:6] = (0xAAAAAAAA).to_bytes(4, "little")
+add("q5_0_mixed_high_bits", "Q5_0", b, 32,
+    [(i, i + 1, -16.0 if i % 2 == 0 else 0.0, 1e-3) for i in range(32)], D + "986-1023")
+
+b = bytearray(24)
+b[2:4] = f16(3.0)
+b[8:24] = b"\xaa" * 16
+add("q5_1_zero_scale", "Q5_1", b, 32, [(0, 32, 3.0, 1e-3)], D + "1027-1042")
+b = bytearray(24)
+b[0:2] = f16(1.0)
+b[4:8] = b"\xff" * 4
+b[8:24] = b"\x77" * 16
+add("q5_1_known_values", "Q5_1", b, 32, [(0, 32, 23.0, 1e-2)], D + "1044-1070")
+b = bytearray(24)
+b[0:2] = f16(0.5)
+b[2:4] = f16(10.0)
+add("q5_1_with_minimum", "Q5_1", b, 32, [(0, 32, 10.0, 1e-2)], D + "1072-1092")
+b = bytearray(48)
+b[0:2] = f16(1.0)
+b[24:26] = f16(1.0)
+b[26:28] = f16(5.0)
+add("q5_1_two_blocks", "Q5_1", b, 64, [(0, 32, 0.0, 1e-3), (32, 64, 5.0, 1e-2)], D + "1094-1127")
+b = bytearray(24)
+b[0:2] = f16(1.0)
+b[4:8] = b"\xff" * 4
+b[8:24] = b"\xff" * 16
+add("q5_1_max_quant", "Q5_1", b, 32, [(0, 32, 31.0, 1e-2)], D + "1129-1155")
+
+# ---- Q2_K -----------------------------------------------------------------
+b = bytearray(84)
+b[0:80] = b"\xff" * 80
+add("q2_k_zero_d_dmin", "Q2_K", b, 256, [(0, 256, 0.0, 0.0)], D + "1410-1427")
+b = bytearray(84)
+b[80:82] = f16(1.0)
+b[0] = 0x03
+b[16:20] = b"\xaa" * 4
+add("q2_k_known_values", "Q2_K", b, 256, [(0, 16, 6.0, 1e-3), (16, 256, 0.0, 1e-6)], D + "1429-1470")
+b = bytearray(84)
+b[80:82] = f16(1.0)
+b[82:84] = f16(0.5)
+b[0] = 0x41
+add("q2_k_with_dmin", "Q2_K", b, 256, [(0, 16, -2.0, 1e-3), (16, 256, 0.0, 1e-6)], D + "1472-1510")
+b = bytearray(84)
+b[80:82] = f16(2.0)
+b[82:84] = f16(1.0)
+b[0] = 0xFF
+b[16:20] = b"\xff" * 4
+add("q2_k_max_quant", "Q2_K", b, 256, [(0, 16, 75.0, 1e-1)], D + "1512-1542")
+b = bytearray(168)
+b[80:82] = f16(1.0)
+b[84 + 80:84 + 82] = f16(1.0)
+add("q2_k_two_blocks", "Q2_K", b, 512, [(0, 512, 0.0, 0.0)], D + "1544-1561")
+
+# ---- Q3_K -----------------------------------------------------------------
+b = bytearray(110)
+b[0:108] = b"\xff" * 108
+add("q3_k_zero_d", "Q3_K", b, 256, [(0, 256, 0.0, 0.0)], D + "1571-1585")
+
+
+def q3k_unit_scales(d):
+    b = bytearray(110)
+    b[108:110] = f16(d)
+    b[96:104] = b"\x11" * 8     # low nibbles 1
+    b[104:108] = b"\xaa" * 4    # high crumbs 2 -> 1 | 2 << 4 = 33 -> scale +1
+    return b
+
+
+b = q3k_unit_scales(1.0)
+b[0:32] = b"\xff" * 32
+add("q3_k_centered_q4", "Q3_K", b, 256, [(0, 256, 0.0, 1e-4)], D + "1587-1621")
+b = bytearray(110)
+b[108:110] = f16(0.5)
+b[96] = 0x01
+b[104] = 0x02
+b[0] = b[1] = 0xFF
+b[32:36] = b"\x55" * 4
+add("q3_k_known_values", "Q3_K", b, 256, [(0, 16, 0.5, 1e-3)], D + "1623-1670")
+b = bytearray(110)
+b[108:110] = f16(1.0)
+add("q3_k_zero_scales_nonzero_d", "Q3_K", b, 256, [(0, 256, 128.0, 1e-1)], D + "1672-1690")
+b = q3k_unit_scales(1.0)
+b[0:32] = b"\xff" * 32
+b[32:96] = b"\xff" * 64
+add("q3_k_all_q3_max", "Q3_K", b, 256, [(0, 256, 3.0, 1e-3)], D + "1692-1726")
+b = bytearray(110)
+b[108:110] = f16(0.5)
+b[96:104] = b"\x22" * 8
+b[104:108] = b"\xaa" * 4
+add("q3_k_all_q3_min", "Q3_K", b, 256, [(0, 256, -4.0, 1e-3)], D + "1728-1760")
+b = bytearray(110)
+b[108:110] = f16(1.0)
+b[96] = 0x0F
+b[104] = 0x01
+b[0] = b[1] = 0xFF
+b[32:36] = b"\x55" * 4
+add("q3_k_negative_scale", "Q3_K", b, 256, [(0, 16, -1.0, 1e-3)], D + "1762-1794")
+b = bytearray(220)
+b[0:108] = b"\xab" * 108
+b[110:218] = b"\xcd" * 108
+add("q3_k_two_blocks", "Q3_K", b, 512, [(0, 512, 0.0, 0.0)], D + "1796-1811")
+b = bytearray(110)
+b[108:110] = f16(1.0)
+b[96] = 0x01
+b[104] = 0x02
+b[1] = 0xFF
+add("q3_k_mixed_high_bits", "Q3_K", b, 256, [(0, 8, -4.0, 1e-3), (8, 16, 0.0, 1e-3)], D + "1813-1853")
+
+# ---- Q5_K -----------------------------------------------------------------
+b = bytearray(176)
+b[4:176] = b"\xff" * 172
+add("q5_k_zero_d_dmin", "Q5_K", b, 256, [(0, 256, 0.0, 0.0)], D + "1863-1877")
+b = bytearray(176)
+b[0:2] = f16(1.0)
+b[4] = 0x02
+b[48:64] = b"\x33" * 16
+add("q5_k_known_values", "Q5_K", b, 256, [(0, 32, 6.0, 1e-3), (32, 256, 0.0, 1e-6)], D + "1879-1921")
+b = bytearray(176)
+b[0:2] = f16(1.0)
+b[2:4] = f16(0.5)
+b[4] = 0x01
+b[8] = 0x04
+add("q5_k_with_dmin", "Q5_K", b, 256, [(0, 32, -2.0, 1e-3)], D + "1923-1954")
+b = bytearray(176)
+b[0:2] = f16(1.0)
+b[4] = 0x01
+b[16:48] = b"\xff" * 32
+add("q5_k_with_high_bit", "Q5_K", b, 256, [(0, 32, 16.0, 1e-3)], D + "1956-1988")
+b = bytearray(176)
+b[0:2] = f16(0.5)
+b[4] = 0x04
+b[16:48] = b"\xff" * 32
+b[48:176] = b"\xff" * 128
+add("q5_k_max_quant", "Q5_K", b, 256, [(0, 32, 62.0, 1e-1)], D + "1990-2024")
+b = bytearray(176)
+b[0:2] = f16(1.0)
+b[4] = 0x01
+b[17] = 0xFF
+add("q5_k_mixed_high_bits", "Q5_K", b, 256, [(0, 8, 0.0, 1e-4), (8, 16, 16.0, 1e-3), (16, 32, 0.0, 1e-4)], D + "2026-2065")
+b = bytearray(352)
+b[0:2] = f16(1.0)
+b[176:178] = f16(2.0)
+add("q5_k_two_blocks", "Q5_K", b, 512, [(0, 512, 0.0, 0.0)], D + "2067-2083")
+b = bytearray(176)
+b[0:2] = f16(1.0)
+b[2:4] = f16(1.0)
+b[4] = 0x02
+b[8] = 0x03
+add("q5_k_scale_packing", "Q5_K", b, 256, [(0, 32, -3.0, 1e-3)], D + "2087-2116")
+b = bytearray(176)
+b[0:2] = f16(0.1)
+b[4] = 0x03
+b[12] = 0x02
+b[48:64] = b"\x11" * 16
+add("q5_k_high_scale_bits", "Q5_K", b, 256, [(0, 32, float(np.float32(np.float16(0.1)) * np.float32(35.0)), 1e-2)],
+    D + "2118-2145")
+
 # ---- fused nn-core product (Q8_0 / Q4_0): weight rows all equal ------------
 matmul = []
 

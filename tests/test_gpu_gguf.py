@@ -16,7 +16,7 @@ from oracle import qwen3_ref as ref
 pytestmark = pytest.mark.gpu
 
 HID, HEADS, KV, HD, FFN, LAYERS, VOCAB, SEQ = 512, 4, 2, 128, 1024, 2, 1024, 32
-GG = {Q.Q4_K: "Q4K", Q.Q6_K: "Q6K", Q.Q8_0: "Q8_0", Q.Q4_0: "Q4_0", Q.Q4_1: "Q4_1"}
+GG = {v: k for k, v in G.QUANT_OF.items()}
 
 
 def _write(path, tied, seed=5):
@@ -38,14 +38,15 @@ def _write(path, tied, seed=5):
         return v
 
     # every GGUF format the library multiplies with appears in some projection
-    fmts = {"q": Q.Q4_K, "k": Q.Q8_0, "v": Q.Q6_K, "o": Q.Q4_K, "gate": Q.Q4_0, "up": Q.Q4_1, "down": Q.Q4_K}
+    fmts = [{"q": Q.Q4_K, "k": Q.Q8_0, "v": Q.Q6_K, "o": Q.Q4_K, "gate": Q.Q4_0, "up": Q.Q4_1, "down": Q.Q4_K},
+            {"q": Q.Q5_K, "k": Q.Q5_0, "v": Q.Q5_1, "o": Q.Q3_K, "gate": Q.Q2_K, "up": Q.Q5_K, "down": Q.Q5_0}]
     gname = {"q": "attn_q", "k": "attn_k", "v": "attn_v", "o": "attn_output", "gate": "ffn_gate", "up": "ffn_up", "down": "ffn_down"}
     for li in range(LAYERS):
         shapes = [("q", HEADS * HD, HID), ("k", KV * HD, HID), ("v", KV * HD, HID), ("o", HID, HEADS * HD),
                   ("gate", FFN, HID), ("up", FFN, HID), ("down", HID, FFN)]
         L = {}
         for i, (nm, n, k) in enumerate(shapes):
-            L[nm] = qw(f"blk.{li}.{gname[nm]}.weight", fmts[nm], n, k, seed + 10 * li + i)
+            L[nm] = qw(f"blk.{li}.{gname[nm]}.weight", fmts[li % 2][nm], n, k, seed + 10 * li + i)
         L["in_norm"] = norm(f"blk.{li}.attn_norm.weight", HID)
         L["post_norm"] = norm(f"blk.{li}.ffn_norm.weight", HID)
         L["q_norm"] = norm(f"blk.{li}.attn_q_norm.weight", HD)

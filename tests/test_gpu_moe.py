@@ -36,7 +36,7 @@ def _make(layout, fmt, E, H, I, seed):
 
 
 @pytest.mark.parametrize("layout,fmt", [(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS), (moe.LAYOUT_NK, Q.MXFP4_SPLIT),
-                                        (moe.LAYOUT_NK, Q.Q4_K)])
+                                        (moe.LAYOUT_NK, Q.Q4_K), (moe.LAYOUT_NK, Q.Q5_K), (moe.LAYOUT_NK, Q.Q3_K)])
 @pytest.mark.parametrize("T", [1, 7, 64])
 def test_moe_forward_matches_oracle(layout, fmt, T):
     E, H, I, k, limit = 8, 256, 256, 4, 7.0

@@ -99,6 +99,60 @@ def test_q6_k_matches_numpy_transcription():
     assert np.array_equal(a.view(np.uint32), _numpy_q6_k(data).view(np.uint32))
 
 
+def _h(blk, off):
+    return blk[:, off:off + 2].copy().view(np.float16).astype(np.float32)[:, 0][:, None]
+
+
+def _numpy_flat(fmt, data):
+    """Independent numpy transcriptions (flat element index) of the Q5_0 / Q5_1 / Q2_K / Q3_K / Q5_K
+    formulas of crates/nn-gguf/src/dequant.rs:241-316,476-684, every operation rounded to f32."""
+    f = np.float32
+    if fmt in (Q.Q5_0, Q.Q5_1):
+        hdr = 2 if fmt == Q.Q5_0 else 4
+        blk = data.reshape(-1, hdr + 20)
+        idx = np.arange(32)
+        qh = blk[:, hdr:hdr + 4].copy().view("<u4")
+        q = ((blk[:, hdr + 4 + idx // 2] >> (4 * (idx % 2))) & 15) | (((qh >> idx) & 1) << 4).astype(np.uint8)
+        if fmt == Q.Q5_0:
+            return (_h(blk, 0) * (q.astype(np.int32) - 16).astype(f)).reshape(-1)
+        return (_h(blk, 0) * q.astype(f) + _h(blk, 2)).reshape(-1)
+    idx = np.arange(256)
+    if fmt == Q.Q2_K:
+        blk = data.reshape(-1, 84)
+        sc = (blk[:, idx // 16] & 15).astype(f)
+        mn = (blk[:, idx // 16] >> 4).astype(f)
+        q = ((blk[:, 16 + idx // 4] >> (2 * (idx % 4))) & 3).astype(f)
+        return ((_h(blk, 80) * sc) * q - _h(blk, 82) * mn).reshape(-1)
+    if fmt == Q.Q3_K:
+        blk = data.reshape(-1, 110)
+        k = idx // 16
+        lo4 = (blk[:, 96 + k // 2] >> (4 * (k % 2))) & 15
+        hi2 = (blk[:, 104 + k // 4] >> (2 * (k % 4))) & 3
+        sc = ((lo4 | (hi2 << 4)).astype(np.int32) - 32).astype(f)
+        q = ((blk[:, 32 + idx // 4] >> (2 * (idx % 4))) & 3) | (((blk[:, idx // 8] >> (idx % 8)) & 1) << 2)
+        return ((_h(blk, 108) * sc) * (q.astype(np.int32) - 4).astype(f)).reshape(-1)
+    blk = data.reshape(-1, 176)
+    S = blk[:, 4:16]
+    j = idx // 32
+    sc = ((S[:, j // 2] >> (4 * (j % 2))) & 15) | (((S[:, 8 + j // 4] >> (2 * (j % 4))) & 3) << 4)
+    mn = ((S[:, 4 + j // 2] >> (4 * (j % 2))) & 15) | (((S[:, 10 + j // 4] >> (2 * (j % 4))) & 3) << 4)
+    q = ((blk[:, 48 + idx // 2] >> (4 * (idx % 2))) & 15) | (((blk[:, 16 + idx // 8] >> (idx % 8)) & 1) << 4)
+    return ((_h(blk, 0) * sc.astype(f)) * q.astype(f) - _h(blk, 2) * mn.astype(f)).reshape(-1)
+
+
+@pytest.mark.parametrize("fmt", [Q.Q5_0, Q.Q5_1, Q.Q2_K, Q.Q3_K, Q.Q5_K])
+def test_flat_index_formats_match_numpy_transcription(fmt):
+    data, _ = F.gen_weight(fmt, 0x5EED + int(fmt), 8, 1024)
+    assert data.size == 8 * 1024 // F.GEOMETRY[fmt].elems * F.GEOMETRY[fmt].bytes
+    a = orc.dequantize(fmt, data, 8 * 1024)
+    assert a.size == 8 * 1024 and np.all(np.isfinite(a))
+    assert np.array_equal(a.view(np.uint32), _numpy_flat(fmt, data).view(np.uint32))
+    # a short buffer decodes only its whole blocks (validate_dequant_input, dequant.rs:123-139)
+    g = F.GEOMETRY[fmt]
+    short = orc.dequantize(fmt, data[:3 * g.bytes + 5], 8 * 1024)
+    assert short.size == 3 * g.elems and np.array_equal(short, a[:3 * g.elems])
+
+
 def test_q4_k_ggml_variant_differs_only_in_order_and_packing():
     # A block whose 12 scale bytes hold 6-bit values below 16 in bytes 0..7 and zero in
     # bytes 8..11 decodes, under the GGML packing, to sc_j = S[j], m_j = S[j+4] for j<4
