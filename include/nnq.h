@@ -60,6 +60,7 @@ typedef enum nnq_status {
     NNQ_ERR_DATA_LENGTH = 8,      /* TensorError::DataLengthMismatch: bytes != blocks*size */
     NNQ_ERR_RANK_MISMATCH = 9,    /* TensorError::RankMismatch: input rank < 2             */
     NNQ_ERR_UNSUPPORTED = 10,     /* TensorError::Unsupported                              */
+    NNQ_ERR_VALUE_OUT_OF_RANGE = 11, /* TensorError::ValueOutOfRange: non-finite encoder input */
     NNQ_ERR_OUT_OF_MEMORY = 20,   /* BackendErrorKind::OutOfMemory                         */
     NNQ_ERR_DISPATCH_FAILED = 21, /* BackendErrorKind::DispatchFailed (launch / CUDA error)*/
     NNQ_ERR_TIMEOUT = 22,         /* BackendErrorKind::Timeout (a bounded device wait ran out) */
@@ -169,6 +170,26 @@ NNQ_API void nnq_weight_destroy(nnq_weight *w);
 /* Shape, format and stored byte counts of a weight (any out pointer may be NULL). */
 NNQ_API nnq_status nnq_weight_info(const nnq_weight *w, nnq_format *fmt, int64_t *n, int64_t *k,
                            size_t *nbytes, size_t *scales_nbytes);
+
+/* ---- quantization (f32 -> blocks) --------------------------------------------------- */
+
+/* Encode `num_elements` f32 values resident on the device into blocks, byte-identical to the
+ * reference's CPU encoders; the last block is padded with zeros as the reference pads it.
+ *   NNQ_Q4_K_GGML    BlockQ4K::quantize behind QLinear::from_linear
+ *                    (crates/nn-core/src/layers/quantized/linear.rs:95-162,195-254,309-343)
+ *   NNQ_MXFP4_CORE   quantize_tensor / quantize_block
+ *                    (crates/nn-core/src/layers/quantized/mxfp4.rs:183-207,307-329)
+ *   NNQ_MXFP4_GPTOSS Mxfp4Tensor::quantize (crates/nn-gptoss/src/quantize.rs:122-153);
+ *                    `scales_dev` receives one byte per block
+ * Other formats: NNQ_ERR_UNSUPPORTED (the reference has no encoder for them).
+ * `dst_dev` must be 16-byte aligned and hold blocks * block bytes (nnq_format_geometry);
+ * *blocks (optional) receives the block count. A non-finite input is
+ * NNQ_ERR_VALUE_OUT_OF_RANGE where the reference returns ValueOutOfRange (the nn-gptoss
+ * encoder encodes it as zero instead). The call waits for the stream: encoding is a
+ * load-time step. */
+NNQ_API nnq_status nnq_quantize(nnq_ctx *ctx, nnq_format fmt, const float *src_dev, int64_t num_elements,
+                                void *dst_dev, size_t dst_nbytes, void *scales_dev, size_t scales_nbytes,
+                                int64_t *blocks, void *stream);
 
 /* ---- dequantization (bit-exact gate) ---------------------------------------------- */
 

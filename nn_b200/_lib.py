@@ -37,6 +37,8 @@ SIGNATURES = {
     "nnq_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "nnq_dequantize_raw": (c_int, [c_void_p, c_int, c_void_p, c_size_t, c_void_p, c_size_t, c_int64, c_void_p,
                                    ctypes.POINTER(c_int64), c_void_p]),
+    "nnq_quantize": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_size_t, c_void_p, c_size_t,
+                             ctypes.POINTER(c_int64), c_void_p]),
     "nnq_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
     "nnq_linear_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int]),
     "nnq_linear_batch": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int64,

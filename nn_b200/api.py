@@ -73,6 +73,10 @@ class InvalidArgument(TensorError):
     pass
 
 
+class ValueOutOfRange(TensorError):
+    """``TensorError::ValueOutOfRange``: a non-finite value reached an encoder."""
+
+
 class BackendFailure(TensorError):
     """``TensorError::BackendFailure{domain: Cuda, kind, message}``."""
 
@@ -83,7 +87,7 @@ class BackendFailure(TensorError):
 
 _STATUS_ERRORS = {
     1: InvalidArgument, 2: NotQuantized, 3: WrongQuantType, 4: ShapeMismatch, 5: WeightRank, 6: BiasMismatch,
-    7: InvalidShape, 8: DataLengthMismatch, 9: RankMismatch, 10: Unsupported,
+    7: InvalidShape, 8: DataLengthMismatch, 9: RankMismatch, 10: Unsupported, 11: ValueOutOfRange,
 }
 _BACKEND_KINDS = {20: "OutOfMemory", 21: "DispatchFailed", 22: "Timeout", 23: "NoDevice", 24: "Other"}
 
@@ -353,6 +357,33 @@ def from_quantized(data, quant_type, shape, scales=None) -> QuantizedTensor:
     return QuantizedTensor(data, quant_type, shape, scales)
 
 
+def quantize(values, quant_type, backend: Optional[Backend] = None):
+    """Encode f32 values into blocks on the device with the reference's encoders:
+    ``Q4_K_GGML`` = ``BlockQ4K::quantize`` as ``QLinear::from_linear`` applies it
+    (crates/nn-core/src/layers/quantized/linear.rs:95-162,309-343), ``MXFP4_CORE`` =
+    ``quantize_tensor`` (mxfp4.rs:307-329), ``MXFP4_GPTOSS`` = ``Mxfp4Tensor::quantize``
+    (crates/nn-gptoss/src/quantize.rs:122-153). `values`: torch tensor (moved to the backend's
+    device as f32) or numpy array; the tail block is zero-padded. Returns (uint8 device tensor
+    of blocks, uint8 device tensor of scale bytes or None). A non-finite value raises
+    ValueOutOfRange where the reference does."""
+    torch = _torch()
+    b = backend or gpu_backend()
+    fmt = QuantFormat(quant_type)
+    dev = torch.device("cuda", b.device)
+    v = torch.as_tensor(values).to(device=dev, dtype=torch.float32).contiguous().reshape(-1)
+    g = GEOMETRY[fmt]
+    nb = (v.numel() + g.elems - 1) // g.elems
+    out = torch.empty(nb * g.bytes, dtype=torch.uint8, device=dev)
+    sc = torch.empty(nb * g.scale_bytes, dtype=torch.uint8, device=dev) if g.scale_bytes else None
+    blocks = ctypes.c_int64()
+    b.check(b._lib.nnq_quantize(b._ctx, int(fmt), v.data_ptr() if v.numel() else None, v.numel(),
+                                out.data_ptr() if nb else None, out.numel(), sc.data_ptr() if sc is not None and nb else None,
+                                sc.numel() if sc is not None else 0, ctypes.byref(blocks),
+                                _stream_ptr(torch.cuda.current_stream(dev))))
+    assert blocks.value == nb
+    return out, sc
+
+
 # --------------------------------------------------------------------------- #
 # the op API
 # --------------------------------------------------------------------------- #
@@ -555,6 +586,20 @@ class QLinear:
             raise BiasMismatch(f"bias shape mismatch: expected [{weight.dims()[0]}], got {list(bias.shape)}")
         self.weight = weight
         self.bias = bias
+
+    @classmethod
+    def from_linear(cls, weight, bias=None, backend: Optional[Backend] = None) -> "QLinear":
+        """``QLinear::from_linear(linear, GgmlDType::Q4K)`` (linear.rs:309-343): quantize an f32
+        [out_features, in_features] weight to nn-core's Q4_K blocks on the device. The product
+        needs blocks that do not straddle rows: in_features must be a multiple of 256."""
+        if len(weight.shape) != 2:
+            raise WeightRank(f"weight must be 2-D [out_features, in_features], got rank {len(weight.shape)}")
+        n, k = int(weight.shape[0]), int(weight.shape[1])
+        if k % 256:
+            raise Unsupported(f"in_features {k} is not a multiple of the Q4_K block (256)")
+        b = backend or gpu_backend()
+        blocks, _ = quantize(weight, QuantFormat.Q4_K_GGML, b)
+        return cls(DeviceWeight.from_device(b, QuantFormat.Q4_K_GGML, blocks, n, k), bias)
 
     def is_quantized(self) -> bool:
         return True

@@ -341,6 +341,26 @@ nnq_status nnq_dequantize_raw(nnq_ctx *ctx, nnq_format fmt, const void *src_dev,
                               (cudaStream_t)stream);
 }
 
+nnq_status nnq_quantize(nnq_ctx *ctx, nnq_format fmt, const float *src_dev, int64_t num_elements, void *dst_dev,
+                        size_t dst_nbytes, void *scales_dev, size_t scales_nbytes, int64_t *blocks, void *stream) {
+    if (!ctx) return NNQ_ERR_INVALID_ARG;
+    if ((int)fmt < 0 || fmt >= NNQ_FORMAT_COUNT) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", (int)fmt);
+    if (fmt != NNQ_Q4_K_GGML && fmt != NNQ_MXFP4_CORE && fmt != NNQ_MXFP4_GPTOSS)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "no encoder for format %d", (int)fmt);
+    if (num_elements < 0) return fail(ctx, NNQ_ERR_INVALID_ARG, "negative element count");
+    Geometry g = geometry(fmt);
+    const int64_t nb = (num_elements + g.elems - 1) / g.elems;
+    if (blocks) *blocks = nb;
+    if (nb == 0) return NNQ_OK;
+    if (!src_dev || !dst_dev || (g.scale_bytes && !scales_dev)) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
+    if (dst_nbytes < (size_t)nb * g.bytes || (g.scale_bytes && scales_nbytes < (size_t)nb * g.scale_bytes))
+        return fail(ctx, NNQ_ERR_DATA_LENGTH, "output holds fewer than %lld blocks", (long long)nb);
+    if (((uintptr_t)dst_dev & 15u) || ((uintptr_t)src_dev & 3u)) return fail(ctx, NNQ_ERR_INVALID_ARG, "output must be 16-byte aligned");
+    nnq_status s = set_device(ctx);
+    if (s != NNQ_OK) return s;
+    return launch_quantize(ctx, fmt, src_dev, num_elements, (uint8_t *)dst_dev, (uint8_t *)scales_dev, (cudaStream_t)stream);
+}
+
 // ---- the product --------------------------------------------------------------------
 
 static nnq_status linear_checked(nnq_ctx *ctx, const nnq_weight *w, const void *x_dev, nnq_dtype x_dt,

@@ -89,6 +89,10 @@ nnq_status check_cuda(nnq_ctx *ctx, cudaError_t e, const char *what);
 nnq_status launch_dequant_raw(nnq_ctx *ctx, int fmt, const uint8_t *src, const uint8_t *scales,
                               int64_t nblocks, float *dst, cudaStream_t stream);
 
+// quantize.cu
+nnq_status launch_quantize(nnq_ctx *ctx, int fmt, const float *src, int64_t n, uint8_t *dst, uint8_t *scales,
+                           cudaStream_t stream);
+
 // linear_generic.cu
 struct LinearArgs {
     const uint8_t *w;       // raw blocks

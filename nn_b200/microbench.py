@@ -2,11 +2,13 @@
 
   python -m nn_b200.microbench linear --fmt q4_k --n 12288 --k 4096 --m 16 [--x f32] [--path tensor]
   python -m nn_b200.microbench moe --layout nk --tokens 64
+  python -m nn_b200.microbench codec --fmt q4_k_ggml --elements 268435456
 
 `linear` rotates `--copies` distinct weights so that every call streams its weight from HBM
 (more bytes in rotation than L2 holds unless --copies says otherwise); `moe` times one
-mixture-of-experts block of the gpt-oss expert geometry. CUDA events around `--reps` calls
-after 3 warm-up calls; one line per run.
+mixture-of-experts block of the gpt-oss expert geometry. `codec` times the block
+encoder (where the reference has one) and the decoder over one flat tensor larger than L2.
+CUDA events around `--reps` calls after 3 warm-up calls; one line per run.
 """
 from __future__ import annotations
 
@@ -128,6 +130,47 @@ def run_moe(a):
     lib.nnq_moe_destroy(h)
 
 
+def run_codec(a):
+    import torch
+
+    from . import api
+    from .formats import GEOMETRY, QuantFormat as Q
+    names = dict(_formats(), q4_k_ggml=Q.Q4_K_GGML, mxfp4_core=Q.MXFP4_CORE, mxfp4_gptoss=Q.MXFP4_GPTOSS, q5_0=Q.Q5_0,
+                 q5_1=Q.Q5_1, q2_k=Q.Q2_K, q3_k=Q.Q3_K, q5_k=Q.Q5_K)
+    fmt = names[a.fmt]
+    b = api.gpu_backend()
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    g = GEOMETRY[fmt]
+    n = a.elements // g.elems * g.elems
+    nb = n // g.elems
+    src = torch.randn(n, device=dev, generator=gen) * 0.05
+    out = torch.empty(n, device=dev)
+    if fmt in (Q.Q4_K_GGML, Q.MXFP4_CORE, Q.MXFP4_GPTOSS):
+        sec = _timed(torch, lambda: api.quantize(src, fmt, b), a.reps)
+        blocks, scales = api.quantize(src, fmt, b)
+        moved = n * 4 + nb * (g.bytes + g.scale_bytes)
+        print(f"encode {a.fmt} {n} weights: {sec * 1e3:.2f} ms, {moved / sec / 1e9:.0f} GB/s "
+              f"({n * 4 / 1e6:.0f} MB read, {nb * (g.bytes + g.scale_bytes) / 1e6:.0f} MB written)", flush=True)
+    else:
+        blocks = torch.randint(0, 256, (nb, g.bytes), dtype=torch.uint8, device=dev, generator=gen)
+        blocks[:, 1] = 0x20   # keeps most f16 scale fields small and finite
+        blocks, scales = blocks.reshape(-1), None
+    decoded = ctypes.c_int64()
+    sp, sn = (scales.data_ptr(), scales.numel()) if scales is not None else (None, 0)
+
+    def dec():
+        b.check(b._lib.nnq_dequantize_raw(b._ctx, int(fmt), blocks.data_ptr(), blocks.numel(), sp, sn, n, out.data_ptr(),
+                                          ctypes.byref(decoded), None))
+
+    sec = _timed(torch, dec, a.reps)
+    b.device_status()
+    moved = n * 4 + nb * (g.bytes + g.scale_bytes)
+    print(f"decode {a.fmt} {n} weights: {sec * 1e3:.2f} ms, {moved / sec / 1e9:.0f} GB/s "
+          f"({nb * (g.bytes + g.scale_bytes) / 1e6:.0f} MB read, {n * 4 / 1e6:.0f} MB written)", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -148,8 +191,12 @@ def main():
     p.add_argument("--inter", type=int, default=2880)
     p.add_argument("--top-k", type=int, default=4)
     p.add_argument("--reps", type=int, default=10)
+    p = sub.add_parser("codec")
+    p.add_argument("--fmt", default="q4_k_ggml")
+    p.add_argument("--elements", type=int, default=1 << 28)
+    p.add_argument("--reps", type=int, default=5)
     a = ap.parse_args()
-    (run_linear if a.cmd == "linear" else run_moe)(a)
+    {"linear": run_linear, "moe": run_moe, "codec": run_codec}[a.cmd](a)
 
 
 if __name__ == "__main__":

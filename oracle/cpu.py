@@ -32,8 +32,7 @@ def build(force: bool = False) -> str:
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(_SO):
-            build()
+        build()   # no-op when the library is newer than its source
         _lib = ctypes.CDLL(_SO)
         _lib.orc_f16_to_f32.restype = ctypes.c_float
         _lib.orc_f16_to_f32.argtypes = [ctypes.c_uint16]
@@ -43,6 +42,14 @@ def lib():
             f = getattr(_lib, name)
             f.restype = ctypes.c_size_t
             f.argtypes = [_u8p, ctypes.c_size_t, ctypes.c_size_t, _f32p]
+        _lib.orc_f32_to_f16.restype = ctypes.c_uint16
+        _lib.orc_f32_to_f16.argtypes = [ctypes.c_float]
+        _lib.orc_quantize_q4_k_ggml.restype = ctypes.c_longlong
+        _lib.orc_quantize_q4_k_ggml.argtypes = [_f32p, ctypes.c_size_t, _u8p]
+        _lib.orc_quantize_mxfp4_core.restype = ctypes.c_longlong
+        _lib.orc_quantize_mxfp4_core.argtypes = [_f32p, ctypes.c_size_t, _u8p]
+        _lib.orc_quantize_mxfp4_gptoss.restype = ctypes.c_longlong
+        _lib.orc_quantize_mxfp4_gptoss.argtypes = [_f32p, ctypes.c_size_t, _u8p, _u8p]
         _lib.orc_mxfp4_core_scale.restype = ctypes.c_float
         _lib.orc_mxfp4_core_scale.argtypes = [ctypes.c_uint8]
         _lib.orc_mxfp4_gptoss_scale.restype = ctypes.c_float
@@ -85,6 +92,47 @@ def _f32(a):
 _DEQ = {0: "orc_dequant_q4_0", 1: "orc_dequant_q4_1", 2: "orc_dequant_q8_0", 3: "orc_dequant_q4_k",
         4: "orc_dequant_q4_k_ggml", 5: "orc_dequant_q6_k", 9: "orc_dequant_q5_0", 10: "orc_dequant_q5_1",
         11: "orc_dequant_q2_k", 12: "orc_dequant_q3_k", 13: "orc_dequant_q5_k"}
+
+
+class ValueOutOfRange(ValueError):
+    """The reference's TensorError::ValueOutOfRange (a non-finite input to an encoder)."""
+
+
+def quantize(fmt: int, values):
+    """f32 -> blocks with the reference's encoders: format 4 = BlockQ4K::quantize, 6 = nn-core
+    quantize_tensor, 8 = nn-gptoss Mxfp4Tensor::quantize. Returns (bytes, scale bytes or None);
+    the tail block is padded with zeros as the reference pads it."""
+    fmt = int(fmt)
+    v, vp = _f32(np.asarray(values, np.float32).reshape(-1))
+    if fmt == 4:
+        out = np.zeros((v.size + 255) // 256 * 144, np.uint8)
+        rc = lib().orc_quantize_q4_k_ggml(vp, v.size, out.ctypes.data_as(_u8p))
+        sc = None
+    elif fmt == 6:
+        out = np.zeros((v.size + 31) // 32 * 17, np.uint8)
+        rc = lib().orc_quantize_mxfp4_core(vp, v.size, out.ctypes.data_as(_u8p))
+        sc = None
+    elif fmt == 8:
+        nb = (v.size + 31) // 32
+        out, sc = np.zeros(nb * 16, np.uint8), np.zeros(nb, np.uint8)
+        rc = lib().orc_quantize_mxfp4_gptoss(vp, v.size, out.ctypes.data_as(_u8p), sc.ctypes.data_as(_u8p))
+    else:
+        raise ValueError("the reference has encoders for formats 4, 6 and 8 only")
+    if rc < 0:
+        raise ValueOutOfRange("non-finite value")
+    return out, sc
+
+
+def mxfp4_core_scale(e: int) -> float:
+    return float(lib().orc_mxfp4_core_scale(int(e)))
+
+
+def mxfp4_gptoss_scale(e: int) -> float:
+    return float(lib().orc_mxfp4_gptoss_scale(int(e)))
+
+
+def f32_to_f16(v: float) -> int:
+    return int(lib().orc_f32_to_f16(float(v)))
 
 
 def f16_to_f32(bits: int) -> float:

@@ -623,6 +623,219 @@ ORC_API void orc_nncpu_linear(const float *x, const float *w, const float *bias,
 ORC_API int orc_have_avx2(void) { return have_avx2(); }
 
 /* ------------------------------------------------------------------------- */
+/* f32 -> block encoders                                                     */
+/* ------------------------------------------------------------------------- */
+
+/* binary32 -> binary16, round to nearest even, overflow to infinity, NaN kept quiet:
+ * half::f16::from_f32 as used at crates/nn-core/src/layers/quantized/linear.rs:137-138. */
+static uint16_t f32_to_f16_bits(float f) {
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint16_t sign = (uint16_t)((x >> 16) & 0x8000u);
+    uint32_t exp = (x >> 23) & 0xFFu, man = x & 0x7FFFFFu;
+    if (exp == 0xFF) return (uint16_t)(sign | 0x7C00u | (man ? (0x0200u | (man >> 13)) : 0));
+    int e = (int)exp - 127 + 15;
+    if (e >= 31) return (uint16_t)(sign | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return sign;                 /* below half of the smallest subnormal */
+        man |= 0x800000u;
+        int shift = 14 - e;                       /* 14 .. 24 */
+        uint32_t h = man >> shift, rem = man & ((1u << shift) - 1), half = 1u << (shift - 1);
+        if (rem > half || (rem == half && (h & 1))) h++;
+        return (uint16_t)(sign | h);
+    }
+    uint32_t h = ((uint32_t)e << 10) | (man >> 13), rem = man & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (h & 1))) h++;   /* a carry into the exponent is correct */
+    return (uint16_t)(sign | h);
+}
+
+ORC_API uint16_t orc_f32_to_f16(float f) { return f32_to_f16_bits(f); }
+
+/* nearest_int (linear.rs:178-192): round half away from zero; non-finite or outside i32 is an error. */
+static int q4k_nearest_int(float v, int *err) {
+    if (!isfinite(v)) { *err = 1; return 0; }
+    float r = roundf(v);
+    if (r < -2147483648.0f || r > 2147483648.0f) { *err = 1; return 0; }
+    if (r >= 2147483648.0f) return INT32_MAX;     /* `as i32` saturates */
+    return (int)r;
+}
+
+/* f32::min / f32::max folds of the reference: NaN operands are ignored, ties keep the accumulator. */
+static float fold_min(float acc, float v) { return v < acc ? v : acc; }
+static float fold_max(float acc, float v) { return v > acc ? v : acc; }
+
+/* make_qkx1_quants(nmax, ntry, x[32]) (linear.rs:195-254): (scale, min) of one sub-block. */
+static void q4k_make_qkx1(int nmax, int ntry, const float *x, float *scale_out, float *min_out, int *err) {
+    const int n = 32;
+    uint8_t l[32] = {0};
+    float mn = INFINITY, mx = -INFINITY;
+    for (int i = 0; i < n; i++) { mn = fold_min(mn, x[i]); mx = fold_max(mx, x[i]); }
+    if (mx == mn) {
+        if (mn >= 0.0f) { *scale_out = nmax > 0 ? mn / (float)nmax : 0.0f; *min_out = 0.0f; }
+        else { *scale_out = 0.0f; *min_out = -mn; }
+        return;
+    }
+    float min = fold_min(mn, 0.0f);
+    float iscale = (float)nmax / (mx - min);
+    float scale = 1.0f / iscale;
+    for (int t = 0; t < ntry; t++) {
+        float sumlx = 0.0f;
+        int suml2 = 0, changed = 0;
+        for (int i = 0; i < n; i++) {
+            int li = q4k_nearest_int(iscale * (x[i] - min), err);
+            if (*err) return;
+            li = li < 0 ? 0 : (li > nmax ? nmax : li);
+            if ((uint8_t)li != l[i]) { l[i] = (uint8_t)li; changed = 1; }
+            sumlx += (x[i] - min) * (float)li;
+            suml2 += li * li;
+        }
+        if (suml2 == 0) { *scale_out = 0.0f; *min_out = 0.0f; return; }
+        scale = sumlx / (float)suml2;
+        if (scale == 0.0f) { *scale_out = 0.0f; *min_out = -min; return; }
+        float sum = 0.0f;
+        for (int i = 0; i < n; i++) sum += x[i] - scale * (float)l[i];
+        min = fold_min(sum / (float)n, 0.0f);
+        iscale = 1.0f / scale;
+        if (!changed) break;
+    }
+    *scale_out = scale;
+    *min_out = -min;
+}
+
+/* BlockQ4K::quantize (linear.rs:95-162) over a flat f32 buffer padded with zeros to whole
+ * 256-weight blocks as QLinear::from_linear does (linear.rs:318-336). Output: 144-byte blocks
+ * in nn-core's element order and scale packing (format code 4). Returns the number of blocks
+ * written, or -1 when the reference returns ValueOutOfRange. */
+ORC_API long long orc_quantize_q4_k_ggml(const float *src, size_t num_elements, uint8_t *out) {
+    size_t nb = (num_elements + 255) / 256;
+    for (size_t b = 0; b < nb; b++) {
+        float v[256];
+        for (int i = 0; i < 256; i++) v[i] = b * 256 + i < num_elements ? src[b * 256 + i] : 0.0f;
+        uint8_t *blk = out + b * 144, *S = blk + 4, *qs = blk + 16;
+        memset(blk, 0, 144);
+        float ss[8], sm[8];
+        int err = 0;
+        for (int j = 0; j < 8; j++) {
+            q4k_make_qkx1(15, 5, v + 32 * j, &ss[j], &sm[j], &err);
+            if (err) return -1;
+        }
+        float max_scale = 0.0f, max_min = 0.0f;
+        for (int j = 0; j < 8; j++) { max_scale = fold_max(max_scale, ss[j]); max_min = fold_max(max_min, sm[j]); }
+        float inv_scale = max_scale > 0.0f ? 63.0f / max_scale : 0.0f;
+        float inv_min = max_min > 0.0f ? 63.0f / max_min : 0.0f;
+        uint8_t LS[8], LM[8];
+        for (int j = 0; j < 8; j++) {
+            int a = q4k_nearest_int(inv_scale * ss[j], &err), c = q4k_nearest_int(inv_min * sm[j], &err);
+            if (err) return -1;
+            uint8_t ls = (uint8_t)a, lm = (uint8_t)c;     /* `as u8` keeps the low byte */
+            ls = ls < 63 ? ls : 63;
+            lm = lm < 63 ? lm : 63;
+            LS[j] = ls; LM[j] = lm;
+            if (j < 4) { S[j] = ls; S[j + 4] = lm; }
+            else {
+                S[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                S[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                S[j] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        uint16_t dh = f32_to_f16_bits(max_scale / 63.0f), mh = f32_to_f16_bits(max_min / 63.0f);
+        blk[0] = (uint8_t)dh; blk[1] = (uint8_t)(dh >> 8); blk[2] = (uint8_t)mh; blk[3] = (uint8_t)(mh >> 8);
+        uint8_t l[256] = {0};
+        for (int j = 0; j < 8; j++) {
+            float bd = f16_bits_to_f32(dh) * (float)LS[j];
+            if (bd != 0.0f) {
+                float bm = f16_bits_to_f32(mh) * (float)LM[j];
+                for (int i = 0; i < 32; i++) {
+                    int q = q4k_nearest_int((v[32 * j + i] + bm) / bd, &err);
+                    if (err) return -1;
+                    l[32 * j + i] = (uint8_t)(q < 0 ? 0 : (q > 15 ? 15 : q));
+                }
+            }
+        }
+        for (int j = 0; j < 256; j += 64)
+            for (int k = 0; k < 32; k++) qs[j / 2 + k] = (uint8_t)(l[j + k] | (l[j + k + 32] << 4));
+    }
+    return (long long)nb;
+}
+
+/* Nearest E2M1 magnitude by minimum distance, first wins on ties
+ * (encode_e1m2, mxfp4.rs:94-117; quantize_to_fp4, crates/nn-gptoss/src/quantize.rs:93-116). */
+static uint8_t nearest_e2m1(float abs_scaled) {
+    uint8_t best = 0;
+    float best_dist = 3.40282347e+38f;
+    for (uint8_t i = 0; i < 8; i++) {
+        float dist = fabsf(abs_scaled - E2M1_MAG[i]);
+        if (dist < best_dist) { best_dist = dist; best = i; }
+    }
+    return best;
+}
+
+/* quantize_tensor / quantize_block (mxfp4.rs:183-207,307-329) into 17-byte blocks (format code 6):
+ * shared exponent = clamp(ceil(log2(max|v| / 6)) + 127, 0, 254), 0 for an all-zero block; the tail
+ * block is padded with zeros. Returns the number of blocks, or -1 for a non-finite input. */
+ORC_API long long orc_quantize_mxfp4_core(const float *src, size_t num_elements, uint8_t *out) {
+    size_t nb = (num_elements + 31) / 32;
+    for (size_t b = 0; b < nb; b++) {
+        float v[32];
+        for (int i = 0; i < 32; i++) {
+            v[i] = b * 32 + i < num_elements ? src[b * 32 + i] : 0.0f;
+            if (!isfinite(v[i])) return -1;
+        }
+        float max_abs = 0.0f;
+        for (int i = 0; i < 32; i++) { float a = fabsf(v[i]); if (a > max_abs) max_abs = a; }
+        uint8_t e = 0;
+        if (max_abs != 0.0f) {
+            int eb = (int)ceilf(log2f(max_abs / 6.0f)) + 127;
+            e = (uint8_t)(eb < 0 ? 0 : (eb > 254 ? 254 : eb));
+        }
+        float scale = orc_mxfp4_core_scale(e);
+        uint8_t *blk = out + b * 17;
+        memset(blk, 0, 17);
+        blk[0] = e;
+        for (int i = 0; i < 32; i++) {
+            uint8_t code = 0;
+            if (!(v[i] == 0.0f || scale == 0.0f))
+                code = (uint8_t)((v[i] < 0.0f ? 8 : 0) | nearest_e2m1(fabsf(v[i]) / scale));
+            blk[1 + i / 2] |= (uint8_t)(i % 2 == 0 ? code : code << 4);
+        }
+    }
+    return (long long)nb;
+}
+
+/* Mxfp4Tensor::quantize (crates/nn-gptoss/src/quantize.rs:64-153) into data[nb*16] + scales[nb]
+ * (format code 8): scale byte = biased exponent of max|v| minus 2 (0 for zero / subnormal maxima,
+ * at most 254), non-finite values are skipped in the maximum and encode as 0; the even element
+ * goes to the HIGH nibble. Returns the number of blocks. */
+ORC_API long long orc_quantize_mxfp4_gptoss(const float *src, size_t num_elements, uint8_t *data, uint8_t *scales) {
+    size_t nb = (num_elements + 31) / 32;
+    for (size_t b = 0; b < nb; b++) {
+        float v[32];
+        for (int i = 0; i < 32; i++) v[i] = b * 32 + i < num_elements ? src[b * 32 + i] : 0.0f;
+        float max_abs = 0.0f;
+        for (int i = 0; i < 32; i++) { float a = fabsf(v[i]); if (isfinite(a) && a > max_abs) max_abs = a; }
+        uint8_t sb = 0;
+        if (isfinite(max_abs) && max_abs > 0.0f) {
+            uint32_t bits;
+            memcpy(&bits, &max_abs, 4);
+            uint32_t be = (bits >> 23) & 0xFFu;
+            if (be != 0) { uint32_t se = be >= 2 ? be - 2 : 0; sb = (uint8_t)(se < 254 ? se : 254); }
+        }
+        scales[b] = sb;
+        float scale = orc_mxfp4_gptoss_scale(sb);
+        for (int p = 0; p < 16; p++) {
+            uint8_t c[2];
+            for (int h = 0; h < 2; h++) {
+                float x = v[2 * p + h];
+                c[h] = 0;
+                if (isfinite(x) && scale > 0.0f) c[h] = (uint8_t)(nearest_e2m1(fabsf(x) / scale) | (x < 0.0f ? 8 : 0));
+            }
+            data[b * 16 + p] = (uint8_t)((c[0] << 4) | c[1]);
+        }
+    }
+    return (long long)nb;
+}
+
+/* ------------------------------------------------------------------------- */
 /* the reference's CPU forward of one quantized linear, as it is timed        */
 /* ------------------------------------------------------------------------- */
 
