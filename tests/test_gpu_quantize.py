@@ -19,7 +19,12 @@ ENC = [Q.Q4_K_GGML, Q.MXFP4_CORE, Q.MXFP4_GPTOSS]
 
 def _same(fmt, v):
     v = np.asarray(v, f32)
-    want, want_sc = orc.quantize(fmt, v)
+    try:
+        want, want_sc = orc.quantize(fmt, v)
+    except orc.ValueOutOfRange:      # e.g. Q4_K on values whose f16 super-block scale overflows
+        with pytest.raises(api.ValueOutOfRange):
+            api.quantize(torch.from_numpy(v), fmt)
+        return None, None
     got, got_sc = api.quantize(torch.from_numpy(v), fmt)
     got = got.cpu().numpy()
     bad = np.nonzero(got != want)[0]
@@ -99,9 +104,11 @@ def test_q4_k_sub_block_patterns():
         elif kind == 11:
             b = (s.uniform(256) * 15).astype(f32)
         parts.append(b.astype(f32))
-    blocks, _ = _same(Q.Q4_K_GGML, np.concatenate(parts))
-    out = orc.dequantize(Q.Q4_K_GGML, blocks, 12 * 256)
-    assert np.all(np.isfinite(out))
+    for part in parts:
+        _same(Q.Q4_K_GGML, part)
+    blocks, _ = _same(Q.Q4_K_GGML, np.concatenate(parts[:6] + parts[7:]))
+    out = orc.dequantize(Q.Q4_K_GGML, blocks, 11 * 256)
+    assert blocks is not None and np.all(np.isfinite(out[:11 * 256]))
 
 
 @pytest.mark.parametrize("fmt", ENC)
