@@ -57,8 +57,9 @@ def test_rounding_edges(fmt):
     s = F.Stream(91)
     # block maxima on and next to powers of two and 6 * 2^e, over a wide exponent range; ties between
     # neighbouring magnitudes; signed zeros; subnormals
-    blocks = []
+    compared = 0
     for e in list(range(-140, 128, 7)) + [-126, -127, -1, 0, 1]:
+        blocks = []
         for m in (1.0, 1.5, 6.0 / 4.0, 1.25, 1.75):
             top = f32(m) * f32(2.0) ** f32(e) if e > -127 else f32(m * 2.0 ** -126) * f32(2.0 ** (e + 126))
             if not np.isfinite(top) or top > 3.0e38:
@@ -69,10 +70,15 @@ def test_rounding_edges(fmt):
                 b = (s.uniform(32) * 2 - 1).astype(f32) * f32(t)
                 b[0] = t
                 b[1] = -t * f32(0.5)
-                b[2:10] = f32(t) * np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 0.125], f32) / f32(6.0)
+                b[2:10] = (f32(t) / f32(6.0)) * np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 0.125], f32)
                 b[10], b[11] = 0.0, -0.0
+                assert np.all(np.isfinite(b))
                 blocks.append(b)
-    _same(fmt, np.concatenate(blocks))
+        if blocks:   # per exponent, so that a range the reference rejects (Q4_K: f16 scale overflow) stays local
+            compared += _same(fmt, np.concatenate(blocks))[0] is not None
+    # nn-core's Q4_K encoder rejects blocks whose f16 super-block scale overflows (inf * 0 reaches nearest_int);
+    # there the device must raise too, which _same checked
+    assert compared >= (24 if fmt == Q.Q4_K_GGML else 44)
 
 
 def test_q4_k_sub_block_patterns():
