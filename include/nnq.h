@@ -191,6 +191,29 @@ NNQ_API nnq_status nnq_quantize(nnq_ctx *ctx, nnq_format fmt, const float *src_d
                                 void *dst_dev, size_t dst_nbytes, void *scales_dev, size_t scales_nbytes,
                                 int64_t *blocks, void *stream);
 
+/* ---- INT8 per-channel weights (W8A16) ------------------------------------------------ */
+
+/* Buffers follow the reference's GPU kernel contract (crates/nn-metal/src/int8_gemm_msl.rs:35-52):
+ * W uint8 [N, K] read as signed bytes, scale f32 [N], zero_point int32 [N];
+ * w = (f32(q) - f32(zero_point)) * scale. All pointers are device pointers.
+ *
+ * nnq_int8_quantize_per_channel: quantize_per_channel + compute_channel_params
+ * (crates/nn-core/src/layers/quantized/int8.rs:82-137,187-221); mode 0 = Int8Mode::Symmetric,
+ * 1 = Asymmetric; byte-identical outputs; a non-finite weight is NNQ_ERR_VALUE_OUT_OF_RANGE.
+ * Waits for the stream (a load-time step).
+ * nnq_int8_dequantize_per_channel: dequantize_per_channel (int8.rs:146-185), bit-identical.
+ * nnq_int8_linear: Int8Linear::forward (int8_linear.rs:175-213) without materialising the f32
+ * weight: y[M, N] = x[M, K] . w^T (+ bias), f32 accumulation. Eight tokens share one pass
+ * over the weights; larger M repeats the pass. */
+NNQ_API nnq_status nnq_int8_quantize_per_channel(nnq_ctx *ctx, const float *w_dev, int64_t n, int64_t k, int mode,
+                                                 void *q_dev, float *scale_dev, int32_t *zp_dev, void *stream);
+NNQ_API nnq_status nnq_int8_dequantize_per_channel(nnq_ctx *ctx, const void *q_dev, const float *scale_dev,
+                                                   const int32_t *zp_dev, int64_t n, int64_t k, float *dst_dev,
+                                                   void *stream);
+NNQ_API nnq_status nnq_int8_linear(nnq_ctx *ctx, const void *q_dev, const float *scale_dev, const int32_t *zp_dev,
+                                   int64_t n, int64_t k, const void *x_dev, nnq_dtype x_dt, int64_t m,
+                                   const float *bias_dev, void *y_dev, nnq_dtype y_dt, void *stream);
+
 /* ---- dequantization (bit-exact gate) ---------------------------------------------- */
 
 /* Dequantize a weight to f32 [N, K] on the device. Bit-identical to the reference's

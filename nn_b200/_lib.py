@@ -39,6 +39,10 @@ SIGNATURES = {
                                    ctypes.POINTER(c_int64), c_void_p]),
     "nnq_quantize": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_size_t, c_void_p, c_size_t,
                              ctypes.POINTER(c_int64), c_void_p]),
+    "nnq_int8_quantize_per_channel": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nnq_int8_dequantize_per_channel": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "nnq_int8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p,
+                                c_void_p, c_int, c_void_p]),
     "nnq_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
     "nnq_linear_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int]),
     "nnq_linear_batch": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int64,

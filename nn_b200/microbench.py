@@ -3,6 +3,7 @@
   python -m nn_b200.microbench linear --fmt q4_k --n 12288 --k 4096 --m 16 [--x f32] [--path tensor]
   python -m nn_b200.microbench moe --layout nk --tokens 64
   python -m nn_b200.microbench codec --fmt q4_k_ggml --elements 268435456
+  python -m nn_b200.microbench int8 --n 12288 --k 4096 --m 1
 
 `linear` rotates `--copies` distinct weights so that every call streams its weight from HBM
 (more bytes in rotation than L2 holds unless --copies says otherwise); `moe` times one
@@ -171,6 +172,35 @@ def run_codec(a):
           f"({nb * (g.bytes + g.scale_bytes) / 1e6:.0f} MB read, {n * 4 / 1e6:.0f} MB written)", flush=True)
 
 
+def run_int8(a):
+    import torch
+
+    from . import api, int8
+    b = api.gpu_backend()
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    layers = []
+    for _ in range(a.copies):
+        q = torch.randint(0, 256, (a.n, a.k), dtype=torch.uint8, device=dev, generator=gen)
+        p = int8.Int8QuantParams(torch.rand(a.n, device=dev, generator=gen) * 1e-3,
+                                 torch.randint(-20, 20, (a.n,), dtype=torch.int32, device=dev, generator=gen))
+        layers.append(int8.Int8Linear(q, p, None, b))
+    x = torch.randn(a.m, a.k, device=dev, generator=gen)
+    if a.x == "bf16":
+        x = x.to(torch.bfloat16)
+    i = [0]
+
+    def one():
+        layers[i[0] % a.copies].forward(x, check_finite=False)
+        i[0] += 1
+
+    sec = _timed(torch, one, a.reps)
+    algo = a.n * a.k + a.n * 8 + a.m * a.k * (4 if a.x == "f32" else 2) + a.m * a.n * 4
+    print(f"int8 linear N={a.n} K={a.k} M={a.m} x={a.x}: {sec * 1e6:.1f} us, {algo / sec / 1e9:.0f} GB/s algorithmic, "
+          f"{2.0 * a.m * a.n * a.k / sec / 1e12:.2f} TFLOP/s", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -195,8 +225,15 @@ def main():
     p.add_argument("--fmt", default="q4_k_ggml")
     p.add_argument("--elements", type=int, default=1 << 28)
     p.add_argument("--reps", type=int, default=5)
+    p = sub.add_parser("int8")
+    p.add_argument("--n", type=int, default=12288)
+    p.add_argument("--k", type=int, default=4096)
+    p.add_argument("--m", type=int, default=1)
+    p.add_argument("--x", default="f32", choices=["bf16", "f32"])
+    p.add_argument("--copies", type=int, default=8)
+    p.add_argument("--reps", type=int, default=40)
     a = ap.parse_args()
-    {"linear": run_linear, "moe": run_moe, "codec": run_codec}[a.cmd](a)
+    {"linear": run_linear, "moe": run_moe, "codec": run_codec, "int8": run_int8}[a.cmd](a)
 
 
 if __name__ == "__main__":

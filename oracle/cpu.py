@@ -50,6 +50,9 @@ def lib():
         _lib.orc_quantize_mxfp4_core.argtypes = [_f32p, ctypes.c_size_t, _u8p]
         _lib.orc_quantize_mxfp4_gptoss.restype = ctypes.c_longlong
         _lib.orc_quantize_mxfp4_gptoss.argtypes = [_f32p, ctypes.c_size_t, _u8p, _u8p]
+        _lib.orc_int8_quantize_per_channel.restype = ctypes.c_int
+        _lib.orc_int8_quantize_per_channel.argtypes = [_f32p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, _u8p, _f32p, _i32p]
+        _lib.orc_int8_dequantize_per_channel.argtypes = [_u8p, _f32p, _i32p, ctypes.c_size_t, ctypes.c_size_t, _f32p]
         _lib.orc_mxfp4_core_scale.restype = ctypes.c_float
         _lib.orc_mxfp4_core_scale.argtypes = [ctypes.c_uint8]
         _lib.orc_mxfp4_gptoss_scale.restype = ctypes.c_float
@@ -121,6 +124,29 @@ def quantize(fmt: int, values):
     if rc < 0:
         raise ValueOutOfRange("non-finite value")
     return out, sc
+
+
+def int8_quantize_per_channel(w, mode: int):
+    """(q uint8 [n, k], scale f32 [n], zero_point i32 [n]) of an f32 [n, k] weight; mode 0 symmetric, 1 asymmetric."""
+    w = np.ascontiguousarray(w, np.float32)
+    n, k = w.shape
+    q, sc, zp = np.zeros((n, k), np.uint8), np.zeros(n, np.float32), np.zeros(n, np.int32)
+    rc = lib().orc_int8_quantize_per_channel(w.ctypes.data_as(_f32p), n, k, int(mode), q.ctypes.data_as(_u8p),
+                                             sc.ctypes.data_as(_f32p), zp.ctypes.data_as(_i32p))
+    if rc != 0:
+        raise ValueOutOfRange("non-finite weight value")
+    return q, sc, zp
+
+
+def int8_dequantize_per_channel(q, scale, zp) -> np.ndarray:
+    q = np.ascontiguousarray(q, np.uint8)
+    scale = np.ascontiguousarray(scale, np.float32)
+    zp = np.ascontiguousarray(zp, np.int32)
+    n, k = q.shape
+    out = np.zeros((n, k), np.float32)
+    lib().orc_int8_dequantize_per_channel(q.ctypes.data_as(_u8p), scale.ctypes.data_as(_f32p), zp.ctypes.data_as(_i32p), n, k,
+                                          out.ctypes.data_as(_f32p))
+    return out
 
 
 def mxfp4_core_scale(e: int) -> float:

@@ -836,6 +836,69 @@ ORC_API long long orc_quantize_mxfp4_gptoss(const float *src, size_t num_element
 }
 
 /* ------------------------------------------------------------------------- */
+/* INT8 per-channel weights (W8A16)                                          */
+/* ------------------------------------------------------------------------- */
+
+/* `as i32` of an f32: saturating, NaN -> 0. */
+static int32_t f32_as_i32(float v) {
+    if (isnan(v)) return 0;
+    if (v >= 2147483648.0f) return INT32_MAX;
+    if (v <= -2147483648.0f) return INT32_MIN;
+    return (int32_t)v;
+}
+
+/* quantize_per_channel (crates/nn-core/src/layers/quantized/int8.rs:82-137) with
+ * compute_channel_params (int8.rs:187-221). mode 0 = symmetric (scale = max|w| / 127, zero
+ * point 0), 1 = asymmetric (scale = (max - min) / 255, zero point = round(-128 - min / scale)).
+ * q = clamp(round(w / scale + zp), -128, 127), 0 where scale == 0. Returns 0, or -1 when a
+ * weight is not finite (ValueOutOfRange). */
+ORC_API int orc_int8_quantize_per_channel(const float *w, size_t n, size_t k, int mode, uint8_t *q,
+                                          float *scale, int32_t *zp) {
+    for (size_t i = 0; i < n * k; i++)
+        if (!isfinite(w[i])) return -1;
+    for (size_t r = 0; r < n; r++) {
+        const float *row = w + r * k;
+        float sc = 0.0f;
+        int32_t z = 0;
+        if (k != 0) {
+            if (mode == 0) {
+                float abs_max = 0.0f;
+                for (size_t i = 0; i < k; i++) abs_max = fold_max(abs_max, fabsf(row[i]));
+                if (abs_max != 0.0f) sc = abs_max / 127.0f;
+            } else {
+                float mn = INFINITY, mx = -INFINITY;
+                for (size_t i = 0; i < k; i++) { mn = fold_min(mn, row[i]); mx = fold_max(mx, row[i]); }
+                float range = mx - mn;
+                if (range != 0.0f) {
+                    sc = range / 255.0f;
+                    z = f32_as_i32(roundf(-128.0f - mn / sc));
+                }
+            }
+        }
+        scale[r] = sc;
+        zp[r] = z;
+        for (size_t i = 0; i < k; i++) {
+            int8_t v = 0;
+            if (sc != 0.0f) {
+                float qf = roundf(row[i] / sc + (float)z);
+                qf = qf < -128.0f ? -128.0f : (qf > 127.0f ? 127.0f : qf);
+                v = (int8_t)qf;
+            }
+            q[r * k + i] = (uint8_t)v;
+        }
+    }
+    return 0;
+}
+
+/* dequantize_per_channel (int8.rs:146-185): w = (f32(q as i8) - f32(zp)) * scale. */
+ORC_API void orc_int8_dequantize_per_channel(const uint8_t *q, const float *scale, const int32_t *zp, size_t n,
+                                             size_t k, float *out) {
+    for (size_t r = 0; r < n; r++)
+        for (size_t i = 0; i < k; i++)
+            out[r * k + i] = ((float)(int8_t)q[r * k + i] - (float)zp[r]) * scale[r];
+}
+
+/* ------------------------------------------------------------------------- */
 /* the reference's CPU forward of one quantized linear, as it is timed        */
 /* ------------------------------------------------------------------------- */
 
