@@ -203,7 +203,7 @@ NNQ_API nnq_status nnq_quantize(nnq_ctx *ctx, nnq_format fmt, const float *src_d
  * Waits for the stream (a load-time step).
  * nnq_int8_dequantize_per_channel: dequantize_per_channel (int8.rs:146-185), bit-identical.
  * nnq_int8_linear: Int8Linear::forward (int8_linear.rs:175-213) without materialising the f32
- * weight: y[M, N] = x[M, K] . w^T (+ bias), f32 accumulation. Eight tokens share one pass
+ * weight: y[M, N] = x[M, K] . w^T (+ bias), f32 accumulation. Four tokens share one pass
  * over the weights; larger M repeats the pass. */
 NNQ_API nnq_status nnq_int8_quantize_per_channel(nnq_ctx *ctx, const float *w_dev, int64_t n, int64_t k, int mode,
                                                  void *q_dev, float *scale_dev, int32_t *zp_dev, void *stream);

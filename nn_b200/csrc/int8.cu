@@ -6,8 +6,8 @@
 //
 // The product streams one byte per weight: a warp owns an output row, lanes take 16-byte chunks
 // of it, bytes become floats with one byte-permute and one subtraction (the zero point rides in the
-// subtraction's constant), the row's scale is applied once to the reduced sum. HBM-bound at one
-// token; up to eight tokens share a pass over the weights.
+// subtraction's constant), the row's scale is applied once to the reduced sum; four rows share each
+// load of the activations and up to four tokens share a pass over the weights.
 #include <cuda_bf16.h>
 #include <math.h>
 
@@ -132,58 +132,83 @@ __device__ __forceinline__ float x_at(const __nv_bfloat16 *p, int64_t i) { retur
 __device__ __forceinline__ void y_put(float *p, int64_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void y_put(__nv_bfloat16 *p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+constexpr int kI8LinThreads = 128;
+constexpr int kI8Rows = 4;   // output rows per warp: one load of the activations serves four rows
+
 // y[t][n] = scale[n] * sum_k (q[n][k] - zp[n]) * x[t][k] (+ bias[n]) for tokens [t0, t0 + MT)
 template <typename XT, typename YT, int MT, bool VEC>
-__global__ void __launch_bounds__(kI8Threads)
+__global__ void __launch_bounds__(kI8LinThreads)
 int8_linear_kernel(const uint8_t *__restrict__ q, const float *__restrict__ scale, const int *__restrict__ zp,
                    const XT *__restrict__ x, const float *__restrict__ bias, YT *__restrict__ y, int64_t m, int64_t n,
                    int64_t k, int64_t t0) {
+    constexpr int R = kI8Rows;
     const int lane = threadIdx.x & 31;
-    const int64_t warps = (int64_t)gridDim.x * (kI8Threads / 32);
-    for (int64_t r = (int64_t)blockIdx.x * (kI8Threads / 32) + (threadIdx.x >> 5); r < n; r += warps) {
-        const uint8_t *row = q + r * k;
-        const int z = __ldg(zp + r);
-        const float zf = (float)z;
-        // float(byte ^ 0x80) + 2^23 minus this constant = q - zp, exact while the constant is
-        const bool fast = z > -4000000 && z < 4000000;
-        const float c = 8388608.0f + 128.0f + zf;
-        float acc[MT];
+    const int64_t units = (n + R - 1) / R;
+    const int64_t warps = (int64_t)gridDim.x * (kI8LinThreads / 32);
+    for (int64_t u = (int64_t)blockIdx.x * (kI8LinThreads / 32) + (threadIdx.x >> 5); u < units; u += warps) {
+        const uint8_t *row[R];
+        float zf[R], c[R];
+        bool fast = true;
 #pragma unroll
-        for (int t = 0; t < MT; t++) acc[t] = 0.0f;
+        for (int r = 0; r < R; r++) {
+            const int64_t rr = u * R + r < n ? u * R + r : n - 1;   // rows past the end repeat the last one; not stored
+            row[r] = q + rr * k;
+            const int z = __ldg(zp + rr);
+            zf[r] = (float)z;
+            // float(byte ^ 0x80) + 2^23 minus this constant = q - zp, exact while the constant is
+            c[r] = 8388608.0f + 128.0f + zf[r];
+            fast = fast && z > -4000000 && z < 4000000;
+        }
+        float acc[R][MT];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int t = 0; t < MT; t++) acc[r][t] = 0.0f;
         const int64_t kv = VEC ? (k & ~(int64_t)15) : 0;
         for (int64_t k0 = (int64_t)lane * 16; k0 < kv; k0 += 32 * 16) {
-            const uint4 qq = __ldg(reinterpret_cast<const uint4 *>(row + k0));
-            const uint32_t qw[4] = {qq.x ^ 0x80808080u, qq.y ^ 0x80808080u, qq.z ^ 0x80808080u, qq.w ^ 0x80808080u};
-            float wv[16];
+            uint4 raw[R];
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                float f = __uint_as_float(__byte_perm(qw[i >> 2], 0x4B000000u, 0x7540u + (i & 3)));
-                wv[i] = fast ? __fsub_rn(f, c) : __fsub_rn(__fsub_rn(f, 8388736.0f), zf);
-            }
+            for (int r = 0; r < R; r++) raw[r] = __ldg(reinterpret_cast<const uint4 *>(row[r] + k0));
+            float xv[MT][16];
 #pragma unroll
             for (int t = 0; t < MT; t++) {
-                if (t0 + t < m) {
-                    float xv[16];
-                    load_x16<XT>(x + (t0 + t) * k + k0, xv);
+                const int64_t tt = t0 + t < m ? t0 + t : m - 1;
+                load_x16<XT>(x + tt * k + k0, xv[t]);
+            }
 #pragma unroll
-                    for (int i = 0; i < 16; i++) acc[t] = fmaf(wv[i], xv[i], acc[t]);
+            for (int r = 0; r < R; r++) {
+                const uint32_t qw[4] = {raw[r].x ^ 0x80808080u, raw[r].y ^ 0x80808080u, raw[r].z ^ 0x80808080u, raw[r].w ^ 0x80808080u};
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float f = __uint_as_float(__byte_perm(qw[i >> 2], 0x4B000000u, 0x7540u + (i & 3)));
+                    const float wv = fast ? __fsub_rn(f, c[r]) : __fsub_rn(__fsub_rn(f, 8388736.0f), zf[r]);
+#pragma unroll
+                    for (int t = 0; t < MT; t++) acc[r][t] = fmaf(wv, xv[t][i], acc[r][t]);
                 }
             }
         }
         for (int64_t i = kv + lane; i < k; i += 32) {   // ragged tail, or everything when rows are not 16-byte aligned
-            const float wv = __fsub_rn((float)(int8_t)__ldg(row + i), zf);
 #pragma unroll
-            for (int t = 0; t < MT; t++)
-                if (t0 + t < m) acc[t] = fmaf(wv, x_at(x, (t0 + t) * k + i), acc[t]);
+            for (int r = 0; r < R; r++) {
+                const float wv = __fsub_rn((float)(int8_t)__ldg(row[r] + i), zf[r]);
+#pragma unroll
+                for (int t = 0; t < MT; t++) {
+                    const int64_t tt = t0 + t < m ? t0 + t : m - 1;
+                    acc[r][t] = fmaf(wv, x_at(x, tt * k + i), acc[r][t]);
+                }
+            }
         }
-        const float sc = __ldg(scale + r);
-        const float b = bias ? __ldg(bias + r) : 0.0f;
 #pragma unroll
-        for (int t = 0; t < MT; t++) {
-            float v = acc[t];
+        for (int r = 0; r < R; r++) {
+            const int64_t rr = u * R + r;
 #pragma unroll
-            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && t0 + t < m) y_put(y, (t0 + t) * n + r, fmaf(v, sc, b));
+            for (int t = 0; t < MT; t++) {
+                float v = acc[r][t];
+#pragma unroll
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && rr < n && t0 + t < m)
+                    y_put(y, (t0 + t) * n + rr, fmaf(v, __ldg(scale + rr), bias ? __ldg(bias + rr) : 0.0f));
+            }
         }
     }
 }
@@ -191,19 +216,18 @@ int8_linear_kernel(const uint8_t *__restrict__ q, const float *__restrict__ scal
 template <typename XT, typename YT, int MT>
 static void launch_i8(const uint8_t *q, const float *scale, const int *zp, const void *x, const float *bias, void *y,
                       int64_t m, int64_t n, int64_t k, int64_t t0, int grid, bool vec, cudaStream_t st) {
-    if (vec) int8_linear_kernel<XT, YT, MT, true><<<grid, kI8Threads, 0, st>>>(q, scale, zp, (const XT *)x, bias, (YT *)y, m, n, k, t0);
-    else int8_linear_kernel<XT, YT, MT, false><<<grid, kI8Threads, 0, st>>>(q, scale, zp, (const XT *)x, bias, (YT *)y, m, n, k, t0);
+    if (vec) int8_linear_kernel<XT, YT, MT, true><<<grid, kI8LinThreads, 0, st>>>(q, scale, zp, (const XT *)x, bias, (YT *)y, m, n, k, t0);
+    else int8_linear_kernel<XT, YT, MT, false><<<grid, kI8LinThreads, 0, st>>>(q, scale, zp, (const XT *)x, bias, (YT *)y, m, n, k, t0);
 }
 
 template <typename XT, typename YT>
 static void launch_i8_m(const uint8_t *q, const float *scale, const int *zp, const void *x, const float *bias, void *y,
                         int64_t m, int64_t n, int64_t k, int grid, bool vec, long long *launches, cudaStream_t st) {
-    for (int64_t t0 = 0; t0 < m; t0 += 8) {   // eight tokens share a pass over the weights
+    for (int64_t t0 = 0; t0 < m; t0 += 4) {   // four tokens share a pass over the weights
         const int64_t left = m - t0;
         if (left == 1) launch_i8<XT, YT, 1>(q, scale, zp, x, bias, y, m, n, k, t0, grid, vec, st);
         else if (left == 2) launch_i8<XT, YT, 2>(q, scale, zp, x, bias, y, m, n, k, t0, grid, vec, st);
-        else if (left <= 4) launch_i8<XT, YT, 4>(q, scale, zp, x, bias, y, m, n, k, t0, grid, vec, st);
-        else launch_i8<XT, YT, 8>(q, scale, zp, x, bias, y, m, n, k, t0, grid, vec, st);
+        else launch_i8<XT, YT, 4>(q, scale, zp, x, bias, y, m, n, k, t0, grid, vec, st);
         (*launches)++;
     }
 }
@@ -268,7 +292,8 @@ nnq_status nnq_int8_linear(nnq_ctx *ctx, const void *q_dev, const float *scale_d
     cudaStream_t st = (cudaStream_t)stream;
     // 16-byte chunks need aligned rows and activations
     const bool vec = k % 16 == 0 && !((uintptr_t)q_dev & 15u) && !((uintptr_t)x_dev & 15u);
-    const int64_t want = (n + kI8Threads / 32 - 1) / (kI8Threads / 32), cap = (int64_t)ctx->sm_count * 8;
+    const int64_t units = (n + kI8Rows - 1) / kI8Rows, per_cta = kI8LinThreads / 32;
+    const int64_t want = (units + per_cta - 1) / per_cta, cap = (int64_t)ctx->sm_count * 16;
     const int grid = (int)(want < cap ? want : cap);
     if (x_dt == NNQ_F32 && y_dt == NNQ_F32) launch_i8_m<float, float>((const uint8_t *)q_dev, scale_dev, zp_dev, x_dev, bias_dev, y_dev, m, n, k, grid, vec, &ctx->launches, st);
     else if (x_dt == NNQ_F32) launch_i8_m<float, __nv_bfloat16>((const uint8_t *)q_dev, scale_dev, zp_dev, x_dev, bias_dev, y_dev, m, n, k, grid, vec, &ctx->launches, st);
