@@ -440,15 +440,56 @@ nnq_status nnq_linear_batch(nnq_ctx *ctx, int count, const nnq_weight *const *w,
     return NNQ_OK;
 }
 
+// Results of at most this many bytes are written by the kernels straight into the pinned host
+// buffer (it is mapped into the device's address space), which saves the device-to-host copy
+// operation and its hand-over between the compute and copy engines; larger results go through
+// device memory and one bulk copy. The outputs are write-only in every product kernel.
+constexpr size_t kZeroCopyOutBytes = 1 << 20;
+
+static void *mapped_output(nnq_ctx *ctx, size_t bytes) {
+    static const char *env = getenv("NNQ_HOST_ZEROCOPY");   // measurement aid: 0 keeps the copy
+    if ((env && atoi(env) == 0) || bytes > kZeroCopyOutBytes) return nullptr;
+    void *dev = nullptr;
+    if (cudaHostGetDevicePointer(&dev, ctx->h_stage_y, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return dev;
+}
+
+// Small inputs are pulled from the mapped pinned buffer by a copy kernel instead of a copy-engine
+// operation: the product kernel then follows a kernel on its own engine (no engine hand-over).
+constexpr size_t kKernelCopyInBytes = 256 << 10;
+
+__global__ void __launch_bounds__(256) stage_in_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, size_t n16) {
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n16; i += (size_t)gridDim.x * 256) dst[i] = src[i];
+}
+
+// Queues the copy of the staged inputs (a multiple of 16 bytes is available in both buffers).
+static nnq_status stage_in(nnq_ctx *ctx, size_t bytes, cudaStream_t st) {
+    static const char *env = getenv("NNQ_HOST_KERNEL_COPY");   // measurement aid: 0 keeps the copy engine
+    void *src = nullptr;
+    if (!(env && atoi(env) == 0) && bytes <= kKernelCopyInBytes &&
+        cudaHostGetDevicePointer(&src, ctx->h_stage_x, 0) == cudaSuccess) {
+        const size_t n16 = (bytes + 15) / 16;
+        const int grid = (int)((n16 + 255) / 256 < 16 ? (n16 + 255) / 256 : 16);
+        stage_in_kernel<<<grid, 256, 0, st>>>((const uint4 *)src, (uint4 *)ctx->d_stage_x, n16);
+        ctx->launches++;
+        return check_cuda(ctx, cudaGetLastError(), "stage-in launch");
+    }
+    cudaGetLastError();
+    return check_cuda(ctx, cudaMemcpyAsync(ctx->d_stage_x, ctx->h_stage_x, bytes, cudaMemcpyHostToDevice, st), "h2d");
+}
+
 static nnq_status grow(nnq_ctx *ctx, void **p, size_t *cap, size_t need, bool pinned_host) {
     if (need <= *cap) return NNQ_OK;
-    size_t want = need < 4096 ? 4096 : need + need / 2;
+    size_t want = need < 4096 ? 4096 : (need + need / 2 + 255) & ~(size_t)255;
     if (*p) {
         if (pinned_host) cudaFreeHost(*p); else cudaFree(*p);
         *p = nullptr;
         *cap = 0;
     }
-    cudaError_t e = pinned_host ? cudaMallocHost(p, want) : cudaMalloc(p, want);
+    cudaError_t e = pinned_host ? cudaHostAlloc(p, want, cudaHostAllocMapped | cudaHostAllocPortable) : cudaMalloc(p, want);
     if (e != cudaSuccess) return check_cuda(ctx, e, "staging allocation");
     *cap = want;
     return NNQ_OK;
@@ -484,13 +525,15 @@ nnq_status nnq_linear_host(nnq_ctx *ctx, const nnq_weight *w, const void *x_host
     memcpy(ctx->h_stage_x, x_host, xb);
     size_t boff = (xb + 15) & ~(size_t)15;
     if (bb) memcpy((uint8_t *)ctx->h_stage_x + boff, bias_host, bb);
-    s = check_cuda(ctx, cudaMemcpyAsync(ctx->d_stage_x, ctx->h_stage_x, in_bytes, cudaMemcpyHostToDevice, st), "h2d");
+    s = stage_in(ctx, in_bytes, st);
     if (s != NNQ_OK) return s;
     const float *bias_dev = bb ? (const float *)((uint8_t *)ctx->d_stage_x + boff) : nullptr;
-    s = linear_checked(ctx, w, ctx->d_stage_x, x_dt, m, bias_dev, ctx->d_stage_y, y_dt);
-    if (s == NNQ_OK) s = linear_dispatch(ctx, w, ctx->d_stage_x, x_dt, m, bias_dev, ctx->d_stage_y, y_dt, st);
+    void *direct = mapped_output(ctx, yb);
+    void *y_dev = direct ? direct : ctx->d_stage_y;
+    s = linear_checked(ctx, w, ctx->d_stage_x, x_dt, m, bias_dev, y_dev, y_dt);
+    if (s == NNQ_OK) s = linear_dispatch(ctx, w, ctx->d_stage_x, x_dt, m, bias_dev, y_dev, y_dt, st);
     if (s != NNQ_OK) return s;
-    s = check_cuda(ctx, cudaMemcpyAsync(ctx->h_stage_y, ctx->d_stage_y, yb, cudaMemcpyDeviceToHost, st), "d2h");
+    if (!direct) s = check_cuda(ctx, cudaMemcpyAsync(ctx->h_stage_y, ctx->d_stage_y, yb, cudaMemcpyDeviceToHost, st), "d2h");
     if (s == NNQ_OK) s = wait_host_stream(ctx);
     if (s != NNQ_OK) return s;
     memcpy(y_host, ctx->h_stage_y, yb);
@@ -546,6 +589,8 @@ nnq_status nnq_linear_batch_host(nnq_ctx *ctx, int count, const nnq_weight *cons
     const void *xd[kMaxBatch];
     const float *bd[kMaxBatch];
     void *yd[kMaxBatch];
+    void *direct = mapped_output(ctx, out_bytes);
+    uint8_t *y_base = direct ? (uint8_t *)direct : (uint8_t *)ctx->d_stage_y;
     for (int i = 0; i < count; i++) {
         bool first = true;
         for (int j = 0; j < i; j++) first = first && x_off[j] != x_off[i];
@@ -556,14 +601,14 @@ nnq_status nnq_linear_batch_host(nnq_ctx *ctx, int count, const nnq_weight *cons
             memcpy((uint8_t *)ctx->h_stage_x + b_off[i], bias_host[i], (size_t)w[i]->n * 4);
             bd[i] = (const float *)((uint8_t *)ctx->d_stage_x + b_off[i]);
         }
-        yd[i] = (uint8_t *)ctx->d_stage_y + y_off[i];
+        yd[i] = y_base + y_off[i];
     }
     cudaStream_t st = ctx->host_stream;
-    s = check_cuda(ctx, cudaMemcpyAsync(ctx->d_stage_x, ctx->h_stage_x, in_bytes, cudaMemcpyHostToDevice, st), "h2d");
+    s = stage_in(ctx, in_bytes, st);
     if (s != NNQ_OK) return s;
     s = nnq_linear_batch(ctx, count, w, xd, x_dt, m, bd, yd, y_dt, st);
     if (s != NNQ_OK) return s;
-    s = check_cuda(ctx, cudaMemcpyAsync(ctx->h_stage_y, ctx->d_stage_y, out_bytes, cudaMemcpyDeviceToHost, st), "d2h");
+    if (!direct) s = check_cuda(ctx, cudaMemcpyAsync(ctx->h_stage_y, ctx->d_stage_y, out_bytes, cudaMemcpyDeviceToHost, st), "d2h");
     if (s == NNQ_OK) s = wait_host_stream(ctx);
     if (s != NNQ_OK) return s;
     for (int i = 0; i < count; i++) memcpy(y_host[i], (uint8_t *)ctx->h_stage_y + y_off[i], (size_t)m * w[i]->n * elem_size(y_dt));
