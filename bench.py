@@ -447,7 +447,8 @@ def run_nnq(args, rank, world, local_rank):
 def other_configs(torch, backend, layers, gen, dev):
     """Short device-timed runs of the path's other configurations (inputs resident in HBM, more
     weight bytes per pass than L2 holds): the Q4_K sweep at 16 / 128 / 512 tokens over the same
-    36 layers, the Q8_0 4096 x 4096 GEMV with f32 activations, and a Q6_K vocabulary-sized GEMV."""
+    36 layers, the Q8_0 4096 x 4096 GEMV with f32 activations, a Q6_K vocabulary-sized GEMV and the same shape with
+    INT8 per-channel weights."""
     import ctypes
 
     from nn_b200 import api
@@ -527,6 +528,29 @@ def other_configs(torch, backend, layers, gen, dev):
     out["qwen3_8b_decode_ctx2048"] = decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm)
     out["q8_0_gemv_4096x4096_f32_m1"] = gemv(QuantFormat.Q8_0, W.gen_q8_0_device, 4096, 4096, 10, True, 40)
     out["q6_k_gemv_151936x4096_bf16_m1"] = gemv(QuantFormat.Q6_K, W.gen_q6_k_device, 151936, 4096, 1, False, 10)
+
+    def int8_gemv(n, k, reps):
+        q = torch.randint(0, 256, (n, k), dtype=torch.uint8, device=dev, generator=gen)
+        scale = torch.rand(n, device=dev, generator=gen) * 1e-3
+        zp = torch.randint(-20, 20, (n,), dtype=torch.int32, device=dev, generator=gen)
+        x = torch.randn(1, k, device=dev, generator=gen)
+        y = torch.empty(1, n, dtype=torch.float32, device=dev)
+
+        def one():
+            st = lib.nnq_int8_linear(ctx, q.data_ptr(), scale.data_ptr(), zp.data_ptr(), n, k, x.data_ptr(), api.F32, 1, None,
+                                     y.data_ptr(), api.F32, None)
+            if st != 0:
+                backend.check(st)
+
+        sec = timed(one, reps)
+        algo = n * k + n * 8 + k * 4 + n * 4   # one byte per weight, scale + zero point per row, x and y once
+        return {"us": sec * 1e6, "gbs": algo / sec / 1e9, "bound": "hbm", "frac": algo / sec / 1e9 / peak_hbm,
+                "weights_rotated": 1}
+
+    try:   # a side measurement must not take the headline down
+        out["int8_w8a16_gemv_151936x4096_f32_m1"] = int8_gemv(151936, 4096, 10)
+    except Exception as e:
+        out["int8_w8a16_gemv_151936x4096_f32_m1"] = {"error": str(e)[:200]}
     backend.device_status()
     return out
 
