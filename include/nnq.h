@@ -276,6 +276,54 @@ NNQ_API nnq_status nnq_linear_batch_host(nnq_ctx *ctx, int count, const nnq_weig
                                          const void *const *x_host, nnq_dtype x_dt, int64_t m,
                                          const float *const *bias_host, void *const *y_host, nnq_dtype y_dt);
 
+/* ---- compiled product plan ---------------------------------------------------------- */
+
+/* A recorded sequence of M = 1 products (one token) run as ONE kernel launch: the counterpart, for
+ * this path, of the reference's compiled dispatch plan, which is built once from a trace and then
+ * replayed step by step (CompiledModel, crates/nn-metal/src/compiled_model.rs:232,305-311;
+ * run_steps, crates/nn-metal/src/compiled_model_execute.rs:124). The products are added in the
+ * order a decoder layer issues them (crates/nn-qwen3/src/layers.rs:40-47,94-167): a group is up to
+ * 4 products that share their activations (q / k / v, gate / up), each group is one
+ * nnq_linear_batch call's worth of work. nnq_plan_run gives the same results as those calls made
+ * one after another on a stream: by default every group sees everything the groups before it
+ * wrote. With NNQ_PLAN_ANALYZE_DEPS a group only waits for the latest earlier group whose
+ * buffers overlap its own (its input was written, or its output was read or written, there).
+ * The persistent kernel keeps streaming weights while a group waits for its activations, so a
+ * plan runs faster than the separate launches (no ramp and tail per product).
+ *   - weights: Q4_K / Q4_K_GGML with K a multiple of 256; activations x_dt, outputs y_dt as in
+ *     nnq_linear; every pointer is fixed at nnq_plan_add time (CUDA-graph style): the caller
+ *     updates the contents of the buffers, not their addresses;
+ *   - nnq_plan_finalize allocates the plan's device tables (never later: nnq_plan_run allocates
+ *     nothing and does not synchronise, so it may be captured in a CUDA graph);
+ *   - a bounded device wait that runs out ends the launch and nnq_device_status reports
+ *     NNQ_ERR_TIMEOUT; call nnq_plan_reset before the plan is run again;
+ *   - one plan must not run twice at the same time (its counters are shared). */
+typedef struct nnq_plan nnq_plan;
+#define NNQ_PLAN_ANALYZE_DEPS 1
+NNQ_API nnq_status nnq_plan_create(nnq_ctx *ctx, nnq_dtype x_dt, nnq_dtype y_dt, int flags, nnq_plan **out);
+NNQ_API nnq_status nnq_plan_add(nnq_plan *p, int count, const nnq_weight *const *w, const void *x_dev,
+                                const float *const *bias_dev, void *const *y_dev);
+/* A row-parallel product whose partial outputs are summed over the ranks of `comm` inside the
+ * kernel (see nnq_comm_linear): every rank adds the same group at the same place of its plan.
+ * No counterpart in the reference (single device). */
+NNQ_API nnq_status nnq_plan_add_reduced(nnq_plan *p, nnq_comm *comm, const nnq_weight *w, const void *x_dev,
+                                        const float *bias_dev, void *y_dev);
+NNQ_API nnq_status nnq_plan_finalize(nnq_plan *p);
+NNQ_API nnq_status nnq_plan_run(nnq_plan *p, void *stream);
+NNQ_API nnq_status nnq_plan_reset(nnq_plan *p, void *stream);
+/* Bound of a dependency wait in polls of the group counter (default 2^21, about a second). */
+NNQ_API nnq_status nnq_plan_set_spin_limit(nnq_plan *p, unsigned polls);
+/* Groups recorded; after nnq_plan_finalize also the grid (CTAs), the copy-ring depth per warp, the
+ * shared memory per CTA and the bytes of device tables the plan holds. Any pointer may be NULL. */
+NNQ_API nnq_status nnq_plan_info(const nnq_plan *p, int *groups, int *ctas, int *stages, size_t *smem_bytes,
+                                 size_t *table_bytes);
+/* The group whose completion group `group` waits for (-1: none), after nnq_plan_finalize. */
+NNQ_API nnq_status nnq_plan_dependency(const nnq_plan *p, int group, int *dep);
+/* How a group of row_tiles x k_tiles tiles is split over `ctas` CTAs: the largest number of tiles
+ * any CTA gets and the largest number of CTAs any row tile is spread over. Host arithmetic only. */
+NNQ_API nnq_status nnq_plan_geometry(int row_tiles, int k_tiles, int ctas, int *max_tiles_per_cta, int *max_parts);
+NNQ_API void nnq_plan_destroy(nnq_plan *p);
+
 /* ---- mixture-of-experts block ------------------------------------------------------ */
 
 /* Storage of the expert weight tensors.

@@ -66,6 +66,19 @@ SIGNATURES = {
     "nnq_decoder_buffers": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                     ctypes.POINTER(c_void_p)]),
     "nnq_decoder_destroy": (None, [c_void_p]),
+    "nnq_plan_create": (c_int, [c_void_p, c_int, c_int, c_int, ctypes.POINTER(c_void_p)]),
+    "nnq_plan_add": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p), c_void_p, ctypes.POINTER(c_void_p),
+                             ctypes.POINTER(c_void_p)]),
+    "nnq_plan_add_reduced": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nnq_plan_finalize": (c_int, [c_void_p]),
+    "nnq_plan_run": (c_int, [c_void_p, c_void_p]),
+    "nnq_plan_reset": (c_int, [c_void_p, c_void_p]),
+    "nnq_plan_set_spin_limit": (c_int, [c_void_p, ctypes.c_uint]),
+    "nnq_plan_info": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int),
+                              ctypes.POINTER(c_size_t), ctypes.POINTER(c_size_t)]),
+    "nnq_plan_dependency": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int)]),
+    "nnq_plan_geometry": (c_int, [c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
+    "nnq_plan_destroy": (None, [c_void_p]),
     "nnq_moe_create": (c_int, [c_void_p, c_int, c_int, c_int, c_int, ctypes.c_float, c_void_p, c_void_p, c_int, c_int,
                                c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p,
                                c_size_t, c_void_p, ctypes.POINTER(c_void_p)]),

@@ -136,6 +136,12 @@ nnq_status nnq_init(int device, nnq_ctx **out) {
     if (s == NNQ_OK) s = check_cuda(ctx, cudaMemset(ctx->d_status, 0, sizeof(int)), "cudaMemset status");
     if (s == NNQ_OK) s = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking), "stream");
     if (s == NNQ_OK) s = check_cuda(ctx, cudaEventCreateWithFlags(&ctx->host_event, cudaEventDisableTiming), "event");
+    if (s == NNQ_OK) {
+        // split-K partial sums of the tensor path: at most 2 * SMs output tiles of 128 x 128 f32
+        ctx->partials_bytes = (size_t)2 * ctx->sm_count * 128 * 128 * sizeof(float);
+        s = check_cuda(ctx, cudaMalloc(&ctx->d_partials, ctx->partials_bytes), "cudaMalloc split-K scratch");
+        if (s != NNQ_OK) ctx->partials_bytes = 0;
+    }
     if (s == NNQ_OK) s = skinny_init(ctx);
     if (s != NNQ_OK) {
         nnq_destroy(ctx);
@@ -447,7 +453,7 @@ nnq_status nnq_linear_batch(nnq_ctx *ctx, int count, const nnq_weight *const *w,
 constexpr size_t kZeroCopyOutBytes = 1 << 20;
 
 static void *mapped_output(nnq_ctx *ctx, size_t bytes) {
-    static const char *env = getenv("NNQ_HOST_ZEROCOPY");   // measurement aid: 0 keeps the copy
+    static const char *env = diag_env("NNQ_HOST_ZEROCOPY");   // measurement aid: 0 keeps the copy
     if ((env && atoi(env) == 0) || bytes > kZeroCopyOutBytes) return nullptr;
     void *dev = nullptr;
     if (cudaHostGetDevicePointer(&dev, ctx->h_stage_y, 0) != cudaSuccess) {
@@ -467,7 +473,9 @@ __global__ void __launch_bounds__(256) stage_in_kernel(const uint4 *__restrict__
 
 // Queues the copy of the staged inputs (a multiple of 16 bytes is available in both buffers).
 static nnq_status stage_in(nnq_ctx *ctx, size_t bytes, cudaStream_t st) {
-    static const char *env = getenv("NNQ_HOST_KERNEL_COPY");   // measurement aid: 0 keeps the copy engine
+    if (!ctx->h_stage_x || !ctx->d_stage_x || bytes > ctx->stage_x_bytes)
+        return fail(ctx, NNQ_ERR_OUT_OF_MEMORY, "staging buffers are not allocated");
+    static const char *env = diag_env("NNQ_HOST_KERNEL_COPY");   // measurement aid: 0 keeps the copy engine
     void *src = nullptr;
     if (!(env && atoi(env) == 0) && bytes <= kKernelCopyInBytes &&
         cudaHostGetDevicePointer(&src, ctx->h_stage_x, 0) == cudaSuccess) {
@@ -495,6 +503,35 @@ static nnq_status grow(nnq_ctx *ctx, void **p, size_t *cap, size_t need, bool pi
     return NNQ_OK;
 }
 
+// Makes the staging pairs (pinned host + device) hold in_bytes / out_bytes. The recorded capacity
+// of a pair is dropped to zero BEFORE its buffers are replaced, so a failed allocation leaves the
+// context saying "no staging" (the next call allocates again) rather than a stale size over a
+// freed pointer.
+static nnq_status grow_staging(nnq_ctx *ctx, size_t in_bytes, size_t out_bytes) {
+    nnq_status s;
+    if (in_bytes > ctx->stage_x_bytes || !ctx->h_stage_x || !ctx->d_stage_x) {
+        size_t cap_h = 0, cap_d = 0;
+        ctx->stage_x_bytes = 0;
+        if (ctx->h_stage_x) cudaFreeHost(ctx->h_stage_x);
+        if (ctx->d_stage_x) cudaFree(ctx->d_stage_x);
+        ctx->h_stage_x = ctx->d_stage_x = nullptr;
+        if ((s = grow(ctx, &ctx->h_stage_x, &cap_h, in_bytes, true)) != NNQ_OK) return s;
+        if ((s = grow(ctx, &ctx->d_stage_x, &cap_d, in_bytes, false)) != NNQ_OK) return s;
+        ctx->stage_x_bytes = cap_h < cap_d ? cap_h : cap_d;
+    }
+    if (out_bytes > ctx->stage_y_bytes || !ctx->h_stage_y || !ctx->d_stage_y) {
+        size_t cap_h = 0, cap_d = 0;
+        ctx->stage_y_bytes = 0;
+        if (ctx->h_stage_y) cudaFreeHost(ctx->h_stage_y);
+        if (ctx->d_stage_y) cudaFree(ctx->d_stage_y);
+        ctx->h_stage_y = ctx->d_stage_y = nullptr;
+        if ((s = grow(ctx, &ctx->h_stage_y, &cap_h, out_bytes, true)) != NNQ_OK) return s;
+        if ((s = grow(ctx, &ctx->d_stage_y, &cap_d, out_bytes, false)) != NNQ_OK) return s;
+        ctx->stage_y_bytes = cap_h < cap_d ? cap_h : cap_d;
+    }
+    return NNQ_OK;
+}
+
 nnq_status nnq_linear_host(nnq_ctx *ctx, const nnq_weight *w, const void *x_host, nnq_dtype x_dt, int64_t m,
                            const float *bias_host, void *y_host, nnq_dtype y_dt) {
     if (!ctx) return NNQ_ERR_INVALID_ARG;
@@ -509,18 +546,7 @@ nnq_status nnq_linear_host(nnq_ctx *ctx, const nnq_weight *w, const void *x_host
     size_t bb = bias_host ? (size_t)w->n * 4 : 0;
     // staging: [x | bias] share the pinned input buffer so that one copy moves both
     size_t in_bytes = ((xb + 15) & ~(size_t)15) + bb;
-    size_t cap_hx = ctx->stage_x_bytes, cap_dx = ctx->stage_x_bytes;
-    if (in_bytes > ctx->stage_x_bytes) {
-        if ((s = grow(ctx, &ctx->h_stage_x, &cap_hx, in_bytes, true)) != NNQ_OK) return s;
-        if ((s = grow(ctx, &ctx->d_stage_x, &cap_dx, in_bytes, false)) != NNQ_OK) return s;
-        ctx->stage_x_bytes = cap_hx < cap_dx ? cap_hx : cap_dx;
-    }
-    size_t cap_hy = ctx->stage_y_bytes, cap_dy = ctx->stage_y_bytes;
-    if (yb > ctx->stage_y_bytes) {
-        if ((s = grow(ctx, &ctx->h_stage_y, &cap_hy, yb, true)) != NNQ_OK) return s;
-        if ((s = grow(ctx, &ctx->d_stage_y, &cap_dy, yb, false)) != NNQ_OK) return s;
-        ctx->stage_y_bytes = cap_hy < cap_dy ? cap_hy : cap_dy;
-    }
+    if ((s = grow_staging(ctx, in_bytes, yb)) != NNQ_OK) return s;
     cudaStream_t st = ctx->host_stream;
     memcpy(ctx->h_stage_x, x_host, xb);
     size_t boff = (xb + 15) & ~(size_t)15;
@@ -574,18 +600,7 @@ nnq_status nnq_linear_batch_host(nnq_ctx *ctx, int count, const nnq_weight *cons
         b_off[i] = in_bytes;
         if (bias_host && bias_host[i]) in_bytes += ((size_t)w[i]->n * 4 + 255) & ~(size_t)255;
     }
-    size_t cap_hx = ctx->stage_x_bytes, cap_dx = ctx->stage_x_bytes;
-    if (in_bytes > ctx->stage_x_bytes) {
-        if ((s = grow(ctx, &ctx->h_stage_x, &cap_hx, in_bytes, true)) != NNQ_OK) return s;
-        if ((s = grow(ctx, &ctx->d_stage_x, &cap_dx, in_bytes, false)) != NNQ_OK) return s;
-        ctx->stage_x_bytes = cap_hx < cap_dx ? cap_hx : cap_dx;
-    }
-    size_t cap_hy = ctx->stage_y_bytes, cap_dy = ctx->stage_y_bytes;
-    if (out_bytes > ctx->stage_y_bytes) {
-        if ((s = grow(ctx, &ctx->h_stage_y, &cap_hy, out_bytes, true)) != NNQ_OK) return s;
-        if ((s = grow(ctx, &ctx->d_stage_y, &cap_dy, out_bytes, false)) != NNQ_OK) return s;
-        ctx->stage_y_bytes = cap_hy < cap_dy ? cap_hy : cap_dy;
-    }
+    if ((s = grow_staging(ctx, in_bytes, out_bytes)) != NNQ_OK) return s;
     const void *xd[kMaxBatch];
     const float *bd[kMaxBatch];
     void *yd[kMaxBatch];

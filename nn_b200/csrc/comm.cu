@@ -109,6 +109,17 @@ allreduce_oneshot_kernel(uint8_t *const *peers, int rank, int world, size_t slot
     if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned *>(local) = seq;
 }
 
+nnq_status comm_view(nnq_comm *c, CommView *out) {
+    if (!c || !out) return NNQ_ERR_INVALID_ARG;
+    for (int p = 0; p < c->world; p++)
+        if (!c->peer[p]) return fail(c->ctx, NNQ_ERR_INVALID_ARG, "peer %d has not been opened", p);
+    out->peer_table = c->d_peer_table;
+    out->slot_bytes = c->slot_bytes;
+    out->rank = c->rank;
+    out->world = c->world;
+    return NNQ_OK;
+}
+
 }  // namespace nnq
 
 using namespace nnq;

@@ -25,4 +25,11 @@ struct FusedReduce {
     int enabled;
 };
 
+// What a kernel outside comm.cu needs to know about an opened communicator.
+struct CommView {
+    uint8_t *const *peer_table;   // device table of every rank's buffer
+    size_t slot_bytes;
+    int rank, world;
+};
+
 }  // namespace nnq

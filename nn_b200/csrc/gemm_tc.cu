@@ -431,7 +431,7 @@ static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, int ks
     // a full wave of smaller ones, because every CTA decodes its weight tile for itself)
     if (a.m > 256 && 2 * ctas(4) >= sm_count) mt = 4;
     else if (a.m > 128 && 2 * ctas(2) >= sm_count) mt = 2;
-    static const char *env_mt = getenv("NNQ_TC_MT");   // tuning aid
+    static const char *env_mt = diag_env("NNQ_TC_MT");   // tuning aid
     if (env_mt && (atoi(env_mt) == 1 || atoi(env_mt) == 2 || atoi(env_mt) == 4)) mt = atoi(env_mt);
     if (mt != 1) ksplit = 1;
     if (mt == 1) return f32 ? launch_one<FMT, 1, float>(a, status, ksplit, partials, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, ksplit, partials, stream);
@@ -498,17 +498,9 @@ nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
             if (ksplit > nkb / 4) ksplit = (int)(nkb / 4);
             if (ksplit < 1) ksplit = 1;
         }
-        if (ksplit > 1) {
-            const size_t need = (size_t)ksplit * a.m * a.n * sizeof(float);
-            if (need > ctx->partials_bytes) {
-                cudaFree(ctx->d_partials);   // synchronises: an earlier product may still use it
-                ctx->d_partials = nullptr;
-                ctx->partials_bytes = 0;
-                nnq_status s = check_cuda(ctx, cudaMalloc(&ctx->d_partials, need), "cudaMalloc split-K scratch");
-                if (s != NNQ_OK) return s;
-                ctx->partials_bytes = need;
-            }
-        }
+        // the scratch is sized once, at context creation, for the largest split this rule can ask
+        // for (ksplit * ctas <= 2 * SMs tiles of 128 x 128 f32): nothing is allocated here
+        while (ksplit > 1 && (size_t)ksplit * a.m * a.n * sizeof(float) > ctx->partials_bytes) ksplit--;
     }
     switch (a.fmt) {
         case NNQ_Q4_0: e = launch_fmt<NNQ_Q4_0>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;

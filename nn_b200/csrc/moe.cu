@@ -428,7 +428,7 @@ static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 // rows per local expert on average (below that the weights are streamed once per 16 rows by the
 // grouped token-column kernel, which is HBM-bound and wins).
 static bool moe_tensor_mode(const nnq_moe *m, int64_t T) {
-    static const char *env = getenv("NNQ_MOE_TENSOR");   // tuning aid: 0 keeps the token-column kernel
+    static const char *env = diag_env("NNQ_MOE_TENSOR");   // tuning aid: 0 keeps the token-column kernel
     if (env && atoi(env) == 0) return false;
     return m->layout == NNQ_MOE_NK && m->fmt < NNQ_Q5_0 && m->hidden % 64 == 0 && m->inter % 64 == 0 && T * m->top_k >= 64 * (int64_t)m->n_experts;   // per expert of the whole block: shards of one block agree
 }
@@ -697,7 +697,7 @@ nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, i
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_scales, down_scales, down_scales_bytes, "down scales");
     if (s == NNQ_OK) s = upload(ctx, (void **)&m->d_dn_bias, down_bias, (size_t)expert_count * hidden * 4, "down bias");
     // tiled copies for the grouped kernel
-    static const char *env_tiled = getenv("NNQ_MOE_TILED");   // tuning aid: 0 keeps the row kernels
+    static const char *env_tiled = diag_env("NNQ_MOE_TILED");   // tuning aid: 0 keeps the row kernels
     if (s == NNQ_OK && layout == NNQ_MOE_KN_GPTOSS && !(env_tiled && atoi(env_tiled) == 0)) {
         // [E, K, N] tensors: tiles of the transposed products (rows = N)
         const size_t gs = tiled_bytes_kn(2 * (int64_t)inter, hidden, nullptr);

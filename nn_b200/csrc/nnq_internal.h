@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stddef.h>
+#include <stdlib.h>
 
 #include "../../include/nnq.h"
 
@@ -81,6 +82,17 @@ struct nnq_weight {
 };
 
 namespace nnq {
+
+// Tuning and diagnostic switches exist only in builds made with -DNNQ_DIAG; the shipped library
+// reads no environment variable.
+static inline const char *diag_env(const char *name) {
+#ifdef NNQ_DIAG
+    return getenv(name);
+#else
+    (void)name;
+    return nullptr;
+#endif
+}
 
 nnq_status fail(nnq_ctx *ctx, nnq_status s, const char *fmt, ...);
 nnq_status check_cuda(nnq_ctx *ctx, cudaError_t e, const char *what);

@@ -136,9 +136,9 @@ nnq_status build_tiled(nnq_ctx *ctx, nnq_weight *w) {
 // CTAs per SM with a 2-deep ring when that fits, else two with up to 4 stages, else one;
 // stages = 0 when K is too large altogether.
 static void pick_stages(int kblocks, bool f32x, int *stages, int *ctas_per_sm) {
-    static const char *env_st = getenv("NNQ_SKINNY_STAGES");  // tuning aid
+    static const char *env_st = diag_env("NNQ_SKINNY_STAGES");  // tuning aid
     const int forced = env_st ? atoi(env_st) : 0;
-    static const char *env_ctas = getenv("NNQ_SKINNY_CTAS");  // tuning aid
+    static const char *env_ctas = diag_env("NNQ_SKINNY_CTAS");  // tuning aid
     int max_ctas = f32x ? 2 : 3;   // register budget of the two instantiations
     if (env_ctas && atoi(env_ctas) > 0 && atoi(env_ctas) < max_ctas) max_ctas = atoi(env_ctas);
     for (int ctas = max_ctas; ctas >= 1; ctas--) {
@@ -186,7 +186,7 @@ static cudaError_t launch_kernel(const SkinnyParams &P, int grid, int smem_bytes
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    static const char *env_pdl = getenv("NNQ_SKINNY_PDL");  // tuning aid
+    static const char *env_pdl = diag_env("NNQ_SKINNY_PDL");  // tuning aid
     cfg.numAttrs = env_pdl && atoi(env_pdl) == 0 ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, skinny_q4k_m1_kernel<F32X, KS, FUSED>, P);
 }
@@ -236,6 +236,7 @@ static cudaError_t launch_mn_fmt(const SkinnyParams &P, int nt, bool f32x, int g
     return nt == 1 ? launch_mn<FMT, SB, 1, false>(P, grid, smem_bytes, stream) : launch_mn<FMT, SB, 2, false>(P, grid, smem_bytes, stream);
 }
 
+#ifdef NNQ_DIAG
 // Diagnostic only (NNQ_SKINNY_DIAG=4): read the tiled weights of the jobs with plain coalesced
 // 16-byte loads and nothing else -- the read bandwidth a launch of this size can reach.
 __global__ void __launch_bounds__(256) stream_read_kernel(const SkinnyParams P, int *sink) {
@@ -250,6 +251,7 @@ __global__ void __launch_bounds__(256) stream_read_kernel(const SkinnyParams P, 
     }
     if (acc == 0x12345678u && sink) *sink = 1;   // keeps the loads alive; sink is NULL
 }
+#endif
 
 // One launch: jobs that share their activations (same x pointer, same K).
 static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, int x_dt, int m, int y_dt,
@@ -264,9 +266,9 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     const int tile_sb = jobs[0].w->tile_sb;
     P.kblocks = (int)(jobs[0].w->k / (32 * tile_sb));
     P.status = ctx->d_status;
-    static const char *env_diag = getenv("NNQ_SKINNY_DIAG");
+    static const char *env_diag = diag_env("NNQ_SKINNY_DIAG");
     P.diag = env_diag ? atoi(env_diag) : 0;
-    static const char *env_l2 = getenv("NNQ_SKINNY_L2PF");
+    static const char *env_l2 = diag_env("NNQ_SKINNY_L2PF");
     P.l2_prefetch = env_l2 ? atoi(env_l2) : 0;
     const bool f32x = x_dt == NNQ_F32;
     int ctas_per_sm = 0;
@@ -274,7 +276,7 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
     // One token of bf16 activations on few row tiles (one wave of the token-column kernel, e.g. the
     // 4096-row o / down projections): the token-column kernel has no activation staging after the
     // dependency wait and wins by a few percent; larger launches keep the M = 1 kernel.
-    static const char *env_tc = getenv("NNQ_SKINNY_TOKCOL");  // tuning aid: the row-tile limit of that rule
+    static const char *env_tc = diag_env("NNQ_SKINNY_TOKCOL");  // tuning aid: the row-tile limit of that rule
     int64_t job_tiles = 0;
     for (int i = 0; i < count; i++) job_tiles += (jobs[i].w->n + 15) / 16;
     const int64_t tokcol_limit = env_tc ? atoi(env_tc) : 2 * ctx->sm_count;
@@ -314,23 +316,25 @@ static nnq_status launch_group(nnq_ctx *ctx, const SkinnyJob *jobs, int count, i
         ctx->launches++;
         return check_cuda(ctx, e, "skinny launch");
     }
+#ifdef NNQ_DIAG
     if (P.diag == 4) {
         stream_read_kernel<<<ctx->sm_count * 8, 256, 0, stream>>>(P, nullptr);
         ctx->launches++;
         return check_cuda(ctx, cudaGetLastError(), "diag launch");
     }
+#endif
     // K split over the warps of a CTA: all 8 warps share a row tile when K allows, so that even
     // the smallest projections spread over every SM
     const int slots = ctx->sm_count * ctas_per_sm;
     int ksplit = 1;
     while (ksplit < kWarps && P.kblocks >= 2 * ksplit) ksplit *= 2;
-    static const char *env_ks = getenv("NNQ_SKINNY_KS");  // tuning aid
+    static const char *env_ks = diag_env("NNQ_SKINNY_KS");  // tuning aid
     if (env_ks && atoi(env_ks) > 0) ksplit = atoi(env_ks);
     // persistent grid: every CTA resident
     const int rg = kWarps / ksplit;
     const int units = (tiles + rg - 1) / rg;
     int grid = units < slots ? units : slots;
-    static const char *env_grid = getenv("NNQ_SKINNY_GRID");  // tuning aid
+    static const char *env_grid = diag_env("NNQ_SKINNY_GRID");  // tuning aid
     if (env_grid && atoi(env_grid) > 0) grid = atoi(env_grid);
     if (grid > units) grid = units;
     if (grid < 1) grid = 1;

@@ -33,7 +33,7 @@ struct SkinnyParams {
     int kblocks;        // tiles along K (K / 256; K / 192 for six-block MXFP4 tiles)
     int total_tiles;    // row tiles of all jobs
     int stages;         // ring depth per warp
-    int diag;           // diagnostics (NNQ_SKINNY_DIAG): bit 0 = skip the arithmetic (stream only),
+    int diag;           // builds with -DNNQ_DIAG only: bit 0 = skip the arithmetic (stream only),
                         // bit 1 = do not wait for the previous kernel; 4 = plain streaming read
     int l2_prefetch;    // 1 = ask L2 for the warp's whole weight stream at kernel start
     int *status;

@@ -196,6 +196,16 @@ __device__ __forceinline__ void tile_mac(const uint8_t *stage, uint32_t xs_s, ui
     }
     float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     float c2[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // second accumulator chain: halves the MMA dependency depth
+#ifdef NNQ_TILE_CHAINS4
+    // four accumulator pairs (one per sub-block pair) instead of two chains of eight MMAs
+    float ca[4][4], cb[4][4];
+#pragma unroll
+    for (int p = 0; p < 4; p++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) ca[p][i] = cb[p][i] = 0.0f;
+#define c ca[p]
+#define c2 cb[p]
+#endif
 #pragma unroll
     for (int p = 0; p < 4; p++) {
         const uint4 q = st[16 + 32 * p + lane];
@@ -220,6 +230,15 @@ __device__ __forceinline__ void tile_mac(const uint8_t *stage, uint32_t xs_s, ui
                     and_or(v3, K.mhi, K.k64), make_uint2(BL.v[p][1].z, BL.v[p][1].w));
         }
     }
+#ifdef NNQ_TILE_CHAINS4
+#undef c
+#undef c2
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        c[i] = (ca[0][i] + ca[1][i]) + (ca[2][i] + ca[3][i]);
+        c2[i] = (cb[0][i] + cb[1][i]) + (cb[2][i] + cb[3][i]);
+    }
+#endif
     // c[0], c[1]: row g, sub-blocks 2t, 2t+1; c[2], c[3]: row g+8
     const float4 tb = *reinterpret_cast<const float4 *>(tab + t * 4);
 #pragma unroll
@@ -239,83 +258,114 @@ __device__ __forceinline__ void tile_mac(const uint8_t *stage, uint32_t xs_s, ui
     }
 }
 
-// Stage the activations of super-blocks kb_begin, kb_begin + kb_step, ... < kb_end; one warp per
-// super-block, 8 consecutive elements (one word of one sub-block) per lane. Every super-block gets
-// its own power-of-two prescale to fp16 (its largest |x| lands in [1, 2): exact, and fp16 stays in
-// range whatever the magnitude of x), so that a warp can stage its own part of K without waiting
-// for the rest of the CTA. Writes the half-expanded operand, the per-sub-block offset sums and
-// 1 / prescale.
+// Stage one super-block of activations (256 values, 8 consecutive ones per lane in xv: one word of
+// one sub-block). Every super-block gets its own power-of-two prescale to fp16 (its largest |x|
+// lands in [1, 2): exact, and fp16 stays in range whatever the magnitude of x), so that a warp can
+// stage its own part of K without waiting for the rest of the CTA. Writes the half-expanded
+// operand, the per-sub-block offset sums and 1 / prescale.
 template <bool F32X>
-__device__ __forceinline__ void stage_x_warp(const void *x, int kb_begin, int kb_end, int kb_step, uint8_t *xs,
-                                             uint8_t *xs_lo, float *tab, float *xinv, int lane) {
+__device__ __forceinline__ void stage_x_block(const float (&xv)[8], int kb, uint8_t *xs, uint8_t *xs_lo, float *tab,
+                                              float *xinv, int lane) {
     const int sb8 = lane >> 2;
     const bool odd = sb8 & 1;
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(xv[k]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    uint32_t ex = (__float_as_uint(amax) >> 23) & 0xFFu;
+    ex = amax > 0.0f && ex < 255u ? min(max(ex, 1u), 253u) : 127u;
+    const float scale = __uint_as_float((254u - ex) << 23);
+    uint32_t ph[4], pl[4];
+    float xr[8];  // the values the MMAs will see
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        float s0 = xv[2 * k] * scale, s1 = xv[2 * k + 1] * scale;
+        __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
+        xr[2 * k] = __half2float(h0);
+        xr[2 * k + 1] = __half2float(h1);
+        ph[k] = __half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+        if (F32X) {
+            __half l0 = __float2half_rn(s0 - xr[2 * k]), l1 = __float2half_rn(s1 - xr[2 * k + 1]);
+            xr[2 * k] += __half2float(l0);
+            xr[2 * k + 1] += __half2float(l1);
+            pl[k] = __half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+        }
+    }
+    // lane = 4 * sub-block + word: its 32 bytes of the operand image are contiguous
+    uint4 *dst = reinterpret_cast<uint4 *>(xs + kb * 1024 + lane * 32);
+    dst[0] = odd ? make_uint4(0, ph[0], 0, ph[1]) : make_uint4(ph[0], 0, ph[1], 0);
+    dst[1] = odd ? make_uint4(0, ph[2], 0, ph[3]) : make_uint4(ph[2], 0, ph[3], 0);
+    if (F32X) {
+        uint4 *dl = reinterpret_cast<uint4 *>(xs_lo + kb * 1024 + lane * 32);
+        dl[0] = odd ? make_uint4(0, pl[0], 0, pl[1]) : make_uint4(pl[0], 0, pl[1], 0);
+        dl[1] = odd ? make_uint4(0, pl[2], 0, pl[3]) : make_uint4(pl[2], 0, pl[3], 0);
+    }
+    // within a word (8 elements), elements 0,1,4,5 carry offset 1024 and 2,3,6,7 offset 64
+    float sa = (xr[0] + xr[1]) + (xr[4] + xr[5]), sb = (xr[2] + xr[3]) + (xr[6] + xr[7]);
+    float ox = 1024.0f * sa + 64.0f * sb;
+    float sx = sa + sb;
+#pragma unroll
+    for (int o2 = 1; o2 < 4; o2 <<= 1) {  // the 4 lanes of one sub-block are consecutive
+        ox += __shfl_xor_sync(0xFFFFFFFFu, ox, o2);
+        sx += __shfl_xor_sync(0xFFFFFFFFu, sx, o2);
+    }
+    if ((lane & 3) == 0) {
+        float *e = tab + (kb * 4 + (sb8 >> 1)) * 4 + (sb8 & 1);
+        e[0] = ox;
+        e[2] = sx;
+    }
+    if (lane == 0) xinv[kb] = __uint_as_float(ex << 23);
+}
+
+// This lane's 8 activations of super-block kb. FRESH = true reads with loads that bypass L1
+// (ld.global.cg): for a kernel that stages activations another CTA of the same launch has just written.
+template <bool F32X, bool FRESH>
+__device__ __forceinline__ void load_x_block(const void *x, int kb, int lane, float (&xv)[8]) {
+    const int i = kb * 256 + lane * 8;
+    if (F32X) {
+        const float4 *px = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + i);
+        float4 a = FRESH ? __ldcg(px) : __ldg(px), b = FRESH ? __ldcg(px + 1) : __ldg(px + 1);
+        xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w;
+        xv[4] = b.x; xv[5] = b.y; xv[6] = b.z; xv[7] = b.w;
+    } else {
+        const uint4 *pv = reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(x) + i);
+        uint4 v = FRESH ? __ldcg(pv) : __ldg(pv);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            xv[2 * k] = __uint_as_float(u[k] << 16);
+            xv[2 * k + 1] = __uint_as_float(u[k] & 0xFFFF0000u);
+        }
+    }
+}
+
+// Stage the activations of super-blocks kb_begin, kb_begin + kb_step, ... < kb_end; one warp per
+// super-block.
+template <bool F32X, bool FRESH = false>
+__device__ __forceinline__ void stage_x_warp(const void *x, int kb_begin, int kb_end, int kb_step, uint8_t *xs,
+                                             uint8_t *xs_lo, float *tab, float *xinv, int lane) {
 #pragma unroll 2
     for (int kb = kb_begin; kb < kb_end; kb += kb_step) {
         float xv[8];
-        const int i = kb * 256 + lane * 8;
-        if (F32X) {
-            const float4 *px = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + i);
-            float4 a = __ldg(px), b = __ldg(px + 1);
-            xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w;
-            xv[4] = b.x; xv[5] = b.y; xv[6] = b.z; xv[7] = b.w;
-        } else {
-            uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(x) + i));
-            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        load_x_block<F32X, FRESH>(x, kb, lane, xv);
+        stage_x_block<F32X>(xv, kb, xs, xs_lo, tab, xinv, lane);
+    }
+}
+
+// The same with the loads of up to BATCH super-blocks issued before the first is processed: one
+// memory round trip instead of one per super-block.
+template <bool F32X, bool FRESH, int BATCH>
+__device__ __forceinline__ void stage_x_warp_batched(const void *x, int kb_begin, int kb_end, int kb_step, uint8_t *xs,
+                                                     uint8_t *xs_lo, float *tab, float *xinv, int lane) {
+    for (int kb0 = kb_begin; kb0 < kb_end; kb0 += BATCH * kb_step) {
+        float xv[BATCH][8];
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                xv[2 * k] = __uint_as_float(u[k] << 16);
-                xv[2 * k + 1] = __uint_as_float(u[k] & 0xFFFF0000u);
-            }
-        }
-        float amax = 0.0f;
+        for (int r = 0; r < BATCH; r++)
+            if (kb0 + r * kb_step < kb_end) load_x_block<F32X, FRESH>(x, kb0 + r * kb_step, lane, xv[r]);
 #pragma unroll
-        for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(xv[k]));
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-        uint32_t ex = (__float_as_uint(amax) >> 23) & 0xFFu;
-        ex = amax > 0.0f && ex < 255u ? min(max(ex, 1u), 253u) : 127u;
-        const float scale = __uint_as_float((254u - ex) << 23);
-        uint32_t ph[4], pl[4];
-        float xr[8];  // the values the MMAs will see
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            float s0 = xv[2 * k] * scale, s1 = xv[2 * k + 1] * scale;
-            __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
-            xr[2 * k] = __half2float(h0);
-            xr[2 * k + 1] = __half2float(h1);
-            ph[k] = __half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
-            if (F32X) {
-                __half l0 = __float2half_rn(s0 - xr[2 * k]), l1 = __float2half_rn(s1 - xr[2 * k + 1]);
-                xr[2 * k] += __half2float(l0);
-                xr[2 * k + 1] += __half2float(l1);
-                pl[k] = __half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
-            }
-        }
-        // lane = 4 * sub-block + word: its 32 bytes of the operand image are contiguous
-        uint4 *dst = reinterpret_cast<uint4 *>(xs + kb * 1024 + lane * 32);
-        dst[0] = odd ? make_uint4(0, ph[0], 0, ph[1]) : make_uint4(ph[0], 0, ph[1], 0);
-        dst[1] = odd ? make_uint4(0, ph[2], 0, ph[3]) : make_uint4(ph[2], 0, ph[3], 0);
-        if (F32X) {
-            uint4 *dl = reinterpret_cast<uint4 *>(xs_lo + kb * 1024 + lane * 32);
-            dl[0] = odd ? make_uint4(0, pl[0], 0, pl[1]) : make_uint4(pl[0], 0, pl[1], 0);
-            dl[1] = odd ? make_uint4(0, pl[2], 0, pl[3]) : make_uint4(pl[2], 0, pl[3], 0);
-        }
-        // within a word (8 elements), elements 0,1,4,5 carry offset 1024 and 2,3,6,7 offset 64
-        float sa = (xr[0] + xr[1]) + (xr[4] + xr[5]), sb = (xr[2] + xr[3]) + (xr[6] + xr[7]);
-        float ox = 1024.0f * sa + 64.0f * sb;
-        float sx = sa + sb;
-#pragma unroll
-        for (int o2 = 1; o2 < 4; o2 <<= 1) {  // the 4 lanes of one sub-block are consecutive
-            ox += __shfl_xor_sync(0xFFFFFFFFu, ox, o2);
-            sx += __shfl_xor_sync(0xFFFFFFFFu, sx, o2);
-        }
-        if ((lane & 3) == 0) {
-            float *e = tab + (kb * 4 + (sb8 >> 1)) * 4 + (sb8 & 1);
-            e[0] = ox;
-            e[2] = sx;
-        }
-        if (lane == 0) xinv[kb] = __uint_as_float(ex << 23);
+        for (int r = 0; r < BATCH; r++)
+            if (kb0 + r * kb_step < kb_end) stage_x_block<F32X>(xv[r], kb0 + r * kb_step, xs, xs_lo, tab, xinv, lane);
     }
 }
 
@@ -438,7 +488,10 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     // let the next kernel in the stream start its own weight prefetch; wait for the previous
     // one before touching activations
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (!(P.diag & 2)) asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef NNQ_DIAG
+    if (!(P.diag & 2))
+#endif
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // fused all-reduce: the exchange this launch takes part in (the epoch word is written by the
     // previous exchange, which the wait above has seen complete)
     unsigned ar_seq = 0;
@@ -545,7 +598,9 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
 #pragma unroll 1
             for (int k = 0; k < nkb; k++) {
                 ok &= mbar_wait_fast(bar_s + 8 * slot, phase);
+#ifdef NNQ_DIAG
                 if (!(P.diag & 1))
+#endif
                     tile_mac<F32X>(ring + slot * kTileBytes, xs_s + (kb_lo + k) * 1024, xs_lo_s + (kb_lo + k) * 1024,
                                    tab + (kb_lo + k) * 16, xinv[kb_lo + k], lane, g, t, K, B, BL, yg, yg8);
                 consumed++;
