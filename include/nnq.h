@@ -415,6 +415,18 @@ NNQ_API nnq_status nnq_comm_create(nnq_ctx *ctx, int rank, int world, size_t max
 NNQ_API nnq_status nnq_comm_get_handle(nnq_comm *c, void *handle64);
 NNQ_API nnq_status nnq_comm_open_peers(nnq_comm *c, const void *handles);
 NNQ_API nnq_status nnq_comm_all_reduce(nnq_comm *c, void *buf_dev, nnq_dtype dt, int64_t count, void *stream);
+/* Bound of every device-side wait of kernels that use this communicator, in polls of a flag
+ * (default 2^22, a few seconds). Synchronises the device. After a wait has run out
+ * (NNQ_ERR_TIMEOUT from nnq_device_status) this rank's sequence numbers are out of step with its
+ * peers': destroy the communicators of all ranks and build new ones. Mirrors the Timeout kind of
+ * the reference's backend errors (crates/nn-core/src/error.rs:48-93). */
+NNQ_API nnq_status nnq_comm_set_spin_limit(nnq_comm *c, unsigned polls);
+/* Single-process set-up (one process driving several GPUs with peer access enabled, or several
+ * communicators on one device): instead of exchanging IPC handles, pass every rank's buffer
+ * (nnq_comm_local_buffer of that rank's communicator) as a device pointer valid in this process;
+ * peer_dev_ptrs has `world` entries, the entry of this rank is ignored. */
+NNQ_API nnq_status nnq_comm_local_buffer(nnq_comm *c, void **dev_ptr);
+NNQ_API nnq_status nnq_comm_open_local_peers(nnq_comm *c, void *const *peer_dev_ptrs);
 /* Row-parallel product and its all-reduce in one call: y = sum over ranks of (x_r * W_r^T) + bias,
  * the same y on every rank (pass the same bias everywhere; it is added once). For M = 1 on a tiled
  * Q4_K shard (and max_bytes >= 8 * N) this is ONE kernel: the warp that finishes a row tile sends
@@ -456,11 +468,20 @@ NNQ_API nnq_status nnq_decoder_set_layer(nnq_decoder *d, int layer, const nnq_we
                                          const float *post_norm, const float *q_norm, const float *k_norm);
 NNQ_API nnq_status nnq_decoder_set_head(nnq_decoder *d, const void *embed_bf16_dev, const float *final_norm,
                                         const nnq_weight *lm_head);
-/* Tensor-parallel decoder (tp_world > 1): set_layer takes this rank's shards (q / k / v / gate / up
+/* The caches hold max_seq positions and do not grow (the reference's KvCacheLayer::append doubles
+ * its buffer instead, crates/nn-core/src/layers/generation/kv_cache.rs:132): the step that would
+ * consume position max_seq is refused with NNQ_ERR_UNSUPPORTED by nnq_decoder_step, and, when a
+ * captured graph is replayed past the end, by nnq_device_status (the step then changes no state).
+ * Tensor-parallel decoder (tp_world > 1): set_layer takes this rank's shards (q / k / v / gate / up
  * split by rows: heads [rank * n_heads / world, ...), FFN rows likewise; o / down split along K in
  * the same ranges), norms, embedding and the vocabulary projection are replicated, and the o and
  * down products are exchanged through `comm` (nnq_comm_linear; max_bytes >= 8 * hidden). All ranks
- * hold identical hidden states and produce the same token. */
+ * hold identical hidden states and produce the same token. The vocabulary projection is either
+ * replicated ([vocab, hidden] on every rank) or vocabulary-parallel: set_head takes this rank's
+ * rows [rank * vocab / world, (rank + 1) * vocab / world) (nnq_weight_create_shard, axis 0), each
+ * rank forms the logits of its rows only (at their global offsets in the logits buffer) and the
+ * ranks agree on the greedy token by exchanging (value, index) through `comm`
+ * (max_bytes >= 8 * hidden + 16), keeping the reference's rule that the last of equal maxima wins. */
 NNQ_API nnq_status nnq_decoder_set_comm(nnq_decoder *d, nnq_comm *comm);
 /* next input token and the position it is written at (synchronises the stream) */
 NNQ_API nnq_status nnq_decoder_reset(nnq_decoder *d, int token, int pos, void *stream);

@@ -54,6 +54,9 @@ SIGNATURES = {
     "nnq_comm_get_handle": (c_int, [c_void_p, c_void_p]),
     "nnq_comm_open_peers": (c_int, [c_void_p, c_void_p]),
     "nnq_comm_all_reduce": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
+    "nnq_comm_set_spin_limit": (c_int, [c_void_p, ctypes.c_uint]),
+    "nnq_comm_local_buffer": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "nnq_comm_open_local_peers": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
     "nnq_comm_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
     "nnq_comm_destroy": (None, [c_void_p]),
     "nnq_decoder_create": (c_int, [c_void_p, c_void_p, ctypes.POINTER(c_void_p)]),

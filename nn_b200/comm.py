@@ -10,12 +10,13 @@ from . import api
 
 
 class PeerComm:
-    def __init__(self, backend: api.Backend, rank: int, world: int, max_bytes: int = 1 << 16, group=None):
+    def __init__(self, backend: api.Backend, rank: int, world: int, max_bytes: int = 1 << 16, group=None,
+                 exchange_handles: bool = True):
         self.backend, self.rank, self.world = backend, rank, world
         h = ctypes.c_void_p()
         backend.check(backend._lib.nnq_comm_create(backend._ctx, rank, world, max_bytes, ctypes.byref(h)))
         self._handle = h
-        if world > 1:
+        if world > 1 and exchange_handles:
             import torch.distributed as dist
             mine = ctypes.create_string_buffer(64)
             backend.check(backend._lib.nnq_comm_get_handle(h, mine))
@@ -24,6 +25,22 @@ class PeerComm:
             blob = ctypes.create_string_buffer(b"".join(gathered), 64 * world)
             backend.check(backend._lib.nnq_comm_open_peers(h, blob))
             dist.barrier(group=group)
+
+    def local_buffer(self) -> int:
+        """Device address of this rank's exchange buffer (for open_local_peers of the other ranks)."""
+        p = ctypes.c_void_p()
+        self.backend.check(self.backend._lib.nnq_comm_local_buffer(self._handle, ctypes.byref(p)))
+        return p.value
+
+    def open_local_peers(self, buffers):
+        """Single-process set-up: `buffers[r]` is rank r's local_buffer(), valid in this process."""
+        arr = (ctypes.c_void_p * self.world)(*[ctypes.c_void_p(b) for b in buffers])
+        self.backend.check(self.backend._lib.nnq_comm_open_local_peers(self._handle, arr))
+
+    def set_spin_limit(self, polls: int):
+        """Bound of the device-side waits (polls of a flag); a wait that runs out surfaces as
+        BackendFailure(kind="Timeout") from Backend.device_status()."""
+        self.backend.check(self.backend._lib.nnq_comm_set_spin_limit(self._handle, int(polls)))
 
     def all_reduce(self, tensor, stream=None):
         """In-place sum over the ranks of a contiguous f32 / bf16 CUDA tensor."""

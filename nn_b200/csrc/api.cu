@@ -96,6 +96,7 @@ const char *nnq_status_str(nnq_status s) {
         case NNQ_ERR_DATA_LENGTH: return "data length mismatch";
         case NNQ_ERR_RANK_MISMATCH: return "rank mismatch";
         case NNQ_ERR_UNSUPPORTED: return "unsupported";
+        case NNQ_ERR_VALUE_OUT_OF_RANGE: return "value out of range";
         case NNQ_ERR_OUT_OF_MEMORY: return "backend failure: out of memory";
         case NNQ_ERR_DISPATCH_FAILED: return "backend failure: dispatch failed";
         case NNQ_ERR_TIMEOUT: return "backend failure: timeout";
@@ -193,7 +194,9 @@ nnq_status nnq_device_status(nnq_ctx *ctx, void *stream) {
     if (v == 0) return NNQ_OK;
     check_cuda(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), st), "status clear");
     cudaStreamSynchronize(st);
-    return fail(ctx, v == 1 ? NNQ_ERR_TIMEOUT : NNQ_ERR_OTHER, "device status word = %d", v);
+    if (v == 1) return fail(ctx, NNQ_ERR_TIMEOUT, "a bounded device wait ran out (device status word = 1)");
+    if (v == 2) return fail(ctx, NNQ_ERR_UNSUPPORTED, "a decoder was stepped past its last position (max_seq): its context is full, reset it");
+    return fail(ctx, NNQ_ERR_OTHER, "device status word = %d", v);
 }
 
 int64_t nnq_launch_count(const nnq_ctx *ctx) { return ctx ? ctx->launches : 0; }

@@ -61,14 +61,15 @@ allreduce_oneshot_kernel(uint8_t *const *peers, int rank, int world, size_t slot
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     uint8_t *local = peers[rank];
-    __shared__ unsigned seq_s;
+    __shared__ unsigned seq_s, limit_s;
     __shared__ int failed_s;
     if (threadIdx.x == 0) {
         seq_s = *reinterpret_cast<volatile unsigned *>(local) + 1u;
+        limit_s = comm_spin_limit(local);
         failed_s = 0;
     }
     __syncthreads();
-    const unsigned seq = seq_s;
+    const unsigned seq = seq_s, limit = limit_s;
     const int parity = (int)(seq & 1u);
     // 1. push this rank's vector into every peer (and into its own slot)
     for (int p = 0; p < world; p++) {
@@ -85,7 +86,7 @@ allreduce_oneshot_kernel(uint8_t *const *peers, int rank, int world, size_t slot
         volatile unsigned *my_flag = reinterpret_cast<volatile unsigned *>(local + 64) + p;
         unsigned spins = 0;
         while ((int)(*my_flag - seq) < 0) {
-            if (++spins > kCommSpins) {
+            if (++spins > limit) {
                 failed_s = 1;
                 break;
             }
@@ -143,6 +144,8 @@ nnq_status nnq_comm_create(nnq_ctx *ctx, int rank, int world, size_t max_bytes, 
     const size_t total = comm_data_offset(2, 0, world, c->slot_bytes);
     s = check_cuda(ctx, cudaMalloc(&c->d_local, total), "cudaMalloc comm buffer");
     if (s == NNQ_OK) s = check_cuda(ctx, cudaMemset(c->d_local, 0, total), "cudaMemset comm buffer");
+    const unsigned default_limit = kCommSpins;
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaMemcpy(c->d_local + kCommSpinLimitOffset, &default_limit, 4, cudaMemcpyHostToDevice), "comm wait bound");
     if (s == NNQ_OK) s = check_cuda(ctx, cudaMalloc(&c->d_peer_table, sizeof(uint8_t *) * kCommMaxWorld), "cudaMalloc peer table");
     if (s == NNQ_OK) s = check_cuda(ctx, cudaDeviceSynchronize(), "comm init");
     if (s != NNQ_OK) {
@@ -182,6 +185,32 @@ nnq_status nnq_comm_open_peers(nnq_comm *c, const void *handles) {
         if (s != NNQ_OK) return s;
         c->peer[p] = (uint8_t *)ptr;
         c->opened[p] = true;
+    }
+    return check_cuda(c->ctx, cudaMemcpy(c->d_peer_table, c->peer, sizeof(c->peer), cudaMemcpyHostToDevice), "peer table");
+}
+
+nnq_status nnq_comm_set_spin_limit(nnq_comm *c, unsigned polls) {
+    if (!c || polls == 0) return NNQ_ERR_INVALID_ARG;
+    cudaSetDevice(c->ctx->device);
+    nnq_status s = check_cuda(c->ctx, cudaDeviceSynchronize(), "comm wait bound");
+    if (s == NNQ_OK) s = check_cuda(c->ctx, cudaMemcpy(c->d_local + kCommSpinLimitOffset, &polls, 4, cudaMemcpyHostToDevice), "comm wait bound");
+    return s;
+}
+
+nnq_status nnq_comm_local_buffer(nnq_comm *c, void **dev_ptr) {
+    if (!c || !dev_ptr) return NNQ_ERR_INVALID_ARG;
+    *dev_ptr = c->d_local;
+    return NNQ_OK;
+}
+
+nnq_status nnq_comm_open_local_peers(nnq_comm *c, void *const *peer_dev_ptrs) {
+    if (!c || !peer_dev_ptrs) return NNQ_ERR_INVALID_ARG;
+    cudaSetDevice(c->ctx->device);
+    for (int p = 0; p < c->world; p++) {
+        if (p == c->rank) continue;
+        if (!peer_dev_ptrs[p]) return fail(c->ctx, NNQ_ERR_INVALID_ARG, "peer %d: NULL buffer", p);
+        c->peer[p] = (uint8_t *)peer_dev_ptrs[p];
+        c->opened[p] = false;   // not an IPC mapping: nothing to close
     }
     return check_cuda(c->ctx, cudaMemcpy(c->d_peer_table, c->peer, sizeof(c->peer), cudaMemcpyHostToDevice), "peer table");
 }

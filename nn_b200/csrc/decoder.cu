@@ -16,8 +16,13 @@
 
 #include <new>
 
+#include "comm.cuh"
 #include "nnq_internal.h"
 #include "pdl.cuh"
+
+namespace nnq {
+nnq_status comm_view(nnq_comm *c, CommView *out);   // comm.cu
+}
 
 struct nnq_decoder {
     nnq_ctx *ctx;
@@ -39,6 +44,8 @@ struct nnq_decoder {
     int ready;                  // bit set of what has been supplied
     nnq_comm *comm;             // tensor parallel: exchange of the row-parallel products (NULL when tp_world = 1)
     int lh, lkv;                // query / key-value heads held by this rank
+    int head_rows, head_row0;   // rows of the vocabulary projection held by this rank and the first of them
+    long long host_pos;         // position of the next step as far as the host knows it (-1: unknown)
 };
 
 namespace nnq {
@@ -296,20 +303,78 @@ dec_argmax_stage1_kernel(const float *__restrict__ logits, int n, float *__restr
     }
 }
 
-// picks the winner, records it and advances the device-side (token, position) pair
-__global__ void dec_argmax_stage2_kernel(const float *__restrict__ bv_in, const int *__restrict__ bi_in, int blocks,
-                                         int *__restrict__ state, int *__restrict__ tokens, int max_seq) {
-    pdl_prologue();
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    float bv = -INFINITY;
-    int bi = -1;
-    for (int b = 0; b < blocks; b++) arg_better(bv, bi, bv_in[b], bi_in[b]);
+// Records the winning token and advances the device-side (token, position) pair. state[3] is set
+// by the step that fills the last position; a step that finds it set has nowhere to write:
+// it raises the context's status word (2 = context full) and changes nothing.
+__device__ __forceinline__ void dec_commit_token(int bi, int *state, int *tokens, int max_seq) {
     if (bi < 0) bi = 0;   // all NaN: the reference returns index 0
     const int pos = state[1];
     tokens[pos] = bi;
     state[0] = bi;
     if (pos + 1 < max_seq) state[1] = pos + 1;
+    else state[3] = 1;
     state[2] += 1;
+}
+
+// picks the winner among the block maxima
+__global__ void dec_argmax_stage2_kernel(const float *__restrict__ bv_in, const int *__restrict__ bi_in, int blocks,
+                                         int *__restrict__ state, int *__restrict__ tokens, int max_seq, int *status) {
+    pdl_prologue();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    if (state[3]) {
+        atomicExch(status, 2);
+        return;
+    }
+    float bv = -INFINITY;
+    int bi = -1;
+    for (int b = 0; b < blocks; b++) arg_better(bv, bi, bv_in[b], bi_in[b]);
+    dec_commit_token(bi, state, tokens, max_seq);
+}
+
+// Vocabulary-parallel head: every rank holds the maximum of its slice of the logits; the ranks
+// exchange (value, index) through the last 16 bytes of their communicator slots as two 8-byte
+// (payload, sequence number) stores, wait (bounded) for the peers' records and all pick the same
+// winner: the larger value, of equal values the larger index -- the reference's "last maximum"
+// rule survives the gather because it only depends on (value, index), not on arrival order.
+__global__ void dec_argmax_exchange_kernel(const float *__restrict__ bv_in, const int *__restrict__ bi_in, int blocks,
+                                           int index_offset, uint8_t *const *peers, int rank, int world, size_t slot_bytes,
+                                           int *__restrict__ state, int *__restrict__ tokens, int max_seq, int *status) {
+    pdl_prologue();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    uint8_t *local = peers[rank];
+    const unsigned seq = *reinterpret_cast<volatile unsigned *>(local) + 1u;
+    const unsigned limit = comm_spin_limit(local);
+    float bv = -INFINITY;
+    int bi = -1;
+    for (int b = 0; b < blocks; b++) arg_better(bv, bi, bv_in[b], bi_in[b]);
+    if (bi >= 0) bi += index_offset;
+    const int par = (int)(seq & 1u);
+    const size_t mine = comm_data_offset(par, rank, world, slot_bytes) + slot_bytes - 16;
+    for (int p = 0; p < world; p++) {
+        if (p == rank) continue;
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(peers[p] + mine), "r"(__float_as_uint(bv)), "r"(seq) : "memory");
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(peers[p] + mine + 8), "r"((unsigned)bi), "r"(seq) : "memory");
+    }
+    bool ok = true;
+    for (int r = 0; r < world; r++) {
+        if (r == rank) continue;
+        const uint8_t *src = local + comm_data_offset(par, r, world, slot_bytes) + slot_bytes - 16;
+        uint32_t vb = 0, ib = 0, t0 = 0, t1 = 0;
+        unsigned spins = 0;
+        do {
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(vb), "=r"(t0) : "l"(src) : "memory");
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(ib), "=r"(t1) : "l"(src + 8) : "memory");
+        } while ((t0 != seq || t1 != seq) && ++spins <= limit);
+        if (t0 != seq || t1 != seq) {
+            ok = false;
+            continue;
+        }
+        arg_better(bv, bi, __uint_as_float(vb), (int)ib);
+    }
+    if (!ok) atomicExch(status, 1);
+    if (state[3]) atomicExch(status, 2);
+    else dec_commit_token(bi, state, tokens, max_seq);
+    *reinterpret_cast<volatile unsigned *>(local) = seq;   // this exchange is complete
 }
 
 }  // namespace nnq
@@ -351,6 +416,9 @@ nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_d
     d->act_dt = c.act_dtype;
     d->lh = c.n_heads / c.tp_world;
     d->lkv = c.n_kv_heads / c.tp_world;
+    d->head_rows = c.vocab;
+    d->head_row0 = 0;
+    d->host_pos = -1;
     d->layers = new (std::nothrow) nnq_decoder::Layer[c.n_layers]();
     if (!d->layers) {
         delete d;
@@ -444,7 +512,19 @@ nnq_status nnq_decoder_set_head(nnq_decoder *d, const void *embed_bf16_dev, cons
     if (!d) return NNQ_ERR_INVALID_ARG;
     nnq_ctx *ctx = d->ctx;
     if (!embed_bf16_dev || !final_norm) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL tensor");
-    if (!shape_is(lm_head, d->cfg.vocab, d->cfg.hidden)) return fail(ctx, NNQ_ERR_SHAPE_MISMATCH, "vocabulary projection must be [vocab, hidden]");
+    // tensor parallel: either the whole [vocab, hidden] projection on every rank, or this rank's
+    // rows [rank * vocab / world, (rank + 1) * vocab / world) of it (vocabulary parallel: the ranks
+    // then agree on the greedy token through the communicator)
+    const nnq_decoder_config &c = d->cfg;
+    if (shape_is(lm_head, c.vocab, c.hidden)) {
+        d->head_rows = c.vocab;
+        d->head_row0 = 0;
+    } else if (c.tp_world > 1 && c.vocab % c.tp_world == 0 && shape_is(lm_head, c.vocab / c.tp_world, c.hidden)) {
+        d->head_rows = c.vocab / c.tp_world;
+        d->head_row0 = c.tp_rank * d->head_rows;
+    } else {
+        return fail(ctx, NNQ_ERR_SHAPE_MISMATCH, "vocabulary projection must be [vocab, hidden] (or this rank's [vocab / world, hidden] rows)");
+    }
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
     d->d_embed = embed_bf16_dev;
@@ -465,6 +545,7 @@ nnq_status nnq_decoder_reset(nnq_decoder *d, int token, int pos, void *stream) {
     if (token < 0 || token >= d->cfg.vocab || pos < 0 || pos >= d->cfg.max_seq) return fail(d->ctx, NNQ_ERR_INVALID_ARG, "token or position out of range");
     cudaSetDevice(d->ctx->device);
     const int st[4] = {token, pos, 0, 0};
+    d->host_pos = pos;
     nnq_status s = check_cuda(d->ctx, cudaMemcpyAsync(d->d_state, st, sizeof(st), cudaMemcpyHostToDevice, (cudaStream_t)stream), "decoder state");
     if (s == NNQ_OK) s = check_cuda(d->ctx, cudaStreamSynchronize((cudaStream_t)stream), "decoder state");   // st is on the stack
     return s;
@@ -487,6 +568,20 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
     if (c.tp_world > 1 && !d->comm) return fail(ctx, NNQ_ERR_INVALID_ARG, "communicator has not been set");
     for (int l = 0; l < c.n_layers; l++)
         if (!d->layers[l].q) return fail(ctx, NNQ_ERR_INVALID_ARG, "layer %d has not been set", l);
+    // The caches hold max_seq positions and never grow (the reference's KvCacheLayer::append doubles
+    // its buffer instead): a step past the last position is refused here, and -- for captured graphs
+    // that the host does not see being replayed -- by the device-side flag behind nnq_device_status.
+    if (d->host_pos >= c.max_seq)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "the decoder's context is full (max_seq = %d positions): reset it", c.max_seq);
+    if (d->host_pos >= 0) d->host_pos++;
+    const bool vocab_parallel = d->head_rows != c.vocab;
+    CommView cv = {};
+    if (vocab_parallel) {
+        nnq_status sv = comm_view(d->comm, &cv);
+        if (sv != NNQ_OK) return sv;
+        if (cv.slot_bytes < (size_t)8 * c.hidden + 16)
+            return fail(ctx, NNQ_ERR_UNSUPPORTED, "a vocabulary-parallel head needs communicator slots of at least 8 * hidden + 16 bytes (have %zu)", cv.slot_bytes);
+    }
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
     cudaStream_t st = (cudaStream_t)stream;
@@ -532,11 +627,17 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
         ctx->launches += 6;
     }
     launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, d->d_final_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
-    if ((s = nnq_linear(ctx, d->lm_head, d->d_xn, adt, 1, nullptr, d->d_logits, NNQ_F32, st)) != NNQ_OK) return s;
+    // the logits of this rank's rows land at their global offsets in the [vocab] buffer
+    float *logits = d->d_logits + d->head_row0;
+    if ((s = nnq_linear(ctx, d->lm_head, d->d_xn, adt, 1, nullptr, logits, NNQ_F32, st)) != NNQ_OK) return s;
     float *bv = reinterpret_cast<float *>(d->d_state + 4);
     int *bi = d->d_state + 4 + kArgmaxBlocks;
-    launch_pdl(dec_argmax_stage1_kernel, dim3(kArgmaxBlocks), dim3(256), st, d->d_logits, c.vocab, bv, bi);
-    launch_pdl(dec_argmax_stage2_kernel, dim3(1), dim3(32), st, bv, bi, kArgmaxBlocks, d->d_state, d->d_tokens, c.max_seq);
+    launch_pdl(dec_argmax_stage1_kernel, dim3(kArgmaxBlocks), dim3(256), st, logits, d->head_rows, bv, bi);
+    if (vocab_parallel)
+        launch_pdl(dec_argmax_exchange_kernel, dim3(1), dim3(32), st, bv, bi, kArgmaxBlocks, d->head_row0, cv.peer_table, cv.rank, cv.world,
+                   cv.slot_bytes, d->d_state, d->d_tokens, c.max_seq, ctx->d_status);
+    else
+        launch_pdl(dec_argmax_stage2_kernel, dim3(1), dim3(32), st, bv, bi, kArgmaxBlocks, d->d_state, d->d_tokens, c.max_seq, ctx->d_status);
     ctx->launches += 3;
     return check_cuda(ctx, cudaGetLastError(), "decoder step launch");
 }

@@ -21,7 +21,7 @@
 // order (fixed order: deterministic). Counters only ever count up (a row tile with n parts is
 // complete when its counter is a multiple of n), so nothing is reset between launches.
 #pragma once
-#include "q4k_e4m3.cuh"
+#include "skinny_m1.cuh"
 
 namespace nnq {
 
@@ -121,17 +121,6 @@ __host__ __device__ inline PlanSmem plan_smem(int kt_max, int acc_slots, int sta
     return p;
 }
 
-// Bounded wait that sleeps between tries: a warp whose tile has not arrived yet leaves the issue
-// slots (and the half-rate logic pipe its loop counter runs on) to the warps that have work.
-__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    for (unsigned i = 0; i < kWaitSpins; i++) {
-        __nanosleep(64);
-        if (mbar_try_wait(bar, parity)) return true;
-    }
-    return false;
-}
-
 // read-only load of a pointer field of a descriptor
 template <typename T>
 __device__ __forceinline__ T *ldg_ptr(T *const *p) {
@@ -176,8 +165,11 @@ plan_q4k_kernel(const __grid_constant__ PlanParams P) {
     // every launch of the plan adds nc arrivals to each group's counter
     const unsigned epoch = *reinterpret_cast<volatile unsigned *>(P.epoch);
     const unsigned target = (epoch + 1u) * (unsigned)nc;
-    unsigned ar_base = 0;
-    if (P.nfused) ar_base = *reinterpret_cast<volatile unsigned *>(P.fr.peers[P.fr.rank]);
+    unsigned ar_base = 0, ar_limit = 0;
+    if (P.nfused) {
+        ar_base = *reinterpret_cast<volatile unsigned *>(P.fr.peers[P.fr.rank]);
+        ar_limit = comm_spin_limit(P.fr.peers[P.fr.rank]);
+    }
 
     // ---- weight stream of this warp: runs ahead of the compute, across group boundaries ----
     int pf_g = -1, pf_i = 0, pf_hi = 0, pf_job_end = 0, pf_slot = 0;
@@ -275,7 +267,7 @@ plan_q4k_kernel(const __grid_constant__ PlanParams P) {
                 unsigned spins = 0;
                 do {
                     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(tag) : "l"(src) : "memory");
-                } while (tag != seq && ++spins <= P.spin_limit);
+                } while (tag != seq && ++spins <= ar_limit);
                 ok = ok && tag == seq;
                 sum += __uint_as_float(bits);
             }
@@ -328,8 +320,7 @@ plan_q4k_kernel(const __grid_constant__ PlanParams P) {
         if (*dead) break;   // uniform: nobody writes the flag between this barrier and the next
         PLAN_STAMP(1)
         const void *gx = gd->x;
-        if (F32X) stage_x_warp_batched<F32X, true, 1>(gx, warp, kt, kPlanWarps, xs, xs_lo, tab, xinv, lane);
-        else stage_x_warp_e4m3<true, 3>(gx, warp, kt, kPlanWarps, xs, tab, xinv, lane);
+        stage_x_warp_batched<F32X, true, F32X ? 1 : 3>(gx, warp, kt, kPlanWarps, xs, xs_lo, tab, xinv, lane);
         __syncthreads();
         PLAN_STAMP(2)
 
@@ -340,7 +331,7 @@ plan_q4k_kernel(const __grid_constant__ PlanParams P) {
             const int kstep = kPlanWarps % kt;
 #pragma unroll 1
             for (; i < hi; i += kPlanWarps) {
-                if (!warp_failed && !mbar_wait_backoff(bar_s + 8 * slot, phase)) {
+                if (!warp_failed && !mbar_wait_fast(bar_s + 8 * slot, phase)) {
                     // the copy never landed: record it and stop touching the ring (the copies
                     // still in flight are waited for, bounded, before the kernel returns)
                     warp_failed = true;
@@ -351,11 +342,8 @@ plan_q4k_kernel(const __grid_constant__ PlanParams P) {
                 }
                 if (warp_failed) continue;
                 float yg = 0.0f, yg8 = 0.0f;
-                if (F32X)
-                    tile_mac<F32X>(ring + slot * kTileBytes, xs_s + kb * 1024, xs_lo_s + kb * 1024, tab + kb * 16, xinv[kb],
-                                   lane, g, t, K, B, BL, yg, yg8);
-                else
-                    tile_mac_e4m3(ring + slot * kTileBytes, xs_s + kb * 1024, tab + kb * 16, xinv[kb], lane, g, t, B, yg, yg8);
+                tile_mac<F32X>(ring + slot * kTileBytes, xs_s + kb * 1024, xs_lo_s + kb * 1024, tab + kb * 16, xinv[kb],
+                               lane, g, t, K, B, BL, yg, yg8);
                 yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 1);
                 yg8 += __shfl_xor_sync(0xFFFFFFFFu, yg8, 1);
                 yg += __shfl_xor_sync(0xFFFFFFFFu, yg, 2);

@@ -494,8 +494,11 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // fused all-reduce: the exchange this launch takes part in (the epoch word is written by the
     // previous exchange, which the wait above has seen complete)
-    unsigned ar_seq = 0;
-    if (FUSED) ar_seq = *reinterpret_cast<volatile unsigned *>(P.fr.peers[P.fr.rank]) + 1u;
+    unsigned ar_seq = 0, ar_limit = 0;
+    if (FUSED) {
+        ar_seq = *reinterpret_cast<volatile unsigned *>(P.fr.peers[P.fr.rank]) + 1u;
+        ar_limit = comm_spin_limit(P.fr.peers[P.fr.rank]);
+    }
 
     if (KS == kWarps) {
         // the warp owns its part of K: no other warp reads what it stages
@@ -549,7 +552,7 @@ skinny_q4k_m1_kernel(const __grid_constant__ SkinnyParams P) {
                     unsigned spins = 0;
                     do {
                         asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(tag) : "l"(src) : "memory");
-                    } while (tag != ar_seq && ++spins <= kCommSpins);
+                    } while (tag != ar_seq && ++spins <= ar_limit);
                     ok = ok && tag == ar_seq;
                     acc += __uint_as_float(bits);
                 }

@@ -13,12 +13,24 @@ Follows, in the reference tree:
   crates/nn-core/src/dyn_tensor/ops/math.rs:140          silu(x) = x / (1 + exp(-x))
   crates/nn-core/src/layers/generation/autoregressive_sampling.rs:14-21   argmax, last of equal maxima
 Weights are given dequantized (f32 [n, k]); the quantized decode itself is pinned elsewhere.
+
+`act_bf16=True` rounds the four vectors per layer that feed a product (the normed hidden state
+twice, the attention output, silu(gate) * up) and the final normed state to bf16 (round to nearest
+even) before the product, and leaves everything else in f32: the rounding points of a decoder
+whose products take bf16 activations.
 """
 from __future__ import annotations
 
 import numpy as np
 
 F = np.float32
+
+
+def bf16_round(x):
+    """f32 -> nearest bf16 (ties to even) -> f32."""
+    u = np.ascontiguousarray(x, dtype=F).view(np.uint32)
+    r = ((u >> np.uint32(16)) & np.uint32(1)) + np.uint32(0x7FFF)
+    return ((u + r) & np.uint32(0xFFFF0000)).view(F)
 
 
 def rms_norm(x, w, eps):
@@ -45,7 +57,7 @@ def argmax_last(v) -> int:
     return int(len(v) - 1 - np.argmax(v[::-1]))
 
 
-def step(model: dict, token: int, pos: int, kcache: np.ndarray, vcache: np.ndarray):
+def step(model: dict, token: int, pos: int, kcache: np.ndarray, vcache: np.ndarray, act_bf16: bool = False):
     """model: cfg (dict), embed [vocab, hidden] f32, layers (list of dicts with q k v o gate up down
     in_norm post_norm q_norm k_norm), final_norm, lm_head. kcache / vcache: [layers, kv_heads,
     max_seq, head_dim] f32, updated in place at `pos`. Returns (logits f32 [vocab], next token)."""
@@ -54,8 +66,9 @@ def step(model: dict, token: int, pos: int, kcache: np.ndarray, vcache: np.ndarr
     cos, sin = model["rope"]
     h = model["embed"][token].astype(F)
     scale = F(1.0 / np.sqrt(float(hd)))
+    act = bf16_round if act_bf16 else (lambda a: a)
     for li, L in enumerate(model["layers"]):
-        x = rms_norm(h, L["in_norm"], eps)
+        x = act(rms_norm(h, L["in_norm"], eps))
         q = (L["q"] @ x).reshape(nh, hd)
         k = (L["k"] @ x).reshape(nkv, hd)
         v = (L["v"] @ x).reshape(nkv, hd)
@@ -70,11 +83,11 @@ def step(model: dict, token: int, pos: int, kcache: np.ndarray, vcache: np.ndarr
             p = np.exp(s - s.max(), dtype=F)
             p = p / p.sum(dtype=F)
             out[head] = p @ vcache[li, kv, : pos + 1, :]
-        h = h + L["o"] @ out.reshape(-1)
-        x = rms_norm(h, L["post_norm"], eps)
+        h = h + L["o"] @ act(out.reshape(-1))
+        x = act(rms_norm(h, L["post_norm"], eps))
         g = L["gate"] @ x
         u = L["up"] @ x
         with np.errstate(over="ignore"):   # exp(-g) may reach +inf, which gives the correct limit 0
-            h = h + L["down"] @ ((g / (F(1.0) + np.exp(-g, dtype=F))) * u)
-    logits = (model["lm_head"] @ rms_norm(h, model["final_norm"], eps)).astype(F)
+            h = h + L["down"] @ act((g / (F(1.0) + np.exp(-g, dtype=F))) * u)
+    logits = (model["lm_head"] @ act(rms_norm(h, model["final_norm"], eps))).astype(F)
     return logits, argmax_last(logits)

@@ -29,7 +29,9 @@ def oracle_linear(fmt, w, scales, x, bias, n, k):
 
 
 def max_rel_err(y, ref):
-    """max |y - ref| over the largest |ref|: the 'max relative error' of the tolerance."""
+    """max |y - ref| over the largest |ref|: the 'max relative error' of the tolerance. One scale
+    for the whole output, so it says little about small elements next to large ones: every bar in
+    these tests is asserted on this measure AND on max_scaled_err, the element-wise one."""
     denom = float(np.max(np.abs(ref))) or 1.0
     return float(np.max(np.abs(y.astype(np.float64) - ref.astype(np.float64)))) / denom
 

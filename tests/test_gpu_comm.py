@@ -71,6 +71,55 @@ def test_fused_linear_world_one_matches_plain_product():
     wt.release()
 
 
+def test_a_peer_that_never_arrives_ends_in_a_timeout_status():
+    """Failure made on the host: rank 0 of a two-rank world whose rank 1 never calls. Both
+    communicators live in this process on one device (rank 1's buffer is plain local memory that
+    nobody writes), the wait bound is short, and nothing faults: the kernel returns, the status
+    word reads Timeout once and is clear afterwards, and a healthy communicator still works."""
+    b = api.gpu_backend()
+    c0 = comm.PeerComm(b, 0, 2, max_bytes=4096, exchange_handles=False)
+    c1 = comm.PeerComm(b, 1, 2, max_bytes=4096, exchange_handles=False)
+    bufs = [c0.local_buffer(), c1.local_buffer()]
+    c0.open_local_peers(bufs)
+    c1.open_local_peers(bufs)
+    c0.set_spin_limit(2000)
+    x = torch.ones(256, device="cuda:0")
+    c0.all_reduce(x)                      # rank 1 never publishes: the bounded wait runs out
+    torch.cuda.synchronize()
+    with pytest.raises(api.BackendFailure) as e:
+        b.device_status()
+    assert e.value.kind == "Timeout"
+    b.device_status()                     # cleared by the read
+    # the fused product + exchange kernel gives up the same way
+    from nn_b200 import formats as F
+    from nn_b200.formats import QuantFormat as Q
+    n, k = 320, 2048
+    w, _ = F.gen_weight(Q.Q4_K, 3, n, k)
+    wt = api.from_quantized(w, Q.Q4_K, [n, k])
+    xs = torch.from_numpy(F.gen_activations(4, 1, k, bf16=True)).to("cuda:0").to(torch.bfloat16)
+    c0.linear(xs, wt, None)
+    torch.cuda.synchronize()
+    with pytest.raises(api.BackendFailure) as e:
+        b.device_status()
+    assert e.value.kind == "Timeout"
+    # a healthy world-1 communicator on the same context is unaffected
+    c = comm.PeerComm(b, 0, 1, max_bytes=4096)
+    y = torch.arange(100, device="cuda:0", dtype=torch.float32)
+    c.all_reduce(y)
+    torch.cuda.synchronize()
+    b.device_status()
+    assert torch.equal(y, torch.arange(100, device="cuda:0", dtype=torch.float32))
+    want = api.quantized_linear(xs, wt, None, out_dtype=torch.float32)
+    c2 = comm.PeerComm(b, 0, 1, max_bytes=n * 8)
+    got = c2.linear(xs, wt, None)
+    torch.cuda.synchronize()
+    b.device_status()
+    assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+    for cc in (c, c2, c0, c1):
+        cc.release()
+    wt.release()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -116,9 +165,20 @@ def _worker(rank, world, port, out):
             want = api.quantized_linear(x, full, bias, out_dtype=torch.float32)
             torch.cuda.synchronize()
             ok = ok and float((got - want).abs().max()) <= 1e-4 * float(want.abs().max())
+            # identical bits on every rank
+            sums = [None] * world
+            dist.all_gather_object(sums, got.cpu().numpy().tobytes())
+            ok = ok and all(s_ == sums[0] for s_ in sums)
+            # fused exchanges and plain all-reduces alternate on one communicator
+            z = torch.full((64,), float(rank + 1), device=dev)
+            c.all_reduce(z)
+            torch.cuda.synchronize()
+            ok = ok and bool((z == float(world * (world + 1) // 2)).all())
         b.device_status()
+        oks = [None] * world
+        dist.all_gather_object(oks, bool(ok))     # a wrong result on any rank fails the test
         if rank == 0:
-            np.save(out, np.array([1 if ok else 0]))
+            np.save(out, np.array([1 if all(oks) else 0]))
         dist.barrier()
         c.release()
     finally:

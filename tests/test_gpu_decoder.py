@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _build(act_dtype, seed=11, backend=None, tp=(0, 1), comm=None):
+def _build(act_dtype, seed=11, backend=None, tp=(0, 1), comm=None, vocab_parallel=False):
     """Decoder + dequantized model; with tp = (rank, world) the decoder holds that rank's shards."""
     rank, world = tp
     cfg = decoder.DecoderConfig(hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, n_layers=2, vocab=1024,
@@ -63,16 +63,24 @@ def _build(act_dtype, seed=11, backend=None, tp=(0, 1), comm=None):
     model["embed"] = embed_bf16.float().cpu().numpy()
     model["final_norm"] = norm(cfg.hidden)
     head, head_f = qw(Q.Q6_K, cfg.vocab, cfg.hidden, seed + 99)
+    if vocab_parallel and world > 1:
+        head = head.shard(0, rank, world)     # this rank's rows of the vocabulary projection
     model["lm_head"] = head_f
     dec.set_head(embed_bf16, model["final_norm"], head)
     return cfg, dec, model, (keep, head, embed_bf16)
 
 
-@pytest.mark.parametrize("act_dtype,tol", [(api.F32, 2e-3), (api.BF16, 3e-2)])
+@pytest.mark.parametrize("act_dtype,tol", [(api.F32, 2e-3), (api.BF16, 1e-2)])
 def test_decode_steps_match_reference_restatement(act_dtype, tol):
+    """f32 product inputs: the reference's arithmetic, 2e-3. bf16 product inputs: 1e-2 against the
+    restatement with the same rounding points (the normed states, the attention output and
+    silu(gate) * up rounded to bf16 before their products), and a looser 3e-2 against the all-f32
+    restatement -- input rounding of 2^-9 per element and product grows with depth, which is a
+    property of feeding bf16 activations, not of the kernels."""
     cfg, dec, model, keep = _build(act_dtype)
     kc = np.zeros((cfg.n_layers, cfg.n_kv_heads, cfg.max_seq, cfg.head_dim), np.float32)
     vc = np.zeros_like(kc)
+    kc32, vc32 = np.zeros_like(kc), np.zeros_like(kc)
     dec.reset(3, 0)
     token = 3
     _, _, logits_dev, tokens_dev = dec.buffers()
@@ -82,10 +90,14 @@ def test_decode_steps_match_reference_restatement(act_dtype, tol):
         nxt, npos, steps = dec.state()
         assert (npos, steps) == (pos + 1, pos + 1)
         got = logits_dev.cpu().numpy()
-        want, want_tok = ref.step(model, token, pos, kc, vc)   # teacher-forced with the device's tokens
+        # teacher-forced with the device's tokens
+        want, want_tok = ref.step(model, token, pos, kc, vc, act_bf16=(act_dtype == api.BF16))
         assert np.all(np.isfinite(got))
         err = np.max(np.abs(got - want)) / np.max(np.abs(want))
         assert err <= tol, (pos, err)
+        if act_dtype == api.BF16:
+            want32, _ = ref.step(model, token, pos, kc32, vc32)
+            assert np.max(np.abs(got - want32)) / np.max(np.abs(want32)) <= 3e-2
         assert nxt == ref.argmax_last(got)          # the device argmax is the argmax of the device logits
         top2 = np.sort(want)[-2:]
         if top2[1] - top2[0] > 4 * tol * np.max(np.abs(want)):
@@ -96,8 +108,121 @@ def test_decode_steps_match_reference_restatement(act_dtype, tol):
     assert agree >= 1
     dec.backend.device_status()
     k_dev, v_dev, _, _ = dec.buffers()
-    assert np.max(np.abs(k_dev[:, :, :10].cpu().numpy() - kc[:, :, :10])) <= (5e-3 if act_dtype == api.F32 else 1e-1)
+    assert np.max(np.abs(k_dev[:, :, :10].cpu().numpy() - kc[:, :, :10])) <= (5e-3 if act_dtype == api.F32 else 5e-2)
     dec.release()
+
+
+def test_context_full_is_reported_not_overwritten():
+    """max_seq positions and no more: the host refuses the step past the end, and a captured graph
+    replayed past the end raises the device status word instead of reusing the last slot."""
+    b = api.gpu_backend()
+    cfg, dec, model, keep = _build(api.BF16, seed=51)
+    dec.reset(3, cfg.max_seq - 3)
+    for _ in range(3):
+        dec.step()
+    tok, pos, steps = dec.state()
+    assert (pos, steps) == (cfg.max_seq - 1, 3)
+    b.device_status()
+    with pytest.raises(api.Unsupported):
+        dec.step()
+    toks_before = dec.buffers()[3].clone()
+    # graph replay: the host does not see the steps
+    stream = torch.cuda.Stream(device=DEV)
+    dec.reset(3, cfg.max_seq - 2, stream)
+    with torch.cuda.stream(stream):
+        dec.step(stream)
+        stream.synchronize()
+        dec.reset(3, cfg.max_seq - 2, stream)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            dec.step(torch.cuda.current_stream())
+        g.replay()
+        g.replay()
+        stream.synchronize()
+        b.device_status(stream)          # two steps fit
+        tok2, pos2, steps2 = dec.state(stream)
+        assert (pos2, steps2) == (cfg.max_seq - 1, 2)
+        last = dec.buffers()[3][cfg.max_seq - 1].item()
+        g.replay()                        # no position left
+        stream.synchronize()
+        with pytest.raises(api.Unsupported):
+            b.device_status(stream)
+        b.device_status(stream)           # reported once, then clear
+        assert dec.state(stream) == (tok2, pos2, steps2)
+        assert dec.buffers()[3][cfg.max_seq - 1].item() == last
+    dec.reset(1, 0)
+    dec.step()                            # usable again after a reset
+    b.device_status()
+    dec.release()
+
+
+@pytest.mark.parametrize("act_dtype,tol", [(api.F32, 2e-3), (api.BF16, 1e-2)])
+def test_qwen3_8b_width_steps_at_long_context(act_dtype, tol):
+    """The benchmark's widths (hidden 4096, 32 query / 8 key-value heads, FFN 12288, vocabulary
+    151936, Q4_K projections, Q6_K vocabulary projection), two layers, three tokens from position
+    2048 over caches filled with seeded values. Weights are drawn on the device (the SplitMix64
+    host stream would take minutes at this size) and dequantized by the oracle for the restatement."""
+    from nn_b200 import workload as W
+    b = api.gpu_backend()
+    n_layers, start = 2, 2048
+    cfg = decoder.DecoderConfig(n_layers=n_layers, max_seq=start + 8, act_dtype=act_dtype)
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(808)
+    rng = np.random.default_rng(809)
+
+    def qw(fmt, genfn, n, k, scale):
+        raw = genfn(torch, gen, n, k, scale)
+        w = api.DeviceWeight.from_device(b, fmt, raw, n, k)
+        return w, orc.dequantize(fmt, raw.cpu().numpy(), n * k).reshape(n, k)
+
+    dec = decoder.Decoder(b, cfg)
+    model = {"cfg": dict(n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, head_dim=cfg.head_dim, rms_eps=cfg.rms_eps),
+             "rope": ref.rope_tables(cfg.head_dim, cfg.max_seq, cfg.rope_theta), "layers": []}
+    keep = []
+    qdim, kvdim = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    shapes = [("q", qdim, cfg.hidden), ("k", kvdim, cfg.hidden), ("v", kvdim, cfg.hidden), ("o", cfg.hidden, qdim),
+              ("gate", cfg.ffn, cfg.hidden), ("up", cfg.ffn, cfg.hidden), ("down", cfg.hidden, cfg.ffn)]
+    for li in range(n_layers):
+        L, ws = {}, []
+        for name, n, k in shapes:
+            # block scales small enough that the residual stream stays of order one
+            w, wf = qw(Q.Q4_K, W.gen_q4_k_device, n, k, 2e-5)
+            ws.append(w)
+            L[name] = wf
+        for name, n in (("in_norm", cfg.hidden), ("post_norm", cfg.hidden), ("q_norm", cfg.head_dim), ("k_norm", cfg.head_dim)):
+            L[name] = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        dec.set_layer(li, *ws, L["in_norm"], L["post_norm"], L["q_norm"], L["k_norm"])
+        model["layers"].append(L)
+        keep.append(ws)
+    embed_bf16 = (torch.randn(cfg.vocab, cfg.hidden, device=DEV, generator=gen) * 0.5).to(torch.bfloat16)
+    model["embed"] = embed_bf16.float().cpu().numpy()
+    model["final_norm"] = (1.0 + 0.1 * rng.standard_normal(cfg.hidden)).astype(np.float32)
+    head, head_f = qw(Q.Q6_K, W.gen_q6_k_device, cfg.vocab, cfg.hidden, 1e-3)
+    model["lm_head"] = head_f
+    dec.set_head(embed_bf16, model["final_norm"], head)
+    kdev, vdev, logits_dev, _ = dec.buffers()
+    kdev[:, :, :start].normal_(generator=gen)
+    vdev[:, :, :start].normal_(generator=gen)
+    kc, vc = kdev.cpu().numpy().copy(), vdev.cpu().numpy().copy()
+    token = 1234
+    dec.reset(token, start)
+    for i in range(3):
+        dec.step()
+        nxt, npos, _ = dec.state()
+        assert npos == start + i + 1
+        got = logits_dev.cpu().numpy()
+        want, _ = ref.step(model, token, start + i, kc, vc, act_bf16=(act_dtype == api.BF16))
+        assert np.all(np.isfinite(got))
+        err = np.max(np.abs(got - want)) / np.max(np.abs(want))
+        assert err <= tol, (i, err)
+        assert nxt == ref.argmax_last(got)
+        token = nxt
+    b.device_status()
+    dec.release()
+    head.release()
+    for ws in keep:
+        for w in ws:
+            w.release()
 
 
 def test_generate_graph_replay_equals_stepwise():
@@ -139,25 +264,29 @@ def _tp_worker(rank, world, port, out):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         b = api.Backend(rank)
-        c = comm.PeerComm(b, rank, world, max_bytes=512 * 8)
-        cfg, dec, model, keep = _build(api.BF16, seed=41, backend=b, tp=(rank, world), comm=c)
-        toks = dec.generate(9, 0, 8, use_graph=True)
-        logits = dec.buffers()[2].cpu().numpy()
+        c = comm.PeerComm(b, rank, world, max_bytes=512 * 8 + 256)
+        cfg1, dec1, model1, keep1 = _build(api.BF16, seed=41, backend=b)      # the single-GPU decoder, on every rank
+        want = dec1.generate(9, 0, 8, use_graph=False)
+        l1 = dec1.buffers()[2].cpu().numpy()
         ok = True
+        for vocab_parallel in (False, True):
+            cfg, dec, model, keep = _build(api.BF16, seed=41, backend=b, tp=(rank, world), comm=c, vocab_parallel=vocab_parallel)
+            toks = dec.generate(9, 0, 8, use_graph=True)
+            logits = dec.buffers()[2].cpu().numpy()
+            rows = slice(rank * cfg.vocab // world, (rank + 1) * cfg.vocab // world) if vocab_parallel else slice(0, cfg.vocab)
+            ok = ok and toks == want
+            ok = ok and float(np.max(np.abs(logits[rows] - l1[rows]))) <= 2e-3 * float(np.max(np.abs(l1)))
+            gathered = [None] * world
+            dist.all_gather_object(gathered, toks)
+            ok = ok and all(g == gathered[0] for g in gathered)     # every rank produced the same tokens
+            b.device_status()
+            dec.release()
+        dec1.release()
+        oks = [None] * world
+        dist.all_gather_object(oks, bool(ok))                       # every rank's verdict counts
         if rank == 0:
-            cfg1, dec1, model1, keep1 = _build(api.BF16, seed=41, backend=b)
-            want = dec1.generate(9, 0, 8, use_graph=False)
-            l1 = dec1.buffers()[2].cpu().numpy()
-            ok = toks == want and float(np.max(np.abs(logits - l1))) <= 2e-3 * float(np.max(np.abs(l1)))
-            dec1.release()
-        gathered = [None] * world
-        dist.all_gather_object(gathered, toks)
-        ok = ok and all(g == gathered[0] for g in gathered)     # every rank produced the same tokens
-        b.device_status()
-        if rank == 0:
-            np.save(out, np.array([1 if ok else 0]))
+            np.save(out, np.array([1 if all(oks) else 0]))
         dist.barrier()
-        dec.release()
         c.release()
     finally:
         dist.destroy_process_group()

@@ -9,6 +9,7 @@ torch = pytest.importorskip("torch")
 from nn_b200 import api
 from nn_b200 import formats as F
 from nn_b200.formats import QuantFormat as Q
+from oracle import cpu as orc
 from tests import parity as P
 
 pytestmark = pytest.mark.gpu
@@ -353,3 +354,57 @@ def test_q4_k_activation_range(scale, x_bf16):
     y32, y64, mag = P.oracle_linear(Q.Q4_K, w, None, x, None, n, k)
     P.assert_close(y, y32, y64, mag)
     t.release()
+
+
+# --------------------------------------------------------------------------- #
+# Qwen3-32B layer shapes (hidden 5120, FFN 25600, 64 query / 8 key-value heads x 128)
+# --------------------------------------------------------------------------- #
+
+QWEN3_32B_SHAPES = [(1024, 5120), (5120, 8192), (5120, 25600)]   # k/v, o, down: K = 20, 32, 100 super-blocks
+
+
+@pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q6_K])
+@pytest.mark.parametrize("n,k", QWEN3_32B_SHAPES)
+def test_qwen3_32b_shapes_prefill_and_decode(fmt, n, k):
+    """The large-prefill configuration's own shapes: Q6_K rows of K = 5120 / 25600 are only 8-byte
+    aligned (210-byte blocks), K = 25600 is 100 super-blocks. M = 4096 runs the tensor-core path
+    (bf16 operands: 1e-2), M = 1 the streaming kernels (f32 accumulation: 2e-3). The weights are
+    drawn on the device and dequantized by the oracle; at M = 4096 the oracle product is formed for
+    a seeded sample of 12 token rows (every output column of those rows is checked)."""
+    from nn_b200 import workload as W
+    b = api.gpu_backend()
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(3200 + n + k)
+    raw = (W.gen_q4_k_device if fmt == Q.Q4_K else W.gen_q6_k_device)(torch, gen, n, k)
+    w = api.DeviceWeight.from_device(b, fmt, raw, n, k)
+    deq = orc.dequantize(fmt, raw.cpu().numpy(), n * k).reshape(n, k)
+    assert np.array_equal(w.dequantize().cpu().numpy().view(np.uint32), deq.view(np.uint32))   # bit-exact decode
+    # prefill: 4096 tokens of bf16 activations
+    m = 4096
+    x = torch.randn(m, k, device=DEV, generator=gen).to(torch.bfloat16)
+    y = api.quantized_linear(x, w, None, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    b.device_status()
+    rows = np.sort(F.Stream(n + k).integers(12, 0, m - 1))
+    xs = x[torch.from_numpy(rows).to(DEV)].float().cpu().numpy()
+    y32 = orc.linear_f32(xs, deq, None, len(rows), n, k)
+    y64 = orc.linear_f64(xs, deq, None, len(rows), n, k)
+    mag = orc.linear_abs(xs, deq, len(rows), n, k)
+    got = y[torch.from_numpy(rows).to(DEV)].cpu().numpy()
+    assert np.all(np.isfinite(got))
+    assert P.max_rel_err(got, y32) <= P.TOL_BF16_MMA, P.max_rel_err(got, y32)
+    assert P.max_scaled_err(got, y64, mag) <= P.TOL_BF16_MMA
+    # decode: one token, bf16 and f32 activations, all rows
+    for x_bf16 in (True, False):
+        x1 = torch.randn(1, k, device=DEV, generator=gen)
+        if x_bf16:
+            x1 = x1.to(torch.bfloat16)
+        y1 = api.quantized_linear(x1, w, None, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        b.device_status()
+        xh = x1.float().cpu().numpy()
+        r32 = orc.linear_f32(xh, deq, None, 1, n, k)
+        r64 = orc.linear_f64(xh, deq, None, 1, n, k)
+        rmag = orc.linear_abs(xh, deq, 1, n, k)
+        P.assert_close(y1.cpu().numpy(), r32, r64, rmag)
+    w.release()

@@ -15,7 +15,20 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _make(layout, fmt, E, H, I, seed):
+def _gen(fmt, seed, n, k, fast):
+    """Raw blocks with the benchmark distributions; fast=True draws the MXFP4 payload (codes uniform
+    over all bytes, E8M0 exponent uniform in [-8, 0]) with numpy's PCG64 instead of the SplitMix64
+    counter stream, which takes a minute per full-size expert tensor."""
+    if not fast:
+        return F.gen_weight(fmt, seed, n, k)
+    assert fmt in (Q.MXFP4_GPTOSS, Q.MXFP4_SPLIT)
+    rng = np.random.default_rng(seed)
+    codes = rng.integers(0, 256, size=n * (k // 2), dtype=np.uint8)
+    exps = rng.integers(119, 128, size=n * (k // 32), dtype=np.uint8)
+    return codes, exps
+
+
+def _make(layout, fmt, E, H, I, seed, fast=False):
     s = F.Stream(seed)
     router_w = (s.normal(E * H) * 0.5).astype(np.float32).reshape(E, H)
     router_b = (s.normal(E) * 0.1).astype(np.float32)
@@ -23,13 +36,13 @@ def _make(layout, fmt, E, H, I, seed):
     b_d = (s.normal(E * H) * 0.1).astype(np.float32).reshape(E, H)
     if layout == moe.LAYOUT_KN_GPTOSS:
         # flat nn-gptoss tensors [E, H, 2I] and [E, I, H]: blocks of 32 along the last axis
-        gu, gus = F.gen_weight(Q.MXFP4_GPTOSS, seed + 1, E * H, 2 * I)
-        dn, dns = F.gen_weight(Q.MXFP4_GPTOSS, seed + 2, E * I, H)
+        gu, gus = _gen(Q.MXFP4_GPTOSS, seed + 1, E * H, 2 * I, fast)
+        dn, dns = _gen(Q.MXFP4_GPTOSS, seed + 2, E * I, H, fast)
         w_gu = orc.dequantize(Q.MXFP4_GPTOSS, gu, E * H * 2 * I, gus).reshape(E, H, 2 * I)
         w_d = orc.dequantize(Q.MXFP4_GPTOSS, dn, E * I * H, dns).reshape(E, I, H)
     else:
-        gu, gus = F.gen_weight(fmt, seed + 1, E * 2 * I, H)
-        dn, dns = F.gen_weight(fmt, seed + 2, E * H, I)
+        gu, gus = _gen(fmt, seed + 1, E * 2 * I, H, fast)
+        dn, dns = _gen(fmt, seed + 2, E * H, I, fast)
         w_gu = orc.dequantize(fmt, gu, E * 2 * I * H, gus).reshape(E, 2 * I, H).transpose(0, 2, 1).copy()
         w_d = orc.dequantize(fmt, dn, E * H * I, dns).reshape(E, H, I).transpose(0, 2, 1).copy()
     return router_w, router_b, gu, gus, b_gu, dn, dns, b_d, w_gu, w_d
@@ -136,3 +149,62 @@ def test_expert_parallel_shards_sum_to_full_block(layout, fmt):
     y_ref, _, _ = orc.moe_forward(x, rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
     assert np.max(np.abs(total.cpu().numpy() - y_ref)) / np.max(np.abs(y_ref)) <= 2e-3
     full.release()
+
+
+# --------------------------------------------------------------------------- #
+# gpt-oss-20b geometry: 32 experts, top-4, hidden = inter = 2880
+# --------------------------------------------------------------------------- #
+
+_GPTOSS = {}
+
+
+def _gptoss_block(layout, fmt):
+    """Weights of the full-size block are expensive to draw and to dequantize on the CPU: built
+    once per layout and shared by the decode-sized and the prefill-sized case."""
+    key = (layout, int(fmt))
+    if key not in _GPTOSS:
+        E, H, I, k = 32, 2880, 2880, 4
+        made = _make(layout, fmt, E, H, I, 4242, fast=True)
+        rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = made
+        blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, layout, fmt, gu, gus, bgu, dn, dns, bd)
+        _GPTOSS[key] = (blk, rw, rb, bgu, bd, w_gu, w_d)
+    return _GPTOSS[key]
+
+
+@pytest.mark.parametrize("layout,fmt", [(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS), (moe.LAYOUT_NK, Q.MXFP4_SPLIT)])
+@pytest.mark.parametrize("T", [64, 4096])
+def test_gptoss_20b_geometry(layout, fmt, T):
+    """The benchmark configuration itself (32 experts, top-4, 2880 x 2880 experts): every token of
+    the 64-token decode batch, and a seeded sample of 24 tokens of the 4096-token prefill batch
+    (a token's output depends on no other token, so the oracle runs on the sample alone).
+    64 tokens stay on the f32-accumulating kernels (2e-3); 4096 tokens give 512 routed rows per
+    expert, which the [N, K] layout runs on the tensor cores with bf16 operands (1e-2)."""
+    blk, rw, rb, bgu, bd, w_gu, w_d = _gptoss_block(layout, fmt)
+    H, k = 2880, 4
+    x = F.gen_activations(900 + T, T, H, bf16=True)
+    xt = torch.from_numpy(x).to(DEV)
+    y = blk(xt)
+    idx, wt = blk.route(xt)
+    torch.cuda.synchronize()
+    blk.backend.device_status()
+    sample = np.arange(T) if T <= 64 else np.sort(F.Stream(31).integers(24, 0, T - 1))
+    y_ref, idx_ref, wt_ref = orc.moe_forward(x[sample], rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
+    got = y.cpu().numpy()[sample]
+    assert np.array_equal(idx.cpu().numpy()[sample], idx_ref)
+    # router logits over 2880 terms reach +-100: a rounding difference of 1e-4 in a logit moves a
+    # small softmax weight by 1e-4 of itself, so the weights are compared to 2e-3 of themselves
+    assert np.allclose(wt.cpu().numpy()[sample], wt_ref, rtol=2e-3, atol=1e-7)
+    assert np.all(np.isfinite(got))
+    tol = 1e-2 if (T > 64 and layout == moe.LAYOUT_NK) else 2e-3
+    err = np.max(np.abs(got - y_ref)) / np.max(np.abs(y_ref))
+    assert err <= tol, err
+    # per-token bound as well: one scale per token instead of one for the whole batch
+    per_tok = np.max(np.abs(got - y_ref), axis=1) / np.max(np.abs(y_ref), axis=1)
+    assert np.all(per_tok <= 2 * tol), per_tok.max()
+
+
+def test_gptoss_20b_release():
+    """Frees the shared full-size blocks (kept last in this file)."""
+    for blk, *_ in _GPTOSS.values():
+        blk.release()
+    _GPTOSS.clear()
