@@ -27,6 +27,17 @@ METRIC = "quant_gemv_hbm_gbs"
 UNIT = "GB/s"
 WORKLOAD = "q4_k_projection_sweep_qwen3_8b_m1"
 
+# dram bytes (read + write) per algorithmic byte of the dominant kernel, from its ncu capture on the
+# two-layer case (27.18 MB moved for 27.17 MB of tiles, activations and outputs per launch; the
+# per-launch traffic does not depend on the layer count)
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 27.18 / 27.17
+
+
+def workload_config(m: int, layers: int) -> dict:
+    """The workload both arms report: identical keys and values for the same flags."""
+    return {"workload": WORKLOAD, "m": m, "layers": layers, "format": "Q4_K", "activations": "bf16",
+            "outputs": "bf16", "accumulate": "f32"}
+
 
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -146,12 +157,13 @@ def run_reference(args, rank):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     value = algo / dt / 1e9
-    sample = "one layer (7 projections, 108.5 MB of Q4_K) per step: dequantize whole weight + nn-cpu row dot"
+    sample = ("one layer of the 36 (7 projections, 108.5 MB of Q4_K) per step: dequantize whole weight + nn-cpu row dot, "
+              "all host threads")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "m": 1, "layers_per_step": 1, "format": "Q4_K"},
+        "config": workload_config(args.m, args.layers),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -180,20 +192,28 @@ def run_nnq(args, rank, world, local_rank):
     lib, ctx = backend._lib, backend._ctx
     m = args.m
     # row-parallel partial outputs are summed by the library's one-shot all-reduce over peer memory
-    peer = comm.PeerComm(backend, rank, world, max_bytes=max(m, 2) * W.HIDDEN * 4) if world > 1 else None
+    # slots: 8 bytes per output row of the fused exchange + the record of the distributed argmax
+    peer = comm.PeerComm(backend, rank, world, max_bytes=max(m, 2) * W.HIDDEN * 4 + 256) if world > 1 else None
     gen = torch.Generator(device=dev)
     gen.manual_seed(0x5EED)  # same weights on every rank, each keeps its shard
 
     # ---- weights: `layers` distinct layers, tensor-parallel shards when world > 1 ----
-    layers = []
+    # With N > 1 every rank also keeps the unsharded weights the parity check multiplies: layer 0's
+    # row-parallel projections everywhere, and on rank 0 all layers (the single-GPU decoder the
+    # tensor-parallel tokens are compared with).
+    layers, full_layers = [], []
+    keep_all_full = world > 1 and rank == 0 and m == 1 and args.layers == W.LAYERS and not args.no_others
     for li in range(args.layers):
-        lw = {}
+        lw, fw = {}, {}
         for name, n, k in W.PROJECTIONS:
             raw = W.gen_q4_k_device(torch, gen, n, k)
             shard = (W.TP_AXIS[name], rank, world) if world > 1 else None
             lw[name] = api.DeviceWeight.from_device(backend, QuantFormat.Q4_K, raw, n, k, shard=shard)
+            if world > 1 and (keep_all_full or (li == 0 and W.TP_AXIS[name] == 1)):
+                fw[name] = api.DeviceWeight.from_device(backend, QuantFormat.Q4_K, raw, n, k)
             del raw
         layers.append(lw)
+        full_layers.append(fw)
     torch.cuda.synchronize()
 
     # ---- activations / outputs (bf16), one set per layer ----
@@ -243,12 +263,16 @@ def run_nnq(args, rank, world, local_rank):
 
     stream = torch.cuda.Stream(device=dev)
     graph = None
+    parity = None
     with torch.cuda.stream(stream):
         sp = VP(stream.cuda_stream)
         for _ in range(2):
             step(sp)
         stream.synchronize()
         backend.device_status(stream)
+        parity = None
+        if world > 1:
+            parity = check_tp_products(torch, dist, backend, full_layers[0], xs[0], ys[0], m, world, stream)
         if not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
@@ -337,10 +361,8 @@ def run_nnq(args, rank, world, local_rank):
         achieved = bytes_per_launch / per_launch_s / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "peak_source": f"of {peak_kind}", "frac_of_nominal_8000": achieved / 8000.0,
-                    # dram__bytes_read+write per launch from the ncu capture summarised in profiles/ (2-layer
-                    # case; per-launch traffic does not depend on the layer count): equal to the algorithmic
-                    # bytes within 0.1 %
-                    "traffic": bytes_per_launch * (27.18 / 27.17),
+                    "traffic": bytes_per_launch * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                    "traffic_source": "ncu capture of the two-layer case, scaled by the bytes per launch",
                     "kernel": "skinny_q4k_m1_kernel", "launches_per_step": len(dom_calls),
                     "share_of_step_bytes": dom_bytes / algo_step, "share_of_step_time": dom_ms / ms_per_step,
                     "bytes_per_launch": bytes_per_launch, "us_per_launch": per_launch_s * 1e6,
@@ -362,8 +384,12 @@ def run_nnq(args, rank, world, local_rank):
     elif world > 1 and m == 1 and not args.no_others:
         # tensor-parallel decode: the same shards, o / down exchanged inside the product kernel
         peak_hbm, _ = _peaks()
-        dec = decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, tp=(rank, world), peer=peer)
+        dec = decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, tp=(rank, world), peer=peer,
+                                  full_layers=full_layers if keep_all_full else None, dist=dist)
         if dec is not None:
+            if parity is not None and dec.get("parity") is not None:
+                parity["decode"] = dec.pop("parity")
+                parity["ok"] = bool(parity["ok"] and parity["decode"]["ok"])
             t = torch.tensor([dec["ms_per_token"]], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dec["ms_per_token"] = float(t.item())
@@ -422,19 +448,25 @@ def run_nnq(args, rank, world, local_rank):
                "seconds_per_layer": s1,
                "all_cores": {"value": vN, "cores": cores, "seconds_per_layer": sN}}
 
+    if parity is not None and not parity["ok"]:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "error": "tensor-parallel parity check failed", "parity": parity}), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        raise SystemExit(3)
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "m": m, "layers": args.layers, "format": "Q4_K",
-                       "activations": "bf16", "outputs": "bf16", "accumulate": "f32",
-                       "parallelism": f"tp{world}" if world > 1 else "single",
-                       "weight_bytes_per_step": per_layer.weights * args.layers * world // world,
-                       "l2_policy": "inputs larger than L2 (every step streams all layers' distinct weights)",
-                       "cuda_graph": graph is not None,
-                       "tokens_per_s_equiv": 1e3 / ms_per_step * (36 / args.layers)},
+            "config": workload_config(m, args.layers),
+            "run": {"parallelism": f"tp{world}" if world > 1 else "single",
+                    "weight_bytes_per_step": per_layer.weights * args.layers,
+                    "l2_policy": "inputs larger than L2 (every step streams all layers' distinct weights)",
+                    "cuda_graph": graph is not None,
+                    "tokens_per_s_equiv": 1e3 / ms_per_step * (36 / args.layers)},
+            "parity": parity,
             "roofline": roofline, "clocks": clocks.summary(), "gpu_launches": int(launched),
             "e2e": e2e, "cpu_baseline": cpu, "other_configs": others,
         }
@@ -442,6 +474,200 @@ def run_nnq(args, rank, world, local_rank):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def sweep_variants(torch, backend, layers, gen, dev, peak_hbm):
+    import ctypes
+
+    from nn_b200 import api, plan
+    from nn_b200 import workload as W
+    lib, ctx = backend._lib, backend._ctx
+    VP = ctypes.c_void_p
+    algo = W.layer_bytes(1).algorithmic * len(layers)
+    proj = {p_[0]: p_ for p_ in W.PROJECTIONS}
+    groups = []
+    for lw in layers:
+        for group in W.GROUPS:
+            x = torch.randn(proj[group[0]][2], device=dev, generator=gen).to(torch.bfloat16)
+            ys = [torch.empty(proj[n_][1], dtype=torch.bfloat16, device=dev) for n_ in group]
+            groups.append(([lw[n_] for n_ in group], x, ys))
+    out = {}
+
+    def time_graph(g, reps=10):
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        return {"ms_per_step": ms, "gbs": algo / ms / 1e6, "frac": algo / ms / 1e6 / peak_hbm}
+
+    # (a) four streams
+    calls = []
+    for ws, x, ys in groups:
+        cnt = len(ws)
+        calls.append((cnt, (VP * cnt)(*[w.handle().value for w in ws]), (VP * cnt)(*[x.data_ptr()] * cnt),
+                      (VP * cnt)(*[y.data_ptr() for y in ys])))
+    main = torch.cuda.Stream(device=dev)
+    side = [torch.cuda.Stream(device=dev) for _ in range(3)]
+    with torch.cuda.stream(main):
+        for cnt, wh, xp, yp in calls[:8]:
+            backend.check(lib.nnq_linear_batch(ctx, cnt, wh, xp, api.BF16, 1, None, yp, api.BF16, VP(main.cuda_stream)))
+        main.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=main):
+            cur = torch.cuda.current_stream()
+            fork = torch.cuda.Event()
+            fork.record(cur)
+            lanes = [cur] + side
+            for s_ in side:
+                s_.wait_event(fork)
+            for i, (cnt, wh, xp, yp) in enumerate(calls):
+                backend.check(lib.nnq_linear_batch(ctx, cnt, wh, xp, api.BF16, 1, None, yp, api.BF16,
+                                                   VP(lanes[i % 4].cuda_stream)))
+            for s_ in side:
+                join = torch.cuda.Event()
+                join.record(s_)
+                cur.wait_event(join)
+        row = time_graph(g)
+        row["how"] = "the 144 launches of the headline step dealt over 4 streams of one graph (independent products)"
+        out["separate_launches_4_streams"] = row
+    backend.device_status()
+
+    # (b) the compiled plan
+    for name, analyze in (("plan_kernel_ordered", False), ("plan_kernel_dependency_analysed", True)):
+        pl = plan.ProductPlan(backend, torch.bfloat16, torch.bfloat16, analyze_deps=analyze)
+        for ws, x, ys in groups:
+            pl.add(ws, x, ys)
+        pl.finalize()
+        with torch.cuda.stream(main):
+            pl.run(main)
+            main.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=main):
+                pl.run(torch.cuda.current_stream())
+            row = time_graph(g)
+        row["launches_per_step"] = 1
+        row["info"] = pl.info()
+        out[name] = row
+        backend.device_status()
+        pl.release()
+    return out
+
+
+def prefill_32b(torch, backend, gen, dev, peak_tf, timed):
+    """BASELINE configuration 5 on one GPU: the seven projections of a Qwen3-32B layer (hidden 5120,
+    64 query / 8 key-value heads x 128, FFN 25600) at 4096 tokens of bf16 activations, Q4_K and Q6_K
+    weights, on the tensor-core path; per shape the time, TFLOP/s and the fraction of the measured
+    bf16 peak, and the whole layer."""
+    from nn_b200 import api
+    from nn_b200 import workload as W
+    from nn_b200.formats import QuantFormat
+    lib, ctx = backend._lib, backend._ctx
+    m = 4096
+    shapes = (("q_proj", 8192, 5120), ("k_proj", 1024, 5120), ("v_proj", 1024, 5120), ("o_proj", 5120, 8192),
+              ("gate_proj", 25600, 5120), ("up_proj", 25600, 5120), ("down_proj", 5120, 25600))
+    out = {}
+    for fmt, genfn, tag in ((QuantFormat.Q4_K, W.gen_q4_k_device, "q4_k"), (QuantFormat.Q6_K, W.gen_q6_k_device, "q6_k")):
+        rows, total_s, total_f = {}, 0.0, 0.0
+        for name, n, k in shapes:
+            raw = genfn(torch, gen, n, k)
+            w = api.DeviceWeight.from_device(backend, fmt, raw, n, k)
+            del raw
+            x = torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16)
+            y = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+
+            def one():
+                st = lib.nnq_linear(ctx, w.handle(), x.data_ptr(), api.BF16, m, None, y.data_ptr(), api.BF16, None)
+                if st != 0:
+                    backend.check(st)
+
+            sec = timed(one, 3)
+            flops = 2.0 * m * n * k
+            rows[name] = {"n": n, "k": k, "ms": sec * 1e3, "tflops": flops / sec / 1e12, "frac": flops / sec / 1e12 / peak_tf}
+            total_s += sec
+            total_f += flops
+            w.release()
+            del x, y
+        rows["layer"] = {"ms": total_s * 1e3, "tflops": total_f / total_s / 1e12, "frac": total_f / total_s / 1e12 / peak_tf,
+                         "tflop": total_f / 1e12}
+        out[tag] = rows
+    out["bound"] = "tensor"
+    out["tokens"] = m
+    backend.device_status()
+    return out
+
+
+def moe_block(torch, backend, gen, dev, peak_hbm, peak_tf, timed):
+    """BASELINE configuration 4 on one GPU: one gpt-oss-20b MoE block (32 experts, top-4, hidden =
+    inter = 2880, MXFP4 experts in the [N, K/2] + [N, K/32] layout) at 64 tokens (one decode token of 64
+    sequences: bound by the expert weights, 423 MB) and 4096 tokens (prefill: bound by the tensor
+    cores, 2 * 16384 routed rows * 3 * 2880 * 2880 flop)."""
+    import numpy as np
+
+    from nn_b200 import moe
+    from nn_b200.formats import QuantFormat
+    E, H, I, k = 32, 2880, 2880, 4
+    rng = np.random.default_rng(20)
+    rw = (rng.standard_normal((E, H)) * 0.02).astype(np.float32)
+    rb = np.zeros(E, np.float32)
+
+    def payload(n, kk):
+        return (rng.integers(0, 256, size=n * (kk // 2), dtype=np.uint8), rng.integers(119, 128, size=n * (kk // 32), dtype=np.uint8))
+
+    gu, gus = payload(E * 2 * I, H)
+    dn, dns = payload(E * H, I)
+    blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, moe.LAYOUT_NK, QuantFormat.MXFP4_SPLIT, gu, gus, np.zeros((E, 2 * I), np.float32),
+                       dn, dns, np.zeros((E, H), np.float32), backend=backend)
+    weight_bytes = gu.size + gus.size + dn.size + dns.size
+    out = {"experts": E, "top_k": k, "hidden": H, "inter": I, "format": "MXFP4 [N,K/2]+[N,K/32]", "weight_bytes": int(weight_bytes)}
+    for tokens in (64, 4096):
+        x = (torch.randn(tokens, H, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+        sec = timed(lambda: blk(x), 5 if tokens == 64 else 3)
+        flops = 2.0 * tokens * k * 3 * H * I
+        row = {"us": sec * 1e6, "gbs_over_expert_weights": weight_bytes / sec / 1e9, "tflops": flops / sec / 1e12}
+        if tokens == 64:
+            row["bound"], row["frac"] = "hbm", weight_bytes / sec / 1e9 / peak_hbm
+        else:
+            row["bound"], row["frac"] = "tensor", flops / sec / 1e12 / peak_tf
+        out[f"tokens_{tokens}"] = row
+    backend.device_status()
+    blk.release()
+    return out
+
+
+def check_tp_products(torch, dist, backend, full0, xs0, ys0, m, world, stream):
+    """Before anything is timed at N > 1: the fused row-parallel products of layer 0 (o_proj,
+    down_proj: product + exchange in one kernel), as the warm-up steps left them in the bench's own
+    output buffers, against the library's single-GPU product of the unsharded weight with the
+    concatenated activations. Every rank checks its own copy (the exchange promises the same bits
+    everywhere); the verdict is the minimum over the ranks. bf16 outputs: 2e-3 + one bf16 rounding."""
+    from nn_b200 import api
+    tol = 2e-3 + 2.0 ** -8
+    out = {"ok": True, "tolerance": tol, "products": {}}
+    for name, wfull in full0.items():
+        x_full = torch.cat([xs0[name]] * world, dim=1).contiguous()   # every rank drew the same shard values
+        want = api.quantized_linear(x_full, wfull, None, out_dtype=torch.float32)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        got = ys0[name].float()
+        err = float((got - want).abs().max() / want.abs().max())
+        t = torch.tensor([err], device=got.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        # identical bits on every rank: compare a checksum of the raw outputs
+        cs = ys0[name].view(torch.int16).to(torch.int64).sum().reshape(1)
+        lo, hi = cs.clone(), cs.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = bool(lo.item() == hi.item())
+        out["products"][name] = {"max_rel_err_over_ranks": float(t.item()), "same_bits_on_all_ranks": same}
+        out["ok"] = bool(out["ok"] and float(t.item()) <= tol and same)
+    backend.device_status(stream)
+    return out
 
 
 def other_configs(torch, backend, layers, gen, dev):
@@ -525,6 +751,29 @@ def other_configs(torch, backend, layers, gen, dev):
         return {"us": sec * 1e6, "gbs": algo / sec / 1e9, "bound": "hbm", "frac": algo / sec / 1e9 / peak_hbm,
                 "weights_rotated": copies}
 
+    # ---- the M = 1 sweep issued other ways (same weights, same products) ----
+    # (a) the products are independent (distinct input and output buffers), so they may run
+    #     concurrently: the same 144 launches dealt over four streams of one captured graph;
+    # (b) the compiled plan: all 252 products in one persistent kernel, every group waiting for the
+    #     one before it (the chain a decoder imposes), and with the waits the buffer analysis allows
+    #     it to drop (none are needed here).
+    try:
+        out["q4_k_projection_sweep_m1_variants"] = sweep_variants(torch, backend, layers, gen, dev, peak_hbm)
+    except Exception as e:   # a side measurement must not take the headline down
+        out["q4_k_projection_sweep_m1_variants"] = {"error": str(e)[:200]}
+
+    # ---- large prefill, Qwen3-32B layer shapes, 4096 tokens (tensor-core path) ----
+    try:
+        out["qwen3_32b_prefill_m4096"] = prefill_32b(torch, backend, gen, dev, peak_tf, timed)
+    except Exception as e:
+        out["qwen3_32b_prefill_m4096"] = {"error": str(e)[:200]}
+
+    # ---- gpt-oss-20b MoE block, MXFP4 experts: 64-token decode batch and 4096-token prefill ----
+    try:
+        out["gptoss_20b_moe_block"] = moe_block(torch, backend, gen, dev, peak_hbm, peak_tf, timed)
+    except Exception as e:
+        out["gptoss_20b_moe_block"] = {"error": str(e)[:200]}
+
     out["qwen3_8b_decode_ctx2048"] = decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm)
     out["q8_0_gemv_4096x4096_f32_m1"] = gemv(QuantFormat.Q8_0, W.gen_q8_0_device, 4096, 4096, 10, True, 40)
     out["q6_k_gemv_151936x4096_bf16_m1"] = gemv(QuantFormat.Q6_K, W.gen_q6_k_device, 151936, 4096, 1, False, 10)
@@ -555,34 +804,95 @@ def other_configs(torch, backend, layers, gen, dev):
     return out
 
 
-def decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, prompt=2048, new_tokens=256, tp=(0, 1), peer=None):
+def decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, prompt=2048, new_tokens=256, tp=(0, 1), peer=None,
+                        full_layers=None, dist=None):
     """Batch-1 greedy decode of a Qwen3-8B-shaped model (the bench's 36 Q4_K layers, a Q6_K
     vocabulary projection, bf16 embedding, unit norms): 256 tokens from position 2048. The key /
     value caches of the 2048 earlier positions are filled with seeded random values, which stands
-    in for the prompt pass: the cost of a decode step depends on the context length only."""
+    in for the prompt pass: the cost of a decode step depends on the context length only.
+    With tensor parallelism the vocabulary projection is split by rows over the ranks and the greedy
+    token is agreed on through the communicator; before the timed run, 8 tokens of the
+    tensor-parallel decoder are compared with the single-GPU decoder over the unsharded weights
+    (rank 0 holds them: `full_layers`)."""
     from nn_b200 import api, decoder
     from nn_b200 import workload as W
     from nn_b200.formats import QuantFormat
     if len(layers) != W.LAYERS:
         return None
-    cfg = decoder.DecoderConfig(max_seq=prompt + new_tokens + 8, act_dtype=api.BF16, tp_rank=tp[0], tp_world=tp[1])
+    rank, world = tp
+    cfg = decoder.DecoderConfig(max_seq=prompt + new_tokens + 8, act_dtype=api.BF16, tp_rank=rank, tp_world=world)
     dec = decoder.Decoder(backend, cfg)
     if peer is not None:
         dec.set_comm(peer)
     ones_h = torch.ones(cfg.hidden, device=dev)
     ones_d = torch.ones(cfg.head_dim, device=dev)
-    for li, lw in enumerate(layers):
-        dec.set_layer(li, lw["q_proj"], lw["k_proj"], lw["v_proj"], lw["o_proj"], lw["gate_proj"], lw["up_proj"],
-                      lw["down_proj"], ones_h, ones_h, ones_d, ones_d)
+
+    def set_layers(d, lws):
+        for li, lw in enumerate(lws):
+            d.set_layer(li, lw["q_proj"], lw["k_proj"], lw["v_proj"], lw["o_proj"], lw["gate_proj"], lw["up_proj"],
+                        lw["down_proj"], ones_h, ones_h, ones_d, ones_d)
+
+    set_layers(dec, layers)
     raw = W.gen_q6_k_device(torch, gen, cfg.vocab, cfg.hidden)
-    head = api.DeviceWeight.from_device(backend, QuantFormat.Q6_K, raw, cfg.vocab, cfg.hidden)
+    vocab_parallel = world > 1 and cfg.vocab % world == 0
+    head = api.DeviceWeight.from_device(backend, QuantFormat.Q6_K, raw, cfg.vocab, cfg.hidden,
+                                        shard=(0, rank, world) if vocab_parallel else None)
+    head_full = None
+    if full_layers is not None:
+        head_full = api.DeviceWeight.from_device(backend, QuantFormat.Q6_K, raw, cfg.vocab, cfg.hidden)
     del raw
     embed = torch.randn(cfg.vocab, cfg.hidden, device=dev, generator=gen).to(torch.bfloat16)
     dec.set_head(embed, ones_h, head)
-    kc, vc, _, toks = dec.buffers()
+    kc, vc, logits, toks = dec.buffers()
     kc[:, :, :prompt].normal_(generator=gen)
     vc[:, :, :prompt].normal_(generator=gen)
     stream = torch.cuda.Stream(device=dev)
+
+    # ---- parity of the tensor-parallel decoder (N > 1), before anything is timed ----
+    parity = None
+    if world > 1 and dist is not None:
+        check_tokens = 8
+        with torch.cuda.stream(stream):
+            dec.reset(1, prompt, stream)
+            for _ in range(check_tokens):
+                dec.step(stream)
+            stream.synchronize()
+        backend.device_status(stream)
+        mine = toks[prompt:prompt + check_tokens].cpu().tolist()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        same = all(g_ == gathered[0] for g_ in gathered)
+        verdict = {"tokens": check_tokens, "same_tokens_on_all_ranks": bool(same)}
+        if full_layers is not None:
+            cfg1 = decoder.DecoderConfig(max_seq=cfg.max_seq, act_dtype=api.BF16)
+            dec1 = decoder.Decoder(backend, cfg1)
+            set_layers(dec1, full_layers)
+            dec1.set_head(embed, ones_h, head_full)
+            k1, v1, logits1, toks1 = dec1.buffers()
+            # every rank filled its local heads with the same values: the full cache repeats them
+            k1[:, :, :prompt] = kc[:, :, :prompt].repeat(1, world, 1, 1)
+            v1[:, :, :prompt] = vc[:, :, :prompt].repeat(1, world, 1, 1)
+            with torch.cuda.stream(stream):
+                dec1.reset(1, prompt, stream)
+                for _ in range(check_tokens):
+                    dec1.step(stream)
+                stream.synchronize()
+            backend.device_status(stream)
+            want = toks1[prompt:prompt + check_tokens].cpu().tolist()
+            rows = slice(rank * cfg.vocab // world, (rank + 1) * cfg.vocab // world) if vocab_parallel else slice(0, cfg.vocab)
+            err = float((logits[rows] - logits1[rows]).abs().max() / logits1.abs().max())
+            verdict.update({"tokens_equal_single_gpu": bool(mine == want), "last_logits_max_rel_err": err,
+                            "logits_tolerance": 2e-3})
+            dec1.release()
+            head_full.release()
+        flag = [verdict if rank == 0 else None]
+        dist.broadcast_object_list(flag, src=0)
+        verdict = flag[0]
+        verdict["same_tokens_on_all_ranks"] = bool(same)
+        verdict["ok"] = bool(same and verdict.get("tokens_equal_single_gpu", True)
+                             and verdict.get("last_logits_max_rel_err", 0.0) <= 2e-3)
+        parity = verdict
+
     with torch.cuda.stream(stream):
         dec.reset(1, prompt, stream)
         dec.step(stream)
@@ -603,14 +913,17 @@ def decode_tokens_per_s(torch, backend, layers, gen, dev, peak_hbm, prompt=2048,
     sec = e0.elapsed_time(e1) * 1e-3 / new_tokens
     _, pos, steps = dec.state()
     ctx_mid = prompt + new_tokens // 2
-    # per GPU: its shard of the layers and of the caches, and the whole (replicated) vocabulary projection
-    weights = W.layer_bytes(1).weights * W.LAYERS // tp[1] + cfg.vocab * (cfg.hidden // 256) * 210
-    kv = 2 * cfg.n_layers * (cfg.n_kv_heads // tp[1]) * cfg.head_dim * 4 * ctx_mid
-    out = {"tokens_per_s": 1.0 / sec, "tp": tp[1], "ms_per_token": sec * 1e3, "new_tokens": new_tokens, "prompt_positions": prompt,
+    # per GPU: its shard of the layers, of the caches and of the vocabulary projection
+    head_bytes = cfg.vocab * (cfg.hidden // 256) * 210 // (world if vocab_parallel else 1)
+    weights = W.layer_bytes(1).weights * W.LAYERS // world + head_bytes
+    kv = 2 * cfg.n_layers * (cfg.n_kv_heads // world) * cfg.head_dim * 4 * ctx_mid
+    out = {"tokens_per_s": 1.0 / sec, "tp": world, "ms_per_token": sec * 1e3, "new_tokens": new_tokens, "prompt_positions": prompt,
            "kernels_per_token": int(per_token), "end_position": pos, "steps": steps,
            "hbm_bytes_per_token_per_gpu": weights + kv, "gbs_per_gpu": (weights + kv) / sec / 1e9, "bound": "hbm",
            "frac": (weights + kv) / sec / 1e9 / peak_hbm, "kv_cache": "f32", "product_inputs": "bf16",
-           "prompt": "key/value caches of the first 2048 positions filled with seeded random values"}
+           "vocabulary_projection": "split by rows over the ranks, distributed argmax" if vocab_parallel else "whole on this GPU",
+           "prompt": "key/value caches of the first 2048 positions filled with seeded random values",
+           "parity": parity}
     dec.release()
     head.release()
     return out

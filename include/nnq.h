@@ -379,6 +379,30 @@ NNQ_API nnq_status nnq_moe_forward(nnq_ctx *ctx, const nnq_moe *m, const void *x
 NNQ_API nnq_status nnq_moe_route(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt,
                                  int64_t tokens, int32_t *idx_dev, float *weights_dev, void *stream);
 
+/* Expert parallelism with token dispatch (tokens sharded over the ranks, every rank holding
+ * n_experts / world experts; no counterpart in the reference, which runs on one device). The
+ * library provides the device-side pieces, the exchange of the rows between the ranks is the
+ * caller's all-to-all (NCCL):
+ *   nnq_moe_route          expert indices / weights of the local tokens (router replicated);
+ *   nnq_moe_gather_rows    out[i, :] = x[index[i], :] -- the token permute: rows sorted by
+ *                          destination expert before they are sent;
+ *   nnq_moe_forward_routed the expert MLPs over rows whose routing the caller supplies: idx_dev /
+ *                          weights_dev are [rows, slots] (global expert indices; a row whose expert
+ *                          is not held by this block contributes nothing): on the owner of the
+ *                          experts, slots = 1 and weight 1 give each received row its expert's output
+ *                          (quantized_model.rs:152-189, gather :183 and expert_forward);
+ *   nnq_moe_combine_rows   y[t, :] = sum over the token's slots, in expert-index order, of
+ *                          weights[t, s] * rows[pos[t, s], :] -- the weighted scatter-add of
+ *                          quantized_model.rs:186-188 over the rows that came back (pos < 0: skipped). */
+NNQ_API nnq_status nnq_moe_forward_routed(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt, int64_t rows,
+                                          int slots, const int32_t *idx_dev, const float *weights_dev, float *y_dev,
+                                          void *stream);
+NNQ_API nnq_status nnq_moe_gather_rows(nnq_ctx *ctx, const void *x_dev, nnq_dtype dt, const int32_t *index_dev, int64_t count,
+                                       int64_t width, void *out_dev, void *stream);
+NNQ_API nnq_status nnq_moe_combine_rows(nnq_ctx *ctx, const float *rows_dev, const int32_t *idx_dev, const float *weights_dev,
+                                        const int32_t *pos_dev, int64_t tokens, int hidden, int top_k, float *y_dev,
+                                        void *stream);
+
 /* Same computation as nnq_moe_forward for callers that cannot allocate device memory: an
  * inference server that has handed the whole device to its own memory pool (a library-side
  * cudaMalloc would fail there), or a latency-critical loop that must not take the device-wide
@@ -388,9 +412,10 @@ NNQ_API nnq_status nnq_moe_route(nnq_ctx *ctx, const nnq_moe *m, const void *x_d
  * context's growable scratch buffer, and the call performs no allocation of any kind.
  * Limits and rules:
  *   - tokens * top_k * ((2*inter + hidden) * s + inter) * 4 bytes (plus small tables) must fit the
- *     8 MiB area, with s = 4 for the [E,K,N] layout (partial sums per K slice) and s = 1 otherwise:
- *     55 routed rows (13 tokens at top-4) at gpt-oss-20b's hidden = inter = 2880 in the [E,K,N]
- *     layout; larger calls are rejected with NNQ_ERR_UNSUPPORTED and a message naming both sizes;
+ *     8 MiB area, with s = 1 whenever the expert weights have a tiled layout (both layouts at
+ *     gpt-oss-20b's hidden = inter = 2880: 182 routed rows, 45 tokens at top-4) and s = 4 only for
+ *     an [E,K,N] block whose shape has none (partial sums per K slice); larger calls are rejected
+ *     with NNQ_ERR_UNSUPPORTED and a message naming both sizes;
  *   - the first call on a device looks up the area's address (cudaGetSymbolAddress); make that
  *     first call before any stream capture;
  *   - all calls on a device share the area: two calls whose kernels overlap on the GPU (different

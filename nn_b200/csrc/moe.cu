@@ -427,16 +427,20 @@ static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 // Prefill-sized calls on [N, K] expert weights go through the grouped tcgen05 product: from 64 routed
 // rows per local expert on average (below that the weights are streamed once per 16 rows by the
 // grouped token-column kernel, which is HBM-bound and wins).
-static bool moe_tensor_mode(const nnq_moe *m, int64_t T) {
+static bool moe_tensor_mode(const nnq_moe *m, int64_t T, int k, bool routed) {
     static const char *env = diag_env("NNQ_MOE_TENSOR");   // tuning aid: 0 keeps the token-column kernel
     if (env && atoi(env) == 0) return false;
-    return m->layout == NNQ_MOE_NK && m->fmt < NNQ_Q5_0 && m->hidden % 64 == 0 && m->inter % 64 == 0 && T * m->top_k >= 64 * (int64_t)m->n_experts;   // per expert of the whole block: shards of one block agree
+    return m->layout == NNQ_MOE_NK && m->fmt < NNQ_Q5_0 && m->hidden % 64 == 0 && m->inter % 64 == 0 &&
+           // 64 routed rows per expert on average: with the block's own router the T tokens spread over
+           // all experts (the shards of one block agree), rows routed by the caller all go to local experts
+           T * k >= 64 * (int64_t)(routed ? m->e_local : m->n_experts);
 }
 
-// Carves the scratch buffer; with base == NULL only the size is computed.
-static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
+// Carves the scratch buffer for T rows with k expert slots each; with base == NULL only the size
+// is computed.
+static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m, int k, bool routed = false) {
     MoeScratch s;
-    const int64_t R = T * m->top_k;
+    const int64_t R = T * k;
     size_t off = 0;
     auto take = [&](size_t bytes) { uint8_t *p = base ? base + off : nullptr; off += align256(bytes); return p; };
     s.idx = (int *)take(R * 4);
@@ -449,7 +453,7 @@ static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
     s.gu = (float *)take((size_t)R * 2 * m->inter * 4 * slices);
     s.h = (float *)take((size_t)R * m->inter * 4);
     s.o = (float *)take((size_t)R * m->hidden * 4 * slices);
-    const bool tensor = moe_tensor_mode(m, T);
+    const bool tensor = moe_tensor_mode(m, T, k, routed);
     s.xg = tensor ? (__nv_bfloat16 *)take((size_t)R * m->hidden * 2) : nullptr;
     s.hb = tensor ? (__nv_bfloat16 *)take((size_t)R * m->inter * 2) : nullptr;
     s.slices = slices;
@@ -459,8 +463,8 @@ static MoeScratch carve(uint8_t *base, int64_t T, const nnq_moe *m) {
     return s;
 }
 
-static nnq_status ensure_scratch(nnq_ctx *ctx, const nnq_moe *m, int64_t T, MoeScratch *out) {
-    MoeScratch need = carve(nullptr, T, m);
+static nnq_status ensure_scratch(nnq_ctx *ctx, const nnq_moe *m, int64_t T, int k, bool routed, MoeScratch *out) {
+    MoeScratch need = carve(nullptr, T, m, k, routed);
     if (need.bytes > ctx->moe_bytes) {
         cudaFree(ctx->d_moe);
         ctx->d_moe = nullptr;
@@ -469,7 +473,7 @@ static nnq_status ensure_scratch(nnq_ctx *ctx, const nnq_moe *m, int64_t T, MoeS
         if (s != NNQ_OK) return s;
         ctx->moe_bytes = need.bytes;
     }
-    *out = carve(ctx->d_moe, T, m);
+    *out = carve(ctx->d_moe, T, m, k, routed);
     return NNQ_OK;
 }
 
@@ -481,7 +485,7 @@ template <>
 struct DtypeOf<__nv_bfloat16> { static constexpr int value = NNQ_BF16; };
 
 template <typename XT>
-static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT *x, const int *rowtok,
+static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT *x, const int *rowtok, int top_k,
                            const MoeScratch &s, float *out, int64_t rows, cudaStream_t st) {
     const int K = first ? m->hidden : m->inter;
     const int N = first ? 2 * m->inter : m->hidden;
@@ -499,7 +503,7 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
     }
     if (m->d_gu_tiled) {
         GroupedArgs a = {first ? m->d_gu_tiled : m->d_dn_tiled, first ? m->gu_tile_stride : m->dn_tile_stride, b, x,
-                         DtypeOf<XT>::value, rowtok, s.offset, out, E, m->top_k, N, K, m->fmt, rows,
+                         DtypeOf<XT>::value, rowtok, s.offset, out, E, top_k, N, K, m->fmt, rows,
                          m->layout == NNQ_MOE_KN_GPTOSS ? 1 : 0};
         launch_grouped(ctx, a, st);
         return;
@@ -507,14 +511,14 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
     ctx->launches++;   // one of the row kernels below
     if (m->layout == NNQ_MOE_KN_GPTOSS) {
         dim3 grid((N + 1023) / 1024, E, kMoeKnSplit);
-        moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, m->top_k, s.offset, out,
+        moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, top_k, s.offset, out,
                                                         first ? s.gu_stride : s.o_stride, K, N);
         return;
     }
     Geometry g = geometry(m->fmt);
     size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
     dim3 grid((N + 3) / 4, E);
-#define NNQ_NK(F) case F: moe_nk_kernel<F, XT><<<grid, 128, 0, st>>>(d, sc, eb, es, b, x, rowtok, m->top_k, s.offset, out, K, N); break
+#define NNQ_NK(F) case F: moe_nk_kernel<F, XT><<<grid, 128, 0, st>>>(d, sc, eb, es, b, x, rowtok, top_k, s.offset, out, K, N); break
     switch (m->fmt) {
         NNQ_NK(NNQ_Q4_0); NNQ_NK(NNQ_Q4_1); NNQ_NK(NNQ_Q8_0); NNQ_NK(NNQ_Q4_K); NNQ_NK(NNQ_Q4_K_GGML);
         NNQ_NK(NNQ_Q6_K); NNQ_NK(NNQ_MXFP4_CORE); NNQ_NK(NNQ_MXFP4_SPLIT); NNQ_NK(NNQ_MXFP4_GPTOSS);
@@ -538,42 +542,6 @@ static cudaError_t launch_router(const nnq_moe *m, const XT *x, int64_t T, int *
     }
     moe_router_kernel<XT><<<(int)T, 256, smem, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, m->n_experts, m->top_k, idx, wt);
     return cudaGetLastError();
-}
-
-template <typename XT>
-static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int64_t T, float *y, int *idx_out,
-                                float *wt_out, bool route_only, cudaStream_t st) {
-    MoeScratch s;
-    nnq_status rc = ensure_scratch(ctx, m, T, &s);
-    if (rc != NNQ_OK) return rc;
-    const int E = m->n_experts, k = m->top_k;
-    const int total = (int)(T * k);
-    launch_router<XT>(m, x, T, s.idx, s.wt, st);
-    ctx->launches++;
-    if (idx_out) cudaMemcpyAsync(idx_out, s.idx, (size_t)total * 4, cudaMemcpyDeviceToDevice, st);
-    if (wt_out) cudaMemcpyAsync(wt_out, s.wt, (size_t)total * 4, cudaMemcpyDeviceToDevice, st);
-    if (route_only) return check_cuda(ctx, cudaGetLastError(), "MoE router launch");
-    const int EL = m->e_local;
-    if (EL != E) cudaMemsetAsync(s.pos, 0xFF, (size_t)total * 4, st);   // -1: assignment served elsewhere
-    if (total <= kGroupSmallMax) {
-        launch_pdl(moe_group_small_kernel, dim3(1), dim3(256), st, s.idx, total, s.count, s.offset, s.rowtok, s.pos, m->e_begin, EL);
-    } else {
-        moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
-        moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
-        moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
-        ctx->launches += 2;
-    }
-    if (s.xg) {
-        moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, m->top_k, s.offset, m->e_local, m->hidden, s.xg);
-        ctx->launches++;
-    }
-    launch_product<XT>(ctx, m, true, x, s.rowtok, s, s.gu, total, st);
-    int64_t hi = (int64_t)total * m->inter;
-    launch_pdl(moe_swiglu_kernel, dim3((unsigned)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
-    launch_product<float>(ctx, m, false, s.h, nullptr, s, s.o, total, st);
-    launch_pdl(moe_combine_kernel, dim3((unsigned)T, T < 1024 ? 4 : 1), dim3(256), st, s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
-    ctx->launches += 3;   // grouping, SwiGLU, combine (the products count themselves)
-    return check_cuda(ctx, cudaGetLastError(), "MoE launch");
 }
 
 // ---------------------------------------------------------------------------------
@@ -604,33 +572,70 @@ static nnq_status static_scratch_base(nnq_ctx *ctx, uint8_t **base) {
 }
 
 // The launches of one forward pass over a scratch area the caller of this function provides.
+// Routing comes from the block's router (given_idx == NULL: k = top_k slots per token) or from the
+// caller (given_idx / given_wt: [T, k] expert indices and weights already on the device; rows
+// whose expert lives elsewhere contribute nothing). route_only stops after the router.
 template <typename XT>
-static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int64_t T, float *y,
-                                   const MoeScratch &s, cudaStream_t st) {
-    const int E = m->n_experts, k = m->top_k;
+static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int64_t T, int k, const int *given_idx,
+                                   const float *given_wt, float *y, const MoeScratch &s, bool route_only, cudaStream_t st) {
+    const int E = m->n_experts;
     const int total = (int)(T * k);
-    launch_router<XT>(m, x, T, s.idx, s.wt, st);
+    const int *idx = s.idx;
+    const float *wt = s.wt;
+    if (given_idx) {
+        idx = given_idx;
+        wt = given_wt;
+    } else {
+        launch_router<XT>(m, x, T, s.idx, s.wt, st);
+        ctx->launches++;
+    }
+    if (route_only) return check_cuda(ctx, cudaGetLastError(), "MoE router launch");
     const int EL = m->e_local;
     if (EL != E) cudaMemsetAsync(s.pos, 0xFF, (size_t)total * 4, st);   // -1: assignment served elsewhere
     if (total <= kGroupSmallMax) {
-        launch_pdl(moe_group_small_kernel, dim3(1), dim3(256), st, s.idx, total, s.count, s.offset, s.rowtok, s.pos, m->e_begin, EL);
+        launch_pdl(moe_group_small_kernel, dim3(1), dim3(256), st, idx, total, s.count, s.offset, s.rowtok, s.pos, m->e_begin, EL);
     } else {
-        moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
+        moe_group_kernel<<<EL, 256, 0, st>>>(idx, total, s.count, s.offset, s.rowtok, s.pos, 0, m->e_begin);
         moe_scan_kernel<<<1, 32, 0, st>>>(s.count, s.offset, EL);
-        moe_group_kernel<<<EL, 256, 0, st>>>(s.idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
+        moe_group_kernel<<<EL, 256, 0, st>>>(idx, total, s.count, s.offset, s.rowtok, s.pos, 1, m->e_begin);
         ctx->launches += 2;
     }
     if (s.xg) {
-        moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, m->top_k, s.offset, m->e_local, m->hidden, s.xg);
+        moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, k, s.offset, m->e_local, m->hidden, s.xg);
         ctx->launches++;
     }
-    launch_product<XT>(ctx, m, true, x, s.rowtok, s, s.gu, total, st);
+    launch_product<XT>(ctx, m, true, x, s.rowtok, k, s, s.gu, total, st);
     int64_t hi = (int64_t)total * m->inter;
     launch_pdl(moe_swiglu_kernel, dim3((unsigned)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
-    launch_product<float>(ctx, m, false, s.h, nullptr, s, s.o, total, st);
-    launch_pdl(moe_combine_kernel, dim3((unsigned)T, T < 1024 ? 4 : 1), dim3(256), st, s.o, s.idx, s.wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
-    ctx->launches += 4;   // router, grouping, SwiGLU, combine (the products count themselves)
+    launch_product<float>(ctx, m, false, s.h, nullptr, k, s, s.o, total, st);
+    launch_pdl(moe_combine_kernel, dim3((unsigned)T, T < 1024 ? 4 : 1), dim3(256), st, s.o, idx, wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
+    ctx->launches += 3;   // grouping, SwiGLU, combine (the router and the products count themselves)
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
+}
+
+// Forward pass over the context's growable scratch buffer.
+template <typename XT>
+static nnq_status forward_typed(nnq_ctx *ctx, const nnq_moe *m, const XT *x, int64_t T, int k, const int *given_idx,
+                                const float *given_wt, float *y, int *idx_out, float *wt_out, bool route_only, cudaStream_t st) {
+    MoeScratch s;
+    nnq_status rc = ensure_scratch(ctx, m, T, k, given_idx != nullptr, &s);
+    if (rc != NNQ_OK) return rc;
+    rc = run_with_scratch<XT>(ctx, m, x, T, k, given_idx, given_wt, y, s, route_only, st);
+    if (rc != NNQ_OK) return rc;
+    const size_t total = (size_t)T * k;
+    if (idx_out) cudaMemcpyAsync(idx_out, s.idx, total * 4, cudaMemcpyDeviceToDevice, st);
+    if (wt_out) cudaMemcpyAsync(wt_out, s.wt, total * 4, cudaMemcpyDeviceToDevice, st);
+    return check_cuda(ctx, cudaGetLastError(), "MoE routing copy");
+}
+
+// Gathers rows of a [rows, H] matrix by index: out[i, :] = x[index[i], :] (the token permute of
+// expert parallelism: rows sorted by destination before they are sent).
+template <typename XT>
+__global__ void moe_gather_rows_kernel(const XT *__restrict__ x, const int *__restrict__ index, int64_t n, int H, XT *__restrict__ out) {
+    const int64_t r = blockIdx.x;
+    if (r >= n) return;
+    const XT *src = x + (size_t)index[r] * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) out[(size_t)r * H + j] = src[j];
 }
 
 }  // namespace nnq
@@ -776,8 +781,53 @@ static nnq_status moe_call(nnq_ctx *ctx, const nnq_moe *m, const void *x, nnq_dt
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
     cudaStream_t st = (cudaStream_t)stream;
-    if (x_dt == NNQ_F32) return forward_typed<float>(ctx, m, (const float *)x, tokens, y, idx_out, wt_out, route_only, st);
-    return forward_typed<__nv_bfloat16>(ctx, m, (const __nv_bfloat16 *)x, tokens, y, idx_out, wt_out, route_only, st);
+    if (x_dt == NNQ_F32) return forward_typed<float>(ctx, m, (const float *)x, tokens, m->top_k, nullptr, nullptr, y, idx_out, wt_out, route_only, st);
+    return forward_typed<__nv_bfloat16>(ctx, m, (const __nv_bfloat16 *)x, tokens, m->top_k, nullptr, nullptr, y, idx_out, wt_out, route_only, st);
+}
+
+nnq_status nnq_moe_forward_routed(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt, int64_t rows, int slots,
+                                  const int32_t *idx_dev, const float *weights_dev, float *y_dev, void *stream) {
+    if (!ctx || !m) return NNQ_ERR_INVALID_ARG;
+    if (m->ctx != ctx) return fail(ctx, NNQ_ERR_INVALID_ARG, "MoE block belongs to another context");
+    if (slots < 1 || slots > kMaxTopK) return fail(ctx, NNQ_ERR_INVALID_ARG, "1..%d expert slots per row", kMaxTopK);
+    if (rows < 0 || rows * slots > (int64_t)1 << 30) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad row count");
+    if ((int)x_dt < 0 || x_dt > NNQ_BF16) return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown dtype");
+    if (rows == 0) return NNQ_OK;
+    if (!x_dev || !y_dev || !idx_dev || !weights_dev) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dt == NNQ_F32) return forward_typed<float>(ctx, m, (const float *)x_dev, rows, slots, idx_dev, weights_dev, y_dev, nullptr, nullptr, false, st);
+    return forward_typed<__nv_bfloat16>(ctx, m, (const __nv_bfloat16 *)x_dev, rows, slots, idx_dev, weights_dev, y_dev, nullptr, nullptr, false, st);
+}
+
+nnq_status nnq_moe_gather_rows(nnq_ctx *ctx, const void *x_dev, nnq_dtype dt, const int32_t *index_dev, int64_t count, int64_t width,
+                               void *out_dev, void *stream) {
+    if (!ctx) return NNQ_ERR_INVALID_ARG;
+    if ((int)dt < 0 || dt > NNQ_BF16 || count < 0 || width < 1 || width > (1 << 24) || count > (int64_t)1 << 30) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad gather arguments");
+    if (count == 0) return NNQ_OK;
+    if (!x_dev || !index_dev || !out_dev) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dt == NNQ_F32) moe_gather_rows_kernel<float><<<(unsigned)count, 256, 0, st>>>((const float *)x_dev, index_dev, count, (int)width, (float *)out_dev);
+    else moe_gather_rows_kernel<__nv_bfloat16><<<(unsigned)count, 256, 0, st>>>((const __nv_bfloat16 *)x_dev, index_dev, count, (int)width, (__nv_bfloat16 *)out_dev);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "gather launch");
+}
+
+nnq_status nnq_moe_combine_rows(nnq_ctx *ctx, const float *rows_dev, const int32_t *idx_dev, const float *weights_dev,
+                                const int32_t *pos_dev, int64_t tokens, int hidden, int top_k, float *y_dev, void *stream) {
+    if (!ctx) return NNQ_ERR_INVALID_ARG;
+    if (tokens < 0 || hidden < 1 || top_k < 1 || top_k > kMaxTopK || tokens > (int64_t)1 << 28) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad combine arguments");
+    if (tokens == 0) return NNQ_OK;
+    if (!rows_dev || !idx_dev || !weights_dev || !pos_dev || !y_dev) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
+    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    if (s != NNQ_OK) return s;
+    moe_combine_kernel<<<dim3((unsigned)tokens, tokens < 1024 ? 4 : 1), 256, 0, (cudaStream_t)stream>>>(rows_dev, idx_dev, weights_dev, pos_dev, (int)tokens, hidden,
+                                                                                                        top_k, y_dev, 1, 0);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "combine launch");
 }
 
 nnq_status nnq_moe_forward(nnq_ctx *ctx, const nnq_moe *m, const void *x_dev, nnq_dtype x_dt, int64_t tokens,
@@ -800,7 +850,7 @@ nnq_status nnq_moe_forward_static(nnq_ctx *ctx, const nnq_moe *m, const void *x_
     if (!x_dev || !y_dev) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
     // size check first: it needs no device work
     if (tokens > ((int64_t)1 << 24)) return fail(ctx, NNQ_ERR_UNSUPPORTED, "token count beyond the fixed scratch area");
-    const size_t need = carve(nullptr, tokens, m).bytes;
+    const size_t need = carve(nullptr, tokens, m, m->top_k).bytes;
     if (need > kStaticScratchBytes)
         return fail(ctx, NNQ_ERR_UNSUPPORTED,
                     "this call needs %zu bytes of scratch, the fixed area holds %zu: use nnq_moe_forward or fewer tokens",
@@ -812,10 +862,10 @@ nnq_status nnq_moe_forward_static(nnq_ctx *ctx, const nnq_moe *m, const void *x_
     // Nothing in the area has to start at zero: every table and buffer is fully written by the
     // launches below before it is read (counts are stored, not accumulated), so stale contents
     // of an earlier call are harmless.
-    const MoeScratch sc = carve(base, tokens, m);
+    const MoeScratch sc = carve(base, tokens, m, m->top_k);
     cudaStream_t st = (cudaStream_t)stream;
-    if (x_dt == NNQ_F32) return run_with_scratch<float>(ctx, m, (const float *)x_dev, tokens, y_dev, sc, st);
-    return run_with_scratch<__nv_bfloat16>(ctx, m, (const __nv_bfloat16 *)x_dev, tokens, y_dev, sc, st);
+    if (x_dt == NNQ_F32) return run_with_scratch<float>(ctx, m, (const float *)x_dev, tokens, m->top_k, nullptr, nullptr, y_dev, sc, false, st);
+    return run_with_scratch<__nv_bfloat16>(ctx, m, (const __nv_bfloat16 *)x_dev, tokens, m->top_k, nullptr, nullptr, y_dev, sc, false, st);
 }
 
 }  // extern "C"

@@ -84,6 +84,21 @@ class MoeBlock:
                                      wt.data_ptr(), api._stream_ptr(None)))
         return idx, wt
 
+    def forward_routed(self, rows, experts, weights, slots: int = 1):
+        """The expert MLPs over rows whose routing the caller supplies: experts / weights are
+        [n, slots] (int32 global expert indices / f32); rows routed to experts this block does not
+        hold contribute nothing. Returns f32 [n, hidden]."""
+        import torch
+        b = self.backend
+        rows = rows.contiguous()
+        n = rows.shape[0]
+        y = torch.empty((n, self.hidden), dtype=torch.float32, device=rows.device)
+        if n:
+            b.check(b._lib.nnq_moe_forward_routed(b._ctx, self._handle, rows.data_ptr(), api._dtype_code(rows), n, slots,
+                                                  experts.contiguous().data_ptr(), weights.contiguous().data_ptr(), y.data_ptr(),
+                                                  api._stream_ptr(None)))
+        return y
+
     def release(self):
         if self._handle is not None:
             self.backend._lib.nnq_moe_destroy(self._handle)
@@ -94,3 +109,102 @@ class MoeBlock:
             self.release()
         except Exception:
             pass
+
+
+# --------------------------------------------------------------------------- #
+# expert parallelism with token dispatch (all-to-all)
+# --------------------------------------------------------------------------- #
+
+def dispatch_plan(idx, n_experts: int, world: int):
+    """Index arithmetic of the token dispatch, on whatever device `idx` lives ([T, k] expert
+    indices of the local tokens; torch tensor). Experts are split evenly over the ranks, rank r
+    holding experts [r * E / world, (r + 1) * E / world). Returns
+      order        [T*k] int64: the assignments (flat index t * k + slot) sorted by expert, ties in
+                   flat order (stable) -- hence sorted by destination rank too;
+      send_experts [T*k] int32: the expert of each sorted assignment;
+      src_token    [T*k] int32: the token whose activations that assignment sends;
+      send_counts  [world] int64: assignments per destination rank;
+      pos          [T, k] int32: where (t, slot) sits in the sorted order (the row that comes back).
+    """
+    import torch
+    t, k = idx.shape
+    per_rank = n_experts // world
+    flat = idx.reshape(-1).to(torch.int64)
+    order = torch.argsort(flat, stable=True)
+    send_experts = flat[order]
+    send_counts = torch.bincount(send_experts // per_rank, minlength=world)
+    pos = torch.empty(t * k, dtype=torch.int64, device=idx.device)
+    pos[order] = torch.arange(t * k, dtype=torch.int64, device=idx.device)
+    return (order, send_experts.to(torch.int32), (order // k).to(torch.int32), send_counts,
+            pos.reshape(t, k).to(torch.int32))
+
+
+def gather_rows(backend, x, index):
+    """out[i, :] = x[index[i], :] (library kernel; index int32 on the device)."""
+    import torch
+    x = x.contiguous()
+    out = torch.empty((index.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+    if index.shape[0]:
+        backend.check(backend._lib.nnq_moe_gather_rows(backend._ctx, x.data_ptr(), api._dtype_code(x), index.contiguous().data_ptr(),
+                                                       index.shape[0], x.shape[1], out.data_ptr(), api._stream_ptr(None)))
+    return out
+
+
+def combine_rows(backend, rows, idx, wt, pos):
+    """y[t, :] = sum over the slots of token t, in expert-index order, of wt[t, s] * rows[pos[t, s], :]."""
+    import torch
+    t, k = idx.shape
+    y = torch.empty((t, rows.shape[1]), dtype=torch.float32, device=rows.device)
+    if t:
+        backend.check(backend._lib.nnq_moe_combine_rows(backend._ctx, rows.contiguous().data_ptr(), idx.contiguous().data_ptr(),
+                                                        wt.contiguous().data_ptr(), pos.contiguous().data_ptr(), t, rows.shape[1], k,
+                                                        y.data_ptr(), api._stream_ptr(None)))
+    return y
+
+
+class ExpertParallelMoe:
+    """One MoE block over `world` ranks: every rank holds its own tokens and E / world experts
+    (``shard`` built with ``expert_range=(rank * E / world, E / world)``, router replicated).
+    forward: route locally -> sort the assignments by expert and gather their rows (library
+    kernel) -> all-to-all (NCCL) -> the owners run their experts over the received rows (library
+    kernels, routing supplied) -> all-to-all back -> weighted sum per token in expert-index order
+    (library kernel). Same result as the single-device block on the concatenated tokens
+    (crates/nn-gptoss/src/quantized_model.rs:132-194)."""
+
+    def __init__(self, shard: MoeBlock, rank: int, world: int, group=None):
+        if shard.n_experts % world:
+            raise api.InvalidShape(f"{shard.n_experts} experts do not split evenly over {world} ranks")
+        self.shard, self.rank, self.world, self.group = shard, rank, world, group
+
+    def _exchange(self, rows, send_counts, recv_counts):
+        import torch
+        import torch.distributed as dist
+        out = torch.empty((int(sum(recv_counts)),) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+        dist.all_to_all_single(out, rows.contiguous(), list(recv_counts), list(send_counts), group=self.group)
+        return out
+
+    def forward(self, x):
+        import torch
+        import torch.distributed as dist
+        s, b = self.shard, self.shard.backend
+        if x.shape[-1] != s.hidden:
+            raise api.ShapeMismatch(f"input last dim {x.shape[-1]} != hidden {s.hidden}")
+        xs = x.contiguous().reshape(-1, s.hidden)
+        t, k = xs.shape[0], s.top_k
+        dev = xs.device
+        idx, wt = s.route(xs)
+        order, send_experts, src_token, send_counts, pos = dispatch_plan(idx, s.n_experts, self.world)
+        # how many rows every rank sends to every other one (host-visible: the split sizes)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        sc, rc = send_counts.cpu().tolist(), recv_counts.cpu().tolist()
+        send_rows = gather_rows(b, xs, src_token)
+        recv_rows = self._exchange(send_rows, sc, rc)
+        recv_experts = self._exchange(send_experts, sc, rc)
+        ones = torch.ones(recv_rows.shape[0], dtype=torch.float32, device=dev)
+        out_rows = s.forward_routed(recv_rows, recv_experts, ones, 1)
+        back = self._exchange(out_rows, rc, sc)          # rows return in this rank's sorted send order
+        y = combine_rows(b, back, idx, wt, pos)
+        return y.reshape(tuple(x.shape[:-1]) + (s.hidden,))
+
+    __call__ = forward

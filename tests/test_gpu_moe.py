@@ -151,6 +151,114 @@ def test_expert_parallel_shards_sum_to_full_block(layout, fmt):
     full.release()
 
 
+@pytest.mark.parametrize("layout,fmt", [(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS), (moe.LAYOUT_NK, Q.MXFP4_SPLIT), (moe.LAYOUT_NK, Q.Q4_K)])
+def test_expert_parallel_token_dispatch_on_one_device(layout, fmt):
+    """The device-side pieces of expert parallelism with token dispatch (gather by destination,
+    experts over supplied routing, weighted combine) with the all-to-all played by hand: four
+    "ranks" on one GPU hold 8 / 4 experts each and ragged shares of the tokens."""
+    E, H, I, k, world = 8, 256, 256, 4, 4
+    shares = [10, 9, 11, 7]
+    T = sum(shares)
+    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(layout, fmt, E, H, I, 500)
+    x = F.gen_activations(501, T, H, bf16=True)
+    xt = torch.from_numpy(x).to(DEV)
+    full = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, layout, fmt, gu, gus, bgu, dn, dns, bd)
+    y_full = full(xt)
+    ec = E // world
+    rs = lambda a: None if a is None else np.asarray(a).reshape(E, -1)
+    gu2, dn2, gus2, dns2 = rs(gu), rs(dn), rs(gus), rs(dns)
+    shards = []
+    for r in range(world):
+        sl = slice(r * ec, (r + 1) * ec)
+        shards.append(moe.MoeBlock(E, H, I, k, 7.0, rw, rb, layout, fmt, gu2[sl], None if gus2 is None else gus2[sl], bgu[sl],
+                                   dn2[sl], None if dns2 is None else dns2[sl], bd[sl], expert_range=(r * ec, ec)))
+    b = full.backend
+    xs = torch.split(xt, shares)
+    plans, sends = [], []
+    for r in range(world):
+        idx, wt = shards[r].route(xs[r])
+        order, send_experts, src_token, send_counts, pos = moe.dispatch_plan(idx, E, world)
+        rows = moe.gather_rows(b, xs[r], src_token)
+        counts = send_counts.cpu().tolist()
+        plans.append((idx, wt, pos, counts))
+        sends.append((torch.split(rows, counts), torch.split(send_experts, counts)))
+    # "all-to-all": destination d receives, from every source in rank order, the slice meant for it
+    outs = []
+    for d in range(world):
+        recv_rows = torch.cat([sends[r][0][d] for r in range(world)])
+        recv_experts = torch.cat([sends[r][1][d] for r in range(world)])
+        assert bool(((recv_experts // ec) == d).all())
+        ones = torch.ones(recv_rows.shape[0], device=DEV)
+        out = shards[d].forward_routed(recv_rows, recv_experts, ones, 1)
+        outs.append(torch.split(out, [plans[r][3][d] for r in range(world)]))
+    ys = []
+    for r in range(world):
+        back = torch.cat([outs[d][r] for d in range(world)])     # this rank's rows, in its sorted order
+        idx, wt, pos, _ = plans[r]
+        ys.append(moe.combine_rows(b, back, idx, wt, pos))
+    y = torch.cat(ys)
+    torch.cuda.synchronize()
+    b.device_status()
+    assert float((y - y_full).abs().max() / y_full.abs().max()) <= 1e-5
+    y_ref, _, _ = orc.moe_forward(x, rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
+    assert np.max(np.abs(y.cpu().numpy() - y_ref)) / np.max(np.abs(y_ref)) <= 2e-3
+    for s_ in shards:
+        s_.release()
+    full.release()
+
+
+def _ep_worker(rank, world, port, out):
+    import os
+
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        dev = f"cuda:{rank}"
+        E, H, I, k = 8, 256, 256, 4
+        layout, fmt = moe.LAYOUT_NK, Q.MXFP4_SPLIT
+        rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(layout, fmt, E, H, I, 700)
+        shares = [13, 20][:world] if world == 2 else [9] * world
+        x = F.gen_activations(701, sum(shares), H, bf16=True)
+        b = api.Backend(rank)
+        ec = E // world
+        sl = slice(rank * ec, (rank + 1) * ec)
+        rs = lambda a: np.asarray(a).reshape(E, -1)
+        shard = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, layout, fmt, rs(gu)[sl], rs(gus)[sl], bgu[sl], rs(dn)[sl], rs(dns)[sl], bd[sl],
+                             backend=b, expert_range=(rank * ec, ec))
+        ep = moe.ExpertParallelMoe(shard, rank, world)
+        lo = sum(shares[:rank])
+        y = ep(torch.from_numpy(x[lo:lo + shares[rank]]).to(dev)).cpu().numpy()
+        torch.cuda.synchronize()
+        b.device_status()
+        y_ref, _, _ = orc.moe_forward(x[lo:lo + shares[rank]], rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
+        ok = bool(np.max(np.abs(y - y_ref)) / np.max(np.abs(y_ref)) <= 2e-3)
+        oks = [None] * world
+        dist.all_gather_object(oks, ok)
+        if rank == 0:
+            np.save(out, np.array([1 if all(oks) else 0]))
+        dist.barrier()
+        shard.release()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_all_to_all_two_gpus(tmp_path):
+    import socket
+
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    out = str(tmp_path / "ok.npy")
+    mp.spawn(_ep_worker, args=(2, port, out), nprocs=2, join=True)
+    assert int(np.load(out)[0]) == 1
+
+
 # --------------------------------------------------------------------------- #
 # gpt-oss-20b geometry: 32 experts, top-4, hidden = inter = 2880
 # --------------------------------------------------------------------------- #
