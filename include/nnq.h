@@ -157,10 +157,12 @@ NNQ_API nnq_status nnq_weight_create(nnq_ctx *ctx, nnq_format fmt, const void *d
 
 /* Tensor-parallel shard of an [N, K] weight given as raw bytes (host or device).
  * axis 0 (column-parallel): rows [rank*N/world, (rank+1)*N/world).
- * axis 1 (row-parallel): whole blocks [rank*KB/world, (rank+1)*KB/world) of every row,
- * KB = K / block size, gathered into a contiguous [N, K/world] weight.
- * The split must be even, else NNQ_ERR_INVALID_SHAPE. No counterpart in the reference,
- * which runs on one device. */
+ * axis 1 (row-parallel): whole units [rank*U/world, (rank+1)*U/world) of every row, gathered
+ * into a contiguous [N, K_rank] weight; a unit is 256 weights when K is a multiple of 256 (every
+ * shard then keeps a tiled layout), else one block. The shards may differ by one unit (K = 25600
+ * over 8 ranks: 13 or 12 super-blocks); nnq_weight_info gives a shard's K. Rows (axis 0) must
+ * split evenly, else NNQ_ERR_INVALID_SHAPE. No counterpart in the reference, which runs on one
+ * device. */
 NNQ_API nnq_status nnq_weight_create_shard(nnq_ctx *ctx, nnq_format fmt, const void *data, size_t nbytes,
                                    const void *scales, size_t scales_nbytes, int64_t n,
                                    int64_t k, int axis, int rank, int world, nnq_weight **out);
@@ -513,6 +515,15 @@ NNQ_API nnq_status nnq_decoder_reset(nnq_decoder *d, int token, int pos, void *s
 /* one token: consumes (token, pos), appends to the caches, leaves the logits in the logits buffer,
  * stores the argmax as the next token and advances the position */
 NNQ_API nnq_status nnq_decoder_step(nnq_decoder *d, void *stream);
+/* Prompt pass: runs `count` prompt tokens (host array) through the decoder at positions
+ * start_pos .. start_pos + count - 1 in blocks of up to 256 rows -- the products on the M > 16 paths,
+ * attention under the causal mask (every row sees the cache up to its own position:
+ * crates/nn-qwen3/src/forward_common.rs:55-64,189-204, crates/nn-core/src/layers/attention/sdpa.rs:118-141)
+ * -- fills the caches, leaves the logits of the last prompt token in the logits buffer, stores its
+ * greedy successor as the next token and sets the position to start_pos + count, so that
+ * nnq_decoder_step continues the sequence. No nnq_decoder_reset is needed before it. The first call
+ * allocates the row buffers; the call synchronises the stream (not for graph capture). */
+NNQ_API nnq_status nnq_decoder_prefill(nnq_decoder *d, const int32_t *tokens_host, int count, int start_pos, void *stream);
 /* reads (next token, next position, steps taken) back; synchronises the stream */
 NNQ_API nnq_status nnq_decoder_state(nnq_decoder *d, int *token, int *pos, int *steps, void *stream);
 /* device buffers: key / value caches [layers, kv_heads, max_seq, head_dim] f32, logits [vocab] f32,

@@ -65,6 +65,7 @@ SIGNATURES = {
     "nnq_decoder_set_comm": (c_int, [c_void_p, c_void_p]),
     "nnq_decoder_reset": (c_int, [c_void_p, c_int, c_int, c_void_p]),
     "nnq_decoder_step": (c_int, [c_void_p, c_void_p]),
+    "nnq_decoder_prefill": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "nnq_decoder_state": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_void_p]),
     "nnq_decoder_buffers": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                     ctypes.POINTER(c_void_p)]),

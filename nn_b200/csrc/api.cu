@@ -271,15 +271,21 @@ nnq_status nnq_weight_create_shard(nnq_ctx *ctx, nnq_format fmt, const void *dat
         if (s == NNQ_OK && w->scales_nbytes)
             s = check_cuda(ctx, cudaMemcpy(w->d_scales, (const uint8_t *)scales + (size_t)rank * ns * row_s, w->scales_nbytes, cudaMemcpyDefault), "shard scales upload");
     } else {
-        if (kb % world) return fail(ctx, NNQ_ERR_INVALID_SHAPE, "%lld blocks per row not divisible by %d ranks", (long long)kb, world);
-        int64_t kbs = kb / world;
+        // K is dealt out in units of whole blocks -- of 256 weights when K is a multiple of 256, so that
+        // every shard keeps a tiled layout -- rank r taking units [r * U / world, (r + 1) * U / world):
+        // the shards may differ by one unit (Qwen3-32B's down_proj: 100 super-blocks over 8 ranks = 13 or 12)
+        const int64_t per_unit = (k % 256 == 0 && 256 % g.elems == 0) ? 256 / g.elems : 1;
+        const int64_t units = kb / per_unit;
+        if (units < world) return fail(ctx, NNQ_ERR_INVALID_SHAPE, "%lld units of K cannot be split over %d ranks", (long long)units, world);
+        const int64_t b0 = (rank * units / world) * per_unit, b1 = ((rank + 1) * units / world) * per_unit;
+        const int64_t kbs = b1 - b0;
         size_t row_b = (size_t)kb * g.bytes, row_s = (size_t)kb * g.scale_bytes;
         size_t sh_b = (size_t)kbs * g.bytes, sh_s = (size_t)kbs * g.scale_bytes;
         if ((s = alloc_weight(ctx, fmt, n, kbs * g.elems, n * sh_b, n * sh_s, &w)) != NNQ_OK) return s;
         if (w->nbytes)
-            s = check_cuda(ctx, cudaMemcpy2D(w->d_raw, sh_b, (const uint8_t *)data + (size_t)rank * sh_b, row_b, sh_b, n, cudaMemcpyDefault), "shard upload");
+            s = check_cuda(ctx, cudaMemcpy2D(w->d_raw, sh_b, (const uint8_t *)data + (size_t)b0 * g.bytes, row_b, sh_b, n, cudaMemcpyDefault), "shard upload");
         if (s == NNQ_OK && w->scales_nbytes)
-            s = check_cuda(ctx, cudaMemcpy2D(w->d_scales, sh_s, (const uint8_t *)scales + (size_t)rank * sh_s, row_s, sh_s, n, cudaMemcpyDefault), "shard scales upload");
+            s = check_cuda(ctx, cudaMemcpy2D(w->d_scales, sh_s, (const uint8_t *)scales + (size_t)b0 * g.scale_bytes, row_s, sh_s, n, cudaMemcpyDefault), "shard scales upload");
     }
     if (s == NNQ_OK) s = finish_weight(ctx, w);
     if (s != NNQ_OK) {

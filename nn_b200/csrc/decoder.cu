@@ -46,6 +46,12 @@ struct nnq_decoder {
     int lh, lkv;                // query / key-value heads held by this rank
     int head_rows, head_row0;   // rows of the vocabulary projection held by this rank and the first of them
     long long host_pos;         // position of the next step as far as the host knows it (-1: unknown)
+    // prompt pass: row-major [rows, width] versions of the step's buffers, allocated by the first
+    // nnq_decoder_prefill call (pf_rows rows)
+    int pf_rows;
+    float *pf_h, *pf_delta, *pf_q, *pf_k, *pf_v, *pf_qrot, *pf_g, *pf_u;
+    void *pf_xn, *pf_attn, *pf_mid;
+    int *pf_tokens;
 };
 
 namespace nnq {
@@ -377,6 +383,147 @@ __global__ void dec_argmax_exchange_kernel(const float *__restrict__ bv_in, cons
     *reinterpret_cast<volatile unsigned *>(local) = seq;   // this exchange is complete
 }
 
+// ---- prompt pass: the same operations over a block of rows (one row per prompt token) ----
+
+// row r: h = embedding of tokens[r] (first layer) or h += delta; xn = RMSNorm(h) * w. One CTA per row.
+__global__ void __launch_bounds__(256)
+dec_norm_rows_kernel(float *__restrict__ h, const float *__restrict__ delta, const __nv_bfloat16 *__restrict__ embed,
+                     const int *__restrict__ tokens, const float *__restrict__ w, float eps, void *__restrict__ xn, int act_dt,
+                     int hidden) {
+    __shared__ float red[32];
+    const size_t r = blockIdx.x;
+    float *hr = h + r * hidden;
+    const float *dr = delta ? delta + r * hidden : nullptr;
+    const __nv_bfloat16 *er = embed ? embed + (size_t)tokens[r] * hidden : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = er ? __bfloat162float(er[i]) : hr[i] + dr[i];
+        hr[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float rms = sqrtf(block_sum(ss, red) / (float)hidden + eps);
+    char *xr = reinterpret_cast<char *>(xn) + r * hidden * (act_dt == NNQ_F32 ? 4 : 2);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) store_act(xr, act_dt, i, (hr[i] / rms) * w[i]);
+}
+
+// grid (heads, rows): per-head RMSNorm + half-split rotation at position pos0 + row, append of k / v
+__global__ void __launch_bounds__(256)
+dec_qk_rope_rows_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                        const float *__restrict__ qw, const float *__restrict__ kw, const float *__restrict__ cosv,
+                        const float *__restrict__ sinv, int pos0, float eps, float *__restrict__ qrot, float *__restrict__ kcache,
+                        float *__restrict__ vcache, int n_heads, int n_kv, int hd, int max_seq) {
+    __shared__ float red[32];
+    __shared__ float xs[256];
+    const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x, pos = pos0 + row;
+    const int half = hd / 2;
+    const size_t qoff = (size_t)row * n_heads * hd, kvoff = (size_t)row * n_kv * hd;
+    if (head >= n_heads + n_kv) {
+        const int kvh = head - n_heads - n_kv;
+        if (d < hd) vcache[((size_t)kvh * max_seq + pos) * hd + d] = v[kvoff + kvh * hd + d];
+        return;
+    }
+    const bool is_q = head < n_heads;
+    const float *src = is_q ? q + qoff + head * hd : k + kvoff + (head - n_heads) * hd;
+    const float *w = is_q ? qw : kw;
+    const float x = d < hd ? src[d] : 0.0f;
+    const float rms = sqrtf(block_sum(x * x, red) / (float)hd + eps);
+    if (d < hd) xs[d] = (x / rms) * w[d];
+    __syncthreads();
+    if (d >= hd) return;
+    const int i = d < half ? d : d - half;
+    const float c = cosv[(size_t)pos * half + i], sn = sinv[(size_t)pos * half + i];
+    const float y = d < half ? xs[d] * c - xs[d + half] * sn : xs[d - half] * sn + xs[d] * c;
+    if (is_q) qrot[qoff + head * hd + d] = y;
+    else kcache[((size_t)(head - n_heads) * max_seq + pos) * hd + d] = y;
+}
+
+// Causal attention of a block of query rows over the cache: one warp per (kv head, row) serves the
+// G query heads of the group over keys 0 .. pos0 + row (the mask of the reference's prompt pass:
+// crates/nn-core/src/layers/attention/sdpa.rs:118-141), same batch-of-32-keys scheme as the decode
+// kernel, normalised output written directly.
+template <int G>
+__global__ void __launch_bounds__(32)
+dec_attn_rows_kernel(const float *__restrict__ qrot, const float *__restrict__ kcache, const float *__restrict__ vcache, int pos0,
+                     float scale, void *__restrict__ out, int act_dt, int n_heads, int hd, int max_seq) {
+    __shared__ __align__(16) float qs[G][128];
+    const int kvh = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
+    const int j1 = pos0 + row + 1;
+    const size_t qoff = (size_t)row * n_heads * hd;
+#pragma unroll
+    for (int g = 0; g < G; g++)
+        *reinterpret_cast<float4 *>(&qs[g][4 * lane]) = *reinterpret_cast<const float4 *>(qrot + qoff + (kvh * G + g) * hd + 4 * lane);
+    __syncwarp();
+    float m[G], l[G];
+    float4 acc[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+        acc[g] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    const float *kb = kcache + (size_t)kvh * max_seq * hd, *vb = vcache + (size_t)kvh * max_seq * hd;
+    for (int b0 = 0; b0 < j1; b0 += 32) {
+        const int j = b0 + lane;
+        const bool valid = j < j1;
+        const float4 *krow = reinterpret_cast<const float4 *>(kb + (size_t)(valid ? j : b0) * hd);
+        float dot[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) dot[g] = 0.0f;
+#pragma unroll 16
+        for (int d4 = 0; d4 < 32; d4++) {
+            const float4 kv = krow[d4];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float4 qv = *reinterpret_cast<const float4 *>(&qs[g][4 * d4]);
+                dot[g] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, dot[g]))));
+            }
+        }
+        float p[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const float sc = valid ? dot[g] * scale : -INFINITY;
+            float bm = sc;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
+            const float mn = fmaxf(m[g], bm);
+            const float corr = expf(m[g] - mn);
+            p[g] = expf(sc - mn);
+            float ps = p[g];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xFFFFFFFFu, ps, off);
+            l[g] = l[g] * corr + ps;
+            acc[g].x *= corr; acc[g].y *= corr; acc[g].z *= corr; acc[g].w *= corr;
+            m[g] = mn;
+        }
+        const int nb = min(32, j1 - b0);
+        for (int jj = 0; jj < nb; jj++) {
+            const float4 vv = *reinterpret_cast<const float4 *>(vb + (size_t)(b0 + jj) * hd + 4 * lane);
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const float pj = __shfl_sync(0xFFFFFFFFu, p[g], jj);
+                acc[g].x = fmaf(pj, vv.x, acc[g].x);
+                acc[g].y = fmaf(pj, vv.y, acc[g].y);
+                acc[g].z = fmaf(pj, vv.z, acc[g].z);
+                acc[g].w = fmaf(pj, vv.w, acc[g].w);
+            }
+        }
+    }
+    char *orow = reinterpret_cast<char *>(out) + (size_t)row * n_heads * hd * (act_dt == NNQ_F32 ? 4 : 2);
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const int base = (kvh * G + g) * hd + 4 * lane;
+        store_act(orow, act_dt, base, acc[g].x / l[g]);
+        store_act(orow, act_dt, base + 1, acc[g].y / l[g]);
+        store_act(orow, act_dt, base + 2, acc[g].z / l[g]);
+        store_act(orow, act_dt, base + 3, acc[g].w / l[g]);
+    }
+}
+
+// position of the last prompt token, for the commit of its greedy successor
+__global__ void dec_set_pos_kernel(int *state, int pos) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) state[1] = pos;
+}
+
 }  // namespace nnq
 
 using namespace nnq;
@@ -560,6 +707,40 @@ nnq_status nnq_decoder_buffers(nnq_decoder *d, float **k_cache, float **v_cache,
     return NNQ_OK;
 }
 
+// Vocabulary projection of the normed state in d_xn, greedy argmax (exchanged between the ranks
+// when the projection is split by rows), commit of the token and advance of the position.
+static nnq_status launch_head(nnq_decoder *d, bool vocab_parallel, const CommView &cv, cudaStream_t st) {
+    nnq_ctx *ctx = d->ctx;
+    const nnq_decoder_config &c = d->cfg;
+    nnq_status s;
+    // the logits of this rank's rows land at their global offsets in the [vocab] buffer
+    float *logits = d->d_logits + d->head_row0;
+    if ((s = nnq_linear(ctx, d->lm_head, d->d_xn, (nnq_dtype)d->act_dt, 1, nullptr, logits, NNQ_F32, st)) != NNQ_OK) return s;
+    float *bv = reinterpret_cast<float *>(d->d_state + 4);
+    int *bi = d->d_state + 4 + kArgmaxBlocks;
+    launch_pdl(dec_argmax_stage1_kernel, dim3(kArgmaxBlocks), dim3(256), st, logits, d->head_rows, bv, bi);
+    if (vocab_parallel)
+        launch_pdl(dec_argmax_exchange_kernel, dim3(1), dim3(32), st, bv, bi, kArgmaxBlocks, d->head_row0, cv.peer_table, cv.rank, cv.world,
+                   cv.slot_bytes, d->d_state, d->d_tokens, c.max_seq, ctx->d_status);
+    else
+        launch_pdl(dec_argmax_stage2_kernel, dim3(1), dim3(32), st, bv, bi, kArgmaxBlocks, d->d_state, d->d_tokens, c.max_seq, ctx->d_status);
+    ctx->launches += 2;
+    return check_cuda(ctx, cudaGetLastError(), "decoder head launch");
+}
+
+static nnq_status head_mode(nnq_decoder *d, bool *vocab_parallel, CommView *cv) {
+    const nnq_decoder_config &c = d->cfg;
+    *vocab_parallel = d->head_rows != c.vocab;
+    *cv = CommView{};
+    if (*vocab_parallel) {
+        nnq_status sv = comm_view(d->comm, cv);
+        if (sv != NNQ_OK) return sv;
+        if (cv->slot_bytes < (size_t)8 * c.hidden + 16)
+            return fail(d->ctx, NNQ_ERR_UNSUPPORTED, "a vocabulary-parallel head needs communicator slots of at least 8 * hidden + 16 bytes (have %zu)", cv->slot_bytes);
+    }
+    return NNQ_OK;
+}
+
 nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
     if (!d) return NNQ_ERR_INVALID_ARG;
     nnq_ctx *ctx = d->ctx;
@@ -574,15 +755,11 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
     if (d->host_pos >= c.max_seq)
         return fail(ctx, NNQ_ERR_UNSUPPORTED, "the decoder's context is full (max_seq = %d positions): reset it", c.max_seq);
     if (d->host_pos >= 0) d->host_pos++;
-    const bool vocab_parallel = d->head_rows != c.vocab;
+    bool vocab_parallel = false;
     CommView cv = {};
-    if (vocab_parallel) {
-        nnq_status sv = comm_view(d->comm, &cv);
-        if (sv != NNQ_OK) return sv;
-        if (cv.slot_bytes < (size_t)8 * c.hidden + 16)
-            return fail(ctx, NNQ_ERR_UNSUPPORTED, "a vocabulary-parallel head needs communicator slots of at least 8 * hidden + 16 bytes (have %zu)", cv.slot_bytes);
-    }
-    nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
+    nnq_status s = head_mode(d, &vocab_parallel, &cv);
+    if (s != NNQ_OK) return s;
+    s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
     cudaStream_t st = (cudaStream_t)stream;
     const int hd = c.head_dim, group = c.n_heads / c.n_kv_heads, lh = d->lh, lkv = d->lkv, lffn = c.ffn / c.tp_world;
@@ -627,19 +804,111 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
         ctx->launches += 6;
     }
     launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, d->d_final_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
-    // the logits of this rank's rows land at their global offsets in the [vocab] buffer
-    float *logits = d->d_logits + d->head_row0;
-    if ((s = nnq_linear(ctx, d->lm_head, d->d_xn, adt, 1, nullptr, logits, NNQ_F32, st)) != NNQ_OK) return s;
-    float *bv = reinterpret_cast<float *>(d->d_state + 4);
-    int *bi = d->d_state + 4 + kArgmaxBlocks;
-    launch_pdl(dec_argmax_stage1_kernel, dim3(kArgmaxBlocks), dim3(256), st, logits, d->head_rows, bv, bi);
-    if (vocab_parallel)
-        launch_pdl(dec_argmax_exchange_kernel, dim3(1), dim3(32), st, bv, bi, kArgmaxBlocks, d->head_row0, cv.peer_table, cv.rank, cv.world,
-                   cv.slot_bytes, d->d_state, d->d_tokens, c.max_seq, ctx->d_status);
-    else
-        launch_pdl(dec_argmax_stage2_kernel, dim3(1), dim3(32), st, bv, bi, kArgmaxBlocks, d->d_state, d->d_tokens, c.max_seq, ctx->d_status);
-    ctx->launches += 3;
-    return check_cuda(ctx, cudaGetLastError(), "decoder step launch");
+    ctx->launches++;
+    return launch_head(d, vocab_parallel, cv, st);
+}
+
+nnq_status nnq_decoder_prefill(nnq_decoder *d, const int32_t *tokens_host, int count, int start_pos, void *stream) {
+    if (!d) return NNQ_ERR_INVALID_ARG;
+    nnq_ctx *ctx = d->ctx;
+    const nnq_decoder_config &c = d->cfg;
+    if (!d->ready) return fail(ctx, NNQ_ERR_INVALID_ARG, "decoder head has not been set");
+    if (c.tp_world > 1 && !d->comm) return fail(ctx, NNQ_ERR_INVALID_ARG, "communicator has not been set");
+    for (int l = 0; l < c.n_layers; l++)
+        if (!d->layers[l].q) return fail(ctx, NNQ_ERR_INVALID_ARG, "layer %d has not been set", l);
+    if (!tokens_host || count < 1 || start_pos < 0) return fail(ctx, NNQ_ERR_INVALID_ARG, "bad prompt arguments");
+    if ((long long)start_pos + count > c.max_seq)
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "a prompt of %d tokens at position %d does not fit max_seq = %d", count, start_pos, c.max_seq);
+    for (int i = 0; i < count; i++)
+        if (tokens_host[i] < 0 || tokens_host[i] >= c.vocab) return fail(ctx, NNQ_ERR_INVALID_ARG, "prompt token %d out of range", i);
+    bool vocab_parallel = false;
+    CommView cv = {};
+    nnq_status s = head_mode(d, &vocab_parallel, &cv);
+    if (s != NNQ_OK) return s;
+    if ((s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice")) != NNQ_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int hd = c.head_dim, group = c.n_heads / c.n_kv_heads, lh = d->lh, lkv = d->lkv, lffn = c.ffn / c.tp_world;
+    const int qdim = lh * hd, kvdim = lkv * hd;
+    const nnq_dtype adt = (nnq_dtype)d->act_dt;
+    const size_t es = adt == NNQ_F32 ? 4 : 2;
+    // rows per pass: bounded by the scratch below and, with tensor parallelism, by what one exchange carries
+    int rows_max = 256;
+    if (d->comm) {
+        CommView v;
+        if ((s = comm_view(d->comm, &v)) != NNQ_OK) return s;
+        const size_t fit = v.slot_bytes / ((size_t)c.hidden * 4);
+        if (fit < 1) return fail(ctx, NNQ_ERR_UNSUPPORTED, "communicator slots are smaller than one row of the hidden state");
+        if ((size_t)rows_max > fit) rows_max = (int)fit;
+    }
+    if (!d->pf_h) {
+        d->pf_rows = 256;
+        const size_t R = 256;
+        s = dev_alloc(ctx, (void **)&d->pf_h, R * c.hidden * 4, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_delta, R * c.hidden * 4, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_q, R * qdim * 4, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_k, R * kvdim * 4, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_v, R * kvdim * 4, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_qrot, R * qdim * 4, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_g, R * lffn * 4, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_u, R * lffn * 4, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, &d->pf_xn, R * c.hidden * es, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, &d->pf_attn, R * qdim * es, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, &d->pf_mid, R * lffn * es, "prompt buffer");
+        if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_tokens, R * 4, "prompt buffer");
+        if (s != NNQ_OK) return s;
+    }
+    const size_t layer_cache = (size_t)lkv * c.max_seq * hd;
+    const float scale = (float)(1.0 / sqrt((double)hd));
+    const __nv_bfloat16 *embed = (const __nv_bfloat16 *)d->d_embed;
+    int n = 0;
+    for (int c0 = 0; c0 < count; c0 += n) {
+        n = count - c0 < rows_max ? count - c0 : rows_max;
+        const int pos0 = start_pos + c0;
+        if ((s = check_cuda(ctx, cudaMemcpyAsync(d->pf_tokens, tokens_host + c0, (size_t)n * 4, cudaMemcpyHostToDevice, st), "prompt tokens")) != NNQ_OK) return s;
+        for (int l = 0; l < c.n_layers; l++) {
+            const nnq_decoder::Layer &L = d->layers[l];
+            float *kc = d->d_kcache + l * layer_cache, *vc = d->d_vcache + l * layer_cache;
+            dec_norm_rows_kernel<<<n, 256, 0, st>>>(d->pf_h, l == 0 ? nullptr : d->pf_delta, l == 0 ? embed : nullptr, d->pf_tokens, L.in_norm,
+                                                    c.rms_eps, d->pf_xn, d->act_dt, c.hidden);
+            const nnq_weight *w3[3] = {L.q, L.k, L.v};
+            const void *x3[3] = {d->pf_xn, d->pf_xn, d->pf_xn};
+            void *y3[3] = {d->pf_q, d->pf_k, d->pf_v};
+            if ((s = nnq_linear_batch(ctx, 3, w3, x3, adt, n, nullptr, y3, NNQ_F32, st)) != NNQ_OK) return s;
+            dec_qk_rope_rows_kernel<<<dim3(lh + 2 * lkv, n), hd, 0, st>>>(d->pf_q, d->pf_k, d->pf_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, pos0,
+                                                                         c.rms_eps, d->pf_qrot, kc, vc, lh, lkv, hd, c.max_seq);
+            const dim3 ag(lkv, n);
+            switch (group) {
+                case 1: dec_attn_rows_kernel<1><<<ag, 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
+                case 2: dec_attn_rows_kernel<2><<<ag, 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
+                case 4: dec_attn_rows_kernel<4><<<ag, 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
+                case 8: dec_attn_rows_kernel<8><<<ag, 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
+                default: return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must be 1, 2, 4 or 8");
+            }
+            s = d->comm ? nnq_comm_linear(d->comm, L.o, d->pf_attn, adt, n, nullptr, d->pf_delta, NNQ_F32, st)
+                        : nnq_linear(ctx, L.o, d->pf_attn, adt, n, nullptr, d->pf_delta, NNQ_F32, st);
+            if (s != NNQ_OK) return s;
+            dec_norm_rows_kernel<<<n, 256, 0, st>>>(d->pf_h, d->pf_delta, nullptr, d->pf_tokens, L.post_norm, c.rms_eps, d->pf_xn, d->act_dt, c.hidden);
+            const nnq_weight *w2[2] = {L.gate, L.up};
+            const void *x2[2] = {d->pf_xn, d->pf_xn};
+            void *y2[2] = {d->pf_g, d->pf_u};
+            if ((s = nnq_linear_batch(ctx, 2, w2, x2, adt, n, nullptr, y2, NNQ_F32, st)) != NNQ_OK) return s;
+            const int total = n * lffn;
+            dec_silu_mul_kernel<<<(total + 255) / 256, 256, 0, st>>>(d->pf_g, d->pf_u, d->pf_mid, d->act_dt, total);
+            s = d->comm ? nnq_comm_linear(d->comm, L.down, d->pf_mid, adt, n, nullptr, d->pf_delta, NNQ_F32, st)
+                        : nnq_linear(ctx, L.down, d->pf_mid, adt, n, nullptr, d->pf_delta, NNQ_F32, st);
+            if (s != NNQ_OK) return s;
+            ctx->launches += 5;
+        }
+    }
+    // the last prompt token's state: final norm, vocabulary projection, greedy successor
+    const size_t last = (size_t)(n - 1) * c.hidden;
+    const int st4[4] = {tokens_host[count - 1], start_pos + count - 1, 0, 0};
+    if ((s = check_cuda(ctx, cudaMemcpyAsync(d->d_state, st4, sizeof(st4), cudaMemcpyHostToDevice, st), "decoder state")) != NNQ_OK) return s;
+    launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->pf_h + last, d->pf_delta + last, nullptr, d->d_state, d->d_final_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+    ctx->launches++;
+    if ((s = launch_head(d, vocab_parallel, cv, st)) != NNQ_OK) return s;
+    d->host_pos = (long long)start_pos + count;
+    return check_cuda(ctx, cudaStreamSynchronize(st), "prompt pass");   // tokens_host and st4 are the caller's / the stack's
 }
 
 nnq_status nnq_decoder_state(nnq_decoder *d, int *token, int *pos, int *steps, void *stream) {
@@ -669,6 +938,8 @@ void nnq_decoder_destroy(nnq_decoder *d) {
     cudaFree(d->d_h); cudaFree(d->d_delta); cudaFree(d->d_q); cudaFree(d->d_k); cudaFree(d->d_v); cudaFree(d->d_qrot);
     cudaFree(d->d_g); cudaFree(d->d_u); cudaFree(d->d_logits); cudaFree(d->d_part); cudaFree(d->d_xn); cudaFree(d->d_attn);
     cudaFree(d->d_mid); cudaFree(d->d_state); cudaFree(d->d_tokens);
+    cudaFree(d->pf_h); cudaFree(d->pf_delta); cudaFree(d->pf_q); cudaFree(d->pf_k); cudaFree(d->pf_v); cudaFree(d->pf_qrot);
+    cudaFree(d->pf_g); cudaFree(d->pf_u); cudaFree(d->pf_xn); cudaFree(d->pf_attn); cudaFree(d->pf_mid); cudaFree(d->pf_tokens);
     cudaGetLastError();
     delete d;
 }

@@ -83,6 +83,14 @@ class Decoder:
     def reset(self, token: int, pos: int, stream=None):
         self.backend.check(self.backend._lib.nnq_decoder_reset(self._handle, token, pos, api._stream_ptr(stream)))
 
+    def prefill(self, tokens, start_pos: int = 0, stream=None):
+        """Prompt pass over `tokens` (a sequence of ids) at positions start_pos ..: fills the caches,
+        leaves the last prompt token's logits and its greedy successor as the next input."""
+        import numpy as np
+        arr = np.ascontiguousarray(tokens, dtype=np.int32)
+        self.backend.check(self.backend._lib.nnq_decoder_prefill(self._handle, arr.ctypes.data, int(arr.size), int(start_pos),
+                                                                 api._stream_ptr(stream)))
+
     def step(self, stream=None):
         self.backend.check(self.backend._lib.nnq_decoder_step(self._handle, api._stream_ptr(stream)))
 

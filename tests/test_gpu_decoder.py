@@ -16,11 +16,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _build(act_dtype, seed=11, backend=None, tp=(0, 1), comm=None, vocab_parallel=False):
+def _build(act_dtype, seed=11, backend=None, tp=(0, 1), comm=None, vocab_parallel=False, max_seq=48):
     """Decoder + dequantized model; with tp = (rank, world) the decoder holds that rank's shards."""
     rank, world = tp
     cfg = decoder.DecoderConfig(hidden=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, n_layers=2, vocab=1024,
-                                max_seq=48, rms_eps=1e-6, rope_theta=1e6, act_dtype=act_dtype, tp_rank=rank, tp_world=world)
+                                max_seq=max_seq, rms_eps=1e-6, rope_theta=1e6, act_dtype=act_dtype, tp_rank=rank, tp_world=world)
     s = F.Stream(seed)
     qdim, kvdim = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
 
@@ -223,6 +223,51 @@ def test_qwen3_8b_width_steps_at_long_context(act_dtype, tol):
     for ws in keep:
         for w in ws:
             w.release()
+
+
+@pytest.mark.parametrize("act_dtype", [api.F32, api.BF16])
+@pytest.mark.parametrize("count", [9, 300])
+def test_prompt_pass_matches_token_by_token(act_dtype, count):
+    """A prompt of random ids through nnq_decoder_prefill (M > 1 products, causal mask; 300 tokens
+    take two blocks of rows) against the restatement stepped token by token, then three greedy
+    steps. The prompt products run on the tensor cores with bf16 operands: the 1e-2 class per
+    product, 3e-2 on the logits after two layers (measured well below)."""
+    cfg, dec, model, keep = _build(act_dtype, seed=61, max_seq=count + 8)
+    rng = np.random.default_rng(62)
+    prompt = rng.integers(0, cfg.vocab, size=count).tolist()
+    kc = np.zeros((cfg.n_layers, cfg.n_kv_heads, cfg.max_seq, cfg.head_dim), np.float32)
+    vc = np.zeros_like(kc)
+    bf = act_dtype == api.BF16
+    want = None
+    for i, t in enumerate(prompt):
+        want, want_tok = ref.step(model, t, i, kc, vc, act_bf16=bf)
+    dec.prefill(prompt, 0)
+    nxt, pos, steps = dec.state()
+    assert (pos, steps) == (count, 1)
+    k_dev, v_dev, logits_dev, tokens_dev = dec.buffers()
+    got = logits_dev.cpu().numpy()
+    assert np.all(np.isfinite(got))
+    err = np.max(np.abs(got - want)) / np.max(np.abs(want))
+    assert err <= 3e-2, err
+    assert nxt == ref.argmax_last(got) and int(tokens_dev[count - 1].item()) == nxt
+    # caches: every entry against the restatement's, relative to the largest entry
+    assert np.max(np.abs(k_dev[:, :, :count].cpu().numpy() - kc[:, :, :count])) <= 5e-2 * np.max(np.abs(kc))
+    assert np.max(np.abs(v_dev[:, :, :count].cpu().numpy() - vc[:, :, :count])) <= 5e-2 * np.max(np.abs(vc))
+    # the decode loop continues from the prompt's caches (teacher-forced restatement)
+    token = nxt
+    for i in range(3):
+        dec.step()
+        want, _ = ref.step(model, token, count + i, kc, vc, act_bf16=bf)
+        got = logits_dev.cpu().numpy()
+        assert np.max(np.abs(got - want)) / np.max(np.abs(want)) <= 3e-2
+        token, p2, _ = dec.state()
+        assert p2 == count + i + 1
+    dec.backend.device_status()
+    with pytest.raises(api.Unsupported):
+        dec.prefill(prompt, 9)           # does not fit max_seq
+    with pytest.raises(api.InvalidArgument):
+        dec.prefill([cfg.vocab], 0)      # token out of range
+    dec.release()
 
 
 def test_generate_graph_replay_equals_stepwise():

@@ -314,6 +314,36 @@ def test_tensor_parallel_shards_reassemble(fmt):
     full.release()
 
 
+@pytest.mark.parametrize("fmt,k,world", [(Q.Q4_K, 25600, 8), (Q.Q6_K, 1280, 4), (Q.Q8_0, 96, 2)])
+def test_uneven_row_parallel_shards(fmt, k, world):
+    """K that does not divide by the ranks: 100 super-blocks over 8 ranks (13 / 12, the Qwen3-32B
+    down projection), 5 over 4, three Q8_0 blocks over 2. Every shard holds exactly the bytes the
+    host partition selects, and the shard products sum to the full product."""
+    from nn_b200 import tp
+    n = 48
+    w, sc = F.gen_weight(fmt, 70, n, k)
+    x = F.gen_activations(71, 1, k, bf16=True)
+    full = api.from_quantized(w, fmt, [n, k], sc)
+    xt = torch.from_numpy(x).to(DEV).to(torch.bfloat16)
+    parts = []
+    widths = set()
+    for rank in range(world):
+        sh = full.shard(1, rank, world)
+        ns, ks = tp.shard_shape(fmt, n, k, 1, world, rank)
+        assert sh.dims() == (ns, ks)
+        widths.add(ks)
+        ws, ss = tp.shard_bytes(fmt, w, sc, n, k, 1, rank, world)
+        ref = orc.dequantize(fmt, ws, ns * ks, ss).reshape(ns, ks)
+        assert np.array_equal(sh.dequantize().cpu().numpy().view(np.uint32), ref.view(np.uint32))
+        cols = tp.input_slice(k, 1, rank, world, fmt)
+        parts.append(api.quantized_linear(xt[:, cols].contiguous(), sh, None, out_dtype=torch.float32))
+        sh.release()
+    assert len(widths) == 2                      # the split really is uneven
+    y32, y64, mag = P.oracle_linear(fmt, w, sc, x, None, n, k)
+    P.assert_close(torch.stack(parts).sum(0).cpu().numpy(), y32, y64, mag)
+    full.release()
+
+
 @pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q6_K, Q.MXFP4_SPLIT])
 @pytest.mark.parametrize("axis", [0, 1])
 def test_device_shard_equals_host_partition(fmt, axis):
@@ -326,7 +356,7 @@ def test_device_shard_equals_host_partition(fmt, axis):
     for rank in range(world):
         sh = full.shard(axis, rank, world)
         ws, ss = tp.shard_bytes(fmt, w, sc, n, k, axis, rank, world)
-        ns, ks = tp.shard_shape(fmt, n, k, axis, world)
+        ns, ks = tp.shard_shape(fmt, n, k, axis, world, rank)
         assert sh.dims() == (ns, ks)
         ref = orc.dequantize(fmt, ws, ns * ks, ss).reshape(ns, ks)
         got = sh.dequantize().cpu().numpy()
