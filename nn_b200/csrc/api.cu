@@ -71,8 +71,11 @@ static nnq_status wait_host_stream(nnq_ctx *ctx) {
 }
 
 static nnq_status finish_weight(nnq_ctx *ctx, nnq_weight *w) {
-    // Build the tiled copy when a skinny kernel exists for this format and shape.
-    return build_tiled(ctx, w);
+    // Build the tiled copy when a skinny kernel exists for this format and shape, and make the
+    // bf16 scratch of the large-prefill GEMM large enough for this weight.
+    nnq_status s = build_tiled(ctx, w);
+    if (s == NNQ_OK && w->d_raw) s = dense_scratch_reserve(ctx, w->n, w->k);
+    return s;
 }
 
 }  // namespace nnq
@@ -158,6 +161,7 @@ void nnq_destroy(nnq_ctx *ctx) {
     cudaDeviceSynchronize();
     cudaFree(ctx->d_status);
     cudaFree(ctx->d_partials);
+    cudaFree(ctx->d_dense);
     cudaFree(ctx->d_moe);
     cudaFree(ctx->d_counters);
     cudaFree(ctx->d_batch_desc);
@@ -404,6 +408,8 @@ static nnq_status linear_dispatch(nnq_ctx *ctx, const nnq_weight *w, const void 
         return fail(ctx, NNQ_ERR_UNSUPPORTED, "tensor path needs K to be a multiple of 64 (K=%lld)", (long long)w->k);
     if (path == NNQ_PATH_TENSOR || (path == NNQ_PATH_AUTO && !skinny_ok && tc_ok && (m > 16 || (m >= 5 && x_dt == NNQ_BF16)))) {
         TcArgs a = {w->d_raw, w->d_scales, x_dev, bias_dev, y_dev, m, w->n, w->k, w->fmt, x_dt, y_dt};
+        // hundreds of rows per weight row: decode once to bf16, then the plain GEMM
+        if (gemm_dense_supported(ctx, w, m, x_dt)) return launch_gemm_dense(ctx, a, stream);
         return launch_gemm_tc(ctx, a, stream);
     }
     if ((path == NNQ_PATH_AUTO && skinny_ok) || path == NNQ_PATH_SKINNY) {

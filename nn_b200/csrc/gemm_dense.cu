@@ -1,0 +1,385 @@
+// Large-prefill product (M >= 256 tokens): decode the weight once to bf16, then a plain bf16 GEMM
+// on the 5th-generation tensor cores.
+//
+// With hundreds of activation rows per weight row the decode is a small part of the work: one pass
+// over the raw blocks writes bf16 [N, K] into a scratch buffer owned by the context (0.56 + 2 bytes
+// per weight at HBM speed; weights up to ~60 MB stay in L2 for the GEMM), and the GEMM main loop
+// then does nothing but move tiles and issue MMAs:
+//   * persistent CTAs (one per SM), output tiles of 128 x 256, k steps of 64 (one 128-byte swizzle
+//     row of bf16), a 4-stage ring of (16 KB activation tile + 32 KB weight tile);
+//   * warp 0: one thread issues the TMA loads of both tiles (cp.async.bulk.tensor.2d, 128-byte
+//     swizzle, zero fill beyond M / N) onto the stage's "full" barrier;
+//   * warp 1: one thread issues tcgen05.mma (M 128, N 256, K 16, bf16 x bf16 -> f32) into one of
+//     two 256-column accumulators in tensor memory and commits the stage's "empty" barrier;
+//   * warps 2..5: epilogue -- tcgen05.ld of the finished accumulator (each warp its quarter of
+//     the 128 lanes), bias, conversion, stores -- while the MMA warp already fills the other
+//     accumulator with the next tile.
+// Tiles are numbered m-fastest, so the CTAs running at one time share a few weight tiles and the
+// activation matrix stays in L2. Weights and activations are bf16: the 1e-2 tolerance class.
+// Every barrier wait is bounded; a wait that runs out sets the context's status word, every role
+// leaves its loop and the tensor memory is freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <string.h>
+
+#include "decode.cuh"
+#include "gemm_tc.h"
+#include "sync.cuh"
+
+namespace nnq {
+
+// ---------------------------------------------------------------------------------
+// raw blocks -> bf16 [N, K]
+// ---------------------------------------------------------------------------------
+
+constexpr int kDbThreads = 128;
+
+template <int FMT>
+__global__ void __launch_bounds__(kDbThreads)
+dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__ scales, int64_t nchunks,
+                    uint4 *__restrict__ dst) {
+    __shared__ uint4 tile[kDbThreads * 4 + 4];
+    for (int64_t base = (int64_t)blockIdx.x * kDbThreads; base < nchunks; base += (int64_t)gridDim.x * kDbThreads) {
+        const int64_t c = base + threadIdx.x;
+        if (c < nchunks) {
+            float o[32];
+            Decode<FMT>::chunk(src, scales, c, o);   // the bit-exact decode, then round to nearest even
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t p[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(o[8 * j + 2 * i], o[8 * j + 2 * i + 1]);
+                    p[i] = *reinterpret_cast<uint32_t *>(&v);
+                }
+                tile[threadIdx.x * 4 + j] = make_uint4(p[0], p[1], p[2], p[3]);
+            }
+        }
+        __syncthreads();
+        const int64_t remaining = nchunks - base;
+        const int live = remaining < kDbThreads ? (int)remaining : kDbThreads;
+        uint4 *out = dst + base * 4;
+        for (int idx = threadIdx.x; idx < live * 4; idx += kDbThreads) out[idx] = tile[idx];
+        __syncthreads();
+    }
+}
+
+template <int FMT>
+static cudaError_t launch_dequant_bf16(const uint8_t *src, const uint8_t *scales, int64_t nchunks, void *dst, int sm_count,
+                                       cudaStream_t stream) {
+    const int64_t want = (nchunks + kDbThreads - 1) / kDbThreads;
+    const int64_t cap = (int64_t)sm_count * 16;
+    int grid = (int)(want < cap ? want : cap);
+    if (grid < 1) grid = 1;
+    dequant_bf16_kernel<FMT><<<grid, kDbThreads, 0, stream>>>(src, scales, nchunks, reinterpret_cast<uint4 *>(dst));
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------
+// bf16 GEMM: y[M, N] = x[M, K] * Wd[N, K]^T (+ bias)
+// ---------------------------------------------------------------------------------
+
+constexpr int kDgBM = 128, kDgBN = 256, kDgBK = 64, kDgStages = 4;
+constexpr int kDgABytes = kDgBM * 128, kDgBBytes = kDgBN * 128;
+constexpr int kDgStageBytes = kDgABytes + kDgBBytes;
+constexpr int kDgThreads = 192;
+
+__device__ __forceinline__ void dg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void dg_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t dg_smem_desc(uint32_t addr) {
+    const uint32_t lo = ((addr >> 4) & 0x3FFFu) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void dg_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void dg_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void dg_tma_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void dg_tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kDgThreads, 1)
+gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+                  const float *__restrict__ bias, void *__restrict__ y, int M, int N, int K, int y_dt, int *status) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * kDgStages + 4];   // full[4], empty[4], acc_full[2], acc_empty[2]
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * kDgStages;
+    const uint32_t accf_s = empty_s + 8 * kDgStages, acce_s = accf_s + 16;
+    const int m_tiles = (M + kDgBM - 1) / kDgBM, n_tiles = (N + kDgBN - 1) / kDgBN;
+    const int tiles = m_tiles * n_tiles;
+    const int nkb = K / kDgBK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kDgStages; s++) {
+            mbar_init(full_s + 8 * s, 1);
+            mbar_init(empty_s + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(accf_s + 8 * a, 1);
+            mbar_init(acce_s + 8 * a, 4);
+        }
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    dg_fence_before();
+    __syncthreads();
+    dg_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int slot = 0;
+            uint32_t phase = 0;
+            long long filled = 0;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+                const int m0 = (t % m_tiles) * kDgBM, n0 = (t / m_tiles) * kDgBN;
+                for (int kb = 0; kb < nkb; kb++) {
+                    if (filled >= kDgStages && !mbar_wait_fast(empty_s + 8 * slot, phase ^ 1u)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_s = smem_u32(smem + (size_t)slot * kDgStageBytes);
+                    mbar_expect_tx(full_s + 8 * slot, kDgStageBytes);
+                    dg_tma_2d(a_s, &xmap, kb * kDgBK, m0, full_s + 8 * slot);
+                    dg_tma_2d(a_s + kDgABytes, &wmap, kb * kDgBK, n0, full_s + 8 * slot);
+                    filled++;
+                    if (++slot == kDgStages) {
+                        slot = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // f32 accumulate, bf16 x bf16, both K-major, N = 256, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+            int slot = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, it++) {
+                const int a = it & 1;
+                // the epilogue has read this accumulator's previous tile
+                if (it >= 2 && !mbar_wait_fast(acce_s + 8 * a, (uint32_t)(((it >> 1) - 1) & 1))) {
+                    ok = false;
+                    break;
+                }
+                dg_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(a * kDgBN);
+                for (int kb = 0; kb < nkb; kb++) {
+                    if (!mbar_wait_fast(full_s + 8 * slot, phase)) {
+                        ok = false;
+                        break;
+                    }
+                    dg_fence_after();
+                    const uint32_t a_s = smem_u32(smem + (size_t)slot * kDgStageBytes);
+                    const uint64_t da = dg_smem_desc(a_s), db = dg_smem_desc(a_s + kDgABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) dg_mma(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    dg_commit(empty_s + 8 * slot);
+                    if (++slot == kDgStages) {
+                        slot = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) dg_commit(accf_s + 8 * a);
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;   // the quarter of the 128 TMEM lanes this warp may read
+        int it = 0;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, it++) {
+            const int a = it & 1;
+            const int m0 = (t % m_tiles) * kDgBM, n0 = (t / m_tiles) * kDgBN;
+            if (!mbar_wait_fast(accf_s + 8 * a, (uint32_t)((it >> 1) & 1))) {
+                ok = false;
+                break;
+            }
+            dg_fence_after();
+            const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int cc = 0; cc < kDgBN / 32; cc++) {
+                uint32_t v[32];
+                dg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kDgBN + cc * 32), v);
+                const int col0 = n0 + cc * 32;
+                if (row < M && col0 < N) {
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i++) f[i] = __uint_as_float(v[i]) + (bias && col0 + i < N ? __ldg(bias + col0 + i) : 0.0f);
+                    if (col0 + 32 <= N && (N & 7) == 0) {
+                        if (y_dt == NNQ_F32) {
+                            float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(y) + (size_t)row * N + col0);
+#pragma unroll
+                            for (int i = 0; i < 8; i++) dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+                        } else {
+                            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(y) + (size_t)row * N + col0);
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                uint32_t p[4];
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(f[8 * i + 2 * j], f[8 * i + 2 * j + 1]);
+                                    p[j] = *reinterpret_cast<uint32_t *>(&b2);
+                                }
+                                dst[i] = make_uint4(p[0], p[1], p[2], p[3]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            if (col0 + i < N) {
+                                if (y_dt == NNQ_F32) reinterpret_cast<float *>(y)[(size_t)row * N + col0 + i] = f[i];
+                                else reinterpret_cast<__nv_bfloat16 *>(y)[(size_t)row * N + col0 + i] = __float2bfloat16_rn(f[i]);
+                            }
+                        }
+                    }
+                }
+            }
+            dg_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_s + 8 * a);
+        }
+    }
+    if (!ok) {
+        abort_s = 1;
+        atomicExch(status, 1);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        // with an aborted CTA, MMAs may still be in flight: give the last accumulator a bounded chance
+        if (abort_s) {
+            mbar_wait(accf_s, 0);
+            mbar_wait(accf_s + 8, 0);
+        }
+        dg_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+        cudaGetLastError();
+    }
+    return fn;
+}
+
+// bf16 [rows, k] row-major -> boxes of 64 x box_rows elements, 128-byte swizzle, zero fill outside
+static bool make_map(const void *base, int64_t rows, int64_t k, int box_rows, CUtensorMap *map) {
+    EncodeFn fn = encode_fn();
+    if (!fn || ((uintptr_t)base & 15u) || (k * 2) % 16) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kDgBK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool gemm_dense_supported(const nnq_ctx *ctx, const nnq_weight *w, int64_t m, int x_dt) {
+    return w && w->d_raw && ctx->d_dense && x_dt == NNQ_BF16 && m >= 256 && w->k >= kDgBK && w->k % kDgBK == 0 && w->n >= 1 &&
+           (size_t)w->n * (size_t)w->k * 2 <= ctx->dense_bytes && m < (1ll << 31) && w->n < (1ll << 31) && encode_fn() != nullptr;
+}
+
+nnq_status dense_scratch_reserve(nnq_ctx *ctx, int64_t n, int64_t k) {
+    if (k < kDgBK || k % kDgBK) return NNQ_OK;
+    const size_t need = (size_t)n * (size_t)k * 2;
+    if (need <= ctx->dense_bytes) return NNQ_OK;
+    cudaFree(ctx->d_dense);   // load time: synchronising here is fine
+    ctx->d_dense = nullptr;
+    ctx->dense_bytes = 0;
+    nnq_status s = check_cuda(ctx, cudaMalloc(&ctx->d_dense, need), "cudaMalloc bf16 weight scratch");
+    if (s != NNQ_OK) return s;
+    ctx->dense_bytes = need;
+    return NNQ_OK;
+}
+
+nnq_status launch_gemm_dense(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
+    Geometry g = geometry(a.fmt);
+    const int64_t nchunks = a.n * (a.k / g.elems) * (g.elems / 32);
+    cudaError_t e;
+    switch (a.fmt) {
+#define NNQ_DB(F) case F: e = launch_dequant_bf16<F>(a.w, a.scales, nchunks, ctx->d_dense, ctx->sm_count, stream); break
+        NNQ_DB(NNQ_Q4_0); NNQ_DB(NNQ_Q4_1); NNQ_DB(NNQ_Q8_0); NNQ_DB(NNQ_Q4_K); NNQ_DB(NNQ_Q4_K_GGML); NNQ_DB(NNQ_Q6_K);
+        NNQ_DB(NNQ_MXFP4_CORE); NNQ_DB(NNQ_MXFP4_SPLIT); NNQ_DB(NNQ_MXFP4_GPTOSS); NNQ_DB(NNQ_Q5_0); NNQ_DB(NNQ_Q5_1);
+        NNQ_DB(NNQ_Q2_K); NNQ_DB(NNQ_Q3_K); NNQ_DB(NNQ_Q5_K);
+#undef NNQ_DB
+        default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
+    }
+    ctx->launches++;
+    nnq_status s = check_cuda(ctx, e, "bf16 decode launch");
+    if (s != NNQ_OK) return s;
+    CUtensorMap xmap, wmap;
+    memset(&xmap, 0, sizeof(xmap));
+    memset(&wmap, 0, sizeof(wmap));
+    if (!make_map(a.x, a.m, a.k, kDgBM, &xmap) || !make_map(ctx->d_dense, a.n, a.k, kDgBN, &wmap))
+        return fail(ctx, NNQ_ERR_DISPATCH_FAILED, "tensor map creation failed");
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int smem_bytes = kDgStages * kDgStageBytes + 1024;
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        s = check_cuda(ctx, cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes), "GEMM attribute");
+        if (s != NNQ_OK) return s;
+        configured[dev] = true;
+    }
+    const int64_t tiles = ((a.m + kDgBM - 1) / kDgBM) * ((a.n + kDgBN - 1) / kDgBN);
+    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    gemm_dense_kernel<<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "bf16 GEMM launch");
+}
+
+}  // namespace nnq

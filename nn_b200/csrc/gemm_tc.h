@@ -36,4 +36,10 @@ nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &a, cudaStream
 bool gemm_tc_supported(const nnq_weight *w, int64_t m);
 nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream);
 
+// Large prefill (M >= 256, bf16 activations, K a multiple of 64): decode the weight to bf16 in the
+// context's scratch, then a persistent TMA + tcgen05 GEMM (gemm_dense.cu).
+bool gemm_dense_supported(const nnq_ctx *ctx, const nnq_weight *w, int64_t m, int x_dt);
+nnq_status dense_scratch_reserve(nnq_ctx *ctx, int64_t n, int64_t k);
+nnq_status launch_gemm_dense(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream);
+
 }  // namespace nnq

@@ -50,6 +50,10 @@ struct nnq_ctx {
     size_t partials_bytes;
     unsigned int *d_counters;
     size_t counters_count;
+    // bf16 copy of one weight at a time for the large-prefill GEMM: sized for the largest weight
+    // created on this context (at weight creation, never inside a product call)
+    void *d_dense;
+    size_t dense_bytes;
     // scratch of the mixture-of-experts block (routing tables and intermediate activations)
     uint8_t *d_moe;
     size_t moe_bytes;
