@@ -123,9 +123,16 @@ __device__ __forceinline__ void dg_tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Grouped mode (expert products): the rows of x are sorted by expert (offsets[e] .. offsets[e+1]
+// on the device), expert e multiplies its rows with rows [e * N, (e + 1) * N) of the decoded
+// weights and adds bias + e * N. Row tiles are numbered expert by expert; rows of the next expert
+// inside a tile are computed but not stored. offsets == NULL: a plain product.
+constexpr int kDgMaxGroups = 64;
+
 __global__ void __launch_bounds__(kDgThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
-                  const float *__restrict__ bias, void *__restrict__ y, int M, int N, int K, int y_dt, int *status) {
+                  const float *__restrict__ bias, void *__restrict__ y, int M, int N, int K, int y_dt, int *status,
+                  const int *__restrict__ offsets, int groups) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t bars[2 * kDgStages + 4];   // full[4], empty[4], acc_full[2], acc_empty[2]
@@ -135,9 +142,38 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * kDgStages;
     const uint32_t accf_s = empty_s + 8 * kDgStages, acce_s = accf_s + 16;
-    const int m_tiles = (M + kDgBM - 1) / kDgBM, n_tiles = (N + kDgBN - 1) / kDgBN;
+    __shared__ int tile_begin[kDgMaxGroups + 1], row_begin[kDgMaxGroups + 1];
+    if (tid == 0) {
+        if (offsets) {
+            int acc = 0;
+            for (int e = 0; e < groups; e++) {
+                tile_begin[e] = acc;
+                row_begin[e] = offsets[e];
+                acc += (offsets[e + 1] - offsets[e] + kDgBM - 1) / kDgBM;
+            }
+            tile_begin[groups] = acc;
+            row_begin[groups] = offsets[groups];
+        } else {
+            tile_begin[0] = 0;
+            tile_begin[1] = (M + kDgBM - 1) / kDgBM;
+            row_begin[0] = 0;
+            row_begin[1] = M;
+        }
+    }
+    __syncthreads();
+    const int ngroups = offsets ? groups : 1;
+    const int m_tiles = tile_begin[ngroups], n_tiles = (N + kDgBN - 1) / kDgBN;
     const int tiles = m_tiles * n_tiles;
     const int nkb = K / kDgBK;
+    // tile t -> (group, first row, end of the group's rows, first weight row)
+    auto locate = [&](int t, int &e, int &m0, int &m_end, int &n0) {
+        const int mt = t % m_tiles;
+        e = 0;
+        while (e + 1 < ngroups && mt >= tile_begin[e + 1]) e++;
+        m0 = row_begin[e] + (mt - tile_begin[e]) * kDgBM;
+        m_end = row_begin[e + 1];
+        n0 = (t / m_tiles) * kDgBN;
+    };
 
     if (tid == 0) {
         for (int s = 0; s < kDgStages; s++) {
@@ -168,7 +204,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
             uint32_t phase = 0;
             long long filled = 0;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                const int m0 = (t % m_tiles) * kDgBM, n0 = (t / m_tiles) * kDgBN;
+                int e, m0, m_end, n0;
+                locate(t, e, m0, m_end, n0);
+                const int w0 = e * N + n0;   // weight rows of this group in the decoded [groups * N, K] matrix
                 for (int kb = 0; kb < nkb; kb++) {
                     if (filled >= kDgStages && !mbar_wait_fast(empty_s + 8 * slot, phase ^ 1u)) {
                         ok = false;
@@ -177,7 +215,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
                     const uint32_t a_s = smem_u32(smem + (size_t)slot * kDgStageBytes);
                     mbar_expect_tx(full_s + 8 * slot, kDgStageBytes);
                     dg_tma_2d(a_s, &xmap, kb * kDgBK, m0, full_s + 8 * slot);
-                    dg_tma_2d(a_s + kDgABytes, &wmap, kb * kDgBK, n0, full_s + 8 * slot);
+                    dg_tma_2d(a_s + kDgABytes, &wmap, kb * kDgBK, w0, full_s + 8 * slot);
                     filled++;
                     if (++slot == kDgStages) {
                         slot = 0;
@@ -228,7 +266,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
         int it = 0;
         for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, it++) {
             const int a = it & 1;
-            const int m0 = (t % m_tiles) * kDgBM, n0 = (t / m_tiles) * kDgBN;
+            int e, m0, m_end, n0;
+            locate(t, e, m0, m_end, n0);
+            const float *gbias = bias ? bias + (size_t)e * N : nullptr;
             if (!mbar_wait_fast(accf_s + 8 * a, (uint32_t)((it >> 1) & 1))) {
                 ok = false;
                 break;
@@ -240,10 +280,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
                 uint32_t v[32];
                 dg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kDgBN + cc * 32), v);
                 const int col0 = n0 + cc * 32;
-                if (row < M && col0 < N) {
+                if (row < m_end && col0 < N) {
                     float f[32];
 #pragma unroll
-                    for (int i = 0; i < 32; i++) f[i] = __uint_as_float(v[i]) + (bias && col0 + i < N ? __ldg(bias + col0 + i) : 0.0f);
+                    for (int i = 0; i < 32; i++) f[i] = __uint_as_float(v[i]) + (gbias && col0 + i < N ? __ldg(gbias + col0 + i) : 0.0f);
                     if (col0 + 32 <= N && (N & 7) == 0) {
                         if (y_dt == NNQ_F32) {
                             float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(y) + (size_t)row * N + col0);
@@ -377,9 +417,52 @@ nnq_status launch_gemm_dense(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream)
     }
     const int64_t tiles = ((a.m + kDgBM - 1) / kDgBM) * ((a.n + kDgBN - 1) / kDgBN);
     const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-    gemm_dense_kernel<<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status);
+    gemm_dense_kernel<<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status,
+                                                                nullptr, 0);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "bf16 GEMM launch");
+}
+
+bool gemm_dense_grouped_supported(const nnq_ctx *ctx, const TcGroupArgs &g) {
+    return ctx->d_dense && g.k >= kDgBK && g.k % kDgBK == 0 && g.experts >= 1 && g.experts <= kDgMaxGroups && g.rows_upper >= 1 &&
+           (size_t)g.experts * (size_t)g.n * (size_t)g.k * 2 <= ctx->dense_bytes && g.rows_upper < (1ll << 30) &&
+           (int64_t)g.experts * g.n < (1ll << 31) && encode_fn() != nullptr;
+}
+
+nnq_status launch_gemm_dense_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStream_t stream) {
+    // the experts' raw blocks are one contiguous [experts, N, K] tensor: one decode launch
+    Geometry geo = geometry(g.fmt);
+    const int64_t nchunks = (int64_t)g.experts * g.n * (g.k / geo.elems) * (geo.elems / 32);
+    cudaError_t e;
+    switch (g.fmt) {
+#define NNQ_DB(F) case F: e = launch_dequant_bf16<F>(g.w, g.scales, nchunks, ctx->d_dense, ctx->sm_count, stream); break
+        NNQ_DB(NNQ_Q4_0); NNQ_DB(NNQ_Q4_1); NNQ_DB(NNQ_Q8_0); NNQ_DB(NNQ_Q4_K); NNQ_DB(NNQ_Q4_K_GGML); NNQ_DB(NNQ_Q6_K);
+        NNQ_DB(NNQ_MXFP4_CORE); NNQ_DB(NNQ_MXFP4_SPLIT); NNQ_DB(NNQ_MXFP4_GPTOSS); NNQ_DB(NNQ_Q5_0); NNQ_DB(NNQ_Q5_1);
+        NNQ_DB(NNQ_Q2_K); NNQ_DB(NNQ_Q3_K); NNQ_DB(NNQ_Q5_K);
+#undef NNQ_DB
+        default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", g.fmt);
+    }
+    ctx->launches++;
+    nnq_status s = check_cuda(ctx, e, "bf16 decode launch");
+    if (s != NNQ_OK) return s;
+    CUtensorMap xmap, wmap;
+    memset(&xmap, 0, sizeof(xmap));
+    memset(&wmap, 0, sizeof(wmap));
+    if (!make_map(g.x_bf16, g.rows_upper, g.k, kDgBM, &xmap) || !make_map(ctx->d_dense, (int64_t)g.experts * g.n, g.k, kDgBN, &wmap))
+        return fail(ctx, NNQ_ERR_DISPATCH_FAILED, "tensor map creation failed");
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int smem_bytes = kDgStages * kDgStageBytes + 1024;
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        s = check_cuda(ctx, cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes), "GEMM attribute");
+        if (s != NNQ_OK) return s;
+        configured[dev] = true;
+    }
+    gemm_dense_kernel<<<ctx->sm_count, kDgThreads, smem_bytes, stream>>>(xmap, wmap, g.bias, g.y, (int)g.rows_upper, (int)g.n, (int)g.k, NNQ_F32,
+                                                                         ctx->d_status, g.offsets, g.experts);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "grouped bf16 GEMM launch");
 }
 
 }  // namespace nnq

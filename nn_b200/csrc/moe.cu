@@ -498,7 +498,9 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
         Geometry g = geometry(m->fmt);
         const size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
         TcGroupArgs a = {d, sc, eb, es, first ? (const void *)s.xg : (const void *)s.hb, b, out, s.offset, E, rows, N, K, m->fmt};
-        launch_gemm_tc_grouped(ctx, a, st);
+        // hundreds of rows per expert: all local experts decoded to bf16 once, then the plain grouped GEMM
+        if (rows >= 256 * (int64_t)E && gemm_dense_grouped_supported(ctx, a)) launch_gemm_dense_grouped(ctx, a, st);
+        else launch_gemm_tc_grouped(ctx, a, st);
         return;
     }
     if (m->d_gu_tiled) {
@@ -740,6 +742,11 @@ nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, i
             m->gu_tile_stride = gs;
             m->dn_tile_stride = ds;
         }
+    }
+    // bf16 scratch of the prefill-sized expert products: all local experts of the larger tensor
+    if (s == NNQ_OK && layout == NNQ_MOE_NK && fmt < NNQ_Q5_0) {
+        s = dense_scratch_reserve(ctx, (int64_t)expert_count * 2 * inter, hidden);
+        if (s == NNQ_OK) s = dense_scratch_reserve(ctx, (int64_t)expert_count * hidden, inter);
     }
     if (s != NNQ_OK) {
         nnq_moe_destroy(m);
