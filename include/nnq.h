@@ -93,7 +93,14 @@ typedef enum nnq_format {
     NNQ_Q2_K = 11,
     NNQ_Q3_K = 12,
     NNQ_Q5_K = 13,
-    NNQ_FORMAT_COUNT = 14
+    /* unquantized weights behind the same entry points: f32 / bf16 [N, K] row-major, handled as
+     * "blocks" of 32 consecutive values (K a multiple of 32). The dense branch of Linear::forward
+     * (crates/nn-core/src/layers/core_layers.rs:118-143) and the unquantized experts of
+     * GptOssMoeBlock::forward / fused_moe_forward (crates/nn-gptoss/src/layers.rs:254,
+     * crates/nn-gptoss/src/moe_dispatch.rs:50). */
+    NNQ_F32_DENSE = 14,
+    NNQ_BF16_DENSE = 15,
+    NNQ_FORMAT_COUNT = 16
 } nnq_format;
 
 typedef enum nnq_dtype { NNQ_F32 = 0, NNQ_BF16 = 1 } nnq_dtype;

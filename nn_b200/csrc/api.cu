@@ -352,7 +352,7 @@ nnq_status nnq_dequantize_raw(nnq_ctx *ctx, nnq_format fmt, const void *src_dev,
     if (decoded) *decoded = nb * g.elems;
     if (nb == 0) return NNQ_OK;
     if (!src_dev || !dst_dev || (g.scale_bytes && !scales_dev)) return fail(ctx, NNQ_ERR_INVALID_ARG, "NULL buffer");
-    bool vec16 = fmt == NNQ_Q4_K || fmt == NNQ_Q4_K_GGML || fmt == NNQ_MXFP4_SPLIT || fmt == NNQ_MXFP4_GPTOSS || fmt == NNQ_Q5_K;
+    bool vec16 = fmt == NNQ_Q4_K || fmt == NNQ_Q4_K_GGML || fmt == NNQ_MXFP4_SPLIT || fmt == NNQ_MXFP4_GPTOSS || fmt == NNQ_Q5_K || fmt == NNQ_F32_DENSE || fmt == NNQ_BF16_DENSE;
     if (vec16 && ((uintptr_t)src_dev & 15u)) return fail(ctx, NNQ_ERR_INVALID_ARG, "source must be 16-byte aligned for this format");
     nnq_status s = set_device(ctx);
     if (s != NNQ_OK) return s;

@@ -337,4 +337,34 @@ struct Decode<NNQ_MXFP4_GPTOSS> {
     }
 };
 
+// unquantized weights: a "chunk" is 32 consecutive values
+template <>
+struct Decode<NNQ_F32_DENSE> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const float4 *p = reinterpret_cast<const float4 *>(w) + c * 8;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float4 v = __ldg(p + j);
+            o[4 * j] = v.x; o[4 * j + 1] = v.y; o[4 * j + 2] = v.z; o[4 * j + 3] = v.w;
+        }
+    }
+};
+
+template <>
+struct Decode<NNQ_BF16_DENSE> {
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(w) + c * 4;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint4 v = __ldg(p + j);
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                o[8 * j + 2 * i] = __uint_as_float(u[i] << 16);
+                o[8 * j + 2 * i + 1] = __uint_as_float(u[i] & 0xFFFF0000u);
+            }
+        }
+    }
+};
+
 }  // namespace nnq

@@ -63,6 +63,8 @@ nnq_status launch_dequant_raw(nnq_ctx *ctx, int fmt, const uint8_t *src, const u
         case NNQ_Q2_K: e = launch<NNQ_Q2_K>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
         case NNQ_Q3_K: e = launch<NNQ_Q3_K>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
         case NNQ_Q5_K: e = launch<NNQ_Q5_K>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
+        case NNQ_F32_DENSE: e = launch<NNQ_F32_DENSE>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
+        case NNQ_BF16_DENSE: e = launch<NNQ_BF16_DENSE>(src, scales, nchunks, dst, ctx->sm_count, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", fmt);
     }
     ctx->launches++;

@@ -395,6 +395,7 @@ nnq_status launch_gemm_dense(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream)
         NNQ_DB(NNQ_Q4_0); NNQ_DB(NNQ_Q4_1); NNQ_DB(NNQ_Q8_0); NNQ_DB(NNQ_Q4_K); NNQ_DB(NNQ_Q4_K_GGML); NNQ_DB(NNQ_Q6_K);
         NNQ_DB(NNQ_MXFP4_CORE); NNQ_DB(NNQ_MXFP4_SPLIT); NNQ_DB(NNQ_MXFP4_GPTOSS); NNQ_DB(NNQ_Q5_0); NNQ_DB(NNQ_Q5_1);
         NNQ_DB(NNQ_Q2_K); NNQ_DB(NNQ_Q3_K); NNQ_DB(NNQ_Q5_K);
+        NNQ_DB(NNQ_F32_DENSE); NNQ_DB(NNQ_BF16_DENSE);
 #undef NNQ_DB
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
     }
@@ -439,6 +440,7 @@ nnq_status launch_gemm_dense_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStr
         NNQ_DB(NNQ_Q4_0); NNQ_DB(NNQ_Q4_1); NNQ_DB(NNQ_Q8_0); NNQ_DB(NNQ_Q4_K); NNQ_DB(NNQ_Q4_K_GGML); NNQ_DB(NNQ_Q6_K);
         NNQ_DB(NNQ_MXFP4_CORE); NNQ_DB(NNQ_MXFP4_SPLIT); NNQ_DB(NNQ_MXFP4_GPTOSS); NNQ_DB(NNQ_Q5_0); NNQ_DB(NNQ_Q5_1);
         NNQ_DB(NNQ_Q2_K); NNQ_DB(NNQ_Q3_K); NNQ_DB(NNQ_Q5_K);
+        NNQ_DB(NNQ_F32_DENSE); NNQ_DB(NNQ_BF16_DENSE);
 #undef NNQ_DB
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", g.fmt);
     }

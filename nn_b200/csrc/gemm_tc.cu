@@ -476,6 +476,8 @@ nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStream
         case NNQ_MXFP4_CORE: e = launch_grouped_fmt<NNQ_MXFP4_CORE>(g, ctx->d_status, stream); break;
         case NNQ_MXFP4_SPLIT: e = launch_grouped_fmt<NNQ_MXFP4_SPLIT>(g, ctx->d_status, stream); break;
         case NNQ_MXFP4_GPTOSS: e = launch_grouped_fmt<NNQ_MXFP4_GPTOSS>(g, ctx->d_status, stream); break;
+        case NNQ_F32_DENSE: e = launch_grouped_fmt<NNQ_F32_DENSE>(g, ctx->d_status, stream); break;
+        case NNQ_BF16_DENSE: e = launch_grouped_fmt<NNQ_BF16_DENSE>(g, ctx->d_status, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", g.fmt);
     }
     ctx->launches++;
@@ -517,6 +519,8 @@ nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
         case NNQ_Q2_K: e = launch_fmt<NNQ_Q2_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
         case NNQ_Q3_K: e = launch_fmt<NNQ_Q3_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
         case NNQ_Q5_K: e = launch_fmt<NNQ_Q5_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_F32_DENSE: e = launch_fmt<NNQ_F32_DENSE>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_BF16_DENSE: e = launch_fmt<NNQ_BF16_DENSE>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
     }
     ctx->launches += ksplit > 1 ? 2 : 1;

@@ -118,6 +118,8 @@ nnq_status launch_linear_generic(nnq_ctx *ctx, const LinearArgs &a, cudaStream_t
         case NNQ_Q2_K: e = launch_fmt<NNQ_Q2_K>(a, stream); break;
         case NNQ_Q3_K: e = launch_fmt<NNQ_Q3_K>(a, stream); break;
         case NNQ_Q5_K: e = launch_fmt<NNQ_Q5_K>(a, stream); break;
+        case NNQ_F32_DENSE: e = launch_fmt<NNQ_F32_DENSE>(a, stream); break;
+        case NNQ_BF16_DENSE: e = launch_fmt<NNQ_BF16_DENSE>(a, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
     }
     ctx->launches++;

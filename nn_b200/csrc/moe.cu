@@ -430,7 +430,7 @@ static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 static bool moe_tensor_mode(const nnq_moe *m, int64_t T, int k, bool routed) {
     static const char *env = diag_env("NNQ_MOE_TENSOR");   // tuning aid: 0 keeps the token-column kernel
     if (env && atoi(env) == 0) return false;
-    return m->layout == NNQ_MOE_NK && m->fmt < NNQ_Q5_0 && m->hidden % 64 == 0 && m->inter % 64 == 0 &&
+    return m->layout == NNQ_MOE_NK && (m->fmt < NNQ_Q5_0 || m->fmt >= NNQ_F32_DENSE) && m->hidden % 64 == 0 && m->inter % 64 == 0 &&
            // 64 routed rows per expert on average: with the block's own router the T tokens spread over
            // all experts (the shards of one block agree), rows routed by the caller all go to local experts
            T * k >= 64 * (int64_t)(routed ? m->e_local : m->n_experts);
@@ -485,7 +485,7 @@ template <>
 struct DtypeOf<__nv_bfloat16> { static constexpr int value = NNQ_BF16; };
 
 template <typename XT>
-static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT *x, const int *rowtok, int top_k,
+static nnq_status launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT *x, const int *rowtok, int top_k,
                            const MoeScratch &s, float *out, int64_t rows, cudaStream_t st) {
     const int K = first ? m->hidden : m->inter;
     const int N = first ? 2 * m->inter : m->hidden;
@@ -499,23 +499,21 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
         const size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
         TcGroupArgs a = {d, sc, eb, es, first ? (const void *)s.xg : (const void *)s.hb, b, out, s.offset, E, rows, N, K, m->fmt};
         // hundreds of rows per expert: all local experts decoded to bf16 once, then the plain grouped GEMM
-        if (rows >= 256 * (int64_t)E && gemm_dense_grouped_supported(ctx, a)) launch_gemm_dense_grouped(ctx, a, st);
-        else launch_gemm_tc_grouped(ctx, a, st);
-        return;
+        if (rows >= 256 * (int64_t)E && gemm_dense_grouped_supported(ctx, a)) return launch_gemm_dense_grouped(ctx, a, st);
+        return launch_gemm_tc_grouped(ctx, a, st);
     }
     if (m->d_gu_tiled) {
         GroupedArgs a = {first ? m->d_gu_tiled : m->d_dn_tiled, first ? m->gu_tile_stride : m->dn_tile_stride, b, x,
                          DtypeOf<XT>::value, rowtok, s.offset, out, E, top_k, N, K, m->fmt, rows,
                          m->layout == NNQ_MOE_KN_GPTOSS ? 1 : 0};
-        launch_grouped(ctx, a, st);
-        return;
+        return launch_grouped(ctx, a, st);
     }
     ctx->launches++;   // one of the row kernels below
     if (m->layout == NNQ_MOE_KN_GPTOSS) {
         dim3 grid((N + 1023) / 1024, E, kMoeKnSplit);
         moe_kn_gptoss_kernel<XT><<<grid, 128, 0, st>>>(d, sc, b, x, rowtok, top_k, s.offset, out,
                                                         first ? s.gu_stride : s.o_stride, K, N);
-        return;
+        return NNQ_OK;
     }
     Geometry g = geometry(m->fmt);
     size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
@@ -525,9 +523,11 @@ static void launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT 
         NNQ_NK(NNQ_Q4_0); NNQ_NK(NNQ_Q4_1); NNQ_NK(NNQ_Q8_0); NNQ_NK(NNQ_Q4_K); NNQ_NK(NNQ_Q4_K_GGML);
         NNQ_NK(NNQ_Q6_K); NNQ_NK(NNQ_MXFP4_CORE); NNQ_NK(NNQ_MXFP4_SPLIT); NNQ_NK(NNQ_MXFP4_GPTOSS);
         NNQ_NK(NNQ_Q5_0); NNQ_NK(NNQ_Q5_1); NNQ_NK(NNQ_Q2_K); NNQ_NK(NNQ_Q3_K); NNQ_NK(NNQ_Q5_K);
-        default: break;
+        NNQ_NK(NNQ_F32_DENSE); NNQ_NK(NNQ_BF16_DENSE);
+        default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", (int)m->fmt);
     }
 #undef NNQ_NK
+    return NNQ_OK;
 }
 
 // the router keeps one token's activations in shared memory: allow more than the default 48 KB
@@ -606,10 +606,12 @@ static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, 
         moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, k, s.offset, m->e_local, m->hidden, s.xg);
         ctx->launches++;
     }
-    launch_product<XT>(ctx, m, true, x, s.rowtok, k, s, s.gu, total, st);
+    nnq_status prc = launch_product<XT>(ctx, m, true, x, s.rowtok, k, s, s.gu, total, st);
+    if (prc != NNQ_OK) return prc;
     int64_t hi = (int64_t)total * m->inter;
     launch_pdl(moe_swiglu_kernel, dim3((unsigned)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
-    launch_product<float>(ctx, m, false, s.h, nullptr, k, s, s.o, total, st);
+    prc = launch_product<float>(ctx, m, false, s.h, nullptr, k, s, s.o, total, st);
+    if (prc != NNQ_OK) return prc;
     launch_pdl(moe_combine_kernel, dim3((unsigned)T, T < 1024 ? 4 : 1), dim3(256), st, s.o, idx, wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
     ctx->launches += 3;   // grouping, SwiGLU, combine (the router and the products count themselves)
     return check_cuda(ctx, cudaGetLastError(), "MoE launch");
@@ -744,7 +746,7 @@ nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, i
         }
     }
     // bf16 scratch of the prefill-sized expert products: all local experts of the larger tensor
-    if (s == NNQ_OK && layout == NNQ_MOE_NK && fmt < NNQ_Q5_0) {
+    if (s == NNQ_OK && layout == NNQ_MOE_NK && (fmt < NNQ_Q5_0 || fmt >= NNQ_F32_DENSE)) {
         s = dense_scratch_reserve(ctx, (int64_t)expert_count * 2 * inter, hidden);
         if (s == NNQ_OK) s = dense_scratch_reserve(ctx, (int64_t)expert_count * hidden, inter);
     }

@@ -31,6 +31,8 @@ __host__ __device__ inline Geometry geometry(int fmt) {
         case NNQ_Q2_K: return {256, 84, 0};
         case NNQ_Q3_K: return {256, 110, 0};
         case NNQ_Q5_K: return {256, 176, 0};
+        case NNQ_F32_DENSE: return {32, 128, 0};
+        case NNQ_BF16_DENSE: return {32, 64, 0};
         default: return {0, 0, 0};
     }
 }

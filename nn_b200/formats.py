@@ -37,6 +37,8 @@ class QuantFormat(enum.IntEnum):
     Q2_K = 11
     Q3_K = 12
     Q5_K = 13
+    F32_DENSE = 14    # unquantized weights behind the same entry points: "blocks" of 32 values
+    BF16_DENSE = 15
 
 
 @dataclass(frozen=True)
@@ -61,6 +63,8 @@ GEOMETRY = {
     QuantFormat.Q2_K: BlockGeometry(256, 84, 0),
     QuantFormat.Q3_K: BlockGeometry(256, 110, 0),
     QuantFormat.Q5_K: BlockGeometry(256, 176, 0),
+    QuantFormat.F32_DENSE: BlockGeometry(32, 128, 0),
+    QuantFormat.BF16_DENSE: BlockGeometry(32, 64, 0),
 }
 
 
@@ -233,6 +237,12 @@ def mxfp4_core_bytes(codes: np.ndarray, exps: np.ndarray) -> np.ndarray:
 def gen_weight(fmt: QuantFormat, seed: int, n: int, k: int):
     """(main bytes, scale bytes or None) for any format, benchmark distributions."""
     fmt = QuantFormat(fmt)
+    if fmt in (QuantFormat.F32_DENSE, QuantFormat.BF16_DENSE):
+        # unquantized weights ~ N(0, 0.02), the distribution the benchmark configures for dense parts
+        v = (Stream(seed).normal(n * k) * 0.02).astype(np.float32)
+        if fmt == QuantFormat.F32_DENSE:
+            return v.view(np.uint8).copy(), None
+        return to_bf16_bits(v).astype(np.uint16).view(np.uint8).copy(), None
     if fmt == QuantFormat.Q8_0:
         return gen_q8_0(seed, n, k), None
     if fmt == QuantFormat.Q4_0:

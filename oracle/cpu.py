@@ -53,6 +53,17 @@ def lib():
         _lib.orc_int8_quantize_per_channel.restype = ctypes.c_int
         _lib.orc_int8_quantize_per_channel.argtypes = [_f32p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, _u8p, _f32p, _i32p]
         _lib.orc_int8_dequantize_per_channel.argtypes = [_u8p, _f32p, _i32p, ctypes.c_size_t, ctypes.c_size_t, _f32p]
+        _u32p = ctypes.POINTER(ctypes.c_uint32)
+        sz = ctypes.c_size_t
+        _lib.orc_group_quantize.restype = ctypes.c_int
+        _lib.orc_group_quantize.argtypes = [_f32p, sz, sz, ctypes.c_int, sz, ctypes.c_int, _u8p, _f32p, _i32p]
+        _lib.orc_group_dequantize.argtypes = [_u8p, _f32p, _i32p, sz, sz, ctypes.c_int, sz, _f32p]
+        _lib.orc_gptq_unpack_qweight.argtypes = [_u32p, sz, sz, _f32p]
+        _lib.orc_gptq_unpack_qzeros.argtypes = [_u32p, sz, sz, _f32p]
+        _lib.orc_gptq_dequantize.restype = ctypes.c_int
+        _lib.orc_gptq_dequantize.argtypes = [_f32p, _f32p, _f32p, sz, sz, sz, sz, _f32p]
+        _lib.orc_gptq_load_weight.restype = ctypes.c_int
+        _lib.orc_gptq_load_weight.argtypes = [_u32p, _f32p, _u32p, sz, sz, sz, sz, _f32p]
         _lib.orc_mxfp4_core_scale.restype = ctypes.c_float
         _lib.orc_mxfp4_core_scale.argtypes = [ctypes.c_uint8]
         _lib.orc_mxfp4_gptoss_scale.restype = ctypes.c_float
@@ -149,6 +160,82 @@ def int8_dequantize_per_channel(q, scale, zp) -> np.ndarray:
     return out
 
 
+class ShapeMismatch(ValueError):
+    """The reference's TensorError::ShapeMismatch / DataLengthMismatch."""
+
+
+def group_quantize(w, bits: int, group_size: int, symmetric: bool = True):
+    """quantize_per_group: (packed codes uint8, scale f32 [n * groups], zero_point i32 [n * groups])."""
+    w = np.ascontiguousarray(w, np.float32)
+    n, k = w.shape
+    gpr = k // group_size if group_size else 0
+    q = np.zeros(n * k if bits == 8 else (n * k + 1) // 2, np.uint8)
+    sc, zp = np.zeros(n * gpr, np.float32), np.zeros(n * gpr, np.int32)
+    rc = lib().orc_group_quantize(w.ctypes.data_as(_f32p), n, k, int(bits), int(group_size), int(bool(symmetric)),
+                                  q.ctypes.data_as(_u8p), sc.ctypes.data_as(_f32p), zp.ctypes.data_as(_i32p))
+    if rc in (-1, -2):
+        raise ValueOutOfRange("non-finite weight value" if rc == -1 else "group_size must be > 0")
+    if rc == -3:
+        raise ShapeMismatch("group_size does not divide in_features")
+    return q, sc, zp
+
+
+def group_dequantize(q, scale, zp, n: int, k: int, bits: int, group_size: int) -> np.ndarray:
+    q = np.ascontiguousarray(q, np.uint8)
+    scale = np.ascontiguousarray(scale, np.float32)
+    zp = np.ascontiguousarray(zp, np.int32)
+    out = np.zeros((n, k), np.float32)
+    lib().orc_group_dequantize(q.ctypes.data_as(_u8p), scale.ctypes.data_as(_f32p), zp.ctypes.data_as(_i32p), n, k,
+                               int(bits), int(group_size), out.ctypes.data_as(_f32p))
+    return out
+
+
+def _u32(a):
+    a = np.ascontiguousarray(a, np.uint32)
+    return a, a.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32))
+
+
+def gptq_unpack_qweight(packed) -> np.ndarray:
+    packed, pp = _u32(packed)
+    rows, cols = packed.shape
+    out = np.zeros((rows * 8, cols), np.float32)
+    lib().orc_gptq_unpack_qweight(pp, rows, cols, out.ctypes.data_as(_f32p))
+    return out
+
+
+def gptq_unpack_qzeros(packed) -> np.ndarray:
+    packed, pp = _u32(packed)
+    groups, cols = packed.shape
+    out = np.zeros((groups, cols * 8), np.float32)
+    lib().orc_gptq_unpack_qzeros(pp, groups, cols, out.ctypes.data_as(_f32p))
+    return out
+
+
+def gptq_dequantize(q, scales, zeros, group_size: int) -> np.ndarray:
+    q, qp = _f32(q)
+    scales, sp = _f32(scales)
+    zeros, zp = _f32(zeros)
+    k, n = q.shape
+    if scales.shape[1] != n or zeros.shape != scales.shape:
+        raise ShapeMismatch("scales / zeros shape")
+    out = np.zeros((k, n), np.float32)
+    if lib().orc_gptq_dequantize(qp, sp, zp, k, n, scales.shape[0], int(group_size), out.ctypes.data_as(_f32p)) != 0:
+        raise ShapeMismatch("group count")
+    return out
+
+
+def gptq_load_weight(qweight, scales, qzeros, group_size: int) -> np.ndarray:
+    """f32 [n, k] weight of load_gptq_linear / load_awq_linear."""
+    qweight, qp = _u32(qweight)
+    scales, sp = _f32(scales)
+    qzeros, zp = _u32(qzeros)
+    k, n = qweight.shape[0] * 8, qweight.shape[1]
+    out = np.zeros((n, k), np.float32)
+    if lib().orc_gptq_load_weight(qp, sp, zp, n, k, scales.shape[0], int(group_size), out.ctypes.data_as(_f32p)) != 0:
+        raise ShapeMismatch("group count")
+    return out
+
+
 def mxfp4_core_scale(e: int) -> float:
     return float(lib().orc_mxfp4_core_scale(int(e)))
 
@@ -169,6 +256,10 @@ def dequantize(fmt: int, data, num_elements: int, scales=None) -> np.ndarray:
     """Dequantize raw blocks of any supported format to f32 (flat)."""
     fmt = int(fmt)
     data, dp = _u8(data)
+    if fmt == 14:     # unquantized f32: the bytes are the values
+        return data[: num_elements * 4].view(np.float32).copy()
+    if fmt == 15:     # unquantized bf16: exact widening
+        return (data[: num_elements * 2].view(np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
     if fmt in _DEQ:
         out = np.zeros(num_elements, np.float32)
         n = getattr(lib(), _DEQ[fmt])(dp, data.size, num_elements, out.ctypes.data_as(_f32p))

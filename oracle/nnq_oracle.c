@@ -899,6 +899,132 @@ ORC_API void orc_int8_dequantize_per_channel(const uint8_t *q, const float *scal
 }
 
 /* ------------------------------------------------------------------------- */
+/* INT4 / INT8 per-group weights, GPTQ / AWQ packed weights                   */
+/* ------------------------------------------------------------------------- */
+
+/* unpack_element (crates/nn-core/src/layers/quantized/weight_quant.rs:415-433): element `index`
+ * of the flat packing; int4 codes sit two per byte (even index = low nibble) in two's complement. */
+static int8_t group_code_at(const uint8_t *data, size_t index, int bits) {
+    if (bits == 8) return (int8_t)data[index];
+    uint8_t nib = (index % 2 == 0) ? (uint8_t)(data[index / 2] & 0x0F) : (uint8_t)(data[index / 2] >> 4);
+    return (nib & 0x08) ? (int8_t)(nib | 0xF0) : (int8_t)nib;
+}
+
+/* quantize_per_group (weight_quant.rs:232-328) with compute_group_params (weight_quant.rs:334-365).
+ * Symmetric: scale = max|w| / qmax (7 or 127), zero point 0. Asymmetric: scale = (max - min) /
+ * (15 or 255), zero point = round(qmin - min / scale) with qmin = -8 or -128. Codes
+ * clamp(round(w / scale + zp), qmin, qmax'), qmax' = 7 or 127, 0 where scale == 0; int8 codes one
+ * per byte, int4 codes two per byte over the flat [n * k] index (a last odd element leaves the high
+ * nibble 0). q holds n * k bytes (int8) or (n * k + 1) / 2 (int4). Returns 0; -1 for a non-finite
+ * weight and -2 for group_size == 0 (both ValueOutOfRange); -3 when group_size does not divide k
+ * (ShapeMismatch). */
+ORC_API int orc_group_quantize(const float *w, size_t n, size_t k, int bits, size_t group_size, int symmetric,
+                               uint8_t *q, float *scale, int32_t *zp) {
+    if (group_size == 0) return -2;
+    if (k % group_size != 0) return -3;
+    for (size_t i = 0; i < n * k; i++)
+        if (!isfinite(w[i])) return -1;
+    const float sym_max = bits == 4 ? 7.0f : 127.0f, levels = bits == 4 ? 15.0f : 255.0f;
+    const float lo = bits == 4 ? -8.0f : -128.0f, hi = bits == 4 ? 7.0f : 127.0f;
+    const size_t gpr = k / group_size;
+    if (bits == 4) memset(q, 0, (n * k + 1) / 2);
+    for (size_t r = 0; r < n; r++)
+        for (size_t g = 0; g < gpr; g++) {
+            const float *grp = w + r * k + g * group_size;
+            float sc = 0.0f;
+            int32_t z = 0;
+            if (symmetric) {
+                float abs_max = 0.0f;
+                for (size_t i = 0; i < group_size; i++) abs_max = fold_max(abs_max, fabsf(grp[i]));
+                if (abs_max != 0.0f) sc = abs_max / sym_max;
+            } else {
+                float mn = INFINITY, mx = -INFINITY;
+                for (size_t i = 0; i < group_size; i++) { mn = fold_min(mn, grp[i]); mx = fold_max(mx, grp[i]); }
+                float range = mx - mn;
+                if (range != 0.0f) {
+                    sc = range / levels;
+                    z = f32_as_i32(roundf(lo - mn / sc));
+                }
+            }
+            scale[r * gpr + g] = sc;
+            zp[r * gpr + g] = z;
+            for (size_t i = 0; i < group_size; i++) {
+                int8_t v = 0;
+                if (sc != 0.0f) {
+                    float qf = roundf(grp[i] / sc + (float)z);
+                    qf = qf < lo ? lo : (qf > hi ? hi : qf);
+                    v = (int8_t)qf;
+                }
+                const size_t idx = r * k + g * group_size + i;
+                if (bits == 8) q[idx] = (uint8_t)v;
+                else q[idx / 2] |= (uint8_t)((v & 0x0F) << (4 * (idx % 2)));
+            }
+        }
+    return 0;
+}
+
+/* dequantize (weight_quant.rs:381-412): w = (f32(code) - f32(zero point)) * scale of the group. */
+ORC_API void orc_group_dequantize(const uint8_t *q, const float *scale, const int32_t *zp, size_t n, size_t k,
+                                  int bits, size_t group_size, float *out) {
+    const size_t gpr = k / group_size;
+    for (size_t r = 0; r < n; r++)
+        for (size_t g = 0; g < gpr; g++)
+            for (size_t e = 0; e < group_size; e++) {
+                const size_t idx = r * k + g * group_size + e;
+                out[idx] = ((float)group_code_at(q, idx, bits) - (float)zp[r * gpr + g]) * scale[r * gpr + g];
+            }
+}
+
+/* unpack_gptq_qweight (crates/nn-core/src/layers/quantized/gptq_loader.rs:69-91; AWQ delegates to it,
+ * awq_loader.rs:54-56): packed u32 [rows, cols], bits [4i+3 : 4i] of a word are the i-th of 8
+ * consecutive values along the row axis; out f32 [8 * rows, cols], values 0..15. */
+ORC_API void orc_gptq_unpack_qweight(const uint32_t *packed, size_t rows, size_t cols, float *out) {
+    for (size_t r = 0; r < rows; r++)
+        for (size_t c = 0; c < cols; c++)
+            for (size_t b = 0; b < 8; b++)
+                out[(r * 8 + b) * cols + c] = (float)((packed[r * cols + c] >> (4 * b)) & 0xFu);
+}
+
+/* unpack_gptq_qzeros (gptq_loader.rs:101-123): packed u32 [groups, cols], eight consecutive output
+ * columns per word; out f32 [groups, 8 * cols]. */
+ORC_API void orc_gptq_unpack_qzeros(const uint32_t *packed, size_t groups, size_t cols, float *out) {
+    for (size_t g = 0; g < groups; g++)
+        for (size_t c = 0; c < cols; c++)
+            for (size_t b = 0; b < 8; b++)
+                out[g * cols * 8 + c * 8 + b] = (float)((packed[g * cols + c] >> (4 * b)) & 0xFu);
+}
+
+/* dequantize_gptq (gptq_loader.rs:139-187): q, out f32 [k, n]; scales, zeros f32 [groups, n];
+ * out[i][j] = (q[i][j] - zeros[i / group_size][j]) * scales[i / group_size][j]. Returns 0, or -1
+ * when groups != ceil(k / group_size) (DataLengthMismatch). */
+ORC_API int orc_gptq_dequantize(const float *q, const float *scales, const float *zeros, size_t k, size_t n,
+                                size_t groups, size_t group_size, float *out) {
+    if (group_size == 0 || groups != (k + group_size - 1) / group_size) return -1;
+    for (size_t i = 0; i < k; i++)
+        for (size_t j = 0; j < n; j++) {
+            const size_t g = i / group_size;
+            out[i * n + j] = (q[i * n + j] - zeros[g * n + j]) * scales[g * n + j];
+        }
+    return 0;
+}
+
+/* The weight load_gptq_linear / load_awq_linear build (gptq_loader.rs:329-351, awq_loader.rs:74-96):
+ * unpack both packed tensors, dequantize, transpose to f32 [n, k]. qweight u32 [k / 8, n], scales
+ * f32 [groups, n], qzeros u32 [groups, n / 8]. */
+ORC_API int orc_gptq_load_weight(const uint32_t *qweight, const float *scales, const uint32_t *qzeros, size_t n,
+                                 size_t k, size_t groups, size_t group_size, float *out) {
+    if (group_size == 0 || groups != (k + group_size - 1) / group_size || k % 8 || n % 8) return -1;
+    for (size_t i = 0; i < k; i++)
+        for (size_t j = 0; j < n; j++) {
+            const size_t g = i / group_size;
+            const float qv = (float)((qweight[(i / 8) * n + j] >> (4 * (i % 8))) & 0xFu);
+            const float zv = (float)((qzeros[g * (n / 8) + j / 8] >> (4 * (j % 8))) & 0xFu);
+            out[j * k + i] = (qv - zv) * scales[g * n + j];
+        }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------- */
 /* the reference's CPU forward of one quantized linear, as it is timed        */
 /* ------------------------------------------------------------------------- */
 

@@ -438,3 +438,25 @@ def test_qwen3_32b_shapes_prefill_and_decode(fmt, n, k):
         rmag = orc.linear_abs(xh, deq, 1, n, k)
         P.assert_close(y1.cpu().numpy(), r32, r64, rmag)
     w.release()
+
+
+@pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q8_0, Q.Q6_K, Q.MXFP4_SPLIT, Q.Q5_K, Q.F32_DENSE, Q.BF16_DENSE])
+@pytest.mark.parametrize("m,n,k", [(256, 200, 512), (300, 520, 1024), (1000, 72, 2304)])
+def test_large_batch_takes_the_decode_once_path(fmt, m, n, k):
+    """From 256 rows of bf16 activations on, the weight is decoded to bf16 once and a plain
+    TMA + tcgen05 product follows: ragged M and N tiles, K a multiple of 64, bias, both outputs."""
+    _run(fmt, n, k, m, x_bf16=True, y_bf16=(m == 300), with_bias=(m != 256), seed=900 + m)
+
+
+def test_unquantized_weights_are_bit_exact_at_one_token():
+    """An f32 [n, k] weight behind the same entry point (the dense branch of the reference's
+    Linear): the M = 1 product accumulates in f32, so the f32 bar applies, and the decode of a
+    bf16 weight returns exactly the stored values."""
+    n, k = 96, 1024
+    for fmt in (Q.F32_DENSE, Q.BF16_DENSE):
+        w, _ = F.gen_weight(fmt, 11, n, k)
+        t = api.from_quantized(w, fmt, [n, k])
+        deq = t.dequantize().cpu().numpy()
+        assert np.array_equal(deq.view(np.uint32), orc.dequantize(fmt, w, n * k).reshape(n, k).view(np.uint32))
+        t.release()
+        _run(fmt, n, k, 1, x_bf16=False, y_bf16=False, with_bias=True, seed=12)

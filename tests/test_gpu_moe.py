@@ -49,7 +49,8 @@ def _make(layout, fmt, E, H, I, seed, fast=False):
 
 
 @pytest.mark.parametrize("layout,fmt", [(moe.LAYOUT_KN_GPTOSS, Q.MXFP4_GPTOSS), (moe.LAYOUT_NK, Q.MXFP4_SPLIT),
-                                        (moe.LAYOUT_NK, Q.Q4_K), (moe.LAYOUT_NK, Q.Q5_K), (moe.LAYOUT_NK, Q.Q3_K)])
+                                        (moe.LAYOUT_NK, Q.Q4_K), (moe.LAYOUT_NK, Q.Q5_K), (moe.LAYOUT_NK, Q.Q3_K),
+                                        (moe.LAYOUT_NK, Q.BF16_DENSE), (moe.LAYOUT_NK, Q.F32_DENSE)])
 @pytest.mark.parametrize("T", [1, 7, 64])
 def test_moe_forward_matches_oracle(layout, fmt, T):
     E, H, I, k, limit = 8, 256, 256, 4, 7.0
@@ -72,11 +73,18 @@ def test_moe_forward_matches_oracle(layout, fmt, T):
     blk.release()
 
 
-@pytest.mark.parametrize("fmt", [Q.MXFP4_SPLIT, Q.Q4_K])
+@pytest.mark.parametrize("fmt", [Q.MXFP4_SPLIT, Q.Q4_K, Q.BF16_DENSE])
 def test_prefill_sized_batch_takes_the_tensor_core_path(fmt):
     """From 64 routed rows per expert on, [N, K] experts run the grouped tcgen05 product (bf16
     operands: the 1e-2 bar of the tensor path); ragged expert loads, rows not a multiple of 128."""
-    E, H, I, k, T = 8, 256, 256, 4, 333
+    # 333 tokens: 166 routed rows per expert (the fused-decode tensor path); 1024: 512 per expert
+    # (all experts decoded to bf16 once, then the plain grouped GEMM)
+    for T in (333, 1024):
+        _prefill_case(fmt, T)
+
+
+def _prefill_case(fmt, T):
+    E, H, I, k = 8, 256, 256, 4
     rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(moe.LAYOUT_NK, fmt, E, H, I, 77)
     x = F.gen_activations(78, T, H, bf16=True)
     blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, moe.LAYOUT_NK, fmt, gu, gus, bgu, dn, dns, bd)
