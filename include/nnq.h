@@ -223,6 +223,74 @@ NNQ_API nnq_status nnq_int8_linear(nnq_ctx *ctx, const void *q_dev, const float 
                                    int64_t n, int64_t k, const void *x_dev, nnq_dtype x_dt, int64_t m,
                                    const float *bias_dev, void *y_dev, nnq_dtype y_dt, void *stream);
 
+/* ---- INT4 / INT8 weights with per-group scales; GPTQ / AWQ packed weights ---------- */
+
+/* The reference's QuantizedTensor (crates/nn-core/src/layers/quantized/weight_quant.rs:153-165):
+ * codes for a weight [N, K], int8 one per byte, int4 two per byte over the flat index (even
+ * index in the low nibble, two's complement); scale f32 and zero_point int32 per group of
+ * `group_size` consecutive weights of a row, [N * K / group_size] each; w = (f32(code) -
+ * f32(zp)) * scale. All pointers are device pointers.
+ *
+ * nnq_group_quantize: quantize_per_group + compute_group_params (weight_quant.rs:232-365).
+ * bits 4 or 8; symmetric != 0: scale = max|w| / 7 (127), zero point 0; else scale = (max - min) /
+ * 15 (255), zero point = round(qmin - min / scale). q_dev receives N*K bytes (int8) or
+ * (N*K + 1) / 2 (int4). group_size 0 and a non-finite weight: NNQ_ERR_VALUE_OUT_OF_RANGE;
+ * group_size not dividing K: NNQ_ERR_SHAPE_MISMATCH. Same codes, scales and zero points as the
+ * reference, bit for bit. Waits for the stream (a load-time step).
+ * nnq_group_dequantize: dequantize (weight_quant.rs:381-412) to f32 [N, K], bit-identical. */
+NNQ_API nnq_status nnq_group_quantize(nnq_ctx *ctx, const float *w_dev, int64_t n, int64_t k, int bits, int64_t group_size,
+                                      int symmetric, void *q_dev, float *scale_dev, int32_t *zp_dev, void *stream);
+NNQ_API nnq_status nnq_group_dequantize(nnq_ctx *ctx, const void *q_dev, const float *scale_dev, const int32_t *zp_dev,
+                                        int64_t n, int64_t k, int bits, int64_t group_size, float *dst_dev, void *stream);
+
+/* A group-quantized weight resident on the device, in one layout for both sources: codes row-major
+ * [N, K], scale and zero point f32 [N, groups]. The inputs are copied (per-group form) or repacked
+ * (GPTQ / AWQ); the caller's buffers are not referenced afterwards. Creation waits for the stream
+ * and reserves the context's bf16 scratch for the large-batch product (load-time steps).
+ *
+ * nnq_gq_create_per_group: from the fields of a QuantizedTensor (above).
+ * nnq_gq_create_gptq: load_gptq_linear / load_awq_linear (gptq_loader.rs:329-351,
+ * awq_loader.rs:74-96): qweight u32 [K / 8, N] (bits [4i+3 : 4i] of a word = the i-th of eight
+ * consecutive in-features), scales f32 [groups, N], qzeros u32 [groups, N / 8] (eight consecutive
+ * out-features per word), group = in-feature / group_size, w[n][k] = (q - zero) * scale. groups must
+ * equal ceil(K / group_size) (NNQ_ERR_DATA_LENGTH); K and N multiples of 8 (NNQ_ERR_SHAPE_MISMATCH).
+ * The reference decodes to f32 at load and multiplies dense; here the 4-bit codes stay packed. */
+typedef struct nnq_gq_weight nnq_gq_weight;
+NNQ_API nnq_status nnq_gq_create_per_group(nnq_ctx *ctx, const void *q_dev, const float *scale_dev, const int32_t *zp_dev,
+                                           int64_t n, int64_t k, int bits, int64_t group_size, void *stream,
+                                           nnq_gq_weight **out);
+NNQ_API nnq_status nnq_gq_create_gptq(nnq_ctx *ctx, const uint32_t *qweight_dev, const float *scales_dev,
+                                      const uint32_t *qzeros_dev, int64_t n, int64_t k, int64_t groups, int64_t group_size,
+                                      void *stream, nnq_gq_weight **out);
+/* Any out pointer may be NULL. *streaming: 1 when one-token products run the 16-byte streaming
+ * kernel (K % 32 == 0, group_size % 8 == 0, |zero point| < 4e6), 0 for the element-wise kernel. */
+NNQ_API nnq_status nnq_gq_info(const nnq_gq_weight *w, int64_t *n, int64_t *k, int *bits, int64_t *group_size,
+                               int64_t *groups, int *streaming);
+/* f32 [N, K], bit-identical to dequantize (weight_quant.rs:381-412) / to the weight of
+ * load_gptq_linear (dequantize_gptq then transpose, gptq_loader.rs:139-187,342). */
+NNQ_API nnq_status nnq_gq_dequantize(nnq_gq_weight *w, float *dst_dev, void *stream);
+/* quantized_matmul (weight_quant.rs:451-473) and GptqLinear::forward (gptq_loader.rs:283-311):
+ * y[M, N] = x[M, K] . w^T (+ bias), f32 accumulation. M <= 16: codes streamed once per four
+ * tokens (f32 bar); larger M with K % 64 == 0: one decode to bf16, then the tensor-core product
+ * (bf16 bar, as the other formats). Allocates nothing and does not synchronise. */
+NNQ_API nnq_status nnq_gq_linear(nnq_gq_weight *w, const void *x_dev, nnq_dtype x_dt, int64_t m, const float *bias_dev,
+                                 void *y_dev, nnq_dtype y_dt, void *stream);
+NNQ_API void nnq_gq_destroy(nnq_gq_weight *w);
+
+/* unpack_gptq_qweight (gptq_loader.rs:69-91; unpack_awq_qweight, awq_loader.rs:54-56, is the same
+ * function): u32 [rows, cols] -> f32 [8 * rows, cols], values 0..15.
+ * unpack_gptq_qzeros (gptq_loader.rs:101-123): u32 [groups, cols] -> f32 [groups, 8 * cols].
+ * dequantize_gptq (gptq_loader.rs:139-187): q, dst f32 [K, N]; scales, zeros f32 [groups, N];
+ * dst[i][j] = (q[i][j] - zeros[i / group_size][j]) * scales[i / group_size][j]; groups must equal
+ * ceil(K / group_size) (NNQ_ERR_DATA_LENGTH). */
+NNQ_API nnq_status nnq_gptq_unpack_qweight(nnq_ctx *ctx, const uint32_t *packed_dev, int64_t rows, int64_t cols,
+                                           float *dst_dev, void *stream);
+NNQ_API nnq_status nnq_gptq_unpack_qzeros(nnq_ctx *ctx, const uint32_t *packed_dev, int64_t groups, int64_t cols,
+                                          float *dst_dev, void *stream);
+NNQ_API nnq_status nnq_gptq_dequantize(nnq_ctx *ctx, const float *q_dev, const float *scales_dev, const float *zeros_dev,
+                                       int64_t k, int64_t n, int64_t groups, int64_t group_size, float *dst_dev,
+                                       void *stream);
+
 /* ---- dequantization (bit-exact gate) ---------------------------------------------- */
 
 /* Dequantize a weight to f32 [N, K] on the device. Bit-identical to the reference's

@@ -43,6 +43,20 @@ SIGNATURES = {
     "nnq_int8_dequantize_per_channel": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "nnq_int8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p,
                                 c_void_p, c_int, c_void_p]),
+    "nnq_group_quantize": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nnq_group_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_void_p, c_void_p]),
+    "nnq_gq_create_per_group": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_void_p,
+                                        ctypes.POINTER(c_void_p)]),
+    "nnq_gq_create_gptq": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
+                                   ctypes.POINTER(c_void_p)]),
+    "nnq_gq_info": (c_int, [c_void_p, ctypes.POINTER(c_int64), ctypes.POINTER(c_int64), ctypes.POINTER(c_int),
+                            ctypes.POINTER(c_int64), ctypes.POINTER(c_int64), ctypes.POINTER(c_int)]),
+    "nnq_gq_dequantize": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "nnq_gq_linear": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
+    "nnq_gq_destroy": (None, [c_void_p]),
+    "nnq_gptq_unpack_qweight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "nnq_gptq_unpack_qzeros": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "nnq_gptq_dequantize": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nnq_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
     "nnq_linear_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int]),
     "nnq_linear_batch": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int64,

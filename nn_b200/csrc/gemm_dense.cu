@@ -368,9 +368,12 @@ static bool make_map(const void *base, int64_t rows, int64_t k, int box_rows, CU
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool gemm_dense_shape_ok(const nnq_ctx *ctx, int64_t m, int64_t n, int64_t k, int x_dt) {
+    return ctx->d_dense && x_dt == NNQ_BF16 && m >= 256 && k >= kDgBK && k % kDgBK == 0 && n >= 1 &&
+           (size_t)n * (size_t)k * 2 <= ctx->dense_bytes && m < (1ll << 31) && n < (1ll << 31) && encode_fn() != nullptr;
+}
 bool gemm_dense_supported(const nnq_ctx *ctx, const nnq_weight *w, int64_t m, int x_dt) {
-    return w && w->d_raw && ctx->d_dense && x_dt == NNQ_BF16 && m >= 256 && w->k >= kDgBK && w->k % kDgBK == 0 && w->n >= 1 &&
-           (size_t)w->n * (size_t)w->k * 2 <= ctx->dense_bytes && m < (1ll << 31) && w->n < (1ll << 31) && encode_fn() != nullptr;
+    return w && w->d_raw && gemm_dense_shape_ok(ctx, m, w->n, w->k, x_dt);
 }
 
 nnq_status dense_scratch_reserve(nnq_ctx *ctx, int64_t n, int64_t k) {
@@ -386,7 +389,33 @@ nnq_status dense_scratch_reserve(nnq_ctx *ctx, int64_t n, int64_t k) {
     return NNQ_OK;
 }
 
+// The GEMM alone: w_bf16 is a bf16 [n, k] weight in device memory (16-byte aligned).
+nnq_status launch_gemm_dense_bf16(nnq_ctx *ctx, const void *w_bf16, const TcArgs &a, cudaStream_t stream) {
+    CUtensorMap xmap, wmap;
+    memset(&xmap, 0, sizeof(xmap));
+    memset(&wmap, 0, sizeof(wmap));
+    if (!make_map(a.x, a.m, a.k, kDgBM, &xmap) || !make_map(w_bf16, a.n, a.k, kDgBN, &wmap))
+        return fail(ctx, NNQ_ERR_DISPATCH_FAILED, "tensor map creation failed");
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int smem_bytes = kDgStages * kDgStageBytes + 1024;
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        nnq_status s = check_cuda(ctx, cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes), "GEMM attribute");
+        if (s != NNQ_OK) return s;
+        configured[dev] = true;
+    }
+    const int64_t tiles = ((a.m + kDgBM - 1) / kDgBM) * ((a.n + kDgBN - 1) / kDgBN);
+    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    gemm_dense_kernel<<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status,
+                                                                nullptr, 0);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "bf16 GEMM launch");
+}
+
 nnq_status launch_gemm_dense(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
+    // a bf16 weight is its own decoded form
+    if (a.fmt == NNQ_BF16_DENSE && !((uintptr_t)a.w & 15u)) return launch_gemm_dense_bf16(ctx, a.w, a, stream);
     Geometry g = geometry(a.fmt);
     const int64_t nchunks = a.n * (a.k / g.elems) * (g.elems / 32);
     cudaError_t e;
@@ -402,26 +431,7 @@ nnq_status launch_gemm_dense(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream)
     ctx->launches++;
     nnq_status s = check_cuda(ctx, e, "bf16 decode launch");
     if (s != NNQ_OK) return s;
-    CUtensorMap xmap, wmap;
-    memset(&xmap, 0, sizeof(xmap));
-    memset(&wmap, 0, sizeof(wmap));
-    if (!make_map(a.x, a.m, a.k, kDgBM, &xmap) || !make_map(ctx->d_dense, a.n, a.k, kDgBN, &wmap))
-        return fail(ctx, NNQ_ERR_DISPATCH_FAILED, "tensor map creation failed");
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int smem_bytes = kDgStages * kDgStageBytes + 1024;
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        s = check_cuda(ctx, cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes), "GEMM attribute");
-        if (s != NNQ_OK) return s;
-        configured[dev] = true;
-    }
-    const int64_t tiles = ((a.m + kDgBM - 1) / kDgBM) * ((a.n + kDgBN - 1) / kDgBN);
-    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-    gemm_dense_kernel<<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status,
-                                                                nullptr, 0);
-    ctx->launches++;
-    return check_cuda(ctx, cudaGetLastError(), "bf16 GEMM launch");
+    return launch_gemm_dense_bf16(ctx, ctx->d_dense, a, stream);
 }
 
 bool gemm_dense_grouped_supported(const nnq_ctx *ctx, const TcGroupArgs &g) {

@@ -41,6 +41,9 @@ nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream);
 bool gemm_dense_supported(const nnq_ctx *ctx, const nnq_weight *w, int64_t m, int x_dt);
 nnq_status dense_scratch_reserve(nnq_ctx *ctx, int64_t n, int64_t k);
 nnq_status launch_gemm_dense(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream);
+// the GEMM alone over an already decoded bf16 [n, k] weight (a.w / a.fmt are not read)
+nnq_status launch_gemm_dense_bf16(nnq_ctx *ctx, const void *w_bf16, const TcArgs &a, cudaStream_t stream);
+bool gemm_dense_shape_ok(const nnq_ctx *ctx, int64_t m, int64_t n, int64_t k, int x_dt);
 // the expert products of a prefill-sized MoE call: all local experts decoded at once
 bool gemm_dense_grouped_supported(const nnq_ctx *ctx, const TcGroupArgs &g);
 nnq_status launch_gemm_dense_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStream_t stream);
