@@ -37,6 +37,7 @@ struct nnq_decoder {
     float *d_cos, *d_sin;       // [max_seq, head_dim / 2]
     float *d_kcache, *d_vcache; // [layers, kv_heads, max_seq, head_dim]
     float *d_h, *d_delta, *d_q, *d_k, *d_v, *d_qrot, *d_g, *d_u, *d_logits, *d_part;
+    unsigned int *d_arrived;   // per kv head: attention CTAs that have published their record
     void *d_xn, *d_attn, *d_mid;   // activations fed to the products (f32 or bf16)
     int *d_state;               // [0] token, [1] position, [2] steps taken; then the argmax scratch
     int *d_tokens;              // generated tokens, [max_seq]
@@ -56,7 +57,8 @@ struct nnq_decoder {
 
 namespace nnq {
 
-constexpr int kAttnSplits = 128;
+constexpr int kAttnRanges = 32;   // CTAs per kv head in the decode step's attention
+constexpr int kAttnWarps = 4;
 constexpr int kArgmaxBlocks = 128;
 
 __device__ __forceinline__ float block_sum(float v, float *red) {
@@ -148,121 +150,176 @@ dec_qk_rope_kernel(const float *__restrict__ q, const float *__restrict__ k, con
     else kcache[((size_t)(head - n_heads) * max_seq + pos) * hd + d] = y;
 }
 
-// Grouped-query attention over the cache, split over the keys: one warp per (kv head, split)
-// serves all query heads of the group. Keys are taken 32 at a time: lane j forms the dot products
-// of key j with every query head of the group (the query vectors sit in shared memory, the key row
-// is read once for the whole group), the batch joins the running softmax of each head (maximum,
-// sum), then the value rows are read coalesced (lane l owns dimensions 4l .. 4l+3) and weighted
-// with the probabilities passed by shuffle. Output per head and split: (m, l, acc[hd]).
+// Grouped-query attention over the cache in one launch. The keys are taken in batches of 32; a
+// kv head's batches are dealt to kAttnRanges CTAs (contiguous ranges) and inside a CTA to its four
+// warps. For a batch, lane j forms the dot products of key j with every query head of the group (the
+// query vectors sit in shared memory, the key row is read once for the whole group), the batch joins
+// the running softmax of each head (maximum, sum), then the value rows are read coalesced (lane l
+// owns dimensions 4l .. 4l+3) and weighted with the probabilities passed by shuffle. The warps of a
+// CTA merge through shared memory into one record per head, (m, l, acc[hd]), in global memory; the
+// CTA that finishes last for its kv head (an arrival counter, reset by that CTA for the next
+// launch) merges the records of all ranges and writes the output rows:
+// out[head, d] = sum_s acc_s[d] e^(m_s - M) / sum_s l_s e^(m_s - M).
 template <int G>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(kAttnWarps * 32)
 dec_attn_kernel(const float *__restrict__ qrot, const float *__restrict__ kcache, const float *__restrict__ vcache,
-                const int *__restrict__ state, float scale, float *__restrict__ part, int hd, int max_seq) {
+                const int *__restrict__ state, float scale, float *__restrict__ part, unsigned int *__restrict__ arrived,
+                void *__restrict__ out, int act_dt, int hd, int max_seq) {
     pdl_prologue();
     __shared__ __align__(16) float qs[G][128];
-    const int kvh = blockIdx.x, split = blockIdx.y, lane = threadIdx.x;
+    __shared__ __align__(16) float wacc[kAttnWarps][G][128];
+    __shared__ float wm[kAttnWarps][G], wl[kAttnWarps][G];
+    __shared__ int s_last;
+    const int kvh = blockIdx.x, range = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int ctx = state[1] + 1;
-    const int per = (ctx + kAttnSplits - 1) / kAttnSplits;
-    const int j0 = split * per, j1 = min(ctx, j0 + per);
-#pragma unroll
-    for (int g = 0; g < G; g++)
-        *reinterpret_cast<float4 *>(&qs[g][4 * lane]) = *reinterpret_cast<const float4 *>(qrot + (kvh * G + g) * hd + 4 * lane);
-    __syncwarp();
-    float m[G], l[G];
-    float4 acc[G];
-#pragma unroll
-    for (int g = 0; g < G; g++) {
-        m[g] = -INFINITY;
-        l[g] = 0.0f;
-        acc[g] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-    const float *kb = kcache + (size_t)kvh * max_seq * hd, *vb = vcache + (size_t)kvh * max_seq * hd;
-    for (int b0 = j0; b0 < j1; b0 += 32) {
-        const int j = b0 + lane;
-        const bool valid = j < j1;
-        const float4 *krow = reinterpret_cast<const float4 *>(kb + (size_t)(valid ? j : b0) * hd);
-        float dot[G];
-#pragma unroll
-        for (int g = 0; g < G; g++) dot[g] = 0.0f;
-#pragma unroll 16
-        for (int d4 = 0; d4 < 32; d4++) {
-            const float4 kv = krow[d4];
-#pragma unroll
-            for (int g = 0; g < G; g++) {
-                const float4 qv = *reinterpret_cast<const float4 *>(&qs[g][4 * d4]);
-                dot[g] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, dot[g]))));
-            }
-        }
-        float p[G];
+    const int nb = (ctx + 31) >> 5;                              // batches of 32 keys in the context
+    const int bper = (nb + kAttnRanges - 1) / kAttnRanges;       // batches per range
+    const int used = (nb + bper - 1) / bper;                     // ranges that hold keys
+    const int b_lo = range * bper, b_hi = min(nb, b_lo + bper);
+    if (b_lo < b_hi) {
+        for (int i = threadIdx.x; i < G * 32; i += kAttnWarps * 32)
+            *reinterpret_cast<float4 *>(&qs[i >> 5][4 * (i & 31)]) = *reinterpret_cast<const float4 *>(qrot + (kvh * G + (i >> 5)) * hd + 4 * (i & 31));
+        __syncthreads();
+        float m[G], l[G];
+        float4 acc[G];
 #pragma unroll
         for (int g = 0; g < G; g++) {
-            const float s = valid ? dot[g] * scale : -INFINITY;
-            float bm = s;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
-            const float mn = fmaxf(m[g], bm);   // finite: the batch holds at least one key
-            const float corr = expf(m[g] - mn);
-            p[g] = expf(s - mn);
-            float ps = p[g];
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xFFFFFFFFu, ps, off);
-            l[g] = l[g] * corr + ps;
-            acc[g].x *= corr; acc[g].y *= corr; acc[g].z *= corr; acc[g].w *= corr;
-            m[g] = mn;
+            m[g] = -INFINITY;
+            l[g] = 0.0f;
+            acc[g] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
-        const int nb = min(32, j1 - b0);
-        for (int jj = 0; jj < nb; jj++) {
-            const float4 vv = *reinterpret_cast<const float4 *>(vb + (size_t)(b0 + jj) * hd + 4 * lane);
+        const float *kb = kcache + (size_t)kvh * max_seq * hd, *vb = vcache + (size_t)kvh * max_seq * hd;
+        for (int b = b_lo + warp; b < b_hi; b += kAttnWarps) {
+            const int b0 = b << 5, j1 = min(ctx, b0 + 32);
+            const int j = b0 + lane;
+            const bool valid = j < j1;
+            const float4 *krow = reinterpret_cast<const float4 *>(kb + (size_t)(valid ? j : b0) * hd);
+            // the value rows of the batch are wanted after the softmax: ask L2 for them now (lane j: row j)
+            if (valid) {
+                const char *vrow = reinterpret_cast<const char *>(vb + (size_t)j * hd);
+#pragma unroll
+                for (int c = 0; c < 4; c++) asm volatile("prefetch.global.L2 [%0];" ::"l"(vrow + 128 * c));
+            }
+            float dot[G];
+#pragma unroll
+            for (int g = 0; g < G; g++) dot[g] = 0.0f;
+#pragma unroll 16
+            for (int d4 = 0; d4 < 32; d4++) {
+                const float4 kv = krow[d4];
+#pragma unroll
+                for (int g = 0; g < G; g++) {
+                    const float4 qv = *reinterpret_cast<const float4 *>(&qs[g][4 * d4]);
+                    dot[g] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, dot[g]))));
+                }
+            }
+            float p[G];
 #pragma unroll
             for (int g = 0; g < G; g++) {
-                const float pj = __shfl_sync(0xFFFFFFFFu, p[g], jj);
-                acc[g].x = fmaf(pj, vv.x, acc[g].x);
-                acc[g].y = fmaf(pj, vv.y, acc[g].y);
-                acc[g].z = fmaf(pj, vv.z, acc[g].z);
-                acc[g].w = fmaf(pj, vv.w, acc[g].w);
+                const float s = valid ? dot[g] * scale : -INFINITY;
+                float bm = s;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
+                const float mn = fmaxf(m[g], bm);   // finite: the batch holds at least one key
+                const float corr = expf(m[g] - mn);
+                p[g] = expf(s - mn);
+                float ps = p[g];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xFFFFFFFFu, ps, off);
+                l[g] = l[g] * corr + ps;
+                acc[g].x *= corr; acc[g].y *= corr; acc[g].z *= corr; acc[g].w *= corr;
+                m[g] = mn;
+            }
+            const int nk = j1 - b0;
+#pragma unroll 4
+            for (int jj = 0; jj < nk; jj++) {
+                const float4 vv = *reinterpret_cast<const float4 *>(vb + (size_t)(b0 + jj) * hd + 4 * lane);
+#pragma unroll
+                for (int g = 0; g < G; g++) {
+                    const float pj = __shfl_sync(0xFFFFFFFFu, p[g], jj);
+                    acc[g].x = fmaf(pj, vv.x, acc[g].x);
+                    acc[g].y = fmaf(pj, vv.y, acc[g].y);
+                    acc[g].z = fmaf(pj, vv.z, acc[g].z);
+                    acc[g].w = fmaf(pj, vv.w, acc[g].w);
+                }
             }
         }
-    }
+        // the warps of the CTA -> one record per head
 #pragma unroll
-    for (int g = 0; g < G; g++) {
-        float *o = part + ((size_t)(kvh * G + g) * kAttnSplits + split) * (hd + 4);   // record: m, l, pad, pad, acc[hd]
-        if (lane == 0) {
-            o[0] = m[g];
-            o[1] = l[g];
+        for (int g = 0; g < G; g++) {
+            if (lane == 0) {
+                wm[warp][g] = m[g];
+                wl[warp][g] = l[g];
+            }
+            *reinterpret_cast<float4 *>(&wacc[warp][g][4 * lane]) = acc[g];
         }
-        *reinterpret_cast<float4 *>(o + 4 + 4 * lane) = acc[g];
-    }
-}
-
-// out[head, d] = sum_s acc_s[d] e^(m_s - M) / sum_s l_s e^(m_s - M); the split weights are formed
-// once per head by the first kAttnSplits threads
-__global__ void __launch_bounds__(128)
-dec_attn_combine_kernel(const float *__restrict__ part, void *__restrict__ out, int act_dt, int hd) {
-    pdl_prologue();
-    __shared__ float wgt[kAttnSplits];
-    __shared__ float red[32];
-    const int head = blockIdx.x, d = threadIdx.x;
-    const float *p = part + (size_t)head * kAttnSplits * (hd + 4);
-    float ms = -INFINITY, ls = 0.0f;
-    if (d < kAttnSplits) {
-        ms = p[d * (hd + 4)];
-        ls = p[d * (hd + 4) + 1];
-    }
-    float M = ms;
+        __syncthreads();
+        for (int i = threadIdx.x; i < G * 128; i += kAttnWarps * 32) {
+            const int g = i >> 7, dd = i & 127;
+            float M = wm[0][g];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, off));
-    if ((d & 31) == 0) red[d >> 5] = M;
-    __syncthreads();
-    M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    const float e = ms == -INFINITY ? 0.0f : expf(ms - M);   // a split without keys has weight 0
-    if (d < kAttnSplits) wgt[d] = e;
-    const float L = block_sum(ls * e, red);
-    float a = 0.0f;
-    if (d < hd) {
-#pragma unroll 8
-        for (int s = 0; s < kAttnSplits; s++) a = fmaf(p[s * (hd + 4) + 4 + d], wgt[s], a);
-        store_act(out, act_dt, head * hd + d, a / L);
+            for (int w = 1; w < kAttnWarps; w++) M = fmaxf(M, wm[w][g]);   // warp 0 always holds a batch: finite
+            float L = 0.0f, a = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; w++) {
+                const float e = wm[w][g] == -INFINITY ? 0.0f : expf(wm[w][g] - M);
+                L = fmaf(wl[w][g], e, L);
+                a = fmaf(wacc[w][g][dd], e, a);
+            }
+            float *o = part + ((size_t)(kvh * kAttnRanges + range) * G + g) * (hd + 4);   // record: m, l, pad, pad, acc[hd]
+            if (dd == 0) {
+                o[0] = M;
+                o[1] = L;
+            }
+            if (dd < hd) o[4 + dd] = a;
+        }
     }
+    // arrival: the records above are published before the count, the last CTA reads them after it
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(arrived + kvh, 1u) == (unsigned)(kAttnRanges - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // a warp per head, a lane per four dimensions; every load of a pass is issued before the first
+    // is used (the records sit in L2: the pass costs one round trip, not one per range)
+    for (int g = warp; g < G; g += kAttnWarps) {
+        const float *rec = part + ((size_t)(kvh * kAttnRanges) * G + g) * (hd + 4);
+        const size_t step = (size_t)G * (hd + 4);
+        float2 ml[kAttnRanges];
+#pragma unroll
+        for (int s = 0; s < kAttnRanges; s++)
+            ml[s] = s < used ? __ldcg(reinterpret_cast<const float2 *>(rec + s * step)) : make_float2(-INFINITY, 0.0f);
+        float M = ml[0].x;
+#pragma unroll
+        for (int s = 1; s < kAttnRanges; s++) M = fmaxf(M, ml[s].x);
+        float L = 0.0f;
+#pragma unroll
+        for (int s = 0; s < kAttnRanges; s++) {
+            ml[s].x = s < used ? expf(ml[s].x - M) : 0.0f;
+            L = fmaf(ml[s].y, ml[s].x, L);
+        }
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int h = 0; h < kAttnRanges; h += 16) {
+            float4 v[16];
+#pragma unroll
+            for (int s = 0; s < 16; s++)
+                v[s] = h + s < used ? __ldcg(reinterpret_cast<const float4 *>(rec + (h + s) * step + 4) + lane) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int s = 0; s < 16; s++) {
+                a.x = fmaf(v[s].x, ml[h + s].x, a.x);
+                a.y = fmaf(v[s].y, ml[h + s].x, a.y);
+                a.z = fmaf(v[s].z, ml[h + s].x, a.z);
+                a.w = fmaf(v[s].w, ml[h + s].x, a.w);
+            }
+        }
+        const int at = (kvh * G + g) * hd + 4 * lane;
+        store_act(out, act_dt, at, a.x / L);
+        store_act(out, act_dt, at + 1, a.y / L);
+        store_act(out, act_dt, at + 2, a.z / L);
+        store_act(out, act_dt, at + 3, a.w / L);
+    }
+    if (threadIdx.x == 0) arrived[kvh] = 0;   // the next launch starts after this grid has ended
 }
 
 __global__ void dec_silu_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, void *__restrict__ mid,
@@ -587,7 +644,9 @@ nnq_status nnq_decoder_create(nnq_ctx *ctx, const nnq_decoder_config *cfg, nnq_d
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_g, (size_t)lffn * 4, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_u, (size_t)lffn * 4, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_logits, (size_t)c.vocab * 4, "decoder buffer");
-    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_part, (size_t)d->lh * kAttnSplits * (hd + 4) * 4, "attention partials");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_part, (size_t)d->lh * kAttnRanges * (hd + 4) * 4, "attention partials");
+    if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->d_arrived, (size_t)(d->lkv > 0 ? d->lkv : 1) * 4, "attention arrival counters");
+    if (s == NNQ_OK) s = check_cuda(ctx, cudaMemset(d->d_arrived, 0, (size_t)(d->lkv > 0 ? d->lkv : 1) * 4), "attention arrival counters clear");
     if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_xn, (size_t)c.hidden * es, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_attn, (size_t)qdim * es, "decoder buffer");
     if (s == NNQ_OK) s = dev_alloc(ctx, &d->d_mid, (size_t)lffn * es, "decoder buffer");
@@ -741,6 +800,19 @@ static nnq_status head_mode(nnq_decoder *d, bool *vocab_parallel, CommView *cv) 
     return NNQ_OK;
 }
 
+// Measurement aid (builds with -DNNQ_DIAG only): NNQ_DEC_SKIP is a bit mask of step parts that are
+// not launched (1 norms, 2 rotation / cache append, 4 attention, 16 SwiGLU, 32 products), to read
+// the cost of each part off the time of a replayed step. The results are meaningless with any bit set.
+#ifdef NNQ_DIAG
+static int dec_skip() {
+    static const int v = getenv("NNQ_DEC_SKIP") ? atoi(getenv("NNQ_DEC_SKIP")) : 0;
+    return v;
+}
+#define DEC_RUN(bit, ...) do { if (!(dec_skip() & (bit))) { __VA_ARGS__; } } while (0)
+#else
+#define DEC_RUN(bit, ...) do { __VA_ARGS__; } while (0)
+#endif
+
 nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
     if (!d) return NNQ_ERR_INVALID_ARG;
     nnq_ctx *ctx = d->ctx;
@@ -769,39 +841,38 @@ nnq_status nnq_decoder_step(nnq_decoder *d, void *stream) {
     const __nv_bfloat16 *embed = (const __nv_bfloat16 *)d->d_embed;
     for (int l = 0; l < c.n_layers; l++) {
         const nnq_decoder::Layer &L = d->layers[l];
-        launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, l == 0 ? embed : nullptr, d->d_state, L.in_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+        DEC_RUN(1, launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, l == 0 ? embed : nullptr, d->d_state, L.in_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden));
         const nnq_weight *w3[3] = {L.q, L.k, L.v};
         const void *x3[3] = {d->d_xn, d->d_xn, d->d_xn};
         void *y3[3] = {d->d_q, d->d_k, d->d_v};
-        if ((s = nnq_linear_batch(ctx, 3, w3, x3, adt, 1, nullptr, y3, NNQ_F32, st)) != NNQ_OK) return s;
-        launch_pdl(dec_qk_rope_kernel, dim3(lh + 2 * lkv), dim3(hd), st, d->d_q, d->d_k, d->d_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, d->d_state,
-                   c.rms_eps, d->d_qrot, d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, lh, lkv, hd, c.max_seq);
-        {
-            const dim3 ag(lkv, kAttnSplits);
+        DEC_RUN(32, if ((s = nnq_linear_batch(ctx, 3, w3, x3, adt, 1, nullptr, y3, NNQ_F32, st)) != NNQ_OK) return s);
+        DEC_RUN(2, launch_pdl(dec_qk_rope_kernel, dim3(lh + 2 * lkv), dim3(hd), st, d->d_q, d->d_k, d->d_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, d->d_state,
+                              c.rms_eps, d->d_qrot, d->d_kcache + l * layer_cache, d->d_vcache + l * layer_cache, lh, lkv, hd, c.max_seq));
+        DEC_RUN(4, {
+            const dim3 ag(lkv, kAttnRanges), ab(kAttnWarps * 32);
             const float *kc = d->d_kcache + l * layer_cache, *vc = d->d_vcache + l * layer_cache;
             switch (group) {
-                case 1: launch_pdl(dec_attn_kernel<1>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
-                case 2: launch_pdl(dec_attn_kernel<2>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
-                case 4: launch_pdl(dec_attn_kernel<4>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
-                case 8: launch_pdl(dec_attn_kernel<8>, ag, dim3(32), st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, hd, c.max_seq); break;
+                case 1: launch_pdl(dec_attn_kernel<1>, ag, ab, st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, d->d_arrived, d->d_attn, d->act_dt, hd, c.max_seq); break;
+                case 2: launch_pdl(dec_attn_kernel<2>, ag, ab, st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, d->d_arrived, d->d_attn, d->act_dt, hd, c.max_seq); break;
+                case 4: launch_pdl(dec_attn_kernel<4>, ag, ab, st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, d->d_arrived, d->d_attn, d->act_dt, hd, c.max_seq); break;
+                case 8: launch_pdl(dec_attn_kernel<8>, ag, ab, st, d->d_qrot, kc, vc, d->d_state, scale, d->d_part, d->d_arrived, d->d_attn, d->act_dt, hd, c.max_seq); break;
                 default: return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must be 1, 2, 4 or 8");
             }
-        }
-        launch_pdl(dec_attn_combine_kernel, dim3(lh), dim3(128), st, d->d_part, d->d_attn, d->act_dt, hd);
+        });
         // row-parallel products: with tensor parallelism the partial sums are exchanged inside the kernel
-        s = d->comm ? nnq_comm_linear(d->comm, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st)
-                    : nnq_linear(ctx, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st);
+        DEC_RUN(32, s = d->comm ? nnq_comm_linear(d->comm, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st)
+                                : nnq_linear(ctx, L.o, d->d_attn, adt, 1, nullptr, d->d_delta, NNQ_F32, st));
         if (s != NNQ_OK) return s;
-        launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, L.post_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
+        DEC_RUN(1, launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, L.post_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden));
         const nnq_weight *w2[2] = {L.gate, L.up};
         const void *x2[2] = {d->d_xn, d->d_xn};
         void *y2[2] = {d->d_g, d->d_u};
-        if ((s = nnq_linear_batch(ctx, 2, w2, x2, adt, 1, nullptr, y2, NNQ_F32, st)) != NNQ_OK) return s;
-        launch_pdl(dec_silu_mul_kernel, dim3((lffn + 255) / 256), dim3(256), st, d->d_g, d->d_u, d->d_mid, d->act_dt, lffn);
-        s = d->comm ? nnq_comm_linear(d->comm, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st)
-                    : nnq_linear(ctx, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st);
+        DEC_RUN(32, if ((s = nnq_linear_batch(ctx, 2, w2, x2, adt, 1, nullptr, y2, NNQ_F32, st)) != NNQ_OK) return s);
+        DEC_RUN(16, launch_pdl(dec_silu_mul_kernel, dim3((lffn + 255) / 256), dim3(256), st, d->d_g, d->d_u, d->d_mid, d->act_dt, lffn));
+        DEC_RUN(32, s = d->comm ? nnq_comm_linear(d->comm, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st)
+                                : nnq_linear(ctx, L.down, d->d_mid, adt, 1, nullptr, d->d_delta, NNQ_F32, st));
         if (s != NNQ_OK) return s;
-        ctx->launches += 6;
+        ctx->launches += 5;
     }
     launch_pdl(dec_norm_kernel, dim3(1), dim3(1024), st, d->d_h, d->d_delta, nullptr, d->d_state, d->d_final_norm, c.rms_eps, d->d_xn, d->act_dt, c.hidden);
     ctx->launches++;
@@ -936,7 +1007,7 @@ void nnq_decoder_destroy(nnq_decoder *d) {
     }
     cudaFree(d->d_final_norm); cudaFree(d->d_cos); cudaFree(d->d_sin); cudaFree(d->d_kcache); cudaFree(d->d_vcache);
     cudaFree(d->d_h); cudaFree(d->d_delta); cudaFree(d->d_q); cudaFree(d->d_k); cudaFree(d->d_v); cudaFree(d->d_qrot);
-    cudaFree(d->d_g); cudaFree(d->d_u); cudaFree(d->d_logits); cudaFree(d->d_part); cudaFree(d->d_xn); cudaFree(d->d_attn);
+    cudaFree(d->d_g); cudaFree(d->d_u); cudaFree(d->d_logits); cudaFree(d->d_part); cudaFree(d->d_arrived); cudaFree(d->d_xn); cudaFree(d->d_attn);
     cudaFree(d->d_mid); cudaFree(d->d_state); cudaFree(d->d_tokens);
     cudaFree(d->pf_h); cudaFree(d->pf_delta); cudaFree(d->pf_q); cudaFree(d->pf_k); cudaFree(d->pf_v); cudaFree(d->pf_qrot);
     cudaFree(d->pf_g); cudaFree(d->pf_u); cudaFree(d->pf_xn); cudaFree(d->pf_attn); cudaFree(d->pf_mid); cudaFree(d->pf_tokens);
