@@ -964,6 +964,51 @@ def other_configs(torch, backend, layers, gen, dev):
         out["int8_w8a16_gemv_151936x4096_f32_m1"] = int8_gemv(151936, 4096, 10)
     except Exception as e:
         out["int8_w8a16_gemv_151936x4096_f32_m1"] = {"error": str(e)[:200]}
+    def group_gemv(bits, n, k, g, reps, gptq_form=False):
+        """One-token product over INT4 / INT8 per-group codes (or a GPTQ-packed weight), bf16 activations;
+        `copies` weights are rotated so that a pass reads more than L2 holds."""
+        import ctypes as ct
+        from nn_b200 import gptq as G
+        from nn_b200 import weight_quant as wq
+        copies = max(1, int(300e6 // (n * k * bits // 8)) + 1)
+        ws = []
+        for _ in range(copies):
+            if gptq_form:
+                qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 8, n), dtype=torch.int32, device=dev, generator=gen)
+                qz = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // g, n // 8), dtype=torch.int32, device=dev, generator=gen)
+                sc = torch.rand(k // g, n, device=dev, generator=gen) * 1e-2
+                ws.append(G.load_gptq_linear(qw, sc, qz, None, g, backend)._packed)
+            else:
+                q = torch.randint(0, 256, (n * k * bits // 8,), dtype=torch.uint8, device=dev, generator=gen)
+                sc = torch.rand(n * (k // g), device=dev, generator=gen) * 1e-2
+                zp = torch.randint(-4, 4, (n * (k // g),), dtype=torch.int32, device=dev, generator=gen)
+                cfgq = wq.QuantizationConfig(wq.QuantDtype.Int4 if bits == 4 else wq.QuantDtype.Int8, g, False)
+                ws.append(wq.QuantizedTensor(q, sc, zp, cfgq, [n, k], backend).device_weight())
+        x = torch.randn(1, k, device=dev, generator=gen).to(torch.bfloat16)
+        y = torch.empty(1, n, dtype=torch.float32, device=dev)
+        i = [0]
+
+        def one():
+            st = lib.nnq_gq_linear(ws[i[0] % copies]._handle, x.data_ptr(), api.BF16, 1, None, y.data_ptr(), api.F32, None)
+            i[0] += 1
+            if st != 0:
+                backend.check(st)
+
+        sec = timed(one, reps)
+        algo = n * k * bits // 8 + n * (k // g) * 8 + k * 2 + n * 4   # codes, scale + zero point per group, x and y once
+        for w in ws:
+            w.release()
+        return {"us": sec * 1e6, "gbs": algo / sec / 1e9, "bound": "hbm", "frac": algo / sec / 1e9 / peak_hbm,
+                "weights_rotated": copies, "group_size": g}
+
+    for key, args_ in (("int4_per_group_gemv_12288x4096_g128_bf16_m1", (4, 12288, 4096, 128, 40)),
+                       ("int8_per_group_gemv_12288x4096_g128_bf16_m1", (8, 12288, 4096, 128, 40)),
+                       ("gptq_int4_gemv_12288x4096_g128_bf16_m1", (4, 12288, 4096, 128, 40, True)),
+                       ("int4_per_group_gemv_151936x4096_g128_bf16_m1", (4, 151936, 4096, 128, 10))):
+        try:
+            out[key] = group_gemv(*args_)
+        except Exception as e:
+            out[key] = {"error": str(e)[:200]}
     backend.device_status()
     return out
 

@@ -217,7 +217,9 @@ constexpr int kGqRows = 4;   // output rows per warp: one load of the activation
 
 // y[t][r] = sum over groups of scale[r][g] * sum_{k in g} (code[r][k] - zp[r][g]) * x[t][k] (+ bias[r])
 // for tokens [t0, t0 + MT). Needs k % 32 == 0, group_size % 8 == 0, 16-byte aligned x, |zp| < 4e6.
-template <int BITS, typename XT, int MT>
+// GC: a 16-byte chunk never straddles a group (group_size a multiple of 32 / 16 weights), so scale and
+// zero point are fetched once per chunk and row.
+template <int BITS, typename XT, int MT, bool GC>
 __global__ void __launch_bounds__(kGqLinThreads)
 gq_linear_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ scale, const float *__restrict__ zpf,
                  int64_t groups, int g, int gshift, int is_signed, const XT *__restrict__ x, const float *__restrict__ bias,
@@ -255,10 +257,19 @@ gq_linear_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ sc
                 const uint4 v = __ldg(reinterpret_cast<const uint4 *>(row[r] + k0 * BITS / 8));
                 raw[r][0] = v.x ^ flip; raw[r][1] = v.y ^ flip; raw[r][2] = v.z ^ flip; raw[r][3] = v.w ^ flip;
             }
+            float cc[R], gsc[R];
+            if (GC) {
+                const int64_t gi = gshift >= 0 ? (k0 >> gshift) : k0 / g;
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    cc[r] = __fadd_rn(off, __ldg(zp[r] + gi));
+                    gsc[r] = __ldg(sc[r] + gi);
+                }
+            }
 #pragma unroll
             for (int s = 0; s < SUBS; s++) {
                 const int64_t kk = k0 + 8 * s;
-                const int64_t gi = gshift >= 0 ? (kk >> gshift) : kk / g;
+                const int64_t gi = GC ? 0 : (gshift >= 0 ? (kk >> gshift) : kk / g);
                 float xv[MT][8];
 #pragma unroll
                 for (int t = 0; t < MT; t++) {
@@ -267,8 +278,8 @@ gq_linear_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ sc
                 }
 #pragma unroll
                 for (int r = 0; r < R; r++) {
-                    const float c = __fadd_rn(off, __ldg(zp[r] + gi));
-                    const float gs = __ldg(sc[r] + gi);
+                    const float c = GC ? cc[r] : __fadd_rn(off, __ldg(zp[r] + gi));
+                    const float gs = GC ? gsc[r] : __ldg(sc[r] + gi);
                     float wv[8];
                     if (BITS == 4) {
                         const uint32_t word = raw[r][s];
@@ -420,16 +431,23 @@ void launch_fast(nnq_gq_weight *w, const void *x, const float *bias, void *y, in
     const int64_t units = (w->n + kGqRows - 1) / kGqRows, per_cta = kGqLinThreads / 32;
     const int64_t want = (units + per_cta - 1) / per_cta, cap = (int64_t)ctx->sm_count * 16;
     const int grid = (int)(want < cap ? want : cap);
+    const bool gc = w->group_size % (BITS == 4 ? 32 : 16) == 0;
     int gshift = -1;
     if ((w->group_size & (w->group_size - 1)) == 0)
         for (gshift = 0; (1 << gshift) < w->group_size; gshift++) {}
     for (int64_t t0 = 0; t0 < m; t0 += 4) {   // four tokens share a pass over the weights
         const int64_t left = m - t0;
-#define NNQ_GQ(MT) gq_linear_kernel<BITS, XT, MT><<<grid, kGqLinThreads, 0, st>>>(w->codes, w->scale, w->zpf, w->groups, w->group_size, \
-                       gshift, w->is_signed, (const XT *)x, bias, y, y_dt, m, w->n, w->k, t0)
-        if (left == 1) NNQ_GQ(1);
-        else if (left == 2) NNQ_GQ(2);
-        else NNQ_GQ(4);
+#define NNQ_GQ(MT, GC) gq_linear_kernel<BITS, XT, MT, GC><<<grid, kGqLinThreads, 0, st>>>(w->codes, w->scale, w->zpf, w->groups, w->group_size, \
+                           gshift, w->is_signed, (const XT *)x, bias, y, y_dt, m, w->n, w->k, t0)
+        if (gc) {
+            if (left == 1) NNQ_GQ(1, true);
+            else if (left == 2) NNQ_GQ(2, true);
+            else NNQ_GQ(4, true);
+        } else {
+            if (left == 1) NNQ_GQ(1, false);
+            else if (left == 2) NNQ_GQ(2, false);
+            else NNQ_GQ(4, false);
+        }
 #undef NNQ_GQ
         ctx->launches++;
     }

@@ -4,11 +4,18 @@
   python -m nn_b200.microbench moe --layout nk --tokens 64
   python -m nn_b200.microbench codec --fmt q4_k_ggml --elements 268435456
   python -m nn_b200.microbench int8 --n 12288 --k 4096 --m 1
+  python -m nn_b200.microbench groupq --bits 4 --n 12288 --k 4096 --group 128 --m 1 [--gptq]
+  python -m nn_b200.microbench decoder --layers 4 --pos 2048 [--eager]
 
 `linear` rotates `--copies` distinct weights so that every call streams its weight from HBM
 (more bytes in rotation than L2 holds unless --copies says otherwise); `moe` times one
 mixture-of-experts block of the gpt-oss expert geometry. `codec` times the block
 encoder (where the reference has one) and the decoder over one flat tensor larger than L2.
+`groupq` times the product over INT4 / INT8 per-group codes (or a GPTQ-packed weight), replayed
+from a CUDA graph so that the host loop does not bound 20 us kernels. `decoder` builds a
+Qwen3-8B-shaped decoder of `--layers` Q4_K layers (no vocabulary head worth timing: a 1024-row Q6_K
+one), places it at `--pos` and replays one captured step; `--eager` issues the launches one by one
+instead (the form a profiler can list).
 CUDA events around `--reps` calls after 3 warm-up calls; one line per run.
 """
 from __future__ import annotations
@@ -201,6 +208,120 @@ def run_int8(a):
           f"{2.0 * a.m * a.n * a.k / sec / 1e12:.2f} TFLOP/s", flush=True)
 
 
+def run_groupq(a):
+    import torch
+
+    from . import api, gptq
+    from . import weight_quant as wq
+    b = api.gpu_backend()
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    n, k, g, bits = a.n, a.k, a.group, a.bits
+    copies = max(1, int(300e6 // (n * k * bits // 8)) + 1)
+    ws = []
+    for _ in range(copies):
+        if a.gptq:
+            qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // 8, n), dtype=torch.int32, device=dev, generator=gen)
+            qz = torch.randint(-2 ** 31, 2 ** 31 - 1, (k // g, n // 8), dtype=torch.int32, device=dev, generator=gen)
+            sc = torch.rand(k // g, n, device=dev, generator=gen) * 1e-2
+            ws.append(gptq.load_gptq_linear(qw, sc, qz, None, g, b)._packed)
+        else:
+            q = torch.randint(0, 256, (n * k * bits // 8,), dtype=torch.uint8, device=dev, generator=gen)
+            sc = torch.rand(n * (k // g), device=dev, generator=gen) * 1e-2
+            zp = torch.randint(-4, 4, (n * (k // g),), dtype=torch.int32, device=dev, generator=gen)
+            cfg = wq.QuantizationConfig(wq.QuantDtype.Int4 if bits == 4 else wq.QuantDtype.Int8, g, False)
+            ws.append(wq.QuantizedTensor(q, sc, zp, cfg, [n, k], b).device_weight())
+    x = torch.randn(a.m, k, device=dev, generator=gen).to(torch.bfloat16)
+    y = torch.empty(a.m, n, dtype=torch.float32, device=dev)
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        def pass_over_copies():
+            for w in ws:
+                b.check(b._lib.nnq_gq_linear(w._handle, x.data_ptr(), api.BF16, a.m, None, y.data_ptr(), api.F32, st.cuda_stream))
+        pass_over_copies()
+        st.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            pass_over_copies()
+        for _ in range(3):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(a.reps):
+            graph.replay()
+        e1.record(st)
+        st.synchronize()
+    b.device_status()
+    sec = e0.elapsed_time(e1) * 1e-3 / a.reps / copies
+    algo = n * k * bits // 8 + n * (k // g) * 8 + a.m * k * 2 + a.m * n * 4
+    print(f"groupq {'gptq ' if a.gptq else ''}int{bits} N={n} K={k} group={g} M={a.m}: {sec * 1e6:.1f} us, "
+          f"{algo / sec / 1e9:.0f} GB/s algorithmic ({copies} weights in rotation)", flush=True)
+    for w in ws:
+        w.release()
+
+
+def run_decoder(a):
+    import torch
+
+    from . import api, decoder
+    from . import workload as W
+    from .formats import QuantFormat as Q
+    b = api.gpu_backend()
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    cfg = decoder.DecoderConfig(n_layers=a.layers, vocab=1024, max_seq=a.pos + 64, act_dtype=api.BF16)
+    dec = decoder.Decoder(b, cfg)
+    oh, od = torch.ones(cfg.hidden, device=dev), torch.ones(cfg.head_dim, device=dev)
+    keep = []
+    for li in range(a.layers):
+        lw = {}
+        for name, n, k in W.PROJECTIONS:
+            raw = W.gen_q4_k_device(torch, gen, n, k)
+            lw[name] = api.DeviceWeight.from_device(b, Q.Q4_K, raw, n, k)
+            del raw
+        keep.append(lw)
+        dec.set_layer(li, lw["q_proj"], lw["k_proj"], lw["v_proj"], lw["o_proj"], lw["gate_proj"], lw["up_proj"],
+                      lw["down_proj"], oh, oh, od, od)
+    head = api.DeviceWeight.from_device(b, Q.Q6_K, W.gen_q6_k_device(torch, gen, cfg.vocab, cfg.hidden), cfg.vocab, cfg.hidden)
+    embed = torch.randn(cfg.vocab, cfg.hidden, device=dev, generator=gen).to(torch.bfloat16)
+    dec.set_head(embed, oh, head)
+    kc, vc, _, _ = dec.buffers()
+    kc.normal_(generator=gen)
+    vc.normal_(generator=gen)
+    st = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(st):
+        dec.reset(1, a.pos, st)
+        dec.step(st)
+        st.synchronize()
+        if a.eager:
+            def one():
+                dec.reset(1, a.pos, st)
+                dec.step(st)
+        else:
+            dec.reset(1, a.pos, st)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=st):
+                dec.step(torch.cuda.current_stream())
+            def one():
+                graph.replay()
+        for _ in range(3):
+            one()
+        dec.reset(1, a.pos, st)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(a.reps):
+            one()
+        e1.record(st)
+        st.synchronize()
+    b.device_status(st)
+    ms = e0.elapsed_time(e1) / a.reps
+    print(f"decoder step, {a.layers} layers, context {a.pos}.., {'eager' if a.eager else 'graph'}: {ms * 1e3:.1f} us per token, "
+          f"{ms * 1e3 / a.layers:.1f} us per layer", flush=True)
+    dec.release()
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -232,8 +353,22 @@ def main():
     p.add_argument("--x", default="f32", choices=["bf16", "f32"])
     p.add_argument("--copies", type=int, default=8)
     p.add_argument("--reps", type=int, default=40)
+    p = sub.add_parser("groupq")
+    p.add_argument("--bits", type=int, default=4, choices=[4, 8])
+    p.add_argument("--n", type=int, default=12288)
+    p.add_argument("--k", type=int, default=4096)
+    p.add_argument("--group", type=int, default=128)
+    p.add_argument("--m", type=int, default=1)
+    p.add_argument("--gptq", action="store_true")
+    p.add_argument("--reps", type=int, default=20)
+    p = sub.add_parser("decoder")
+    p.add_argument("--layers", type=int, default=4)
+    p.add_argument("--pos", type=int, default=2048)
+    p.add_argument("--eager", action="store_true")
+    p.add_argument("--reps", type=int, default=20)
     a = ap.parse_args()
-    {"linear": run_linear, "moe": run_moe, "codec": run_codec, "int8": run_int8}[a.cmd](a)
+    {"linear": run_linear, "moe": run_moe, "codec": run_codec, "int8": run_int8, "groupq": run_groupq,
+     "decoder": run_decoder}[a.cmd](a)
 
 
 if __name__ == "__main__":
