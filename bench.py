@@ -569,7 +569,7 @@ def sweep_variants(torch, backend, layers, gen, dev, peak_hbm):
 
 
 def prefill_32b(torch, backend, gen, dev, peak_tf, timed):
-    """BASELINE configuration 5 on one GPU: the seven projections of a Qwen3-32B layer (hidden 5120,
+    """The Qwen3-32B prefill configuration on one GPU: the seven projections of a Qwen3-32B layer (hidden 5120,
     64 query / 8 key-value heads x 128, FFN 25600) at 4096 tokens of bf16 activations, Q4_K and Q6_K
     weights, on the tensor-core path; per shape the time, TFLOP/s and the fraction of the measured
     bf16 peak, and the whole layer."""
@@ -612,7 +612,7 @@ def prefill_32b(torch, backend, gen, dev, peak_tf, timed):
 
 
 def moe_block(torch, backend, gen, dev, peak_hbm, peak_tf, timed):
-    """BASELINE configuration 4 on one GPU: one gpt-oss-20b MoE block (32 experts, top-4, hidden =
+    """The gpt-oss-20b configuration on one GPU: one gpt-oss-20b MoE block (32 experts, top-4, hidden =
     inter = 2880, MXFP4 experts in the [N, K/2] + [N, K/32] layout) at 64 tokens (one decode token of 64
     sequences: bound by the expert weights, 423 MB) and 4096 tokens (prefill: bound by the tensor
     cores, 2 * 16384 routed rows * 3 * 2880 * 2880 flop)."""
@@ -658,7 +658,7 @@ def _peak_tf():
 
 
 def prefill_32b_tp(torch, dist, backend, gen, dev, rank, world):
-    """BASELINE configuration 5 over N GPUs: one Qwen3-32B layer's projections at 4096 tokens, Q4_K,
+    """The Qwen3-32B prefill configuration over N GPUs: one Qwen3-32B layer's projections at 4096 tokens, Q4_K,
     Megatron split -- q / k / v / gate / up by rows (no exchange), o / down along K (13 / 12
     super-blocks per rank for down_proj at 8 ranks) with the [4096, 5120] bf16 partial outputs summed
     by NCCL's all-reduce, issued eagerly on the timing stream (never captured in a graph). Device
@@ -732,7 +732,7 @@ def prefill_32b_tp(torch, dist, backend, gen, dev, rank, world):
 
 
 def moe_block_ep(torch, dist, backend, dev, rank, world):
-    """BASELINE configuration 4 over N GPUs: one gpt-oss-20b MoE block (32 experts, top-4, hidden =
+    """The gpt-oss-20b configuration over N GPUs: one gpt-oss-20b MoE block (32 experts, top-4, hidden =
     inter = 2880, MXFP4) with the experts split over the ranks and the tokens sharded: each rank
     routes its own tokens, rows travel to the experts' owners and back by all-to-all (NCCL), the
     library's kernels gather, run the experts and combine. 64 tokens and 4096 tokens in all; device

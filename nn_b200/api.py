@@ -10,7 +10,7 @@ Same names, argument meaning and error behaviour as nn-core's
 of libnnq_b200.so; torch is used only to own device memory and streams.
 
 The reference is Rust and no Rust toolchain exists in this environment, so this mirror
-is Python over ctypes; a Rust shim would bind the same symbols (see INTEGRATION.md).
+is Python over ctypes; a Rust shim would bind the same symbols.
 """
 from __future__ import annotations
 
