@@ -193,8 +193,8 @@ def run_nnq(args, rank, world, local_rank):
     m = args.m
     # row-parallel partial outputs are summed by the library's one-shot all-reduce over peer memory
     # slots: 8 bytes per output row of the fused exchange + the record of the distributed argmax
-    # (and the [rows, hidden] f32 partial sums of the prompt pass, 64 rows at a time)
-    peer = comm.PeerComm(backend, rank, world, max_bytes=64 * W.HIDDEN * 4 + 256) if world > 1 else None
+    # (and the [rows, hidden] f32 partial sums of the prompt pass, 256 rows at a time)
+    peer = comm.PeerComm(backend, rank, world, max_bytes=256 * W.HIDDEN * 4 + 256) if world > 1 else None
     gen = torch.Generator(device=dev)
     gen.manual_seed(0x5EED)  # same weights on every rank, each keeps its shard
 

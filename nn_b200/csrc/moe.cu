@@ -42,67 +42,99 @@ __device__ __forceinline__ float ld_act<__nv_bfloat16>(const __nv_bfloat16 *p, i
 constexpr int kMaxExperts = 64;
 constexpr int kMaxTopK = 8;
 
-// One CTA per token: the 8 warps share the experts (warp w: experts w, w + 8, ...), every lane
-// accumulates a strided slice of the hidden dimension, shuffle tree per expert; warp 0 then does
-// the softmax and the top-k selection over the logits in shared memory.
-template <typename XT>
+// A CTA serves TOK consecutive tokens: their activations sit in shared memory as f32, the 8 warps
+// share the experts (warp w: experts w, w + 8, ...; four experts at a time so that four weight
+// loads are in flight per lane), every lane accumulates a strided slice of the hidden dimension,
+// shuffle tree per (token, expert); a router weight row is read once per TOK tokens. Warp t then does
+// the softmax and the top-k selection of token t over the logits in shared memory. The summation
+// order of a logit does not depend on TOK.
+template <typename XT, int TOK>
 __global__ void __launch_bounds__(256)
 moe_router_kernel(const XT *__restrict__ x, const float *__restrict__ rw, const float *__restrict__ rb,
                   int T, int H, int E, int top_k, int *__restrict__ idx, float *__restrict__ wt) {
     pdl_prologue();
-    extern __shared__ float xs[];          // the token's activations as f32, then E logits
-    float *logits = xs + H;
+    extern __shared__ float xs[];          // TOK tokens' activations as f32, then TOK x E logits
+    float *logits = xs + (size_t)TOK * H;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int tok = blockIdx.x;
-    if (tok >= T) return;
-    for (int h = threadIdx.x; h < H; h += 256) xs[h] = ld_act<XT>(x, (int64_t)tok * H + h);
+    const int tok0 = blockIdx.x * TOK;
+    if (tok0 >= T) return;
+    const int ntok = min(TOK, T - tok0);
+    for (int i = threadIdx.x; i < ntok * H; i += 256) xs[i] = ld_act<XT>(x, (int64_t)tok0 * H + i);
+    for (int i = ntok * H + threadIdx.x; i < TOK * H; i += 256) xs[i] = 0.0f;
     __syncthreads();
-    for (int e = warp; e < E; e += 8) {
-        const float *w = rw + (int64_t)e * H;
-        float acc = 0.0f;
-        for (int h = lane; h < H; h += 32) acc = fmaf(xs[h], __ldg(w + h), acc);
+    constexpr int EB = 4;
+    for (int e0 = warp; e0 < E; e0 += 8 * EB) {
+        const float *w[EB];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
-        if (lane == 0) logits[e] = acc + __ldg(rb + e);
-    }
-    __syncthreads();
-    if (warp != 0) return;
-    // lane e (and e + 32) holds expert e's logit
-    float l0 = lane < E ? logits[lane] : -CUDART_INF_F;
-    float l1 = lane + 32 < E ? logits[lane + 32] : -CUDART_INF_F;
-    // softmax over the E experts (max-subtracted, f32)
-    float mx = fmaxf(l0, l1);
+        for (int j = 0; j < EB; j++) w[j] = rw + (int64_t)min(e0 + 8 * j, E - 1) * H;   // past the end: repeats the last expert, not stored
+        float acc[TOK][EB];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
-    float p0 = lane < E ? expf(l0 - mx) : 0.0f;
-    float p1 = lane + 32 < E ? expf(l1 - mx) : 0.0f;
-    float sum = p0 + p1;
+        for (int t = 0; t < TOK; t++)
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
-    p0 = p0 / sum;
-    p1 = p1 / sum;
-    if (lane >= E) p0 = -1.0f;
-    if (lane + 32 >= E) p1 = -1.0f;
-    // top-k: k rounds of (largest probability, lowest index) selection
-    float sel_p = 0.0f, wsum = 0.0f;
-    int sel_e = 0;
-    for (int s = 0; s < top_k; s++) {
-        float best = p0 >= p1 ? p0 : p1;
-        int be = p0 >= p1 ? lane : lane + 32;
+            for (int j = 0; j < EB; j++) acc[t][j] = 0.0f;
+        for (int h = lane; h < H; h += 32) {
+            float wv[EB];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            float ob = __shfl_xor_sync(0xFFFFFFFFu, best, off);
-            int oe = __shfl_xor_sync(0xFFFFFFFFu, be, off);
-            if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+            for (int j = 0; j < EB; j++) wv[j] = __ldg(w[j] + h);
+#pragma unroll
+            for (int t = 0; t < TOK; t++) {
+                const float xv = xs[t * H + h];
+#pragma unroll
+                for (int j = 0; j < EB; j++) acc[t][j] = fmaf(xv, wv[j], acc[t][j]);
+            }
         }
-        if (be == lane) p0 = -1.0f;
-        if (be == lane + 32) p1 = -1.0f;
-        if (lane == s) { sel_p = best; sel_e = be; }
-        wsum += best;
+#pragma unroll
+        for (int t = 0; t < TOK; t++)
+#pragma unroll
+            for (int j = 0; j < EB; j++) {
+                float v = acc[t][j];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+                const int e = e0 + 8 * j;
+                if (lane == 0 && e < E) logits[t * E + e] = v + __ldg(rb + e);
+            }
     }
-    if (lane < top_k) {
-        idx[(int64_t)tok * top_k + lane] = sel_e;
-        wt[(int64_t)tok * top_k + lane] = sel_p / wsum;
+    __syncthreads();
+    for (int t = warp; t < ntok; t += 8) {
+        const int tok = tok0 + t;
+        const float *lg = logits + t * E;
+        // lane e (and e + 32) holds expert e's logit
+        float l0 = lane < E ? lg[lane] : -CUDART_INF_F;
+        float l1 = lane + 32 < E ? lg[lane + 32] : -CUDART_INF_F;
+        // softmax over the E experts (max-subtracted, f32)
+        float mx = fmaxf(l0, l1);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+        float p0 = lane < E ? expf(l0 - mx) : 0.0f;
+        float p1 = lane + 32 < E ? expf(l1 - mx) : 0.0f;
+        float sum = p0 + p1;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+        p0 = p0 / sum;
+        p1 = p1 / sum;
+        if (lane >= E) p0 = -1.0f;
+        if (lane + 32 >= E) p1 = -1.0f;
+        // top-k: k rounds of (largest probability, lowest index) selection
+        float sel_p = 0.0f, wsum = 0.0f;
+        int sel_e = 0;
+        for (int s = 0; s < top_k; s++) {
+            float best = p0 >= p1 ? p0 : p1;
+            int be = p0 >= p1 ? lane : lane + 32;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                float ob = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+                int oe = __shfl_xor_sync(0xFFFFFFFFu, be, off);
+                if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+            }
+            if (be == lane) p0 = -1.0f;
+            if (be == lane + 32) p1 = -1.0f;
+            if (lane == s) { sel_p = best; sel_e = be; }
+            wsum += best;
+        }
+        if (lane < top_k) {
+            idx[(int64_t)tok * top_k + lane] = sel_e;
+            wt[(int64_t)tok * top_k + lane] = sel_p / wsum;
+        }
     }
 }
 
@@ -351,23 +383,49 @@ moe_nk_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict__ scal
     }
 }
 
-// h[r, j] = clamp(silu(gu[r, j]), -limit, limit) * gu[r, I + j]   (gate = first half, up = second half)
-__global__ void moe_swiglu_kernel(const float *__restrict__ gu, float *__restrict__ h, const int *__restrict__ offset,
-                                  int E, int inter, float limit, int slices, size_t slice_stride,
-                                  __nv_bfloat16 *__restrict__ h_bf16) {
+// h[r, j] = clamp(silu(gu[r, j]), -limit, limit) * gu[r, I + j]   (gate = first half, up = second half).
+// CTA (r, c) handles row r, columns [1024 c, 1024 c + 1024), four per thread. With h_bf16 given (the
+// tensor-core second product reads bf16) the f32 copy is not written.
+__device__ __forceinline__ float swiglu_one(float g, float u, float limit) {
+    float s = g / (1.0f + expf(-g));
+    s = fminf(fmaxf(s, -limit), limit);
+    return s * u;
+}
+__global__ void __launch_bounds__(256)
+moe_swiglu_kernel(const float *__restrict__ gu, float *__restrict__ h, const int *__restrict__ offset,
+                  int E, int inter, float limit, int slices, size_t slice_stride, __nv_bfloat16 *__restrict__ h_bf16) {
     pdl_prologue();
-    const int64_t total = (int64_t)offset[E] * inter;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        int64_t r = i / inter, j = i % inter;
+    const int64_t r = blockIdx.x;
+    if (r >= offset[E]) return;
+    const int j0 = blockIdx.y * 1024 + threadIdx.x * 4;
+    if (j0 >= inter) return;
+    const float *grow = gu + r * 2 * inter;
+    float out[4];
+    if (slices == 1 && (inter & 3) == 0) {
+        const float4 g = *reinterpret_cast<const float4 *>(grow + j0);
+        const float4 u = *reinterpret_cast<const float4 *>(grow + inter + j0);
+        out[0] = swiglu_one(g.x, u.x, limit);
+        out[1] = swiglu_one(g.y, u.y, limit);
+        out[2] = swiglu_one(g.z, u.z, limit);
+        out[3] = swiglu_one(g.w, u.w, limit);
+        if (h_bf16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(out[0], out[1]), hi = __floats2bfloat162_rn(out[2], out[3]);
+            *reinterpret_cast<uint2 *>(h_bf16 + r * inter + j0) = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+        } else {
+            *reinterpret_cast<float4 *>(h + r * inter + j0) = make_float4(out[0], out[1], out[2], out[3]);
+        }
+        return;
+    }
+    for (int q = 0; q < 4 && j0 + q < inter; q++) {
+        const int j = j0 + q;
         float g = 0.0f, u = 0.0f;
         for (int z = 0; z < slices; z++) {   // K slices of the first product, in order
-            g += gu[z * slice_stride + r * 2 * inter + j];
-            u += gu[z * slice_stride + r * 2 * inter + inter + j];
+            g += grow[z * slice_stride + j];
+            u += grow[z * slice_stride + inter + j];
         }
-        float s = g / (1.0f + expf(-g));
-        s = fminf(fmaxf(s, -limit), limit);
-        h[i] = s * u;
-        if (h_bf16) h_bf16[i] = __float2bfloat16_rn(s * u);   // input of the tensor-core second product
+        const float v = swiglu_one(g, u, limit);
+        if (h_bf16) h_bf16[r * inter + j] = __float2bfloat16_rn(v);
+        else h[r * inter + j] = v;
     }
 }
 
@@ -533,16 +591,22 @@ static nnq_status launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, con
 // the router keeps one token's activations in shared memory: allow more than the default 48 KB
 template <typename XT>
 static cudaError_t launch_router(const nnq_moe *m, const XT *x, int64_t T, int *idx, float *wt, cudaStream_t st) {
-    const size_t smem = (size_t)(m->hidden + kMaxExperts) * 4;
-    static bool configured[64] = {};
+    // eight tokens per CTA once there are enough tokens to fill the machine that way (and their
+    // activations fit in shared memory): the router weights are then read once per eight tokens
+    const bool many = T >= 1024 && (size_t)8 * (m->hidden + kMaxExperts) * 4 <= 200 * 1024;
+    const int tok = many ? 8 : 1;
+    const size_t smem = (size_t)tok * (m->hidden + kMaxExperts) * 4;
+    static bool configured[64][2] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !configured[dev][many]) {
+        cudaError_t e = many ? cudaFuncSetAttribute(moe_router_kernel<XT, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                             : cudaFuncSetAttribute(moe_router_kernel<XT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
-        configured[dev] = true;
+        configured[dev][many] = true;
     }
-    moe_router_kernel<XT><<<(int)T, 256, smem, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, m->n_experts, m->top_k, idx, wt);
+    if (many) moe_router_kernel<XT, 8><<<(int)((T + 7) / 8), 256, smem, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, m->n_experts, m->top_k, idx, wt);
+    else moe_router_kernel<XT, 1><<<(int)T, 256, smem, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, m->n_experts, m->top_k, idx, wt);
     return cudaGetLastError();
 }
 
@@ -608,8 +672,7 @@ static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, 
     }
     nnq_status prc = launch_product<XT>(ctx, m, true, x, s.rowtok, k, s, s.gu, total, st);
     if (prc != NNQ_OK) return prc;
-    int64_t hi = (int64_t)total * m->inter;
-    launch_pdl(moe_swiglu_kernel, dim3((unsigned)((hi + 255) / 256 < 4096 ? (hi + 255) / 256 : 4096)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
+    launch_pdl(moe_swiglu_kernel, dim3((unsigned)total, (unsigned)((m->inter + 1023) / 1024)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
     prc = launch_product<float>(ctx, m, false, s.h, nullptr, k, s, s.o, total, st);
     if (prc != NNQ_OK) return prc;
     launch_pdl(moe_combine_kernel, dim3((unsigned)T, T < 1024 ? 4 : 1), dim3(256), st, s.o, idx, wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
