@@ -110,6 +110,89 @@ allreduce_oneshot_kernel(uint8_t *const *peers, int rank, int world, size_t slot
     if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned *>(local) = seq;
 }
 
+// The same exchange for messages of tens of KB to MB (the [rows, hidden] partial sums of a prompt
+// pass): up to 64 CTAs, each owning a contiguous run of 16-byte units. A CTA pushes its run to every
+// peer; the last CTA of the rank to have pushed publishes the rank's flags; every CTA waits (bounded)
+// for every peer's flag and sums its run in rank order; the last CTA to finish advances the epoch. No
+// CTA waits for another CTA of its own grid, so the grid need not be resident at once. The two arrival
+// counters live at bytes 132 and 136 of the buffer header and are left at zero.
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_multi_kernel(uint8_t *const *peers, int rank, int world, size_t slot_bytes, T *buf, int64_t units, int *status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint8_t *local = peers[rank];
+    __shared__ unsigned seq_s, limit_s;
+    __shared__ int failed_s, last_s;
+    if (threadIdx.x == 0) {
+        seq_s = *reinterpret_cast<volatile unsigned *>(local) + 1u;
+        limit_s = comm_spin_limit(local);
+        failed_s = 0;
+    }
+    __syncthreads();
+    const unsigned seq = seq_s, limit = limit_s;
+    const int parity = (int)(seq & 1u);
+    const int64_t per = (units + gridDim.x - 1) / gridDim.x;
+    const int64_t lo = (int64_t)blockIdx.x * per, hi = lo + per < units ? lo + per : units;
+    const uint4 *src = reinterpret_cast<const uint4 *>(buf);
+    for (int p = 0; p < world; p++) {
+        uint4 *dst = reinterpret_cast<uint4 *>(peers[p] + comm_data_offset(parity, rank, world, slot_bytes));
+        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = src[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    unsigned *pushed = reinterpret_cast<unsigned *>(local + 132), *done = reinterpret_cast<unsigned *>(local + 136);
+    if (threadIdx.x == 0) {
+        last_s = atomicAdd(pushed, 1u) == gridDim.x - 1;
+        if (last_s) *pushed = 0;
+    }
+    __syncthreads();
+    if (last_s && threadIdx.x < world) {
+        __threadfence_system();
+        *(reinterpret_cast<volatile unsigned *>(peers[threadIdx.x] + 64) + rank) = seq;
+    }
+    if (threadIdx.x < world) {
+        volatile unsigned *my_flag = reinterpret_cast<volatile unsigned *>(local + 64) + threadIdx.x;
+        unsigned spins = 0;
+        while ((int)(*my_flag - seq) < 0) {
+            if (++spins > limit) {
+                failed_s = 1;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    __threadfence_system();
+    if (failed_s) {
+        if (threadIdx.x == 0) atomicExch(status, 1);
+    } else {
+        constexpr int PER = 16 / (int)sizeof(T);
+        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            float acc[PER];
+#pragma unroll
+            for (int j = 0; j < PER; j++) acc[j] = 0.0f;
+            for (int r = 0; r < world; r++) {
+                const uint4 *slot = reinterpret_cast<const uint4 *>(local + comm_data_offset(parity, r, world, slot_bytes));
+                uint4 v;
+                asm volatile("ld.global.cv.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(slot + i));
+                const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+                for (int j = 0; j < PER; j++) acc[j] += to_f32<T>(e[j]);
+            }
+            uint4 o;
+            T *oe = reinterpret_cast<T *>(&o);
+#pragma unroll
+            for (int j = 0; j < PER; j++) oe[j] = from_f32<T>(acc[j]);
+            reinterpret_cast<uint4 *>(buf)[i] = o;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
+        *done = 0;
+        *reinterpret_cast<volatile unsigned *>(local) = seq;
+    }
+}
+
 nnq_status comm_view(nnq_comm *c, CommView *out) {
     if (!c || !out) return NNQ_ERR_INVALID_ARG;
     for (int p = 0; p < c->world; p++)
@@ -228,8 +311,12 @@ nnq_status nnq_comm_all_reduce(nnq_comm *c, void *buf_dev, nnq_dtype dt, int64_t
         if (!c->peer[p]) return fail(ctx, NNQ_ERR_INVALID_ARG, "peer %d has not been opened", p);
     nnq_status s = check_cuda(ctx, cudaSetDevice(ctx->device), "cudaSetDevice");
     if (s != NNQ_OK) return s;
+    // large, 16-byte granular messages: the multi-CTA form
+    const size_t bytes = (size_t)count * es;
+    const bool multi = bytes >= 32 * 1024 && bytes % 16 == 0 && !((uintptr_t)buf_dev & 15u) && c->slot_bytes % 16 == 0;
+    const int64_t units = (int64_t)(bytes / 16);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1);
+    cfg.gridDim = dim3(multi ? (unsigned)(units / 1024 < 64 ? (units / 1024 < 1 ? 1 : units / 1024) : 64) : 1u);
     cfg.blockDim = dim3(512);
     cfg.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attr[1];
@@ -243,10 +330,12 @@ nnq_status nnq_comm_all_reduce(nnq_comm *c, void *buf_dev, nnq_dtype dt, int64_t
     cudaError_t e;
     if (dt == NNQ_F32) {
         float *b = (float *)buf_dev;
-        e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<float>, table, c->rank, c->world, c->slot_bytes, b, cnt, status);
+        e = multi ? cudaLaunchKernelEx(&cfg, allreduce_multi_kernel<float>, table, c->rank, c->world, c->slot_bytes, b, units, status)
+                  : cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<float>, table, c->rank, c->world, c->slot_bytes, b, cnt, status);
     } else {
         __nv_bfloat16 *b = (__nv_bfloat16 *)buf_dev;
-        e = cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<__nv_bfloat16>, table, c->rank, c->world, c->slot_bytes, b, cnt, status);
+        e = multi ? cudaLaunchKernelEx(&cfg, allreduce_multi_kernel<__nv_bfloat16>, table, c->rank, c->world, c->slot_bytes, b, units, status)
+                  : cudaLaunchKernelEx(&cfg, allreduce_oneshot_kernel<__nv_bfloat16>, table, c->rank, c->world, c->slot_bytes, b, cnt, status);
     }
     ctx->launches++;
     return check_cuda(ctx, e, "all-reduce launch");

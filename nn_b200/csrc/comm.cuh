@@ -2,7 +2,8 @@
 // product kernel that pushes its partial outputs straight into the peers' slots.
 //   [0, 64)     epoch: sequence number of the last completed exchange
 //   [64, 128)   flags: u32 per source rank, the sequence number that rank has published
-//   [128, 192)  arrival counter of the fused product kernel (CTAs that finished pushing)
+//   [128, 192)  arrival counters: u32 at 128 of the fused product kernel (CTAs that finished pushing),
+//               at 132 / 136 of the multi-CTA all-reduce (CTAs that pushed / that finished)
 //   [192, 196)  bound of every flag wait of kernels that use this communicator, in polls
 //   [256, ...)  data[parity][source rank][slot_bytes]
 #pragma once

@@ -27,6 +27,18 @@ def test_world_one_is_identity_and_sized():
     with pytest.raises(api.Unsupported):
         c.all_reduce(torch.zeros(2000, device="cuda:0"))
     c.release()
+    # messages from 32 KB on take the multi-CTA kernel (several CTAs, 16-byte units, a ragged last run)
+    big = comm.PeerComm(b, 0, 1, max_bytes=3 << 20)
+    for dt, n in ((torch.float32, 8192), (torch.float32, 700_004), (torch.bfloat16, 1_000_008), (torch.float32, 8193)):
+        x = torch.randn(n, device="cuda:0").to(dt)
+        want = x.clone()
+        for _ in range(3):
+            big.all_reduce(x)
+        big.all_reduce(torch.ones(16, device="cuda:0"))    # the small kernel shares the sequence number
+        torch.cuda.synchronize()
+        b.device_status()
+        assert torch.equal(x, want)
+    big.release()
 
 
 def test_fused_linear_world_one_matches_plain_product():
@@ -90,6 +102,21 @@ def test_a_peer_that_never_arrives_ends_in_a_timeout_status():
         b.device_status()
     assert e.value.kind == "Timeout"
     b.device_status()                     # cleared by the read
+    # the multi-CTA form of the all-reduce gives up the same way, and leaves its counters usable
+    cb0 = comm.PeerComm(b, 0, 2, max_bytes=1 << 20, exchange_handles=False)
+    cb1 = comm.PeerComm(b, 1, 2, max_bytes=1 << 20, exchange_handles=False)
+    bb = [cb0.local_buffer(), cb1.local_buffer()]
+    cb0.open_local_peers(bb)
+    cb1.open_local_peers(bb)
+    cb0.set_spin_limit(2000)
+    for _ in range(2):
+        cb0.all_reduce(torch.ones(100_000, device="cuda:0"))
+        torch.cuda.synchronize()
+        with pytest.raises(api.BackendFailure) as e:
+            b.device_status()
+        assert e.value.kind == "Timeout"
+    cb0.release()
+    cb1.release()
     # the fused product + exchange kernel gives up the same way
     from nn_b200 import formats as F
     from nn_b200.formats import QuantFormat as Q
@@ -136,7 +163,7 @@ def _worker(rank, world, port, out):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         b = api.Backend(rank)
-        c = comm.PeerComm(b, rank, world, max_bytes=1 << 15)
+        c = comm.PeerComm(b, rank, world, max_bytes=1 << 21)
         dev = torch.device("cuda", rank)
         ok = True
         for it in range(20):
@@ -149,6 +176,22 @@ def _worker(rank, world, port, out):
                 want += parts[r]
             torch.cuda.synchronize()
             ok = ok and torch.equal(x.cpu(), want)
+        b.device_status()
+        # large messages (multi-CTA kernel), f32 and bf16, alternating with small ones
+        for it, (dt, n) in enumerate(((torch.float32, 300_000), (torch.bfloat16, 500_000), (torch.float32, 524_288))):
+            g = torch.Generator().manual_seed(500 + it)
+            parts = [torch.randn(n, generator=g).to(dt) for _ in range(world)]
+            x = parts[rank].to(dev)
+            c.all_reduce(x)
+            want = parts[0].float().clone()
+            for r in range(1, world):
+                want += parts[r].float()
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(x.cpu(), want.to(dt))
+            z = torch.full((64,), float(rank + 1), device=dev)
+            c.all_reduce(z)
+            torch.cuda.synchronize()
+            ok = ok and bool((z == float(world * (world + 1) // 2)).all())
         b.device_status()
         # row-parallel product fused with its all-reduce against the unsharded product
         from nn_b200 import formats as F
