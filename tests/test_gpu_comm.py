@@ -218,6 +218,37 @@ def _worker(rank, world, port, out):
             torch.cuda.synchronize()
             ok = ok and bool((z == float(world * (world + 1) // 2)).all())
         b.device_status()
+        # the same exchange inside a compiled plan: two row-parallel groups and a plain one per run
+        from nn_b200 import plan
+        pl = plan.ProductPlan(b, torch.bfloat16, torch.float32)
+        cases = []
+        for i, (pn, pk) in enumerate(((520, 8192), (260, 4096))):
+            pw, _ = F.gen_weight(Q.Q4_K, 40 + i, pn, pk)
+            pfull = api.QuantizedTensor(pw, Q.Q4_K, [pn, pk], None, b)
+            pshard = pfull.shard(1, rank, world)
+            px = torch.from_numpy(F.gen_activations(300 + i, 1, pk, bf16=True)).to(dev).to(torch.bfloat16)
+            pks = pk // world
+            pxs = px[:, rank * pks:(rank + 1) * pks].contiguous()
+            py = torch.full((pn,), float("nan"), device=dev)
+            pl.add_reduced(c, pshard, pxs, py)
+            cases.append((pfull, pshard, px, pxs, py))
+        pl.finalize()
+        for it in range(3):
+            pl.run()
+            z = torch.full((64,), float(rank + 1), device=dev)
+            c.all_reduce(z)
+            torch.cuda.synchronize()
+            ok = ok and bool((z == float(world * (world + 1) // 2)).all())
+            for pfull, pshard, px, pxs, py in cases:
+                want = api.quantized_linear(px, pfull, None, out_dtype=torch.float32).reshape(-1)
+                torch.cuda.synchronize()
+                ok = ok and float((py - want).abs().max()) <= 1e-4 * float(want.abs().max())
+                sums = [None] * world
+                dist.all_gather_object(sums, py.cpu().numpy().tobytes())
+                ok = ok and all(s_ == sums[0] for s_ in sums)
+                py.fill_(float("nan"))
+        b.device_status()
+        pl.release()
         oks = [None] * world
         dist.all_gather_object(oks, bool(ok))     # a wrong result on any rank fails the test
         if rank == 0:

@@ -224,3 +224,42 @@ def test_plan_rejects_what_it_cannot_run():
     pl.release()
     for t in (t8, t4, t4b):
         t.release()
+
+
+def test_exchanged_groups_world_one_and_mixed_with_other_exchanges():
+    """Row-parallel groups whose partial sums go through a communicator's slots inside the kernel,
+    on one rank: same values as the plain products, the communicator's sequence number advances by
+    the number of exchanged groups per run, and plain all-reduces on the same communicator still
+    line up afterwards."""
+    from nn_b200 import comm
+    b = api.gpu_backend()
+    shapes = [(520, 2048), (200, 1024), (1030, 512)]
+    c = comm.PeerComm(b, 0, 1, max_bytes=max(n for n, _ in shapes) * 8)
+    pl = plan.ProductPlan(b, torch.bfloat16, torch.float32)
+    keep = []
+    for i, (n, k) in enumerate(shapes):
+        (w, t), = _weights([(n, k)], 2000 + i)
+        x = F.gen_activations(300 + i, 1, k, bf16=True)
+        xt = torch.from_numpy(x).to(DEV).to(torch.bfloat16)
+        y = torch.full((n,), float("nan"), device=DEV)
+        bias = torch.from_numpy((F.Stream(9 + i).normal(n) * 0.5).astype(np.float32)).to(DEV) if i == 1 else None
+        if i == 2:
+            pl.add([t], xt, [y])                 # a plain group between exchanged ones
+        else:
+            pl.add_reduced(c, t, xt, y, bias)
+        keep.append((w, t, x, y, bias, n, k))
+    pl.finalize()
+    for rep in range(3):
+        pl.run()
+        z = torch.full((64,), 2.0, device=DEV)
+        c.all_reduce(z)                          # shares the sequence number with the plan's exchanges
+        torch.cuda.synchronize()
+        b.device_status()
+        assert bool((z == 2.0).all())
+        for w, t, x, y, bias, n, k in keep:
+            _check(y, Q.Q4_K, w, x, bias.cpu().numpy() if bias is not None else None, n, k)
+            y.fill_(float("nan"))
+    pl.release()
+    c.release()
+    for _, t, *_ in keep:
+        t.release()
