@@ -512,7 +512,10 @@ NNQ_API nnq_status nnq_moe_forward_static(nnq_ctx *ctx, const nnq_moe *m, const 
  * identical bits everywhere), is a single kernel without host synchronisation (graph-capturable),
  * and must be called the same number of times, in the same order, by every rank. A peer that
  * never arrives makes the bounded device wait run out: nnq_device_status then reports
- * NNQ_ERR_TIMEOUT and the buffer contents are undefined. */
+ * NNQ_ERR_TIMEOUT and the buffer contents are undefined. A rank whose wait ran out has still
+ * advanced its sequence number while the late peer has not, so after a timeout the ranks no longer
+ * agree on it: destroy the communicators of all ranks and create new ones (there is no in-place
+ * resynchronisation). Messages of 32 KB and more use several CTAs; smaller ones a single CTA. */
 NNQ_API nnq_status nnq_comm_create(nnq_ctx *ctx, int rank, int world, size_t max_bytes, nnq_comm **out);
 NNQ_API nnq_status nnq_comm_get_handle(nnq_comm *c, void *handle64);
 NNQ_API nnq_status nnq_comm_open_peers(nnq_comm *c, const void *handles);

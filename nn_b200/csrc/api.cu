@@ -23,6 +23,7 @@ nnq_status fail(nnq_ctx *ctx, nnq_status s, const char *fmt, ...) {
 
 nnq_status check_cuda(nnq_ctx *ctx, cudaError_t e, const char *what) {
     if (e == cudaSuccess) return NNQ_OK;
+    cudaGetLastError();   // the error has been taken here: a later launch check must not meet it again
     nnq_status s = e == cudaErrorMemoryAllocation ? NNQ_ERR_OUT_OF_MEMORY : NNQ_ERR_DISPATCH_FAILED;
     return fail(ctx, s, "%s: %s", what, cudaGetErrorString(e));
 }

@@ -460,3 +460,24 @@ def test_unquantized_weights_are_bit_exact_at_one_token():
         assert np.array_equal(deq.view(np.uint32), orc.dequantize(fmt, w, n * k).reshape(n, k).view(np.uint32))
         t.release()
         _run(fmt, n, k, 1, x_bf16=False, y_bf16=False, with_bias=True, seed=12)
+
+
+def test_failed_staging_growth_leaves_the_context_usable():
+    """A host call whose staging buffers cannot be allocated returns OutOfMemory before it touches
+    the caller's buffers, and the next host call reallocates and gives the right answer."""
+    n, k = 64, 512
+    w, _ = F.gen_weight(Q.Q4_K, 18, n, k)
+    t = api.from_quantized(w, Q.Q4_K, [n, k])
+    x = F.gen_activations(19, 2, k, bf16=False)
+    want = api.quantized_linear(x, t, None)
+    b = t.backend
+    y = np.zeros((2, n), np.float32)
+    for _ in range(2):
+        # 2^36 rows of 512 floats: the pinned allocation is refused; only the sizes are read before that
+        st = b._lib.nnq_linear_host(b._ctx, t.handle(), x.ctypes.data, api.F32, 1 << 36, None, y.ctypes.data, api.F32)
+        with pytest.raises(api.BackendFailure) as e:
+            b.check(st)
+        assert e.value.kind in ("OutOfMemory", "DispatchFailed")   # the runtime's word for an impossible size
+        got = api.quantized_linear(x, t, None)
+        assert np.array_equal(got, want)
+    t.release()
