@@ -287,6 +287,16 @@ class GgufFile:
         if info is None:
             raise TensorNotFound(name)
         fmt = QUANT_OF.get(info.dtype)
+        if fmt is None and info.dtype in ("F32", "BF16", "F16"):
+            # unquantized tensors go through the same entry points as dense weights (the reference's
+            # read_tensor_f32 passthrough, reader.rs:253-284): f32 and bf16 as stored, f16 widened
+            # exactly to f32
+            from .formats import QuantFormat
+            raw = self.tensor_data(name)
+            if info.dtype == "F16":
+                raw = raw.view("<f2").astype(np.float32).view(np.uint8)
+            dense = QuantFormat.BF16_DENSE if info.dtype == "BF16" else QuantFormat.F32_DENSE
+            return api.QuantizedTensor(raw, dense, info.shape, None, backend)
         if fmt is None:
             raise api.Unsupported(f"{name}: no quantized product for GGUF dtype {info.dtype}")
         return api.QuantizedTensor(self.tensor_data(name), fmt, info.shape, None, backend)

@@ -197,11 +197,15 @@ def test_open_maps_the_file_and_returns_raw_blocks(tmp_path):
 
 def test_quantized_refuses_formats_without_a_product():
     from nn_b200 import api
-    b = G.write_gguf(None, {}, [("w", [1, 32], "Q8_1", np.zeros(40, np.uint8)), ("x", [4], "F32", np.zeros(4, "<f4"))])
+    b = G.write_gguf(None, {}, [("w", [1, 32], "Q8_1", np.zeros(40, np.uint8)), ("x", [4], "I32", np.zeros(4, "<i4")),
+                                ("v", [4], "F32", np.zeros(4, "<f4"))])
     f = G.GgufFile.from_bytes(b)
     for name in ("w", "x"):
         with pytest.raises(api.Unsupported):
             f.quantized(name)
+    # an unquantized tensor is a dense weight of the same entry points: whole 32-value units only
+    with pytest.raises(api.InvalidShape):
+        f.quantized("v")
 
 
 def test_qwen3_name_map():

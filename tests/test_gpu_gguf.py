@@ -32,21 +32,37 @@ def _write(path, tied, seed=5):
         tensors.append((name, [n, k], GG[fmt], raw))
         return orc.dequantize(fmt, raw, n * k, None).reshape(n, k)
 
+    def dense(name, kind, n, k, sd):
+        v = (F.Stream(sd).normal(n * k) * 0.05).astype(np.float32)
+        if kind == "F16":
+            stored = v.astype("<f2")
+            w = stored.astype(np.float32)
+        elif kind == "BF16":
+            stored = F.to_bf16_bits(v).astype("<u2")
+            w = F.bf16_bits_to_f32(stored)
+        else:
+            stored, w = v, v
+        tensors.append((name, [n, k], kind, stored))
+        return np.asarray(w, np.float32).reshape(n, k)
+
     def norm(name, n):
         v = (1.0 + 0.1 * s.normal(n)).astype(np.float32)
         tensors.append((name, [n], "F32", v))
         return v
 
     # every GGUF format the library multiplies with appears in some projection
+    # (and, in the second layer, the unquantized tensor types a file may carry for a projection)
     fmts = [{"q": Q.Q4_K, "k": Q.Q8_0, "v": Q.Q6_K, "o": Q.Q4_K, "gate": Q.Q4_0, "up": Q.Q4_1, "down": Q.Q4_K},
-            {"q": Q.Q5_K, "k": Q.Q5_0, "v": Q.Q5_1, "o": Q.Q3_K, "gate": Q.Q2_K, "up": Q.Q5_K, "down": Q.Q5_0}]
+            {"q": Q.Q5_K, "k": "F16", "v": "BF16", "o": Q.Q3_K, "gate": Q.Q2_K, "up": "F32", "down": Q.Q5_0}]
     gname = {"q": "attn_q", "k": "attn_k", "v": "attn_v", "o": "attn_output", "gate": "ffn_gate", "up": "ffn_up", "down": "ffn_down"}
     for li in range(LAYERS):
         shapes = [("q", HEADS * HD, HID), ("k", KV * HD, HID), ("v", KV * HD, HID), ("o", HID, HEADS * HD),
                   ("gate", FFN, HID), ("up", FFN, HID), ("down", HID, FFN)]
         L = {}
         for i, (nm, n, k) in enumerate(shapes):
-            L[nm] = qw(f"blk.{li}.{gname[nm]}.weight", fmts[li % 2][nm], n, k, seed + 10 * li + i)
+            kind = fmts[li % 2][nm]
+            make = dense if isinstance(kind, str) else qw
+            L[nm] = make(f"blk.{li}.{gname[nm]}.weight", kind, n, k, seed + 10 * li + i)
         L["in_norm"] = norm(f"blk.{li}.attn_norm.weight", HID)
         L["post_norm"] = norm(f"blk.{li}.ffn_norm.weight", HID)
         L["q_norm"] = norm(f"blk.{li}.attn_q_norm.weight", HD)
