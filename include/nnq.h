@@ -594,7 +594,7 @@ NNQ_API nnq_status nnq_decoder_reset(nnq_decoder *d, int token, int pos, void *s
  * stores the argmax as the next token and advances the position */
 NNQ_API nnq_status nnq_decoder_step(nnq_decoder *d, void *stream);
 /* Prompt pass: runs `count` prompt tokens (host array) through the decoder at positions
- * start_pos .. start_pos + count - 1 in blocks of up to 256 rows -- the products on the M > 16 paths,
+ * start_pos .. start_pos + count - 1 in blocks of up to 1024 rows -- the products on the M > 16 paths,
  * attention under the causal mask (every row sees the cache up to its own position:
  * crates/nn-qwen3/src/forward_common.rs:55-64,189-204, crates/nn-core/src/layers/attention/sdpa.rs:118-141)
  * -- fills the caches, leaves the logits of the last prompt token in the logits buffer, stores its

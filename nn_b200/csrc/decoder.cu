@@ -59,6 +59,10 @@ namespace nnq {
 
 constexpr int kAttnRanges = 32;   // CTAs per kv head in the decode step's attention
 constexpr int kAttnWarps = 4;
+// Rows of a prompt that go through the layers together: large enough that the products run on the
+// decode-once tensor path with several row tiles per weight tile (about 210 KB of buffers per row at
+// the Qwen3-8B shape).
+constexpr int kPrefillRows = 1024;
 constexpr int kArgmaxBlocks = 128;
 
 __device__ __forceinline__ float block_sum(float v, float *red) {
@@ -494,85 +498,92 @@ dec_qk_rope_rows_kernel(const float *__restrict__ q, const float *__restrict__ k
     else kcache[((size_t)(head - n_heads) * max_seq + pos) * hd + d] = y;
 }
 
-// Causal attention of a block of query rows over the cache: one warp per (kv head, row) serves the
-// G query heads of the group over keys 0 .. pos0 + row (the mask of the reference's prompt pass:
-// crates/nn-core/src/layers/attention/sdpa.rs:118-141), same batch-of-32-keys scheme as the decode
-// kernel, normalised output written directly.
-template <int G>
+// Causal attention of a block of query rows over the cache: one warp per (kv head, R consecutive
+// rows) serves the G query heads of the group for all R rows (G * R = 16 query vectors in shared
+// memory), so that a key / value row is read once per R rows; row r sees keys 0 .. pos0 + r (the mask
+// of the reference's prompt pass: crates/nn-core/src/layers/attention/sdpa.rs:118-141). Same
+// batch-of-32-keys scheme as the decode kernel, normalised output written directly.
+template <int G, int R>
 __global__ void __launch_bounds__(32)
 dec_attn_rows_kernel(const float *__restrict__ qrot, const float *__restrict__ kcache, const float *__restrict__ vcache, int pos0,
-                     float scale, void *__restrict__ out, int act_dt, int n_heads, int hd, int max_seq) {
-    __shared__ __align__(16) float qs[G][128];
-    const int kvh = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
-    const int j1 = pos0 + row + 1;
-    const size_t qoff = (size_t)row * n_heads * hd;
+                     int n, float scale, void *__restrict__ out, int act_dt, int n_heads, int hd, int max_seq) {
+    constexpr int P = G * R;   // pair p = r * G + g
+    __shared__ __align__(16) float qs[P][128];
+    const int kvh = blockIdx.x, r0 = blockIdx.y * R, lane = threadIdx.x;
+    const int rows = min(R, n - r0);
+    const int jmax = pos0 + r0 + rows;   // keys the last row of this block sees
 #pragma unroll
-    for (int g = 0; g < G; g++)
-        *reinterpret_cast<float4 *>(&qs[g][4 * lane]) = *reinterpret_cast<const float4 *>(qrot + qoff + (kvh * G + g) * hd + 4 * lane);
+    for (int p = 0; p < P; p++) {
+        const int row = r0 + min(p / G, rows - 1);   // rows past the end repeat the last one; not stored
+        *reinterpret_cast<float4 *>(&qs[p][4 * lane]) =
+            *reinterpret_cast<const float4 *>(qrot + (size_t)row * n_heads * hd + (kvh * G + p % G) * hd + 4 * lane);
+    }
     __syncwarp();
-    float m[G], l[G];
-    float4 acc[G];
+    float m[P], l[P];
+    float4 acc[P];
 #pragma unroll
-    for (int g = 0; g < G; g++) {
-        m[g] = -INFINITY;
-        l[g] = 0.0f;
-        acc[g] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int p = 0; p < P; p++) {
+        m[p] = -INFINITY;
+        l[p] = 0.0f;
+        acc[p] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
     const float *kb = kcache + (size_t)kvh * max_seq * hd, *vb = vcache + (size_t)kvh * max_seq * hd;
-    for (int b0 = 0; b0 < j1; b0 += 32) {
+    for (int b0 = 0; b0 < jmax; b0 += 32) {
         const int j = b0 + lane;
-        const bool valid = j < j1;
-        const float4 *krow = reinterpret_cast<const float4 *>(kb + (size_t)(valid ? j : b0) * hd);
-        float dot[G];
+        const float4 *krow = reinterpret_cast<const float4 *>(kb + (size_t)(j < jmax ? j : b0) * hd);
+        float dot[P];
 #pragma unroll
-        for (int g = 0; g < G; g++) dot[g] = 0.0f;
-#pragma unroll 16
+        for (int p = 0; p < P; p++) dot[p] = 0.0f;
+#pragma unroll 8
         for (int d4 = 0; d4 < 32; d4++) {
             const float4 kv = krow[d4];
 #pragma unroll
-            for (int g = 0; g < G; g++) {
-                const float4 qv = *reinterpret_cast<const float4 *>(&qs[g][4 * d4]);
-                dot[g] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, dot[g]))));
+            for (int p = 0; p < P; p++) {
+                const float4 qv = *reinterpret_cast<const float4 *>(&qs[p][4 * d4]);
+                dot[p] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, dot[p]))));
             }
         }
-        float p[G];
 #pragma unroll
-        for (int g = 0; g < G; g++) {
-            const float sc = valid ? dot[g] * scale : -INFINITY;
+        for (int p = 0; p < P; p++) {
+            // key j is visible to row r0 + p / G up to position pos0 + row; the first batch holds key 0
+            // for every row, so the running maximum is finite from then on
+            const bool valid = j <= pos0 + r0 + min(p / G, rows - 1);
+            const float sc = valid ? dot[p] * scale : -INFINITY;
             float bm = sc;
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, off));
-            const float mn = fmaxf(m[g], bm);
-            const float corr = expf(m[g] - mn);
-            p[g] = expf(sc - mn);
-            float ps = p[g];
+            const float mn = fmaxf(m[p], bm);
+            const float corr = expf(m[p] - mn);
+            dot[p] = expf(sc - mn);   // the probability, kept in place of the score
+            float ps = dot[p];
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xFFFFFFFFu, ps, off);
-            l[g] = l[g] * corr + ps;
-            acc[g].x *= corr; acc[g].y *= corr; acc[g].z *= corr; acc[g].w *= corr;
-            m[g] = mn;
+            l[p] = l[p] * corr + ps;
+            acc[p].x *= corr; acc[p].y *= corr; acc[p].z *= corr; acc[p].w *= corr;
+            m[p] = mn;
         }
-        const int nb = min(32, j1 - b0);
+        const int nb = min(32, jmax - b0);
         for (int jj = 0; jj < nb; jj++) {
             const float4 vv = *reinterpret_cast<const float4 *>(vb + (size_t)(b0 + jj) * hd + 4 * lane);
 #pragma unroll
-            for (int g = 0; g < G; g++) {
-                const float pj = __shfl_sync(0xFFFFFFFFu, p[g], jj);
-                acc[g].x = fmaf(pj, vv.x, acc[g].x);
-                acc[g].y = fmaf(pj, vv.y, acc[g].y);
-                acc[g].z = fmaf(pj, vv.z, acc[g].z);
-                acc[g].w = fmaf(pj, vv.w, acc[g].w);
+            for (int p = 0; p < P; p++) {
+                const float pj = __shfl_sync(0xFFFFFFFFu, dot[p], jj);
+                acc[p].x = fmaf(pj, vv.x, acc[p].x);
+                acc[p].y = fmaf(pj, vv.y, acc[p].y);
+                acc[p].z = fmaf(pj, vv.z, acc[p].z);
+                acc[p].w = fmaf(pj, vv.w, acc[p].w);
             }
         }
     }
-    char *orow = reinterpret_cast<char *>(out) + (size_t)row * n_heads * hd * (act_dt == NNQ_F32 ? 4 : 2);
 #pragma unroll
-    for (int g = 0; g < G; g++) {
-        const int base = (kvh * G + g) * hd + 4 * lane;
-        store_act(orow, act_dt, base, acc[g].x / l[g]);
-        store_act(orow, act_dt, base + 1, acc[g].y / l[g]);
-        store_act(orow, act_dt, base + 2, acc[g].z / l[g]);
-        store_act(orow, act_dt, base + 3, acc[g].w / l[g]);
+    for (int p = 0; p < P; p++) {
+        if (p / G >= rows) continue;
+        char *orow = reinterpret_cast<char *>(out) + (size_t)(r0 + p / G) * n_heads * hd * (act_dt == NNQ_F32 ? 4 : 2);
+        const int base = (kvh * G + p % G) * hd + 4 * lane;
+        store_act(orow, act_dt, base, acc[p].x / l[p]);
+        store_act(orow, act_dt, base + 1, acc[p].y / l[p]);
+        store_act(orow, act_dt, base + 2, acc[p].z / l[p]);
+        store_act(orow, act_dt, base + 3, acc[p].w / l[p]);
     }
 }
 
@@ -903,7 +914,7 @@ nnq_status nnq_decoder_prefill(nnq_decoder *d, const int32_t *tokens_host, int c
     const nnq_dtype adt = (nnq_dtype)d->act_dt;
     const size_t es = adt == NNQ_F32 ? 4 : 2;
     // rows per pass: bounded by the scratch below and, with tensor parallelism, by what one exchange carries
-    int rows_max = 256;
+    int rows_max = kPrefillRows;
     if (d->comm) {
         CommView v;
         if ((s = comm_view(d->comm, &v)) != NNQ_OK) return s;
@@ -912,8 +923,8 @@ nnq_status nnq_decoder_prefill(nnq_decoder *d, const int32_t *tokens_host, int c
         if ((size_t)rows_max > fit) rows_max = (int)fit;
     }
     if (!d->pf_h) {
-        d->pf_rows = 256;
-        const size_t R = 256;
+        d->pf_rows = kPrefillRows;
+        const size_t R = kPrefillRows;
         s = dev_alloc(ctx, (void **)&d->pf_h, R * c.hidden * 4, "prompt buffer");
         if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_delta, R * c.hidden * 4, "prompt buffer");
         if (s == NNQ_OK) s = dev_alloc(ctx, (void **)&d->pf_q, R * qdim * 4, "prompt buffer");
@@ -947,12 +958,12 @@ nnq_status nnq_decoder_prefill(nnq_decoder *d, const int32_t *tokens_host, int c
             if ((s = nnq_linear_batch(ctx, 3, w3, x3, adt, n, nullptr, y3, NNQ_F32, st)) != NNQ_OK) return s;
             dec_qk_rope_rows_kernel<<<dim3(lh + 2 * lkv, n), hd, 0, st>>>(d->pf_q, d->pf_k, d->pf_v, L.q_norm, L.k_norm, d->d_cos, d->d_sin, pos0,
                                                                          c.rms_eps, d->pf_qrot, kc, vc, lh, lkv, hd, c.max_seq);
-            const dim3 ag(lkv, n);
+            // 16 query vectors per warp: R = 16 / G rows share each key / value row
             switch (group) {
-                case 1: dec_attn_rows_kernel<1><<<ag, 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
-                case 2: dec_attn_rows_kernel<2><<<ag, 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
-                case 4: dec_attn_rows_kernel<4><<<ag, 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
-                case 8: dec_attn_rows_kernel<8><<<ag, 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
+                case 1: dec_attn_rows_kernel<1, 16><<<dim3(lkv, (n + 15) / 16), 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, n, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
+                case 2: dec_attn_rows_kernel<2, 8><<<dim3(lkv, (n + 7) / 8), 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, n, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
+                case 4: dec_attn_rows_kernel<4, 4><<<dim3(lkv, (n + 3) / 4), 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, n, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
+                case 8: dec_attn_rows_kernel<8, 2><<<dim3(lkv, (n + 1) / 2), 32, 0, st>>>(d->pf_qrot, kc, vc, pos0, n, scale, d->pf_attn, d->act_dt, lh, hd, c.max_seq); break;
                 default: return fail(ctx, NNQ_ERR_UNSUPPORTED, "query heads per key/value head must be 1, 2, 4 or 8");
             }
             s = d->comm ? nnq_comm_linear(d->comm, L.o, d->pf_attn, adt, n, nullptr, d->pf_delta, NNQ_F32, st)
