@@ -79,10 +79,11 @@ static cudaError_t launch_dequant_bf16(const uint8_t *src, const uint8_t *scales
 // bf16 GEMM: y[M, N] = x[M, K] * Wd[N, K]^T (+ bias)
 // ---------------------------------------------------------------------------------
 
-constexpr int kDgBM = 128, kDgBN = 256, kDgBK = 64, kDgStages = 4;
-constexpr int kDgABytes = kDgBM * 128, kDgBBytes = kDgBN * 128;
-constexpr int kDgStageBytes = kDgABytes + kDgBBytes;
+// Tile 128 x BN x 64 with BN = 256, or 128 where 256-wide tiles would leave SMs without a tile.
+constexpr int kDgBM = 128, kDgBK = 64, kDgStages = 4;
+constexpr int kDgABytes = kDgBM * 128;
 constexpr int kDgThreads = 192;
+__host__ __device__ constexpr int dg_stage_bytes(int bn) { return kDgABytes + bn * 128; }
 
 __device__ __forceinline__ void dg_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void dg_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -129,10 +130,12 @@ __device__ __forceinline__ void dg_tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
 // inside a tile are computed but not stored. offsets == NULL: a plain product.
 constexpr int kDgMaxGroups = 64;
 
+template <int BN>
 __global__ void __launch_bounds__(kDgThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                   const float *__restrict__ bias, void *__restrict__ y, int M, int N, int K, int y_dt, int *status,
                   const int *__restrict__ offsets, int groups) {
+    constexpr int kDgBN = BN, kDgStageBytes = dg_stage_bytes(BN);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t bars[2 * kDgStages + 4];   // full[4], empty[4], acc_full[2], acc_empty[2]
@@ -227,8 +230,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            // f32 accumulate, bf16 x bf16, both K-major, N = 256, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+            // f32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (((uint32_t)BN >> 3) << 17) | ((128u >> 4) << 24);
             int slot = 0;
             uint32_t phase = 0;
             int it = 0;
@@ -389,26 +392,47 @@ nnq_status dense_scratch_reserve(nnq_ctx *ctx, int64_t n, int64_t k) {
     return NNQ_OK;
 }
 
+// 256-wide tiles unless they would leave more than half of the SMs without a tile (few row tiles,
+// narrow weights): then twice as many 128-wide tiles still fit one wave. (Measured: 4096 x 4096 at
+// 512 rows 64 -> 128 tiles, +13 %; 1024 x 5120 at 4096 rows, 128 tiles of 256 beat 256 of 128.)
+static int dg_pick_bn(const nnq_ctx *ctx, int64_t m_tiles, int64_t n) {
+    return 2 * m_tiles * ((n + 255) / 256) <= ctx->sm_count ? 128 : 256;
+}
+
+static nnq_status dg_configure(nnq_ctx *ctx, int bn) {
+    static bool configured[64][2] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int which = bn == 256 ? 0 : 1;
+    if (dev >= 0 && dev < 64 && !configured[dev][which]) {
+        const int smem_bytes = kDgStages * dg_stage_bytes(bn) + 1024;
+        nnq_status s = check_cuda(ctx, bn == 256 ? cudaFuncSetAttribute(gemm_dense_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes)
+                                                 : cudaFuncSetAttribute(gemm_dense_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes),
+                                  "GEMM attribute");
+        if (s != NNQ_OK) return s;
+        configured[dev][which] = true;
+    }
+    return NNQ_OK;
+}
+
 // The GEMM alone: w_bf16 is a bf16 [n, k] weight in device memory (16-byte aligned).
 nnq_status launch_gemm_dense_bf16(nnq_ctx *ctx, const void *w_bf16, const TcArgs &a, cudaStream_t stream) {
     CUtensorMap xmap, wmap;
     memset(&xmap, 0, sizeof(xmap));
     memset(&wmap, 0, sizeof(wmap));
-    if (!make_map(a.x, a.m, a.k, kDgBM, &xmap) || !make_map(w_bf16, a.n, a.k, kDgBN, &wmap))
+    const int64_t m_tiles = (a.m + kDgBM - 1) / kDgBM;
+    const int bn = dg_pick_bn(ctx, m_tiles, a.n);
+    if (!make_map(a.x, a.m, a.k, kDgBM, &xmap) || !make_map(w_bf16, a.n, a.k, bn, &wmap))
         return fail(ctx, NNQ_ERR_DISPATCH_FAILED, "tensor map creation failed");
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int smem_bytes = kDgStages * kDgStageBytes + 1024;
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        nnq_status s = check_cuda(ctx, cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes), "GEMM attribute");
-        if (s != NNQ_OK) return s;
-        configured[dev] = true;
-    }
-    const int64_t tiles = ((a.m + kDgBM - 1) / kDgBM) * ((a.n + kDgBN - 1) / kDgBN);
+    nnq_status s = dg_configure(ctx, bn);
+    if (s != NNQ_OK) return s;
+    const int smem_bytes = kDgStages * dg_stage_bytes(bn) + 1024;
+    const int64_t tiles = m_tiles * ((a.n + bn - 1) / bn);
     const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-    gemm_dense_kernel<<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status,
-                                                                nullptr, 0);
+    if (bn == 256)
+        gemm_dense_kernel<256><<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status, nullptr, 0);
+    else
+        gemm_dense_kernel<128><<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status, nullptr, 0);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "bf16 GEMM launch");
 }
@@ -460,19 +484,19 @@ nnq_status launch_gemm_dense_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStr
     CUtensorMap xmap, wmap;
     memset(&xmap, 0, sizeof(xmap));
     memset(&wmap, 0, sizeof(wmap));
-    if (!make_map(g.x_bf16, g.rows_upper, g.k, kDgBM, &xmap) || !make_map(ctx->d_dense, (int64_t)g.experts * g.n, g.k, kDgBN, &wmap))
+    // row tiles of all experts: at most rows / 128 + one ragged tile per expert
+    const int bn = dg_pick_bn(ctx, g.rows_upper / kDgBM + g.experts, g.n);
+    if (!make_map(g.x_bf16, g.rows_upper, g.k, kDgBM, &xmap) || !make_map(ctx->d_dense, (int64_t)g.experts * g.n, g.k, bn, &wmap))
         return fail(ctx, NNQ_ERR_DISPATCH_FAILED, "tensor map creation failed");
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int smem_bytes = kDgStages * kDgStageBytes + 1024;
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        s = check_cuda(ctx, cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes), "GEMM attribute");
-        if (s != NNQ_OK) return s;
-        configured[dev] = true;
-    }
-    gemm_dense_kernel<<<ctx->sm_count, kDgThreads, smem_bytes, stream>>>(xmap, wmap, g.bias, g.y, (int)g.rows_upper, (int)g.n, (int)g.k, NNQ_F32,
-                                                                         ctx->d_status, g.offsets, g.experts);
+    s = dg_configure(ctx, bn);
+    if (s != NNQ_OK) return s;
+    const int smem_bytes = kDgStages * dg_stage_bytes(bn) + 1024;
+    if (bn == 256)
+        gemm_dense_kernel<256><<<ctx->sm_count, kDgThreads, smem_bytes, stream>>>(xmap, wmap, g.bias, g.y, (int)g.rows_upper, (int)g.n, (int)g.k, NNQ_F32,
+                                                                                  ctx->d_status, g.offsets, g.experts);
+    else
+        gemm_dense_kernel<128><<<ctx->sm_count, kDgThreads, smem_bytes, stream>>>(xmap, wmap, g.bias, g.y, (int)g.rows_upper, (int)g.n, (int)g.k, NNQ_F32,
+                                                                                  ctx->d_status, g.offsets, g.experts);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "grouped bf16 GEMM launch");
 }
