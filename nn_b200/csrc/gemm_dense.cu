@@ -34,6 +34,35 @@ namespace nnq {
 
 constexpr int kDbThreads = 128;
 
+// MXFP4 straight to bf16 bits, no f32 detour: a magnitude code m >= 2 is (1 + (m & 1) / 2) * 2^((m >> 1) - 1),
+// m == 1 is 0.5, and the block scale is 2^(e - 127), so the product is the bf16 number with exponent field
+// e - 1 + (m >> 1) and top mantissa bit (m & 1): bits = ((e - 1) << 7) + (m' << 6) with m' = m (0 for m == 1),
+// zero for m == 0, sign on bit 15. Exact, hence equal to rounding the f32 decode; valid for 1 <= e <= 251
+// (other exponents take the f32 path).
+__device__ __forceinline__ uint32_t mx_bf16_one(uint32_t nib, uint32_t base) {
+    const uint32_t m = nib & 7u;
+    const uint32_t mp = m == 1u ? 0u : m;
+    const uint32_t mag = m == 0u ? 0u : base + (mp << 6);
+    return mag | ((nib & 8u) << 12);
+}
+
+template <bool HIGH_FIRST>
+__device__ __forceinline__ void mx_chunk_bf16(const uint4 q, uint32_t e, uint4 *out4) {
+    const uint32_t base = (e - 1u) << 7;
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        uint32_t p[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t byte = (qw[v] >> (8 * i)) & 0xFFu;
+            const uint32_t even = HIGH_FIRST ? byte >> 4 : byte & 15u, odd = HIGH_FIRST ? byte & 15u : byte >> 4;
+            p[i] = mx_bf16_one(even, base) | (mx_bf16_one(odd, base) << 16);
+        }
+        out4[v] = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(kDbThreads)
 dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__ scales, int64_t nchunks,
@@ -41,7 +70,18 @@ dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__
     __shared__ uint4 tile[kDbThreads * 4 + 4];
     for (int64_t base = (int64_t)blockIdx.x * kDbThreads; base < nchunks; base += (int64_t)gridDim.x * kDbThreads) {
         const int64_t c = base + threadIdx.x;
-        if (c < nchunks) {
+        bool done = false;
+        if (c < nchunks && (FMT == NNQ_MXFP4_SPLIT || FMT == NNQ_MXFP4_GPTOSS)) {
+            const uint32_t e = __ldg(scales + c);
+            if (e >= 1u && e <= 251u) {
+                uint4 o4[4];
+                mx_chunk_bf16<FMT == NNQ_MXFP4_GPTOSS>(__ldg(reinterpret_cast<const uint4 *>(src + c * 16)), e, o4);
+#pragma unroll
+                for (int j = 0; j < 4; j++) tile[threadIdx.x * 4 + (j ^ ((threadIdx.x >> 1) & 3))] = o4[j];
+                done = true;
+            }
+        }
+        if (c < nchunks && !done) {
             float o[32];
             Decode<FMT>::chunk(src, scales, c, o);   // the bit-exact decode, then round to nearest even
 #pragma unroll
@@ -52,14 +92,16 @@ dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__
                     __nv_bfloat162 v = __floats2bfloat162_rn(o[8 * j + 2 * i], o[8 * j + 2 * i + 1]);
                     p[i] = *reinterpret_cast<uint32_t *>(&v);
                 }
-                tile[threadIdx.x * 4 + j] = make_uint4(p[0], p[1], p[2], p[3]);
+                // chunk-local XOR swizzle: for a fixed j the 16-byte stores of a quarter warp fall into
+                // eight different bank groups (unswizzled, threads 64 bytes apart share two of them)
+                tile[threadIdx.x * 4 + (j ^ ((threadIdx.x >> 1) & 3))] = make_uint4(p[0], p[1], p[2], p[3]);
             }
         }
         __syncthreads();
         const int64_t remaining = nchunks - base;
         const int live = remaining < kDbThreads ? (int)remaining : kDbThreads;
         uint4 *out = dst + base * 4;
-        for (int idx = threadIdx.x; idx < live * 4; idx += kDbThreads) out[idx] = tile[idx];
+        for (int idx = threadIdx.x; idx < live * 4; idx += kDbThreads) out[idx] = tile[(idx & ~3) | ((idx & 3) ^ ((idx >> 3) & 3))];
         __syncthreads();
     }
 }

@@ -481,3 +481,34 @@ def test_failed_staging_growth_leaves_the_context_usable():
         got = api.quantized_linear(x, t, None)
         assert np.array_equal(got, want)
     t.release()
+
+
+@pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q6_K, Q.Q8_0, Q.MXFP4_SPLIT, Q.MXFP4_CORE, Q.MXFP4_GPTOSS, Q.BF16_DENSE])
+def test_decode_once_path_multiplies_the_rounded_decoded_weights(fmt):
+    """With the identity as activations (256 rows, so the decode-once path runs) the product returns
+    the bf16 weights the GEMM was fed: they must be the oracle's decoded weights rounded to bf16, bit
+    for bit -- including MXFP4 blocks with extreme scale exponents, which the direct-to-bf16 decode
+    hands to the f32 decoder (exponent 0) or that sit at the top of its own range."""
+    n, k = 96, 256
+    w, sc = F.gen_weight(fmt, 61, n, k)
+    if fmt == Q.MXFP4_SPLIT or fmt == Q.MXFP4_GPTOSS:
+        sc = np.array(sc, copy=True)
+        sc[:6] = [0, 1, 3, 250, 251, 252]
+    elif fmt == Q.MXFP4_CORE:
+        w = np.array(w, copy=True)
+        w.reshape(-1, 17)[:6, 0] = [0, 1, 3, 250, 251, 252]
+    t = api.from_quantized(w, fmt, [n, k], sc)
+    x = torch.eye(k, device=DEV, dtype=torch.bfloat16)
+    y = api.quantized_linear(x, t, None, out_dtype=torch.float32)     # [k, n] = W^T
+    torch.cuda.synchronize()
+    t.backend.device_status()
+    deq = orc.dequantize(fmt, w, n * k, sc).reshape(n, k)
+    with np.errstate(over="ignore"):
+        want = F.bf16_bits_to_f32(F.to_bf16_bits(deq)).reshape(n, k)
+    got = y.cpu().numpy().T
+    # values compared as numbers (a sum of products with zeros does not keep the sign of a zero weight);
+    # weights below the normal range are left out: the tensor cores flush subnormal operands to zero
+    check = np.isfinite(want) & ((want == 0) | (np.abs(want) >= 2.0 ** -126))
+    assert np.array_equal(got[check], want[check])
+    assert np.all(np.abs(got[~check & np.isfinite(want)]) <= 2.0 ** -126)
+    t.release()
