@@ -67,21 +67,38 @@ template <int FMT>
 __global__ void __launch_bounds__(kDbThreads)
 dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__ scales, int64_t nchunks,
                     uint4 *__restrict__ dst) {
+    if (FMT == NNQ_MXFP4_SPLIT || FMT == NNQ_MXFP4_GPTOSS) {
+        // a thread owns one 32-weight chunk: 64 contiguous output bytes (two whole 32-byte sectors), written
+        // with four 16-byte stores -- the integer decode needs no staging (measured: 366 -> 320 us for the
+        // 282 MB of a gpt-oss gate / up tensor; the f32 decoders below are faster with the staged store)
+        for (int64_t c = (int64_t)blockIdx.x * kDbThreads + threadIdx.x; c < nchunks; c += (int64_t)gridDim.x * kDbThreads) {
+            uint4 o4[4];
+            const uint32_t e = __ldg(scales + c);
+            if (e >= 1u && e <= 251u) {
+                mx_chunk_bf16<FMT == NNQ_MXFP4_GPTOSS>(__ldg(reinterpret_cast<const uint4 *>(src + c * 16)), e, o4);
+            } else {
+                float o[32];
+                Decode<FMT>::chunk(src, scales, c, o);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    uint32_t p[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        __nv_bfloat162 v = __floats2bfloat162_rn(o[8 * j + 2 * i], o[8 * j + 2 * i + 1]);
+                        p[i] = *reinterpret_cast<uint32_t *>(&v);
+                    }
+                    o4[j] = make_uint4(p[0], p[1], p[2], p[3]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) dst[c * 4 + j] = o4[j];
+        }
+        return;
+    }
     __shared__ uint4 tile[kDbThreads * 4 + 4];
     for (int64_t base = (int64_t)blockIdx.x * kDbThreads; base < nchunks; base += (int64_t)gridDim.x * kDbThreads) {
         const int64_t c = base + threadIdx.x;
-        bool done = false;
-        if (c < nchunks && (FMT == NNQ_MXFP4_SPLIT || FMT == NNQ_MXFP4_GPTOSS)) {
-            const uint32_t e = __ldg(scales + c);
-            if (e >= 1u && e <= 251u) {
-                uint4 o4[4];
-                mx_chunk_bf16<FMT == NNQ_MXFP4_GPTOSS>(__ldg(reinterpret_cast<const uint4 *>(src + c * 16)), e, o4);
-#pragma unroll
-                for (int j = 0; j < 4; j++) tile[threadIdx.x * 4 + (j ^ ((threadIdx.x >> 1) & 3))] = o4[j];
-                done = true;
-            }
-        }
-        if (c < nchunks && !done) {
+        if (c < nchunks) {
             float o[32];
             Decode<FMT>::chunk(src, scales, c, o);   // the bit-exact decode, then round to nearest even
 #pragma unroll
