@@ -148,32 +148,28 @@ moe_group_kernel(const int *__restrict__ idx, int total, int *__restrict__ count
                  int *__restrict__ rowtok, int *__restrict__ pos, int pass, int e_begin) {
     const int el = blockIdx.x;          // local expert (this device holds experts e_begin .. e_begin + gridDim.x)
     const int e = e_begin + el;
-    __shared__ int warp_sums[8];
-    __shared__ int base;
-    if (threadIdx.x == 0) base = 0;
-    __syncthreads();
+    __shared__ int warp_sums[2][8];     // double-buffered: one barrier per 256 assignments
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int start = 0; start < total; start += 256) {
+    int base = 0;                       // assignments of this expert before `start` (the same in every thread)
+    for (int start = 0, it = 0; start < total; start += 256, it++) {
         int i = start + threadIdx.x;
         bool hit = i < total && idx[i] == e;
         unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
-        if (lane == 0) warp_sums[warp] = __popc(ballot);
+        if (lane == 0) warp_sums[it & 1][warp] = __popc(ballot);
         __syncthreads();
-        int before = 0;
-        for (int w = 0; w < warp; w++) before += warp_sums[w];
-        int mine = base + before + __popc(ballot & ((1u << lane) - 1u));
+        int before = 0, tot = 0;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const int v = warp_sums[it & 1][w];
+            tot += v;
+            if (w < warp) before += v;
+        }
         if (pass == 1 && hit) {
-            int row = offset[el] + mine;
+            int row = offset[el] + base + before + __popc(ballot & ((1u << lane) - 1u));
             rowtok[row] = i;
             pos[i] = row;
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int tot = 0;
-            for (int w = 0; w < 8; w++) tot += warp_sums[w];
-            base += tot;
-        }
-        __syncthreads();
+        base += tot;
     }
     if (pass == 0 && threadIdx.x == 0) count[el] = base;
 }
@@ -437,6 +433,12 @@ __global__ void moe_gather_bf16_kernel(const XT *__restrict__ x, const int *__re
     const int r = blockIdx.x;
     if (r >= offset[E]) return;
     const XT *src = x + (size_t)(rowtok[r] / top_k) * H;
+    if (sizeof(XT) == 2 && (H & 7) == 0) {   // bf16 rows of whole 16-byte units: a plain copy
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+        uint4 *d4 = reinterpret_cast<uint4 *>(xg + (size_t)r * H);
+        for (int j = threadIdx.x; j < H / 8; j += blockDim.x) d4[j] = __ldg(s4 + j);
+        return;
+    }
     for (int j = threadIdx.x; j < H; j += blockDim.x) xg[(size_t)r * H + j] = __float2bfloat16_rn(ld_act<XT>(src, j));
 }
 
@@ -453,6 +455,30 @@ __global__ void moe_combine_kernel(const float *__restrict__ o, const int *__res
         for (int b = a; b > 0 && idx[(int64_t)t * top_k + order[b]] < idx[(int64_t)t * top_k + order[b - 1]]; b--) {
             int tmp = order[b]; order[b] = order[b - 1]; order[b - 1] = tmp;
         }
+    if (slices == 1 && (H & 3) == 0) {
+        // slot rows and weights once per thread, then four columns at a time (same sums, same order)
+        int rows[kMaxTopK];
+        float ws[kMaxTopK];
+        for (int s = 0; s < top_k; s++) {
+            rows[s] = pos[(int64_t)t * top_k + order[s]];
+            ws[s] = wt[(int64_t)t * top_k + order[s]];
+        }
+        const float4 *o4 = reinterpret_cast<const float4 *>(o);
+        float4 *y4 = reinterpret_cast<float4 *>(y + (size_t)t * H);
+        for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < H / 4; j += gridDim.y * blockDim.x) {
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int s = 0; s < top_k; s++) {
+                if (rows[s] < 0) continue;   // expert held by another device
+                const float4 v = o4[(size_t)rows[s] * (H / 4) + j];
+                acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, ws[s]));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, ws[s]));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, ws[s]));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, ws[s]));
+            }
+            y4[j] = acc;
+        }
+        return;
+    }
     for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < H; j += gridDim.y * blockDim.x) {
         float acc = 0.0f;
         for (int s = 0; s < top_k; s++) {
