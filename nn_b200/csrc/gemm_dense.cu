@@ -66,7 +66,7 @@ __device__ __forceinline__ void mx_chunk_bf16(const uint4 q, uint32_t e, uint4 *
 template <int FMT>
 __global__ void __launch_bounds__(kDbThreads)
 dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__ scales, int64_t nchunks,
-                    uint4 *__restrict__ dst) {
+                    uint4 *__restrict__ dst, int cpr, int half_rows) {
     if (FMT == NNQ_MXFP4_SPLIT || FMT == NNQ_MXFP4_GPTOSS) {
         // a thread owns one 32-weight chunk: 64 contiguous output bytes (two whole 32-byte sectors), written
         // with four 16-byte stores -- the integer decode needs no staging (measured: 366 -> 320 us for the
@@ -90,8 +90,18 @@ dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__
                     o4[j] = make_uint4(p[0], p[1], p[2], p[3]);
                 }
             }
+            // half_rows > 0: every group of 2 * half_rows weight rows (one expert's gate rows, then its up
+            // rows) is written interleaved, gate row j to row 2j and up row j to row 2j + 1, so that a GEMM
+            // tile holds both halves of an output column pair (the fused SwiGLU epilogue)
+            int64_t oc = c;
+            if (half_rows > 0) {   // nchunks < 2^31 here (checked by the launcher): 32-bit divisions
+                const uint32_t c32 = (uint32_t)c, row = c32 / (uint32_t)cpr, cin = c32 - row * (uint32_t)cpr;
+                const uint32_t e = row / (2u * half_rows), r = row - e * 2u * half_rows;
+                const uint32_t r2 = r < (uint32_t)half_rows ? 2u * r : 2u * (r - half_rows) + 1u;
+                oc = (int64_t)(e * 2u * half_rows + r2) * cpr + cin;
+            }
 #pragma unroll
-            for (int j = 0; j < 4; j++) dst[c * 4 + j] = o4[j];
+            for (int j = 0; j < 4; j++) dst[oc * 4 + j] = o4[j];
         }
         return;
     }
@@ -125,12 +135,12 @@ dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__
 
 template <int FMT>
 static cudaError_t launch_dequant_bf16(const uint8_t *src, const uint8_t *scales, int64_t nchunks, void *dst, int sm_count,
-                                       cudaStream_t stream) {
+                                       cudaStream_t stream, int cpr = 1, int half_rows = 0) {
     const int64_t want = (nchunks + kDbThreads - 1) / kDbThreads;
     const int64_t cap = (int64_t)sm_count * 16;
     int grid = (int)(want < cap ? want : cap);
     if (grid < 1) grid = 1;
-    dequant_bf16_kernel<FMT><<<grid, kDbThreads, 0, stream>>>(src, scales, nchunks, reinterpret_cast<uint4 *>(dst));
+    dequant_bf16_kernel<FMT><<<grid, kDbThreads, 0, stream>>>(src, scales, nchunks, reinterpret_cast<uint4 *>(dst), cpr, half_rows);
     return cudaGetLastError();
 }
 
@@ -193,7 +203,7 @@ template <int BN>
 __global__ void __launch_bounds__(kDgThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                   const float *__restrict__ bias, void *__restrict__ y, int M, int N, int K, int y_dt, int *status,
-                  const int *__restrict__ offsets, int groups) {
+                  const int *__restrict__ offsets, int groups, __nv_bfloat16 *__restrict__ h_out, float swiglu_limit) {
     constexpr int kDgBN = BN, kDgStageBytes = dg_stage_bytes(BN);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -342,7 +352,44 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constan
                 uint32_t v[32];
                 dg_tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kDgBN + cc * 32), v);
                 const int col0 = n0 + cc * 32;
-                if (row < m_end && col0 < N) {
+                if (h_out) {
+                    // interleaved gate / up columns (2j, 2j + 1): h[row, j] = clamp(silu(g), +-limit) * u in bf16,
+                    // the input of the second expert product; the bias of column c is the gate bias of c / 2 for
+                    // even c and the up bias (second half of the expert's bias row) for odd c
+                    if (row < m_end && col0 < N) {
+                        const int I = N >> 1;
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int p = 0; p < 16; p += 2) {
+                            float hv[2];
+#pragma unroll
+                            for (int q2 = 0; q2 < 2; q2++) {
+                                const int j = (col0 >> 1) + p + q2;
+                                float gv = __uint_as_float(v[2 * (p + q2)]), uv = __uint_as_float(v[2 * (p + q2) + 1]);
+                                if (gbias && j < I) {
+                                    gv += __ldg(gbias + j);
+                                    uv += __ldg(gbias + I + j);
+                                }
+                                // fast exponential and division (2^-22 relative): far below the bf16 rounding of h,
+                                // and cheap enough for the epilogue to stay hidden behind the next tile's MMAs
+                                float sv = __fdividef(gv, 1.0f + __expf(-gv));
+                                sv = fminf(fmaxf(sv, -swiglu_limit), swiglu_limit);
+                                hv[q2] = sv * uv;
+                            }
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(hv[0], hv[1]);
+                            packed[p >> 1] = *reinterpret_cast<uint32_t *>(&b2);
+                        }
+                        __nv_bfloat16 *dstp = h_out + (size_t)row * I + (col0 >> 1);
+                        if (col0 + 32 <= N && (I & 7) == 0) {
+                            reinterpret_cast<uint4 *>(dstp)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            reinterpret_cast<uint4 *>(dstp)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+                            const __nv_bfloat16 *pk = reinterpret_cast<const __nv_bfloat16 *>(packed);
+                            for (int i = 0; i < 16; i++)
+                                if ((col0 >> 1) + i < I) dstp[i] = pk[i];
+                        }
+                    }
+                } else if (row < m_end && col0 < N) {
                     float f[32];
 #pragma unroll
                     for (int i = 0; i < 32; i++) f[i] = __uint_as_float(v[i]) + (gbias && col0 + i < N ? __ldg(gbias + col0 + i) : 0.0f);
@@ -489,9 +536,9 @@ nnq_status launch_gemm_dense_bf16(nnq_ctx *ctx, const void *w_bf16, const TcArgs
     const int64_t tiles = m_tiles * ((a.n + bn - 1) / bn);
     const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
     if (bn == 256)
-        gemm_dense_kernel<256><<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status, nullptr, 0);
+        gemm_dense_kernel<256><<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status, nullptr, 0, nullptr, 0.0f);
     else
-        gemm_dense_kernel<128><<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status, nullptr, 0);
+        gemm_dense_kernel<128><<<grid, kDgThreads, smem_bytes, stream>>>(xmap, wmap, a.bias, a.y, (int)a.m, (int)a.n, (int)a.k, a.y_dt, ctx->d_status, nullptr, 0, nullptr, 0.0f);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "bf16 GEMM launch");
 }
@@ -523,13 +570,22 @@ bool gemm_dense_grouped_supported(const nnq_ctx *ctx, const TcGroupArgs &g) {
            (int64_t)g.experts * g.n < (1ll << 31) && encode_fn() != nullptr;
 }
 
+bool gemm_dense_grouped_fuses_swiglu(const TcGroupArgs &g) {
+    return g.h_out != nullptr && (g.fmt == NNQ_MXFP4_SPLIT || g.fmt == NNQ_MXFP4_GPTOSS) && g.n % 2 == 0 &&
+           (int64_t)g.experts * g.n * (g.k / 32) < (1ll << 31);
+}
+
 nnq_status launch_gemm_dense_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStream_t stream) {
     // the experts' raw blocks are one contiguous [experts, N, K] tensor: one decode launch
     Geometry geo = geometry(g.fmt);
     const int64_t nchunks = (int64_t)g.experts * g.n * (g.k / geo.elems) * (geo.elems / 32);
     cudaError_t e;
+    // SwiGLU in the GEMM's epilogue (g.h_out given): needs the gate / up rows interleaved in the decoded copy,
+    // which the direct MXFP4 decode can write at no cost
+    const bool fuse = gemm_dense_grouped_fuses_swiglu(g);
+    const int cpr = (int)(g.k / 32), half = fuse ? (int)(g.n / 2) : 0;
     switch (g.fmt) {
-#define NNQ_DB(F) case F: e = launch_dequant_bf16<F>(g.w, g.scales, nchunks, ctx->d_dense, ctx->sm_count, stream); break
+#define NNQ_DB(F) case F: e = launch_dequant_bf16<F>(g.w, g.scales, nchunks, ctx->d_dense, ctx->sm_count, stream, cpr, half); break
         NNQ_DB(NNQ_Q4_0); NNQ_DB(NNQ_Q4_1); NNQ_DB(NNQ_Q8_0); NNQ_DB(NNQ_Q4_K); NNQ_DB(NNQ_Q4_K_GGML); NNQ_DB(NNQ_Q6_K);
         NNQ_DB(NNQ_MXFP4_CORE); NNQ_DB(NNQ_MXFP4_SPLIT); NNQ_DB(NNQ_MXFP4_GPTOSS); NNQ_DB(NNQ_Q5_0); NNQ_DB(NNQ_Q5_1);
         NNQ_DB(NNQ_Q2_K); NNQ_DB(NNQ_Q3_K); NNQ_DB(NNQ_Q5_K);
@@ -552,10 +608,10 @@ nnq_status launch_gemm_dense_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStr
     const int smem_bytes = kDgStages * dg_stage_bytes(bn) + 1024;
     if (bn == 256)
         gemm_dense_kernel<256><<<ctx->sm_count, kDgThreads, smem_bytes, stream>>>(xmap, wmap, g.bias, g.y, (int)g.rows_upper, (int)g.n, (int)g.k, NNQ_F32,
-                                                                                  ctx->d_status, g.offsets, g.experts);
+                                                                                  ctx->d_status, g.offsets, g.experts, fuse ? g.h_out : nullptr, g.swiglu_limit);
     else
         gemm_dense_kernel<128><<<ctx->sm_count, kDgThreads, smem_bytes, stream>>>(xmap, wmap, g.bias, g.y, (int)g.rows_upper, (int)g.n, (int)g.k, NNQ_F32,
-                                                                                  ctx->d_status, g.offsets, g.experts);
+                                                                                  ctx->d_status, g.offsets, g.experts, fuse ? g.h_out : nullptr, g.swiglu_limit);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "grouped bf16 GEMM launch");
 }

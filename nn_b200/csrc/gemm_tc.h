@@ -1,5 +1,7 @@
 // Tensor-core (tcgen05 / TMEM) prefill product: internal declarations.
 #pragma once
+#include <cuda_bf16.h>
+
 #include "nnq_internal.h"
 
 namespace nnq {
@@ -29,7 +31,14 @@ struct TcGroupArgs {
     int64_t rows_upper;     // upper bound of offsets[experts] (allocation size of x and y in rows)
     int64_t n, k;
     int fmt;
+    // decode-once path only: with h_out given and an MXFP4 format the product is the gate / up product
+    // of an expert block (n = 2 * inter, gate rows first) and its epilogue writes
+    // h_out[row, j] = clamp(silu(gate_j), +-swiglu_limit) * up_j in bf16 instead of y
+    // (gemm_dense_grouped_fuses_swiglu tells)
+    __nv_bfloat16 *h_out = nullptr;
+    float swiglu_limit = 0.0f;
 };
+bool gemm_dense_grouped_fuses_swiglu(const TcGroupArgs &g);
 nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &a, cudaStream_t stream);
 
 // K must be a multiple of 64 (one 128-byte swizzle row of bf16 per stage).

@@ -570,7 +570,7 @@ struct DtypeOf<__nv_bfloat16> { static constexpr int value = NNQ_BF16; };
 
 template <typename XT>
 static nnq_status launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, const XT *x, const int *rowtok, int top_k,
-                           const MoeScratch &s, float *out, int64_t rows, cudaStream_t st) {
+                           const MoeScratch &s, float *out, int64_t rows, cudaStream_t st, bool *swiglu_done = nullptr) {
     const int K = first ? m->hidden : m->inter;
     const int N = first ? 2 * m->inter : m->hidden;
     const uint8_t *d = first ? m->d_gu : m->d_dn;
@@ -583,7 +583,16 @@ static nnq_status launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, con
         const size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
         TcGroupArgs a = {d, sc, eb, es, first ? (const void *)s.xg : (const void *)s.hb, b, out, s.offset, E, rows, N, K, m->fmt};
         // hundreds of rows per expert: all local experts decoded to bf16 once, then the plain grouped GEMM
-        if (rows >= 256 * (int64_t)E && gemm_dense_grouped_supported(ctx, a)) return launch_gemm_dense_grouped(ctx, a, st);
+        if (rows >= 256 * (int64_t)E && gemm_dense_grouped_supported(ctx, a)) {
+            if (first && swiglu_done && s.slices == 1) {
+                // gate / up product: SwiGLU in the GEMM's epilogue where the decode can interleave the rows
+                a.h_out = s.hb;
+                a.swiglu_limit = m->limit;
+                *swiglu_done = gemm_dense_grouped_fuses_swiglu(a);
+                if (!*swiglu_done) a.h_out = nullptr;
+            }
+            return launch_gemm_dense_grouped(ctx, a, st);
+        }
         return launch_gemm_tc_grouped(ctx, a, st);
     }
     if (m->d_gu_tiled) {
@@ -696,9 +705,11 @@ static nnq_status run_with_scratch(nnq_ctx *ctx, const nnq_moe *m, const XT *x, 
         moe_gather_bf16_kernel<XT><<<total, 256, 0, st>>>(x, s.rowtok, k, s.offset, m->e_local, m->hidden, s.xg);
         ctx->launches++;
     }
-    nnq_status prc = launch_product<XT>(ctx, m, true, x, s.rowtok, k, s, s.gu, total, st);
+    bool swiglu_done = false;
+    nnq_status prc = launch_product<XT>(ctx, m, true, x, s.rowtok, k, s, s.gu, total, st, &swiglu_done);
     if (prc != NNQ_OK) return prc;
-    launch_pdl(moe_swiglu_kernel, dim3((unsigned)total, (unsigned)((m->inter + 1023) / 1024)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
+    if (!swiglu_done)
+        launch_pdl(moe_swiglu_kernel, dim3((unsigned)total, (unsigned)((m->inter + 1023) / 1024)), dim3(256), st, s.gu, s.h, s.offset, m->e_local, m->inter, m->limit, s.slices, s.gu_stride, s.hb);
     prc = launch_product<float>(ctx, m, false, s.h, nullptr, k, s, s.o, total, st);
     if (prc != NNQ_OK) return prc;
     launch_pdl(moe_combine_kernel, dim3((unsigned)T, T < 1024 ? 4 : 1), dim3(256), st, s.o, idx, wt, s.pos, (int)T, m->hidden, k, y, s.slices, s.o_stride);
