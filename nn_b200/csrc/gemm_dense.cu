@@ -71,11 +71,10 @@ dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__
         // a thread owns one 32-weight chunk: 64 contiguous output bytes (two whole 32-byte sectors), written
         // with four 16-byte stores -- the integer decode needs no staging (measured: 366 -> 320 us for the
         // 282 MB of a gpt-oss gate / up tensor; the f32 decoders below are faster with the staged store)
-        for (int64_t c = (int64_t)blockIdx.x * kDbThreads + threadIdx.x; c < nchunks; c += (int64_t)gridDim.x * kDbThreads) {
+        auto emit = [&](int64_t c, uint32_t e, const uint4 q) {
             uint4 o4[4];
-            const uint32_t e = __ldg(scales + c);
             if (e >= 1u && e <= 251u) {
-                mx_chunk_bf16<FMT == NNQ_MXFP4_GPTOSS>(__ldg(reinterpret_cast<const uint4 *>(src + c * 16)), e, o4);
+                mx_chunk_bf16<FMT == NNQ_MXFP4_GPTOSS>(q, e, o4);
             } else {
                 float o[32];
                 Decode<FMT>::chunk(src, scales, c, o);
@@ -96,13 +95,24 @@ dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__
             int64_t oc = c;
             if (half_rows > 0) {   // nchunks < 2^31 here (checked by the launcher): 32-bit divisions
                 const uint32_t c32 = (uint32_t)c, row = c32 / (uint32_t)cpr, cin = c32 - row * (uint32_t)cpr;
-                const uint32_t e = row / (2u * half_rows), r = row - e * 2u * half_rows;
+                const uint32_t ex = row / (2u * half_rows), r = row - ex * 2u * half_rows;
                 const uint32_t r2 = r < (uint32_t)half_rows ? 2u * r : 2u * (r - half_rows) + 1u;
-                oc = (int64_t)(e * 2u * half_rows + r2) * cpr + cin;
+                oc = (int64_t)(ex * 2u * half_rows + r2) * cpr + cin;
             }
 #pragma unroll
             for (int j = 0; j < 4; j++) dst[oc * 4 + j] = o4[j];
+        };
+        // two chunks per iteration: both loads are in flight before either is decoded
+        const int64_t stride = (int64_t)gridDim.x * kDbThreads;
+        int64_t c = (int64_t)blockIdx.x * kDbThreads + threadIdx.x;
+        for (; c + stride < nchunks; c += 2 * stride) {
+            const uint32_t e0 = __ldg(scales + c), e1 = __ldg(scales + c + stride);
+            const uint4 q0 = __ldg(reinterpret_cast<const uint4 *>(src + c * 16));
+            const uint4 q1 = __ldg(reinterpret_cast<const uint4 *>(src + (c + stride) * 16));
+            emit(c, e0, q0);
+            emit(c + stride, e1, q1);
         }
+        if (c < nchunks) emit(c, __ldg(scales + c), __ldg(reinterpret_cast<const uint4 *>(src + c * 16)));
         return;
     }
     __shared__ uint4 tile[kDbThreads * 4 + 4];
