@@ -42,6 +42,48 @@ __device__ __forceinline__ float ld_act<__nv_bfloat16>(const __nv_bfloat16 *p, i
 constexpr int kMaxExperts = 64;
 constexpr int kMaxTopK = 8;
 
+// Softmax over the E logits of one token (lg, shared memory) and top-k selection by one warp.
+__device__ __forceinline__ void route_token(const float *lg, int E, int top_k, int tok, int *__restrict__ idx,
+                                            float *__restrict__ wt, int lane) {
+    // lane e (and e + 32) holds expert e's logit
+    float l0 = lane < E ? lg[lane] : -CUDART_INF_F;
+    float l1 = lane + 32 < E ? lg[lane + 32] : -CUDART_INF_F;
+    // softmax over the E experts (max-subtracted, f32)
+    float mx = fmaxf(l0, l1);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    float p0 = lane < E ? expf(l0 - mx) : 0.0f;
+    float p1 = lane + 32 < E ? expf(l1 - mx) : 0.0f;
+    float sum = p0 + p1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+    p0 = p0 / sum;
+    p1 = p1 / sum;
+    if (lane >= E) p0 = -1.0f;
+    if (lane + 32 >= E) p1 = -1.0f;
+    // top-k: k rounds of (largest probability, lowest index) selection
+    float sel_p = 0.0f, wsum = 0.0f;
+    int sel_e = 0;
+    for (int s = 0; s < top_k; s++) {
+        float best = p0 >= p1 ? p0 : p1;
+        int be = p0 >= p1 ? lane : lane + 32;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            float ob = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+            int oe = __shfl_xor_sync(0xFFFFFFFFu, be, off);
+            if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+        }
+        if (be == lane) p0 = -1.0f;
+        if (be == lane + 32) p1 = -1.0f;
+        if (lane == s) { sel_p = best; sel_e = be; }
+        wsum += best;
+    }
+    if (lane < top_k) {
+        idx[(int64_t)tok * top_k + lane] = sel_e;
+        wt[(int64_t)tok * top_k + lane] = sel_p / wsum;
+    }
+}
+
 // A CTA serves TOK consecutive tokens: their activations sit in shared memory as f32, the 8 warps
 // share the experts (warp w: experts w, w + 8, ...; four experts at a time so that four weight
 // loads are in flight per lane), every lane accumulates a strided slice of the hidden dimension,
@@ -95,47 +137,45 @@ moe_router_kernel(const XT *__restrict__ x, const float *__restrict__ rw, const 
             }
     }
     __syncthreads();
-    for (int t = warp; t < ntok; t += 8) {
-        const int tok = tok0 + t;
-        const float *lg = logits + t * E;
-        // lane e (and e + 32) holds expert e's logit
-        float l0 = lane < E ? lg[lane] : -CUDART_INF_F;
-        float l1 = lane + 32 < E ? lg[lane + 32] : -CUDART_INF_F;
-        // softmax over the E experts (max-subtracted, f32)
-        float mx = fmaxf(l0, l1);
+    for (int t = warp; t < ntok; t += 8) route_token(logits + t * E, E, top_k, tok0 + t, idx, wt, lane);
+}
+
+// Fewer tokens than fill the machine one CTA each: a cluster of four CTAs serves a token, every CTA
+// forms a quarter of the logits (a warp per expert, the same lane-strided sums as above: identical
+// bits) and sends them into the first CTA's shared memory, which then routes the token.
+constexpr int kRouterCluster = 4;
+
+__device__ __forceinline__ void st_cluster_f32(const float *local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+template <typename XT>
+__global__ void __cluster_dims__(kRouterCluster, 1, 1) __launch_bounds__(256)
+moe_router_cluster_kernel(const XT *__restrict__ x, const float *__restrict__ rw, const float *__restrict__ rb,
+                          int T, int H, int E, int top_k, int *__restrict__ idx, float *__restrict__ wt) {
+    pdl_prologue();
+    extern __shared__ float xs[];          // the token's activations as f32, then E logits (used in the first CTA)
+    float *logits = xs + H;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int tok = blockIdx.x / kRouterCluster;   // the grid is exactly kRouterCluster * T CTAs
+    for (int i = threadIdx.x; i < H; i += 256) xs[i] = ld_act<XT>(x, (int64_t)tok * H + i);
+    __syncthreads();
+    for (int e = (int)rank + kRouterCluster * warp; e < E; e += kRouterCluster * 8) {
+        const float *w = rw + (int64_t)e * H;
+        float acc = 0.0f;
+#pragma unroll 6
+        for (int h = lane; h < H; h += 32) acc = fmaf(xs[h], __ldg(w + h), acc);
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
-        float p0 = lane < E ? expf(l0 - mx) : 0.0f;
-        float p1 = lane + 32 < E ? expf(l1 - mx) : 0.0f;
-        float sum = p0 + p1;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
-        p0 = p0 / sum;
-        p1 = p1 / sum;
-        if (lane >= E) p0 = -1.0f;
-        if (lane + 32 >= E) p1 = -1.0f;
-        // top-k: k rounds of (largest probability, lowest index) selection
-        float sel_p = 0.0f, wsum = 0.0f;
-        int sel_e = 0;
-        for (int s = 0; s < top_k; s++) {
-            float best = p0 >= p1 ? p0 : p1;
-            int be = p0 >= p1 ? lane : lane + 32;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                float ob = __shfl_xor_sync(0xFFFFFFFFu, best, off);
-                int oe = __shfl_xor_sync(0xFFFFFFFFu, be, off);
-                if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
-            }
-            if (be == lane) p0 = -1.0f;
-            if (be == lane + 32) p1 = -1.0f;
-            if (lane == s) { sel_p = best; sel_e = be; }
-            wsum += best;
-        }
-        if (lane < top_k) {
-            idx[(int64_t)tok * top_k + lane] = sel_e;
-            wt[(int64_t)tok * top_k + lane] = sel_p / wsum;
-        }
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+        if (lane == 0) st_cluster_f32(logits + e, 0, acc + __ldg(rb + e));
     }
+    // every CTA's stores into the first CTA are complete and visible after the cluster barrier
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank == 0 && warp == 0) route_token(logits, E, top_k, tok, idx, wt, lane);
 }
 
 // ---------------------------------------------------------------------------------
@@ -641,6 +681,8 @@ static cudaError_t launch_router(const nnq_moe *m, const XT *x, int64_t T, int *
         configured[dev][many] = true;
     }
     if (many) moe_router_kernel<XT, 8><<<(int)((T + 7) / 8), 256, smem, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, m->n_experts, m->top_k, idx, wt);
+    else if (smem <= 48 * 1024 && T * kRouterCluster < (1 << 30))
+        moe_router_cluster_kernel<XT><<<(int)T * kRouterCluster, 256, smem, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, m->n_experts, m->top_k, idx, wt);
     else moe_router_kernel<XT, 1><<<(int)T, 256, smem, st>>>(x, m->d_router_w, m->d_router_b, (int)T, m->hidden, m->n_experts, m->top_k, idx, wt);
     return cudaGetLastError();
 }
