@@ -548,16 +548,16 @@ struct MoeScratch {
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-// Prefill-sized calls on [N, K] expert weights go through the grouped tcgen05 product: from 64 routed
+// Prefill-sized calls on [N, K] expert weights go through the grouped tcgen05 products: from 32 routed
 // rows per local expert on average (below that the weights are streamed once per 16 rows by the
-// grouped token-column kernel, which is HBM-bound and wins).
+// grouped token-column kernel, which is HBM-bound and wins; the gpt-oss block crosses over near 240 tokens).
 static bool moe_tensor_mode(const nnq_moe *m, int64_t T, int k, bool routed) {
     static const char *env = diag_env("NNQ_MOE_TENSOR");   // tuning aid: 0 keeps the token-column kernel
     if (env && atoi(env) == 0) return false;
     return m->layout == NNQ_MOE_NK && (m->fmt < NNQ_Q5_0 || m->fmt >= NNQ_F32_DENSE) && m->hidden % 64 == 0 && m->inter % 64 == 0 &&
-           // 64 routed rows per expert on average: with the block's own router the T tokens spread over
+           // 32 routed rows per expert on average: with the block's own router the T tokens spread over
            // all experts (the shards of one block agree), rows routed by the caller all go to local experts
-           T * k >= 64 * (int64_t)(routed ? m->e_local : m->n_experts);
+           T * k >= (env ? atoi(env) : 32) * (int64_t)(routed ? m->e_local : m->n_experts);
 }
 
 // Carves the scratch buffer for T rows with k expert slots each; with base == NULL only the size
@@ -622,8 +622,16 @@ static nnq_status launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, con
         Geometry g = geometry(m->fmt);
         const size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
         TcGroupArgs a = {d, sc, eb, es, first ? (const void *)s.xg : (const void *)s.hb, b, out, s.offset, E, rows, N, K, m->fmt};
-        // hundreds of rows per expert: all local experts decoded to bf16 once, then the plain grouped GEMM
-        if (rows >= 256 * (int64_t)E && gemm_dense_grouped_supported(ctx, a)) {
+        // all local experts decoded to bf16 once, then the plain grouped GEMM. Measured against the product
+        // with the decode fused in (32 experts of about 2880 x 2880, top-4): MXFP4 and Q8_0 experts are ahead
+        // decoded once at every size that reaches this mode, Q4_K experts from about 100 rows per expert
+        // (64 rows: 0.84 ms fused, 0.88 ms decoded once; 128 rows: 1.24 against 0.96); Q6_K follows Q4_K
+        const bool k_quant = m->fmt == NNQ_Q4_K || m->fmt == NNQ_Q4_K_GGML || m->fmt == NNQ_Q6_K;
+        int64_t dense_rows = k_quant ? 96 : 32;
+#ifdef NNQ_DIAG
+        if (const char *e = getenv("NNQ_MOE_DENSE_ROWS")) dense_rows = atoi(e);
+#endif
+        if (rows >= dense_rows * (int64_t)E && gemm_dense_grouped_supported(ctx, a)) {
             if (first && swiglu_done && s.slices == 1) {
                 // gate / up product: SwiGLU in the GEMM's epilogue where the decode can interleave the rows
                 a.h_out = s.hb;

@@ -118,14 +118,32 @@ def run_moe(a):
 
     rw = (torch.randn(E, H, device=dev, generator=gen) * 0.5).float()
     rb = torch.zeros(E, device=dev)
-    gu, gus = u8(E * H * 2 * I // 2), u8(E * H * 2 * I // 32, 119, 128)
-    dn, dns = u8(E * I * H // 2), u8(E * I * H // 32, 119, 128)
     bgu, bd = torch.zeros(E, 2 * I, device=dev), torch.zeros(E, H, device=dev)
     layout, fmt = (0, 8) if a.layout == "kn" else (1, 7)   # [E,K,N] nn-gptoss | per-expert [N,K] split MXFP4
+    if a.format == "mxfp4":
+        gu, gus = u8(E * H * 2 * I // 2), u8(E * H * 2 * I // 32, 119, 128)
+        dn, dns = u8(E * I * H // 2), u8(E * I * H // 32, 119, 128)
+    else:
+        # [N, K] experts in a GGUF block format: random codes, every f16 scale field a small finite number
+        if a.layout != "nk":
+            raise SystemExit("--format other than mxfp4 needs --layout nk")
+        fmt, elems, nbytes, f16_at = {"q8_0": (2, 32, 34, (0,)), "q4_k": (3, 256, 144, (0, 2))}[a.format]
+        if H % elems or I % elems:
+            raise SystemExit(f"--hidden and --inter must be multiples of {elems} for {a.format}")
+
+        def blocks(n):
+            t = u8(n // elems * nbytes).view(-1, nbytes)
+            for o in f16_at:
+                t[:, o + 1] = 0x1C + (t[:, o + 1] & 3)   # f16 high byte: exponent 7..8 of 15 -> about 2^-8
+            return t.reshape(-1)
+
+        gu, dn = blocks(E * H * 2 * I), blocks(E * I * H)
+        gus = dns = torch.empty(0, dtype=torch.uint8, device=dev)
     h = ctypes.c_void_p()
     b.check(lib.nnq_moe_create(ctx, E, H, I, k, ctypes.c_float(7.0), rw.data_ptr(), rb.data_ptr(), layout, fmt,
-                               gu.data_ptr(), gu.numel(), gus.data_ptr(), gus.numel(), bgu.data_ptr(),
-                               dn.data_ptr(), dn.numel(), dns.data_ptr(), dns.numel(), bd.data_ptr(), ctypes.byref(h)))
+                               gu.data_ptr(), gu.numel(), gus.data_ptr() if gus.numel() else None, gus.numel(), bgu.data_ptr(),
+                               dn.data_ptr(), dn.numel(), dns.data_ptr() if dns.numel() else None, dns.numel(), bd.data_ptr(),
+                               ctypes.byref(h)))
     T = a.tokens
     x = torch.randn(T, H, device=dev, generator=gen).to(torch.bfloat16)
     y = torch.empty(T, H, device=dev)
@@ -133,7 +151,7 @@ def run_moe(a):
     b.device_status()
     wbytes = gu.numel() + gus.numel() + dn.numel() + dns.numel()
     touched = wbytes * min(1.0, T * k / E)
-    print(f"moe layout={a.layout} E={E} hidden={H} inter={I} top{k} tokens={T}: {sec * 1e6:.0f} us, "
+    print(f"moe layout={a.layout} {a.format} E={E} hidden={H} inter={I} top{k} tokens={T}: {sec * 1e6:.0f} us, "
           f"about {touched / 1e6:.0f} MB of expert weights touched -> {touched / sec / 1e9:.0f} GB/s", flush=True)
     lib.nnq_moe_destroy(h)
 
@@ -336,6 +354,7 @@ def main():
     p.add_argument("--reps", type=int, default=40)
     p = sub.add_parser("moe")
     p.add_argument("--layout", default="nk", choices=["nk", "kn"])
+    p.add_argument("--format", default="mxfp4", choices=["mxfp4", "q8_0", "q4_k"])
     p.add_argument("--tokens", type=int, default=64)
     p.add_argument("--experts", type=int, default=32)
     p.add_argument("--hidden", type=int, default=2880)
