@@ -36,6 +36,16 @@ __device__ __forceinline__ float mx_scale_gptoss(uint32_t e) {
     return __uint_as_float(e ? (e << 23) : 0x00800000u);
 }
 
+// Small integers as f32 without the conversion unit (a quarter-rate pipe, which the decoders fused
+// into tensor-core products would otherwise saturate): the integer is placed in the mantissa of 2^23
+// and 2^23 (+ bias) is subtracted, both exact. v < 2^23; returns (float)v - bias.
+__device__ __forceinline__ float u2f(uint32_t v) { return __fsub_rn(__uint_as_float(v | 0x4B000000u), 8388608.0f); }
+__device__ __forceinline__ float u2f_biased(uint32_t v, float bias) {
+    return __fsub_rn(__uint_as_float(v | 0x4B000000u), 8388608.0f + bias);
+}
+// a byte holding an int8 as f32
+__device__ __forceinline__ float s8_to_f(uint32_t byte) { return u2f_biased(byte ^ 0x80u, 128.0f); }
+
 template <int FMT>
 struct Decode;
 
@@ -47,8 +57,8 @@ struct Decode<NNQ_Q4_0> {
 #pragma unroll
         for (int j = 0; j < 16; j++) {
             uint32_t q = __ldg(b + 2 + j);
-            o[2 * j] = __fmul_rn(d, (float)((int)(q & 15u) - 8));
-            o[2 * j + 1] = __fmul_rn(d, (float)((int)(q >> 4) - 8));
+            o[2 * j] = __fmul_rn(d, u2f_biased(q & 15u, 8.0f));
+            o[2 * j + 1] = __fmul_rn(d, u2f_biased(q >> 4, 8.0f));
         }
     }
 };
@@ -62,8 +72,8 @@ struct Decode<NNQ_Q4_1> {
 #pragma unroll
         for (int j = 0; j < 16; j++) {
             uint32_t q = __ldg(b + 4 + j);
-            o[2 * j] = __fadd_rn(__fmul_rn(d, (float)(q & 15u)), m);
-            o[2 * j + 1] = __fadd_rn(__fmul_rn(d, (float)(q >> 4)), m);
+            o[2 * j] = __fadd_rn(__fmul_rn(d, u2f(q & 15u)), m);
+            o[2 * j + 1] = __fadd_rn(__fmul_rn(d, u2f(q >> 4)), m);
         }
     }
 };
@@ -74,7 +84,7 @@ struct Decode<NNQ_Q8_0> {
         const uint8_t *b = w + c * 34;
         float d = f16_bits_to_f32(ld_u16(b));
 #pragma unroll
-        for (int j = 0; j < 32; j++) o[j] = __fmul_rn(d, (float)(int8_t)__ldg(b + 2 + j));
+        for (int j = 0; j < 32; j++) o[j] = __fmul_rn(d, s8_to_f(__ldg(b + 2 + j)));
     }
 };
 
@@ -89,16 +99,24 @@ struct Decode<NNQ_Q4_K> {
                       (((hdr.w >> (8 * (j >> 2) + 2 * (j & 3))) & 3u) << 4);
         uint32_t mn = ((hdr.z >> (8 * (j >> 1) + 4 * (j & 1))) & 15u) |
                       (((hdr.w >> (16 + 8 * (j >> 2) + 2 * (j & 3))) & 3u) << 4);
-        float s = __fmul_rn(d, (float)sc);
-        float m = __fmul_rn(dmin, (float)mn);
+        float s = __fmul_rn(d, u2f(sc));
+        float m = __fmul_rn(dmin, u2f(mn));
         uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+        // Two weights (one byte) per step on the packed f32 pipe, every lane rounded as the scalar
+        // operation would be. The high nibble stays where it is: the mantissa then holds 16 q, and
+        // s / 16 (exact) takes its place as the factor; x - m is x + (-m).
+        const float2 unbias = make_float2(-8388608.0f, -8388608.0f);
+        const float2 s2 = make_float2(s, __fmul_rn(s, 0.0625f));
+        const float2 nm2 = make_float2(-m, -m);
 #pragma unroll
         for (int v = 0; v < 4; v++) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                uint32_t byte = (qw[v] >> (8 * i)) & 0xFFu;
-                o[8 * v + 2 * i] = __fsub_rn(__fmul_rn(s, (float)(byte & 15u)), m);
-                o[8 * v + 2 * i + 1] = __fsub_rn(__fmul_rn(s, (float)(byte >> 4)), m);
+                const uint32_t t = qw[v] >> (8 * i);
+                float2 c = make_float2(__uint_as_float((t & 0x0Fu) | 0x4B000000u), __uint_as_float((t & 0xF0u) | 0x4B000000u));
+                c = __fadd2_rn(__fmul2_rn(__fadd2_rn(c, unbias), s2), nm2);
+                o[8 * v + 2 * i] = c.x;
+                o[8 * v + 2 * i + 1] = c.y;
             }
         }
     }
@@ -129,8 +147,8 @@ struct Decode<NNQ_Q4_K_GGML> {
             sc = (sbyte(j + 4) & 15u) | ((sbyte(j - 4) >> 6) << 4);
             mn = (sbyte(j + 4) >> 4) | ((sbyte(j) >> 6) << 4);
         }
-        float s = __fmul_rn(d, (float)sc);
-        float m = __fmul_rn(dmin, (float)mn);
+        float s = __fmul_rn(d, u2f(sc));
+        float m = __fmul_rn(dmin, u2f(mn));
         const uint4 *qp = reinterpret_cast<const uint4 *>(b + 16 + 32 * (j >> 1));
         int sh = 4 * (j & 1);
 #pragma unroll
@@ -142,7 +160,7 @@ struct Decode<NNQ_Q4_K_GGML> {
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     uint32_t nib = (qw[v] >> (8 * i + sh)) & 15u;
-                    o[16 * h + 4 * v + i] = __fsub_rn(__fmul_rn(s, (float)nib), m);
+                    o[16 * h + 4 * v + i] = __fsub_rn(__fmul_rn(s, u2f(nib)), m);
                 }
         }
     }
@@ -154,22 +172,22 @@ struct Decode<NNQ_Q6_K> {
         const uint8_t *b = w + (c >> 3) * 210;  // only 2-byte aligned: byte loads
         int idx0 = (int)(c & 7) * 32;
         float d = f16_bits_to_f32(ld_u16(b + 208));
-        float s0 = __fmul_rn(d, (float)(int8_t)__ldg(b + 192 + idx0 / 16));
-        float s1 = __fmul_rn(d, (float)(int8_t)__ldg(b + 192 + idx0 / 16 + 1));
+        float s0 = __fmul_rn(d, s8_to_f(__ldg(b + 192 + idx0 / 16)));
+        float s1 = __fmul_rn(d, s8_to_f(__ldg(b + 192 + idx0 / 16 + 1)));
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             uint32_t qh = __ldg(b + 128 + idx0 / 4 + i);
             uint32_t ql0 = __ldg(b + idx0 / 2 + 2 * i);
             uint32_t ql1 = __ldg(b + idx0 / 2 + 2 * i + 1);
             float s = i < 4 ? s0 : s1;
-            int q0 = (int)((ql0 & 15u) | (((qh >> 0) & 3u) << 4)) - 32;
-            int q1 = (int)((ql0 >> 4) | (((qh >> 2) & 3u) << 4)) - 32;
-            int q2 = (int)((ql1 & 15u) | (((qh >> 4) & 3u) << 4)) - 32;
-            int q3 = (int)((ql1 >> 4) | (((qh >> 6) & 3u) << 4)) - 32;
-            o[4 * i + 0] = __fmul_rn(s, (float)q0);
-            o[4 * i + 1] = __fmul_rn(s, (float)q1);
-            o[4 * i + 2] = __fmul_rn(s, (float)q2);
-            o[4 * i + 3] = __fmul_rn(s, (float)q3);
+            const uint32_t q0 = (ql0 & 15u) | (((qh >> 0) & 3u) << 4);
+            const uint32_t q1 = (ql0 >> 4) | (((qh >> 2) & 3u) << 4);
+            const uint32_t q2 = (ql1 & 15u) | (((qh >> 4) & 3u) << 4);
+            const uint32_t q3 = (ql1 >> 4) | (((qh >> 6) & 3u) << 4);
+            o[4 * i + 0] = __fmul_rn(s, u2f_biased(q0, 32.0f));
+            o[4 * i + 1] = __fmul_rn(s, u2f_biased(q1, 32.0f));
+            o[4 * i + 2] = __fmul_rn(s, u2f_biased(q2, 32.0f));
+            o[4 * i + 3] = __fmul_rn(s, u2f_biased(q3, 32.0f));
         }
     }
 };
@@ -185,10 +203,10 @@ struct Decode<NNQ_Q5_0> {
 #pragma unroll
         for (int j = 0; j < 16; j++) {
             uint32_t q = __ldg(b + 6 + j);
-            int x0 = (int)((q & 15u) | (((qh >> (2 * j)) & 1u) << 4)) - 16;
-            int x1 = (int)((q >> 4) | (((qh >> (2 * j + 1)) & 1u) << 4)) - 16;
-            o[2 * j] = __fmul_rn(d, (float)x0);
-            o[2 * j + 1] = __fmul_rn(d, (float)x1);
+            const uint32_t x0 = (q & 15u) | (((qh >> (2 * j)) & 1u) << 4);
+            const uint32_t x1 = (q >> 4) | (((qh >> (2 * j + 1)) & 1u) << 4);
+            o[2 * j] = __fmul_rn(d, u2f_biased(x0, 16.0f));
+            o[2 * j + 1] = __fmul_rn(d, u2f_biased(x1, 16.0f));
         }
     }
 };
@@ -205,8 +223,8 @@ struct Decode<NNQ_Q5_1> {
             uint32_t q = __ldg(b + 8 + j);
             uint32_t x0 = (q & 15u) | (((qh >> (2 * j)) & 1u) << 4);
             uint32_t x1 = (q >> 4) | (((qh >> (2 * j + 1)) & 1u) << 4);
-            o[2 * j] = __fadd_rn(__fmul_rn(d, (float)x0), m);
-            o[2 * j + 1] = __fadd_rn(__fmul_rn(d, (float)x1), m);
+            o[2 * j] = __fadd_rn(__fmul_rn(d, u2f(x0)), m);
+            o[2 * j + 1] = __fadd_rn(__fmul_rn(d, u2f(x1)), m);
         }
     }
 };
@@ -223,14 +241,14 @@ struct Decode<NNQ_Q2_K> {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             uint32_t sb = __ldg(b + idx0 / 16 + h);
-            float s = __fmul_rn(d, (float)(sb & 15u));
-            float m = __fmul_rn(dmin, (float)(sb >> 4));
+            float s = __fmul_rn(d, u2f(sb & 15u));
+            float m = __fmul_rn(dmin, u2f(sb >> 4));
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 uint32_t q = __ldg(b + 16 + idx0 / 4 + 4 * h + i);
 #pragma unroll
                 for (int t = 0; t < 4; t++)
-                    o[16 * h + 4 * i + t] = __fsub_rn(__fmul_rn(s, (float)((q >> (2 * t)) & 3u)), m);
+                    o[16 * h + 4 * i + t] = __fsub_rn(__fmul_rn(s, u2f((q >> (2 * t)) & 3u)), m);
             }
         }
     }
@@ -249,16 +267,16 @@ struct Decode<NNQ_Q3_K> {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             int k = k0 + h;
-            int sc = (int)(((lo >> (4 * h)) & 15u) | (((hi >> (2 * (k & 3))) & 3u) << 4)) - 32;
-            float s = __fmul_rn(d, (float)sc);
+            const uint32_t sc = ((lo >> (4 * h)) & 15u) | (((hi >> (2 * (k & 3))) & 3u) << 4);
+            float s = __fmul_rn(d, u2f_biased(sc, 32.0f));
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 uint32_t q = __ldg(b + 32 + idx0 / 4 + 4 * h + i);
                 uint32_t hm = __ldg(b + idx0 / 8 + 2 * h + i / 2) >> (4 * (i & 1));
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
-                    int q3 = (int)(((q >> (2 * t)) & 3u) | (((hm >> t) & 1u) << 2)) - 4;
-                    o[16 * h + 4 * i + t] = __fmul_rn(s, (float)q3);
+                    const uint32_t q3 = ((q >> (2 * t)) & 3u) | (((hm >> t) & 1u) << 2);
+                    o[16 * h + 4 * i + t] = __fmul_rn(s, u2f_biased(q3, 4.0f));
                 }
             }
         }
@@ -277,14 +295,14 @@ struct Decode<NNQ_Q5_K> {
         const uint8_t *S = b + 4;
         uint32_t sc = ((__ldg(S + j / 2) >> (4 * (j & 1))) & 15u) | (((__ldg(S + 8 + j / 4) >> (2 * (j & 3))) & 3u) << 4);
         uint32_t mn = ((__ldg(S + 4 + j / 2) >> (4 * (j & 1))) & 15u) | (((__ldg(S + 10 + j / 4) >> (2 * (j & 3))) & 3u) << 4);
-        float s = __fmul_rn(d, (float)sc), m = __fmul_rn(dmin, (float)mn);
+        float s = __fmul_rn(d, u2f(sc)), m = __fmul_rn(dmin, u2f(mn));
         uint32_t qh = __ldg(reinterpret_cast<const uint32_t *>(b + 16 + 4 * j));
         uint4 qs = __ldg(reinterpret_cast<const uint4 *>(b + 48 + 16 * j));
         uint32_t qw[4] = {qs.x, qs.y, qs.z, qs.w};
 #pragma unroll
         for (int i = 0; i < 32; i++) {
             uint32_t q5 = ((qw[i / 8] >> (4 * (i & 7))) & 15u) | (((qh >> i) & 1u) << 4);
-            o[i] = __fsub_rn(__fmul_rn(s, (float)q5), m);
+            o[i] = __fsub_rn(__fmul_rn(s, u2f(q5)), m);
         }
     }
 };

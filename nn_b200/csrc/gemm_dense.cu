@@ -488,7 +488,9 @@ static bool make_map(const void *base, int64_t rows, int64_t k, int box_rows, CU
 }
 
 bool gemm_dense_shape_ok(const nnq_ctx *ctx, int64_t m, int64_t n, int64_t k, int x_dt) {
-    return ctx->d_dense && x_dt == NNQ_BF16 && m >= 256 && k >= kDgBK && k % kDgBK == 0 && n >= 1 &&
+    static const char *env_min = diag_env("NNQ_DENSE_MIN_M");   // tuning aid
+    const int64_t min_m = env_min ? atoll(env_min) : 256;
+    return ctx->d_dense && x_dt == NNQ_BF16 && m >= min_m && k >= kDgBK && k % kDgBK == 0 && n >= 1 &&
            (size_t)n * (size_t)k * 2 <= ctx->dense_bytes && m < (1ll << 31) && n < (1ll << 31) && encode_fn() != nullptr;
 }
 bool gemm_dense_supported(const nnq_ctx *ctx, const nnq_weight *w, int64_t m, int x_dt) {

@@ -7,7 +7,9 @@
 //     tensor map of x with 128-byte swizzle, issued by one thread, counted on the stage's "full"
 //     barrier; rows beyond M are zero-filled); f32 activations are converted by the producers;
 //   * 8 producer warps dequantize the 128 x 64 weight tile to bf16 (f32 decode, the bit-exact
-//     one, then round-to-nearest-even) into the same K-major 128-byte-swizzled layout;
+//     one, then round-to-nearest-even) into the same K-major 128-byte-swizzled layout; two such
+//     groups of warps take alternate k steps (with one group an SM held two warps per scheduler
+//     and the decode's dependent chains, not its instruction count, set the pace of a k step);
 //   * one thread issues 4 * MT tcgen05.mma (M 128, N 128, K 16, bf16 x bf16 -> f32) from shared
 //     memory descriptors into the accumulators and commits them onto the stage's "empty" barrier.
 // The larger MT, the more activation rows reuse each dequantized weight tile (the dequantization,
@@ -28,10 +30,39 @@
 
 namespace nnq {
 
-constexpr int kTcProducerWarps = 8;
-constexpr int kTcThreads = (kTcProducerWarps + 1) * 32;
+constexpr int kTcProducerWarps = 8;          // warps that decode one weight tile
+constexpr int kTcGroups = 2;                 // producer groups; group g fills the k steps g, g + kTcGroups, ...
+constexpr int kTcMmaWarp = kTcProducerWarps * kTcGroups;
+constexpr int kTcLoadWarp = kTcMmaWarp + 1;  // streams the raw blocks of formats that take the raw ring
+constexpr int kTcThreads = (kTcLoadWarp + 1) * 32;
 constexpr int kTcBK = 64;                    // k per stage: one 128-byte swizzle row of bf16
 constexpr int kTcTileBytes = 128 * 128;      // 128 rows x 128 bytes
+constexpr int kTcEpiBytes = kTcMmaWarp * 32 * 33 * 4;   // epilogue staging: a 32 x 32 f32 block (+ pad) per warp
+
+// Raw ring (Q4_K): the 144-byte super-blocks of the CTA's 128 weight rows arrive by TMA (the raw tensor
+// seen as rows of 32-bit words), one or two super-blocks of every row per chunk, one copy per chunk and
+// two chunks in flight. Per-thread register loads of the 32 bytes a k step needs kept less than a
+// megabyte in flight on the whole device, and the memory system's latency, not the decode, set the pace
+// (0.47 TB/s of reads in the profile of a 128-row product); a bulk copy per row (128 per chunk) was
+// bound by the rate at which the copy unit takes small copies.
+template <int FMT>
+struct TcRaw { static constexpr bool kRing = FMT == NNQ_Q4_K; };
+template <int MT>
+struct TcRawGeom {
+    static constexpr int kSB = MT == 4 ? 1 : 2;                     // super-blocks of a row per chunk
+    static constexpr int kKb = 4 * kSB;                             // k steps per chunk
+    static constexpr int kPitch = 144 * kSB;                        // the box is stored densely
+    static constexpr int kBytes = 128 * kPitch;                     // one chunk (a multiple of 1024)
+};
+template <int FMT, int MT>
+__host__ __device__ constexpr int tc_ring_bytes() { return TcRaw<FMT>::kRing ? 2 * TcRawGeom<MT>::kBytes : 0; }
+template <int FMT, int MT>
+constexpr int tc_max_stages() { return TcRaw<FMT>::kRing ? (MT == 4 ? 2 : (MT == 2 ? 3 : 4)) : (MT == 4 ? 2 : (MT == 2 ? 4 : 6)); }
+template <int FMT, int MT>
+static int tc_smem_bytes(int stages) {
+    const int tiles = stages * (MT + 1) * kTcTileBytes;
+    return 1024 + tc_ring_bytes<FMT, MT>() + (tiles > kTcEpiBytes ? tiles : kTcEpiBytes);
+}
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -97,20 +128,26 @@ struct TcGroup {
 
 template <int FMT, int MT, typename XT, bool TMAX>
 __global__ void __launch_bounds__(kTcThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscales,
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscales,
                const XT *__restrict__ x, const float *__restrict__ bias, void *__restrict__ y, int64_t M, int64_t N,
                int64_t K, int y_dt, int stages, float *__restrict__ partials, int *status, const TcGroup grp) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles (the dynamic window is not guaranteed to start on one)
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *smem_al = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr bool kRawRing = TcRaw<FMT>::kRing;
+    using RG = TcRawGeom<MT>;
+    uint8_t *rawring = smem_al;                                  // two raw chunks (ring formats only)
+    uint8_t *smem = smem_al + tc_ring_bytes<FMT, MT>();          // the tile stages; reused by the epilogue
     constexpr int kStageBytes = (MT + 1) * kTcTileBytes;   // MT activation tiles, then the weight tile
-    __shared__ __align__(8) uint64_t bars[2 * 8 + 1];      // full[stages], empty[stages], accumulators ready
+    // full[stages], empty[stages], accumulators ready, raw chunk full[2], raw chunk empty[2]
+    __shared__ __align__(8) uint64_t bars[2 * 8 + 1 + 4];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t n0 = (int64_t)blockIdx.x * 128;
     int64_t m0 = (int64_t)blockIdx.y * 128 * MT;
+    int wrow0 = (int)n0;   // first row of this CTA's weight tile in the raw tensor map (all experts' rows)
     if (grp.offsets) {
         // which expert this row tile belongs to; row tiles beyond the last expert have nothing to do
         __shared__ int gsel[3];
@@ -136,14 +173,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
         m0 = gsel[1];
         M = gsel[2];                    // rows of this expert end here: later rows are not stored
         w += (size_t)gsel[0] * grp.w_stride;
+        wrow0 += gsel[0] * (int)N;
         if (wscales) wscales += (size_t)gsel[0] * grp.s_stride;
         if (bias) bias += (size_t)gsel[0] * N;
     }
     // this CTA's share of the k steps (gridDim.z slices of K; partial sums go to `partials`)
     const int nkb_all = (int)(K / kTcBK);
-    const int kb_lo = (int)(((long long)blockIdx.z * nkb_all) / gridDim.z);
-    const int nkb = (int)(((long long)(blockIdx.z + 1) * nkb_all) / gridDim.z) - kb_lo;
+    int kb_lo, nkb;
+    if (kRawRing) {
+        // slices of whole raw chunks (the host asks for no more slices than there are chunks)
+        const int nch_all = (nkb_all + RG::kKb - 1) / RG::kKb;
+        kb_lo = (int)(((long long)blockIdx.z * nch_all) / gridDim.z) * RG::kKb;
+        const int kb_hi = (int)(((long long)(blockIdx.z + 1) * nch_all) / gridDim.z) * RG::kKb;
+        nkb = (kb_hi < nkb_all ? kb_hi : nkb_all) - kb_lo;
+    } else {
+        kb_lo = (int)(((long long)blockIdx.z * nkb_all) / gridDim.z);
+        nkb = (int)(((long long)(blockIdx.z + 1) * nkb_all) / gridDim.z) - kb_lo;
+    }
     const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * 8, acc_s = full_s + 16 * 8;
+    const uint32_t rawfull_s = full_s + 17 * 8, rawempty_s = full_s + 19 * 8;
     constexpr uint32_t kTmemCols = 128 * MT;
 
     if (tid == 0) {
@@ -152,10 +200,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
             mbar_init(empty_s + 8 * s, 1);
         }
         mbar_init(acc_s, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(rawfull_s + 8 * b, 1);
+            mbar_init(rawempty_s + 8 * b, kTcMmaWarp);
+        }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kTcProducerWarps) {
+    if (warp == kTcMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -164,36 +216,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
     bool ok = true;
+    int raw_issued = 0;   // loader warp: raw chunks whose copies were started
 
-    if (warp < kTcProducerWarps) {
+    if (warp < kTcMmaWarp) {
         // ---------------- producers ----------------
         const int64_t cpr = K / 32;                 // 32-weight chunks per weight row
-        const int brow = tid & 127, bhalf = tid >> 7;   // weight tile: row and which 32 of the 64 k
-        int slot = 0;
-        uint32_t phase = 0;
-        // Software pipeline: the tile data of step kb + 1 is decoded into registers right after step kb
-        // has been handed to the tensor core, so that the work runs under the MMAs and under the wait
-        // for a free stage. For Q4_K the raw bytes are loaded one step earlier still (two steps
-        // ahead of their use), so that the decode never waits for global memory.
+        const int pgroup = warp / kTcProducerWarps;             // this warp's producer group
+        const int ptid = tid - pgroup * kTcProducerWarps * 32;  // thread within the group
+        const int brow = ptid & 127, bhalf = ptid >> 7;   // weight tile: row and which 32 of the 64 k
+        // Software pipeline: the tile data of this group's next step is decoded into registers right after
+        // the current step has been handed to the tensor core, so that the work runs under the MMAs and
+        // under the wait for a free stage. Ring formats decode from the raw chunk in shared memory, the
+        // others load their blocks from global memory inside the decode.
         constexpr int kAChunks = (128 * MT * 8) / (kTcProducerWarps * 32);   // 16-byte activation chunks per thread
         uint4 wreg[4];
-        uint4 areg[kAChunks];
-        const int ac = tid & 7;
-        constexpr bool kSplitLoad = FMT == NNQ_Q4_K;
-        uint4 raw_h = make_uint4(0, 0, 0, 0), raw_q = make_uint4(0, 0, 0, 0);
-        auto load_raw = [&](int kb) {
-            if (kSplitLoad && n0 + brow < N) {
-                const int64_t c = (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf;
-                const uint8_t *b = w + (c >> 3) * 144;
-                raw_h = __ldg(reinterpret_cast<const uint4 *>(b));
-                raw_q = __ldg(reinterpret_cast<const uint4 *>(b + 16 + 16 * (int)(c & 7)));
-            }
-        };
+        const int ac = ptid & 7;
         auto fetch = [&](int kb) {
             float wv[32];
-            if (n0 + brow < N) {
-                if (kSplitLoad) Decode<NNQ_Q4_K>::chunk_regs(raw_h, raw_q, (kb * 2 + bhalf) & 7, wv);
-                else Decode<FMT>::chunk(w, wscales, (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf, wv);
+            if (kRawRing) {
+                // k step kb of the whole product = step kl of this CTA's slice (slices start on chunk
+                // boundaries, so sub-block and super-block positions follow from kl alone)
+                const int kl = kb - kb_lo, lc = kl / RG::kKb, inch = kl % RG::kKb;
+                if (inch == pgroup) ok = mbar_wait_fast(rawfull_s + 8 * (lc & 1), (uint32_t)(lc >> 1) & 1u);   // this group's first step in the chunk
+                const uint8_t *rb = rawring + (lc & 1) * RG::kBytes + brow * RG::kPitch + (inch >> 2) * 144;
+                const int j = (inch & 3) * 2 + bhalf;
+                const uint4 hdr = *reinterpret_cast<const uint4 *>(rb);
+                const uint4 qq = *reinterpret_cast<const uint4 *>(rb + 16 + 16 * j);
+                if (ok && n0 + brow < N) {
+                    Decode<NNQ_Q4_K>::chunk_regs(hdr, qq, j, wv);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) wv[i] = 0.0f;
+                }
+                if (inch + kTcGroups >= RG::kKb || kl + kTcGroups >= nkb) {   // this group's last step in the chunk
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(rawempty_s + 8 * (lc & 1));
+                }
+            } else if (n0 + brow < N) {
+                Decode<FMT>::chunk(w, wscales, (n0 + brow) * cpr + (int64_t)kb * 2 + bhalf, wv);
             } else {
 #pragma unroll
                 for (int i = 0; i < 32; i++) wv[i] = 0.0f;
@@ -202,33 +262,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
             for (int c = 0; c < 4; c++)
                 wreg[c] = make_uint4(pack_bf16(wv[8 * c], wv[8 * c + 1]), pack_bf16(wv[8 * c + 2], wv[8 * c + 3]),
                                      pack_bf16(wv[8 * c + 4], wv[8 * c + 5]), pack_bf16(wv[8 * c + 6], wv[8 * c + 7]));
-#pragma unroll
-            for (int i = 0; i < (TMAX ? 0 : kAChunks); i++) {
-                const int r = (tid >> 3) + 32 * i;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                const int64_t row = m0 + r;
-                if (row < M) {
-                    const XT *src = x + row * K + (int64_t)kb * kTcBK + ac * 8;
-                    if (sizeof(XT) == 2) {
-                        v = __ldg(reinterpret_cast<const uint4 *>(src));
-                    } else {
-                        float4 fa = __ldg(reinterpret_cast<const float4 *>(src));
-                        float4 fb = __ldg(reinterpret_cast<const float4 *>(src) + 1);
-                        v = make_uint4(pack_bf16(fa.x, fa.y), pack_bf16(fa.z, fa.w), pack_bf16(fb.x, fb.y), pack_bf16(fb.z, fb.w));
-                    }
-                }
-                areg[i] = v;
-            }
         };
-        load_raw(kb_lo);
-        fetch(kb_lo);
-        if (nkb > 1) load_raw(kb_lo + 1);
-        for (int kb = 0; kb < nkb && ok; kb++) {
+        // activation chunk i of this thread for k step kb (the path without TMA: f32 activations, or a
+        // row pitch the tensor map cannot express); loaded when the stage is filled, four at a time
+        auto load_a = [&](int kb, int i) {
+            const int r = (ptid >> 3) + 32 * i;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            const int64_t row = m0 + r;
+            if (row < M) {
+                const XT *src = x + row * K + (int64_t)kb * kTcBK + ac * 8;
+                if (sizeof(XT) == 2) {
+                    v = __ldg(reinterpret_cast<const uint4 *>(src));
+                } else {
+                    float4 fa = __ldg(reinterpret_cast<const float4 *>(src));
+                    float4 fb = __ldg(reinterpret_cast<const float4 *>(src) + 1);
+                    v = make_uint4(pack_bf16(fa.x, fa.y), pack_bf16(fa.z, fa.w), pack_bf16(fb.x, fb.y), pack_bf16(fb.z, fb.w));
+                }
+            }
+            return v;
+        };
+        if (pgroup < nkb) fetch(kb_lo + pgroup);
+        for (int kb = pgroup; kb < nkb && ok; kb += kTcGroups) {
+            const int slot = kb % stages;
+            const uint32_t phase = (uint32_t)(kb / stages) & 1u;
             if (kb >= stages) ok = mbar_wait_fast(empty_s + 8 * slot, phase ^ 1u);
             if (!ok) break;
             uint8_t *stage = smem + (size_t)slot * kStageBytes;
             uint8_t *bt = stage + MT * kTcTileBytes;
-            if (TMAX && tid == 0) {
+            if (TMAX && ptid == 0) {
                 // the stage is free: let the activation tiles of this k step stream in while the
                 // weight tile is written
                 mbar_expect_tx_only(full_s + 8 * slot, MT * kTcTileBytes);
@@ -239,56 +300,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
 #pragma unroll
             for (int c = 0; c < 4; c++) *reinterpret_cast<uint4 *>(bt + swz(brow, bhalf * 4 + c)) = wreg[c];
 #pragma unroll
-            for (int i = 0; i < (TMAX ? 0 : kAChunks); i++) {
-                const int r = (tid >> 3) + 32 * i;
-                *reinterpret_cast<uint4 *>(stage + (r >> 7) * kTcTileBytes + swz(r & 127, ac)) = areg[i];
+            for (int i0 = 0; i0 < (TMAX ? 0 : kAChunks); i0 += 4) {
+                uint4 av[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) av[j] = load_a(kb_lo + kb, i0 + j);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int r = (ptid >> 3) + 32 * (i0 + j);
+                    *reinterpret_cast<uint4 *>(stage + (r >> 7) * kTcTileBytes + swz(r & 127, ac)) = av[j];
+                }
             }
             fence_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(full_s + 8 * slot);
-            if (++slot == stages) {
-                slot = 0;
-                phase ^= 1u;
-            }
-            if (kb + 1 < nkb) {
-                fetch(kb_lo + kb + 1);
-                if (kb + 2 < nkb) load_raw(kb_lo + kb + 2);
-            }
+            if (kb + kTcGroups < nkb) fetch(kb_lo + kb + kTcGroups);
         }
         // ---------------- epilogue ----------------
         if (ok) ok = mbar_wait_fast(acc_s, 0);
         if (ok) {
             tc_fence_after();
-            const int q = warp & 3, chalf = warp >> 2;   // TMEM lane quarter, column half
+            constexpr int kColsPerWarp = 128 / (kTcMmaWarp / 4);
+            const int q = warp & 3, cpart = warp >> 2;   // TMEM lane quarter, column part
+            // A lane reads one accumulator row; the block is turned through shared memory (the tile stages
+            // are free by now) so that a warp stores 32 consecutive columns of one row per instruction.
+            float *stg = reinterpret_cast<float *>(smem) + warp * (32 * 33);
 #pragma unroll 1
             for (int mt = 0; mt < MT; mt++) {
-                const int64_t row = m0 + mt * 128 + q * 32 + lane;
 #pragma unroll 1
-                for (int cc = 0; cc < 2; cc++) {
-                    const int col0 = chalf * 64 + cc * 32;
+                for (int cc = 0; cc < kColsPerWarp / 32; cc++) {
+                    const int col0 = cpart * kColsPerWarp + cc * 32;
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * 128 + col0), v);
-                    if (row < M) {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            const int64_t col = n0 + col0 + i;
-                            if (col < N) {
-                                float f = __uint_as_float(v[i]);
-                                if (partials) {   // K is split over CTAs: bias and conversion happen in the reduction
-                                    partials[((size_t)blockIdx.z * M + row) * N + col] = f;
-                                    continue;
-                                }
-                                if (bias) f += __ldg(bias + col);
-                                if (y_dt == NNQ_F32) reinterpret_cast<float *>(y)[row * N + col] = f;
-                                else reinterpret_cast<__nv_bfloat16 *>(y)[row * N + col] = __float2bfloat16_rn(f);
-                            }
+                    for (int i = 0; i < 32; i++) stg[lane * 33 + i] = __uint_as_float(v[i]);
+                    __syncwarp();
+                    const int64_t col = n0 + col0 + lane;
+                    const float bv = (bias && !partials && col < N) ? __ldg(bias + col) : 0.0f;
+#pragma unroll 4
+                    for (int rr = 0; rr < 32; rr++) {
+                        const int64_t row = m0 + mt * 128 + q * 32 + rr;
+                        if (row < M && col < N) {
+                            const float f = stg[rr * 33 + lane];
+                            if (partials) partials[((size_t)blockIdx.z * M + row) * N + col] = f;   // bias and conversion happen in the reduction
+                            else if (y_dt == NNQ_F32) reinterpret_cast<float *>(y)[row * N + col] = f + bv;
+                            else reinterpret_cast<__nv_bfloat16 *>(y)[row * N + col] = __float2bfloat16_rn(f + bv);
                         }
                     }
+                    __syncwarp();
                 }
             }
             tc_fence_before();
         }
-    } else if (lane == 0) {
+    } else if (warp == kTcMmaWarp && lane == 0) {
         // ---------------- MMA issuer ----------------
         // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = 128, M = 128
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
@@ -314,13 +377,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const uint8_t *__restri
             }
         }
         if (ok) umma_commit(acc_s);            // accumulators complete
+    } else if (kRawRing && warp == kTcLoadWarp) {
+        // ---------------- raw block loader ----------------
+        const int nch = (nkb + RG::kKb - 1) / RG::kKb;
+        const uint32_t ring_s = smem_u32(rawring);
+        for (int lc = 0; lc < nch && ok; lc++) {
+            const int buf = lc & 1;
+            if (lc >= 2) ok = mbar_wait_fast(rawempty_s + 8 * buf, ((uint32_t)(lc >> 1) & 1u) ^ 1u);
+            if (!ok) break;
+            // a box of 128 rows x kSB super-blocks (36 words each); what lies beyond the row's end or the
+            // tensor's last row arrives as zeros and counts like the rest
+            if (lane == 0) {
+                mbar_expect_tx(rawfull_s + 8 * buf, RG::kBytes);
+                tma_load_2d(ring_s + buf * RG::kBytes, &wmap, (kb_lo / 4 + lc * RG::kSB) * 36, wrow0, rawfull_s + 8 * buf);
+            }
+            raw_issued = lc + 1;
+        }
     }
     if (!ok) {
         abort_s = 1;
         if (lane == 0) atomicExch(status, 1);
     }
     __syncthreads();
-    if (warp == kTcProducerWarps) {
+    if (kRawRing && warp == kTcLoadWarp && abort_s) {
+        // an aborted CTA may leave before its raw chunks were consumed: wait (bounded) for the copies
+        for (int lc = raw_issued > 2 ? raw_issued - 2 : 0; lc < raw_issued; lc++) mbar_wait(rawfull_s + 8 * (lc & 1), (uint32_t)(lc >> 1) & 1u);
+    }
+    if (warp == kTcMmaWarp) {
         // with an aborted CTA, MMAs may still be in flight: give them a bounded chance to finish
         if (abort_s) mbar_wait(acc_s, 0);
         tc_fence_after();
@@ -347,16 +430,18 @@ gemm_tc_reduce_kernel(const float *__restrict__ partials, int slices, const floa
 // ---------------------------------------------------------------------------------
 
 bool gemm_tc_supported(const nnq_weight *w, int64_t m) {
-    return w && w->d_raw && m >= 1 && w->k >= kTcBK && w->k % kTcBK == 0 && w->n >= 1;
+    // (the raw ring's bulk copies read 16-byte aligned super-blocks)
+    return w && w->d_raw && m >= 1 && w->k >= kTcBK && w->k % kTcBK == 0 && w->n >= 1 &&
+           !(TcRaw<NNQ_Q4_K>::kRing && w->fmt == NNQ_Q4_K && ((uintptr_t)w->d_raw & 15u));
 }
 
 // Tensor map of the bf16 activations [M, K]: boxes of 64 x 128 elements, 128-byte swizzle, zero fill
 // beyond M. Returns false when the driver entry point is not available (the producers then stage
 // the activations themselves).
-static bool make_x_map(const TcArgs &a, CUtensorMap *map) {
-    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeFn encode_fn() {
     static EncodeFn fn = nullptr;
     static bool tried = false;
     if (!tried) {
@@ -367,6 +452,10 @@ static bool make_x_map(const TcArgs &a, CUtensorMap *map) {
             fn = reinterpret_cast<EncodeFn>(p);
         cudaGetLastError();
     }
+    return fn;
+}
+static bool make_x_map(const TcArgs &a, CUtensorMap *map) {
+    EncodeFn fn = encode_fn();
     if (!fn || ((uintptr_t)a.x & 15u) || (a.k * 2) % 16) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)a.m};
     const cuuint64_t strides[1] = {(cuuint64_t)a.k * 2};
@@ -376,40 +465,53 @@ static bool make_x_map(const TcArgs &a, CUtensorMap *map) {
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor map of raw Q4_K blocks as 32-bit words: [rows, K / 256 * 36], boxes of 128 rows x sb super-blocks.
+static bool make_w_map(const void *w, int64_t rows, int64_t k, int sb, CUtensorMap *map) {
+    EncodeFn fn = encode_fn();
+    const cuuint64_t row_bytes = (cuuint64_t)(k / 256) * 144;
+    if (!fn || ((uintptr_t)w & 15u) || rows < 1 || rows >= (1ll << 31)) return false;
+    const cuuint64_t dims[2] = {row_bytes / 4, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {36u * (cuuint32_t)sb, 128u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int FMT, int MT, typename XT, bool TMAX>
-static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, int *status, int ksplit, float *partials, int stages,
+static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, const CUtensorMap &wmap, int *status, int ksplit, float *partials, int stages,
                               int smem_bytes, cudaStream_t stream, const TcGroup &grp = TcGroup{nullptr, 0, 0, 0}, int grid_y = 0) {
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, MT, XT, TMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<FMT, MT, XT, TMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
     dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)(grid_y ? grid_y : (a.m + 128 * MT - 1) / (128 * MT)), (unsigned)ksplit);
     gemm_tc_kernel<FMT, MT, XT, TMAX><<<grid, kTcThreads, smem_bytes, stream>>>(
-        map, a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages,
+        map, wmap, a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages,
         ksplit > 1 ? partials : nullptr, status, grp);
     return cudaGetLastError();
 }
 
 template <int FMT, int MT, typename XT>
 static cudaError_t launch_one(const TcArgs &a, int *status, int ksplit, float *partials, cudaStream_t stream) {
-    const int stage_bytes = (MT + 1) * kTcTileBytes;
-    // MT = 1, 2: 96 KB of stages, so that two CTAs (2 x 128 * MT tensor-memory columns) share an SM and
-    // one CTA's decode overlaps the other's MMAs; MT = 4 fills the SM alone
-    int stages = MT == 4 ? 2 : (MT == 2 ? 2 : 3);
+    // one CTA per SM: as many stages as fit beside the raw ring
+    int stages = tc_max_stages<FMT, MT>();
     const int nkb = (int)(a.k / kTcBK);
     if (stages > nkb / ksplit) stages = nkb / ksplit > 0 ? nkb / ksplit : 1;
-    const int smem_bytes = stages * stage_bytes + 1024;
-    CUtensorMap map;
+    const int smem_bytes = tc_smem_bytes<FMT, MT>(stages);
+    CUtensorMap map, wmap;
     memset(&map, 0, sizeof(map));
+    memset(&wmap, 0, sizeof(wmap));
+    if (TcRaw<FMT>::kRing && !make_w_map(a.w, a.n, a.k, TcRawGeom<MT>::kSB, &wmap)) return cudaErrorNotSupported;
     cudaError_t e;
     if (sizeof(XT) == 2 && make_x_map(a, &map))
-        e = launch_cfg<FMT, MT, XT, sizeof(XT) == 2>(a, map, status, ksplit, partials, stages, smem_bytes, stream);
+        e = launch_cfg<FMT, MT, XT, sizeof(XT) == 2>(a, map, wmap, status, ksplit, partials, stages, smem_bytes, stream);
     else
-        e = launch_cfg<FMT, MT, XT, false>(a, map, status, ksplit, partials, stages, smem_bytes, stream);
+        e = launch_cfg<FMT, MT, XT, false>(a, map, wmap, status, ksplit, partials, stages, smem_bytes, stream);
     if (e != cudaSuccess || ksplit == 1) return e;
     const int64_t total = a.m * a.n;
     gemm_tc_reduce_kernel<<<(int)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048), 256, 0, stream>>>(
@@ -442,17 +544,19 @@ static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, int ks
 template <int FMT, int MT>
 static cudaError_t launch_grouped_mt(const TcGroupArgs &g, int *status, cudaStream_t stream) {
     TcArgs a = {g.w, g.scales, g.x_bf16, g.bias, g.y, g.rows_upper, g.n, g.k, g.fmt, NNQ_BF16, NNQ_F32};
-    CUtensorMap map;
+    CUtensorMap map, wmap;
     memset(&map, 0, sizeof(map));
+    memset(&wmap, 0, sizeof(wmap));
     if (!make_x_map(a, &map)) return cudaErrorNotSupported;
-    const int stage_bytes = (MT + 1) * kTcTileBytes;
-    int stages = MT == 4 ? 2 : (MT == 2 ? 2 : 3);
+    // the experts' raw tensors are one contiguous [experts, N, K] tensor (checked by the caller)
+    if (TcRaw<FMT>::kRing && !make_w_map(g.w, (int64_t)g.experts * g.n, g.k, TcRawGeom<MT>::kSB, &wmap)) return cudaErrorNotSupported;
+    int stages = tc_max_stages<FMT, MT>();
     const int nkb = (int)(g.k / kTcBK);
     if (stages > nkb) stages = nkb;
     const TcGroup grp = {g.offsets, g.experts, g.w_stride, g.s_stride};
     // every expert may end with a partly filled row tile
     const int grid_y = (int)(g.rows_upper / (128 * MT)) + g.experts;
-    return launch_cfg<FMT, MT, __nv_bfloat16, true>(a, map, status, 1, nullptr, stages, stages * stage_bytes + 1024, stream, grp, grid_y);
+    return launch_cfg<FMT, MT, __nv_bfloat16, true>(a, map, wmap, status, 1, nullptr, stages, tc_smem_bytes<FMT, MT>(stages), stream, grp, grid_y);
 }
 
 template <int FMT>
@@ -464,7 +568,8 @@ static cudaError_t launch_grouped_fmt(const TcGroupArgs &g, int *status, cudaStr
 }
 
 nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStream_t stream) {
-    if (g.k < kTcBK || g.k % kTcBK || g.experts < 1 || g.rows_upper < 1) return fail(ctx, NNQ_ERR_UNSUPPORTED, "grouped tensor product: unsupported shape");
+    if (g.k < kTcBK || g.k % kTcBK || g.experts < 1 || g.rows_upper < 1 || (g.fmt == NNQ_Q4_K && (((uintptr_t)g.w & 15u) || g.w_stride != (size_t)g.n * (size_t)(g.k / 256) * 144)))
+        return fail(ctx, NNQ_ERR_UNSUPPORTED, "grouped tensor product: unsupported shape");
     cudaError_t e;
     switch (g.fmt) {
         case NNQ_Q4_0: e = launch_grouped_fmt<NNQ_Q4_0>(g, ctx->d_status, stream); break;
@@ -492,12 +597,13 @@ nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
     {
         const int64_t ctas = ((a.n + 127) / 128) * ((a.m + 127) / 128);
         const int64_t nkb = a.k / kTcBK;
-        // aim at two CTAs per SM for very few rows (the partial sums are small), one otherwise
-        const int64_t target = a.m <= 64 ? 2 * ctx->sm_count : ctx->sm_count;
+        const int64_t target = ctx->sm_count;   // one CTA per SM
         if (a.m <= 256 && ctas * 2 <= target) {
             ksplit = (int)(target / ctas);
             if (ksplit > 8) ksplit = 8;
             if (ksplit > nkb / 4) ksplit = (int)(nkb / 4);
+            // formats on the raw ring slice K in whole chunks of 8 k steps
+            if (TcRaw<NNQ_Q4_K>::kRing && a.fmt == NNQ_Q4_K && ksplit > (nkb + 7) / 8) ksplit = (int)((nkb + 7) / 8);
             if (ksplit < 1) ksplit = 1;
         }
         // the scratch is sized once, at context creation, for the largest split this rule can ask
