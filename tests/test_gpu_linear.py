@@ -483,12 +483,36 @@ def test_failed_staging_growth_leaves_the_context_usable():
     t.release()
 
 
+@pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q4_K_GGML, Q.Q6_K, Q.Q8_0, Q.Q4_0, Q.Q5_K])
+@pytest.mark.parametrize("n,k", [(96, 256), (300, 1280)])
+def test_fused_decode_tensor_path_multiplies_the_rounded_decoded_weights(fmt, n, k):
+    """128 rows of activations take the product with the decode fused in (Q4_K: raw blocks through a
+    shared-memory ring, K of 1280 = five super-blocks: a last chunk of one, split over CTAs). With
+    unit vectors as activations it returns the weights its tensor-core operand held: the oracle's
+    decode rounded to bf16, bit for bit. The 128 columns probed are spread over K."""
+    w, sc = F.gen_weight(fmt, 67, n, k)
+    t = api.from_quantized(w, fmt, [n, k], sc)
+    cols = np.unique(np.concatenate([np.arange(0, k, max(1, k // 100)), [k - 1, k - 2, 255, 256 % k]]))[:128]
+    x = torch.zeros(128, k, device=DEV, dtype=torch.bfloat16)
+    x[torch.arange(len(cols)), torch.from_numpy(cols)] = 1.0
+    y = api.quantized_linear(x, t, None, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    t.backend.device_status()
+    deq = orc.dequantize(fmt, w, n * k, sc).reshape(n, k)
+    want = F.bf16_bits_to_f32(F.to_bf16_bits(deq)).reshape(n, k)[:, cols]
+    got = y.cpu().numpy()[: len(cols)].T
+    normal = (want == 0) | (np.abs(want) >= 2.0 ** -126)   # the tensor cores flush subnormal operands
+    assert np.array_equal(got[normal], want[normal])
+    t.release()
+
+
 @pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q6_K, Q.Q8_0, Q.MXFP4_SPLIT, Q.MXFP4_CORE, Q.MXFP4_GPTOSS, Q.BF16_DENSE])
 def test_decode_once_path_multiplies_the_rounded_decoded_weights(fmt):
-    """With the identity as activations (256 rows, so the decode-once path runs) the product returns
-    the bf16 weights the GEMM was fed: they must be the oracle's decoded weights rounded to bf16, bit
-    for bit -- including MXFP4 blocks with extreme scale exponents, which the direct-to-bf16 decode
-    hands to the f32 decoder (exponent 0) or that sit at the top of its own range."""
+    """With the identity (and rows of zeros below it: 384 rows, so that the decode-once path runs for
+    every format) as activations the product returns the bf16 weights the GEMM was fed: they must be
+    the oracle's decoded weights rounded to bf16, bit for bit -- including MXFP4 blocks with extreme
+    scale exponents, which the direct-to-bf16 decode hands to the f32 decoder (exponent 0) or that sit
+    at the top of its own range."""
     n, k = 96, 256
     w, sc = F.gen_weight(fmt, 61, n, k)
     if fmt == Q.MXFP4_SPLIT or fmt == Q.MXFP4_GPTOSS:
@@ -498,14 +522,15 @@ def test_decode_once_path_multiplies_the_rounded_decoded_weights(fmt):
         w = np.array(w, copy=True)
         w.reshape(-1, 17)[:6, 0] = [0, 1, 3, 250, 251, 252]
     t = api.from_quantized(w, fmt, [n, k], sc)
-    x = torch.eye(k, device=DEV, dtype=torch.bfloat16)
-    y = api.quantized_linear(x, t, None, out_dtype=torch.float32)     # [k, n] = W^T
+    x = torch.zeros(384, k, device=DEV, dtype=torch.bfloat16)
+    x[:k] = torch.eye(k, device=DEV, dtype=torch.bfloat16)
+    y = api.quantized_linear(x, t, None, out_dtype=torch.float32)     # rows [0, k) = W^T
     torch.cuda.synchronize()
     t.backend.device_status()
     deq = orc.dequantize(fmt, w, n * k, sc).reshape(n, k)
     with np.errstate(over="ignore"):
         want = F.bf16_bits_to_f32(F.to_bf16_bits(deq)).reshape(n, k)
-    got = y.cpu().numpy().T
+    got = y.cpu().numpy()[:k].T
     # values compared as numbers (a sum of products with zeros does not keep the sign of a zero weight);
     # weights below the normal range are left out: the tensor cores flush subnormal operands to zero
     check = np.isfinite(want) & ((want == 0) | (np.abs(want) >= 2.0 ** -126))
