@@ -216,6 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
     bool ok = true;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     int raw_issued = 0;   // loader warp: raw chunks whose copies were started
 
     if (warp < kTcMmaWarp) {
@@ -289,6 +290,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             if (!ok) break;
             uint8_t *stage = smem + (size_t)slot * kStageBytes;
             uint8_t *bt = stage + MT * kTcTileBytes;
+            if (kb == pgroup && (!TMAX || ptid == 0))
+                asm volatile("griddepcontrol.wait;" ::: "memory");   // activations come from the kernel before this one
             if (TMAX && ptid == 0) {
                 // the stage is free: let the activation tiles of this k step stream in while the
                 // weight tile is written
@@ -317,6 +320,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         }
         // ---------------- epilogue ----------------
         if (ok) ok = mbar_wait_fast(acc_s, 0);
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // (returns at once: the activations were waited for) before any store
         if (ok) {
             tc_fence_after();
             constexpr int kColsPerWarp = 128 / (kTcMmaWarp / 4);
@@ -416,6 +420,8 @@ __global__ void __launch_bounds__(256)
 gemm_tc_reduce_kernel(const float *__restrict__ partials, int slices, const float *__restrict__ bias, void *__restrict__ y,
                       int64_t M, int64_t N, int y_dt) {
     const int64_t total = M * N;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the partial sums of the product before this kernel
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         float f = 0.0f;
         for (int z = 0; z < slices; z++) f += partials[(size_t)z * total + i];
@@ -490,10 +496,22 @@ static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, const CUt
         configured[dev] = true;
     }
     dim3 grid((unsigned)((a.n + 127) / 128), (unsigned)(grid_y ? grid_y : (a.m + 128 * MT - 1) / (128 * MT)), (unsigned)ksplit);
-    gemm_tc_kernel<FMT, MT, XT, TMAX><<<grid, kTcThreads, smem_bytes, stream>>>(
-        map, wmap, a.w, a.scales, reinterpret_cast<const XT *>(a.x), a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages,
-        ksplit > 1 ? partials : nullptr, status, grp);
-    return cudaGetLastError();
+    // Plain products are launched with programmatic stream serialization: the kernel may become resident
+    // while its predecessor drains, streams and decodes its first weight tiles (which depend on nothing),
+    // and waits for the predecessor before it reads activations or writes anything. Grouped launches read
+    // the expert offsets right away and keep the ordinary stream order.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = grp.offsets ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<FMT, MT, XT, TMAX>, map, wmap, a.w, a.scales, reinterpret_cast<const XT *>(a.x),
+                              a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages, ksplit > 1 ? partials : (float *)nullptr, status, grp);
 }
 
 template <int FMT, int MT, typename XT>
@@ -514,9 +532,16 @@ static cudaError_t launch_one(const TcArgs &a, int *status, int ksplit, float *p
         e = launch_cfg<FMT, MT, XT, false>(a, map, wmap, status, ksplit, partials, stages, smem_bytes, stream);
     if (e != cudaSuccess || ksplit == 1) return e;
     const int64_t total = a.m * a.n;
-    gemm_tc_reduce_kernel<<<(int)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048), 256, 0, stream>>>(
-        partials, ksplit, a.bias, a.y, a.m, a.n, a.y_dt);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((total + 255) / 256 < 2048 ? (total + 255) / 256 : 2048));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_tc_reduce_kernel, (const float *)partials, ksplit, a.bias, a.y, a.m, a.n, a.y_dt);
 }
 
 template <int FMT>
