@@ -86,6 +86,21 @@ struct Decode<NNQ_Q8_0> {
 #pragma unroll
         for (int j = 0; j < 32; j++) o[j] = __fmul_rn(d, s8_to_f(__ldg(b + 2 + j)));
     }
+    // one block as 17 halfwords in shared memory (blocks are only 2-byte aligned); two weights per step
+    // on the packed f32 pipe: byte 0 becomes 2^23 + (q + 128), byte 1 2^23 + 256 (q + 128), d / 256 is exact
+    static __device__ __forceinline__ void chunk_halfwords(const uint16_t *p, float *o) {
+        const float d = f16_bits_to_f32(p[0]);
+        const float2 unbias = make_float2(-(8388608.0f + 128.0f), -(8388608.0f + 32768.0f));
+        const float2 d2 = make_float2(d, __fmul_rn(d, 0.00390625f));
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const uint32_t t = p[1 + i];
+            float2 c = make_float2(__uint_as_float((t & 0x00FFu) ^ 0x4B000080u), __uint_as_float((t & 0xFF00u) ^ 0x4B008000u));
+            c = __fmul2_rn(__fadd2_rn(c, unbias), d2);
+            o[2 * i] = c.x;
+            o[2 * i + 1] = c.y;
+        }
+    }
 };
 
 template <>
@@ -131,10 +146,9 @@ struct Decode<NNQ_Q4_K> {
 
 template <>
 struct Decode<NNQ_Q4_K_GGML> {
-    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
-        const uint8_t *b = w + (c >> 3) * 144;
-        int j = (int)(c & 7);  // sub-block: group g = j/2, low nibbles when j even
-        uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+    // sub-block j of a super-block: the 16-byte header and the 32 quant bytes of the pair of sub-blocks
+    // j / 2 are already in registers (low nibbles when j is even)
+    static __device__ __forceinline__ void chunk_regs(const uint4 &hdr, const uint4 &q0, const uint4 &q1, int j, float *o) {
         float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xFFFFu));
         float dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
         uint32_t S[3] = {hdr.y, hdr.z, hdr.w};
@@ -149,20 +163,34 @@ struct Decode<NNQ_Q4_K_GGML> {
         }
         float s = __fmul_rn(d, u2f(sc));
         float m = __fmul_rn(dmin, u2f(mn));
-        const uint4 *qp = reinterpret_cast<const uint4 *>(b + 16 + 32 * (j >> 1));
-        int sh = 4 * (j & 1);
+        // Two weights (two bytes, the same nibble of each) per step on the packed f32 pipe, every lane
+        // rounded as the scalar operation would be. The nibbles stay where they are: the mantissa of
+        // 2^23 then holds 2^p q, and s / 2^p (exact) takes the place of s; x - m is x + (-m).
+        const int sh = 4 * (j & 1);
+        const uint32_t mask_lo = 0x0Fu << sh, mask_hi = 0x0F00u << sh;
+        const float f_lo = sh ? 0.0625f : 1.0f;
+        const float2 unbias = make_float2(-8388608.0f, -8388608.0f);
+        const float2 s2 = make_float2(__fmul_rn(s, f_lo), __fmul_rn(s, f_lo * 0.00390625f));
+        const float2 nm2 = make_float2(-m, -m);
+        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            uint4 q = __ldg(qp + h);
-            uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+        for (int v = 0; v < 8; v++) {
 #pragma unroll
-            for (int v = 0; v < 4; v++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    uint32_t nib = (qw[v] >> (8 * i + sh)) & 15u;
-                    o[16 * h + 4 * v + i] = __fsub_rn(__fmul_rn(s, u2f(nib)), m);
-                }
+            for (int i = 0; i < 2; i++) {
+                const uint32_t t = qw[v] >> (16 * i);
+                float2 c = make_float2(__uint_as_float((t & mask_lo) | 0x4B000000u), __uint_as_float((t & mask_hi) | 0x4B000000u));
+                c = __fadd2_rn(__fmul2_rn(__fadd2_rn(c, unbias), s2), nm2);
+                o[4 * v + 2 * i] = c.x;
+                o[4 * v + 2 * i + 1] = c.y;
+            }
         }
+    }
+    static __device__ __forceinline__ void chunk(const uint8_t *w, const uint8_t *, int64_t c, float *o) {
+        const uint8_t *b = w + (c >> 3) * 144;
+        int j = (int)(c & 7);  // sub-block: group g = j/2, low nibbles when j even
+        uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(b));
+        const uint4 *qp = reinterpret_cast<const uint4 *>(b + 16 + 32 * (j >> 1));
+        chunk_regs(hdr, __ldg(qp), __ldg(qp + 1), j, o);
     }
 };
 

@@ -39,25 +39,33 @@ constexpr int kTcBK = 64;                    // k per stage: one 128-byte swizzl
 constexpr int kTcTileBytes = 128 * 128;      // 128 rows x 128 bytes
 constexpr int kTcEpiBytes = kTcMmaWarp * 32 * 33 * 4;   // epilogue staging: a 32 x 32 f32 block (+ pad) per warp
 
-// Raw ring (Q4_K): the 144-byte super-blocks of the CTA's 128 weight rows arrive by TMA (the raw tensor
-// seen as rows of 32-bit words), one or two super-blocks of every row per chunk, one copy per chunk and
-// two chunks in flight. Per-thread register loads of the 32 bytes a k step needs kept less than a
-// megabyte in flight on the whole device, and the memory system's latency, not the decode, set the pace
-// (0.47 TB/s of reads in the profile of a 128-row product); a bulk copy per row (128 per chunk) was
-// bound by the rate at which the copy unit takes small copies.
-template <int FMT>
-struct TcRaw { static constexpr bool kRing = FMT == NNQ_Q4_K; };
-template <int MT>
+// Raw ring (Q4_K in both element orders, Q8_0): the raw blocks of the CTA's 128 weight rows arrive by TMA
+// (the raw tensor seen as rows of 32-bit words): per box, of every row, one or two 144-byte Q4_K
+// super-blocks or eight 34-byte Q8_0 blocks (256 weights = 4 k steps each), one copy per box and two boxes
+// in flight. Per-thread register loads of the 32 bytes a k step needs kept less than a megabyte in flight
+// on the whole device, and the memory system's latency, not the decode, set the pace (0.47 TB/s of reads in
+// the profile of a 128-row product); a bulk copy per row (128 per box) was bound by the rate at which the
+// copy unit takes small copies. Q8_0 rows are whole 32-bit words (and boxes start on 16 bytes) only when
+// K is a multiple of 256: other K, and the 512-row tile (no room for the ring), load from global memory.
+template <int FMT, int MT>
 struct TcRawGeom {
-    static constexpr int kSB = MT == 4 ? 1 : 2;                     // super-blocks of a row per chunk
-    static constexpr int kKb = 4 * kSB;                             // k steps per chunk
-    static constexpr int kPitch = 144 * kSB;                        // the box is stored densely
-    static constexpr int kBytes = 128 * kPitch;                     // one chunk (a multiple of 1024)
+    static constexpr bool kQ8 = FMT == NNQ_Q8_0;
+    static constexpr bool kRing = FMT == NNQ_Q4_K || FMT == NNQ_Q4_K_GGML || (kQ8 && MT <= 2);
+    static constexpr int kUnitBytes = kQ8 ? 272 : 144;              // bytes of a row per 256 weights
+    static constexpr int kSB = (kQ8 || MT == 4) ? 1 : 2;            // units of a row per box
+    static constexpr int kKb = 4 * kSB;                             // k steps per box
+    static constexpr int kPitch = kUnitBytes * kSB;                 // the box is stored densely
+    static constexpr int kBytes = 128 * kPitch;                     // one box (a multiple of 1024)
 };
+// does a product of this format and K take the ring (given a tile size that has one)?
+static inline bool tc_raw_ring(int fmt, int64_t k) {
+    return fmt == NNQ_Q4_K || fmt == NNQ_Q4_K_GGML || (fmt == NNQ_Q8_0 && k % 256 == 0);
+}
+static inline int tc_raw_unit_bytes(int fmt) { return fmt == NNQ_Q8_0 ? 272 : 144; }
 template <int FMT, int MT>
-__host__ __device__ constexpr int tc_ring_bytes() { return TcRaw<FMT>::kRing ? 2 * TcRawGeom<MT>::kBytes : 0; }
+__host__ __device__ constexpr int tc_ring_bytes() { return TcRawGeom<FMT, MT>::kRing ? 2 * TcRawGeom<FMT, MT>::kBytes : 0; }
 template <int FMT, int MT>
-constexpr int tc_max_stages() { return TcRaw<FMT>::kRing ? (MT == 4 ? 2 : (MT == 2 ? 3 : 4)) : (MT == 4 ? 2 : (MT == 2 ? 4 : 6)); }
+constexpr int tc_max_stages() { return TcRawGeom<FMT, MT>::kRing ? (MT == 4 ? 2 : (MT == 2 ? 3 : 4)) : (MT == 4 ? 2 : (MT == 2 ? 4 : 6)); }
 template <int FMT, int MT>
 static int tc_smem_bytes(int stages) {
     const int tiles = stages * (MT + 1) * kTcTileBytes;
@@ -130,12 +138,12 @@ template <int FMT, int MT, typename XT, bool TMAX>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const uint8_t *__restrict__ w, const uint8_t *__restrict__ wscales,
                const XT *__restrict__ x, const float *__restrict__ bias, void *__restrict__ y, int64_t M, int64_t N,
-               int64_t K, int y_dt, int stages, float *__restrict__ partials, int *status, const TcGroup grp) {
+               int64_t K, int y_dt, int stages, int use_ring, float *__restrict__ partials, int *status, const TcGroup grp) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment of the tiles (the dynamic window is not guaranteed to start on one)
     uint8_t *smem_al = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr bool kRawRing = TcRaw<FMT>::kRing;
-    using RG = TcRawGeom<MT>;
+    using RG = TcRawGeom<FMT, MT>;
+    const bool kRawRing = RG::kRing && use_ring;   // (compile-time false for formats without a ring)
     uint8_t *rawring = smem_al;                                  // two raw chunks (ring formats only)
     uint8_t *smem = smem_al + tc_ring_bytes<FMT, MT>();          // the tile stages; reused by the epilogue
     constexpr int kStageBytes = (MT + 1) * kTcTileBytes;   // MT activation tiles, then the weight tile
@@ -239,12 +247,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 // boundaries, so sub-block and super-block positions follow from kl alone)
                 const int kl = kb - kb_lo, lc = kl / RG::kKb, inch = kl % RG::kKb;
                 if (inch == pgroup) ok = mbar_wait_fast(rawfull_s + 8 * (lc & 1), (uint32_t)(lc >> 1) & 1u);   // this group's first step in the chunk
-                const uint8_t *rb = rawring + (lc & 1) * RG::kBytes + brow * RG::kPitch + (inch >> 2) * 144;
+                const uint8_t *rb = rawring + (lc & 1) * RG::kBytes + brow * RG::kPitch + (inch >> 2) * RG::kUnitBytes;
                 const int j = (inch & 3) * 2 + bhalf;
-                const uint4 hdr = *reinterpret_cast<const uint4 *>(rb);
-                const uint4 qq = *reinterpret_cast<const uint4 *>(rb + 16 + 16 * j);
                 if (ok && n0 + brow < N) {
-                    Decode<NNQ_Q4_K>::chunk_regs(hdr, qq, j, wv);
+                    if (FMT == NNQ_Q4_K) {
+                        Decode<NNQ_Q4_K>::chunk_regs(*reinterpret_cast<const uint4 *>(rb), *reinterpret_cast<const uint4 *>(rb + 16 + 16 * j), j, wv);
+                    } else if (FMT == NNQ_Q4_K_GGML) {
+                        const uint4 *qp = reinterpret_cast<const uint4 *>(rb + 16 + 32 * (j >> 1));
+                        Decode<NNQ_Q4_K_GGML>::chunk_regs(*reinterpret_cast<const uint4 *>(rb), qp[0], qp[1], j, wv);
+                    } else {
+                        Decode<NNQ_Q8_0>::chunk_halfwords(reinterpret_cast<const uint16_t *>(rb + 34 * j), wv);   // block j of the 8
+                    }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i++) wv[i] = 0.0f;
@@ -381,7 +394,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             }
         }
         if (ok) umma_commit(acc_s);            // accumulators complete
-    } else if (kRawRing && warp == kTcLoadWarp) {
+    } else if (RG::kRing && kRawRing && warp == kTcLoadWarp) {
         // ---------------- raw block loader ----------------
         const int nch = (nkb + RG::kKb - 1) / RG::kKb;
         const uint32_t ring_s = smem_u32(rawring);
@@ -389,11 +402,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             const int buf = lc & 1;
             if (lc >= 2) ok = mbar_wait_fast(rawempty_s + 8 * buf, ((uint32_t)(lc >> 1) & 1u) ^ 1u);
             if (!ok) break;
-            // a box of 128 rows x kSB super-blocks (36 words each); what lies beyond the row's end or the
+            // a box of 128 rows x kSB units of 256 weights; what lies beyond the row's end or the
             // tensor's last row arrives as zeros and counts like the rest
             if (lane == 0) {
                 mbar_expect_tx(rawfull_s + 8 * buf, RG::kBytes);
-                tma_load_2d(ring_s + buf * RG::kBytes, &wmap, (kb_lo / 4 + lc * RG::kSB) * 36, wrow0, rawfull_s + 8 * buf);
+                tma_load_2d(ring_s + buf * RG::kBytes, &wmap, (kb_lo / 4 + lc * RG::kSB) * (RG::kUnitBytes / 4), wrow0, rawfull_s + 8 * buf);
             }
             raw_issued = lc + 1;
         }
@@ -403,7 +416,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         if (lane == 0) atomicExch(status, 1);
     }
     __syncthreads();
-    if (kRawRing && warp == kTcLoadWarp && abort_s) {
+    if (RG::kRing && kRawRing && warp == kTcLoadWarp && abort_s) {
         // an aborted CTA may leave before its raw chunks were consumed: wait (bounded) for the copies
         for (int lc = raw_issued > 2 ? raw_issued - 2 : 0; lc < raw_issued; lc++) mbar_wait(rawfull_s + 8 * (lc & 1), (uint32_t)(lc >> 1) & 1u);
     }
@@ -438,7 +451,7 @@ gemm_tc_reduce_kernel(const float *__restrict__ partials, int slices, const floa
 bool gemm_tc_supported(const nnq_weight *w, int64_t m) {
     // (the raw ring's bulk copies read 16-byte aligned super-blocks)
     return w && w->d_raw && m >= 1 && w->k >= kTcBK && w->k % kTcBK == 0 && w->n >= 1 &&
-           !(TcRaw<NNQ_Q4_K>::kRing && w->fmt == NNQ_Q4_K && ((uintptr_t)w->d_raw & 15u));
+           !(tc_raw_ring(w->fmt, w->k) && ((uintptr_t)w->d_raw & 15u));
 }
 
 // Tensor map of the bf16 activations [M, K]: boxes of 64 x 128 elements, 128-byte swizzle, zero fill
@@ -471,21 +484,21 @@ static bool make_x_map(const TcArgs &a, CUtensorMap *map) {
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Tensor map of raw Q4_K blocks as 32-bit words: [rows, K / 256 * 36], boxes of 128 rows x sb super-blocks.
-static bool make_w_map(const void *w, int64_t rows, int64_t k, int sb, CUtensorMap *map) {
+// Tensor map of raw blocks as 32-bit words: [rows, K / 256 * unit_bytes / 4], boxes of 128 rows x sb units.
+static bool make_w_map(const void *w, int64_t rows, int64_t k, int unit_bytes, int sb, CUtensorMap *map) {
     EncodeFn fn = encode_fn();
-    const cuuint64_t row_bytes = (cuuint64_t)(k / 256) * 144;
+    const cuuint64_t row_bytes = (cuuint64_t)(k / 256) * (cuuint64_t)unit_bytes;
     if (!fn || ((uintptr_t)w & 15u) || rows < 1 || rows >= (1ll << 31)) return false;
     const cuuint64_t dims[2] = {row_bytes / 4, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {row_bytes};
-    const cuuint32_t box[2] = {36u * (cuuint32_t)sb, 128u};
+    const cuuint32_t box[2] = {(cuuint32_t)(unit_bytes / 4 * sb), 128u};
     const cuuint32_t estr[2] = {1u, 1u};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int FMT, int MT, typename XT, bool TMAX>
-static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, const CUtensorMap &wmap, int *status, int ksplit, float *partials, int stages,
+static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, const CUtensorMap &wmap, bool ring, int *status, int ksplit, float *partials, int stages,
                               int smem_bytes, cudaStream_t stream, const TcGroup &grp = TcGroup{nullptr, 0, 0, 0}, int grid_y = 0) {
     static bool configured[64] = {};
     int dev = 0;
@@ -511,7 +524,7 @@ static cudaError_t launch_cfg(const TcArgs &a, const CUtensorMap &map, const CUt
     cfg.attrs = attr;
     cfg.numAttrs = grp.offsets ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<FMT, MT, XT, TMAX>, map, wmap, a.w, a.scales, reinterpret_cast<const XT *>(a.x),
-                              a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages, ksplit > 1 ? partials : (float *)nullptr, status, grp);
+                              a.bias, a.y, a.m, a.n, a.k, a.y_dt, stages, ring ? 1 : 0, ksplit > 1 ? partials : (float *)nullptr, status, grp);
 }
 
 template <int FMT, int MT, typename XT>
@@ -524,12 +537,14 @@ static cudaError_t launch_one(const TcArgs &a, int *status, int ksplit, float *p
     CUtensorMap map, wmap;
     memset(&map, 0, sizeof(map));
     memset(&wmap, 0, sizeof(wmap));
-    if (TcRaw<FMT>::kRing && !make_w_map(a.w, a.n, a.k, TcRawGeom<MT>::kSB, &wmap)) return cudaErrorNotSupported;
+    using RG = TcRawGeom<FMT, MT>;
+    const bool ring = RG::kRing && tc_raw_ring(FMT, a.k);
+    if (ring && !make_w_map(a.w, a.n, a.k, RG::kUnitBytes, RG::kSB, &wmap)) return cudaErrorNotSupported;
     cudaError_t e;
     if (sizeof(XT) == 2 && make_x_map(a, &map))
-        e = launch_cfg<FMT, MT, XT, sizeof(XT) == 2>(a, map, wmap, status, ksplit, partials, stages, smem_bytes, stream);
+        e = launch_cfg<FMT, MT, XT, sizeof(XT) == 2>(a, map, wmap, ring, status, ksplit, partials, stages, smem_bytes, stream);
     else
-        e = launch_cfg<FMT, MT, XT, false>(a, map, wmap, status, ksplit, partials, stages, smem_bytes, stream);
+        e = launch_cfg<FMT, MT, XT, false>(a, map, wmap, ring, status, ksplit, partials, stages, smem_bytes, stream);
     if (e != cudaSuccess || ksplit == 1) return e;
     const int64_t total = a.m * a.n;
     cudaLaunchConfig_t cfg = {};
@@ -574,14 +589,16 @@ static cudaError_t launch_grouped_mt(const TcGroupArgs &g, int *status, cudaStre
     memset(&wmap, 0, sizeof(wmap));
     if (!make_x_map(a, &map)) return cudaErrorNotSupported;
     // the experts' raw tensors are one contiguous [experts, N, K] tensor (checked by the caller)
-    if (TcRaw<FMT>::kRing && !make_w_map(g.w, (int64_t)g.experts * g.n, g.k, TcRawGeom<MT>::kSB, &wmap)) return cudaErrorNotSupported;
+    using RG = TcRawGeom<FMT, MT>;
+    const bool ring = RG::kRing && tc_raw_ring(FMT, g.k);
+    if (ring && !make_w_map(g.w, (int64_t)g.experts * g.n, g.k, RG::kUnitBytes, RG::kSB, &wmap)) return cudaErrorNotSupported;
     int stages = tc_max_stages<FMT, MT>();
     const int nkb = (int)(g.k / kTcBK);
     if (stages > nkb) stages = nkb;
     const TcGroup grp = {g.offsets, g.experts, g.w_stride, g.s_stride};
     // every expert may end with a partly filled row tile
     const int grid_y = (int)(g.rows_upper / (128 * MT)) + g.experts;
-    return launch_cfg<FMT, MT, __nv_bfloat16, true>(a, map, wmap, status, 1, nullptr, stages, tc_smem_bytes<FMT, MT>(stages), stream, grp, grid_y);
+    return launch_cfg<FMT, MT, __nv_bfloat16, true>(a, map, wmap, ring, status, 1, nullptr, stages, tc_smem_bytes<FMT, MT>(stages), stream, grp, grid_y);
 }
 
 template <int FMT>
@@ -593,7 +610,7 @@ static cudaError_t launch_grouped_fmt(const TcGroupArgs &g, int *status, cudaStr
 }
 
 nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStream_t stream) {
-    if (g.k < kTcBK || g.k % kTcBK || g.experts < 1 || g.rows_upper < 1 || (g.fmt == NNQ_Q4_K && (((uintptr_t)g.w & 15u) || g.w_stride != (size_t)g.n * (size_t)(g.k / 256) * 144)))
+    if (g.k < kTcBK || g.k % kTcBK || g.experts < 1 || g.rows_upper < 1 || (tc_raw_ring(g.fmt, g.k) && (((uintptr_t)g.w & 15u) || g.w_stride != (size_t)g.n * (size_t)(g.k / 256) * (size_t)tc_raw_unit_bytes(g.fmt))))
         return fail(ctx, NNQ_ERR_UNSUPPORTED, "grouped tensor product: unsupported shape");
     cudaError_t e;
     switch (g.fmt) {
@@ -627,8 +644,9 @@ nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
             ksplit = (int)(target / ctas);
             if (ksplit > 8) ksplit = 8;
             if (ksplit > nkb / 4) ksplit = (int)(nkb / 4);
-            // formats on the raw ring slice K in whole chunks of 8 k steps
-            if (TcRaw<NNQ_Q4_K>::kRing && a.fmt == NNQ_Q4_K && ksplit > (nkb + 7) / 8) ksplit = (int)((nkb + 7) / 8);
+            // formats on the raw ring slice K in whole boxes
+            const int64_t box_kb = a.fmt == NNQ_Q8_0 ? 4 : 8;   // (K splits only with the 128-row tile)
+            if (tc_raw_ring(a.fmt, a.k) && ksplit > (nkb + box_kb - 1) / box_kb) ksplit = (int)((nkb + box_kb - 1) / box_kb);
             if (ksplit < 1) ksplit = 1;
         }
         // the scratch is sized once, at context creation, for the largest split this rule can ask

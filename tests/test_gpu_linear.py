@@ -506,6 +506,13 @@ def test_fused_decode_tensor_path_multiplies_the_rounded_decoded_weights(fmt, n,
     t.release()
 
 
+@pytest.mark.parametrize("fmt", [Q.Q8_0, Q.Q4_0])
+def test_fused_decode_tensor_path_k_not_a_multiple_of_256(fmt):
+    """K = 320: Q8_0 rows are then not whole 16-byte units and the product loads its blocks from global
+    memory instead of the shared-memory ring; same exactness."""
+    test_fused_decode_tensor_path_multiplies_the_rounded_decoded_weights(fmt, 200, 320)
+
+
 @pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q6_K, Q.Q8_0, Q.MXFP4_SPLIT, Q.MXFP4_CORE, Q.MXFP4_GPTOSS, Q.BF16_DENSE])
 def test_decode_once_path_multiplies_the_rounded_decoded_weights(fmt):
     """With the identity (and rows of zeros below it: 384 rows, so that the decode-once path runs for
