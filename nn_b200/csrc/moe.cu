@@ -622,12 +622,17 @@ static nnq_status launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, con
         Geometry g = geometry(m->fmt);
         const size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
         TcGroupArgs a = {d, sc, eb, es, first ? (const void *)s.xg : (const void *)s.hb, b, out, s.offset, E, rows, N, K, m->fmt};
-        // all local experts decoded to bf16 once, then the plain grouped GEMM. Measured against the product
-        // with the decode fused in (32 experts of about 2880 x 2880, top-4): MXFP4 and Q8_0 experts are ahead
-        // decoded once at every size that reaches this mode, Q4_K experts from about 100 rows per expert
-        // (64 rows: 0.84 ms fused, 0.88 ms decoded once; 128 rows: 1.24 against 0.96); Q6_K follows Q4_K
-        const bool k_quant = m->fmt == NNQ_Q4_K || m->fmt == NNQ_Q4_K_GGML || m->fmt == NNQ_Q6_K;
-        int64_t dense_rows = k_quant ? 96 : 32;
+        // all local experts decoded to bf16 once, then the plain grouped GEMM -- or the grouped product with
+        // the decode fused in. Measured (32 experts of about 3000 x 3000, top-4; ms per block fused / decoded
+        // once at 64, 128 and 256 rows per expert): MXFP4 1.24 / 0.87 at 64 rows, decoded once at every size
+        // (its decode to bf16 is integer work at copy speed); Q4_K, whose fused decode streams the raw blocks
+        // through the TMA ring, 0.71 / 0.88, 0.99 / 0.97, 1.23 / 1.24; Q8_0 (ring when K is a multiple of 256)
+        // 0.77 / 1.12, 1.03 / 1.21, 1.30 / 1.46, but its 512-row tile has no ring; Q6_K (no ring) as measured
+        // before the ring existed, from about 100 rows per expert
+        int64_t dense_rows = 32;
+        if (m->fmt == NNQ_Q4_K || m->fmt == NNQ_Q4_K_GGML) dense_rows = 128;
+        else if (m->fmt == NNQ_Q6_K) dense_rows = 96;
+        else if (m->fmt == NNQ_Q8_0 && K % 256 == 0) dense_rows = 384;
 #ifdef NNQ_DIAG
         if (const char *e = getenv("NNQ_MOE_DENSE_ROWS")) dense_rows = atoi(e);
 #endif

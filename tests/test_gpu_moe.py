@@ -77,9 +77,10 @@ def test_moe_forward_matches_oracle(layout, fmt, T):
 def test_prefill_sized_batch_takes_the_tensor_core_path(fmt):
     """From 32 routed rows per expert on, [N, K] experts run the grouped tcgen05 products (bf16
     operands: the 1e-2 bar of the tensor path); ragged expert loads, rows not a multiple of 128."""
-    # 8 experts, top-4. 70 tokens: 35 routed rows per expert; 150: 75 (Q4_K experts still take the
-    # product with the decode fused in, the others are decoded to bf16 once and multiplied by the plain
-    # grouped GEMM); 333 and 1024: 166 and 512 rows per expert, decoded once for every format
+    # 8 experts, top-4. 70 tokens: 35 routed rows per expert; 150: 75 (Q4_K experts take the product
+    # with the decode fused in up to 127 rows per expert, the others are decoded to bf16 once and
+    # multiplied by the plain grouped GEMM); 333 and 1024: 166 and 512 rows per expert, decoded once
+    # for every format
     for T in (70, 150, 333, 1024):
         _prefill_case(fmt, T)
 
