@@ -142,8 +142,8 @@ nnq_status nnq_init(int device, nnq_ctx **out) {
     if (s == NNQ_OK) s = check_cuda(ctx, cudaStreamCreateWithFlags(&ctx->host_stream, cudaStreamNonBlocking), "stream");
     if (s == NNQ_OK) s = check_cuda(ctx, cudaEventCreateWithFlags(&ctx->host_event, cudaEventDisableTiming), "event");
     if (s == NNQ_OK) {
-        // split-K partial sums of the tensor path: at most 2 * SMs output tiles of 128 x 128 f32
-        ctx->partials_bytes = (size_t)2 * ctx->sm_count * 128 * 128 * sizeof(float);
+        // split-K partial sums of the tensor path: at most SMs output tiles of 512 x 128 f32
+        ctx->partials_bytes = (size_t)ctx->sm_count * 512 * 128 * sizeof(float);
         s = check_cuda(ctx, cudaMalloc(&ctx->d_partials, ctx->partials_bytes), "cudaMalloc split-K scratch");
         if (s != NNQ_OK) ctx->partials_bytes = 0;
     }

@@ -495,16 +495,14 @@ bool gemm_dense_shape_ok(const nnq_ctx *ctx, int64_t m, int64_t n, int64_t k, in
 }
 bool gemm_dense_supported(const nnq_ctx *ctx, const nnq_weight *w, int64_t m, int x_dt) {
     // Formats whose fused decode reads its raw blocks through the TMA ring keep it for longer. Measured on
-    // 4096 x 4096, 12288 x 4096 and 4096 x 12288: Q4_K (either element order) is ahead fused at 256 rows
-    // (252 against 300 us for the three) and level at 512 (354 against 361); Q8_0 is ahead at 256 rows
-    // (175 against 239 us) and behind at 512, where its 512-row tile has no room for the ring. Up to 512
-    // rows a Q4_K weight whose 128-row tiles fill at least half of the SMs stays fused as well
-    // (12288 x 4096 at 512 rows: 73 against 95 us; 4096-row weights, 32 tiles: 46 against 37).
+    // 4096 x 4096, 12288 x 4096 and 4096 x 12288 (us, fused / decoded once): Q4_K (either element order)
+    // 26 / 34, 53 / 68, 50 / 97 at 256 rows, 38 / 37, 75 / 95, 69 / 99 at 512 rows, 64 / 41, 142 / 122,
+    // 127 / 113 at 1024 rows; Q8_0 29 / 42, 58 / 84, 55 / 113 at 256 rows, 47 / 43, 113 / 111, 100 / 115 at
+    // 512 rows (its 512-row tile has no room for the ring).
     if (w) {
         const bool q4k = w->fmt == NNQ_Q4_K || w->fmt == NNQ_Q4_K_GGML;
         const bool q8 = w->fmt == NNQ_Q8_0 && w->k % 256 == 0;
-        if ((q4k || q8) && m < 384) return false;
-        if (q4k && m <= 512 && 2 * ((w->n + 127) / 128) >= ctx->sm_count) return false;
+        if ((q4k && m <= 512) || (q8 && m < 384)) return false;
     }
     return w && w->d_raw && gemm_dense_shape_ok(ctx, m, w->n, w->k, x_dt);
 }

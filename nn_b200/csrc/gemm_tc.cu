@@ -560,25 +560,11 @@ static cudaError_t launch_one(const TcArgs &a, int *status, int ksplit, float *p
 }
 
 template <int FMT>
-static cudaError_t launch_fmt(const TcArgs &a, int *status, int sm_count, int ksplit, float *partials, cudaStream_t stream) {
+static cudaError_t launch_fmt(const TcArgs &a, int *status, int mt, int ksplit, float *partials, cudaStream_t stream) {
     const bool f32 = a.x_dt == NNQ_F32;
-    // Rows per CTA: the more rows share a decoded weight tile the less decode work, but the grid
-    // must still cover the machine. Take the largest tile that leaves at least one CTA per two SMs.
-    // (Decoding the whole weight to bf16 first and multiplying afterwards was measured slower than
-    // decoding per tile even at M = 4096: the tile pipeline, not the decode, is the limit.)
-    const int64_t ntiles = (a.n + 127) / 128;
-    auto ctas = [&](int mt) { return ntiles * ((a.m + 128 * mt - 1) / (128 * mt)); };
-    int mt = 1;
-    // (measured with the activation tiles arriving by TMA: half a wave of the largest tile still beats
-    // a full wave of smaller ones, because every CTA decodes its weight tile for itself)
-    if (a.m > 256 && 2 * ctas(4) >= sm_count) mt = 4;
-    else if (a.m > 128 && 2 * ctas(2) >= sm_count) mt = 2;
-    static const char *env_mt = diag_env("NNQ_TC_MT");   // tuning aid
-    if (env_mt && (atoi(env_mt) == 1 || atoi(env_mt) == 2 || atoi(env_mt) == 4)) mt = atoi(env_mt);
-    if (mt != 1) ksplit = 1;
     if (mt == 1) return f32 ? launch_one<FMT, 1, float>(a, status, ksplit, partials, stream) : launch_one<FMT, 1, __nv_bfloat16>(a, status, ksplit, partials, stream);
-    if (mt == 2) return f32 ? launch_one<FMT, 2, float>(a, status, 1, nullptr, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, 1, nullptr, stream);
-    return f32 ? launch_one<FMT, 4, float>(a, status, 1, nullptr, stream) : launch_one<FMT, 4, __nv_bfloat16>(a, status, 1, nullptr, stream);
+    if (mt == 2) return f32 ? launch_one<FMT, 2, float>(a, status, ksplit, partials, stream) : launch_one<FMT, 2, __nv_bfloat16>(a, status, ksplit, partials, stream);
+    return f32 ? launch_one<FMT, 4, float>(a, status, ksplit, partials, stream) : launch_one<FMT, 4, __nv_bfloat16>(a, status, ksplit, partials, stream);
 }
 
 template <int FMT, int MT>
@@ -633,43 +619,51 @@ nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStream
 
 nnq_status launch_gemm_tc(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream) {
     cudaError_t e;
-    // Small grids (few rows, few output tiles) split K over CTAs so that every SM works; the f32
-    // partial sums go through a scratch buffer owned by the context and are added in slice order.
+    // Rows per CTA: as many 128-row accumulators (1, 2 or 4) as the activation rows fill, because every
+    // CTA decodes its weight tile for itself and the decode, not the MMA, is the expensive part. Where that
+    // leaves fewer tiles than half the SMs, K is split over CTAs instead of shrinking the tile (a smaller
+    // tile decodes every weight tile several times); the f32 partial sums go through a scratch buffer owned
+    // by the context and are added in slice order by a second kernel.
+    const int64_t ntiles = (a.n + 127) / 128;
+    int mt = a.m > 256 ? 4 : (a.m > 128 ? 2 : 1);
+    if (mt == 4 && a.fmt == NNQ_Q8_0 && tc_raw_ring(a.fmt, a.k)) mt = 2;   // the 512-row tile leaves no room for the Q8_0 ring
+    static const char *env_mt = diag_env("NNQ_TC_MT");   // tuning aid
+    if (env_mt && (atoi(env_mt) == 1 || atoi(env_mt) == 2 || atoi(env_mt) == 4)) mt = atoi(env_mt);
     int ksplit = 1;
     {
-        const int64_t ctas = ((a.n + 127) / 128) * ((a.m + 127) / 128);
+        const int64_t ctas = ntiles * ((a.m + 128 * mt - 1) / (128 * mt));
         const int64_t nkb = a.k / kTcBK;
         const int64_t target = ctx->sm_count;   // one CTA per SM
-        if (a.m <= 256 && ctas * 2 <= target) {
+        if (ctas * 2 <= target) {
             ksplit = (int)(target / ctas);
             if (ksplit > 8) ksplit = 8;
             if (ksplit > nkb / 4) ksplit = (int)(nkb / 4);
             // formats on the raw ring slice K in whole boxes
-            const int64_t box_kb = a.fmt == NNQ_Q8_0 ? 4 : 8;   // (K splits only with the 128-row tile)
+            const int64_t box_kb = (a.fmt == NNQ_Q8_0 || mt == 4) ? 4 : 8;
             if (tc_raw_ring(a.fmt, a.k) && ksplit > (nkb + box_kb - 1) / box_kb) ksplit = (int)((nkb + box_kb - 1) / box_kb);
             if (ksplit < 1) ksplit = 1;
         }
         // the scratch is sized once, at context creation, for the largest split this rule can ask
-        // for (ksplit * ctas <= 2 * SMs tiles of 128 x 128 f32): nothing is allocated here
+        // for (ksplit * ctas <= SMs tiles of 512 x 128 f32): nothing is allocated here
         while (ksplit > 1 && (size_t)ksplit * a.m * a.n * sizeof(float) > ctx->partials_bytes) ksplit--;
     }
     switch (a.fmt) {
-        case NNQ_Q4_0: e = launch_fmt<NNQ_Q4_0>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q4_1: e = launch_fmt<NNQ_Q4_1>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q8_0: e = launch_fmt<NNQ_Q8_0>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q4_K: e = launch_fmt<NNQ_Q4_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q4_K_GGML: e = launch_fmt<NNQ_Q4_K_GGML>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q6_K: e = launch_fmt<NNQ_Q6_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q5_0: e = launch_fmt<NNQ_Q5_0>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q5_1: e = launch_fmt<NNQ_Q5_1>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q2_K: e = launch_fmt<NNQ_Q2_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q3_K: e = launch_fmt<NNQ_Q3_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_Q5_K: e = launch_fmt<NNQ_Q5_K>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_F32_DENSE: e = launch_fmt<NNQ_F32_DENSE>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
-        case NNQ_BF16_DENSE: e = launch_fmt<NNQ_BF16_DENSE>(a, ctx->d_status, ctx->sm_count, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q4_0: e = launch_fmt<NNQ_Q4_0>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q4_1: e = launch_fmt<NNQ_Q4_1>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q8_0: e = launch_fmt<NNQ_Q8_0>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q4_K: e = launch_fmt<NNQ_Q4_K>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q4_K_GGML: e = launch_fmt<NNQ_Q4_K_GGML>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q6_K: e = launch_fmt<NNQ_Q6_K>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_MXFP4_CORE: e = launch_fmt<NNQ_MXFP4_CORE>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_MXFP4_SPLIT: e = launch_fmt<NNQ_MXFP4_SPLIT>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_MXFP4_GPTOSS: e = launch_fmt<NNQ_MXFP4_GPTOSS>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q5_0: e = launch_fmt<NNQ_Q5_0>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q5_1: e = launch_fmt<NNQ_Q5_1>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q2_K: e = launch_fmt<NNQ_Q2_K>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q3_K: e = launch_fmt<NNQ_Q3_K>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_Q5_K: e = launch_fmt<NNQ_Q5_K>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_F32_DENSE: e = launch_fmt<NNQ_F32_DENSE>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
+        case NNQ_BF16_DENSE: e = launch_fmt<NNQ_BF16_DENSE>(a, ctx->d_status, mt, ksplit, ctx->d_partials, stream); break;
         default: return fail(ctx, NNQ_ERR_INVALID_ARG, "unknown format %d", a.fmt);
     }
     ctx->launches += ksplit > 1 ? 2 : 1;
