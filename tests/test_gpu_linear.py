@@ -443,8 +443,10 @@ def test_qwen3_32b_shapes_prefill_and_decode(fmt, n, k):
 @pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q8_0, Q.Q6_K, Q.MXFP4_SPLIT, Q.Q5_K, Q.F32_DENSE, Q.BF16_DENSE])
 @pytest.mark.parametrize("m,n,k", [(256, 200, 512), (300, 520, 1024), (1000, 72, 2304)])
 def test_large_batch_takes_the_decode_once_path(fmt, m, n, k):
-    """From 256 rows of bf16 activations on, the weight is decoded to bf16 once and a plain
-    TMA + tcgen05 product follows: ragged M and N tiles, K a multiple of 64, bias, both outputs."""
+    """From 256 rows of bf16 activations on (Q8_0: 384, Q4_K: 513 -- their fused decode is the faster
+    one below that, so the smaller cases here run it with two accumulators per CTA and K split over
+    CTAs), the weight is decoded to bf16 once and a plain TMA + tcgen05 product follows: ragged M and
+    N tiles, K a multiple of 64, bias, both outputs."""
     _run(fmt, n, k, m, x_bf16=True, y_bf16=(m == 300), with_bias=(m != 256), seed=900 + m)
 
 
@@ -515,7 +517,7 @@ def test_fused_decode_tensor_path_k_not_a_multiple_of_256(fmt):
 
 @pytest.mark.parametrize("fmt", [Q.Q4_K, Q.Q6_K, Q.Q8_0, Q.MXFP4_SPLIT, Q.MXFP4_CORE, Q.MXFP4_GPTOSS, Q.BF16_DENSE])
 def test_decode_once_path_multiplies_the_rounded_decoded_weights(fmt):
-    """With the identity (and rows of zeros below it: 384 rows, so that the decode-once path runs for
+    """With the identity (and rows of zeros below it: 640 rows, so that the decode-once path runs for
     every format) as activations the product returns the bf16 weights the GEMM was fed: they must be
     the oracle's decoded weights rounded to bf16, bit for bit -- including MXFP4 blocks with extreme
     scale exponents, which the direct-to-bf16 decode hands to the f32 decoder (exponent 0) or that sit
@@ -529,7 +531,7 @@ def test_decode_once_path_multiplies_the_rounded_decoded_weights(fmt):
         w = np.array(w, copy=True)
         w.reshape(-1, 17)[:6, 0] = [0, 1, 3, 250, 251, 252]
     t = api.from_quantized(w, fmt, [n, k], sc)
-    x = torch.zeros(384, k, device=DEV, dtype=torch.bfloat16)
+    x = torch.zeros(640, k, device=DEV, dtype=torch.bfloat16)
     x[:k] = torch.eye(k, device=DEV, dtype=torch.bfloat16)
     y = api.quantized_linear(x, t, None, out_dtype=torch.float32)     # rows [0, k) = W^T
     torch.cuda.synchronize()
