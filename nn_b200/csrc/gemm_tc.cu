@@ -31,13 +31,14 @@
 namespace nnq {
 
 constexpr int kTcProducerWarps = 8;          // warps that decode one weight tile
-constexpr int kTcGroups = 2;                 // producer groups; group g fills the k steps g, g + kTcGroups, ...
+constexpr int kTcGroups = 3;                 // producer groups (at most); group g of G fills the k steps g, g + G, ...
 constexpr int kTcMmaWarp = kTcProducerWarps * kTcGroups;
 constexpr int kTcLoadWarp = kTcMmaWarp + 1;  // streams the raw blocks of formats that take the raw ring
 constexpr int kTcThreads = (kTcLoadWarp + 1) * 32;
 constexpr int kTcBK = 64;                    // k per stage: one 128-byte swizzle row of bf16
 constexpr int kTcTileBytes = 128 * 128;      // 128 rows x 128 bytes
-constexpr int kTcEpiBytes = kTcMmaWarp * 32 * 33 * 4;   // epilogue staging: a 32 x 32 f32 block (+ pad) per warp
+constexpr int kTcEpiWarps = 16;                 // warps that carry the accumulators out (four per TMEM lane quarter)
+constexpr int kTcEpiBytes = kTcEpiWarps * 32 * 33 * 4;   // epilogue staging: a 32 x 32 f32 block (+ pad) per warp
 
 // Raw ring (Q4_K in both element orders, Q8_0): the raw blocks of the CTA's 128 weight rows arrive by TMA
 // (the raw tensor seen as rows of 32-bit words): per box, of every row, one or two 144-byte Q4_K
@@ -210,7 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
         mbar_init(acc_s, 1);
         for (int b = 0; b < 2; b++) {
             mbar_init(rawfull_s + 8 * b, 1);
-            mbar_init(rawempty_s + 8 * b, kTcMmaWarp);
+            mbar_init(rawempty_s + 8 * b, kTcProducerWarps * (stages >= kTcGroups ? kTcGroups : 2));
         }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,10 +225,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
     bool ok = true;
+    // Producer groups in use: never more than stages. A group waits for "the stage was freed u times" by
+    // parity, which is only right while it cannot be two uses ahead of the tensor core; its own previous
+    // k step (G steps back) was filled after the step G + stages back had been consumed, so G <= stages
+    // keeps it within one use. (The 512-row tile has room for two stages: two groups, eight idle warps.)
+    const int ngroups = stages >= kTcGroups ? kTcGroups : 2;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     int raw_issued = 0;   // loader warp: raw chunks whose copies were started
 
-    if (warp < kTcMmaWarp) {
+    if (warp < kTcProducerWarps * ngroups) {
         // ---------------- producers ----------------
         const int64_t cpr = K / 32;                 // 32-weight chunks per weight row
         const int pgroup = warp / kTcProducerWarps;             // this warp's producer group
@@ -246,7 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
                 // k step kb of the whole product = step kl of this CTA's slice (slices start on chunk
                 // boundaries, so sub-block and super-block positions follow from kl alone)
                 const int kl = kb - kb_lo, lc = kl / RG::kKb, inch = kl % RG::kKb;
-                if (inch == pgroup) ok = mbar_wait_fast(rawfull_s + 8 * (lc & 1), (uint32_t)(lc >> 1) & 1u);   // this group's first step in the chunk
+                if (inch < ngroups) ok = mbar_wait_fast(rawfull_s + 8 * (lc & 1), (uint32_t)(lc >> 1) & 1u);   // this group's first step in the chunk
                 const uint8_t *rb = rawring + (lc & 1) * RG::kBytes + brow * RG::kPitch + (inch >> 2) * RG::kUnitBytes;
                 const int j = (inch & 3) * 2 + bhalf;
                 if (ok && n0 + brow < N) {
@@ -262,7 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
 #pragma unroll
                     for (int i = 0; i < 32; i++) wv[i] = 0.0f;
                 }
-                if (inch + kTcGroups >= RG::kKb || kl + kTcGroups >= nkb) {   // this group's last step in the chunk
+                if (inch + ngroups >= RG::kKb || kl + ngroups >= nkb) {   // this group's last step in the chunk
                     __syncwarp();
                     if (lane == 0) mbar_arrive(rawempty_s + 8 * (lc & 1));
                 }
@@ -296,7 +302,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             return v;
         };
         if (pgroup < nkb) fetch(kb_lo + pgroup);
-        for (int kb = pgroup; kb < nkb && ok; kb += kTcGroups) {
+        for (int kb = pgroup; kb < nkb && ok; kb += ngroups) {
             const int slot = kb % stages;
             const uint32_t phase = (uint32_t)(kb / stages) & 1u;
             if (kb >= stages) ok = mbar_wait_fast(empty_s + 8 * slot, phase ^ 1u);
@@ -329,14 +335,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__
             fence_async_smem();      // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(full_s + 8 * slot);
-            if (kb + kTcGroups < nkb) fetch(kb_lo + kb + kTcGroups);
+            if (kb + ngroups < nkb) fetch(kb_lo + kb + ngroups);
         }
         // ---------------- epilogue ----------------
         if (ok) ok = mbar_wait_fast(acc_s, 0);
         asm volatile("griddepcontrol.wait;" ::: "memory");   // (returns at once: the activations were waited for) before any store
-        if (ok) {
+        if (ok && warp < kTcEpiWarps) {
             tc_fence_after();
-            constexpr int kColsPerWarp = 128 / (kTcMmaWarp / 4);
+            constexpr int kColsPerWarp = 128 / (kTcEpiWarps / 4);
             const int q = warp & 3, cpart = warp >> 2;   // TMEM lane quarter, column part
             // A lane reads one accumulator row; the block is turned through shared memory (the tile stages
             // are free by now) so that a warp stores 32 consecutive columns of one row per instruction.
