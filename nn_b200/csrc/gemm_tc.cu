@@ -7,14 +7,17 @@
 //     tensor map of x with 128-byte swizzle, issued by one thread, counted on the stage's "full"
 //     barrier; rows beyond M are zero-filled); f32 activations are converted by the producers;
 //   * 8 producer warps dequantize the 128 x 64 weight tile to bf16 (f32 decode, the bit-exact
-//     one, then round-to-nearest-even) into the same K-major 128-byte-swizzled layout; two such
-//     groups of warps take alternate k steps (with one group an SM held two warps per scheduler
-//     and the decode's dependent chains, not its instruction count, set the pace of a k step);
+//     one, then round-to-nearest-even) into the same K-major 128-byte-swizzled layout; up to
+//     three such groups of warps take k steps in turn (with one group an SM held two warps per
+//     scheduler and the decode's dependent chains, not its instruction count, set the pace of a
+//     k step); Q4_K and Q8_0 blocks reach them through a TMA ring in shared memory (below);
 //   * one thread issues 4 * MT tcgen05.mma (M 128, N 128, K 16, bf16 x bf16 -> f32) from shared
 //     memory descriptors into the accumulators and commits them onto the stage's "empty" barrier.
 // The larger MT, the more activation rows reuse each dequantized weight tile (the dequantization,
-// not the MMA, is the expensive part at small M). After the last k step the producer warps read
-// the accumulators back with tcgen05.ld, add the bias and store f32 / bf16.
+// not the MMA, is the expensive part at small M); where that leaves few tiles, K is split over
+// gridDim.z CTAs and a second kernel adds the partial sums in slice order. After the last k step
+// sixteen warps read the accumulators back with tcgen05.ld, turn them through shared memory, add
+// the bias and store coalesced rows of f32 / bf16.
 // Weights are rounded to bf16, so results carry the 1e-2 tolerance of the tensor path.
 // Every barrier wait is bounded; on a timeout the CTA records it, skips the rest and still frees
 // its tensor memory.
