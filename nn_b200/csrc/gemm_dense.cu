@@ -143,6 +143,46 @@ dequant_bf16_kernel(const uint8_t *__restrict__ src, const uint8_t *__restrict__
     }
 }
 
+// nn-gptoss expert tensors [E, K, N] (MXFP4, 32-weight blocks along N, the even column in the high
+// nibble) -> bf16 [E, N, K]: a CTA turns a 64 x 64 tile through shared memory. Reads are 16 bytes per
+// thread (one block), writes 128 contiguous bytes per output row. half_rows > 0 interleaves the output
+// rows of every expert (row j -> 2j, row half_rows + j -> 2j + 1), as the fused SwiGLU epilogue wants.
+constexpr int kKnTile = 64;
+__global__ void __launch_bounds__(128)
+dequant_kn_bf16_kernel(const uint8_t *__restrict__ data, const uint8_t *__restrict__ scales, __nv_bfloat16 *__restrict__ dst,
+                       int K, int N, int half_rows) {
+    __shared__ __align__(16) uint16_t tile[kKnTile][kKnTile + 8];   // [n][k]; 144-byte rows keep 16-byte reads aligned
+    const int e = blockIdx.z, k0 = blockIdx.y * kKnTile, n0 = blockIdx.x * kKnTile;
+    const int kk = threadIdx.x & 63, blk = threadIdx.x >> 6;          // this thread's k row and which 32 of the 64 columns
+    const size_t row = (size_t)e * K + k0 + kk;
+    const uint4 q = __ldg(reinterpret_cast<const uint4 *>(data + row * (size_t)(N / 2) + n0 / 2 + blk * 16));
+    const uint32_t ex = __ldg(scales + row * (size_t)(N / 32) + n0 / 32 + blk);
+    const bool direct = ex >= 1u && ex <= 251u;
+    const uint32_t base = (ex - 1u) << 7;
+    const float scale = mx_scale_gptoss(ex);
+    auto one = [&](uint32_t nib) -> uint16_t {
+        if (direct) return (uint16_t)mx_bf16_one(nib, base);
+        return __bfloat16_as_ushort(__float2bfloat16_rn(e2m1_value(nib, scale)));
+    };
+    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t byte = (qw[v] >> (8 * i)) & 0xFFu;
+            const int col = blk * 32 + v * 8 + i * 2;
+            tile[col][kk] = one(byte >> 4);
+            tile[col + 1][kk] = one(byte & 15u);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kKnTile * 8; i += 128) {
+        const int r = i >> 3, c = i & 7, n = n0 + r;
+        const int nn = half_rows > 0 ? (n < half_rows ? 2 * n : 2 * (n - half_rows) + 1) : n;
+        *reinterpret_cast<uint4 *>(dst + ((size_t)e * N + nn) * K + k0 + c * 8) = *reinterpret_cast<const uint4 *>(&tile[r][c * 8]);
+    }
+}
+
 template <int FMT>
 static cudaError_t launch_dequant_bf16(const uint8_t *src, const uint8_t *scales, int64_t nchunks, void *dst, int sm_count,
                                        cudaStream_t stream, int cpr = 1, int half_rows = 0) {
@@ -587,6 +627,7 @@ nnq_status launch_gemm_dense(nnq_ctx *ctx, const TcArgs &a, cudaStream_t stream)
 }
 
 bool gemm_dense_grouped_supported(const nnq_ctx *ctx, const TcGroupArgs &g) {
+    if (g.kn && (g.fmt != NNQ_MXFP4_GPTOSS || g.n % kKnTile || g.k % kKnTile || ((uintptr_t)g.w & 15u))) return false;
     return ctx->d_dense && g.k >= kDgBK && g.k % kDgBK == 0 && g.experts >= 1 && g.experts <= kDgMaxGroups && g.rows_upper >= 1 &&
            (size_t)g.experts * (size_t)g.n * (size_t)g.k * 2 <= ctx->dense_bytes && g.rows_upper < (1ll << 30) &&
            (int64_t)g.experts * g.n < (1ll << 31) && encode_fn() != nullptr;
@@ -606,6 +647,11 @@ nnq_status launch_gemm_dense_grouped(nnq_ctx *ctx, const TcGroupArgs &g, cudaStr
     // which the direct MXFP4 decode can write at no cost
     const bool fuse = gemm_dense_grouped_fuses_swiglu(g);
     const int cpr = (int)(g.k / 32), half = fuse ? (int)(g.n / 2) : 0;
+    if (g.kn) {
+        dequant_kn_bf16_kernel<<<dim3((unsigned)(g.n / kKnTile), (unsigned)(g.k / kKnTile), (unsigned)g.experts), 128, 0, stream>>>(
+            g.w, g.scales, static_cast<__nv_bfloat16 *>(ctx->d_dense), (int)g.k, (int)g.n, half);
+        e = cudaGetLastError();
+    } else
     switch (g.fmt) {
 #define NNQ_DB(F) case F: e = launch_dequant_bf16<F>(g.w, g.scales, nchunks, ctx->d_dense, ctx->sm_count, stream, cpr, half); break
         NNQ_DB(NNQ_Q4_0); NNQ_DB(NNQ_Q4_1); NNQ_DB(NNQ_Q8_0); NNQ_DB(NNQ_Q4_K); NNQ_DB(NNQ_Q4_K_GGML); NNQ_DB(NNQ_Q6_K);

@@ -37,6 +37,9 @@ struct TcGroupArgs {
     // (gemm_dense_grouped_fuses_swiglu tells)
     __nv_bfloat16 *h_out = nullptr;
     float swiglu_limit = 0.0f;
+    // decode-once path only: the experts are nn-gptoss [experts, K, N] MXFP4 tensors (codes [E, K, N / 2],
+    // scale bytes [E, K, N / 32], blocks along N); the decode transposes them into the [N, K] copy
+    bool kn = false;
 };
 bool gemm_dense_grouped_fuses_swiglu(const TcGroupArgs &g);
 nnq_status launch_gemm_tc_grouped(nnq_ctx *ctx, const TcGroupArgs &a, cudaStream_t stream);

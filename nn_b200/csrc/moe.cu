@@ -554,7 +554,13 @@ static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 static bool moe_tensor_mode(const nnq_moe *m, int64_t T, int k, bool routed) {
     static const char *env = diag_env("NNQ_MOE_TENSOR");   // tuning aid: 0 keeps the token-column kernel
     if (env && atoi(env) == 0) return false;
-    return m->layout == NNQ_MOE_NK && (m->fmt < NNQ_Q5_0 || m->fmt >= NNQ_F32_DENSE) && m->hidden % 64 == 0 && m->inter % 64 == 0 &&
+    // nn-gptoss [E, K, N] experts take the decode-once form only (a transposing decode into the context's
+    // bf16 scratch, sized when the block was created) and need the single-slice output buffers that come
+    // with their tiled copies
+    const bool nk = m->layout == NNQ_MOE_NK && (m->fmt < NNQ_Q5_0 || m->fmt >= NNQ_F32_DENSE);
+    const bool kn = m->layout == NNQ_MOE_KN_GPTOSS && m->d_gu_tiled != nullptr && m->ctx->d_dense != nullptr &&
+                    (size_t)m->e_local * 2 * (size_t)m->inter * (size_t)m->hidden * 2 <= m->ctx->dense_bytes;
+    return (nk || kn) && m->hidden % 64 == 0 && m->inter % 64 == 0 &&
            // 32 routed rows per expert on average: with the block's own router the T tokens spread over
            // all experts (the shards of one block agree), rows routed by the caller all go to local experts
            T * k >= (env ? atoi(env) : 32) * (int64_t)(routed ? m->e_local : m->n_experts);
@@ -622,6 +628,7 @@ static nnq_status launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, con
         Geometry g = geometry(m->fmt);
         const size_t eb = (size_t)N * (K / g.elems) * g.bytes, es = (size_t)N * (K / g.elems) * g.scale_bytes;
         TcGroupArgs a = {d, sc, eb, es, first ? (const void *)s.xg : (const void *)s.hb, b, out, s.offset, E, rows, N, K, m->fmt};
+        a.kn = m->layout == NNQ_MOE_KN_GPTOSS;
         // all local experts decoded to bf16 once, then the plain grouped GEMM -- or the grouped product with
         // the decode fused in. Measured (32 experts of about 3000 x 3000, top-4; ms per block fused / decoded
         // once at 64, 128 and 256 rows per expert): MXFP4 1.24 / 0.87 at 64 rows, decoded once at every size
@@ -636,7 +643,8 @@ static nnq_status launch_product(nnq_ctx *ctx, const nnq_moe *m, bool first, con
 #ifdef NNQ_DIAG
         if (const char *e = getenv("NNQ_MOE_DENSE_ROWS")) dense_rows = atoi(e);
 #endif
-        if (rows >= dense_rows * (int64_t)E && gemm_dense_grouped_supported(ctx, a)) {
+        if (a.kn && !gemm_dense_grouped_supported(ctx, a)) return fail(ctx, NNQ_ERR_UNSUPPORTED, "[E, K, N] experts: no bf16 scratch for the prefill-sized product");
+        if ((a.kn || rows >= dense_rows * (int64_t)E) && gemm_dense_grouped_supported(ctx, a)) {
             if (first && swiglu_done && s.slices == 1) {
                 // gate / up product: SwiGLU in the GEMM's epilogue where the decode can interleave the rows
                 a.h_out = s.hb;
@@ -901,7 +909,7 @@ nnq_status nnq_moe_create_shard(nnq_ctx *ctx, int n_experts, int expert_begin, i
         }
     }
     // bf16 scratch of the prefill-sized expert products: all local experts of the larger tensor
-    if (s == NNQ_OK && layout == NNQ_MOE_NK && (fmt < NNQ_Q5_0 || fmt >= NNQ_F32_DENSE)) {
+    if (s == NNQ_OK && ((layout == NNQ_MOE_NK && (fmt < NNQ_Q5_0 || fmt >= NNQ_F32_DENSE)) || (layout == NNQ_MOE_KN_GPTOSS && m->d_gu_tiled))) {
         s = dense_scratch_reserve(ctx, (int64_t)expert_count * 2 * inter, hidden);
         if (s == NNQ_OK) s = dense_scratch_reserve(ctx, (int64_t)expert_count * hidden, inter);
     }

@@ -85,11 +85,18 @@ def test_prefill_sized_batch_takes_the_tensor_core_path(fmt):
         _prefill_case(fmt, T)
 
 
-def _prefill_case(fmt, T):
+@pytest.mark.parametrize("T", [70, 333, 1024])
+def test_prefill_sized_batch_of_kn_gptoss_experts(T):
+    """nn-gptoss [E, K, N] experts at prefill size: a transposing decode into the bf16 scratch, then the
+    grouped GEMM with SwiGLU in the epilogue of the gate / up product (same numerics as [N, K] MXFP4)."""
+    _prefill_case(Q.MXFP4_GPTOSS, T, moe.LAYOUT_KN_GPTOSS)
+
+
+def _prefill_case(fmt, T, layout=moe.LAYOUT_NK):
     E, H, I, k = 8, 256, 256, 4
-    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(moe.LAYOUT_NK, fmt, E, H, I, 77)
+    rw, rb, gu, gus, bgu, dn, dns, bd, w_gu, w_d = _make(layout, fmt, E, H, I, 77)
     x = F.gen_activations(78, T, H, bf16=True)
-    blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, moe.LAYOUT_NK, fmt, gu, gus, bgu, dn, dns, bd)
+    blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, layout, fmt, gu, gus, bgu, dn, dns, bd)
     y = blk(torch.from_numpy(x).to(DEV)).cpu().numpy()
     blk.backend.device_status()
     y_ref, _, _ = orc.moe_forward(x, rw, rb, w_gu, bgu, w_d, bd, k, 7.0)
@@ -296,7 +303,7 @@ def test_gptoss_20b_geometry(layout, fmt, T):
     the 64-token decode batch, and a seeded sample of 24 tokens of the 4096-token prefill batch
     (a token's output depends on no other token, so the oracle runs on the sample alone).
     64 tokens stay on the f32-accumulating kernels (2e-3); 4096 tokens give 512 routed rows per
-    expert, which the [N, K] layout runs on the tensor cores with bf16 operands (1e-2)."""
+    expert, which both layouts run on the tensor cores with bf16 operands (1e-2)."""
     blk, rw, rb, bgu, bd, w_gu, w_d = _gptoss_block(layout, fmt)
     H, k = 2880, 4
     x = F.gen_activations(900 + T, T, H, bf16=True)
@@ -313,7 +320,7 @@ def test_gptoss_20b_geometry(layout, fmt, T):
     # small softmax weight by 1e-4 of itself, so the weights are compared to 2e-3 of themselves
     assert np.allclose(wt.cpu().numpy()[sample], wt_ref, rtol=2e-3, atol=1e-7)
     assert np.all(np.isfinite(got))
-    tol = 1e-2 if (T > 64 and layout == moe.LAYOUT_NK) else 2e-3
+    tol = 1e-2 if T > 64 else 2e-3
     err = np.max(np.abs(got - y_ref)) / np.max(np.abs(y_ref))
     assert err <= tol, err
     # per-token bound as well: one scale per token instead of one for the whole batch
