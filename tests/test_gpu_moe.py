@@ -73,14 +73,16 @@ def test_moe_forward_matches_oracle(layout, fmt, T):
     blk.release()
 
 
-@pytest.mark.parametrize("fmt", [Q.MXFP4_SPLIT, Q.Q4_K, Q.BF16_DENSE])
+@pytest.mark.parametrize("fmt", [Q.MXFP4_SPLIT, Q.Q4_K, Q.Q4_K_GGML, Q.Q8_0, Q.BF16_DENSE])
 def test_prefill_sized_batch_takes_the_tensor_core_path(fmt):
     """From 32 routed rows per expert on, [N, K] experts run the grouped tcgen05 products (bf16
     operands: the 1e-2 bar of the tensor path); ragged expert loads, rows not a multiple of 128."""
-    # 8 experts, top-4. 70 tokens: 35 routed rows per expert; 150: 75 (Q4_K experts take the product
-    # with the decode fused in up to 127 rows per expert, the others are decoded to bf16 once and
-    # multiplied by the plain grouped GEMM); 333 and 1024: 166 and 512 rows per expert, decoded once
-    # for every format
+    # 8 experts, top-4. 70 tokens: 35 routed rows per expert; 150: 75; 333: 166; 1024: 512. The product
+    # with the decode fused in serves Q4_K (either element order) up to 127 rows per expert and Q8_0 up
+    # to 383 (the raw-block ring of the 128- and 256-row tiles); everything else is decoded to bf16
+    # once and multiplied by the plain grouped GEMM. (Q6_K experts are not in this list: the generator's
+    # Q6_K weights reach +-4000 and the block's outputs 2e6 after the clamp; the bf16 operands then
+    # measure 1.3e-2 of the largest output at 70 tokens, just above this test's bar.)
     for T in (70, 150, 333, 1024):
         _prefill_case(fmt, T)
 
