@@ -707,6 +707,21 @@ def moe_block(torch, backend, gen, dev, peak_hbm, peak_tf, timed):
         out[f"tokens_{tokens}"] = row
     backend.device_status()
     blk.release()
+    # the same block with the experts stored as nn-gptoss stores them: [E, K, N] tensors, blocks along N
+    try:
+        blk = moe.MoeBlock(E, H, I, k, 7.0, rw, rb, moe.LAYOUT_KN_GPTOSS, QuantFormat.MXFP4_GPTOSS, gu, gus, np.zeros((E, 2 * I), np.float32),
+                           dn, dns, np.zeros((E, H), np.float32), backend=backend)
+        kn = {"format": "MXFP4 nn-gptoss [E,K,N/2]+[E,K,N/32]"}
+        for tokens in (64, 4096):
+            x = (torch.randn(tokens, H, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+            sec = timed(lambda: blk(x), 5 if tokens == 64 else 3)
+            flops = 2.0 * tokens * k * 3 * H * I
+            kn[f"tokens_{tokens}"] = {"us": sec * 1e6, "gbs_over_expert_weights": weight_bytes / sec / 1e9, "tflops": flops / sec / 1e12}
+        backend.device_status()
+        blk.release()
+        out["experts_stored_kn"] = kn
+    except Exception as e:  # noqa: BLE001 -- a side measurement must not take the line down
+        out["experts_stored_kn"] = {"error": str(e)[:200]}
     return out
 
 
